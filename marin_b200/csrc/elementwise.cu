@@ -1,0 +1,181 @@
+// Embedding, RMSNorm, fused q/k-norm + rotation + paged cache write, SwiGLU, row gather, arg-max.
+// Each kernel takes its sizes as arguments; sums, norms and angles are float32 whatever the
+// activation dtype.  The formulas are the reference's (crates/cuda/src/kernels.cu:43-67,147-175,
+// crates/cuda/src/kv_format.cu:48-72); the fusion and the page layout are this engine's own.
+#include "common.cuh"
+
+// ---- embedding: out[t, :] = float(table[ids[t], :]) -------------------------------------------------
+template <typename TW>
+__global__ void embed_kernel(const int* __restrict__ ids, const TW* __restrict__ table, float* __restrict__ out, int h) {
+    const int t = blockIdx.x;
+    const TW* row = table + (size_t)ids[t] * h;
+    float* dst = out + (size_t)t * h;
+    for (int i = threadIdx.x; i < h; i += blockDim.x) dst[i] = to_f32(row[i]);
+}
+
+MB_API int mb_embed(const int* ids, const void* table, int table_dtype, float* out, int tokens, int h, cudaStream_t s) {
+    if (tokens <= 0) return 0;
+    if (table_dtype == MB_F32) embed_kernel<float><<<tokens, 256, 0, s>>>(ids, (const float*)table, out, h);
+    else if (table_dtype == MB_BF16) embed_kernel<bf16><<<tokens, 256, 0, s>>>(ids, (const bf16*)table, out, h);
+    else return MB_ERR_BAD_DTYPE;
+    return mb_last_error();
+}
+
+// ---- RMSNorm over rows of a float32 matrix ---------------------------------------------------------
+template <typename TO>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, float eps, int unit_offset,
+                               TO* __restrict__ out, int n) {
+    __shared__ float scratch[32];
+    const float* row = x + (size_t)blockIdx.x * n;
+    TO* dst = out + (size_t)blockIdx.x * n;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) { float v = row[i]; ss += v * v; }
+    ss = block_sum(ss, scratch);
+    const float scale = 1.0f / sqrtf(ss / (float)n + eps);
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const float wi = unit_offset ? 1.0f + w[i] : w[i];
+        dst[i] = from_f32<TO>(row[i] * scale * wi);
+    }
+}
+
+MB_API int mb_rmsnorm(const float* x, const float* w, float eps, int unit_offset, void* out, int out_dtype,
+                      int rows, int n, cudaStream_t s) {
+    if (rows <= 0) return 0;
+    const int threads = n >= 1024 ? 256 : 128;
+    if (out_dtype == MB_F32) rmsnorm_kernel<float><<<rows, threads, 0, s>>>(x, w, eps, unit_offset, (float*)out, n);
+    else if (out_dtype == MB_BF16) rmsnorm_kernel<bf16><<<rows, threads, 0, s>>>(x, w, eps, unit_offset, (bf16*)out, n);
+    else return MB_ERR_BAD_DTYPE;
+    return mb_last_error();
+}
+
+// ---- per-head RMSNorm of q and k, rotation of q and k, k and v into their pages ---------------------
+// One warp per (token, head).  Heads 0..H-1 are queries, H..H+K-1 keys, H+K..H+2K-1 values, as they
+// lie in a row of the fused projection.  Page layout: [page][kv_head][offset in page][d].
+template <typename T>
+__global__ void qk_norm_rope_write_kernel(const T* __restrict__ qkv, int row_stride, T* __restrict__ q_out,
+                                          const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
+                                          const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                                          int rotary_dim, int interleaved, const int* __restrict__ slot_mapping,
+                                          T* __restrict__ k_cache, T* __restrict__ v_cache, int H, int K, int d,
+                                          int page_size, int heads_total) {
+    extern __shared__ float smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x;
+    const int head = blockIdx.y * (blockDim.x >> 5) + warp;
+    if (head >= heads_total) return;
+    float* buf = smem + (size_t)warp * d;
+    const T* src = qkv + (size_t)t * row_stride + (size_t)head * d;
+    const bool is_q = head < H, is_k = !is_q && head < H + K;
+    float ss = 0.0f;
+    for (int i = lane; i < d; i += 32) { float v = to_f32(src[i]); buf[i] = v; ss += v * v; }
+    const float* w = is_q ? q_w : (is_k ? k_w : nullptr);
+    if (w != nullptr) {
+        ss = warp_sum(ss);
+        const float scale = 1.0f / sqrtf(ss / (float)d + eps);
+        __syncwarp();
+        for (int i = lane; i < d; i += 32) buf[i] = buf[i] * scale * w[i];
+    }
+    __syncwarp();
+    if ((is_q || is_k) && inv_freq != nullptr) {
+        const float pos = (float)positions[t];
+        const int half = rotary_dim >> 1;
+        for (int i = lane; i < half; i += 32) {
+            const int ia = interleaved ? 2 * i : i, ib = interleaved ? 2 * i + 1 : i + half;
+            float sn, cs;
+            sincosf(pos * inv_freq[i], &sn, &cs);
+            const float a = buf[ia], b = buf[ib];
+            buf[ia] = a * cs - b * sn;
+            buf[ib] = b * cs + a * sn;
+        }
+        __syncwarp();
+    }
+    T* dst;
+    if (is_q) {
+        dst = q_out + ((size_t)t * H + head) * d;
+    } else {
+        const int slot = slot_mapping[t];
+        if (slot < 0) return;
+        const int kh = is_k ? head - H : head - H - K;
+        const size_t page = (size_t)(slot / page_size), off = (size_t)(slot % page_size);
+        dst = (is_k ? k_cache : v_cache) + ((page * K + kh) * page_size + off) * d;
+    }
+    for (int i = lane; i < d; i += 32) dst[i] = from_f32<T>(buf[i]);
+}
+
+MB_API int mb_qk_norm_rope_write(const void* qkv, int dtype, void* q_out, const float* q_w, const float* k_w, float eps,
+                                 const int* positions, const float* inv_freq, int rotary_dim, int interleaved,
+                                 const int* slot_mapping, void* k_cache, void* v_cache, int tokens, int H, int K, int d,
+                                 int page_size, int write_kv, cudaStream_t s) {
+    if (tokens <= 0) return 0;
+    if (d <= 0 || rotary_dim > d || (rotary_dim & 1)) return MB_ERR_BAD_SIZE;
+    const int heads_total = write_kv ? H + 2 * K : H;
+    const int row_stride = heads_total * d;
+    const int warps = 4;
+    dim3 grid(tokens, (heads_total + warps - 1) / warps);
+    const size_t smem = (size_t)warps * d * sizeof(float);
+    if (smem > 48 * 1024) return MB_ERR_BAD_SIZE;
+    if (dtype == MB_F32)
+        qk_norm_rope_write_kernel<float><<<grid, warps * 32, smem, s>>>(
+            (const float*)qkv, row_stride, (float*)q_out, q_w, k_w, eps, positions, inv_freq, rotary_dim, interleaved,
+            slot_mapping, (float*)k_cache, (float*)v_cache, H, K, d, page_size, heads_total);
+    else if (dtype == MB_BF16)
+        qk_norm_rope_write_kernel<bf16><<<grid, warps * 32, smem, s>>>(
+            (const bf16*)qkv, row_stride, (bf16*)q_out, q_w, k_w, eps, positions, inv_freq, rotary_dim, interleaved,
+            slot_mapping, (bf16*)k_cache, (bf16*)v_cache, H, K, d, page_size, heads_total);
+    else return MB_ERR_BAD_DTYPE;
+    return mb_last_error();
+}
+
+// ---- SwiGLU: out[t, i] = g / (1 + exp(-g)) * u with g = gu[t, i], u = gu[t, I + i] -------------------
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total) {
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; idx < total; idx += stride) {
+        const size_t t = idx / I, i = idx % I;
+        const float g = to_f32(gu[t * 2 * I + i]), u = to_f32(gu[t * 2 * I + I + i]);
+        out[idx] = from_f32<T>(g / (1.0f + expf(-g)) * u);
+    }
+}
+
+MB_API int mb_swiglu(const void* gate_up, void* out, int dtype, int tokens, int I, cudaStream_t s) {
+    const size_t total = (size_t)tokens * I;
+    if (total == 0) return 0;
+    const int threads = 256;
+    const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+    if (dtype == MB_F32) swiglu_kernel<float><<<blocks, threads, 0, s>>>((const float*)gate_up, (float*)out, I, total);
+    else if (dtype == MB_BF16) swiglu_kernel<bf16><<<blocks, threads, 0, s>>>((const bf16*)gate_up, (bf16*)out, I, total);
+    else return MB_ERR_BAD_DTYPE;
+    return mb_last_error();
+}
+
+// ---- rows of the residual stream whose logits are wanted ----------------------------------------------
+__global__ void gather_rows_kernel(const float* __restrict__ src, const int* __restrict__ rows, float* __restrict__ out, int h) {
+    const float* row = src + (size_t)rows[blockIdx.x] * h;
+    float* dst = out + (size_t)blockIdx.x * h;
+    for (int i = threadIdx.x; i < h; i += blockDim.x) dst[i] = row[i];
+}
+
+MB_API int mb_gather_rows(const float* src, const int* rows, float* out, int count, int h, cudaStream_t s) {
+    if (count <= 0) return 0;
+    gather_rows_kernel<<<count, 256, 0, s>>>(src, rows, out, h);
+    return mb_last_error();
+}
+
+// ---- y += x (float32 residual, x in the activation dtype) ---------------------------------------------
+template <typename T>
+__global__ void add_into_kernel(float* __restrict__ y, const T* __restrict__ x, size_t total) {
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (; idx < total; idx += stride) y[idx] += to_f32(x[idx]);
+}
+
+MB_API int mb_add_into(float* y, const void* x, int dtype, size_t total, cudaStream_t s) {
+    if (total == 0) return 0;
+    const int threads = 256;
+    const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+    if (dtype == MB_F32) add_into_kernel<float><<<blocks, threads, 0, s>>>(y, (const float*)x, total);
+    else if (dtype == MB_BF16) add_into_kernel<bf16><<<blocks, threads, 0, s>>>(y, (const bf16*)x, total);
+    else return MB_ERR_BAD_DTYPE;
+    return mb_last_error();
+}

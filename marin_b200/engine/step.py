@@ -1,0 +1,180 @@
+"""The step function: one batch of (request, its next tokens) through the model, from the cache.
+
+A step takes, for each participating request, its next tokens — a portion of a prompt of
+any length, or a single decoded token — and the places among them whose logits are wanted.
+All entries run as one flat batch; only the tokens given are computed, everything earlier
+comes from the cache.  Lengths are committed after the model ran, so a step that fails
+leaves the cache as it was (the reference commits the same way,
+crates/model/src/qwen3/gpu.rs:374-375).  The reference's forward takes one sequence per
+pass (crates/runtime/src/lib.rs:67-100); the mixed batch is this engine's own design.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, Hashable, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache.manager import DROPPED, CacheManager, PagedView, StateView
+from ..cache.pages import OutOfPages
+from ..models.model import Model
+from ..parts.base import Runtime
+from .context import Span, StepContext, Workspace
+
+
+class StepError(ValueError):
+    """A step that cannot run as asked: unknown request, bad token id, context full."""
+
+
+@dataclass
+class StepEntry:
+    req_id: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = field(default_factory=list)
+
+
+class CacheViews:
+    """Hands each schedule entry its view of the cache for the current step."""
+
+    def __init__(self, cache: CacheManager):
+        self.cache = cache
+
+    def view(self, index: int, ctx: StepContext):
+        cache = self.cache
+        owner_index = cache.cache_of[index] if cache.cache_of[index] is not None else index
+        if owner_index in cache.place:
+            g, j = cache.place[owner_index]
+            group = cache.groups[g]
+            return PagedView(group.k[j], group.v[j], ctx.group_block_tables[g], ctx.group_slot_mappings[g],
+                             cache.page_size, owner=owner_index == index)
+        if owner_index in cache.state:
+            return StateView(cache.state[owner_index], ctx.state_slots, owner=owner_index == index)
+        return None
+
+
+class Runner:
+    """Owns the model, the cache manager and the workspace; ``step`` is the only way tokens run."""
+
+    def __init__(self, model: Model, cache: CacheManager, rt: Runtime, max_seq_len: int):
+        self.model, self.cache, self.rt = model, cache, rt
+        self.max_seq_len = int(max_seq_len)
+        self.max_pages_per_seq = -(-self.max_seq_len // cache.page_size)
+        self.workspace = Workspace(rt.device)
+        self.views = CacheViews(cache)
+        self.vocab = model.spec.vocab_size
+        self.steps_run = 0
+
+    # ---- requests ----------------------------------------------------------------------------------
+    def begin(self, req_id: Hashable) -> None:
+        self.cache.admit(req_id)
+
+    def end(self, req_id: Hashable) -> None:
+        self.cache.release(req_id)
+
+    def length(self, req_id: Hashable) -> int:
+        return self.cache.length(req_id)
+
+    # ---- the step ------------------------------------------------------------------------------------
+    def _validate(self, entries: Sequence[StepEntry]) -> None:
+        if not entries:
+            raise StepError("a step needs at least one entry")
+        seen = set()
+        for e in entries:
+            if e.req_id in seen:
+                raise StepError(f"request {e.req_id!r} appears twice in one step")
+            seen.add(e.req_id)
+            if e.req_id not in self.cache.requests:
+                raise StepError(f"request {e.req_id!r} is not live")
+            n = len(e.tokens)
+            if n == 0:
+                raise StepError(f"request {e.req_id!r} brings no tokens")
+            for t in e.tokens:
+                if not 0 <= int(t) < self.vocab:
+                    raise StepError(f"request {e.req_id!r}: token id {t} is outside the vocabulary of {self.vocab}")
+            for w in e.want:
+                if not 0 <= int(w) < n:
+                    raise StepError(f"request {e.req_id!r}: wanted place {w} is outside its {n} tokens")
+            new_len = self.cache.length(e.req_id) + n
+            if new_len > self.max_seq_len:
+                raise StepError(f"request {e.req_id!r}: context full ({new_len} positions needed, capacity {self.max_seq_len})")
+
+    def build_context(self, entries: Sequence[StepEntry], pad_requests: int = 0) -> StepContext:
+        """Flattens the entries (single tokens first) into the arrays the kernels read, and copies
+        them to the device in one transfer."""
+        cache, page = self.cache, self.cache.page_size
+        order = sorted(range(len(entries)), key=lambda i: (len(entries[i].tokens) != 1, i))
+        num_decode = sum(1 for e in entries if len(e.tokens) == 1)
+        R = len(entries)
+        T = sum(len(e.tokens) for e in entries)
+        maxb = self.max_pages_per_seq
+        G = len(cache.groups)
+        tok = np.zeros(T, np.int32)
+        pos = np.zeros(T, np.int32)
+        req = np.zeros(T, np.int32)
+        cu = np.zeros(R + 1, np.int32)
+        lens = np.zeros(R, np.int32)
+        slots = np.zeros(R, np.int32)
+        tables = np.zeros((G, R, maxb), np.int32)
+        slot_maps = np.zeros((G, T), np.int32)
+        spans: List[Span] = []
+        flat_start: Dict[int, int] = {}
+        at = 0
+        for row, i in enumerate(order):
+            e = entries[i]
+            rc = cache.requests[e.req_id]
+            n = len(e.tokens)
+            flat_start[i] = at
+            tok[at:at + n] = np.asarray(e.tokens, np.int32)
+            p = np.arange(rc.length, rc.length + n, dtype=np.int32)
+            pos[at:at + n] = p
+            req[at:at + n] = row
+            cu[row + 1] = at + n
+            lens[row] = rc.length + n
+            slots[row] = rc.slot
+            for g in range(G):
+                ids = np.asarray(rc.pages[g], np.int32)
+                tables[g, row, :len(ids)] = np.maximum(ids, 0)
+                slot_maps[g, at:at + n] = ids[p // page] * page + (p % page)
+            spans.append(Span(row, e.req_id, at, n, rc.length, rc.slot))
+            at += n
+        rows: List[int] = []
+        for i, e in enumerate(entries):
+            rows.extend(flat_start[i] + int(w) for w in e.want)
+        logit_rows = np.asarray(rows, np.int32)
+        parts = [tok, pos, req, cu, lens, slots, logit_rows, tables.reshape(-1), slot_maps.reshape(-1)]
+        packed = np.concatenate(parts) if parts else np.zeros(0, np.int32)
+        host = torch.from_numpy(packed)
+        if self.rt.device.type == "cuda":
+            host = host.pin_memory()
+        dev = host.to(self.rt.device, non_blocking=True)
+        views, at = [], 0
+        for p in parts:
+            views.append(dev[at:at + p.size])
+            at += p.size
+        d_tok, d_pos, d_req, d_cu, d_lens, d_slots, d_rows, d_tables, d_maps = views
+        return StepContext(
+            num_tokens=T, num_requests=R, num_decode=num_decode, num_logit_rows=len(rows),
+            max_query_len=max(len(e.tokens) for e in entries), max_seq_len=int(lens.max()),
+            token_ids=d_tok, positions=d_pos, req_index=d_req, cu_tokens=d_cu, seq_lens=d_lens,
+            state_slots=d_slots, logit_rows=d_rows,
+            group_block_tables=[d_tables.view(G, R, maxb)[g] for g in range(G)] if G else [],
+            group_slot_mappings=[d_maps.view(G, T)[g] for g in range(G)] if G else [],
+            spans=spans, workspace=self.workspace,
+        )
+
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Runs the entries as one batch; returns float32 logits ``[wanted, vocab]`` on the device,
+        in the order of the entries and of each entry's ``want``."""
+        self._validate(entries)
+        wanted = [(e.req_id, self.cache.length(e.req_id) + len(e.tokens)) for e in entries]
+        if not self.cache.can_reserve(wanted):
+            raise OutOfPages(f"the step needs more pages than are free ({self.cache.free_pages()} free per group)")
+        for req_id, new_len in wanted:
+            self.cache.reserve(req_id, new_len)
+        ctx = self.build_context(entries)
+        logits = self.model.forward(ctx, self.views)
+        for req_id, new_len in wanted:
+            self.cache.commit(req_id, new_len)
+        self.steps_run += 1
+        return logits

@@ -1,0 +1,146 @@
+"""Compiles the CUDA sources of ``csrc/`` for sm_100a into shared libraries, at first use.
+
+Each library is built with ``nvcc`` directly (no framework headers, so a file compiles in
+seconds) into ``marin_b200/csrc/_build/`` beside the sources, named by a hash of its sources
+and flags, and loaded with ``ctypes``.  The reference compiles its kernels at start-up too
+(NVRTC, crates/cuda/src/gpu.rs:159-164).  If the package folder is read-only the build goes to
+a per-user temporary folder.  A line is printed when a compile starts and every few seconds
+while it runs, so that a first call does not look hung.
+"""
+from __future__ import annotations
+
+import ctypes
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from typing import Dict, List, Optional, Sequence
+
+CSRC = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "csrc")
+ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
+BASE_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
+
+_loaded: Dict[str, ctypes.CDLL] = {}
+_lock = threading.Lock()
+
+
+class KernelBuildError(RuntimeError):
+    pass
+
+
+def _nvcc() -> str:
+    for cand in (os.environ.get("MARIN_B200_NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and os.path.exists(cand):
+            return cand
+    raise KernelBuildError("nvcc was not found (looked at $MARIN_B200_NVCC, PATH and /usr/local/cuda/bin); "
+                           "the CUDA kernels of marin_b200 cannot be built and there is no other path")
+
+
+def _build_dir() -> str:
+    override = os.environ.get("MARIN_B200_BUILD_DIR")
+    candidates = [override] if override else []
+    candidates.append(os.path.join(CSRC, "_build"))
+    candidates.append(os.path.join(tempfile.gettempdir(), f"marin_b200_build_{os.getuid()}"))
+    for path in candidates:
+        try:
+            os.makedirs(path, exist_ok=True)
+            probe = os.path.join(path, f".w{os.getpid()}")
+            with open(probe, "w"):
+                pass
+            os.remove(probe)
+            return path
+        except OSError:
+            continue
+    raise KernelBuildError(f"no writable build folder among {candidates}")
+
+
+def _digest(sources: Sequence[str], flags: Sequence[str]) -> str:
+    h = hashlib.sha256()
+    for name in sorted(os.listdir(CSRC)):
+        if name.endswith((".cuh", ".h")):
+            with open(os.path.join(CSRC, name), "rb") as fh:
+                h.update(name.encode() + b"\0" + fh.read())
+    for src in sources:
+        with open(os.path.join(CSRC, src), "rb") as fh:
+            h.update(src.encode() + b"\0" + fh.read())
+    h.update(" ".join(flags).encode())
+    return h.hexdigest()[:16]
+
+
+def library_path(name: str, sources: Sequence[str], defines: Sequence[str] = ()) -> str:
+    flags = ARCH_FLAGS + BASE_FLAGS + [f"-D{d}" for d in defines]
+    return os.path.join(_build_dir(), f"{name}-{_digest(sources, flags)}.so")
+
+
+def build(name: str, sources: Sequence[str], defines: Sequence[str] = (), verbose: bool = True) -> str:
+    """Compiles ``sources`` (names inside csrc/) into one shared library unless it is already built."""
+    flags = ARCH_FLAGS + BASE_FLAGS + [f"-D{d}" for d in defines]
+    out = os.path.join(_build_dir(), f"{name}-{_digest(sources, flags)}.so")
+    if os.path.exists(out):
+        return out
+    tmp = f"{out}.{os.getpid()}.tmp"
+    cmd = [_nvcc()] + flags + ["-I", CSRC, "-o", tmp] + [os.path.join(CSRC, s) for s in sources]
+    if verbose:
+        print(f"[marin_b200] compiling {name} for sm_100a ({', '.join(sources)}) ...", file=sys.stderr, flush=True)
+    started = time.time()
+    proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    while True:
+        try:
+            output, _ = proc.communicate(timeout=10)
+            break
+        except subprocess.TimeoutExpired:
+            if verbose:
+                print(f"[marin_b200] ... still compiling {name} ({time.time() - started:.0f} s)", file=sys.stderr, flush=True)
+    if proc.returncode != 0:
+        if os.path.exists(tmp):
+            os.remove(tmp)
+        raise KernelBuildError(f"nvcc failed for {name}:\n{' '.join(cmd)}\n{output}")
+    os.replace(tmp, out)
+    if verbose:
+        print(f"[marin_b200] built {os.path.basename(out)} in {time.time() - started:.1f} s", file=sys.stderr, flush=True)
+    return out
+
+
+def load(name: str, sources: Sequence[str], defines: Sequence[str] = ()) -> ctypes.CDLL:
+    """The library, built if need be and loaded once per process."""
+    key = name + "|" + "|".join(defines)
+    with _lock:
+        lib = _loaded.get(key)
+        if lib is None:
+            lib = ctypes.CDLL(build(name, sources, defines))
+            _loaded[key] = lib
+        return lib
+
+
+#: every library of the package: name → sources.  ``build_all`` compiles them all.
+LIBRARIES: Dict[str, List[str]] = {
+    "mb_elementwise": ["elementwise.cu"],
+    "mb_gemm_simple": ["gemm_simple.cu"],
+    "mb_attention_simple": ["attention_simple.cu"],
+    "mb_sampling": ["sampling.cu"],
+}
+
+
+def build_all(verbose: bool = True) -> List[str]:
+    """Compiles every library (in parallel).  Used by the build check and before timing."""
+    results: Dict[str, object] = {}
+
+    def work(n: str) -> None:
+        try:
+            results[n] = build(n, LIBRARIES[n], verbose=verbose)
+        except Exception as err:  # noqa: BLE001 - reported below
+            results[n] = err
+
+    threads = [threading.Thread(target=work, args=(n,)) for n in LIBRARIES]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    errors = [r for r in results.values() if isinstance(r, Exception)]
+    if errors:
+        raise errors[0]
+    return [str(results[n]) for n in LIBRARIES]

@@ -1,0 +1,144 @@
+"""The kernels as Python functions over torch CUDA tensors.
+
+Every function checks shapes and dtypes on the host, then launches hand-written CUDA on the
+current stream through ``ctypes``; results land in the ``out`` argument.  There is no other
+implementation behind these names: on a machine without CUDA, or if a library cannot be built,
+the call raises.  (The reference funnels its launches through checked wrappers the same way,
+crates/cuda/src/ops.rs:53-236.)
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import build
+
+_c_int, _c_float, _c_void_p, _c_size_t = ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_size_t
+
+F32, BF16 = 0, 1
+_DTYPE_CODE = {torch.float32: F32, torch.bfloat16: BF16}
+
+_ERRORS = {-2: "unsupported dtype combination", -3: "unsupported size", -4: "a device-side wait gave up"}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _code(t: torch.Tensor) -> int:
+    try:
+        return _DTYPE_CODE[t.dtype]
+    except KeyError:
+        raise KernelError(f"dtype {t.dtype} is not supported by the kernels (float32 or bfloat16)") from None
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return _c_void_p(t.data_ptr()) if t is not None else _c_void_p(0)
+
+
+def _stream():
+    return _c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need_cuda(*tensors: torch.Tensor) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("marin_b200 kernels run on CUDA tensors only; there is no CPU path")
+        if t is not None and not t.is_contiguous():
+            raise KernelError("marin_b200 kernels need contiguous tensors")
+
+
+def _check(rc: int, what: str) -> None:
+    if rc == 0:
+        return
+    if rc in _ERRORS:
+        raise KernelError(f"{what}: {_ERRORS[rc]}")
+    raise KernelError(f"{what}: CUDA error {rc} ({torch.cuda.cudart().cudaGetErrorString(rc) if hasattr(torch.cuda.cudart(), 'cudaGetErrorString') else ''})")
+
+
+def _lib(name: str):
+    return build.load(name, build.LIBRARIES[name])
+
+
+def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> None:
+    _need_cuda(ids, table, out)
+    T, h = out.shape
+    assert ids.dtype == torch.int32 and ids.numel() == T and table.shape[1] == h and out.dtype == torch.float32
+    _check(_lib("mb_elementwise").mb_embed(_ptr(ids), _ptr(table), _code(table), _ptr(out), _c_int(T), _c_int(h), _stream()), "embed")
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, unit_offset: bool = False) -> None:
+    _need_cuda(x, weight, out)
+    rows, n = x.shape
+    assert x.dtype == torch.float32 and weight.dtype == torch.float32 and weight.numel() == n and out.shape == x.shape
+    _check(_lib("mb_elementwise").mb_rmsnorm(_ptr(x), _ptr(weight), _c_float(eps), _c_int(int(unit_offset)), _ptr(out),
+                                            _code(out), _c_int(rows), _c_int(n), _stream()), "rmsnorm")
+
+
+def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
+    """``out[t, n] (+)= sum_k x[t, k] * w[n, k]``."""
+    _need_cuda(x, w, out)
+    T, K = x.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and tuple(out.shape) == (T, N), (x.shape, w.shape, out.shape)
+    _check(_lib("mb_gemm_simple").mb_gemm_simple(_ptr(x), _code(x), _ptr(w), _code(w), _ptr(out), _code(out), _c_int(T),
+                                                _c_int(N), _c_int(K), _c_int(int(accumulate)), _stream()), "gemm")
+
+
+def qk_norm_rope_write(qkv, q_out, q_weight, k_weight, eps, positions, inv_freq, rotary_dim, interleaved,
+                       slot_mapping, k_cache, v_cache, H, K, d, write_kv=True) -> None:
+    _need_cuda(qkv, q_out, q_weight, k_weight, positions, inv_freq, slot_mapping, k_cache, v_cache)
+    T = qkv.shape[0]
+    heads_total = H + 2 * K if write_kv else H
+    assert qkv.shape[1] == heads_total * d and tuple(q_out.shape) == (T, H * d) and q_out.dtype == qkv.dtype
+    assert k_cache.dtype == qkv.dtype and v_cache.dtype == qkv.dtype
+    assert k_cache.shape[1] == K and k_cache.shape[3] == d
+    page_size = k_cache.shape[2]
+    _check(_lib("mb_elementwise").mb_qk_norm_rope_write(
+        _ptr(qkv), _code(qkv), _ptr(q_out), _ptr(q_weight), _ptr(k_weight), _c_float(eps), _ptr(positions),
+        _ptr(inv_freq), _c_int(rotary_dim if inv_freq is not None else 0), _c_int(int(interleaved)), _ptr(slot_mapping),
+        _ptr(k_cache), _ptr(v_cache), _c_int(T), _c_int(H), _c_int(K), _c_int(d), _c_int(page_size),
+        _c_int(int(write_kv)), _stream()), "qk_norm_rope_write")
+
+
+def attention(q, k_cache, v_cache, out, ctx, block_table, H, K, d, scale, window=0) -> None:
+    """Causal attention of the step's tokens over the paged cache (their own keys included)."""
+    _need_cuda(q, k_cache, v_cache, out, block_table)
+    T = q.shape[0]
+    page_size = k_cache.shape[2]
+    assert tuple(q.shape) == (T, H * d) and out.shape == q.shape and k_cache.dtype == q.dtype
+    _check(_lib("mb_attention_simple").mb_attention_simple(
+        _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _code(q), _ptr(block_table), _c_int(block_table.shape[1]),
+        _ptr(ctx.req_index), _ptr(ctx.positions), _c_int(T), _c_int(H), _c_int(K), _c_int(d), _c_int(page_size),
+        _c_float(scale), _c_int(window), _stream()), "attention")
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    _need_cuda(gate_up, out)
+    T, I = out.shape
+    assert gate_up.shape == (T, 2 * I) and gate_up.dtype == out.dtype
+    _check(_lib("mb_elementwise").mb_swiglu(_ptr(gate_up), _ptr(out), _code(out), _c_int(T), _c_int(I), _stream()), "swiglu")
+
+
+def gather_rows(src: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:
+    _need_cuda(src, rows, out)
+    W, h = out.shape
+    assert src.dtype == torch.float32 and out.dtype == torch.float32 and rows.dtype == torch.int32 and rows.numel() == W
+    _check(_lib("mb_elementwise").mb_gather_rows(_ptr(src), _ptr(rows), _ptr(out), _c_int(W), _c_int(h), _stream()), "gather_rows")
+
+
+def add_into(y: torch.Tensor, x: torch.Tensor) -> None:
+    """``y += x`` with ``y`` float32 (the residual stream)."""
+    _need_cuda(y, x)
+    assert y.dtype == torch.float32 and y.numel() == x.numel()
+    _check(_lib("mb_elementwise").mb_add_into(_ptr(y), _ptr(x), _code(x), _c_size_t(y.numel()), _stream()), "add_into")
+
+
+def argmax(logits: torch.Tensor, usable: int, out: torch.Tensor) -> None:
+    """``out[r]`` = id of the largest of the first ``usable`` logits of row ``r`` (lowest id among equals)."""
+    _need_cuda(logits, out)
+    rows, vocab = logits.shape
+    assert logits.dtype == torch.float32 and out.dtype == torch.int32 and out.numel() == rows
+    _check(_lib("mb_sampling").mb_argmax(_ptr(logits), _c_int(rows), _c_int(vocab), _c_int(usable), _ptr(out), _stream()), "argmax")

@@ -1,0 +1,74 @@
+"""A model assembled from a :class:`ModelSpec`: embedding, blocks run in schedule order,
+final norm and head.  It owns weights only; caches and batches come from outside."""
+from __future__ import annotations
+
+from typing import Dict, List
+
+import torch
+
+from ..kernels import ops
+from ..parts.base import Runtime
+from ..parts.registry import lookup
+from ..parts.spec import ModelSpec, TensorSpec
+
+
+class Model:
+    def __init__(self, spec: ModelSpec):
+        self.spec = spec
+        self.embedding = lookup("embedding", spec.embedding.kind)(**spec.embedding.params)
+        self.blocks = [lookup("block", layer.block)(layer) for layer in spec.layers]
+        self.final_norm = lookup("norm", spec.final_norm.kind)(**spec.final_norm.params)
+        self.head = lookup("head", spec.head.kind)(**spec.head.params)
+        for i, entry in enumerate(spec.schedule):
+            if not 0 <= entry.layer < len(self.blocks):
+                raise ValueError(f"schedule entry {i} names layer {entry.layer}, the model has {len(self.blocks)}")
+            if entry.cache_of is not None:
+                if not 0 <= entry.cache_of < i or spec.schedule[entry.cache_of].cache_of is not None:
+                    raise ValueError(f"schedule entry {i} must read the cache of an earlier entry that owns one")
+        self.rt: Runtime | None = None
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        specs = list(self.embedding.tensor_specs())
+        for block in self.blocks:
+            specs += block.tensor_specs()
+        specs += self.final_norm.tensor_specs()
+        specs += self.head.tensor_specs()
+        return specs
+
+    def cache_needs(self) -> List[object]:
+        """What each schedule entry keeps between steps (None for entries that read another's cache)."""
+        needs = []
+        for entry in self.spec.schedule:
+            need = self.blocks[entry.layer].mixer.cache_need()
+            needs.append(need if entry.cache_of is None else None)
+        return needs
+
+    def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
+        self.rt = rt
+        self.embedding.load(tensors, rt)
+        for block in self.blocks:
+            block.load(tensors, rt)
+        self.final_norm.load(tensors, rt)
+        self.head.load(tensors, rt)
+        if getattr(self.head, "tied", False):
+            self.head.tie(self.embedding.table)
+
+    def forward(self, ctx, caches) -> torch.Tensor:
+        """Runs the step's tokens through every schedule entry; returns float32 logits
+        ``[len(ctx.logit_rows), vocab]`` at the rows asked for."""
+        rt, ws = self.rt, ctx.workspace
+        T = ctx.num_tokens
+        hidden = ws.get("hidden", (T, self.spec.hidden_size), torch.float32)
+        self.embedding.forward(ctx.token_ids, hidden)
+        for i, entry in enumerate(self.spec.schedule):
+            self.blocks[entry.layer].forward(hidden, ctx, caches.view(i, ctx))
+        W = ctx.num_logit_rows
+        if W == 0:
+            return torch.empty(0, self.spec.vocab_size, device=rt.device, dtype=torch.float32)
+        rows = ws.get("logit_hidden", (W, self.spec.hidden_size), torch.float32)
+        ops.gather_rows(hidden, ctx.logit_rows, rows)
+        normed = ws.get("logit_normed", (W, self.spec.hidden_size), rt.dtype)
+        self.final_norm.forward(rows, normed)
+        logits = ws.get("logits", (W, self.spec.vocab_size), torch.float32)
+        self.head.forward(normed, logits)
+        return logits

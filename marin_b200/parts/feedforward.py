@@ -1,0 +1,54 @@
+"""Feed-forward parts.
+
+Interface: ``forward(x, ctx, residual)`` reads ``x`` ``[T, hidden]`` (activation dtype) and
+**adds** its output into ``residual`` (float32 ``[T, hidden]``).  A routed feed-forward
+(experts) has the same interface; what it routes on is its own business.
+"""
+from __future__ import annotations
+
+from typing import Dict, List
+
+import torch
+
+from ..kernels import ops
+from .base import Part, Runtime
+from .registry import register_feedforward
+from .spec import TensorSpec
+
+
+class FeedForward(Part):
+    def forward(self, x: torch.Tensor, ctx, residual: torch.Tensor) -> None:
+        raise NotImplementedError
+
+
+@register_feedforward("swiglu")
+class SwiGLU(FeedForward):
+    """``down( g / (1 + exp(-g)) * u )`` with ``g = x W_gate^T`` and ``u = x W_up^T``, no bias
+    (crates/model/src/qwen3/mlp.rs:22-37, crates/tensor/src/silu.rs:18)."""
+
+    def __init__(self, hidden: int, intermediate: int, name: str):
+        self.hidden, self.intermediate, self.name = int(hidden), int(intermediate), name
+        self.w_gate_up = self.w_down = None
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        n, h, i = self.name, self.hidden, self.intermediate
+        return [
+            TensorSpec(f"{n}.gate_proj.weight", (i, h)),
+            TensorSpec(f"{n}.up_proj.weight", (i, h)),
+            TensorSpec(f"{n}.down_proj.weight", (h, i)),
+        ]
+
+    def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
+        n = self.name
+        gate, up = tensors.pop(f"{n}.gate_proj.weight"), tensors.pop(f"{n}.up_proj.weight")
+        self.w_gate_up = rt.matrix(torch.cat([gate, up], dim=0))
+        self.w_down = rt.matrix(tensors.pop(f"{n}.down_proj.weight"))
+
+    def forward(self, x: torch.Tensor, ctx, residual: torch.Tensor) -> None:
+        T = x.shape[0]
+        ws = ctx.workspace
+        gate_up = ws.get("gate_up", (T, 2 * self.intermediate), x.dtype)
+        ops.gemm(x, self.w_gate_up, gate_up)
+        act = ws.get("ffn_act", (T, self.intermediate), x.dtype)
+        ops.swiglu(gate_up, act)
+        ops.gemm(act, self.w_down, residual, accumulate=True)

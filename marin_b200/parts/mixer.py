@@ -1,0 +1,128 @@
+"""Mixers: the parts that let tokens see other tokens.
+
+Interface every mixer has (a test can register its own):
+
+``cache_need()`` → what it keeps between steps: a :class:`PagedKV` (keys and values
+in pages, all of them or a window), a :class:`StateNeed` (fixed-size per-request
+state), or None.
+
+``forward(x, ctx, cache, residual)`` → reads ``x`` ``[T, hidden]`` (activation dtype),
+mixes over each request's tokens and what ``cache`` holds, and **adds** its output
+into ``residual`` (float32 ``[T, hidden]``).  ``ctx`` is the step's
+:class:`marin_b200.engine.context.StepContext`; ``cache`` is this run's view of the
+cache (:class:`marin_b200.cache.manager.PagedView` or ``StateView``).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from ..kernels import ops
+from .base import Part, Runtime
+from .registry import lookup, register_mixer
+from .spec import PartSpec, TensorSpec
+
+
+@dataclass(frozen=True)
+class PagedKV:
+    """Keys and values of ``kv_heads`` heads of ``head_dim`` per position, kept in pages.
+    ``window`` = how many of the latest positions are ever read again (None: all)."""
+
+    kv_heads: int
+    head_dim: int
+    window: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class StateNeed:
+    """A fixed-size state per request: ``shape`` elements of ``dtype``, zeroed when a request starts."""
+
+    shape: Tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+class Mixer(Part):
+    def cache_need(self):
+        return None
+
+    def forward(self, x: torch.Tensor, ctx, cache, residual: torch.Tensor) -> None:
+        raise NotImplementedError
+
+
+@register_mixer("gqa_attention")
+class GQAttention(Mixer):
+    """Causal grouped-query attention over the paged cache.
+
+    ``q,k,v = x W^T`` (no bias); optional per-head RMSNorm of q and k over ``head_dim``
+    *before* the rotation; keys (normed, rotated) and values (raw) go to the cache; query
+    head ``h`` reads kv head ``h // (heads // kv_heads)``; scores scaled by
+    ``1/sqrt(head_dim)``; softmax in float32 over positions ``0..=pos`` (or the last
+    ``window``); output through ``o_proj`` added to the residual
+    (crates/model/src/qwen3/layer.rs:59-88, crates/tensor/src/attention.rs:148-169).
+    """
+
+    def __init__(self, hidden: int, heads: int, kv_heads: int, head_dim: int, name: str,
+                 position: PartSpec, qk_norm: bool = True, norm_eps: float = 1e-6,
+                 window: Optional[int] = None, scale: Optional[float] = None):
+        self.hidden, self.heads, self.kv_heads, self.head_dim = int(hidden), int(heads), int(kv_heads), int(head_dim)
+        if self.heads % self.kv_heads != 0:
+            raise ValueError(f"{heads} heads cannot share {kv_heads} kv heads evenly")
+        self.name, self.qk_norm, self.norm_eps = name, bool(qk_norm), float(norm_eps)
+        self.window = int(window) if window else None
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.head_dim)
+        self.position = lookup("position", position.kind)(**position.params)
+        self.q_dim, self.kv_dim = self.heads * self.head_dim, self.kv_heads * self.head_dim
+        self.w_qkv = self.w_o = self.q_weight = self.k_weight = None
+
+    def cache_need(self):
+        return PagedKV(self.kv_heads, self.head_dim, self.window)
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        n, h, d = self.name, self.hidden, self.head_dim
+        specs = [
+            TensorSpec(f"{n}.q_proj.weight", (self.q_dim, h)),
+            TensorSpec(f"{n}.k_proj.weight", (self.kv_dim, h)),
+            TensorSpec(f"{n}.v_proj.weight", (self.kv_dim, h)),
+            TensorSpec(f"{n}.o_proj.weight", (h, self.q_dim)),
+        ]
+        if self.qk_norm:
+            specs += [TensorSpec(f"{n}.q_norm.weight", (d,), "norm"), TensorSpec(f"{n}.k_norm.weight", (d,), "norm")]
+        return specs
+
+    def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
+        n = self.name
+        q, k, v = (tensors.pop(f"{n}.{p}_proj.weight") for p in "qkv")
+        # One matrix for the three projections: one pass over x instead of three.
+        self.w_qkv = rt.matrix(torch.cat([q, k, v], dim=0))
+        self.w_o = rt.matrix(tensors.pop(f"{n}.o_proj.weight"))
+        if self.qk_norm:
+            self.q_weight = rt.f32(tensors.pop(f"{n}.q_norm.weight"))
+            self.k_weight = rt.f32(tensors.pop(f"{n}.k_norm.weight"))
+        self.position.load(tensors, rt)
+        self.rt = rt
+
+    def forward(self, x: torch.Tensor, ctx, cache, residual: torch.Tensor) -> None:
+        T = x.shape[0]
+        ws = ctx.workspace
+        writes = cache.owner
+        if writes:
+            qkv = ws.get("qkv", (T, self.q_dim + 2 * self.kv_dim), x.dtype)
+            ops.gemm(x, self.w_qkv, qkv)
+        else:
+            # This run reads another run's cache: only the queries are computed.
+            qkv = ws.get("qkv", (T, self.q_dim), x.dtype)
+            ops.gemm(x, self.w_qkv[: self.q_dim], qkv)
+        q = ws.get("q", (T, self.q_dim), x.dtype)
+        pos = self.position
+        ops.qk_norm_rope_write(
+            qkv, q, self.q_weight, self.k_weight, self.norm_eps, ctx.positions,
+            pos.inv_freq, pos.rotary_dim, pos.interleaved, cache.slot_mapping,
+            cache.k, cache.v, self.heads, self.kv_heads, self.head_dim, writes,
+        )
+        out = ws.get("attn_out", (T, self.q_dim), x.dtype)
+        ops.attention(q, cache.k, cache.v, out, ctx, cache.block_table, self.heads, self.kv_heads,
+                      self.head_dim, self.scale, self.window or 0)
+        ops.gemm(out, self.w_o, residual, accumulate=True)
