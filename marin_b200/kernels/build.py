@@ -40,22 +40,30 @@ def _nvcc() -> str:
                            "the CUDA kernels of marin_b200 cannot be built and there is no other path")
 
 
+_build_dir_cache: Optional[str] = None
+_dir_lock = threading.Lock()
+
+
 def _build_dir() -> str:
-    override = os.environ.get("MARIN_B200_BUILD_DIR")
-    candidates = [override] if override else []
-    candidates.append(os.path.join(CSRC, "_build"))
-    candidates.append(os.path.join(tempfile.gettempdir(), f"marin_b200_build_{os.getuid()}"))
-    for path in candidates:
-        try:
-            os.makedirs(path, exist_ok=True)
-            probe = os.path.join(path, f".w{os.getpid()}")
-            with open(probe, "w"):
-                pass
-            os.remove(probe)
-            return path
-        except OSError:
-            continue
-    raise KernelBuildError(f"no writable build folder among {candidates}")
+    global _build_dir_cache
+    with _dir_lock:
+        if _build_dir_cache is not None:
+            return _build_dir_cache
+        override = os.environ.get("MARIN_B200_BUILD_DIR")
+        candidates = [override] if override else []
+        candidates.append(os.path.join(CSRC, "_build"))
+        candidates.append(os.path.join(tempfile.gettempdir(), f"marin_b200_build_{os.getuid()}"))
+        for path in candidates:
+            try:
+                os.makedirs(path, exist_ok=True)
+                fd, probe = tempfile.mkstemp(prefix=".probe", dir=path)
+                os.close(fd)
+                os.remove(probe)
+                _build_dir_cache = path
+                return path
+            except OSError:
+                continue
+        raise KernelBuildError(f"no writable build folder among {candidates}")
 
 
 def _digest(sources: Sequence[str], flags: Sequence[str]) -> str:

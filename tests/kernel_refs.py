@@ -83,17 +83,17 @@ def attention(q, k_cache, v_cache, out, ctx, block_table, H, K, d, scale, window
     res = torch.zeros(T, H, d, dtype=torch.float32, device=q.device)
     positions = ctx.positions.tolist()
     reqs = ctx.req_index.tolist()
+    head_kv = torch.arange(H, device=q.device) // group
     for t in range(T):
         pos, r = positions[t], reqs[t]
         lo = max(0, pos - window + 1) if window > 0 else 0
         keys = torch.arange(lo, pos + 1, device=q.device)
         pages = block_table[r].long()[keys // page_size]
-        kk = k_cache[pages, :, keys % page_size, :].float()   # [n, K, d]
-        vv = v_cache[pages, :, keys % page_size, :].float()
-        for h in range(H):
-            s = (kk[:, h // group, :] @ qf[t, h]) * scale
-            p = torch.softmax(s, dim=0)
-            res[t, h] = p @ vv[:, h // group, :]
+        kk = k_cache[pages, :, keys % page_size, :].float()[:, head_kv, :]   # [n, H, d]
+        vv = v_cache[pages, :, keys % page_size, :].float()[:, head_kv, :]
+        s = torch.einsum("nhd,hd->hn", kk, qf[t]) * scale
+        p = torch.softmax(s, dim=-1)
+        res[t] = torch.einsum("hn,nhd->hd", p, vv)
     out.copy_(res.view(T, H * d).to(out.dtype))
 
 

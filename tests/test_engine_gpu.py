@@ -1,0 +1,184 @@
+"""The engine on the GPU against the plain implementation, in 32-bit and in bfloat16, under every
+way of cutting the work: each request alone and whole; most of it in one step and the last 32
+tokens one by one; portions of changing size down to two tokens; and mixed batches of up to four
+live requests with so few pages that they are used again.  Also long decoding, the first tokens of
+a sequence and greedy generation through the entry point.
+
+Tolerances (fixed; the reference's chunking gate is 1e-4 (1 + |x|), crates/model/tests/kv_append.rs:27-60):
+float32: |diff| <= 1e-4 + 1e-4 |ref|.  bfloat16 (activations rounded to 8 bits of mantissa between
+kernels, logits of standard deviation ~1): max |diff| <= 0.15 and mean |diff| <= 0.02 against the plain
+float32 result computed from the same bfloat16 weights.
+"""
+import random
+
+import pytest
+import torch
+
+import plain_qwen3 as plain
+from helpers import CONFIGS, PAGE, make_model_dir, mixed_schedule, portions, random_prompt, run_mixed, run_portions, run_whole
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = ["float32", "bfloat16"]
+LENGTHS = {"A": {"a": 37, "b": 9, "c": 120, "d": 1, "e": 64, "f": 40, "g": 33},
+           "B": {"a": 100, "b": 1, "c": 250, "d": 17, "e": 64, "f": 129, "g": 48},
+           "C": {"a": 50, "b": 180, "c": 16, "d": 97, "e": 2, "f": 33}}
+
+
+def close(got: torch.Tensor, want: torch.Tensor, dtype: str, what=""):
+    got, want = got.float().cpu(), want.float()
+    assert got.shape == want.shape, (got.shape, want.shape)
+    err = (got - want).abs()
+    if dtype == "float32":
+        bad = err > 1e-4 + 1e-4 * want.abs()
+        if bad.any():
+            first = int(torch.nonzero(bad.any(dim=1))[0])
+            raise AssertionError(f"{what}: first wrong position {first} of {got.shape[0]}, max err {err.max():.3e}")
+    else:
+        rowmax = err.max(dim=1).values
+        if err.max() > 0.15 or err.mean() > 0.02:
+            first = int(torch.nonzero(rowmax > 0.15)[0]) if (rowmax > 0.15).any() else -1
+            raise AssertionError(f"{what}: max err {err.max():.3e} mean {err.mean():.3e}, first position over the limit {first}")
+
+
+class Case:
+    def __init__(self, tmp, name, dtype):
+        from marin_b200.cache import CacheManager
+        from marin_b200.engine import Runner, load_model, parse_dtype
+        from marin_b200.parts import Runtime
+
+        raw = CONFIGS[name]
+        self.name, self.dtype, self.raw = name, dtype, raw
+        self.dir = make_model_dir(str(tmp / f"{name}-{dtype}"), raw, seed=11, dtype=parse_dtype(dtype), matrix_std=0.1)
+        self.cfg, self.w = plain.read_config(self.dir), plain.read_weights(self.dir)
+        rng = random.Random(5)
+        self.tokens = {rid: random_prompt(rng, raw["vocab_size"], n) for rid, n in LENGTHS[name].items()}
+        self.want = {rid: plain.forward(self.cfg, self.w, t) for rid, t in self.tokens.items()}
+        self.rt = Runtime(torch.device("cuda:0"), parse_dtype(dtype))
+        self.config, self.model = load_model(self.dir, self.rt)
+        self.page = PAGE[name]
+
+    def runner(self, num_pages, max_requests=4):
+        from marin_b200.cache import CacheManager
+        from marin_b200.engine import Runner
+
+        cache = CacheManager(self.model.cache_needs(), [e.cache_of for e in self.model.spec.schedule], self.page,
+                             num_pages, max_requests)
+        cache.allocate(self.rt.device, self.rt.dtype)
+        return Runner(self.model, cache, self.rt, self.config.max_position_embeddings)
+
+
+@pytest.fixture(scope="module", params=[(n, d) for n in "ABC" for d in DTYPES], ids=lambda p: f"{p[0]}-{p[1]}")
+def case(request, tmp_path_factory):
+    return Case(tmp_path_factory.mktemp("models"), *request.param)
+
+
+def test_each_request_alone_and_whole(case):
+    runner = case.runner(num_pages=-(-max(LENGTHS[case.name].values()) // case.page))
+    for rid, toks in case.tokens.items():
+        close(run_whole(runner, rid, toks), case.want[rid], case.dtype, f"whole {rid}")
+    runner.cache.check()
+
+
+def test_most_in_one_step_then_the_last_32_one_by_one(case):
+    runner = case.runner(num_pages=-(-max(LENGTHS[case.name].values()) // case.page))
+    for rid, toks in case.tokens.items():
+        n = len(toks)
+        tail = min(32, n - 1)
+        sizes = ([n - tail] if n - tail else []) + [1] * tail
+        close(run_portions(runner, rid, toks, sizes), case.want[rid], case.dtype, f"decode tail {rid}")
+
+
+def test_portions_of_changing_size(case):
+    runner = case.runner(num_pages=-(-max(LENGTHS[case.name].values()) // case.page))
+    for k, (rid, toks) in enumerate(case.tokens.items()):
+        cycle = [[7, 2, 13, 3, 2, 5], [2, 2, 31, 2, 17], [64, 2, 3]][k % 3]
+        close(run_portions(runner, rid, toks, portions(len(toks), cycle)), case.want[rid], case.dtype, f"portions {rid}")
+
+
+def test_mixed_batches_with_pages_used_again(case):
+    rng = random.Random(7)
+    lengths = LENGTHS[case.name]
+    need = sorted((-(-n // case.page) for n in lengths.values()), reverse=True)
+    runner = case.runner(num_pages=sum(need[:4]))        # four live requests fit only through reuse
+    steps = mixed_schedule(rng, lengths, max_live=4, decode_tail=9)
+    assert any(len(e) >= 3 and any(n == 1 for _, n in e) and any(n > 1 for _, n in e) for e, _ in steps)
+    got = run_mixed(runner, case.tokens, steps)
+    for rid in case.tokens:
+        close(got[rid], case.want[rid], case.dtype, f"mixed {rid}")
+    runner.cache.check()
+    assert all(g.pool.num_held == 0 for g in runner.cache.groups)
+    # and once more over the same pool, in another order: every page has been used before
+    steps = mixed_schedule(random.Random(8), dict(reversed(list(lengths.items()))), max_live=3, decode_tail=4)
+    got = run_mixed(runner, case.tokens, steps)
+    for rid in case.tokens:
+        close(got[rid], case.want[rid], case.dtype, f"mixed again {rid}")
+
+
+def test_long_decoding(case):
+    """A short prompt, then every further token one by one up to the context limit."""
+    n = case.raw["max_position_embeddings"]
+    toks = random_prompt(random.Random(9), case.raw["vocab_size"], n)
+    want = plain.forward(case.cfg, case.w, toks)
+    runner = case.runner(num_pages=-(-n // case.page))
+    close(run_portions(runner, "long", toks, [5] + [1] * (n - 5)), want, case.dtype, "long decoding")
+
+
+def test_first_tokens_of_a_sequence(case):
+    runner = case.runner(num_pages=8)
+    rng = random.Random(10)
+    for n in (1, 2, 3, 5):
+        toks = random_prompt(rng, case.raw["vocab_size"], n)
+        want = plain.forward(case.cfg, case.w, toks)
+        close(run_whole(runner, f"w{n}", toks), want, case.dtype, f"first {n} whole")
+        close(run_portions(runner, f"p{n}", toks, [1] * n), want, case.dtype, f"first {n} one by one")
+
+
+def test_greedy_generation_through_the_entry_point(case):
+    from marin_b200 import Engine, SamplingParams, StopReason
+
+    engine = Engine(case.dir, dtype=case.dtype, ctx=case.raw["max_position_embeddings"], page_size=case.page,
+                    max_batch=3, token_budget=24)
+    rng = random.Random(12)
+    prompts = [random_prompt(rng, case.raw["vocab_size"], n) for n in (5, 30, 1, 12)]
+    outs = engine.generate(prompts, SamplingParams(temperature=0.0, max_tokens=12))
+    assert [o.stop for o in outs] == [StopReason.MAX_TOKENS] * 4
+    for prompt, out in zip(prompts, outs):
+        assert len(out.tokens) == 12
+        if case.dtype == "float32":
+            assert out.tokens == plain.greedy(case.cfg, case.w, prompt, 12)
+        else:
+            # bfloat16 may pick another token where two logits are nearly equal: every token must be
+            # (nearly) the best one given the tokens before it
+            ids = list(prompt)
+            for tok in out.tokens:
+                row = plain.forward(case.cfg, case.w, ids)[-1]
+                assert float(row.max() - row[tok]) <= 0.15
+                ids.append(tok)
+    engine.cache.check()
+    assert not engine.cache.requests
+
+
+def test_schedule_may_repeat_a_layer_and_share_a_cache(case):
+    """The order layers run in is data: layer 0 twice, the second run reading the first run's cache."""
+    if case.name != "A":
+        pytest.skip("one configuration is enough")
+    from marin_b200.cache import CacheManager
+    from marin_b200.engine import Runner, build_model
+    from marin_b200.models import architecture_of
+    from marin_b200.parts import ScheduleEntry
+    from marin_b200.models.model import Model
+    from marin_b200.weights import load_tensors
+
+    spec = architecture_of(case.config).build_spec(case.config)
+    spec.schedule = [ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(1), ScheduleEntry(0, cache_of=0)]
+    model = Model(spec)
+    model.load(load_tensors(case.dir, model.tensor_specs(), spec.ignorable), case.rt)
+    cache = CacheManager(model.cache_needs(), [e.cache_of for e in spec.schedule], case.page, 40, 4)
+    cache.allocate(case.rt.device, case.rt.dtype)
+    assert len(cache.groups) == 1 and len(cache.groups[0].entries) == 3
+    runner = Runner(model, cache, case.rt, 128)
+    toks = case.tokens["a"]
+    want = plain.forward(case.cfg, case.w, toks, schedule=[(0, None), (1, None), (1, None), (0, 0)])
+    close(run_whole(runner, "w", toks), want, case.dtype, "schedule whole")
+    close(run_portions(runner, "p", toks, portions(len(toks), [5, 2, 1, 9])), want, case.dtype, "schedule portions")

@@ -1,0 +1,285 @@
+"""Each CUDA kernel alone against its plain torch twin (tests/kernel_refs.py), at sizes other than
+the engine's: widths and vocabularies that are no power of two, head sizes in steps of 16, odd
+head counts and groups, scrambled block tables, windows."""
+import math
+import random
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+import kernel_refs as ref
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype):
+    return dict(rtol=2e-5, atol=2e-6) if dtype == torch.float32 else dict(rtol=1.6e-2, atol=1e-3)
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from marin_b200.kernels import ops as o
+    return o
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("vocab,h,tokens", [(333, 72, 5), (1000, 2560, 37), (17, 8, 1)])
+def test_embed(ops, dtype, vocab, h, tokens):
+    g = torch.Generator(device=DEV).manual_seed(1)
+    table = torch.randn(vocab, h, device=DEV, generator=g).to(dtype)
+    ids = torch.randint(0, vocab, (tokens,), device=DEV, generator=g, dtype=torch.int32)
+    ids[0] = vocab - 1
+    out, want = torch.empty(tokens, h, device=DEV), torch.empty(tokens, h, device=DEV)
+    ops.embed(ids, table, out)
+    ref.embed(ids, table, want)
+    assert torch.equal(out, want)
+
+
+@pytest.mark.parametrize("out_dtype", DTYPES)
+@pytest.mark.parametrize("rows,n,eps,unit", [(3, 72, 1e-5, False), (17, 2560, 1e-6, False), (1, 5120, 1e-6, True), (5, 1, 1e-3, False), (2, 1031, 1e-6, False)])
+def test_rmsnorm(ops, out_dtype, rows, n, eps, unit):
+    g = torch.Generator(device=DEV).manual_seed(2)
+    x = torch.randn(rows, n, device=DEV, generator=g) * 3.0
+    w = 1.0 + 0.2 * torch.randn(n, device=DEV, generator=g)
+    out, want = torch.empty(rows, n, device=DEV, dtype=out_dtype), torch.empty(rows, n, device=DEV, dtype=out_dtype)
+    ops.rmsnorm(x, w, eps, out, unit)
+    ref.rmsnorm(x.double(), w.double(), eps, want, unit)
+    torch.testing.assert_close(out.float(), want.float(), **tol(out_dtype))
+
+
+GEMM_SHAPES = [(1, 72, 72), (5, 333, 136), (64, 256, 64), (65, 130, 200), (16, 1000, 2560), (130, 96, 1031), (8, 384, 96)]
+
+
+@pytest.mark.parametrize("combo", ["f32", "bf16", "bf16_f32out"])
+@pytest.mark.parametrize("T,N,K", GEMM_SHAPES)
+def test_gemm(ops, combo, T, N, K):
+    g = torch.Generator(device=DEV).manual_seed(3)
+    in_dtype = torch.float32 if combo == "f32" else torch.bfloat16
+    out_dtype = torch.bfloat16 if combo == "bf16" else torch.float32
+    x = torch.randn(T, K, device=DEV, generator=g).to(in_dtype)
+    w = (torch.randn(N, K, device=DEV, generator=g) / math.sqrt(K)).to(in_dtype)
+    out = torch.empty(T, N, device=DEV, dtype=out_dtype)
+    ops.gemm(x, w, out)
+    want = (x.double() @ w.double().t())
+    torch.testing.assert_close(out.double(), want, **(dict(rtol=1e-5, atol=1e-5) if out_dtype == torch.float32 else dict(rtol=1e-2, atol=1e-2)))
+    if out_dtype == torch.float32:
+        base = torch.randn(T, N, device=DEV, generator=g)
+        acc = base.clone()
+        ops.gemm(x, w, acc, accumulate=True)
+        torch.testing.assert_close(acc.double(), base.double() + want, rtol=1e-5, atol=1e-5)
+
+
+def test_gemm_rows_do_not_depend_on_the_batch(ops):
+    """A row's result is the same alone and among 200 other rows (float32 path: bit for bit)."""
+    g = torch.Generator(device=DEV).manual_seed(4)
+    x = torch.randn(201, 320, device=DEV, generator=g)
+    w = torch.randn(96, 320, device=DEV, generator=g)
+    full, one = torch.empty(201, 96, device=DEV), torch.empty(1, 96, device=DEV)
+    ops.gemm(x, w, full)
+    ops.gemm(x[137:138].contiguous(), w, one)
+    assert torch.equal(full[137:138], one)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,K,d,rot,inter,norm,page", [(4, 2, 16, 16, False, True, 4), (6, 3, 48, 48, False, True, 16), (8, 2, 128, 128, False, True, 16),
+                                                       (5, 5, 32, 16, True, False, 8), (3, 1, 80, 80, False, True, 2), (2, 2, 256, 256, False, True, 32)])
+def test_qk_norm_rope_write(ops, dtype, H, K, d, rot, inter, norm, page):
+    g = torch.Generator(device=DEV).manual_seed(5)
+    T, pages = 23, 12
+    qkv = torch.randn(T, (H + 2 * K) * d, device=DEV, generator=g).to(dtype)
+    qw = (1 + 0.1 * torch.randn(d, device=DEV, generator=g)) if norm else None
+    kw = (1 + 0.1 * torch.randn(d, device=DEV, generator=g)) if norm else None
+    positions = torch.randint(0, 4000, (T,), device=DEV, generator=g, dtype=torch.int32)
+    inv_freq = torch.pow(torch.tensor(1e6), -(torch.arange(rot // 2, dtype=torch.float32) * 2.0 / rot)).to(DEV)
+    slots = torch.randperm(pages * page, device=DEV, generator=g)[:T].to(torch.int32)
+    slots[3] = -1      # a padded token writes nothing
+    caches = [torch.zeros(pages, K, page, d, device=DEV, dtype=dtype) for _ in range(4)]
+    q1, q2 = torch.empty(T, H * d, device=DEV, dtype=dtype), torch.empty(T, H * d, device=DEV, dtype=dtype)
+    ops.qk_norm_rope_write(qkv, q1, qw, kw, 1e-6, positions, inv_freq, rot, inter, slots, caches[0], caches[1], H, K, d, True)
+    ref.qk_norm_rope_write(qkv, q2, qw, kw, 1e-6, positions, inv_freq, rot, inter, slots, caches[2], caches[3], H, K, d, True)
+    t = dict(rtol=1e-4, atol=2e-4) if dtype == torch.float32 else dict(rtol=1.6e-2, atol=2e-2)
+    torch.testing.assert_close(q1.float(), q2.float(), **t)
+    torch.testing.assert_close(caches[0].float(), caches[2].float(), **t)
+    assert torch.equal(caches[1], caches[3])       # values are copied unchanged
+    # queries only (a layer that reads another layer's cache)
+    q_only = qkv[:, : H * d].contiguous()
+    q3 = torch.empty_like(q1)
+    before = caches[0].clone()
+    ops.qk_norm_rope_write(q_only, q3, qw, kw, 1e-6, positions, inv_freq, rot, inter, slots, caches[0], caches[1], H, K, d, False)
+    assert torch.equal(q3, q1) and torch.equal(caches[0], before)
+
+
+def paged_case(gen, dtype, lens_new, H, K, d, page, pages, scale_far=None):
+    """Requests [(cached, new)] with scrambled block tables and a filled cache."""
+    R = len(lens_new)
+    maxb = max(-(-(c + n) // page) for c, n in lens_new) + 1
+    perm = torch.randperm(pages, generator=gen, device=DEV).tolist()
+    table = torch.zeros(R, maxb, dtype=torch.int32, device=DEV)
+    at = 0
+    positions, req_index = [], []
+    for r, (c, n) in enumerate(lens_new):
+        nb = -(-(c + n) // page)
+        table[r, :nb] = torch.tensor(perm[at:at + nb], dtype=torch.int32)
+        at += nb
+        positions += list(range(c, c + n))
+        req_index += [r] * n
+    assert at <= pages
+    T = len(positions)
+    k_cache = torch.randn(pages, K, page, d, device=DEV, generator=gen).to(dtype)
+    v_cache = torch.randn(pages, K, page, d, device=DEV, generator=gen).to(dtype)
+    q = torch.randn(T, H * d, device=DEV, generator=gen).to(dtype)
+    ctx = SimpleNamespace(
+        positions=torch.tensor(positions, dtype=torch.int32, device=DEV),
+        req_index=torch.tensor(req_index, dtype=torch.int32, device=DEV),
+        cu_tokens=torch.tensor([0] + list(torch.tensor([n for _, n in lens_new]).cumsum(0)), dtype=torch.int32, device=DEV),
+        seq_lens=torch.tensor([c + n for c, n in lens_new], dtype=torch.int32, device=DEV),
+        num_tokens=T, num_requests=R, num_decode=sum(1 for _, n in lens_new if n == 1),
+        max_query_len=max(n for _, n in lens_new), max_seq_len=max(c + n for c, n in lens_new),
+    )
+    return q, k_cache, v_cache, table, ctx
+
+
+ATT_LAYOUTS = [(4, 2, 16, 4), (8, 2, 32, 8), (6, 3, 48, 16), (32, 8, 128, 16), (5, 1, 64, 16), (3, 3, 80, 32), (2, 1, 256, 64)]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,K,d,page", ATT_LAYOUTS)
+@pytest.mark.parametrize("window", [0, 37])
+def test_attention_mixed_batch(ops, dtype, H, K, d, page, window):
+    g = torch.Generator(device=DEV).manual_seed(6)
+    # decodes first (as the step function orders them), then prompt portions, some from position 0
+    lens_new = [(130, 1), (63, 1), (0, 1), (255, 1), (0, 70), (129, 65), (17, 2), (64, 128)]
+    pages = sum(-(-(c + n) // page) for c, n in lens_new) + 3
+    q, kc, vc, table, ctx = paged_case(g, dtype, lens_new, H, K, d, page, pages)
+    out, want = torch.empty_like(q), torch.empty_like(q)
+    scale = 1.0 / math.sqrt(d)
+    ops.attention(q, kc, vc, out, ctx, table, H, K, d, scale, window)
+    ref.attention(q, kc, vc, want, ctx, table, H, K, d, scale, window)
+    t = dict(rtol=1e-4, atol=1e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(out.float(), want.float(), **t)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("context", [1, 15, 16, 17, 127, 128, 129, 255, 256, 257, 1023, 1025, 2049])
+def test_attention_decode_at_page_and_chunk_edges(ops, dtype, context):
+    g = torch.Generator(device=DEV).manual_seed(7)
+    H, K, d, page = 8, 2, 64, 16
+    lens_new = [(context - 1, 1), (max(0, context - 3), 1)]
+    pages = sum(-(-(c + n) // page) for c, n in lens_new) + 2
+    q, kc, vc, table, ctx = paged_case(g, dtype, lens_new, H, K, d, page, pages)
+    out, want = torch.empty_like(q), torch.empty_like(q)
+    ops.attention(q, kc, vc, out, ctx, table, H, K, d, 0.125, 0)
+    ref.attention(q, kc, vc, want, ctx, table, H, K, d, 0.125, 0)
+    t = dict(rtol=1e-4, atol=1e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(out.float(), want.float(), **t)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("far_key", [0, 3, 15, 16, 511, 640, 700])
+def test_attention_finds_one_far_key_among_hundreds(ops, dtype, far_key):
+    """Random inputs spread attention thinly, so a skipped key would hardly show.  Here one key far
+    back matches the query exactly and strongly: the output must be that key's value."""
+    g = torch.Generator(device=DEV).manual_seed(8)
+    H, K, d, page = 4, 2, 32, 16
+    lens_new = [(700, 1), (690, 11)]
+    pages = sum(-(-(c + n) // page) for c, n in lens_new) + 1
+    q, kc, vc, table, ctx = paged_case(g, dtype, lens_new, H, K, d, page, pages)
+    kc.mul_(0.05)
+    # token 0 (request 0) and the last token of request 1: their query equals 40 x the far key's direction
+    for t_idx, r in ((0, 0), (11, 1)):
+        pg = int(table[r, far_key // page])
+        for h in range(H):
+            key = torch.randn(d, device=DEV, generator=g)
+            key = key / key.norm()
+            kc[pg, h // (H // K), far_key % page] = (key * 6).to(dtype)
+            q.view(-1, H, d)[t_idx, h] = (kc[pg, h // (H // K), far_key % page].float() * 2).to(dtype)
+    out, want = torch.empty_like(q), torch.empty_like(q)
+    ops.attention(q, kc, vc, out, ctx, table, H, K, d, 1.0, 0)
+    ref.attention(q, kc, vc, want, ctx, table, H, K, d, 1.0, 0)
+    t = dict(rtol=1e-4, atol=1e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(out.float(), want.float(), **t)
+    for t_idx, r in ((0, 0), (11, 1)):
+        pg = int(table[r, far_key // page])
+        for h in range(H):
+            v = vc[pg, h // (H // K), far_key % page].float()
+            torch.testing.assert_close(out.view(-1, H, d)[t_idx, h].float(), v, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_window_edge(ops, dtype):
+    """A key that matches the query strongly lies just outside the window for one token and just
+    inside it for the next: it must count for the second only."""
+    g = torch.Generator(device=DEV).manual_seed(9)
+    H, K, d, page, window = 2, 1, 32, 8, 50
+    lens_new = [(100, 2)]          # queries at positions 100 and 101
+    q, kc, vc, table, ctx = paged_case(g, dtype, lens_new, H, K, d, page, 16)
+    kc.mul_(0.05)
+    edge = 101 - window + 1        # 52: inside for position 101, inside for 100 too (51..100) -> use 51 / 52
+    outside_for_101 = 51           # visible to position 100 (51..100), not to 101 (52..101)
+    key = torch.randn(d, device=DEV, generator=g)
+    key = key / key.norm() * 6
+    kc[int(table[0, outside_for_101 // page]), 0, outside_for_101 % page] = key.to(dtype)
+    q.view(2, H, d)[:] = (key * 2).to(dtype)
+    out, want = torch.empty_like(q), torch.empty_like(q)
+    ops.attention(q, kc, vc, out, ctx, table, H, K, d, 1.0, window)
+    ref.attention(q, kc, vc, want, ctx, table, H, K, d, 1.0, window)
+    t = dict(rtol=1e-4, atol=1e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(out.float(), want.float(), **t)
+    v = vc[int(table[0, outside_for_101 // page]), 0, outside_for_101 % page].float()
+    torch.testing.assert_close(out.view(2, H, d)[0, 0].float(), v, rtol=2e-2, atol=2e-2)
+    assert (out.view(2, H, d)[1, 0].float() - v).abs().max() > 0.1
+    assert edge == 52
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,I", [(1, 136), (7, 320), (33, 9728), (2, 3)])
+def test_swiglu(ops, dtype, T, I):
+    g = torch.Generator(device=DEV).manual_seed(10)
+    gu = (torch.randn(T, 2 * I, device=DEV, generator=g) * 3).to(dtype)
+    out, want = torch.empty(T, I, device=DEV, dtype=dtype), torch.empty(T, I, device=DEV, dtype=dtype)
+    ops.swiglu(gu, out)
+    ref.swiglu(gu, want)
+    torch.testing.assert_close(out.float(), want.float(), **tol(dtype))
+
+
+def test_gather_rows_add_into_argmax(ops):
+    g = torch.Generator(device=DEV).manual_seed(11)
+    src = torch.randn(50, 333, device=DEV, generator=g)
+    rows = torch.tensor([49, 0, 7, 7, 31], dtype=torch.int32, device=DEV)
+    out = torch.empty(5, 333, device=DEV)
+    ops.gather_rows(src, rows, out)
+    assert torch.equal(out, src[rows.long()])
+    for dtype in DTYPES:
+        y = torch.randn(9, 77, device=DEV, generator=g)
+        x = torch.randn(9, 77, device=DEV, generator=g).to(dtype)
+        want = y + x.float()
+        ops.add_into(y, x)
+        assert torch.equal(y, want)
+    logits = torch.randn(6, 151936, device=DEV, generator=g)
+    logits[0, 5] = logits[0, 77777] = 50.0          # lowest id wins a tie
+    logits[1, 151935] = 60.0                        # the last id
+    logits[2, 151000] = 70.0                        # beyond `usable` below: must not be picked
+    ids = torch.empty(6, dtype=torch.int32, device=DEV)
+    ops.argmax(logits, 151936, ids)
+    assert ids.tolist()[:2] == [5, 151935] and int(ids[2]) == 151000
+    ops.argmax(logits, 150000, ids)
+    assert ids.tolist() == torch.argmax(logits[:, :150000], dim=-1).tolist()
+
+
+def test_kernels_refuse_what_they_cannot_do(ops):
+    from marin_b200.kernels.ops import KernelError
+
+    x = torch.zeros(4, 8)
+    with pytest.raises(KernelError):
+        ops.rmsnorm(x, torch.ones(8), 1e-6, torch.empty(4, 8))         # CPU tensors: no CPU path
+    q = torch.zeros(1, 2 * 1024, device=DEV)
+    kc = torch.zeros(2, 1, 16, 1024, device=DEV)
+    ctx = SimpleNamespace(positions=torch.zeros(1, dtype=torch.int32, device=DEV), req_index=torch.zeros(1, dtype=torch.int32, device=DEV))
+    with pytest.raises(KernelError):
+        ops.attention(q, kc, kc, torch.empty_like(q), ctx, torch.zeros(1, 2, dtype=torch.int32, device=DEV), 2, 1, 1024, 1.0, 0)
+    with pytest.raises(KernelError):
+        ops.gemm(torch.zeros(2, 8, device=DEV, dtype=torch.float16), torch.zeros(2, 8, device=DEV, dtype=torch.float16), torch.zeros(2, 2, device=DEV, dtype=torch.float16))

@@ -1,0 +1,264 @@
+"""Each part alone against the plain implementation's function for it, and a toy mixer with state
+of its own — defined here, registered here — built and stepped without a change to the package."""
+import json
+import math
+import os
+import random
+from dataclasses import dataclass
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+import plain_qwen3 as plain
+from helpers import portions, random_prompt, run_mixed, run_portions, run_whole, mixed_schedule
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device(os.environ.get("MARIN_B200_TEST_DEVICE", "cuda:0"))
+
+
+def runtime(dtype=torch.float32):
+    from marin_b200.parts import Runtime
+    return Runtime(DEV, dtype)
+
+
+def harness(mixer, rt, page=8, pages=32, ctx_len=256):
+    """A cache and a step-context builder around one mixer (no model)."""
+    from marin_b200.cache import CacheManager
+    from marin_b200.engine import Runner
+
+    cache = CacheManager([mixer.cache_need()], [None], page, pages, 4)
+    cache.allocate(rt.device, rt.dtype)
+    fake_model = SimpleNamespace(spec=SimpleNamespace(vocab_size=1 << 30))
+    return Runner(fake_model, cache, rt, ctx_len)
+
+
+def test_rmsnorm_part():
+    from marin_b200.parts import lookup
+
+    rt = runtime()
+    norm = lookup("norm", "rmsnorm")(dim=72, eps=3e-6, name="n")
+    assert [(s.name, s.shape, s.role) for s in norm.tensor_specs()] == [("n.weight", (72,), "norm")]
+    w = 1 + 0.1 * torch.randn(72)
+    norm.load({"n.weight": w.to(torch.bfloat16)}, rt)
+    assert norm.weight.dtype == torch.float32
+    x = torch.randn(9, 72)
+    out = torch.empty(9, 72, device=DEV)
+    norm.forward(x.to(DEV), out)
+    torch.testing.assert_close(out.cpu(), plain.rms_norm(x, w.to(torch.bfloat16).float(), 3e-6), rtol=1e-5, atol=1e-6)
+
+
+def test_rotary_part_through_the_fused_kernel():
+    from marin_b200.kernels import ops
+    from marin_b200.parts import lookup
+
+    rt = runtime()
+    H, K, d, T, page = 3, 1, 48, 11, 8
+    pos = lookup("position", "rope")(head_dim=d, theta=5e5)
+    pos.load({}, rt)
+    i = torch.arange(d // 2, dtype=torch.float32)
+    torch.testing.assert_close(pos.inv_freq.cpu(), torch.pow(torch.tensor(5e5), -(i * 2.0 / d)), rtol=1e-6, atol=0)
+    qkv = torch.randn(T, (H + 2 * K) * d)
+    positions = torch.tensor([0, 1, 2, 3, 100, 101, 1000, 2047, 4095, 17, 5], dtype=torch.int32)
+    kc, vc = torch.zeros(4, K, page, d, device=DEV), torch.zeros(4, K, page, d, device=DEV)
+    q_out = torch.empty(T, H * d, device=DEV)
+    slots = torch.arange(T, dtype=torch.int32, device=DEV)
+    ops.qk_norm_rope_write(qkv.to(DEV), q_out, None, None, 0.0, positions.to(DEV), pos.inv_freq, pos.rotary_dim,
+                           pos.interleaved, slots, kc, vc, H, K, d, True)
+    want_q = plain.rope(qkv[:, : H * d].view(T, H, d), positions, 5e5)
+    torch.testing.assert_close(q_out.cpu().view(T, H, d), want_q, rtol=1e-4, atol=2e-4)
+    want_k = plain.rope(qkv[:, H * d:(H + K) * d].view(T, K, d), positions, 5e5)
+    got_k = torch.stack([kc[t // page, :, t % page] for t in range(T)]).cpu()
+    torch.testing.assert_close(got_k, want_k, rtol=1e-4, atol=2e-4)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_mixer_alone(dtype):
+    from marin_b200.engine import StepEntry
+    from marin_b200.parts import PartSpec, lookup
+
+    rt = runtime(dtype)
+    hidden, H, K, d = 72, 6, 3, 48
+    mixer = lookup("mixer", "gqa_attention")(hidden=hidden, heads=H, kv_heads=K, head_dim=d, name="att", qk_norm=True,
+                                             norm_eps=1e-5, position=PartSpec("rope", {"head_dim": d, "theta": 1e4}))
+    g = torch.Generator().manual_seed(1)
+    w = {s.name: (torch.randn(s.shape, generator=g) * (0.1 if s.role == "matrix" else 0.05) + (1.0 if s.role == "norm" else 0.0)).to(dtype)
+         for s in mixer.tensor_specs()}
+    wf = {k: v.float() for k, v in w.items()}
+    mixer.load(dict(w), rt)
+    runner = harness(mixer, rt)
+    T = 29
+    x = torch.randn(T, hidden, generator=g).to(dtype)
+    runner.begin("r")
+    got = []
+    at = 0
+    for n in (13, 1, 1, 14):     # a prompt portion, two single tokens, another portion: all from the cache
+        runner.cache.reserve("r", at + n)
+        ctx = runner.build_context([StepEntry("r", [0] * n, [])])
+        residual = torch.zeros(n, hidden, device=DEV)
+        mixer.forward(x[at:at + n].to(DEV), ctx, runner.views.view(0, ctx), residual)
+        runner.cache.commit("r", at + n)
+        got.append(residual.cpu())
+        at += n
+    got = torch.cat(got)
+    xf = x.float()
+    pos = torch.arange(T)
+    q = plain.rope(plain.rms_norm(plain.linear(xf, wf["att.q_proj.weight"]).view(T, H, d), wf["att.q_norm.weight"], 1e-5), pos, 1e4)
+    k = plain.rope(plain.rms_norm(plain.linear(xf, wf["att.k_proj.weight"]).view(T, K, d), wf["att.k_norm.weight"], 1e-5), pos, 1e4)
+    v = plain.linear(xf, wf["att.v_proj.weight"]).view(T, K, d)
+    want = plain.linear(plain.attention(q, k, v).reshape(T, H * d), wf["att.o_proj.weight"])
+    tol = dict(rtol=1e-4, atol=1e-4) if dtype == torch.float32 else dict(rtol=5e-2, atol=5e-2)
+    torch.testing.assert_close(got, want, **tol)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_swiglu_part_alone(dtype):
+    from marin_b200.engine.context import Workspace
+    from marin_b200.parts import lookup
+
+    rt = runtime(dtype)
+    ffn = lookup("feedforward", "swiglu")(hidden=72, intermediate=136, name="mlp")
+    g = torch.Generator().manual_seed(2)
+    w = {s.name: (torch.randn(s.shape, generator=g) * 0.1).to(dtype) for s in ffn.tensor_specs()}
+    ffn.load(dict(w), rt)
+    x = torch.randn(7, 72, generator=g).to(dtype)
+    base = torch.randn(7, 72, generator=g)
+    residual = base.clone().to(DEV)
+    ffn.forward(x.to(DEV), SimpleNamespace(workspace=Workspace(DEV)), residual)
+    want = base + plain.swiglu_mlp(x.float(), w["mlp.gate_proj.weight"].float(), w["mlp.up_proj.weight"].float(), w["mlp.down_proj.weight"].float())
+    tol = dict(rtol=1e-4, atol=1e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(residual.cpu(), want, **tol)
+
+
+# ---- a toy architecture whose first layer's mixer keeps a state of its own ---------------------------------
+
+def define_toy():
+    from marin_b200.config.base import ModelConfig
+    from marin_b200.models import register_architecture
+    from marin_b200.parts import (LayerSpec, Mixer, ModelSpec, PartSpec, ScheduleEntry, StateNeed, TensorSpec,
+                                  register_mixer)
+
+    @register_mixer("toy_decay")
+    class DecayMixer(Mixer):
+        """s_t = decay * s_{t-1} + W_in x_t ;  y_t = W_out s_t  — a state per request, no pages."""
+
+        def __init__(self, hidden, decay, name):
+            self.hidden, self.decay, self.name = hidden, decay, name
+
+        def cache_need(self):
+            return StateNeed((self.hidden,), torch.float32)
+
+        def tensor_specs(self):
+            return [TensorSpec(f"{self.name}.in_proj.weight", (self.hidden, self.hidden)),
+                    TensorSpec(f"{self.name}.out_proj.weight", (self.hidden, self.hidden))]
+
+        def load(self, tensors, rt):
+            self.w_in = tensors.pop(f"{self.name}.in_proj.weight").to(rt.device, torch.float32)
+            self.w_out = tensors.pop(f"{self.name}.out_proj.weight").to(rt.device, torch.float32)
+
+        def forward(self, x, ctx, cache, residual):
+            u = x.float() @ self.w_in.t()
+            y = torch.empty_like(u)
+            for span in ctx.spans:
+                s = cache.state[span.slot].clone()
+                for j in range(span.start, span.start + span.count):
+                    s = self.decay * s + u[j]
+                    y[j] = s
+                cache.state[span.slot] = s
+            residual += y @ self.w_out.t()
+
+    @dataclass
+    class ToyConfig(ModelConfig):
+        decay: float = 0.5
+        heads: int = 2
+        head_dim: int = 16
+        intermediate: int = 48
+        eps: float = 1e-6
+
+        @classmethod
+        def from_dict(cls, raw, generation=None):
+            return cls(architecture="ToyStateLM", model_type="toy_state", vocab_size=raw["vocab_size"],
+                       hidden_size=raw["hidden_size"], max_position_embeddings=raw["max_position_embeddings"], raw=dict(raw),
+                       decay=raw["decay"], heads=raw["heads"], head_dim=raw["head_dim"], intermediate=raw["intermediate"])
+
+        def to_json_dict(self):
+            return {"architectures": ["ToyStateLM"], "model_type": "toy_state", "vocab_size": self.vocab_size,
+                    "hidden_size": self.hidden_size, "max_position_embeddings": self.max_position_embeddings,
+                    "decay": self.decay, "heads": self.heads, "head_dim": self.head_dim, "intermediate": self.intermediate}
+
+    def build_spec(cfg):
+        h = cfg.hidden_size
+        norm = PartSpec("rmsnorm", {"dim": h, "eps": cfg.eps})
+        ffn = PartSpec("swiglu", {"hidden": h, "intermediate": cfg.intermediate})
+        names = {"norm1": "norm1", "mixer": "mixer", "norm2": "norm2", "feedforward": "mlp"}
+        att = PartSpec("gqa_attention", {"hidden": h, "heads": cfg.heads, "kv_heads": 1, "head_dim": cfg.head_dim,
+                                         "qk_norm": False, "position": PartSpec("rope", {"head_dim": cfg.head_dim, "theta": 100.0})})
+        layers = [LayerSpec("prenorm", norm, PartSpec("toy_decay", {"hidden": h, "decay": cfg.decay}), ffn, "toy.layers.0", names),
+                  LayerSpec("prenorm", norm, att, ffn, "toy.layers.1", names)]
+        return ModelSpec(hidden_size=h, vocab_size=cfg.vocab_size,
+                         embedding=PartSpec("token_table", {"vocab": cfg.vocab_size, "hidden": h, "name": "toy.embed"}),
+                         final_norm=PartSpec("rmsnorm", {"dim": h, "eps": cfg.eps, "name": "toy.norm"}),
+                         head=PartSpec("linear", {"vocab": cfg.vocab_size, "hidden": h, "name": "toy.head"}),
+                         layers=layers, schedule=[ScheduleEntry(0), ScheduleEntry(1)])
+
+    register_architecture("ToyStateLM", "toy_state", ToyConfig, build_spec)
+    return ToyConfig
+
+
+def toy_plain(raw, w, ids):
+    """The toy model on a whole sequence, from plain functions."""
+    h, H, d = raw["hidden_size"], raw["heads"], raw["head_dim"]
+    T = len(ids)
+    x = plain.embed(ids, w["toy.embed.weight"])
+    # layer 0: decay mixer
+    n = plain.rms_norm(x, w["toy.layers.0.norm1.weight"], 1e-6)
+    u = plain.linear(n, w["toy.layers.0.mixer.in_proj.weight"])
+    s, ys = torch.zeros(h), []
+    for t in range(T):
+        s = raw["decay"] * s + u[t]
+        ys.append(s)
+    x = x + plain.linear(torch.stack(ys), w["toy.layers.0.mixer.out_proj.weight"])
+    n = plain.rms_norm(x, w["toy.layers.0.norm2.weight"], 1e-6)
+    x = x + plain.swiglu_mlp(n, w["toy.layers.0.mlp.gate_proj.weight"], w["toy.layers.0.mlp.up_proj.weight"], w["toy.layers.0.mlp.down_proj.weight"])
+    # layer 1: attention without q/k norm, one kv head
+    p = "toy.layers.1."
+    n = plain.rms_norm(x, w[p + "norm1.weight"], 1e-6)
+    pos = torch.arange(T)
+    q = plain.rope(plain.linear(n, w[p + "mixer.q_proj.weight"]).view(T, H, d), pos, 100.0)
+    k = plain.rope(plain.linear(n, w[p + "mixer.k_proj.weight"]).view(T, 1, d), pos, 100.0)
+    v = plain.linear(n, w[p + "mixer.v_proj.weight"]).view(T, 1, d)
+    x = x + plain.linear(plain.attention(q, k, v).reshape(T, H * d), w[p + "mixer.o_proj.weight"])
+    n = plain.rms_norm(x, w[p + "norm2.weight"], 1e-6)
+    x = x + plain.swiglu_mlp(n, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
+    return plain.linear(plain.rms_norm(x, w["toy.norm.weight"], 1e-6), w["toy.head.weight"])
+
+
+def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
+    from marin_b200.cache import CacheManager
+    from marin_b200.engine import Runner, load_model
+    from marin_b200.weights import write_random_model
+
+    ToyConfig = define_toy()
+    raw = {"architectures": ["ToyStateLM"], "model_type": "toy_state", "vocab_size": 97, "hidden_size": 40,
+           "max_position_embeddings": 96, "decay": 0.7, "heads": 2, "head_dim": 16, "intermediate": 48}
+    d = write_random_model(str(tmp_path / "toy"), ToyConfig.from_dict(raw), seed=4, dtype=torch.float32, matrix_std=0.15)
+    rt = runtime()
+    config, model = load_model(d, rt)          # config.json chooses the toy architecture
+    assert type(config).__name__ == "ToyConfig"
+    cache = CacheManager(model.cache_needs(), [e.cache_of for e in model.spec.schedule], 8, 24, 4)
+    cache.allocate(rt.device, rt.dtype)
+    assert len(cache.groups) == 1 and list(cache.state) == [0]      # pages for layer 1, state slots for layer 0
+    runner = Runner(model, cache, rt, 96)
+    w = plain.read_weights(d)
+    rng = random.Random(3)
+    lengths = {"a": 40, "b": 7, "c": 61, "d": 25, "e": 33, "f": 12}
+    tokens = {rid: random_prompt(rng, 97, n) for rid, n in lengths.items()}
+    want = {rid: toy_plain(raw, w, t) for rid, t in tokens.items()}
+    for rid in ("a", "c"):
+        torch.testing.assert_close(run_whole(runner, rid, tokens[rid]).cpu(), want[rid], rtol=1e-4, atol=1e-4)
+        torch.testing.assert_close(run_portions(runner, rid, tokens[rid], portions(lengths[rid], [5, 1, 2, 11])).cpu(),
+                                   want[rid], rtol=1e-4, atol=1e-4)
+    got = run_mixed(runner, tokens, mixed_schedule(rng, lengths, max_live=4))     # state slots are used again too
+    for rid in tokens:
+        torch.testing.assert_close(got[rid].cpu(), want[rid], rtol=1e-4, atol=1e-4)
+    cache.check()
