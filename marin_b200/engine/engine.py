@@ -105,7 +105,46 @@ class Engine:
         self.cache.allocate(self.rt.device, self.rt.dtype)
         self.runner = Runner(self.model, self.cache, self.rt, self.ctx)
         self.max_batch, self.token_budget = max_batch, token_budget
+        self.scheduler = Scheduler(self.cache, max_batch, token_budget, self.ctx)
+        self._requests: Dict[Hashable, Request] = {}
+        self._samplers: Dict[Hashable, Sampler] = {}
         self._next_id = 0
+
+    # ---- requests, one step at a time ------------------------------------------------------------------
+    def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None,
+                    req_id: Optional[Hashable] = None) -> Hashable:
+        """Queues a request (token ids); returns its id.  ``step`` runs it with the others."""
+        params = params or SamplingParams()
+        if req_id is None:
+            req_id = self._next_id
+            self._next_id += 1
+        request = Request(req_id, [int(t) for t in prompt], params)
+        self.scheduler.add(request)
+        self._requests[req_id] = request
+        self._samplers[req_id] = Sampler(params)
+        return req_id
+
+    def has_work(self) -> bool:
+        return self.scheduler.has_work()
+
+    def step(self) -> List[tuple]:
+        """One scheduler decision and one model step.  Returns ``[(req_id, token)]`` for the requests
+        that produced a token in this step (host ints)."""
+        plan = self.scheduler.schedule()
+        if not plan:
+            return []
+        entries = [StepEntry(p.request.req_id, p.tokens, [len(p.tokens) - 1] if p.sample else []) for p in plan]
+        logits = self.runner.step(entries)
+        sampled = self._sample(plan, logits, self._samplers, self.config.vocab_size)
+        return self.scheduler.update(plan, sampled)
+
+    def result(self, req_id: Hashable) -> Generation:
+        r = self._requests[req_id]
+        return Generation(r.req_id, len(r.prompt), list(r.output), r.stop, r.preemptions)
+
+    def forget(self, req_id: Hashable) -> None:
+        self._requests.pop(req_id, None)
+        self._samplers.pop(req_id, None)
 
     # ---- generation -------------------------------------------------------------------------------------
     def generate(self, prompts: Sequence[Sequence[int]],
@@ -117,34 +156,20 @@ class Engine:
         plist = list(params) if isinstance(params, (list, tuple)) else [params] * len(prompts)
         if len(plist) != len(prompts):
             raise ValueError("one SamplingParams per prompt, or one for all")
-        sched = Scheduler(self.cache, self.max_batch, self.token_budget, self.ctx)
-        requests: List[Request] = []
-        samplers: Dict[Hashable, Sampler] = {}
-        for prompt, p in zip(prompts, plist):
-            rid = self._next_id
-            self._next_id += 1
-            r = Request(rid, [int(t) for t in prompt], p)
-            sched.add(r)
-            requests.append(r)
-            samplers[rid] = Sampler(p)
-        vocab = self.config.vocab_size
-        while sched.has_work():
-            plan = sched.schedule()
-            if not plan:
-                if not sched.has_work():
-                    break
+        ids = [self.add_request(prompt, p) for prompt, p in zip(prompts, plist)]
+        idle = 0
+        while self.scheduler.has_work():
+            emitted = self.step()
+            idle = 0 if emitted or self.scheduler.running else idle + 1
+            if idle > 2:
                 raise RuntimeError("the scheduler made no progress")
-            entries = [StepEntry(p.request.req_id, p.tokens, [len(p.tokens) - 1] if p.sample else []) for p in plan]
-            logits = self.runner.step(entries)
-            sampled = self._sample(plan, logits, samplers, vocab)
-            for r in sched.update(plan, sampled):
-                pass
             if on_token is not None:
-                for p in plan:
-                    if p.sample and p.request.output and p.request.req_id in sampled \
-                            and p.request.output[-1] == sampled[p.request.req_id]:
-                        on_token(p.request.req_id, sampled[p.request.req_id])
-        return [Generation(r.req_id, len(r.prompt), list(r.output), r.stop, r.preemptions) for r in requests]
+                for rid, token in emitted:
+                    on_token(rid, token)
+        out = [self.result(i) for i in ids]
+        for i in ids:
+            self.forget(i)
+        return out
 
     def _sample(self, plan: Sequence[Planned], logits: torch.Tensor, samplers: Dict[Hashable, Sampler],
                 vocab: int) -> Dict[Hashable, int]:

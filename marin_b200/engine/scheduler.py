@@ -169,10 +169,10 @@ class Scheduler:
         return plan
 
     # ---- after the step ----------------------------------------------------------------------------------
-    def update(self, plan: Sequence[Planned], sampled: Dict[Hashable, int]) -> List[Request]:
+    def update(self, plan: Sequence[Planned], sampled: Dict[Hashable, int]) -> List[tuple]:
         """Records what ran and the tokens sampled for the requests whose portion ended their known
-        tokens; returns the requests that finished."""
-        done: List[Request] = []
+        tokens; returns ``[(req_id, token)]`` for the tokens that were emitted (a stop token is not)."""
+        emitted: List[tuple] = []
         for p in plan:
             r = p.request
             r.computed += len(p.tokens)
@@ -181,13 +181,12 @@ class Scheduler:
             token = sampled[r.req_id]
             if token in r.params.stop_tokens:
                 self._finish(r, StopReason.END_OF_TEXT)      # the stop token is not emitted
-            else:
-                r.output.append(token)
-                if len(r.output) >= r.params.max_tokens:
-                    self._finish(r, StopReason.MAX_TOKENS)
-                elif r.computed >= self.max_seq_len:
-                    # the cache is full: the token just emitted cannot be fed (generate.rs:217-221)
-                    self._finish(r, StopReason.CONTEXT_FULL)
-            if r.finished:
-                done.append(r)
-        return done
+                continue
+            r.output.append(token)
+            emitted.append((r.req_id, token))
+            if len(r.output) >= r.params.max_tokens:
+                self._finish(r, StopReason.MAX_TOKENS)
+            elif r.computed >= self.max_seq_len:
+                # the cache is full: the token just emitted cannot be fed (generate.rs:217-221)
+                self._finish(r, StopReason.CONTEXT_FULL)
+        return emitted
