@@ -50,8 +50,14 @@ def _need_cuda(*tensors: torch.Tensor) -> None:
             raise KernelError("marin_b200 kernels need contiguous tensors")
 
 
+#: how many kernels of this package were launched (a launcher that returned 0 launched one kernel)
+launches = 0
+
+
 def _check(rc: int, what: str) -> None:
+    global launches
     if rc == 0:
+        launches += 1
         return
     if rc in _ERRORS:
         raise KernelError(f"{what}: {_ERRORS[rc]}")
