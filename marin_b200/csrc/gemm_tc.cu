@@ -1,0 +1,317 @@
+// bf16 matrix product on the 5th-generation tensor cores: out[t, n] (+)= sum_k x[t, k] * w[n, k].
+//
+// The weight matrix is the M operand of tcgen05.mma (128 rows of w per CTA) and the tokens are the N operand
+// (BN = 16..256 tokens per CTA), so that a decode step with a handful of tokens still fills the 128-row
+// datapath and streams every weight exactly once.  Both operands are K-major in global memory (w is
+// [N, K], x is [T, K]) and are brought into shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle,
+// no multicast) through a ring of STAGES buffers guarded by mbarriers; one thread issues the MMAs, whose
+// float32 accumulator lives in tensor memory; four warps read it back with tcgen05.ld and write
+// out[t, n] (32 consecutive n per warp and token: coalesced).
+//
+// Split-K: with few tokens and few weight rows there are fewer tiles than SMs, so blockIdx.z cuts K into
+// slices.  Each slice writes its float32 partial tile to scratch memory; the CTA that arrives last at the
+// tile's counter adds the slices in slice order (so the sum does not depend on which CTA was last) and
+// writes the result.  The counter is left at zero for the next launch.
+//
+// Every wait on an mbarrier has a time limit; a wait that gives up records a code in *error_flag and the
+// kernel winds down (tensor memory is freed on every path).  The reference's counterpart is its mma.sync
+// kernel with hi/lo-split activations (crates/cuda/src/mma.cu:52-141).
+#include <cuda.h>
+
+#include "common.cuh"
+
+#define TC_BM 128          // weight rows per CTA (the MMA's M)
+#define TC_BK 64           // k per pipeline stage: 64 bf16 = one 128-byte swizzle row
+#define TC_WAIT_LIMIT 4000000000LL   // clock ticks (about two seconds) before a wait gives up
+
+#define TC_OUT_BF16 0
+#define TC_OUT_F32 1
+#define TC_OUT_F32_ACC 2
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+
+// Waits until the phase with the given parity has completed, or the time limit passes (returns false).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    const long long start = clock64();
+    for (;;) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+        if (clock64() - start > TC_WAIT_LIMIT) return false;
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+        : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major tile, rows of 128 bytes, 128-byte swizzle; 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    const uint32_t lo = ((smem_addr & 0x3FFFFu) >> 4) | (1u << 16);          // start address; leading offset (unused) = 1
+    const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);              // stride offset 1024 B; version 1; SWIZZLE_128B
+    return ((uint64_t)hi << 32) | lo;
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+template <int BN>
+struct TcSmem {
+    static constexpr int A_BYTES = TC_BM * TC_BK * 2;
+    static constexpr int B_BYTES = BN * TC_BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+};
+
+__device__ __forceinline__ void store_out(void* out, int mode, size_t at, float v) {
+    if (mode == TC_OUT_BF16) ((bf16*)out)[at] = __float2bfloat16_rn(v);
+    else if (mode == TC_OUT_F32) ((float*)out)[at] = v;
+    else ((float*)out)[at] += v;
+}
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,
+                                                      const __grid_constant__ CUtensorMap map_x, void* __restrict__ out,
+                                                      int mode, int T, int N, int K, int kb_per_split,
+                                                      float* __restrict__ partials, int* __restrict__ counters,
+                                                      int* __restrict__ error_flag) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    using L = TcSmem<BN>;
+    uint64_t* full = (uint64_t*)(smem + STAGES * L::STAGE_BYTES);
+    uint64_t* empty = full + STAGES;
+    uint64_t* accum = empty + STAGES;
+    uint32_t* tmem_slot = (uint32_t*)(accum + 1);
+    int* last_slot = (int*)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * TC_BM, t0 = blockIdx.y * BN;
+    const int total_kb = (K + TC_BK - 1) / TC_BK;
+    const int kb_begin = blockIdx.z * kb_per_split;
+    const int kb_end = min(total_kb, kb_begin + kb_per_split);
+    const int nkb = kb_end - kb_begin;
+    constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        mbar_init(accum, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        // ---- producer: TMA loads into the ring ----
+        for (int i = 0; i < nkb; ++i) {
+            const int s = i % STAGES;
+            const uint32_t phase = (i / STAGES) & 1;
+            if (!mbar_wait(&empty[s], phase ^ 1)) { atomicExch(error_flag, 1); break; }
+            mbar_expect_tx(&full[s], L::STAGE_BYTES);
+            uint8_t* a = smem + s * L::STAGE_BYTES;
+            const int k = (kb_begin + i) * TC_BK;
+            tma_load_2d(a, &map_w, k, n0, &full[s]);
+            tma_load_2d(a + L::A_BYTES, &map_x, k, t0, &full[s]);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---- MMA issuer ----
+        constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+        bool ok = true;
+        for (int i = 0; i < nkb && ok; ++i) {
+            const int s = i % STAGES;
+            const uint32_t phase = (i / STAGES) & 1;
+            if (!mbar_wait(&full[s], phase)) { atomicExch(error_flag, 2); ok = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t a = smem_u32(smem + s * L::STAGE_BYTES);
+            const uint64_t adesc = umma_desc(a), bdesc = umma_desc(a + L::A_BYTES);
+#pragma unroll
+            for (int kk = 0; kk < TC_BK / 16; ++kk)
+                umma_bf16(tmem_base, adesc + 2 * kk, bdesc + 2 * kk, idesc, (i > 0 || kk > 0) ? 1u : 0u);
+            umma_commit(&empty[s]);
+        }
+        umma_commit(accum);
+    }
+    __syncwarp();
+
+    // ---- epilogue: every warp reads its 32 lanes of the accumulator ----
+    bool have = nkb > 0;
+    if (have) {
+        if (!mbar_wait(accum, 0)) { if (lane == 0) atomicExch(error_flag, 3); have = false; }
+    }
+    have = __all_sync(0xffffffffu, have);     // tcgen05.ld below is warp-wide: the whole warp takes one path
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const int n = n0 + warp * 32 + lane;
+    const int splits = gridDim.z;
+    const bool direct = splits == 1;
+#pragma unroll 1
+    for (int c0 = 0; c0 < BN; c0 += 16) {
+        float v[16];
+        if (have) tmem_ld16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, v);
+        else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = 0.0f;
+        }
+        if (n < N) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const int t = t0 + c0 + j;
+                if (t < T) {
+                    if (direct) store_out(out, mode, (size_t)t * N + n, v[j]);
+                    else partials[((size_t)blockIdx.z * T + t) * N + n] = v[j];
+                }
+            }
+        }
+    }
+    if (!direct) {
+        // ---- split-K: the CTA that arrives last adds the slices in order ----
+        __threadfence();
+        __syncthreads();
+        const int tile = blockIdx.y * gridDim.x + blockIdx.x;
+        if (threadIdx.x == 0) {
+            const int old = atomicAdd(&counters[tile], 1);
+            *last_slot = old == splits - 1;
+            if (old == splits - 1) counters[tile] = 0;
+        }
+        __syncthreads();
+        if (*last_slot) {
+            __threadfence();
+            if (n < N) {
+                const int t_end = min(T, t0 + BN);
+                for (int t = t0; t < t_end; ++t) {
+                    float sum = 0.0f;
+                    for (int z = 0; z < splits; ++z) sum += __ldcg(&partials[((size_t)z * T + t) * N + n]);
+                    store_out(out, mode, (size_t)t * N + n, sum);
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// ---- host side ----------------------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiled encode_tiled() {
+    static EncodeTiled fn = nullptr;
+    if (fn == nullptr) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult status;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &status) == cudaSuccess &&
+            status == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiled)p;
+    }
+    return fn;
+}
+
+// A [rows, K] bf16 row-major matrix seen as tiles of box_rows x 64 elements with 128-byte swizzle.
+static int make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
+    EncodeTiled enc = encode_tiled();
+    if (enc == nullptr) return MB_ERR_BAD_SIZE;
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : 1000 + (int)r;
+}
+
+template <int BN, int STAGES>
+static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int mode, int T, int N, int K, int splits,
+                     int kb_per_split, float* partials, int* counters, int* error_flag, cudaStream_t s) {
+    constexpr int smem = STAGES * TcSmem<BN>::STAGE_BYTES + 1024 + 256;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    dim3 grid((N + TC_BM - 1) / TC_BM, (T + BN - 1) / BN, splits);
+    gemm_tc_kernel<BN, STAGES><<<grid, 128, smem, s>>>(mw, mx, out, mode, T, N, K, kb_per_split, partials, counters, error_flag);
+    return mb_last_error();
+}
+
+// Tiles a launch with `bn` tokens per CTA would have (for the caller's choice of split).
+MB_API int mb_gemm_tc_tiles(int T, int N, int bn) { return ((N + TC_BM - 1) / TC_BM) * ((T + bn - 1) / bn); }
+
+// x [T, K] bf16, w [N, K] bf16, out [T, N]: bf16 (mode 0), float32 (1), float32 += (2).  K must be a multiple
+// of 8 and both pointers 16-byte aligned (TMA).  splits > 1 needs partials (splits*T*N floats) and counters
+// (one zeroed int per tile).  bn in {16, 32, 64, 128, 256}.
+MB_API int mb_gemm_tc(const void* x, const void* w, void* out, int mode, int T, int N, int K, int bn, int splits,
+                      float* partials, int* counters, int* error_flag, cudaStream_t s) {
+    if (T <= 0 || N <= 0) return 0;
+    if (K <= 0 || K % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return MB_ERR_BAD_SIZE;
+    if (mode < 0 || mode > 2) return MB_ERR_BAD_DTYPE;
+    const int total_kb = (K + TC_BK - 1) / TC_BK;
+    if (splits < 1) splits = 1;
+    if (splits > total_kb) splits = total_kb;
+    int kb_per_split = (total_kb + splits - 1) / splits;
+    splits = (total_kb + kb_per_split - 1) / kb_per_split;
+    if (splits > 1 && (partials == nullptr || counters == nullptr)) return MB_ERR_BAD_SIZE;
+    CUtensorMap mw, mx;
+    int rc = make_map(&mw, w, N, K, TC_BM);
+    if (rc) return rc;
+    rc = make_map(&mx, x, T, K, bn);
+    if (rc) return rc;
+    switch (bn) {
+        case 16: return launch_tc<16, 6>(mw, mx, out, mode, T, N, K, splits, kb_per_split, partials, counters, error_flag, s);
+        case 32: return launch_tc<32, 5>(mw, mx, out, mode, T, N, K, splits, kb_per_split, partials, counters, error_flag, s);
+        case 64: return launch_tc<64, 4>(mw, mx, out, mode, T, N, K, splits, kb_per_split, partials, counters, error_flag, s);
+        case 128: return launch_tc<128, 3>(mw, mx, out, mode, T, N, K, splits, kb_per_split, partials, counters, error_flag, s);
+        case 256: return launch_tc<256, 4>(mw, mx, out, mode, T, N, K, splits, kb_per_split, partials, counters, error_flag, s);
+        default: return MB_ERR_BAD_SIZE;
+    }
+}

@@ -130,6 +130,7 @@ LIBRARIES: Dict[str, List[str]] = {
     "mb_gemm_simple": ["gemm_simple.cu"],
     "mb_attention_simple": ["attention_simple.cu"],
     "mb_sampling": ["sampling.cu"],
+    "mb_gemm_tc": ["gemm_tc.cu"],
 }
 
 

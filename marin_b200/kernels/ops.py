@@ -83,12 +83,64 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
                                             _code(out), _c_int(rows), _c_int(n), _stream()), "rmsnorm")
 
 
+#: bf16 products go to the tcgen05 kernel when their shape allows (False: always the plain kernel)
+use_tensor_cores = True
+SM_COUNT = 148
+_scratch = {}
+
+
+def _gemm_scratch(device):
+    """Split-K partials, per-tile counters (zeroed once; the kernel leaves them at zero) and the error flag."""
+    key = (device.type, device.index)
+    s = _scratch.get(key)
+    if s is None:
+        s = {"partials": torch.empty(8 << 20, device=device, dtype=torch.float32),
+             "counters": torch.zeros(1 << 16, device=device, dtype=torch.int32),
+             "error": torch.zeros(1, device=device, dtype=torch.int32)}
+        _scratch[key] = s
+    return s
+
+
+def check_device_errors(device=None) -> None:
+    """Raises if a kernel's bounded wait gave up since the last check (reads one int: synchronises)."""
+    for s in _scratch.values():
+        code = int(s["error"].item())
+        if code != 0:
+            s["error"].zero_()
+            raise KernelError(f"a tensor-core kernel's wait on an mbarrier gave up (code {code})")
+
+
+def gemm_plan(T: int, N: int, K: int):
+    """Tokens per CTA and the number of K slices for the tensor-core kernel."""
+    bn = 16 if T <= 16 else 32 if T <= 32 else 64 if T <= 64 else 128
+    tiles = -(-N // 128) * -(-T // bn)
+    nkb = -(-K // 64)
+    splits = 1
+    if tiles < SM_COUNT:
+        splits = max(1, min(2 * SM_COUNT // tiles, nkb // 4, 16))
+    return bn, splits
+
+
 def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
-    """``out[t, n] (+)= sum_k x[t, k] * w[n, k]``."""
+    """``out[t, n] (+)= sum_k x[t, k] * w[n, k]``.  bfloat16 inputs run on the tensor cores (tcgen05, float32
+    accumulate); float32 inputs run on the CUDA cores in true float32."""
     _need_cuda(x, w, out)
     T, K = x.shape
     N = w.shape[0]
     assert w.shape[1] == K and tuple(out.shape) == (T, N), (x.shape, w.shape, out.shape)
+    if accumulate and out.dtype != torch.float32:
+        raise KernelError("gemm: accumulate needs a float32 output")
+    if (use_tensor_cores and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and K % 8 == 0
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and T > 0):
+        bn, splits = gemm_plan(T, N, K)
+        s = _gemm_scratch(x.device)
+        while splits > 1 and splits * T * N > s["partials"].numel():
+            splits -= 1
+        mode = 2 if accumulate else (0 if out.dtype == torch.bfloat16 else 1)
+        _check(_lib("mb_gemm_tc").mb_gemm_tc(_ptr(x), _ptr(w), _ptr(out), _c_int(mode), _c_int(T), _c_int(N), _c_int(K),
+                                            _c_int(bn), _c_int(splits), _ptr(s["partials"]), _ptr(s["counters"]),
+                                            _ptr(s["error"]), _stream()), "gemm (tensor cores)")
+        return
     _check(_lib("mb_gemm_simple").mb_gemm_simple(_ptr(x), _code(x), _ptr(w), _code(w), _ptr(out), _code(out), _c_int(T),
                                                 _c_int(N), _c_int(K), _c_int(int(accumulate)), _stream()), "gemm")
 

@@ -282,3 +282,48 @@ def test_kernels_refuse_what_they_cannot_do(ops):
         ops.attention(q, kc, kc, torch.empty_like(q), ctx, torch.zeros(1, 2, dtype=torch.int32, device=DEV), 2, 1, 1024, 1.0, 0)
     with pytest.raises(KernelError):
         ops.gemm(torch.zeros(2, 8, device=DEV, dtype=torch.float16), torch.zeros(2, 8, device=DEV, dtype=torch.float16), torch.zeros(2, 2, device=DEV, dtype=torch.float16))
+
+
+TC_SHAPES = [(1, 128, 64), (8, 6144, 2560), (8, 2560, 4096), (8, 2560, 9728), (64, 2560, 4096), (16, 300, 200), (17, 333, 136),
+             (33, 1000, 72), (100, 257, 320), (200, 640, 1024), (2048, 1280, 2560), (300, 128, 8), (129, 129, 4104)]
+
+
+@pytest.mark.parametrize("T,N,K", TC_SHAPES)
+def test_gemm_tensor_cores(ops, T, N, K):
+    """The tcgen05 kernel at decode shapes (split-K), prefill shapes and ragged edges in every dimension,
+    against a float64 product of the same bf16 inputs.  Run twice: the split-K counters must be back at zero."""
+    g = torch.Generator(device=DEV).manual_seed(13)
+    x = torch.randn(T, K, device=DEV, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    # make rows and columns distinguishable beyond noise: a tile put in the wrong place shows
+    x[:, 0] += torch.arange(T, device=DEV).to(torch.bfloat16) * 0.125
+    w[:, 0] += (torch.arange(N, device=DEV) % 64).to(torch.bfloat16) * 0.0625
+    want = x.double() @ w.double().t()
+    scale = float(want.abs().max())
+    for _ in range(2):
+        out32 = torch.full((T, N), float("nan"), device=DEV)
+        ops.gemm(x, w, out32)
+        ops.check_device_errors()
+        assert float((out32.double() - want).abs().max()) <= 2e-5 * scale + 1e-4
+        out16 = torch.empty(T, N, device=DEV, dtype=torch.bfloat16)
+        ops.gemm(x, w, out16)
+        torch.testing.assert_close(out16.double(), want, rtol=1e-2, atol=1e-2 * scale)
+        base = torch.randn(T, N, device=DEV, generator=g)
+        acc = base.clone()
+        ops.gemm(x, w, acc, accumulate=True)
+        assert float((acc.double() - base.double() - want).abs().max()) <= 2e-5 * scale + 1e-4
+    ops.check_device_errors()
+
+
+def test_gemm_tensor_cores_match_the_plain_kernel(ops):
+    g = torch.Generator(device=DEV).manual_seed(14)
+    x = torch.randn(40, 512, device=DEV, generator=g).to(torch.bfloat16)
+    w = torch.randn(384, 512, device=DEV, generator=g).to(torch.bfloat16)
+    a, b = torch.empty(40, 384, device=DEV), torch.empty(40, 384, device=DEV)
+    ops.gemm(x, w, a)
+    ops.use_tensor_cores = False
+    try:
+        ops.gemm(x, w, b)
+    finally:
+        ops.use_tensor_cores = True
+    torch.testing.assert_close(a, b, rtol=1e-5, atol=1e-3)
