@@ -315,3 +315,93 @@ MB_API int mb_gemm_tc(const void* x, const void* w, void* out, int mode, int T, 
         default: return MB_ERR_BAD_SIZE;
     }
 }
+
+// ---- the entry point that allocates nothing (see gemm_tc_noalloc.h) --------------------------------------------
+#include <stdio.h>
+
+#include "gemm_tc_noalloc.h"
+
+// Split-K scratch for mb_gemm_tc_noalloc: partial tiles, then tile counters, then the error flag.  In host
+// code this name is only a handle for the runtime; its device address comes from cudaGetSymbolAddress below.
+static __device__ __align__(256) unsigned char mb_noalloc_scratch[MB_NOALLOC_SCRATCH_BYTES];
+
+#define MB_NOALLOC_MAX_DEVICES 64
+static unsigned char* noalloc_base[MB_NOALLOC_MAX_DEVICES];     // per device, filled at its first call
+static thread_local char noalloc_message[256] = "";
+
+static int noalloc_setup(unsigned char** base) {
+    int device = -1;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return (int)e;
+    if (device < 0 || device >= MB_NOALLOC_MAX_DEVICES) {
+        snprintf(noalloc_message, sizeof noalloc_message, "device index %d is outside 0..%d", device, MB_NOALLOC_MAX_DEVICES - 1);
+        return MB_ERR_NOALLOC_SETUP;
+    }
+    if (noalloc_base[device] == nullptr) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, mb_noalloc_scratch);       // the address on the device that is current now
+        if (e != cudaSuccess || p == nullptr) {
+            snprintf(noalloc_message, sizeof noalloc_message, "cudaGetSymbolAddress failed on device %d: %s", device,
+                     cudaGetErrorString(e));
+            return e != cudaSuccess ? (int)e : MB_ERR_NOALLOC_SETUP;
+        }
+        noalloc_base[device] = (unsigned char*)p;
+    }
+    *base = noalloc_base[device];
+    return 0;
+}
+
+MB_API const char* mb_gemm_tc_noalloc_last_error(void) { return noalloc_message; }
+
+MB_API int mb_gemm_tc_noalloc_device_error(void) {
+    unsigned char* base = nullptr;
+    if (noalloc_setup(&base) != 0) return -1;
+    int* flag = (int*)(base + (size_t)MB_NOALLOC_MAX_PARTIALS * 4 + (size_t)MB_NOALLOC_MAX_TILES * 4);
+    int value = 0;
+    if (cudaMemcpy(&value, flag, sizeof value, cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    if (value != 0) cudaMemset(flag, 0, sizeof value);
+    return value;
+}
+
+MB_API int mb_gemm_tc_noalloc(const void* x, const void* w, void* out, int mode, int T, int N, int K, cudaStream_t stream) {
+    noalloc_message[0] = 0;
+    if (T <= 0 || N <= 0) return 0;
+    if (K <= 0) return MB_ERR_BAD_SIZE;
+    // the same plan the Python wrapper makes: tokens per CTA, then K slices if there are fewer tiles than SMs
+    const int bn = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : 128;
+    const long long tiles = (long long)((N + TC_BM - 1) / TC_BM) * ((T + bn - 1) / bn);
+    const int total_kb = (K + TC_BK - 1) / TC_BK;
+    int splits = 1;
+    if (tiles < 148) {
+        splits = (int)(296 / tiles);
+        if (splits > total_kb / 4) splits = total_kb / 4;
+        if (splits > 16) splits = 16;
+        if (splits < 1) splits = 1;
+    }
+    if (splits > 1) {
+        const long long need = (long long)splits * T * N;
+        if (need > MB_NOALLOC_MAX_PARTIALS) {
+            snprintf(noalloc_message, sizeof noalloc_message,
+                     "T=%d N=%d K=%d needs %lld floats of split-K scratch (%d slices); the built-in scratch holds %d",
+                     T, N, K, need, splits, MB_NOALLOC_MAX_PARTIALS);
+            return MB_ERR_NOALLOC_TOO_LARGE;
+        }
+        if (tiles > MB_NOALLOC_MAX_TILES) {
+            snprintf(noalloc_message, sizeof noalloc_message, "%lld tiles need counters; the built-in scratch holds %d",
+                     tiles, MB_NOALLOC_MAX_TILES);
+            return MB_ERR_NOALLOC_TOO_LARGE;
+        }
+    }
+    unsigned char* base = nullptr;
+    int rc = noalloc_setup(&base);
+    if (rc != 0) return rc;
+    float* partials = (float*)base;
+    int* counters = (int*)(base + (size_t)MB_NOALLOC_MAX_PARTIALS * 4);
+    int* error_flag = counters + MB_NOALLOC_MAX_TILES;
+    if (splits > 1) {
+        // the counters must start at zero; an earlier call that was cut short may have left them otherwise
+        cudaError_t e = cudaMemsetAsync(counters, 0, (size_t)tiles * sizeof(int), stream);
+        if (e != cudaSuccess) return (int)e;
+    }
+    return mb_gemm_tc(x, w, out, mode, T, N, K, bn, splits, partials, counters, error_flag, stream);
+}
