@@ -1,0 +1,418 @@
+// Fast bf16 attention over the paged cache, compiled for one head size and one group size
+// (-DHEAD_DIM=.. -DGROUP=..: what the model at hand needs, built at first use).
+//
+//  * decode: one new token per request.  A CTA takes one kv head of one request and one chunk of 256 keys
+//    (fixed by absolute position, so the arithmetic does not depend on the batch or on the number of SMs);
+//    all GROUP query heads that share the kv head are served from one pass over K and one over V; the
+//    partial (max, sum, accumulator) of every chunk goes to scratch and a merge kernel combines them.
+//    The reference splits decode attention the same way but sizes chunks by SM count
+//    (crates/cuda/src/attention.rs:23-30, attention.cu:224-351,481-494).
+//  * prefill: a CTA takes 64 consecutive query tokens of one request and one query head, walks the keys in
+//    blocks of 64 with an online softmax in float32; Q K^T and P V run on mma.sync.m16n8k16 (bf16 in,
+//    float32 accumulate).  Portions of prompts at any cached length, causal inside the portion.
+//    (The reference's counterpart: crates/cuda/src/attention_mma.cu:43-180, f16, whole prompts.)
+//
+// Page layout: [page][kv_head][offset in page][HEAD_DIM]; block_table[request][logical page] -> page.
+#include "common.cuh"
+
+#ifndef HEAD_DIM
+#error "compile with -DHEAD_DIM=<multiple of 16, at most 128>"
+#endif
+#ifndef GROUP
+#error "compile with -DGROUP=<query heads per kv head, at most 8>"
+#endif
+static_assert(HEAD_DIM % 16 == 0 && HEAD_DIM >= 16 && HEAD_DIM <= 128, "head size must be a multiple of 16 up to 128");
+static_assert(GROUP >= 1 && GROUP <= 8, "1 to 8 query heads per kv head");
+
+#define D HEAD_DIM
+#define DEC_CHUNK 256                 // keys per CTA
+#define DEC_WARPS 4
+#define DEC_KEYS_PER_WARP (DEC_CHUNK / DEC_WARPS)
+#define DPL (D / 8)                   // dims per lane: 8 lanes share one key
+#define VW (DPL % 8 == 0 ? 8 : (DPL % 4 == 0 ? 4 : 2))   // elements per vector load
+#define NV (DPL / VW)                 // vector loads per lane and key
+
+// Loads this lane's DPL elements of one row: vector v covers dims v * (8 * VW) + sub * VW ..
+__device__ __forceinline__ void load_slice(const bf16* row, int sub, float* dst) {
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+        const bf16* p = row + v * (8 * VW) + sub * VW;
+        if (VW == 8) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(p);
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); dst[v * VW + 2 * i] = f.x; dst[v * VW + 2 * i + 1] = f.y; }
+        } else if (VW == 4) {
+            const uint2 raw = *reinterpret_cast<const uint2*>(p);
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int i = 0; i < 2; ++i) { const float2 f = __bfloat1622float2(h[i]); dst[v * VW + 2 * i] = f.x; dst[v * VW + 2 * i + 1] = f.y; }
+        } else {
+            const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+            dst[v * VW] = f.x; dst[v * VW + 1] = f.y;
+        }
+    }
+}
+
+// The dim a lane's element e stands for.
+__device__ __forceinline__ int slice_dim(int sub, int e) { return (e / VW) * (8 * VW) + sub * VW + (e % VW); }
+
+__global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_split_kernel(
+    const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
+    const int* __restrict__ block_table, int max_pages, const int* __restrict__ seq_lens, int K, int page_size,
+    float scale, int window, float* __restrict__ part_acc, float* __restrict__ part_ml, int max_chunks) {
+    __shared__ float s_p[DEC_WARPS][GROUP][DEC_KEYS_PER_WARP];
+    __shared__ float s_acc[DEC_WARPS][GROUP][D];
+    __shared__ float s_m[DEC_WARPS][GROUP], s_l[DEC_WARPS][GROUP];
+    const int chunk = blockIdx.x, kh = blockIdx.y, r = blockIdx.z;
+    const int H = K * GROUP;
+    const int len = seq_lens[r];
+    const int pos = len - 1;
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int c_begin = chunk * DEC_CHUNK, c_end = min(len, c_begin + DEC_CHUNK);
+    if (c_begin >= len || c_end <= lo) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int sub = lane & 7, quad = lane >> 3;
+    const int* table = block_table + (size_t)r * max_pages;
+
+    float qr[GROUP][DPL];
+#pragma unroll
+    for (int g = 0; g < GROUP; ++g) load_slice(q + ((size_t)r * H + kh * GROUP + g) * D, sub, qr[g]);
+
+    // ---- scores of this warp's 64 keys ----
+    const int w_begin = c_begin + warp * DEC_KEYS_PER_WARP;
+#pragma unroll 4
+    for (int it = 0; it < DEC_KEYS_PER_WARP / 4; ++it) {
+        const int slot = it * 4 + quad;
+        const int key = w_begin + slot;
+        const bool valid = key < len && key >= lo;
+        float kv[DPL];
+        if (valid) {
+            const size_t page = (size_t)table[key / page_size];
+            load_slice(k_cache + ((page * K + kh) * page_size + (size_t)(key % page_size)) * D, sub, kv);
+        } else {
+#pragma unroll
+            for (int e = 0; e < DPL; ++e) kv[e] = 0.0f;
+        }
+#pragma unroll
+        for (int g = 0; g < GROUP; ++g) {
+            float dot = 0.0f;
+#pragma unroll
+            for (int e = 0; e < DPL; ++e) dot = fmaf(qr[g][e], kv[e], dot);
+            dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+            dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+            dot += __shfl_xor_sync(0xffffffffu, dot, 4);
+            if (sub == 0) s_p[warp][g][slot] = valid ? dot * scale : -INFINITY;
+        }
+    }
+    __syncwarp();
+    float m_w[GROUP], l_w[GROUP];
+#pragma unroll
+    for (int g = 0; g < GROUP; ++g) {
+        const float a = s_p[warp][g][lane], b = s_p[warp][g][lane + 32];
+        const float m = warp_max(fmaxf(a, b));
+        const float base = m == -INFINITY ? 0.0f : m;     // a warp whose keys are all masked contributes nothing
+        const float pa = expf(a - base), pb = expf(b - base);
+        __syncwarp();
+        s_p[warp][g][lane] = pa;
+        s_p[warp][g][lane + 32] = pb;
+        m_w[g] = m;
+        l_w[g] = warp_sum(pa + pb);
+    }
+    __syncwarp();
+
+    // ---- sum of p * V over the same keys ----
+    float acc[GROUP][DPL];
+#pragma unroll
+    for (int g = 0; g < GROUP; ++g)
+#pragma unroll
+        for (int e = 0; e < DPL; ++e) acc[g][e] = 0.0f;
+#pragma unroll 4
+    for (int it = 0; it < DEC_KEYS_PER_WARP / 4; ++it) {
+        const int slot = it * 4 + quad;
+        const int key = w_begin + slot;
+        if (key < len && key >= lo) {
+            float vv[DPL];
+            const size_t page = (size_t)table[key / page_size];
+            load_slice(v_cache + ((page * K + kh) * page_size + (size_t)(key % page_size)) * D, sub, vv);
+#pragma unroll
+            for (int g = 0; g < GROUP; ++g) {
+                const float p = s_p[warp][g][slot];
+#pragma unroll
+                for (int e = 0; e < DPL; ++e) acc[g][e] = fmaf(p, vv[e], acc[g][e]);
+            }
+        }
+    }
+    // the four key quads of the warp hold partial sums: add them, then the four warps through shared memory
+#pragma unroll
+    for (int g = 0; g < GROUP; ++g)
+#pragma unroll
+        for (int e = 0; e < DPL; ++e) {
+            float a = acc[g][e];
+            a += __shfl_xor_sync(0xffffffffu, a, 8);
+            a += __shfl_xor_sync(0xffffffffu, a, 16);
+            if (quad == 0) s_acc[warp][g][slice_dim(sub, e)] = a;
+        }
+    if (lane == 0) {
+#pragma unroll
+        for (int g = 0; g < GROUP; ++g) { s_m[warp][g] = m_w[g]; s_l[warp][g] = l_w[g]; }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < GROUP * D; idx += DEC_WARPS * 32) {
+        const int g = idx / D, dd = idx % D;
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < DEC_WARPS; ++w) m = fmaxf(m, s_m[w][g]);
+        float a = 0.0f, l = 0.0f;
+#pragma unroll
+        for (int w = 0; w < DEC_WARPS; ++w) {
+            const float f = s_m[w][g] == -INFINITY ? 0.0f : expf(s_m[w][g] - m);
+            a = fmaf(s_acc[w][g][dd], f, a);
+            l = fmaf(s_l[w][g], f, l);
+        }
+        const size_t at = ((size_t)r * H + kh * GROUP + g) * max_chunks + chunk;
+        part_acc[at * D + dd] = a;
+        if (dd == 0) { part_ml[at * 2] = m; part_ml[at * 2 + 1] = l; }
+    }
+}
+
+// Combines the chunks of one (request, head): out = sum_c acc_c e^(m_c - M) / sum_c l_c e^(m_c - M).
+__global__ void __launch_bounds__(D) attn_decode_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
+                                                           const int* __restrict__ seq_lens, int H, int window, int max_chunks,
+                                                           bf16* __restrict__ out) {
+    const int h = blockIdx.x, r = blockIdx.y, dd = threadIdx.x;
+    const int len = seq_lens[r];
+    if (len <= 0) return;
+    const int pos = len - 1;
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int c_first = lo / DEC_CHUNK, c_last = pos / DEC_CHUNK;
+    const size_t base = ((size_t)r * H + h) * max_chunks;
+    float m = -INFINITY;
+    for (int c = c_first; c <= c_last; ++c) m = fmaxf(m, part_ml[(base + c) * 2]);
+    float a = 0.0f, l = 0.0f;
+    for (int c = c_first; c <= c_last; ++c) {
+        const float mc = part_ml[(base + c) * 2];
+        const float f = mc == -INFINITY ? 0.0f : expf(mc - m);
+        a = fmaf(part_acc[(base + c) * D + dd], f, a);
+        l = fmaf(part_ml[(base + c) * 2 + 1], f, l);
+    }
+    out[((size_t)r * H + h) * D + dd] = __float2bfloat16_rn(a / l);
+}
+
+// ---- prefill ------------------------------------------------------------------------------------------------------
+#define PF_BM 64
+#define PF_BN 64
+#define PF_LD (D + 8)                 // padded row: 16-byte shift per row keeps ldmatrix free of bank conflicts
+#define PF_SMEM (3 * PF_BM * PF_LD * 2)
+
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+
+__device__ __forceinline__ void mma_bf16_16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Rows of one 64-key block of K or V into shared memory; keys past `k_last` are zero (their pages may not exist).
+__device__ __forceinline__ void load_kv_tile(bf16* dst, const bf16* __restrict__ cache, const int* __restrict__ table, int K, int kh,
+                                             int page_size, int key0, int k_last) {
+    constexpr int CHUNKS = D / 8;
+    for (int idx = threadIdx.x; idx < PF_BN * CHUNKS; idx += 128) {
+        const int row = idx / CHUNKS, c = idx % CHUNKS;
+        const int key = key0 + row;
+        uint4 val = make_uint4(0, 0, 0, 0);
+        if (key <= k_last) {
+            const size_t page = (size_t)table[key / page_size];
+            val = *reinterpret_cast<const uint4*>(cache + ((page * K + kh) * page_size + (size_t)(key % page_size)) * D + c * 8);
+        }
+        *reinterpret_cast<uint4*>(dst + row * PF_LD + c * 8) = val;
+    }
+}
+
+__global__ void __launch_bounds__(128) attn_prefill_kernel(
+    const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache, bf16* __restrict__ out,
+    const int* __restrict__ block_table, int max_pages, const int* __restrict__ cu_tokens, const int* __restrict__ seq_lens,
+    int first_req, int K, int page_size, float scale, int window) {
+    extern __shared__ __align__(16) uint8_t pf_smem[];
+    bf16* sQ = reinterpret_cast<bf16*>(pf_smem);
+    bf16* sK = sQ + PF_BM * PF_LD;
+    bf16* sV = sK + PF_BN * PF_LD;
+    const int H = K * GROUP;
+    const int r = first_req + blockIdx.z, h = blockIdx.y, qt = gridDim.x - 1 - blockIdx.x;   // long tiles first
+    const int tok0 = cu_tokens[r], n = cu_tokens[r + 1] - tok0;
+    if (qt * PF_BM >= n) return;
+    const int len = seq_lens[r], pos0 = len - n;
+    const int rows = min(PF_BM, n - qt * PF_BM);
+    const int q_first = pos0 + qt * PF_BM, q_last = q_first + rows - 1;
+    const int k_lo = window > 0 ? max(0, q_first - window + 1) : 0;
+    const int kh = h / GROUP;
+    const int* table = block_table + (size_t)r * max_pages;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    {   // the query tile; rows past the request's tokens are zero
+        constexpr int CHUNKS = D / 8;
+        for (int idx = threadIdx.x; idx < PF_BM * CHUNKS; idx += 128) {
+            const int row = idx / CHUNKS, c = idx % CHUNKS;
+            uint4 val = make_uint4(0, 0, 0, 0);
+            if (row < rows) val = *reinterpret_cast<const uint4*>(q + ((size_t)(tok0 + qt * PF_BM + row) * H + h) * D + c * 8);
+            *reinterpret_cast<uint4*>(sQ + row * PF_LD + c * 8) = val;
+        }
+    }
+    __syncthreads();
+    uint32_t qa[D / 16][4];
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+        const int row = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+        ldsm_x4((uint32_t)__cvta_generic_to_shared(sQ + row * PF_LD + kk * 16 + (lane >> 4) * 8), qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3]);
+    }
+
+    float o[D / 8][4];
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+    const float sl2 = scale * 1.4426950408889634f;
+    const int row0 = warp * 16 + (lane >> 2);                 // this thread's rows: row0 and row0 + 8
+    const int qp0 = q_first + row0, qp1 = qp0 + 8;
+    const int lo0 = window > 0 ? max(0, qp0 - window + 1) : 0, lo1 = window > 0 ? max(0, qp1 - window + 1) : 0;
+
+    for (int kb = k_lo / PF_BN; kb <= q_last / PF_BN; ++kb) {
+        const int key0 = kb * PF_BN;
+        __syncthreads();                                       // the previous block's K and V are no longer read
+        load_kv_tile(sK, k_cache, table, K, kh, page_size, key0, q_last);
+        load_kv_tile(sV, v_cache, table, K, kh, page_size, key0, q_last);
+        __syncthreads();
+
+        float s[PF_BN / 8][4];
+#pragma unroll
+        for (int j = 0; j < PF_BN / 8; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f; }
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+#pragma unroll
+            for (int j = 0; j < PF_BN / 8; j += 2) {
+                uint32_t b0, b1, b2, b3;
+                const int key = j * 8 + (lane & 7) + (lane >> 4) * 8;
+                ldsm_x4((uint32_t)__cvta_generic_to_shared(sK + key * PF_LD + kk * 16 + ((lane >> 3) & 1) * 8), b0, b1, b2, b3);
+                mma_bf16_16816(s[j], qa[kk], b0, b1);
+                mma_bf16_16816(s[j + 1], qa[kk], b2, b3);
+            }
+        }
+        // mask, online softmax
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < PF_BN / 8; ++j) {
+            const int key = key0 + j * 8 + 2 * (lane & 3);
+            s[j][0] = (key <= qp0 && key >= lo0) ? s[j][0] * sl2 : -INFINITY;
+            s[j][1] = (key + 1 <= qp0 && key + 1 >= lo0) ? s[j][1] * sl2 : -INFINITY;
+            s[j][2] = (key <= qp1 && key >= lo1) ? s[j][2] * sl2 : -INFINITY;
+            s[j][3] = (key + 1 <= qp1 && key + 1 >= lo1) ? s[j][3] * sl2 : -INFINITY;
+            mx0 = fmaxf(mx0, fmaxf(s[j][0], s[j][1]));
+            mx1 = fmaxf(mx1, fmaxf(s[j][2], s[j][3]));
+        }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
+        const float base0 = mn0 == -INFINITY ? 0.0f : mn0, base1 = mn1 == -INFINITY ? 0.0f : mn1;
+        const float corr0 = exp2f(m_run[0] - base0), corr1 = exp2f(m_run[1] - base1);
+        m_run[0] = mn0; m_run[1] = mn1;
+        float sum0 = 0.0f, sum1 = 0.0f;
+#pragma unroll
+        for (int j = 0; j < PF_BN / 8; ++j) {
+            s[j][0] = exp2f(s[j][0] - base0); s[j][1] = exp2f(s[j][1] - base0);
+            s[j][2] = exp2f(s[j][2] - base1); s[j][3] = exp2f(s[j][3] - base1);
+            sum0 += s[j][0] + s[j][1];
+            sum1 += s[j][2] + s[j][3];
+        }
+        l_run[0] = l_run[0] * corr0 + sum0;
+        l_run[1] = l_run[1] * corr1 + sum1;
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) { o[i][0] *= corr0; o[i][1] *= corr0; o[i][2] *= corr1; o[i][3] *= corr1; }
+        // O += P V
+#pragma unroll
+        for (int ks = 0; ks < PF_BN / 16; ++ks) {
+            uint32_t pa[4];
+            pa[0] = pack_bf16(s[2 * ks][0], s[2 * ks][1]);
+            pa[1] = pack_bf16(s[2 * ks][2], s[2 * ks][3]);
+            pa[2] = pack_bf16(s[2 * ks + 1][0], s[2 * ks + 1][1]);
+            pa[3] = pack_bf16(s[2 * ks + 1][2], s[2 * ks + 1][3]);
+#pragma unroll
+            for (int dt = 0; dt < D / 8; dt += 2) {
+                uint32_t b0, b1, b2, b3;
+                const int key = ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+                ldsm_x4_trans((uint32_t)__cvta_generic_to_shared(sV + key * PF_LD + dt * 8 + (lane >> 4) * 8), b0, b1, b2, b3);
+                mma_bf16_16816(o[dt], pa, b0, b1);
+                mma_bf16_16816(o[dt + 1], pa, b2, b3);
+            }
+        }
+    }
+    // row sums live in four lanes each
+    l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], 1);
+    l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], 2);
+    l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], 1);
+    l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], 2);
+    const float inv0 = 1.0f / l_run[0], inv1 = 1.0f / l_run[1];
+    const int col = 2 * (lane & 3);
+    if (row0 < rows) {
+        bf16* dst = out + ((size_t)(tok0 + qt * PF_BM + row0) * H + h) * D;
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) *reinterpret_cast<uint32_t*>(dst + i * 8 + col) = pack_bf16(o[i][0] * inv0, o[i][1] * inv0);
+    }
+    if (row0 + 8 < rows) {
+        bf16* dst = out + ((size_t)(tok0 + qt * PF_BM + row0 + 8) * H + h) * D;
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) *reinterpret_cast<uint32_t*>(dst + i * 8 + col) = pack_bf16(o[i][2] * inv1, o[i][3] * inv1);
+    }
+}
+
+// ---- host side ------------------------------------------------------------------------------------------------------
+
+MB_API int mb_attn_head_dim() { return D; }
+MB_API int mb_attn_group() { return GROUP; }
+MB_API int mb_attn_decode_chunk() { return DEC_CHUNK; }
+
+// Decode: q/out rows 0..requests-1 are the single new tokens of requests 0..requests-1.  part_acc holds
+// requests*H*max_chunks*HEAD_DIM floats and part_ml requests*H*max_chunks*2; max_chunks >= ceil(longest/256).
+MB_API int mb_attn_decode(const void* q, const void* k_cache, const void* v_cache, void* out, const int* block_table,
+                          int max_pages, const int* seq_lens, int requests, int K, int page_size, float scale, int window,
+                          float* part_acc, float* part_ml, int max_chunks, cudaStream_t s) {
+    if (requests <= 0) return 0;
+    if (max_chunks <= 0 || K <= 0) return MB_ERR_BAD_SIZE;
+    dim3 grid(max_chunks, K, requests);
+    attn_decode_split_kernel<<<grid, DEC_WARPS * 32, 0, s>>>((const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, block_table,
+                                                             max_pages, seq_lens, K, page_size, scale, window, part_acc, part_ml,
+                                                             max_chunks);
+    int rc = mb_last_error();
+    if (rc) return rc;
+    attn_decode_merge_kernel<<<dim3(K * GROUP, requests), D, 0, s>>>(part_acc, part_ml, seq_lens, K * GROUP, window, max_chunks, (bf16*)out);
+    return mb_last_error();
+}
+
+// Prefill: requests first_req .. first_req+requests-1 of the step, each with its tokens cu_tokens[r]..cu_tokens[r+1].
+MB_API int mb_attn_prefill(const void* q, const void* k_cache, const void* v_cache, void* out, const int* block_table,
+                           int max_pages, const int* cu_tokens, const int* seq_lens, int first_req, int requests,
+                           int max_query_len, int K, int page_size, float scale, int window, cudaStream_t s) {
+    if (requests <= 0 || max_query_len <= 0) return 0;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    dim3 grid((max_query_len + PF_BM - 1) / PF_BM, K * GROUP, requests);
+    attn_prefill_kernel<<<grid, 128, PF_SMEM, s>>>((const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, block_table,
+                                                   max_pages, cu_tokens, seq_lens, first_req, K, page_size, scale, window);
+    return mb_last_error();
+}

@@ -134,17 +134,25 @@ LIBRARIES: Dict[str, List[str]] = {
 }
 
 
+#: (head size, query heads per kv head) the fast attention kernels are built for by ``build_all``; any other
+#: layout a model brings is compiled when that model first runs
+ATTENTION_LAYOUTS = [(128, 4), (128, 5), (16, 2), (32, 4), (48, 2)]
+
+
 def build_all(verbose: bool = True) -> List[str]:
     """Compiles every library (in parallel).  Used by the build check and before timing."""
     results: Dict[str, object] = {}
+    jobs = {n: (src, []) for n, src in LIBRARIES.items()}
+    for d, g in ATTENTION_LAYOUTS:
+        jobs[f"mb_attention_fast_d{d}_g{g}"] = (["attention_fast.cu"], [f"HEAD_DIM={d}", f"GROUP={g}"])
 
     def work(n: str) -> None:
         try:
-            results[n] = build(n, LIBRARIES[n], verbose=verbose)
+            results[n] = build(n, jobs[n][0], jobs[n][1], verbose=verbose)
         except Exception as err:  # noqa: BLE001 - reported below
             results[n] = err
 
-    threads = [threading.Thread(target=work, args=(n,)) for n in LIBRARIES]
+    threads = [threading.Thread(target=work, args=(n,)) for n in jobs]
     for t in threads:
         t.start()
     for t in threads:
@@ -152,4 +160,4 @@ def build_all(verbose: bool = True) -> List[str]:
     errors = [r for r in results.values() if isinstance(r, Exception)]
     if errors:
         raise errors[0]
-    return [str(results[n]) for n in LIBRARIES]
+    return [str(results[n]) for n in jobs]

@@ -54,6 +54,12 @@ def _need_cuda(*tensors: torch.Tensor) -> None:
 launches = 0
 
 
+def launches_extra(n: int) -> None:
+    """A launcher that started more than one kernel says so here."""
+    global launches
+    launches += n
+
+
 def _check(rc: int, what: str) -> None:
     global launches
     if rc == 0:
@@ -161,12 +167,57 @@ def qk_norm_rope_write(qkv, q_out, q_weight, k_weight, eps, positions, inv_freq,
         _c_int(int(write_kv)), _stream()), "qk_norm_rope_write")
 
 
+#: bf16 attention goes to the tensor-core / split-KV kernels when the head layout allows (False: the plain kernel)
+use_fast_attention = True
+_attn_scratch = {}
+
+
+def _attention_lib(d: int, group: int):
+    """The fast attention kernels are compiled for one head size and one group size, at first use."""
+    return build.load(f"mb_attention_fast_d{d}_g{group}", ["attention_fast.cu"], [f"HEAD_DIM={d}", f"GROUP={group}"])
+
+
+def fast_attention_supported(dtype, H: int, K: int, d: int) -> bool:
+    return dtype == torch.bfloat16 and d % 16 == 0 and 16 <= d <= 128 and H % K == 0 and 1 <= H // K <= 8
+
+
+def _decode_scratch(device, requests: int, H: int, chunks: int, d: int):
+    need = requests * H * chunks
+    key = (device.type, device.index)
+    held = _attn_scratch.get(key)
+    if held is None or held[0].numel() < need * d or held[1].numel() < need * 2:
+        grow = max(need, 2 * (held[1].numel() // 2) if held else 0)
+        held = (torch.empty(grow * d, device=device, dtype=torch.float32), torch.empty(grow * 2, device=device, dtype=torch.float32))
+        _attn_scratch[key] = held
+    return held
+
+
 def attention(q, k_cache, v_cache, out, ctx, block_table, H, K, d, scale, window=0) -> None:
-    """Causal attention of the step's tokens over the paged cache (their own keys included)."""
+    """Causal attention of the step's tokens over the paged cache (their own keys included).  The first
+    ``ctx.num_decode`` requests bring one token each (rows 0..num_decode-1); the rest bring portions."""
     _need_cuda(q, k_cache, v_cache, out, block_table)
     T = q.shape[0]
     page_size = k_cache.shape[2]
     assert tuple(q.shape) == (T, H * d) and out.shape == q.shape and k_cache.dtype == q.dtype
+    if T == 0:
+        return
+    if use_fast_attention and fast_attention_supported(q.dtype, H, K, d):
+        lib = _attention_lib(d, H // K)
+        max_pages = block_table.shape[1]
+        nd = ctx.num_decode
+        if nd > 0:
+            chunks = getattr(ctx, "attn_chunks", None) or -(-ctx.max_seq_len // 256)
+            part_acc, part_ml = _decode_scratch(q.device, nd, H, chunks, d)
+            _check(lib.mb_attn_decode(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), _c_int(max_pages),
+                                      _ptr(ctx.seq_lens), _c_int(nd), _c_int(K), _c_int(page_size), _c_float(scale),
+                                      _c_int(window), _ptr(part_acc), _ptr(part_ml), _c_int(chunks), _stream()), "attention (decode)")
+            launches_extra(1)
+        if ctx.num_requests > nd:
+            _check(lib.mb_attn_prefill(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), _c_int(max_pages),
+                                       _ptr(ctx.cu_tokens), _ptr(ctx.seq_lens), _c_int(nd), _c_int(ctx.num_requests - nd),
+                                       _c_int(ctx.max_query_len), _c_int(K), _c_int(page_size), _c_float(scale),
+                                       _c_int(window), _stream()), "attention (prefill)")
+        return
     _check(_lib("mb_attention_simple").mb_attention_simple(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _code(q), _ptr(block_table), _c_int(block_table.shape[1]),
         _ptr(ctx.req_index), _ptr(ctx.positions), _c_int(T), _c_int(H), _c_int(K), _c_int(d), _c_int(page_size),

@@ -327,3 +327,17 @@ def test_gemm_tensor_cores_match_the_plain_kernel(ops):
     finally:
         ops.use_tensor_cores = True
     torch.testing.assert_close(a, b, rtol=1e-5, atol=1e-3)
+
+
+@pytest.mark.parametrize("H,K,d,page", [(32, 8, 128, 16), (8, 2, 64, 16), (6, 3, 48, 8), (40, 8, 128, 16)])
+@pytest.mark.parametrize("window", [0, 300])
+def test_attention_long_contexts_bf16(ops, H, K, d, page, window):
+    """Several decode chunks and several query tiles per request, at the engine's page size."""
+    g = torch.Generator(device=DEV).manual_seed(15)
+    lens_new = [(1000, 1), (255, 1), (256, 1), (2049, 1), (900, 150), (0, 200), (511, 2)]
+    pages = sum(-(-(c + n) // page) for c, n in lens_new) + 3
+    q, kc, vc, table, ctx = paged_case(g, torch.bfloat16, lens_new, H, K, d, page, pages)
+    out, want = torch.empty_like(q), torch.empty_like(q)
+    ops.attention(q, kc, vc, out, ctx, table, H, K, d, 1.0 / math.sqrt(d), window)
+    ref.attention(q, kc, vc, want, ctx, table, H, K, d, 1.0 / math.sqrt(d), window)
+    torch.testing.assert_close(out.float(), want.float(), rtol=2e-2, atol=2e-2)
