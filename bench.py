@@ -181,9 +181,12 @@ def decode_e2e(engine, batch, steps, warmup, context):
     from marin_b200 import SamplingParams
 
     vocab = engine.config.vocab_size
-    prompt_len = context - (steps + warmup) - 1
+    # the prompts are read in portions under the token budget, one request after another, while the requests
+    # that are through already decode: leave room for those tokens so that the timed steps end near `context`
+    prefill_steps = -(-batch * context // engine.token_budget) + batch
+    prompt_len = context - (steps + warmup) - prefill_steps - 2
     g = torch.Generator().manual_seed(3)
-    params = SamplingParams(temperature=0.0, max_tokens=steps + warmup + 1)
+    params = SamplingParams(temperature=0.0, max_tokens=context)
     ids = [engine.add_request(torch.randint(0, vocab, (prompt_len,), generator=g).tolist(), params) for _ in range(batch)]
     produced = {i: 0 for i in ids}
     while min(produced.values()) < 1:                       # prompts (untimed)
@@ -198,9 +201,8 @@ def decode_e2e(engine, batch, steps, warmup, context):
         got += len(engine.step())                           # sampled ids are host ints here
     torch.cuda.synchronize()
     seconds = time.perf_counter() - t0
-    while engine.has_work():
-        engine.step()
     for i in ids:
+        engine.scheduler.cancel(i)
         engine.forget(i)
     h2d = 4 * (batch * 3 + (batch + 1) + batch * 2 + batch + batch * (engine.runner.max_pages_per_seq + 1))
     return {"value": got / seconds, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * batch,

@@ -1,7 +1,7 @@
 // Fast bf16 attention over the paged cache, compiled for one head size and one group size
 // (-DHEAD_DIM=.. -DGROUP=..: what the model at hand needs, built at first use).
 //
-//  * decode: one new token per request.  A CTA takes one kv head of one request and one chunk of 256 keys
+//  * decode: one new token per request.  A CTA takes one kv head of one request and one chunk of 128 keys
 //    (fixed by absolute position, so the arithmetic does not depend on the batch or on the number of SMs);
 //    all GROUP query heads that share the kv head are served from one pass over K and one over V; the
 //    partial (max, sum, accumulator) of every chunk goes to scratch and a merge kernel combines them.
@@ -22,10 +22,10 @@
 #error "compile with -DGROUP=<query heads per kv head, at most 8>"
 #endif
 static_assert(HEAD_DIM % 16 == 0 && HEAD_DIM >= 16 && HEAD_DIM <= 128, "head size must be a multiple of 16 up to 128");
-static_assert(GROUP >= 1 && GROUP <= 8, "1 to 8 query heads per kv head");
+static_assert(GROUP * 4 <= 2 * (128 / 4) && GROUP >= 1 && GROUP <= 8, "1 to 8 query heads per kv head");
 
 #define D HEAD_DIM
-#define DEC_CHUNK 256                 // keys per CTA
+#define DEC_CHUNK 128                 // keys per CTA
 #define DEC_WARPS 4
 #define DEC_KEYS_PER_WARP (DEC_CHUNK / DEC_WARPS)
 #define DPL (D / 8)                   // dims per lane: 8 lanes share one key
@@ -57,12 +57,26 @@ __device__ __forceinline__ void load_slice(const bf16* row, int sub, float* dst)
 // The dim a lane's element e stands for.
 __device__ __forceinline__ int slice_dim(int sub, int e) { return (e / VW) * (8 * VW) + sub * VW + (e % VW); }
 
+// 16 bytes from global to shared memory without passing through registers.
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// Reads this lane's DPL elements of a row that lies in shared memory.
+__device__ __forceinline__ void load_slice_smem(const bf16* row, int sub, float* dst) { load_slice(row, sub, dst); }
+
+#define DEC_SMEM (DEC_WARPS * 2 * DEC_KEYS_PER_WARP * D * 2)
+
+// Every warp first asks for all of its keys and values (cp.async, so that they are all in flight at once),
+// then computes from shared memory: scores, softmax over its keys, p * V.
 __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_split_kernel(
     const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
     const int* __restrict__ block_table, int max_pages, const int* __restrict__ seq_lens, int K, int page_size,
     float scale, int window, float* __restrict__ part_acc, float* __restrict__ part_ml, int max_chunks) {
+    extern __shared__ __align__(16) uint8_t dec_smem[];
     __shared__ float s_p[DEC_WARPS][GROUP][DEC_KEYS_PER_WARP];
-    __shared__ float s_acc[DEC_WARPS][GROUP][D];
     __shared__ float s_m[DEC_WARPS][GROUP], s_l[DEC_WARPS][GROUP];
     const int chunk = blockIdx.x, kh = blockIdx.y, r = blockIdx.z;
     const int H = K * GROUP;
@@ -74,26 +88,43 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_split_kernel(
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int sub = lane & 7, quad = lane >> 3;
     const int* table = block_table + (size_t)r * max_pages;
+    bf16* sK = reinterpret_cast<bf16*>(dec_smem) + (size_t)warp * 2 * DEC_KEYS_PER_WARP * D;
+    bf16* sV = sK + DEC_KEYS_PER_WARP * D;
+    const int w_begin = c_begin + warp * DEC_KEYS_PER_WARP;
 
+    // ---- ask for the warp's keys, then its values: 16-byte pieces, a row of D*2 bytes is D/8 pieces ----
+    constexpr int PIECES = D / 8;
+#pragma unroll
+    for (int which = 0; which < 2; ++which) {
+        const bf16* cache = which == 0 ? k_cache : v_cache;
+        bf16* dst = which == 0 ? sK : sV;
+#pragma unroll 4
+        for (int idx = lane; idx < DEC_KEYS_PER_WARP * PIECES; idx += 32) {
+            const int slot = idx / PIECES, piece = idx % PIECES;
+            const int key = w_begin + slot;
+            if (key < len && key >= lo) {
+                const size_t page = (size_t)table[key / page_size];
+                cp_async16(dst + slot * D + piece * 8, cache + ((page * K + kh) * page_size + (size_t)(key % page_size)) * D + piece * 8);
+            } else {
+                *reinterpret_cast<uint4*>(dst + slot * D + piece * 8) = make_uint4(0, 0, 0, 0);
+            }
+        }
+        cp_async_commit();
+    }
     float qr[GROUP][DPL];
 #pragma unroll
     for (int g = 0; g < GROUP; ++g) load_slice(q + ((size_t)r * H + kh * GROUP + g) * D, sub, qr[g]);
+    cp_async_wait<1>();
+    __syncwarp();
 
-    // ---- scores of this warp's 64 keys ----
-    const int w_begin = c_begin + warp * DEC_KEYS_PER_WARP;
-#pragma unroll 4
+    // ---- scores ----
+#pragma unroll 2
     for (int it = 0; it < DEC_KEYS_PER_WARP / 4; ++it) {
         const int slot = it * 4 + quad;
         const int key = w_begin + slot;
         const bool valid = key < len && key >= lo;
         float kv[DPL];
-        if (valid) {
-            const size_t page = (size_t)table[key / page_size];
-            load_slice(k_cache + ((page * K + kh) * page_size + (size_t)(key % page_size)) * D, sub, kv);
-        } else {
-#pragma unroll
-            for (int e = 0; e < DPL; ++e) kv[e] = 0.0f;
-        }
+        load_slice_smem(sK + slot * D, sub, kv);
 #pragma unroll
         for (int g = 0; g < GROUP; ++g) {
             float dot = 0.0f;
@@ -109,41 +140,43 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_split_kernel(
     float m_w[GROUP], l_w[GROUP];
 #pragma unroll
     for (int g = 0; g < GROUP; ++g) {
-        const float a = s_p[warp][g][lane], b = s_p[warp][g][lane + 32];
-        const float m = warp_max(fmaxf(a, b));
+        float sc[DEC_KEYS_PER_WARP / 32];
+        float m = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < DEC_KEYS_PER_WARP / 32; ++i) { sc[i] = s_p[warp][g][lane + 32 * i]; m = fmaxf(m, sc[i]); }
+        m = warp_max(m);
         const float base = m == -INFINITY ? 0.0f : m;     // a warp whose keys are all masked contributes nothing
-        const float pa = expf(a - base), pb = expf(b - base);
-        __syncwarp();
-        s_p[warp][g][lane] = pa;
-        s_p[warp][g][lane + 32] = pb;
+        float sum = 0.0f;
+#pragma unroll
+        for (int i = 0; i < DEC_KEYS_PER_WARP / 32; ++i) { const float p = expf(sc[i] - base); s_p[warp][g][lane + 32 * i] = p; sum += p; }
         m_w[g] = m;
-        l_w[g] = warp_sum(pa + pb);
+        l_w[g] = warp_sum(sum);
     }
+    cp_async_wait<0>();
     __syncwarp();
 
-    // ---- sum of p * V over the same keys ----
+    // ---- sum of p * V ----
     float acc[GROUP][DPL];
 #pragma unroll
     for (int g = 0; g < GROUP; ++g)
 #pragma unroll
         for (int e = 0; e < DPL; ++e) acc[g][e] = 0.0f;
-#pragma unroll 4
+#pragma unroll 2
     for (int it = 0; it < DEC_KEYS_PER_WARP / 4; ++it) {
         const int slot = it * 4 + quad;
-        const int key = w_begin + slot;
-        if (key < len && key >= lo) {
-            float vv[DPL];
-            const size_t page = (size_t)table[key / page_size];
-            load_slice(v_cache + ((page * K + kh) * page_size + (size_t)(key % page_size)) * D, sub, vv);
+        float vv[DPL];
+        load_slice_smem(sV + slot * D, sub, vv);
 #pragma unroll
-            for (int g = 0; g < GROUP; ++g) {
-                const float p = s_p[warp][g][slot];
+        for (int g = 0; g < GROUP; ++g) {
+            const float p = s_p[warp][g][slot];
 #pragma unroll
-                for (int e = 0; e < DPL; ++e) acc[g][e] = fmaf(p, vv[e], acc[g][e]);
-            }
+            for (int e = 0; e < DPL; ++e) acc[g][e] = fmaf(p, vv[e], acc[g][e]);
         }
     }
     // the four key quads of the warp hold partial sums: add them, then the four warps through shared memory
+    // (the key/value buffers are free now: each warp's accumulators go where its keys were)
+    float* s_acc = reinterpret_cast<float*>(sK);              // [GROUP][D] floats per warp: GROUP*D*4 <= 2*KEYS*D*2 bytes
+    __syncwarp();
 #pragma unroll
     for (int g = 0; g < GROUP; ++g)
 #pragma unroll
@@ -151,13 +184,15 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_split_kernel(
             float a = acc[g][e];
             a += __shfl_xor_sync(0xffffffffu, a, 8);
             a += __shfl_xor_sync(0xffffffffu, a, 16);
-            if (quad == 0) s_acc[warp][g][slice_dim(sub, e)] = a;
+            if (quad == 0) s_acc[g * D + slice_dim(sub, e)] = a;
         }
     if (lane == 0) {
 #pragma unroll
         for (int g = 0; g < GROUP; ++g) { s_m[warp][g] = m_w[g]; s_l[warp][g] = l_w[g]; }
     }
     __syncthreads();
+    const float* all_acc = reinterpret_cast<const float*>(dec_smem);
+    constexpr int WARP_FLOATS = 2 * DEC_KEYS_PER_WARP * D / 2;    // a warp's buffer, in floats
     for (int idx = threadIdx.x; idx < GROUP * D; idx += DEC_WARPS * 32) {
         const int g = idx / D, dd = idx % D;
         float m = -INFINITY;
@@ -167,7 +202,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_split_kernel(
 #pragma unroll
         for (int w = 0; w < DEC_WARPS; ++w) {
             const float f = s_m[w][g] == -INFINITY ? 0.0f : expf(s_m[w][g] - m);
-            a = fmaf(s_acc[w][g][dd], f, a);
+            a = fmaf(all_acc[w * WARP_FLOATS + g * D + dd], f, a);
             l = fmaf(s_l[w][g], f, l);
         }
         const size_t at = ((size_t)r * H + kh * GROUP + g) * max_chunks + chunk;
@@ -384,14 +419,20 @@ MB_API int mb_attn_group() { return GROUP; }
 MB_API int mb_attn_decode_chunk() { return DEC_CHUNK; }
 
 // Decode: q/out rows 0..requests-1 are the single new tokens of requests 0..requests-1.  part_acc holds
-// requests*H*max_chunks*HEAD_DIM floats and part_ml requests*H*max_chunks*2; max_chunks >= ceil(longest/256).
+// requests*H*max_chunks*HEAD_DIM floats and part_ml requests*H*max_chunks*2; max_chunks >= ceil(longest/128).
 MB_API int mb_attn_decode(const void* q, const void* k_cache, const void* v_cache, void* out, const int* block_table,
                           int max_pages, const int* seq_lens, int requests, int K, int page_size, float scale, int window,
                           float* part_acc, float* part_ml, int max_chunks, cudaStream_t s) {
     if (requests <= 0) return 0;
     if (max_chunks <= 0 || K <= 0) return MB_ERR_BAD_SIZE;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
     dim3 grid(max_chunks, K, requests);
-    attn_decode_split_kernel<<<grid, DEC_WARPS * 32, 0, s>>>((const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, block_table,
+    attn_decode_split_kernel<<<grid, DEC_WARPS * 32, DEC_SMEM, s>>>((const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, block_table,
                                                              max_pages, seq_lens, K, page_size, scale, window, part_acc, part_ml,
                                                              max_chunks);
     int rc = mb_last_error();

@@ -58,3 +58,6 @@ class StepContext:
     spans: List[Span]
     workspace: Workspace
     extras: Dict[str, object] = field(default_factory=dict)
+    #: set for captured decode steps: fixed number of key chunks and the scratch the capture owns
+    attn_chunks: int = 0
+    attn_scratch: object = None

@@ -82,7 +82,8 @@ class Generation:
 class Engine:
     def __init__(self, model: Union[str, None] = None, *, config: Optional[ModelConfig] = None, seed: int = 0,
                  dtype="bfloat16", ctx: Optional[int] = None, page_size: int = 16, num_pages: Optional[int] = None,
-                 max_batch: int = 64, token_budget: int = 2048, device="cuda:0", _rt: Optional[Runtime] = None):
+                 max_batch: int = 64, token_budget: int = 2048, device="cuda:0", cuda_graphs: bool = True,
+                 _rt: Optional[Runtime] = None):
         """``model``: a folder with config.json and model.safetensors; or ``config`` + ``seed`` for
         random weights.  ``num_pages``: pages per cache group (default: enough for ``max_batch``
         sequences of ``ctx`` positions)."""
@@ -104,6 +105,9 @@ class Engine:
                                   self.num_pages, max_requests=max_batch)
         self.cache.allocate(self.rt.device, self.rt.dtype)
         self.runner = Runner(self.model, self.cache, self.rt, self.ctx)
+        if cuda_graphs and self.rt.device.type == "cuda":
+            sizes = [b for b in (1, 2, 4, 8, 16, 32, 64, 128, 256) if b < max_batch] + [max_batch]
+            self.runner.enable_graphs(sizes)
         self.max_batch, self.token_budget = max_batch, token_budget
         self.scheduler = Scheduler(self.cache, max_batch, token_budget, self.ctx)
         self._requests: Dict[Hashable, Request] = {}

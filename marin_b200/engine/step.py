@@ -99,24 +99,26 @@ class Runner:
             if new_len > self.max_seq_len:
                 raise StepError(f"request {e.req_id!r}: context full ({new_len} positions needed, capacity {self.max_seq_len})")
 
-    def build_context(self, entries: Sequence[StepEntry], pad_requests: int = 0) -> StepContext:
+    def build_context(self, entries: Sequence[StepEntry], pad_to: int = 0, static=None) -> StepContext:
         """Flattens the entries (single tokens first) into the arrays the kernels read, and copies
-        them to the device in one transfer."""
+        them to the device in one transfer.  ``pad_to`` (decode batches only) pads the batch with empty
+        requests up to a fixed size; ``static`` is then the device buffer a captured graph reads."""
         cache, page = self.cache, self.cache.page_size
         order = sorted(range(len(entries)), key=lambda i: (len(entries[i].tokens) != 1, i))
         num_decode = sum(1 for e in entries if len(e.tokens) == 1)
-        R = len(entries)
-        T = sum(len(e.tokens) for e in entries)
+        real_R = len(entries)
+        real_T = sum(len(e.tokens) for e in entries)
+        R, T = (pad_to, pad_to) if pad_to else (real_R, real_T)
         maxb = self.max_pages_per_seq
         G = len(cache.groups)
         tok = np.zeros(T, np.int32)
         pos = np.zeros(T, np.int32)
-        req = np.zeros(T, np.int32)
-        cu = np.zeros(R + 1, np.int32)
+        req = np.arange(T, dtype=np.int32) if pad_to else np.zeros(T, np.int32)
+        cu = np.arange(R + 1, dtype=np.int32) if pad_to else np.zeros(R + 1, np.int32)
         lens = np.zeros(R, np.int32)
         slots = np.zeros(R, np.int32)
         tables = np.zeros((G, R, maxb), np.int32)
-        slot_maps = np.zeros((G, T), np.int32)
+        slot_maps = np.full((G, T), -1, np.int32)
         spans: List[Span] = []
         flat_start: Dict[int, int] = {}
         at = 0
@@ -138,23 +140,33 @@ class Runner:
                 slot_maps[g, at:at + n] = ids[p // page] * page + (p % page)
             spans.append(Span(row, e.req_id, at, n, rc.length, rc.slot))
             at += n
-        rows: List[int] = []
-        for i, e in enumerate(entries):
-            rows.extend(flat_start[i] + int(w) for w in e.want)
-        logit_rows = np.asarray(rows, np.int32)
+        if pad_to:
+            logit_rows = np.arange(pad_to, dtype=np.int32)
+            num_rows = pad_to
+        else:
+            rows: List[int] = []
+            for i, e in enumerate(entries):
+                rows.extend(flat_start[i] + int(w) for w in e.want)
+            logit_rows = np.asarray(rows, np.int32)
+            num_rows = len(rows)
         parts = [tok, pos, req, cu, lens, slots, logit_rows, tables.reshape(-1), slot_maps.reshape(-1)]
-        packed = np.concatenate(parts) if parts else np.zeros(0, np.int32)
-        host = torch.from_numpy(packed)
-        if self.rt.device.type == "cuda":
-            host = host.pin_memory()
-        dev = host.to(self.rt.device, non_blocking=True)
+        packed = np.concatenate(parts)
+        if static is not None:
+            host, dev = static
+            host.numpy()[:] = packed
+            dev.copy_(host, non_blocking=True)
+        else:
+            host = torch.from_numpy(packed)
+            if self.rt.device.type == "cuda":
+                host = host.pin_memory()
+            dev = host.to(self.rt.device, non_blocking=True)
         views, at = [], 0
         for p in parts:
             views.append(dev[at:at + p.size])
             at += p.size
         d_tok, d_pos, d_req, d_cu, d_lens, d_slots, d_rows, d_tables, d_maps = views
         return StepContext(
-            num_tokens=T, num_requests=R, num_decode=num_decode, num_logit_rows=len(rows),
+            num_tokens=T, num_requests=R, num_decode=R if pad_to else num_decode, num_logit_rows=num_rows,
             max_query_len=max(len(e.tokens) for e in entries), max_seq_len=int(lens.max()),
             token_ids=d_tok, positions=d_pos, req_index=d_req, cu_tokens=d_cu, seq_lens=d_lens,
             state_slots=d_slots, logit_rows=d_rows,
@@ -162,6 +174,76 @@ class Runner:
             group_slot_mappings=[d_maps.view(G, T)[g] for g in range(G)] if G else [],
             spans=spans, workspace=self.workspace,
         )
+
+    def packed_size(self, pad_to: int) -> int:
+        G = len(self.cache.groups)
+        return pad_to * 3 + (pad_to + 1) + pad_to * 2 + pad_to + G * pad_to * self.max_pages_per_seq + G * pad_to
+
+    # ---- decode steps as CUDA graphs -----------------------------------------------------------------------
+    def enable_graphs(self, batch_sizes: Sequence[int] = (1, 2, 4, 8, 16, 32, 64)) -> None:
+        """Steps in which every request brings exactly one token are replayed from a CUDA graph captured per
+        padded batch size: the kernels' arguments live in one static device buffer that each step overwrites.
+        Mixers that keep their state through Python-side loops cannot be captured; graphs are then left off."""
+        if self.cache.state_needs:
+            return
+        self.graph_sizes = sorted(set(int(b) for b in batch_sizes))
+        self.graphs: Dict[int, dict] = {}
+
+    def _graph_for(self, bucket: int, entries: Sequence[StepEntry]) -> dict:
+        g = self.graphs.get(bucket)
+        if g is not None:
+            return g
+        from ..kernels import ops
+
+        size = self.packed_size(bucket)
+        host = torch.zeros(size, dtype=torch.int32).pin_memory()
+        dev = torch.zeros(size, dtype=torch.int32, device=self.rt.device)
+        chunks = -(-self.max_seq_len // ops.DECODE_CHUNK)
+        heads = max((b.mixer.heads for b in self.model.blocks if hasattr(b.mixer, "heads")), default=1)
+        hd = max((b.mixer.head_dim for b in self.model.blocks if hasattr(b.mixer, "head_dim")), default=1)
+        g = {"static": (host, dev), "workspace": Workspace(self.rt.device), "graph": None, "logits": None,
+             "attn_chunks": chunks,
+             "attn_scratch": (torch.empty(bucket * heads * chunks * hd, device=self.rt.device, dtype=torch.float32),
+                              torch.empty(bucket * heads * chunks * 2, device=self.rt.device, dtype=torch.float32))}
+        self.graphs[bucket] = g
+
+        def run():
+            ctx = self.build_context(entries, pad_to=bucket, static=g["static"])
+            ctx.workspace = g["workspace"]
+            ctx.attn_chunks, ctx.attn_scratch = g["attn_chunks"], g["attn_scratch"]
+            return self.model.forward(ctx, self.views)
+
+        run()                                    # warm up: builds kernels, sizes the workspace
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        ctx = self.build_context(entries, pad_to=bucket, static=g["static"])
+        ctx.workspace = g["workspace"]
+        ctx.attn_chunks, ctx.attn_scratch = g["attn_chunks"], g["attn_scratch"]
+        torch.cuda.synchronize()
+        launches = ops.launches
+        with torch.cuda.graph(graph):
+            g["logits"] = self.model.forward(ctx, self.views)
+        g["launches"] = ops.launches - launches
+        g["graph"] = graph
+        return g
+
+    def _step_graph(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        sizes = getattr(self, "graph_sizes", None)
+        if not sizes or any(len(e.tokens) != 1 for e in entries):
+            return None
+        bucket = next((b for b in sizes if b >= len(entries)), None)
+        if bucket is None:
+            return None
+        from ..kernels import ops
+
+        g = self._graph_for(bucket, entries)
+        self.build_context(entries, pad_to=bucket, static=g["static"])      # refresh the static buffer
+        g["graph"].replay()
+        ops.launches_extra(g["launches"])
+        rows = [i for i, e in enumerate(entries) for _ in e.want]
+        if rows == list(range(len(entries))):
+            return g["logits"][: len(entries)]
+        return g["logits"][torch.as_tensor(rows, device=self.rt.device, dtype=torch.long)]
 
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Runs the entries as one batch; returns float32 logits ``[wanted, vocab]`` on the device,
@@ -172,8 +254,10 @@ class Runner:
             raise OutOfPages(f"the step needs more pages than are free ({self.cache.free_pages()} free per group)")
         for req_id, new_len in wanted:
             self.cache.reserve(req_id, new_len)
-        ctx = self.build_context(entries)
-        logits = self.model.forward(ctx, self.views)
+        logits = self._step_graph(entries)
+        if logits is None:
+            ctx = self.build_context(entries)
+            logits = self.model.forward(ctx, self.views)
         for req_id, new_len in wanted:
             self.cache.commit(req_id, new_len)
         self.steps_run += 1

@@ -169,6 +169,7 @@ def qk_norm_rope_write(qkv, q_out, q_weight, k_weight, eps, positions, inv_freq,
 
 #: bf16 attention goes to the tensor-core / split-KV kernels when the head layout allows (False: the plain kernel)
 use_fast_attention = True
+DECODE_CHUNK = 128      # keys per CTA of the split-KV decode kernel (attention_fast.cu: DEC_CHUNK)
 _attn_scratch = {}
 
 
@@ -206,8 +207,8 @@ def attention(q, k_cache, v_cache, out, ctx, block_table, H, K, d, scale, window
         max_pages = block_table.shape[1]
         nd = ctx.num_decode
         if nd > 0:
-            chunks = getattr(ctx, "attn_chunks", None) or -(-ctx.max_seq_len // 256)
-            part_acc, part_ml = _decode_scratch(q.device, nd, H, chunks, d)
+            chunks = getattr(ctx, "attn_chunks", None) or -(-ctx.max_seq_len // DECODE_CHUNK)
+            part_acc, part_ml = getattr(ctx, "attn_scratch", None) or _decode_scratch(q.device, nd, H, chunks, d)
             _check(lib.mb_attn_decode(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), _c_int(max_pages),
                                       _ptr(ctx.seq_lens), _c_int(nd), _c_int(K), _c_int(page_size), _c_float(scale),
                                       _c_int(window), _ptr(part_acc), _ptr(part_ml), _c_int(chunks), _stream()), "attention (decode)")

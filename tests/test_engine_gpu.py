@@ -58,14 +58,17 @@ class Case:
         self.config, self.model = load_model(self.dir, self.rt)
         self.page = PAGE[name]
 
-    def runner(self, num_pages, max_requests=4):
+    def runner(self, num_pages, max_requests=4, graphs=False):
         from marin_b200.cache import CacheManager
         from marin_b200.engine import Runner
 
         cache = CacheManager(self.model.cache_needs(), [e.cache_of for e in self.model.spec.schedule], self.page,
                              num_pages, max_requests)
         cache.allocate(self.rt.device, self.rt.dtype)
-        return Runner(self.model, cache, self.rt, self.config.max_position_embeddings)
+        runner = Runner(self.model, cache, self.rt, self.config.max_position_embeddings)
+        if graphs:
+            runner.enable_graphs((1, 2, 4))          # single-token steps replay captured CUDA graphs
+        return runner
 
 
 @pytest.fixture(scope="module", params=[(n, d) for n in "ABC" for d in DTYPES], ids=lambda p: f"{p[0]}-{p[1]}")
@@ -80,8 +83,9 @@ def test_each_request_alone_and_whole(case):
     runner.cache.check()
 
 
-def test_most_in_one_step_then_the_last_32_one_by_one(case):
-    runner = case.runner(num_pages=-(-max(LENGTHS[case.name].values()) // case.page))
+@pytest.mark.parametrize("graphs", [False, True], ids=["eager", "graphs"])
+def test_most_in_one_step_then_the_last_32_one_by_one(case, graphs):
+    runner = case.runner(num_pages=-(-max(LENGTHS[case.name].values()) // case.page), graphs=graphs)
     for rid, toks in case.tokens.items():
         n = len(toks)
         tail = min(32, n - 1)
@@ -96,11 +100,12 @@ def test_portions_of_changing_size(case):
         close(run_portions(runner, rid, toks, portions(len(toks), cycle)), case.want[rid], case.dtype, f"portions {rid}")
 
 
-def test_mixed_batches_with_pages_used_again(case):
+@pytest.mark.parametrize("graphs", [False, True], ids=["eager", "graphs"])
+def test_mixed_batches_with_pages_used_again(case, graphs):
     rng = random.Random(7)
     lengths = LENGTHS[case.name]
     need = sorted((-(-n // case.page) for n in lengths.values()), reverse=True)
-    runner = case.runner(num_pages=sum(need[:4]))        # four live requests fit only through reuse
+    runner = case.runner(num_pages=sum(need[:4]), graphs=graphs)        # four live requests fit only through reuse
     steps = mixed_schedule(rng, lengths, max_live=4, decode_tail=9)
     assert any(len(e) >= 3 and any(n == 1 for _, n in e) and any(n > 1 for _, n in e) for e, _ in steps)
     got = run_mixed(runner, case.tokens, steps)
@@ -120,7 +125,7 @@ def test_long_decoding(case):
     n = case.raw["max_position_embeddings"]
     toks = random_prompt(random.Random(9), case.raw["vocab_size"], n)
     want = plain.forward(case.cfg, case.w, toks)
-    runner = case.runner(num_pages=-(-n // case.page))
+    runner = case.runner(num_pages=-(-n // case.page), graphs=True)
     close(run_portions(runner, "long", toks, [5] + [1] * (n - 5)), want, case.dtype, "long decoding")
 
 
