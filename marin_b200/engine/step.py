@@ -152,9 +152,11 @@ class Runner:
         parts = [tok, pos, req, cu, lens, slots, logit_rows, tables.reshape(-1), slot_maps.reshape(-1)]
         packed = np.concatenate(parts)
         if static is not None:
-            host, dev = static
+            host, dev, copied = static
+            copied.synchronize()                 # the last step's copy has left the pinned buffer
             host.numpy()[:] = packed
             dev.copy_(host, non_blocking=True)
+            copied.record()
         else:
             host = torch.from_numpy(packed)
             if self.rt.device.type == "cuda":
@@ -201,7 +203,7 @@ class Runner:
         chunks = -(-self.max_seq_len // ops.DECODE_CHUNK)
         heads = max((b.mixer.heads for b in self.model.blocks if hasattr(b.mixer, "heads")), default=1)
         hd = max((b.mixer.head_dim for b in self.model.blocks if hasattr(b.mixer, "head_dim")), default=1)
-        g = {"static": (host, dev), "workspace": Workspace(self.rt.device), "graph": None, "logits": None,
+        g = {"static": (host, dev, torch.cuda.Event()), "workspace": Workspace(self.rt.device), "graph": None, "logits": None,
              "attn_chunks": chunks,
              "attn_scratch": (torch.empty(bucket * heads * chunks * hd, device=self.rt.device, dtype=torch.float32),
                               torch.empty(bucket * heads * chunks * 2, device=self.rt.device, dtype=torch.float32))}
