@@ -22,7 +22,7 @@
 #error "compile with -DGROUP=<query heads per kv head, at most 8>"
 #endif
 static_assert(HEAD_DIM % 16 == 0 && HEAD_DIM >= 16 && HEAD_DIM <= 128, "head size must be a multiple of 16 up to 128");
-static_assert(GROUP * 4 <= 2 * (128 / 4) && GROUP >= 1 && GROUP <= 8, "1 to 8 query heads per kv head");
+static_assert(GROUP >= 1 && GROUP <= 8, "1 to 8 query heads per kv head");
 
 #define D HEAD_DIM
 #define DEC_CHUNK 128                 // keys per CTA
@@ -57,189 +57,6 @@ __device__ __forceinline__ void load_slice(const bf16* row, int sub, float* dst)
 // The dim a lane's element e stands for.
 __device__ __forceinline__ int slice_dim(int sub, int e) { return (e / VW) * (8 * VW) + sub * VW + (e % VW); }
 
-// 16 bytes from global to shared memory without passing through registers.
-__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-
-// Reads this lane's DPL elements of a row that lies in shared memory.
-__device__ __forceinline__ void load_slice_smem(const bf16* row, int sub, float* dst) { load_slice(row, sub, dst); }
-
-#define DEC_SMEM (DEC_WARPS * 2 * DEC_KEYS_PER_WARP * D * 2)
-
-// Every warp first asks for all of its keys and values (cp.async, so that they are all in flight at once),
-// then computes from shared memory: scores, softmax over its keys, p * V.
-__global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_split_kernel(
-    const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
-    const int* __restrict__ block_table, int max_pages, const int* __restrict__ seq_lens, int K, int page_size,
-    float scale, int window, float* __restrict__ part_acc, float* __restrict__ part_ml, int max_chunks) {
-    extern __shared__ __align__(16) uint8_t dec_smem[];
-    __shared__ float s_p[DEC_WARPS][GROUP][DEC_KEYS_PER_WARP];
-    __shared__ float s_m[DEC_WARPS][GROUP], s_l[DEC_WARPS][GROUP];
-    const int chunk = blockIdx.x, kh = blockIdx.y, r = blockIdx.z;
-    const int H = K * GROUP;
-    const int len = seq_lens[r];
-    const int pos = len - 1;
-    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-    const int c_begin = chunk * DEC_CHUNK, c_end = min(len, c_begin + DEC_CHUNK);
-    if (c_begin >= len || c_end <= lo) return;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int sub = lane & 7, quad = lane >> 3;
-    const int* table = block_table + (size_t)r * max_pages;
-    bf16* sK = reinterpret_cast<bf16*>(dec_smem) + (size_t)warp * 2 * DEC_KEYS_PER_WARP * D;
-    bf16* sV = sK + DEC_KEYS_PER_WARP * D;
-    const int w_begin = c_begin + warp * DEC_KEYS_PER_WARP;
-
-    // ---- ask for the warp's keys, then its values: 16-byte pieces, a row of D*2 bytes is D/8 pieces ----
-    constexpr int PIECES = D / 8;
-#pragma unroll
-    for (int which = 0; which < 2; ++which) {
-        const bf16* cache = which == 0 ? k_cache : v_cache;
-        bf16* dst = which == 0 ? sK : sV;
-#pragma unroll 4
-        for (int idx = lane; idx < DEC_KEYS_PER_WARP * PIECES; idx += 32) {
-            const int slot = idx / PIECES, piece = idx % PIECES;
-            const int key = w_begin + slot;
-            if (key < len && key >= lo) {
-                const size_t page = (size_t)table[key / page_size];
-                cp_async16(dst + slot * D + piece * 8, cache + ((page * K + kh) * page_size + (size_t)(key % page_size)) * D + piece * 8);
-            } else {
-                *reinterpret_cast<uint4*>(dst + slot * D + piece * 8) = make_uint4(0, 0, 0, 0);
-            }
-        }
-        cp_async_commit();
-    }
-    float qr[GROUP][DPL];
-#pragma unroll
-    for (int g = 0; g < GROUP; ++g) load_slice(q + ((size_t)r * H + kh * GROUP + g) * D, sub, qr[g]);
-    cp_async_wait<1>();
-    __syncwarp();
-
-    // ---- scores ----
-#pragma unroll 2
-    for (int it = 0; it < DEC_KEYS_PER_WARP / 4; ++it) {
-        const int slot = it * 4 + quad;
-        const int key = w_begin + slot;
-        const bool valid = key < len && key >= lo;
-        float kv[DPL];
-        load_slice_smem(sK + slot * D, sub, kv);
-#pragma unroll
-        for (int g = 0; g < GROUP; ++g) {
-            float dot = 0.0f;
-#pragma unroll
-            for (int e = 0; e < DPL; ++e) dot = fmaf(qr[g][e], kv[e], dot);
-            dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-            dot += __shfl_xor_sync(0xffffffffu, dot, 2);
-            dot += __shfl_xor_sync(0xffffffffu, dot, 4);
-            if (sub == 0) s_p[warp][g][slot] = valid ? dot * scale : -INFINITY;
-        }
-    }
-    __syncwarp();
-    float m_w[GROUP], l_w[GROUP];
-#pragma unroll
-    for (int g = 0; g < GROUP; ++g) {
-        float sc[DEC_KEYS_PER_WARP / 32];
-        float m = -INFINITY;
-#pragma unroll
-        for (int i = 0; i < DEC_KEYS_PER_WARP / 32; ++i) { sc[i] = s_p[warp][g][lane + 32 * i]; m = fmaxf(m, sc[i]); }
-        m = warp_max(m);
-        const float base = m == -INFINITY ? 0.0f : m;     // a warp whose keys are all masked contributes nothing
-        float sum = 0.0f;
-#pragma unroll
-        for (int i = 0; i < DEC_KEYS_PER_WARP / 32; ++i) { const float p = expf(sc[i] - base); s_p[warp][g][lane + 32 * i] = p; sum += p; }
-        m_w[g] = m;
-        l_w[g] = warp_sum(sum);
-    }
-    cp_async_wait<0>();
-    __syncwarp();
-
-    // ---- sum of p * V ----
-    float acc[GROUP][DPL];
-#pragma unroll
-    for (int g = 0; g < GROUP; ++g)
-#pragma unroll
-        for (int e = 0; e < DPL; ++e) acc[g][e] = 0.0f;
-#pragma unroll 2
-    for (int it = 0; it < DEC_KEYS_PER_WARP / 4; ++it) {
-        const int slot = it * 4 + quad;
-        float vv[DPL];
-        load_slice_smem(sV + slot * D, sub, vv);
-#pragma unroll
-        for (int g = 0; g < GROUP; ++g) {
-            const float p = s_p[warp][g][slot];
-#pragma unroll
-            for (int e = 0; e < DPL; ++e) acc[g][e] = fmaf(p, vv[e], acc[g][e]);
-        }
-    }
-    // the four key quads of the warp hold partial sums: add them, then the four warps through shared memory
-    // (the key/value buffers are free now: each warp's accumulators go where its keys were)
-    float* s_acc = reinterpret_cast<float*>(sK);              // [GROUP][D] floats per warp: GROUP*D*4 <= 2*KEYS*D*2 bytes
-    __syncwarp();
-#pragma unroll
-    for (int g = 0; g < GROUP; ++g)
-#pragma unroll
-        for (int e = 0; e < DPL; ++e) {
-            float a = acc[g][e];
-            a += __shfl_xor_sync(0xffffffffu, a, 8);
-            a += __shfl_xor_sync(0xffffffffu, a, 16);
-            if (quad == 0) s_acc[g * D + slice_dim(sub, e)] = a;
-        }
-    if (lane == 0) {
-#pragma unroll
-        for (int g = 0; g < GROUP; ++g) { s_m[warp][g] = m_w[g]; s_l[warp][g] = l_w[g]; }
-    }
-    __syncthreads();
-    const float* all_acc = reinterpret_cast<const float*>(dec_smem);
-    constexpr int WARP_FLOATS = 2 * DEC_KEYS_PER_WARP * D / 2;    // a warp's buffer, in floats
-    for (int idx = threadIdx.x; idx < GROUP * D; idx += DEC_WARPS * 32) {
-        const int g = idx / D, dd = idx % D;
-        float m = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < DEC_WARPS; ++w) m = fmaxf(m, s_m[w][g]);
-        float a = 0.0f, l = 0.0f;
-#pragma unroll
-        for (int w = 0; w < DEC_WARPS; ++w) {
-            const float f = s_m[w][g] == -INFINITY ? 0.0f : expf(s_m[w][g] - m);
-            a = fmaf(all_acc[w * WARP_FLOATS + g * D + dd], f, a);
-            l = fmaf(s_l[w][g], f, l);
-        }
-        const size_t at = ((size_t)r * H + kh * GROUP + g) * max_chunks + chunk;
-        part_acc[at * D + dd] = a;
-        if (dd == 0) { part_ml[at * 2] = m; part_ml[at * 2 + 1] = l; }
-    }
-}
-
-// Combines the chunks of one (request, head): out = sum_c acc_c e^(m_c - M) / sum_c l_c e^(m_c - M).
-__global__ void __launch_bounds__(D) attn_decode_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
-                                                           const int* __restrict__ seq_lens, int H, int window, int max_chunks,
-                                                           bf16* __restrict__ out) {
-    const int h = blockIdx.x, r = blockIdx.y, dd = threadIdx.x;
-    const int len = seq_lens[r];
-    if (len <= 0) return;
-    const int pos = len - 1;
-    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-    const int c_first = lo / DEC_CHUNK, c_last = pos / DEC_CHUNK;
-    const size_t base = ((size_t)r * H + h) * max_chunks;
-    float m = -INFINITY;
-    for (int c = c_first; c <= c_last; ++c) m = fmaxf(m, part_ml[(base + c) * 2]);
-    float a = 0.0f, l = 0.0f;
-    for (int c = c_first; c <= c_last; ++c) {
-        const float mc = part_ml[(base + c) * 2];
-        const float f = mc == -INFINITY ? 0.0f : expf(mc - m);
-        a = fmaf(part_acc[(base + c) * D + dd], f, a);
-        l = fmaf(part_ml[(base + c) * 2 + 1], f, l);
-    }
-    out[((size_t)r * H + h) * D + dd] = __float2bfloat16_rn(a / l);
-}
-
-// ---- prefill ------------------------------------------------------------------------------------------------------
-#define PF_BM 64
-#define PF_BN 64
-#define PF_LD (D + 8)                 // padded row: 16-byte shift per row keeps ldmatrix free of bank conflicts
-#define PF_SMEM (3 * PF_BM * PF_LD * 2)
-
 __device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
 }
@@ -259,6 +76,202 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
 }
+
+// 16 bytes from global to shared memory without passing through registers.
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+#define LDP (D + 8)                   // padded row of a tile in shared memory (elements): ldmatrix without bank conflicts
+#define DEC_Q_BYTES (16 * LDP * 2)
+#define DEC_WARP_BYTES (2 * DEC_KEYS_PER_WARP * LDP * 2)
+#define DEC_SMEM (DEC_Q_BYTES + DEC_WARPS * DEC_WARP_BYTES)
+static_assert(GROUP * D * 4 <= DEC_WARP_BYTES, "a warp's accumulators are written over its key buffer");
+
+// Every warp first asks for all of its keys and values (cp.async: they are all in flight at once), then
+// works from shared memory on the tensor cores: the GROUP query heads are rows 0..GROUP-1 of a 16-row
+// tile (the other rows are zero), S = Q K^T and O = P V are mma.sync.m16n8k16, the softmax over the warp's
+// keys is float32 in the exp2 domain.  Partial (m, l, acc) per chunk: m is in log2 units.
+__global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_split_kernel(
+    const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
+    const int* __restrict__ block_table, int max_pages, const int* __restrict__ seq_lens, int K, int page_size,
+    float scale, int window, float* __restrict__ part_acc, float* __restrict__ part_ml, int max_chunks) {
+    extern __shared__ __align__(16) uint8_t dec_smem[];
+    __shared__ float s_m[DEC_WARPS][8], s_l[DEC_WARPS][8];
+    const int chunk = blockIdx.x, kh = blockIdx.y, r = blockIdx.z;
+    const int H = K * GROUP;
+    const int len = seq_lens[r];
+    const int pos = len - 1;
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int c_begin = chunk * DEC_CHUNK, c_end = min(len, c_begin + DEC_CHUNK);
+    if (c_begin >= len || c_end <= lo) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int* table = block_table + (size_t)r * max_pages;
+    bf16* sQ = reinterpret_cast<bf16*>(dec_smem);
+    bf16* sK = reinterpret_cast<bf16*>(dec_smem + DEC_Q_BYTES + (size_t)warp * DEC_WARP_BYTES);
+    bf16* sV = sK + DEC_KEYS_PER_WARP * LDP;
+    const int w_begin = c_begin + warp * DEC_KEYS_PER_WARP;
+
+    // ---- ask for the warp's keys, then its values: 16-byte pieces, a row is D/8 pieces ----
+    constexpr int PIECES = D / 8;
+#pragma unroll
+    for (int which = 0; which < 2; ++which) {
+        const bf16* cache = which == 0 ? k_cache : v_cache;
+        bf16* dst = which == 0 ? sK : sV;
+#pragma unroll 4
+        for (int idx = lane; idx < DEC_KEYS_PER_WARP * PIECES; idx += 32) {
+            const int slot = idx / PIECES, piece = idx % PIECES;
+            const int key = w_begin + slot;
+            if (key < len && key >= lo) {
+                const size_t page = (size_t)table[key / page_size];
+                cp_async16(dst + slot * LDP + piece * 8, cache + ((page * K + kh) * page_size + (size_t)(key % page_size)) * D + piece * 8);
+            } else {
+                *reinterpret_cast<uint4*>(dst + slot * LDP + piece * 8) = make_uint4(0, 0, 0, 0);
+            }
+        }
+        cp_async_commit();
+    }
+    // the query tile: GROUP heads, the rest of the 16 rows zero
+    for (int idx = threadIdx.x; idx < 16 * PIECES; idx += DEC_WARPS * 32) {
+        const int row = idx / PIECES, piece = idx % PIECES;
+        uint4 val = make_uint4(0, 0, 0, 0);
+        if (row < GROUP) val = *reinterpret_cast<const uint4*>(q + ((size_t)r * H + kh * GROUP + row) * D + piece * 8);
+        *reinterpret_cast<uint4*>(sQ + row * LDP + piece * 8) = val;
+    }
+    __syncthreads();
+    uint32_t qa[D / 16][4];
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+        const int row = (lane & 7) + ((lane >> 3) & 1) * 8;
+        ldsm_x4((uint32_t)__cvta_generic_to_shared(sQ + row * LDP + kk * 16 + (lane >> 4) * 8), qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3]);
+    }
+    cp_async_wait<1>();
+    __syncwarp();
+
+    // ---- scores of the warp's keys: S = Q K^T ----
+    constexpr int NT = DEC_KEYS_PER_WARP / 8;
+    float sc[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) { sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.0f; }
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+#pragma unroll
+        for (int j = 0; j < NT; j += 2) {
+            uint32_t b0, b1, b2, b3;
+            const int key = j * 8 + (lane & 7) + (lane >> 4) * 8;
+            ldsm_x4((uint32_t)__cvta_generic_to_shared(sK + key * LDP + kk * 16 + ((lane >> 3) & 1) * 8), b0, b1, b2, b3);
+            mma_bf16_16816(sc[j], qa[kk], b0, b1);
+            mma_bf16_16816(sc[j + 1], qa[kk], b2, b3);
+        }
+    }
+    // this thread's row (= query head) is lane / 4; only rows below GROUP mean anything
+    const float sl2 = scale * 1.4426950408889634f;
+    float m = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+        const int key = w_begin + j * 8 + 2 * (lane & 3);
+        sc[j][0] = (key < len && key >= lo) ? sc[j][0] * sl2 : -INFINITY;
+        sc[j][1] = (key + 1 < len && key + 1 >= lo) ? sc[j][1] * sl2 : -INFINITY;
+        m = fmaxf(m, fmaxf(sc[j][0], sc[j][1]));
+    }
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+    const float base = m == -INFINITY ? 0.0f : m;          // a warp whose keys are all masked contributes nothing
+    float l = 0.0f;
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+        sc[j][0] = exp2f(sc[j][0] - base);
+        sc[j][1] = exp2f(sc[j][1] - base);
+        l += sc[j][0] + sc[j][1];
+    }
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    cp_async_wait<0>();
+    __syncwarp();
+
+    // ---- O = P V ----
+    float o[D / 8][4];
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
+#pragma unroll
+    for (int ks = 0; ks < DEC_KEYS_PER_WARP / 16; ++ks) {
+        uint32_t pa[4];
+        pa[0] = pack_bf16(sc[2 * ks][0], sc[2 * ks][1]);
+        pa[1] = 0u;
+        pa[2] = pack_bf16(sc[2 * ks + 1][0], sc[2 * ks + 1][1]);
+        pa[3] = 0u;
+#pragma unroll
+        for (int dt = 0; dt < D / 8; dt += 2) {
+            uint32_t b0, b1, b2, b3;
+            const int key = ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+            ldsm_x4_trans((uint32_t)__cvta_generic_to_shared(sV + key * LDP + dt * 8 + (lane >> 4) * 8), b0, b1, b2, b3);
+            mma_bf16_16816(o[dt], pa, b0, b1);
+            mma_bf16_16816(o[dt + 1], pa, b2, b3);
+        }
+    }
+    // each warp leaves (m, l, acc) of its keys in shared memory (over its key buffer), then the CTA adds the warps
+    float* s_acc = reinterpret_cast<float*>(sK);
+    __syncwarp();
+    const int g_row = lane >> 2;
+    if (g_row < GROUP) {
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) {
+            s_acc[g_row * D + i * 8 + 2 * (lane & 3)] = o[i][0];
+            s_acc[g_row * D + i * 8 + 2 * (lane & 3) + 1] = o[i][1];
+        }
+        if ((lane & 3) == 0) { s_m[warp][g_row] = m; s_l[warp][g_row] = l; }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < GROUP * D; idx += DEC_WARPS * 32) {
+        const int g = idx / D, dd = idx % D;
+        float mm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < DEC_WARPS; ++w) mm = fmaxf(mm, s_m[w][g]);
+        float a = 0.0f, ll = 0.0f;
+#pragma unroll
+        for (int w = 0; w < DEC_WARPS; ++w) {
+            const float f = s_m[w][g] == -INFINITY ? 0.0f : exp2f(s_m[w][g] - mm);
+            const float* wacc = reinterpret_cast<const float*>(dec_smem + DEC_Q_BYTES + (size_t)w * DEC_WARP_BYTES);
+            a = fmaf(wacc[g * D + dd], f, a);
+            ll = fmaf(s_l[w][g], f, ll);
+        }
+        const size_t at = ((size_t)r * H + kh * GROUP + g) * max_chunks + chunk;
+        part_acc[at * D + dd] = a;
+        if (dd == 0) { part_ml[at * 2] = mm; part_ml[at * 2 + 1] = ll; }
+    }
+}
+
+// Combines the chunks of one (request, head): out = sum_c acc_c 2^(m_c - M) / sum_c l_c 2^(m_c - M)
+// (the chunks' maxima are in log2 units).
+__global__ void __launch_bounds__(D) attn_decode_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
+                                                           const int* __restrict__ seq_lens, int H, int window, int max_chunks,
+                                                           bf16* __restrict__ out) {
+    const int h = blockIdx.x, r = blockIdx.y, dd = threadIdx.x;
+    const int len = seq_lens[r];
+    if (len <= 0) return;
+    const int pos = len - 1;
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int c_first = lo / DEC_CHUNK, c_last = pos / DEC_CHUNK;
+    const size_t base = ((size_t)r * H + h) * max_chunks;
+    float m = -INFINITY;
+    for (int c = c_first; c <= c_last; ++c) m = fmaxf(m, part_ml[(base + c) * 2]);
+    float a = 0.0f, l = 0.0f;
+    for (int c = c_first; c <= c_last; ++c) {
+        const float mc = part_ml[(base + c) * 2];
+        const float f = mc == -INFINITY ? 0.0f : exp2f(mc - m);
+        a = fmaf(part_acc[(base + c) * D + dd], f, a);
+        l = fmaf(part_ml[(base + c) * 2 + 1], f, l);
+    }
+    out[((size_t)r * H + h) * D + dd] = __float2bfloat16_rn(a / l);
+}
+
+// ---- prefill ------------------------------------------------------------------------------------------------------
+#define PF_BM 64
+#define PF_BN 64
+#define PF_LD LDP
+#define PF_SMEM (3 * PF_BM * PF_LD * 2)
 
 // Rows of one 64-key block of K or V into shared memory; keys past `k_last` are zero (their pages may not exist).
 __device__ __forceinline__ void load_kv_tile(bf16* dst, const bf16* __restrict__ cache, const int* __restrict__ table, int K, int kh,

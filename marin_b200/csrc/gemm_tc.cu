@@ -113,7 +113,7 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
                                                       const __grid_constant__ CUtensorMap map_x, void* __restrict__ out,
                                                       int mode, int T, int N, int K, int kb_per_split,
                                                       float* __restrict__ partials, int* __restrict__ counters,
-                                                      int* __restrict__ error_flag) {
+                                                      int* __restrict__ error_flag, int cluster_reduce) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     using L = TcSmem<BN>;
@@ -188,6 +188,43 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
     const int n = n0 + warp * 32 + lane;
     const int splits = gridDim.z;
     const bool direct = splits == 1;
+    if (cluster_reduce && !direct) {
+        // ---- split-K inside a thread-block cluster: the K slices of one tile are the CTAs of one cluster.  Each
+        // leaves its float32 partial tile in its own shared memory (the pipeline buffers are free now); after a
+        // cluster barrier CTA z adds rows [z*128/S, (z+1)*128/S) of all S partials, in slice order, reading its
+        // peers' tiles through distributed shared memory, and writes that part of the output.
+        float* red = reinterpret_cast<float*>(smem);                 // [BN][128]: red[t][row]
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 16) {
+            float v[16];
+            if (have) tmem_ld16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, v);
+            else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) v[j] = 0.0f;
+            }
+#pragma unroll
+            for (int j = 0; j < 16; ++j) red[(c0 + j) * TC_BM + warp * 32 + lane] = v[j];
+        }
+        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+        const int rows_per = TC_BM / splits;                         // splits is 2, 4 or 8
+        const int row_first = blockIdx.z * rows_per;
+        const int t_count = min(BN, T - t0);
+        const uint32_t red_addr = smem_u32(red);
+        for (int idx = threadIdx.x; idx < t_count * rows_per; idx += 128) {
+            const int tt = idx / rows_per, row = row_first + idx % rows_per;
+            float sum = 0.0f;
+            for (int z = 0; z < splits; ++z) {
+                uint32_t remote;
+                float pv;
+                asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(red_addr + (uint32_t)(tt * TC_BM + row) * 4u), "r"(z));
+                asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(pv) : "r"(remote) : "memory");
+                sum += pv;
+            }
+            if (n0 + row < N) store_out(out, mode, (size_t)(t0 + tt) * N + n0 + row, sum);
+        }
+        // nobody leaves while a peer may still read its tile
+        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    } else {
 #pragma unroll 1
     for (int c0 = 0; c0 < BN; c0 += 16) {
         float v[16];
@@ -208,7 +245,7 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
         }
     }
     if (!direct) {
-        // ---- split-K: the CTA that arrives last adds the slices in order ----
+        // ---- split-K through global scratch: the CTA that arrives last adds the slices in order ----
         __threadfence();
         __syncthreads();
         const int tile = blockIdx.y * gridDim.x + blockIdx.x;
@@ -229,6 +266,7 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
                 }
             }
         }
+    }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -271,16 +309,33 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int K, int box
 
 template <int BN, int STAGES>
 static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int mode, int T, int N, int K, int splits,
-                     int kb_per_split, float* partials, int* counters, int* error_flag, cudaStream_t s) {
+                     int kb_per_split, float* partials, int* counters, int* error_flag, int cluster_reduce, cudaStream_t s) {
     constexpr int smem = STAGES * TcSmem<BN>::STAGE_BYTES + 1024 + 256;
+    static_assert(STAGES * TcSmem<BN>::STAGE_BYTES >= BN * TC_BM * 4, "the cluster reduction reuses the pipeline buffers");
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    dim3 grid((N + TC_BM - 1) / TC_BM, (T + BN - 1) / BN, splits);
-    gemm_tc_kernel<BN, STAGES><<<grid, 128, smem, s>>>(mw, mx, out, mode, T, N, K, kb_per_split, partials, counters, error_flag);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((N + TC_BM - 1) / TC_BM, (T + BN - 1) / BN, splits);
+    cfg.blockDim = dim3(128);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    cfg.attrs = attr;
+    cfg.numAttrs = 0;
+    if (cluster_reduce && splits > 1) {
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 1;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = splits;
+        cfg.numAttrs = 1;
+    }
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, STAGES>, mw, mx, out, mode, T, N, K, kb_per_split, partials,
+                                       counters, error_flag, (cluster_reduce && splits > 1) ? 1 : 0);
+    if (e != cudaSuccess) return (int)e;
     return mb_last_error();
 }
 
@@ -290,8 +345,8 @@ MB_API int mb_gemm_tc_tiles(int T, int N, int bn) { return ((N + TC_BM - 1) / TC
 // x [T, K] bf16, w [N, K] bf16, out [T, N]: bf16 (mode 0), float32 (1), float32 += (2).  K must be a multiple
 // of 8 and both pointers 16-byte aligned (TMA).  splits > 1 needs partials (splits*T*N floats) and counters
 // (one zeroed int per tile).  bn in {16, 32, 64, 128, 256}.
-MB_API int mb_gemm_tc(const void* x, const void* w, void* out, int mode, int T, int N, int K, int bn, int splits,
-                      float* partials, int* counters, int* error_flag, cudaStream_t s) {
+static int gemm_tc_dispatch(const void* x, const void* w, void* out, int mode, int T, int N, int K, int bn, int splits,
+                            float* partials, int* counters, int* error_flag, int cluster_reduce, cudaStream_t s) {
     if (T <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return MB_ERR_BAD_SIZE;
     if (mode < 0 || mode > 2) return MB_ERR_BAD_DTYPE;
@@ -299,21 +354,42 @@ MB_API int mb_gemm_tc(const void* x, const void* w, void* out, int mode, int T, 
     if (splits < 1) splits = 1;
     if (splits > total_kb) splits = total_kb;
     int kb_per_split = (total_kb + splits - 1) / splits;
-    splits = (total_kb + kb_per_split - 1) / kb_per_split;
-    if (splits > 1 && (partials == nullptr || counters == nullptr)) return MB_ERR_BAD_SIZE;
+    if (cluster_reduce) {
+        // the cluster is the K slices: 2, 4 or 8 of them, none empty
+        if (splits != 1 && splits != 2 && splits != 4 && splits != 8) return MB_ERR_BAD_SIZE;
+        if ((splits - 1) * kb_per_split >= total_kb) return MB_ERR_BAD_SIZE;
+    } else {
+        splits = (total_kb + kb_per_split - 1) / kb_per_split;
+        if (splits > 1 && (partials == nullptr || counters == nullptr)) return MB_ERR_BAD_SIZE;
+    }
     CUtensorMap mw, mx;
     int rc = make_map(&mw, w, N, K, TC_BM);
     if (rc) return rc;
     rc = make_map(&mx, x, T, K, bn);
     if (rc) return rc;
     switch (bn) {
-        case 16: return launch_tc<16, 6>(mw, mx, out, mode, T, N, K, splits, kb_per_split, partials, counters, error_flag, s);
-        case 32: return launch_tc<32, 5>(mw, mx, out, mode, T, N, K, splits, kb_per_split, partials, counters, error_flag, s);
-        case 64: return launch_tc<64, 4>(mw, mx, out, mode, T, N, K, splits, kb_per_split, partials, counters, error_flag, s);
-        case 128: return launch_tc<128, 3>(mw, mx, out, mode, T, N, K, splits, kb_per_split, partials, counters, error_flag, s);
-        case 256: return launch_tc<256, 4>(mw, mx, out, mode, T, N, K, splits, kb_per_split, partials, counters, error_flag, s);
+        case 16: return launch_tc<16, 6>(mw, mx, out, mode, T, N, K, splits, kb_per_split, partials, counters, error_flag, cluster_reduce, s);
+        case 32: return launch_tc<32, 5>(mw, mx, out, mode, T, N, K, splits, kb_per_split, partials, counters, error_flag, cluster_reduce, s);
+        case 64: return launch_tc<64, 4>(mw, mx, out, mode, T, N, K, splits, kb_per_split, partials, counters, error_flag, cluster_reduce, s);
+        case 128: return launch_tc<128, 3>(mw, mx, out, mode, T, N, K, splits, kb_per_split, partials, counters, error_flag, cluster_reduce, s);
+        case 256: return launch_tc<256, 4>(mw, mx, out, mode, T, N, K, splits, kb_per_split, partials, counters, error_flag, cluster_reduce, s);
         default: return MB_ERR_BAD_SIZE;
     }
+}
+
+// x [T, K] bf16, w [N, K] bf16, out [T, N]: bf16 (mode 0), float32 (1), float32 += (2).  K must be a multiple
+// of 8 and both pointers 16-byte aligned (TMA).  splits > 1 needs partials (splits*T*N floats) and counters
+// (one zeroed int per tile).  bn in {16, 32, 64, 128, 256}.
+MB_API int mb_gemm_tc(const void* x, const void* w, void* out, int mode, int T, int N, int K, int bn, int splits,
+                      float* partials, int* counters, int* error_flag, cudaStream_t s) {
+    return gemm_tc_dispatch(x, w, out, mode, T, N, K, bn, splits, partials, counters, error_flag, 0, s);
+}
+
+// The same product with the K slices of a tile as one thread-block cluster (splits in {1, 2, 4, 8}): the slices
+// are added through distributed shared memory, no global scratch is touched.
+MB_API int mb_gemm_tc_cluster(const void* x, const void* w, void* out, int mode, int T, int N, int K, int bn, int splits,
+                              int* error_flag, cudaStream_t s) {
+    return gemm_tc_dispatch(x, w, out, mode, T, N, K, bn, splits, nullptr, nullptr, error_flag, 1, s);
 }
 
 // ---- the entry point that allocates nothing (see gemm_tc_noalloc.h) --------------------------------------------

@@ -117,13 +117,18 @@ def check_device_errors(device=None) -> None:
 
 
 def gemm_plan(T: int, N: int, K: int):
-    """Tokens per CTA and the number of K slices for the tensor-core kernel."""
+    """Tokens per CTA and the number of K slices (1, 2, 4 or 8: the CTAs of one cluster) for the tensor-core
+    kernel.  K is cut when there are fewer tiles than SMs, as far as every slice keeps at least 4 k-blocks."""
     bn = 16 if T <= 16 else 32 if T <= 32 else 64 if T <= 64 else 128
     tiles = -(-N // 128) * -(-T // bn)
     nkb = -(-K // 64)
     splits = 1
     if tiles < SM_COUNT:
-        splits = max(1, min(2 * SM_COUNT // tiles, nkb // 4, 16))
+        for cand in (8, 4, 2):
+            per = -(-nkb // cand)
+            if tiles * cand <= 2 * SM_COUNT + 32 and per >= 4 and (cand - 1) * per < nkb:
+                splits = cand
+                break
     return bn, splits
 
 
@@ -140,12 +145,9 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool =
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and T > 0):
         bn, splits = gemm_plan(T, N, K)
         s = _gemm_scratch(x.device)
-        while splits > 1 and splits * T * N > s["partials"].numel():
-            splits -= 1
         mode = 2 if accumulate else (0 if out.dtype == torch.bfloat16 else 1)
-        _check(_lib("mb_gemm_tc").mb_gemm_tc(_ptr(x), _ptr(w), _ptr(out), _c_int(mode), _c_int(T), _c_int(N), _c_int(K),
-                                            _c_int(bn), _c_int(splits), _ptr(s["partials"]), _ptr(s["counters"]),
-                                            _ptr(s["error"]), _stream()), "gemm (tensor cores)")
+        _check(_lib("mb_gemm_tc").mb_gemm_tc_cluster(_ptr(x), _ptr(w), _ptr(out), _c_int(mode), _c_int(T), _c_int(N), _c_int(K),
+                                                    _c_int(bn), _c_int(splits), _ptr(s["error"]), _stream()), "gemm (tensor cores)")
         return
     _check(_lib("mb_gemm_simple").mb_gemm_simple(_ptr(x), _code(x), _ptr(w), _code(w), _ptr(out), _code(out), _c_int(T),
                                                 _c_int(N), _c_int(K), _c_int(int(accumulate)), _stream()), "gemm")
