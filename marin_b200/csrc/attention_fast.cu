@@ -25,9 +25,7 @@ static_assert(HEAD_DIM % 16 == 0 && HEAD_DIM >= 16 && HEAD_DIM <= 128, "head siz
 static_assert(GROUP >= 1 && GROUP <= 8, "1 to 8 query heads per kv head");
 
 #define D HEAD_DIM
-#define DEC_CHUNK 128                 // keys per CTA
 #define DEC_WARPS 4
-#define DEC_KEYS_PER_WARP (DEC_CHUNK / DEC_WARPS)
 #define DPL (D / 8)                   // dims per lane: 8 lanes share one key
 #define VW (DPL % 8 == 0 ? 8 : (DPL % 4 == 0 ? 4 : 2))   // elements per vector load
 #define NV (DPL / VW)                 // vector loads per lane and key
@@ -85,19 +83,23 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 #define LDP (D + 8)                   // padded row of a tile in shared memory (elements): ldmatrix without bank conflicts
+#define DEC_STAGES 3                  // per-warp ring of 16-key stages
+#define DEC_STAGE_KEYS 16
 #define DEC_Q_BYTES (16 * LDP * 2)
-#define DEC_WARP_BYTES (2 * DEC_KEYS_PER_WARP * LDP * 2)
+#define DEC_STAGE_BYTES (2 * DEC_STAGE_KEYS * LDP * 2)          // keys then values
+#define DEC_WARP_BYTES (DEC_STAGES * DEC_STAGE_BYTES)
 #define DEC_SMEM (DEC_Q_BYTES + DEC_WARPS * DEC_WARP_BYTES)
-static_assert(GROUP * D * 4 <= DEC_WARP_BYTES, "a warp's accumulators are written over its key buffer");
+static_assert(GROUP * D * 4 <= DEC_WARP_BYTES, "a warp's accumulators are written over its stage buffers");
 
-// Every warp first asks for all of its keys and values (cp.async: they are all in flight at once), then
-// works from shared memory on the tensor cores: the GROUP query heads are rows 0..GROUP-1 of a 16-row
-// tile (the other rows are zero), S = Q K^T and O = P V are mma.sync.m16n8k16, the softmax over the warp's
-// keys is float32 in the exp2 domain.  Partial (m, l, acc) per chunk: m is in log2 units.
+// Decode.  A CTA takes `split_keys` consecutive keys (by absolute position) of one kv head of one request; each of
+// its four warps takes a quarter of them and walks it in stages of 16 keys through its own ring of cp.async
+// buffers (three stages in flight per warp, no block-wide barrier in the loop).  The GROUP query heads are rows
+// 0..GROUP-1 of a 16-row tile (the other rows are zero); S = Q K^T and O = P V are mma.sync.m16n8k16, the
+// softmax runs online in float32 in the exp2 domain.  Partial (m, l, acc) per CTA: m is in log2 units.
 __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_split_kernel(
     const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
     const int* __restrict__ block_table, int max_pages, const int* __restrict__ seq_lens, int K, int page_size,
-    float scale, int window, float* __restrict__ part_acc, float* __restrict__ part_ml, int max_chunks) {
+    float scale, int window, float* __restrict__ part_acc, float* __restrict__ part_ml, int max_chunks, int split_keys) {
     extern __shared__ __align__(16) uint8_t dec_smem[];
     __shared__ float s_m[DEC_WARPS][8], s_l[DEC_WARPS][8];
     const int chunk = blockIdx.x, kh = blockIdx.y, r = blockIdx.z;
@@ -105,34 +107,41 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_split_kernel(
     const int len = seq_lens[r];
     const int pos = len - 1;
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-    const int c_begin = chunk * DEC_CHUNK, c_end = min(len, c_begin + DEC_CHUNK);
+    const int c_begin = chunk * split_keys, c_end = min(len, c_begin + split_keys);
     if (c_begin >= len || c_end <= lo) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int* table = block_table + (size_t)r * max_pages;
     bf16* sQ = reinterpret_cast<bf16*>(dec_smem);
-    bf16* sK = reinterpret_cast<bf16*>(dec_smem + DEC_Q_BYTES + (size_t)warp * DEC_WARP_BYTES);
-    bf16* sV = sK + DEC_KEYS_PER_WARP * LDP;
-    const int w_begin = c_begin + warp * DEC_KEYS_PER_WARP;
-
-    // ---- ask for the warp's keys, then its values: 16-byte pieces, a row is D/8 pieces ----
+    uint8_t* ring = dec_smem + DEC_Q_BYTES + (size_t)warp * DEC_WARP_BYTES;
+    const int kpw = split_keys / DEC_WARPS;
+    const int w_begin = c_begin + warp * kpw, w_stop = min(len, w_begin + kpw);
+    const int first = max(w_begin, (lo / DEC_STAGE_KEYS) * DEC_STAGE_KEYS);
+    const int n_it = w_stop > first ? (w_stop - first + DEC_STAGE_KEYS - 1) / DEC_STAGE_KEYS : 0;
     constexpr int PIECES = D / 8;
+
+    // stage i: keys first + 16 i .. + 16, K rows then V rows; rows outside [lo, len) are zero
+    auto issue = [&](int i) {
+        if (i < n_it) {
+            bf16* dst = reinterpret_cast<bf16*>(ring + (size_t)(i % DEC_STAGES) * DEC_STAGE_BYTES);
 #pragma unroll
-    for (int which = 0; which < 2; ++which) {
-        const bf16* cache = which == 0 ? k_cache : v_cache;
-        bf16* dst = which == 0 ? sK : sV;
-#pragma unroll 4
-        for (int idx = lane; idx < DEC_KEYS_PER_WARP * PIECES; idx += 32) {
-            const int slot = idx / PIECES, piece = idx % PIECES;
-            const int key = w_begin + slot;
-            if (key < len && key >= lo) {
-                const size_t page = (size_t)table[key / page_size];
-                cp_async16(dst + slot * LDP + piece * 8, cache + ((page * K + kh) * page_size + (size_t)(key % page_size)) * D + piece * 8);
-            } else {
-                *reinterpret_cast<uint4*>(dst + slot * LDP + piece * 8) = make_uint4(0, 0, 0, 0);
+            for (int idx = lane; idx < 2 * DEC_STAGE_KEYS * PIECES; idx += 32) {
+                const int row = idx / PIECES, piece = idx % PIECES;           // rows 0..15 keys, 16..31 values
+                const int key = first + i * DEC_STAGE_KEYS + (row & (DEC_STAGE_KEYS - 1));
+                bf16* d = dst + row * LDP + piece * 8;
+                if (key < len && key >= lo) {
+                    const bf16* cache = row < DEC_STAGE_KEYS ? k_cache : v_cache;
+                    const size_t page = (size_t)table[key / page_size];
+                    cp_async16(d, cache + ((page * K + kh) * page_size + (size_t)(key % page_size)) * D + piece * 8);
+                } else {
+                    *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
+                }
             }
         }
         cp_async_commit();
-    }
+    };
+#pragma unroll
+    for (int i = 0; i < DEC_STAGES; ++i) issue(i);
+
     // the query tile: GROUP heads, the rest of the 16 rows zero
     for (int idx = threadIdx.x; idx < 16 * PIECES; idx += DEC_WARPS * 32) {
         const int row = idx / PIECES, piece = idx % PIECES;
@@ -147,72 +156,77 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_split_kernel(
         const int row = (lane & 7) + ((lane >> 3) & 1) * 8;
         ldsm_x4((uint32_t)__cvta_generic_to_shared(sQ + row * LDP + kk * 16 + (lane >> 4) * 8), qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3]);
     }
-    cp_async_wait<1>();
-    __syncwarp();
 
-    // ---- scores of the warp's keys: S = Q K^T ----
-    constexpr int NT = DEC_KEYS_PER_WARP / 8;
-    float sc[NT][4];
-#pragma unroll
-    for (int j = 0; j < NT; ++j) { sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.0f; }
-#pragma unroll
-    for (int kk = 0; kk < D / 16; ++kk) {
-#pragma unroll
-        for (int j = 0; j < NT; j += 2) {
-            uint32_t b0, b1, b2, b3;
-            const int key = j * 8 + (lane & 7) + (lane >> 4) * 8;
-            ldsm_x4((uint32_t)__cvta_generic_to_shared(sK + key * LDP + kk * 16 + ((lane >> 3) & 1) * 8), b0, b1, b2, b3);
-            mma_bf16_16816(sc[j], qa[kk], b0, b1);
-            mma_bf16_16816(sc[j + 1], qa[kk], b2, b3);
-        }
-    }
-    // this thread's row (= query head) is lane / 4; only rows below GROUP mean anything
     const float sl2 = scale * 1.4426950408889634f;
-    float m = -INFINITY;
+    float m_run = -INFINITY, l_run = 0.0f;              // of this thread's row (= query head lane / 4)
+    float o[D / 8][2];
 #pragma unroll
-    for (int j = 0; j < NT; ++j) {
-        const int key = w_begin + j * 8 + 2 * (lane & 3);
-        sc[j][0] = (key < len && key >= lo) ? sc[j][0] * sl2 : -INFINITY;
-        sc[j][1] = (key + 1 < len && key + 1 >= lo) ? sc[j][1] * sl2 : -INFINITY;
-        m = fmaxf(m, fmaxf(sc[j][0], sc[j][1]));
-    }
-    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
-    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
-    const float base = m == -INFINITY ? 0.0f : m;          // a warp whose keys are all masked contributes nothing
-    float l = 0.0f;
-#pragma unroll
-    for (int j = 0; j < NT; ++j) {
-        sc[j][0] = exp2f(sc[j][0] - base);
-        sc[j][1] = exp2f(sc[j][1] - base);
-        l += sc[j][0] + sc[j][1];
-    }
-    l += __shfl_xor_sync(0xffffffffu, l, 1);
-    l += __shfl_xor_sync(0xffffffffu, l, 2);
-    cp_async_wait<0>();
-    __syncwarp();
+    for (int i = 0; i < D / 8; ++i) { o[i][0] = o[i][1] = 0.0f; }
 
-    // ---- O = P V ----
-    float o[D / 8][4];
+    for (int it = 0; it < n_it; ++it) {
+        cp_async_wait<DEC_STAGES - 1>();
+        __syncwarp();
+        const bf16* sK = reinterpret_cast<const bf16*>(ring + (size_t)(it % DEC_STAGES) * DEC_STAGE_BYTES);
+        const bf16* sV = sK + DEC_STAGE_KEYS * LDP;
+        float sc[2][4];
+        sc[0][0] = sc[0][1] = sc[0][2] = sc[0][3] = sc[1][0] = sc[1][1] = sc[1][2] = sc[1][3] = 0.0f;
 #pragma unroll
-    for (int i = 0; i < D / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
+        for (int kk = 0; kk < D / 16; ++kk) {
+            uint32_t b0, b1, b2, b3;
+            const int key = (lane & 7) + (lane >> 4) * 8;
+            ldsm_x4((uint32_t)__cvta_generic_to_shared(sK + key * LDP + kk * 16 + ((lane >> 3) & 1) * 8), b0, b1, b2, b3);
+            mma_bf16_16816(sc[0], qa[kk], b0, b1);
+            mma_bf16_16816(sc[1], qa[kk], b2, b3);
+        }
+        const int key0 = first + it * DEC_STAGE_KEYS + 2 * (lane & 3);
+        float mx = -INFINITY;
 #pragma unroll
-    for (int ks = 0; ks < DEC_KEYS_PER_WARP / 16; ++ks) {
+        for (int j = 0; j < 2; ++j) {
+            const int key = key0 + j * 8;
+            sc[j][0] = (key < len && key >= lo) ? sc[j][0] * sl2 : -INFINITY;
+            sc[j][1] = (key + 1 < len && key + 1 >= lo) ? sc[j][1] * sl2 : -INFINITY;
+            mx = fmaxf(mx, fmaxf(sc[j][0], sc[j][1]));
+        }
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m_run, mx);
+        const float base = m_new == -INFINITY ? 0.0f : m_new;
+        const float corr = exp2f(m_run - base);
+        m_run = m_new;
+        float sum = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            sc[j][0] = exp2f(sc[j][0] - base);
+            sc[j][1] = exp2f(sc[j][1] - base);
+            sum += sc[j][0] + sc[j][1];
+        }
+        l_run = l_run * corr + sum;
         uint32_t pa[4];
-        pa[0] = pack_bf16(sc[2 * ks][0], sc[2 * ks][1]);
+        pa[0] = pack_bf16(sc[0][0], sc[0][1]);
         pa[1] = 0u;
-        pa[2] = pack_bf16(sc[2 * ks + 1][0], sc[2 * ks + 1][1]);
+        pa[2] = pack_bf16(sc[1][0], sc[1][1]);
         pa[3] = 0u;
 #pragma unroll
         for (int dt = 0; dt < D / 8; dt += 2) {
             uint32_t b0, b1, b2, b3;
-            const int key = ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+            const int key = (lane & 7) + ((lane >> 3) & 1) * 8;
             ldsm_x4_trans((uint32_t)__cvta_generic_to_shared(sV + key * LDP + dt * 8 + (lane >> 4) * 8), b0, b1, b2, b3);
-            mma_bf16_16816(o[dt], pa, b0, b1);
-            mma_bf16_16816(o[dt + 1], pa, b2, b3);
+            float c0[4] = {o[dt][0] * corr, o[dt][1] * corr, 0.0f, 0.0f};
+            float c1[4] = {o[dt + 1][0] * corr, o[dt + 1][1] * corr, 0.0f, 0.0f};
+            mma_bf16_16816(c0, pa, b0, b1);
+            mma_bf16_16816(c1, pa, b2, b3);
+            o[dt][0] = c0[0]; o[dt][1] = c0[1];
+            o[dt + 1][0] = c1[0]; o[dt + 1][1] = c1[1];
         }
+        __syncwarp();                                   // the stage is free: refill it
+        issue(it + DEC_STAGES);
     }
-    // each warp leaves (m, l, acc) of its keys in shared memory (over its key buffer), then the CTA adds the warps
-    float* s_acc = reinterpret_cast<float*>(sK);
+    cp_async_wait<0>();
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+
+    // each warp leaves (m, l, acc) of its keys in shared memory (over its ring), then the CTA adds the warps
+    float* s_acc = reinterpret_cast<float*>(ring);
     __syncwarp();
     const int g_row = lane >> 2;
     if (g_row < GROUP) {
@@ -221,7 +235,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_split_kernel(
             s_acc[g_row * D + i * 8 + 2 * (lane & 3)] = o[i][0];
             s_acc[g_row * D + i * 8 + 2 * (lane & 3) + 1] = o[i][1];
         }
-        if ((lane & 3) == 0) { s_m[warp][g_row] = m; s_l[warp][g_row] = l; }
+        if ((lane & 3) == 0) { s_m[warp][g_row] = m_run; s_l[warp][g_row] = l_run; }
     }
     __syncthreads();
     for (int idx = threadIdx.x; idx < GROUP * D; idx += DEC_WARPS * 32) {
@@ -247,13 +261,13 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_split_kernel(
 // (the chunks' maxima are in log2 units).
 __global__ void __launch_bounds__(D) attn_decode_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                                            const int* __restrict__ seq_lens, int H, int window, int max_chunks,
-                                                           bf16* __restrict__ out) {
+                                                           int split_keys, bf16* __restrict__ out) {
     const int h = blockIdx.x, r = blockIdx.y, dd = threadIdx.x;
     const int len = seq_lens[r];
     if (len <= 0) return;
     const int pos = len - 1;
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-    const int c_first = lo / DEC_CHUNK, c_last = pos / DEC_CHUNK;
+    const int c_first = lo / split_keys, c_last = pos / split_keys;
     const size_t base = ((size_t)r * H + h) * max_chunks;
     float m = -INFINITY;
     for (int c = c_first; c <= c_last; ++c) m = fmaxf(m, part_ml[(base + c) * 2]);
@@ -429,15 +443,14 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(
 
 MB_API int mb_attn_head_dim() { return D; }
 MB_API int mb_attn_group() { return GROUP; }
-MB_API int mb_attn_decode_chunk() { return DEC_CHUNK; }
-
-// Decode: q/out rows 0..requests-1 are the single new tokens of requests 0..requests-1.  part_acc holds
-// requests*H*max_chunks*HEAD_DIM floats and part_ml requests*H*max_chunks*2; max_chunks >= ceil(longest/128).
+// Decode: q/out rows 0..requests-1 are the single new tokens of requests 0..requests-1.  A CTA takes split_keys
+// keys (a multiple of 64); part_acc holds requests*H*max_chunks*HEAD_DIM floats and part_ml requests*H*max_chunks*2,
+// with max_chunks >= ceil(longest/split_keys).
 MB_API int mb_attn_decode(const void* q, const void* k_cache, const void* v_cache, void* out, const int* block_table,
                           int max_pages, const int* seq_lens, int requests, int K, int page_size, float scale, int window,
-                          float* part_acc, float* part_ml, int max_chunks, cudaStream_t s) {
+                          float* part_acc, float* part_ml, int max_chunks, int split_keys, cudaStream_t s) {
     if (requests <= 0) return 0;
-    if (max_chunks <= 0 || K <= 0) return MB_ERR_BAD_SIZE;
+    if (max_chunks <= 0 || K <= 0 || split_keys < 64 || split_keys % 64 != 0) return MB_ERR_BAD_SIZE;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attn_decode_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM);
@@ -447,10 +460,11 @@ MB_API int mb_attn_decode(const void* q, const void* k_cache, const void* v_cach
     dim3 grid(max_chunks, K, requests);
     attn_decode_split_kernel<<<grid, DEC_WARPS * 32, DEC_SMEM, s>>>((const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, block_table,
                                                              max_pages, seq_lens, K, page_size, scale, window, part_acc, part_ml,
-                                                             max_chunks);
+                                                             max_chunks, split_keys);
     int rc = mb_last_error();
     if (rc) return rc;
-    attn_decode_merge_kernel<<<dim3(K * GROUP, requests), D, 0, s>>>(part_acc, part_ml, seq_lens, K * GROUP, window, max_chunks, (bf16*)out);
+    attn_decode_merge_kernel<<<dim3(K * GROUP, requests), D, 0, s>>>(part_acc, part_ml, seq_lens, K * GROUP, window, max_chunks,
+                                                                    split_keys, (bf16*)out);
     return mb_last_error();
 }
 

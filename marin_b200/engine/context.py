@@ -59,5 +59,5 @@ class StepContext:
     workspace: Workspace
     extras: Dict[str, object] = field(default_factory=dict)
     #: set for captured decode steps: fixed number of key chunks and the scratch the capture owns
-    attn_chunks: int = 0
+    attn_split: object = None     # (keys per CTA, chunks per sequence)
     attn_scratch: object = None

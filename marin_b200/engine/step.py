@@ -200,11 +200,14 @@ class Runner:
         size = self.packed_size(bucket)
         host = torch.zeros(size, dtype=torch.int32).pin_memory()
         dev = torch.zeros(size, dtype=torch.int32, device=self.rt.device)
-        chunks = -(-self.max_seq_len // ops.DECODE_CHUNK)
-        heads = max((b.mixer.heads for b in self.model.blocks if hasattr(b.mixer, "heads")), default=1)
-        hd = max((b.mixer.head_dim for b in self.model.blocks if hasattr(b.mixer, "head_dim")), default=1)
+        mixers = [b.mixer for b in self.model.blocks if hasattr(b.mixer, "kv_heads")]
+        heads = max((m.heads for m in mixers), default=1)
+        kv_heads = min((m.kv_heads for m in mixers), default=1)
+        hd = max((m.head_dim for m in mixers), default=1)
+        # the split of the keys is fixed by the context capacity, so that the captured grid fits every step
+        split, chunks = ops.decode_split(bucket, kv_heads, self.max_seq_len)
         g = {"static": (host, dev, torch.cuda.Event()), "workspace": Workspace(self.rt.device), "graph": None, "logits": None,
-             "attn_chunks": chunks,
+             "attn_split": (split, chunks),
              "attn_scratch": (torch.empty(bucket * heads * chunks * hd, device=self.rt.device, dtype=torch.float32),
                               torch.empty(bucket * heads * chunks * 2, device=self.rt.device, dtype=torch.float32))}
         self.graphs[bucket] = g
@@ -212,7 +215,7 @@ class Runner:
         def run():
             ctx = self.build_context(entries, pad_to=bucket, static=g["static"])
             ctx.workspace = g["workspace"]
-            ctx.attn_chunks, ctx.attn_scratch = g["attn_chunks"], g["attn_scratch"]
+            ctx.attn_split, ctx.attn_scratch = g["attn_split"], g["attn_scratch"]
             return self.model.forward(ctx, self.views)
 
         run()                                    # warm up: builds kernels, sizes the workspace
@@ -220,7 +223,7 @@ class Runner:
         graph = torch.cuda.CUDAGraph()
         ctx = self.build_context(entries, pad_to=bucket, static=g["static"])
         ctx.workspace = g["workspace"]
-        ctx.attn_chunks, ctx.attn_scratch = g["attn_chunks"], g["attn_scratch"]
+        ctx.attn_split, ctx.attn_scratch = g["attn_split"], g["attn_scratch"]
         torch.cuda.synchronize()
         launches = ops.launches
         with torch.cuda.graph(graph):

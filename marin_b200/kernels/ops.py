@@ -171,7 +171,16 @@ def qk_norm_rope_write(qkv, q_out, q_weight, k_weight, eps, positions, inv_freq,
 
 #: bf16 attention goes to the tensor-core / split-KV kernels when the head layout allows (False: the plain kernel)
 use_fast_attention = True
-DECODE_CHUNK = 128      # keys per CTA of the split-KV decode kernel (attention_fast.cu: DEC_CHUNK)
+DECODE_SPLITS = (1024, 512, 256, 128, 64)      # keys per CTA the split-KV decode kernel may be given
+
+
+def decode_split(requests: int, kv_heads: int, longest: int):
+    """Keys per CTA and chunks per sequence for decode attention over sequences of up to ``longest`` keys: the
+    largest split that still gives every SM about four CTAs (the kernel keeps two resident per SM)."""
+    for split in DECODE_SPLITS:
+        chunks = -(-longest // split)
+        if requests * kv_heads * chunks >= 4 * SM_COUNT or split == DECODE_SPLITS[-1]:
+            return split, chunks
 _attn_scratch = {}
 
 
@@ -209,11 +218,12 @@ def attention(q, k_cache, v_cache, out, ctx, block_table, H, K, d, scale, window
         max_pages = block_table.shape[1]
         nd = ctx.num_decode
         if nd > 0:
-            chunks = getattr(ctx, "attn_chunks", None) or -(-ctx.max_seq_len // DECODE_CHUNK)
+            split, chunks = getattr(ctx, "attn_split", None) or decode_split(nd, K, ctx.max_seq_len)
             part_acc, part_ml = getattr(ctx, "attn_scratch", None) or _decode_scratch(q.device, nd, H, chunks, d)
             _check(lib.mb_attn_decode(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), _c_int(max_pages),
                                       _ptr(ctx.seq_lens), _c_int(nd), _c_int(K), _c_int(page_size), _c_float(scale),
-                                      _c_int(window), _ptr(part_acc), _ptr(part_ml), _c_int(chunks), _stream()), "attention (decode)")
+                                      _c_int(window), _ptr(part_acc), _ptr(part_ml), _c_int(chunks), _c_int(split), _stream()),
+                   "attention (decode)")
             launches_extra(1)
         if ctx.num_requests > nd:
             _check(lib.mb_attn_prefill(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), _c_int(max_pages),
