@@ -98,7 +98,7 @@ static_assert(GROUP * D * 4 <= DEC_WARP_BYTES, "a warp's accumulators are writte
 // softmax runs online in float32 in the exp2 domain.  Partial (m, l, acc) per CTA: m is in log2 units.
 __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_split_kernel(
     const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
-    const int* __restrict__ block_table, int max_pages, const int* __restrict__ seq_lens, int K, int page_size,
+    const int* __restrict__ block_table, int max_pages, const int* __restrict__ seq_lens, int K, int page_shift,
     float scale, int window, float* __restrict__ part_acc, float* __restrict__ part_ml, int max_chunks, int split_keys) {
     extern __shared__ __align__(16) uint8_t dec_smem[];
     __shared__ float s_m[DEC_WARPS][8], s_l[DEC_WARPS][8];
@@ -120,18 +120,22 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_split_kernel(
     constexpr int PIECES = D / 8;
 
     // stage i: keys first + 16 i .. + 16, K rows then V rows; rows outside [lo, len) are zero
+    const int page_mask = (1 << page_shift) - 1;
+    const size_t head_rows = (size_t)kh << page_shift;             // rows before this kv head inside a page
+    const size_t page_rows = (size_t)K << page_shift;              // rows of a whole page
     auto issue = [&](int i) {
         if (i < n_it) {
             bf16* dst = reinterpret_cast<bf16*>(ring + (size_t)(i % DEC_STAGES) * DEC_STAGE_BYTES);
+            const int key_base = first + i * DEC_STAGE_KEYS;
 #pragma unroll
             for (int idx = lane; idx < 2 * DEC_STAGE_KEYS * PIECES; idx += 32) {
                 const int row = idx / PIECES, piece = idx % PIECES;           // rows 0..15 keys, 16..31 values
-                const int key = first + i * DEC_STAGE_KEYS + (row & (DEC_STAGE_KEYS - 1));
+                const int key = key_base + (row & (DEC_STAGE_KEYS - 1));
                 bf16* d = dst + row * LDP + piece * 8;
                 if (key < len && key >= lo) {
                     const bf16* cache = row < DEC_STAGE_KEYS ? k_cache : v_cache;
-                    const size_t page = (size_t)table[key / page_size];
-                    cp_async16(d, cache + ((page * K + kh) * page_size + (size_t)(key % page_size)) * D + piece * 8);
+                    const size_t at = (size_t)table[key >> page_shift] * page_rows + head_rows + (size_t)(key & page_mask);
+                    cp_async16(d, cache + at * D + piece * 8);
                 } else {
                     *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
                 }
@@ -289,15 +293,16 @@ __global__ void __launch_bounds__(D) attn_decode_merge_kernel(const float* __res
 
 // Rows of one 64-key block of K or V into shared memory; keys past `k_last` are zero (their pages may not exist).
 __device__ __forceinline__ void load_kv_tile(bf16* dst, const bf16* __restrict__ cache, const int* __restrict__ table, int K, int kh,
-                                             int page_size, int key0, int k_last) {
+                                             int page_shift, int key0, int k_last) {
     constexpr int CHUNKS = D / 8;
+    const int page_mask = (1 << page_shift) - 1;
     for (int idx = threadIdx.x; idx < PF_BN * CHUNKS; idx += 128) {
         const int row = idx / CHUNKS, c = idx % CHUNKS;
         const int key = key0 + row;
         uint4 val = make_uint4(0, 0, 0, 0);
         if (key <= k_last) {
-            const size_t page = (size_t)table[key / page_size];
-            val = *reinterpret_cast<const uint4*>(cache + ((page * K + kh) * page_size + (size_t)(key % page_size)) * D + c * 8);
+            const size_t at = (((size_t)table[key >> page_shift] * K + kh) << page_shift) + (size_t)(key & page_mask);
+            val = *reinterpret_cast<const uint4*>(cache + at * D + c * 8);
         }
         *reinterpret_cast<uint4*>(dst + row * PF_LD + c * 8) = val;
     }
@@ -306,7 +311,7 @@ __device__ __forceinline__ void load_kv_tile(bf16* dst, const bf16* __restrict__
 __global__ void __launch_bounds__(128) attn_prefill_kernel(
     const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache, bf16* __restrict__ out,
     const int* __restrict__ block_table, int max_pages, const int* __restrict__ cu_tokens, const int* __restrict__ seq_lens,
-    int first_req, int K, int page_size, float scale, int window) {
+    int first_req, int K, int page_shift, float scale, int window) {
     extern __shared__ __align__(16) uint8_t pf_smem[];
     bf16* sQ = reinterpret_cast<bf16*>(pf_smem);
     bf16* sK = sQ + PF_BM * PF_LD;
@@ -352,8 +357,8 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(
     for (int kb = k_lo / PF_BN; kb <= q_last / PF_BN; ++kb) {
         const int key0 = kb * PF_BN;
         __syncthreads();                                       // the previous block's K and V are no longer read
-        load_kv_tile(sK, k_cache, table, K, kh, page_size, key0, q_last);
-        load_kv_tile(sV, v_cache, table, K, kh, page_size, key0, q_last);
+        load_kv_tile(sK, k_cache, table, K, kh, page_shift, key0, q_last);
+        load_kv_tile(sV, v_cache, table, K, kh, page_shift, key0, q_last);
         __syncthreads();
 
         float s[PF_BN / 8][4];
@@ -441,6 +446,13 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(
 
 // ---- host side ------------------------------------------------------------------------------------------------------
 
+// Pages hold a power-of-two number of positions: the kernels shift and mask instead of dividing.
+static int page_shift_of(int page_size) {
+    for (int s = 0; s < 16; ++s)
+        if ((1 << s) == page_size) return s;
+    return -1;
+}
+
 MB_API int mb_attn_head_dim() { return D; }
 MB_API int mb_attn_group() { return GROUP; }
 // Decode: q/out rows 0..requests-1 are the single new tokens of requests 0..requests-1.  A CTA takes split_keys
@@ -451,6 +463,8 @@ MB_API int mb_attn_decode(const void* q, const void* k_cache, const void* v_cach
                           float* part_acc, float* part_ml, int max_chunks, int split_keys, cudaStream_t s) {
     if (requests <= 0) return 0;
     if (max_chunks <= 0 || K <= 0 || split_keys < 64 || split_keys % 64 != 0) return MB_ERR_BAD_SIZE;
+    const int page_shift = page_shift_of(page_size);
+    if (page_shift < 0) return MB_ERR_BAD_SIZE;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attn_decode_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM);
@@ -459,7 +473,7 @@ MB_API int mb_attn_decode(const void* q, const void* k_cache, const void* v_cach
     }
     dim3 grid(max_chunks, K, requests);
     attn_decode_split_kernel<<<grid, DEC_WARPS * 32, DEC_SMEM, s>>>((const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, block_table,
-                                                             max_pages, seq_lens, K, page_size, scale, window, part_acc, part_ml,
+                                                             max_pages, seq_lens, K, page_shift, scale, window, part_acc, part_ml,
                                                              max_chunks, split_keys);
     int rc = mb_last_error();
     if (rc) return rc;
@@ -473,6 +487,8 @@ MB_API int mb_attn_prefill(const void* q, const void* k_cache, const void* v_cac
                            int max_pages, const int* cu_tokens, const int* seq_lens, int first_req, int requests,
                            int max_query_len, int K, int page_size, float scale, int window, cudaStream_t s) {
     if (requests <= 0 || max_query_len <= 0) return 0;
+    const int page_shift = page_shift_of(page_size);
+    if (page_shift < 0) return MB_ERR_BAD_SIZE;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM);
@@ -481,6 +497,6 @@ MB_API int mb_attn_prefill(const void* q, const void* k_cache, const void* v_cac
     }
     dim3 grid((max_query_len + PF_BM - 1) / PF_BM, K * GROUP, requests);
     attn_prefill_kernel<<<grid, 128, PF_SMEM, s>>>((const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, block_table,
-                                                   max_pages, cu_tokens, seq_lens, first_req, K, page_size, scale, window);
+                                                   max_pages, cu_tokens, seq_lens, first_req, K, page_shift, scale, window);
     return mb_last_error();
 }

@@ -171,17 +171,16 @@ def qk_norm_rope_write(qkv, q_out, q_weight, k_weight, eps, positions, inv_freq,
 
 #: bf16 attention goes to the tensor-core / split-KV kernels when the head layout allows (False: the plain kernel)
 use_fast_attention = True
-DECODE_SPLITS = (1024, 512, 256, 128, 64)      # keys per CTA the split-KV decode kernel may be given
+DECODE_SPLITS = (4096, 2048, 1024, 512, 256, 128, 64)      # keys per CTA the split-KV decode kernel may be given
 
 
 def decode_split(requests: int, kv_heads: int, longest: int):
     """Keys per CTA and chunks per sequence for decode attention over sequences of up to ``longest`` keys: the
-    largest split that still gives every SM about four CTAs (the kernel keeps two resident per SM)."""
+    largest split that still gives about one CTA per SM (long CTAs amortise their start-up; measured on B200)."""
     for split in DECODE_SPLITS:
         chunks = -(-longest // split)
-        if requests * kv_heads * chunks >= 4 * SM_COUNT or split == DECODE_SPLITS[-1]:
+        if requests * kv_heads * chunks >= SM_COUNT or split == DECODE_SPLITS[-1]:
             return split, chunks
-_attn_scratch = {}
 
 
 def _attention_lib(d: int, group: int):
