@@ -171,6 +171,7 @@ def qk_norm_rope_write(qkv, q_out, q_weight, k_weight, eps, positions, inv_freq,
 
 #: bf16 attention goes to the tensor-core / split-KV kernels when the head layout allows (False: the plain kernel)
 use_fast_attention = True
+_attn_scratch = {}
 DECODE_SPLITS = (4096, 2048, 1024, 512, 256, 128, 64)      # keys per CTA the split-KV decode kernel may be given
 
 
