@@ -14,6 +14,7 @@
 //
 // Page layout: [page][kv_head][offset in page][HEAD_DIM]; block_table[request][logical page] -> page.
 #include "common.cuh"
+#include "launch.cuh"
 
 #ifndef HEAD_DIM
 #error "compile with -DHEAD_DIM=<multiple of 16, at most 128>"
@@ -100,6 +101,8 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_split_kernel(
     const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
     const int* __restrict__ block_table, int max_pages, const int* __restrict__ seq_lens, int K, int page_shift,
     float scale, int window, float* __restrict__ part_acc, float* __restrict__ part_ml, int max_chunks, int split_keys) {
+    pdl_wait();
+    pdl_launch_dependents();
     extern __shared__ __align__(16) uint8_t dec_smem[];
     __shared__ float s_m[DEC_WARPS][8], s_l[DEC_WARPS][8];
     const int chunk = blockIdx.x, kh = blockIdx.y, r = blockIdx.z;
@@ -266,6 +269,8 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_split_kernel(
 __global__ void __launch_bounds__(D) attn_decode_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                                            const int* __restrict__ seq_lens, int H, int window, int max_chunks,
                                                            int split_keys, bf16* __restrict__ out) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int h = blockIdx.x, r = blockIdx.y, dd = threadIdx.x;
     const int len = seq_lens[r];
     if (len <= 0) return;
@@ -312,6 +317,8 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(
     const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache, bf16* __restrict__ out,
     const int* __restrict__ block_table, int max_pages, const int* __restrict__ cu_tokens, const int* __restrict__ seq_lens,
     int first_req, int K, int page_shift, float scale, int window) {
+    pdl_wait();
+    pdl_launch_dependents();
     extern __shared__ __align__(16) uint8_t pf_smem[];
     bf16* sQ = reinterpret_cast<bf16*>(pf_smem);
     bf16* sK = sQ + PF_BM * PF_LD;
@@ -472,14 +479,12 @@ MB_API int mb_attn_decode(const void* q, const void* k_cache, const void* v_cach
         configured = true;
     }
     dim3 grid(max_chunks, K, requests);
-    attn_decode_split_kernel<<<grid, DEC_WARPS * 32, DEC_SMEM, s>>>((const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, block_table,
-                                                             max_pages, seq_lens, K, page_shift, scale, window, part_acc, part_ml,
-                                                             max_chunks, split_keys);
-    int rc = mb_last_error();
+    int rc = launch_kernel(attn_decode_split_kernel, grid, DEC_WARPS * 32, DEC_SMEM, s, 0, (const bf16*)q, (const bf16*)k_cache,
+                           (const bf16*)v_cache, block_table, max_pages, seq_lens, K, page_shift, scale, window, part_acc, part_ml,
+                           max_chunks, split_keys);
     if (rc) return rc;
-    attn_decode_merge_kernel<<<dim3(K * GROUP, requests), D, 0, s>>>(part_acc, part_ml, seq_lens, K * GROUP, window, max_chunks,
-                                                                    split_keys, (bf16*)out);
-    return mb_last_error();
+    return launch_kernel(attn_decode_merge_kernel, dim3(K * GROUP, requests), D, 0, s, 0, (const float*)part_acc, (const float*)part_ml,
+                         seq_lens, K * GROUP, window, max_chunks, split_keys, (bf16*)out);
 }
 
 // Prefill: requests first_req .. first_req+requests-1 of the step, each with its tokens cu_tokens[r]..cu_tokens[r+1].
@@ -496,7 +501,6 @@ MB_API int mb_attn_prefill(const void* q, const void* k_cache, const void* v_cac
         configured = true;
     }
     dim3 grid((max_query_len + PF_BM - 1) / PF_BM, K * GROUP, requests);
-    attn_prefill_kernel<<<grid, 128, PF_SMEM, s>>>((const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, block_table,
-                                                   max_pages, cu_tokens, seq_lens, first_req, K, page_shift, scale, window);
-    return mb_last_error();
+    return launch_kernel(attn_prefill_kernel, grid, 128, PF_SMEM, s, 0, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
+                         (bf16*)out, block_table, max_pages, cu_tokens, seq_lens, first_req, K, page_shift, scale, window);
 }

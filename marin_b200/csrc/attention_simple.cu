@@ -4,6 +4,7 @@
 // of the fast kernels (the reference's generic kernel has the same shape, crates/cuda/src/attention.cu:6-96).
 // Page layout: [page][kv_head][offset in page][d].
 #include "common.cuh"
+#include "launch.cuh"
 
 #define AS_THREADS 128
 #define AS_MAX_D_PER_THREAD 4
@@ -13,6 +14,8 @@ __global__ void __launch_bounds__(AS_THREADS) attention_simple_kernel(
     const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache, T* __restrict__ out,
     const int* __restrict__ block_table, int max_pages, const int* __restrict__ req_index,
     const int* __restrict__ positions, int H, int K, int d, int page_size, float scale, int window) {
+    pdl_wait();
+    pdl_launch_dependents();
     extern __shared__ float smem[];
     float* qs = smem;                 // [d]
     float* ps = smem + d;             // [AS_THREADS]
@@ -85,11 +88,11 @@ MB_API int mb_attention_simple(const void* q, const void* k_cache, const void* v
     dim3 grid(tokens, H);
     const size_t smem = (size_t)(d + AS_THREADS + 32) * sizeof(float);
     if (dtype == MB_F32)
-        attention_simple_kernel<float><<<grid, AS_THREADS, smem, s>>>(
+        return launch_kernel(attention_simple_kernel<float>, grid, AS_THREADS, smem, s, 0,
             (const float*)q, (const float*)k_cache, (const float*)v_cache, (float*)out, block_table, max_pages,
             req_index, positions, H, K, d, page_size, scale, window);
     else if (dtype == MB_BF16)
-        attention_simple_kernel<bf16><<<grid, AS_THREADS, smem, s>>>(
+        return launch_kernel(attention_simple_kernel<bf16>, grid, AS_THREADS, smem, s, 0,
             (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, block_table, max_pages,
             req_index, positions, H, K, d, page_size, scale, window);
     else return MB_ERR_BAD_DTYPE;

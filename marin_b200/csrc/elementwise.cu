@@ -3,10 +3,13 @@
 // activation dtype.  The formulas are the reference's (crates/cuda/src/kernels.cu:43-67,147-175,
 // crates/cuda/src/kv_format.cu:48-72); the fusion and the page layout are this engine's own.
 #include "common.cuh"
+#include "launch.cuh"
 
 // ---- embedding: out[t, :] = float(table[ids[t], :]) -------------------------------------------------
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ ids, const TW* __restrict__ table, float* __restrict__ out, int h) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int t = blockIdx.x;
     const TW* row = table + (size_t)ids[t] * h;
     float* dst = out + (size_t)t * h;
@@ -15,8 +18,8 @@ __global__ void embed_kernel(const int* __restrict__ ids, const TW* __restrict__
 
 MB_API int mb_embed(const int* ids, const void* table, int table_dtype, float* out, int tokens, int h, cudaStream_t s) {
     if (tokens <= 0) return 0;
-    if (table_dtype == MB_F32) embed_kernel<float><<<tokens, 256, 0, s>>>(ids, (const float*)table, out, h);
-    else if (table_dtype == MB_BF16) embed_kernel<bf16><<<tokens, 256, 0, s>>>(ids, (const bf16*)table, out, h);
+    if (table_dtype == MB_F32) return launch_kernel(embed_kernel<float>, tokens, 256, 0, s, 0, ids, (const float*)table, out, h);
+    else if (table_dtype == MB_BF16) return launch_kernel(embed_kernel<bf16>, tokens, 256, 0, s, 0, ids, (const bf16*)table, out, h);
     else return MB_ERR_BAD_DTYPE;
     return mb_last_error();
 }
@@ -25,6 +28,8 @@ MB_API int mb_embed(const int* ids, const void* table, int table_dtype, float* o
 template <typename TO>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, float eps, int unit_offset,
                                TO* __restrict__ out, int n) {
+    pdl_wait();
+    pdl_launch_dependents();
     __shared__ float scratch[32];
     const float* row = x + (size_t)blockIdx.x * n;
     TO* dst = out + (size_t)blockIdx.x * n;
@@ -42,8 +47,8 @@ MB_API int mb_rmsnorm(const float* x, const float* w, float eps, int unit_offset
                       int rows, int n, cudaStream_t s) {
     if (rows <= 0) return 0;
     const int threads = n >= 1024 ? 256 : 128;
-    if (out_dtype == MB_F32) rmsnorm_kernel<float><<<rows, threads, 0, s>>>(x, w, eps, unit_offset, (float*)out, n);
-    else if (out_dtype == MB_BF16) rmsnorm_kernel<bf16><<<rows, threads, 0, s>>>(x, w, eps, unit_offset, (bf16*)out, n);
+    if (out_dtype == MB_F32) return launch_kernel(rmsnorm_kernel<float>, rows, threads, 0, s, 0, x, w, eps, unit_offset, (float*)out, n);
+    else if (out_dtype == MB_BF16) return launch_kernel(rmsnorm_kernel<bf16>, rows, threads, 0, s, 0, x, w, eps, unit_offset, (bf16*)out, n);
     else return MB_ERR_BAD_DTYPE;
     return mb_last_error();
 }
@@ -58,6 +63,8 @@ __global__ void qk_norm_rope_write_kernel(const T* __restrict__ qkv, int row_str
                                           int rotary_dim, int interleaved, const int* __restrict__ slot_mapping,
                                           T* __restrict__ k_cache, T* __restrict__ v_cache, int H, int K, int d,
                                           int page_size, int heads_total) {
+    pdl_wait();
+    pdl_launch_dependents();
     extern __shared__ float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x;
@@ -115,11 +122,11 @@ MB_API int mb_qk_norm_rope_write(const void* qkv, int dtype, void* q_out, const 
     const size_t smem = (size_t)warps * d * sizeof(float);
     if (smem > 48 * 1024) return MB_ERR_BAD_SIZE;
     if (dtype == MB_F32)
-        qk_norm_rope_write_kernel<float><<<grid, warps * 32, smem, s>>>(
+        return launch_kernel(qk_norm_rope_write_kernel<float>, grid, warps * 32, smem, s, 0,
             (const float*)qkv, row_stride, (float*)q_out, q_w, k_w, eps, positions, inv_freq, rotary_dim, interleaved,
             slot_mapping, (float*)k_cache, (float*)v_cache, H, K, d, page_size, heads_total);
     else if (dtype == MB_BF16)
-        qk_norm_rope_write_kernel<bf16><<<grid, warps * 32, smem, s>>>(
+        return launch_kernel(qk_norm_rope_write_kernel<bf16>, grid, warps * 32, smem, s, 0,
             (const bf16*)qkv, row_stride, (bf16*)q_out, q_w, k_w, eps, positions, inv_freq, rotary_dim, interleaved,
             slot_mapping, (bf16*)k_cache, (bf16*)v_cache, H, K, d, page_size, heads_total);
     else return MB_ERR_BAD_DTYPE;
@@ -129,6 +136,8 @@ MB_API int mb_qk_norm_rope_write(const void* qkv, int dtype, void* q_out, const 
 // ---- SwiGLU: out[t, i] = g / (1 + exp(-g)) * u with g = gu[t, i], u = gu[t, I + i] -------------------
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total) {
+    pdl_wait();
+    pdl_launch_dependents();
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (; idx < total; idx += stride) {
@@ -143,14 +152,16 @@ MB_API int mb_swiglu(const void* gate_up, void* out, int dtype, int tokens, int 
     if (total == 0) return 0;
     const int threads = 256;
     const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
-    if (dtype == MB_F32) swiglu_kernel<float><<<blocks, threads, 0, s>>>((const float*)gate_up, (float*)out, I, total);
-    else if (dtype == MB_BF16) swiglu_kernel<bf16><<<blocks, threads, 0, s>>>((const bf16*)gate_up, (bf16*)out, I, total);
+    if (dtype == MB_F32) return launch_kernel(swiglu_kernel<float>, blocks, threads, 0, s, 0, (const float*)gate_up, (float*)out, I, total);
+    else if (dtype == MB_BF16) return launch_kernel(swiglu_kernel<bf16>, blocks, threads, 0, s, 0, (const bf16*)gate_up, (bf16*)out, I, total);
     else return MB_ERR_BAD_DTYPE;
     return mb_last_error();
 }
 
 // ---- rows of the residual stream whose logits are wanted ----------------------------------------------
 __global__ void gather_rows_kernel(const float* __restrict__ src, const int* __restrict__ rows, float* __restrict__ out, int h) {
+    pdl_wait();
+    pdl_launch_dependents();
     const float* row = src + (size_t)rows[blockIdx.x] * h;
     float* dst = out + (size_t)blockIdx.x * h;
     for (int i = threadIdx.x; i < h; i += blockDim.x) dst[i] = row[i];
@@ -158,13 +169,14 @@ __global__ void gather_rows_kernel(const float* __restrict__ src, const int* __r
 
 MB_API int mb_gather_rows(const float* src, const int* rows, float* out, int count, int h, cudaStream_t s) {
     if (count <= 0) return 0;
-    gather_rows_kernel<<<count, 256, 0, s>>>(src, rows, out, h);
-    return mb_last_error();
+    return launch_kernel(gather_rows_kernel, count, 256, 0, s, 0, src, rows, out, h);
 }
 
 // ---- y += x (float32 residual, x in the activation dtype) ---------------------------------------------
 template <typename T>
 __global__ void add_into_kernel(float* __restrict__ y, const T* __restrict__ x, size_t total) {
+    pdl_wait();
+    pdl_launch_dependents();
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (; idx < total; idx += stride) y[idx] += to_f32(x[idx]);
@@ -174,8 +186,8 @@ MB_API int mb_add_into(float* y, const void* x, int dtype, size_t total, cudaStr
     if (total == 0) return 0;
     const int threads = 256;
     const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
-    if (dtype == MB_F32) add_into_kernel<float><<<blocks, threads, 0, s>>>(y, (const float*)x, total);
-    else if (dtype == MB_BF16) add_into_kernel<bf16><<<blocks, threads, 0, s>>>(y, (const bf16*)x, total);
+    if (dtype == MB_F32) return launch_kernel(add_into_kernel<float>, blocks, threads, 0, s, 0, y, (const float*)x, total);
+    else if (dtype == MB_BF16) return launch_kernel(add_into_kernel<bf16>, blocks, threads, 0, s, 0, y, (const bf16*)x, total);
     else return MB_ERR_BAD_DTYPE;
     return mb_last_error();
 }

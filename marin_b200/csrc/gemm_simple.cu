@@ -4,6 +4,7 @@
 // precision mode) and the plain twin the tensor-core kernel is tested against.  The reference's
 // counterpart is its warp-per-row kernel (crates/cuda/src/kernels.cu:73-116).
 #include "common.cuh"
+#include "launch.cuh"
 
 #define GS_TILE 64
 #define GS_BK 16
@@ -11,6 +12,8 @@
 template <typename TX, typename TW, typename TO, bool ACC>
 __global__ void __launch_bounds__(256) gemm_simple_kernel(const TX* __restrict__ x, const TW* __restrict__ w,
                                                           TO* __restrict__ out, int T, int N, int K) {
+    pdl_wait();
+    pdl_launch_dependents();
     __shared__ float sx[GS_BK][GS_TILE + 1];
     __shared__ float sw[GS_BK][GS_TILE + 1];
     const int t0 = blockIdx.y * GS_TILE, n0 = blockIdx.x * GS_TILE;
@@ -65,11 +68,8 @@ __global__ void __launch_bounds__(256) gemm_simple_kernel(const TX* __restrict__
 template <typename TX, typename TW, typename TO>
 static int launch(const void* x, const void* w, void* out, int T, int N, int K, int accumulate, cudaStream_t s) {
     dim3 grid((N + GS_TILE - 1) / GS_TILE, (T + GS_TILE - 1) / GS_TILE);
-    if (accumulate)
-        gemm_simple_kernel<TX, TW, TO, true><<<grid, 256, 0, s>>>((const TX*)x, (const TW*)w, (TO*)out, T, N, K);
-    else
-        gemm_simple_kernel<TX, TW, TO, false><<<grid, 256, 0, s>>>((const TX*)x, (const TW*)w, (TO*)out, T, N, K);
-    return mb_last_error();
+    if (accumulate) return launch_kernel(gemm_simple_kernel<TX, TW, TO, true>, grid, 256, 0, s, 0, (const TX*)x, (const TW*)w, (TO*)out, T, N, K);
+    return launch_kernel(gemm_simple_kernel<TX, TW, TO, false>, grid, 256, 0, s, 0, (const TX*)x, (const TW*)w, (TO*)out, T, N, K);
 }
 
 // x [T, K] (x_dtype), w [N, K] (w_dtype), out [T, N] (out_dtype); accumulate: out += (float32 out only).

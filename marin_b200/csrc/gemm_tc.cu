@@ -19,6 +19,7 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include "launch.cuh"
 
 #define TC_BM 128          // weight rows per CTA (the MMA's M)
 #define TC_BK 64           // k per pipeline stage: 64 bf16 = one 128-byte swizzle row
@@ -146,9 +147,19 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
 
+    pdl_launch_dependents();
     if (warp == 0 && lane == 0) {
-        // ---- producer: TMA loads into the ring ----
-        for (int i = 0; i < nkb; ++i) {
+        // ---- producer: TMA loads into the ring.  The weights are written by no kernel, so the first tiles of w
+        // are asked for before the wait on the kernels ahead in the stream; x is read only after it. ----
+        const int early = min(nkb, STAGES);
+        for (int i = 0; i < early; ++i) {
+            mbar_expect_tx(&full[i], L::STAGE_BYTES);
+            tma_load_2d(smem + i * L::STAGE_BYTES, &map_w, (kb_begin + i) * TC_BK, n0, &full[i]);
+        }
+        pdl_wait();
+        for (int i = 0; i < early; ++i)
+            tma_load_2d(smem + i * L::STAGE_BYTES + L::A_BYTES, &map_x, (kb_begin + i) * TC_BK, t0, &full[i]);
+        for (int i = early; i < nkb; ++i) {
             const int s = i % STAGES;
             const uint32_t phase = (i / STAGES) & 1;
             if (!mbar_wait(&empty[s], phase ^ 1)) { atomicExch(error_flag, 1); break; }
@@ -179,6 +190,7 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
     __syncwarp();
 
     // ---- epilogue: every warp reads its 32 lanes of the accumulator ----
+    pdl_wait();                                   // out may be read (+=) and is written: only after the kernels ahead
     bool have = nkb > 0;
     if (have) {
         if (!mbar_wait(accum, 0)) { if (lane == 0) atomicExch(error_flag, 3); have = false; }
@@ -318,25 +330,10 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* out, in
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((N + TC_BM - 1) / TC_BM, (T + BN - 1) / BN, splits);
-    cfg.blockDim = dim3(128);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = s;
-    cudaLaunchAttribute attr[1];
-    cfg.attrs = attr;
-    cfg.numAttrs = 0;
-    if (cluster_reduce && splits > 1) {
-        attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = 1;
-        attr[0].val.clusterDim.y = 1;
-        attr[0].val.clusterDim.z = splits;
-        cfg.numAttrs = 1;
-    }
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, STAGES>, mw, mx, out, mode, T, N, K, kb_per_split, partials,
-                                       counters, error_flag, (cluster_reduce && splits > 1) ? 1 : 0);
-    if (e != cudaSuccess) return (int)e;
-    return mb_last_error();
+    const bool clustered = cluster_reduce && splits > 1;
+    return launch_kernel(gemm_tc_kernel<BN, STAGES>, dim3((N + TC_BM - 1) / TC_BM, (T + BN - 1) / BN, splits), dim3(128), smem, s,
+                         clustered ? splits : 0, mw, mx, out, mode, T, N, K, kb_per_split, partials, counters, error_flag,
+                         clustered ? 1 : 0);
 }
 
 // Tiles a launch with `bn` tokens per CTA would have (for the caller's choice of split).

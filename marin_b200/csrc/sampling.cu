@@ -1,11 +1,14 @@
 // Sampling on the device.  arg-max: the largest logit among the first `usable`, the lowest id among
 // equals (the reference's greedy rule, crates/sampler/src/lib.rs:40-48); one block per row.
 #include "common.cuh"
+#include "launch.cuh"
 
 #define AM_THREADS 512
 
 __global__ void __launch_bounds__(AM_THREADS) argmax_kernel(const float* __restrict__ logits, int vocab, int usable,
                                                             int* __restrict__ out) {
+    pdl_wait();
+    pdl_launch_dependents();
     __shared__ float best_v[AM_THREADS / 32];
     __shared__ int best_i[AM_THREADS / 32];
     const float* row = logits + (size_t)blockIdx.x * vocab;
@@ -40,6 +43,5 @@ __global__ void __launch_bounds__(AM_THREADS) argmax_kernel(const float* __restr
 MB_API int mb_argmax(const float* logits, int rows, int vocab, int usable, int* out, cudaStream_t s) {
     if (rows <= 0) return 0;
     if (usable <= 0 || usable > vocab) return MB_ERR_BAD_SIZE;
-    argmax_kernel<<<rows, AM_THREADS, 0, s>>>(logits, vocab, usable, out);
-    return mb_last_error();
+    return launch_kernel(argmax_kernel, rows, AM_THREADS, 0, s, 0, logits, vocab, usable, out);
 }
