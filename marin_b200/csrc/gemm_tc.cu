@@ -287,6 +287,129 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
     }
 }
 
+// ---- the persistent kernel for many tokens -------------------------------------------------------------------------
+// One CTA per SM walks over output tiles (128 weight rows x BN tokens).  Warp 0 feeds the shared-memory ring with
+// TMA and runs ahead into the next tile; warp 1 issues the MMAs into one of two accumulators in tensor memory;
+// warps 2..5 drain the other accumulator (tcgen05.ld, convert, store) meanwhile, so the tensor cores do not wait
+// for the epilogue.
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(192) gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w,
+                                                                 const __grid_constant__ CUtensorMap map_x,
+                                                                 void* __restrict__ out, int mode, int T, int N, int K,
+                                                                 int* __restrict__ error_flag) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    using L = TcSmem<BN>;
+    uint64_t* full = (uint64_t*)(smem + STAGES * L::STAGE_BYTES);
+    uint64_t* empty = full + STAGES;
+    uint64_t* acc_full = empty + STAGES;       // [2]
+    uint64_t* acc_empty = acc_full + 2;        // [2]
+    uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_n = (N + TC_BM - 1) / TC_BM, tiles_t = (T + BN - 1) / BN;
+    const int total_tiles = tiles_n * tiles_t;
+    const int nkb = (K + TC_BK - 1) / TC_BK;
+    constexpr uint32_t TMEM_COLS = 2 * BN <= 32 ? 32 : 2 * BN <= 64 ? 64 : 2 * BN <= 128 ? 128 : 2 * BN <= 256 ? 256 : 512;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+    pdl_wait();
+    pdl_launch_dependents();
+
+    if (warp == 0 && lane == 0) {
+        int it = 0;                                                   // k-blocks issued so far, over all tiles
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            const int n0 = (tile % tiles_n) * TC_BM, t0 = (tile / tiles_n) * BN;
+            for (int kb = 0; kb < nkb; ++kb, ++it) {
+                const int s = it % STAGES;
+                const uint32_t phase = (it / STAGES) & 1;
+                if (!mbar_wait(&empty[s], phase ^ 1)) { atomicExch(error_flag, 11); ok = false; break; }
+                mbar_expect_tx(&full[s], L::STAGE_BYTES);
+                uint8_t* a = smem + s * L::STAGE_BYTES;
+                tma_load_2d(a, &map_w, kb * TC_BK, n0, &full[s]);
+                tma_load_2d(a + L::A_BYTES, &map_x, kb * TC_BK, t0, &full[s]);
+            }
+        }
+    } else if (warp == 1 && lane == 0) {
+        constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+        int it = 0, local = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+            const int buf = local & 1;
+            const uint32_t acc_phase = (local >> 1) & 1;
+            if (!mbar_wait(&acc_empty[buf], acc_phase ^ 1)) { atomicExch(error_flag, 12); ok = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
+            for (int kb = 0; kb < nkb; ++kb, ++it) {
+                const int s = it % STAGES;
+                const uint32_t phase = (it / STAGES) & 1;
+                if (!mbar_wait(&full[s], phase)) { atomicExch(error_flag, 13); ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a = smem_u32(smem + s * L::STAGE_BYTES);
+                const uint64_t adesc = umma_desc(a), bdesc = umma_desc(a + L::A_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < TC_BK / 16; ++kk)
+                    umma_bf16(tmem_d, adesc + 2 * kk, bdesc + 2 * kk, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+                umma_commit(&empty[s]);
+            }
+            umma_commit(&acc_full[buf]);
+        }
+    } else if (warp >= 2) {
+        const int quarter = warp & 3;                                 // the 32 TMEM lanes this warp may read
+        int local = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
+            const int n0 = (tile % tiles_n) * TC_BM, t0 = (tile / tiles_n) * BN;
+            const int buf = local & 1;
+            const uint32_t acc_phase = (local >> 1) & 1;
+            if (ok && !mbar_wait(&acc_full[buf], acc_phase)) { if (lane == 0) atomicExch(error_flag, 14); ok = false; }
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int n = n0 + quarter * 32 + lane;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                float v[16];
+                tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c0), v);
+                if (n < N) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int t = t0 + c0 + j;
+                        if (t < T) store_out(out, mode, (size_t)t * N + n, v[j]);
+                    }
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
 // ---- host side ----------------------------------------------------------------------------------------------
 
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -338,6 +461,47 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* out, in
 
 // Tiles a launch with `bn` tokens per CTA would have (for the caller's choice of split).
 MB_API int mb_gemm_tc_tiles(int T, int N, int bn) { return ((N + TC_BM - 1) / TC_BM) * ((T + bn - 1) / bn); }
+
+template <int BN, int STAGES>
+static int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int mode, int T, int N, int K, int ctas,
+                             int* error_flag, cudaStream_t s) {
+    constexpr int smem = STAGES * TcSmem<BN>::STAGE_BYTES + 1024 + 256;
+    static_assert(smem <= 227 * 1024, "the ring does not fit shared memory");
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    const int tiles = ((N + TC_BM - 1) / TC_BM) * ((T + BN - 1) / BN);
+    return launch_kernel(gemm_tc_persistent_kernel<BN, STAGES>, dim3(tiles < ctas ? tiles : ctas), dim3(192), smem, s, 0, mw, mx, out,
+                         mode, T, N, K, error_flag);
+}
+
+// The persistent kernel: bn tokens per tile (a multiple of 16 from 128 to 256), `ctas` CTAs (one per SM).
+MB_API int mb_gemm_tc_persistent(const void* x, const void* w, void* out, int mode, int T, int N, int K, int bn, int ctas,
+                                 int* error_flag, cudaStream_t s) {
+    if (T <= 0 || N <= 0) return 0;
+    if (K <= 0 || K % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15) || ctas <= 0) return MB_ERR_BAD_SIZE;
+    if (mode < 0 || mode > 2) return MB_ERR_BAD_DTYPE;
+    CUtensorMap mw, mx;
+    int rc = make_map(&mw, w, N, K, TC_BM);
+    if (rc) return rc;
+    rc = make_map(&mx, x, T, K, bn);
+    if (rc) return rc;
+    switch (bn) {
+        case 128: return launch_persistent<128, 6>(mw, mx, out, mode, T, N, K, ctas, error_flag, s);
+        case 144: return launch_persistent<144, 6>(mw, mx, out, mode, T, N, K, ctas, error_flag, s);
+        case 160: return launch_persistent<160, 5>(mw, mx, out, mode, T, N, K, ctas, error_flag, s);
+        case 176: return launch_persistent<176, 5>(mw, mx, out, mode, T, N, K, ctas, error_flag, s);
+        case 192: return launch_persistent<192, 5>(mw, mx, out, mode, T, N, K, ctas, error_flag, s);
+        case 208: return launch_persistent<208, 4>(mw, mx, out, mode, T, N, K, ctas, error_flag, s);
+        case 224: return launch_persistent<224, 4>(mw, mx, out, mode, T, N, K, ctas, error_flag, s);
+        case 240: return launch_persistent<240, 4>(mw, mx, out, mode, T, N, K, ctas, error_flag, s);
+        case 256: return launch_persistent<256, 4>(mw, mx, out, mode, T, N, K, ctas, error_flag, s);
+        default: return MB_ERR_BAD_SIZE;
+    }
+}
 
 // x [T, K] bf16, w [N, K] bf16, out [T, N]: bf16 (mode 0), float32 (1), float32 += (2).  K must be a multiple
 // of 8 and both pointers 16-byte aligned (TMA).  splits > 1 needs partials (splits*T*N floats) and counters

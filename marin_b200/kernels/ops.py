@@ -132,6 +132,21 @@ def gemm_plan(T: int, N: int, K: int):
     return bn, splits
 
 
+PERSISTENT_TILES = (128, 144, 160, 176, 192, 208, 224, 240, 256)
+
+
+def persistent_plan(T: int, N: int) -> int:
+    """Tokens per tile for the persistent kernel: the tile width whose rounds over the SMs waste the least.
+    A tile's time grows with its width plus a fixed part (ramp-up of the ring, the epilogue's tail)."""
+    best = None
+    for bn in PERSISTENT_TILES:
+        tiles = -(-N // 128) * -(-T // bn)
+        cost = -(-tiles // SM_COUNT) * (bn + 24)
+        if best is None or cost < best[0]:
+            best = (cost, bn)
+    return best[1]
+
+
 def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
     """``out[t, n] (+)= sum_k x[t, k] * w[n, k]``.  bfloat16 inputs run on the tensor cores (tcgen05, float32
     accumulate); float32 inputs run on the CUDA cores in true float32."""
@@ -143,6 +158,13 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool =
         raise KernelError("gemm: accumulate needs a float32 output")
     if (use_tensor_cores and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and K % 8 == 0
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and T > 0):
+        mode = 2 if accumulate else (0 if out.dtype == torch.bfloat16 else 1)
+        if T > 128:
+            s = _gemm_scratch(x.device)
+            _check(_lib("mb_gemm_tc").mb_gemm_tc_persistent(_ptr(x), _ptr(w), _ptr(out), _c_int(mode), _c_int(T), _c_int(N),
+                                                           _c_int(K), _c_int(persistent_plan(T, N)), _c_int(SM_COUNT),
+                                                           _ptr(s["error"]), _stream()), "gemm (tensor cores, persistent)")
+            return
         bn, splits = gemm_plan(T, N, K)
         s = _gemm_scratch(x.device)
         mode = 2 if accumulate else (0 if out.dtype == torch.bfloat16 else 1)

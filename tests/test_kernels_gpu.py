@@ -284,7 +284,8 @@ def test_kernels_refuse_what_they_cannot_do(ops):
         ops.gemm(torch.zeros(2, 8, device=DEV, dtype=torch.float16), torch.zeros(2, 8, device=DEV, dtype=torch.float16), torch.zeros(2, 2, device=DEV, dtype=torch.float16))
 
 
-TC_SHAPES = [(1, 128, 64), (8, 6144, 2560), (8, 2560, 4096), (8, 2560, 9728), (64, 2560, 4096), (16, 300, 200), (17, 333, 136),
+TC_SHAPES = [(129, 2560, 4096), (300, 384, 1096), (1000, 1000, 200), (2048, 2560, 9728), (511, 6144, 2560),
+             (1, 128, 64), (8, 6144, 2560), (8, 2560, 4096), (8, 2560, 9728), (64, 2560, 4096), (16, 300, 200), (17, 333, 136),
              (33, 1000, 72), (100, 257, 320), (200, 640, 1024), (2048, 1280, 2560), (300, 128, 8), (129, 129, 4104)]
 
 
