@@ -109,6 +109,30 @@ __device__ __forceinline__ void store_out(void* out, int mode, size_t at, float 
     else ((float*)out)[at] += v;
 }
 
+// Sixteen consecutive tokens of one weight row: out[t_first + j, n] for j < 16, tokens below T only.  For "+=" all
+// sixteen old values are asked for before any is written back, so that their latencies overlap.
+__device__ __forceinline__ void store_chunk(void* out, int mode, int t_first, int n, int T, int N, const float* v) {
+    if (mode == TC_OUT_F32_ACC) {
+        float* o = (float*)out;
+        float old[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) old[j] = (t_first + j < T) ? o[(size_t)(t_first + j) * N + n] : 0.0f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+            if (t_first + j < T) o[(size_t)(t_first + j) * N + n] = old[j] + v[j];
+    } else if (mode == TC_OUT_BF16) {
+        bf16* o = (bf16*)out;
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+            if (t_first + j < T) o[(size_t)(t_first + j) * N + n] = __float2bfloat16_rn(v[j]);
+    } else {
+        float* o = (float*)out;
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+            if (t_first + j < T) o[(size_t)(t_first + j) * N + n] = v[j];
+    }
+}
+
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,
                                                       const __grid_constant__ CUtensorMap map_x, void* __restrict__ out,
@@ -246,12 +270,12 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
             for (int j = 0; j < 16; ++j) v[j] = 0.0f;
         }
         if (n < N) {
+            if (direct) store_chunk(out, mode, t0 + c0, n, T, N, v);
+            else {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                const int t = t0 + c0 + j;
-                if (t < T) {
-                    if (direct) store_out(out, mode, (size_t)t * N + n, v[j]);
-                    else partials[((size_t)blockIdx.z * T + t) * N + n] = v[j];
+                for (int j = 0; j < 16; ++j) {
+                    const int t = t0 + c0 + j;
+                    if (t < T) partials[((size_t)blockIdx.z * T + t) * N + n] = v[j];
                 }
             }
         }
@@ -389,13 +413,7 @@ __global__ void __launch_bounds__(192) gemm_tc_persistent_kernel(const __grid_co
             for (int c0 = 0; c0 < BN; c0 += 16) {
                 float v[16];
                 tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c0), v);
-                if (n < N) {
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const int t = t0 + c0 + j;
-                        if (t < T) store_out(out, mode, (size_t)t * N + n, v[j]);
-                    }
-                }
+                if (n < N) store_chunk(out, mode, t0 + c0, n, T, N, v);
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();

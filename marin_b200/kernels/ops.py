@@ -159,7 +159,7 @@ def gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool =
     if (use_tensor_cores and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and K % 8 == 0
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and T > 0):
         mode = 2 if accumulate else (0 if out.dtype == torch.bfloat16 else 1)
-        if T > 128:
+        if T > 128 and -(-N // 128) * -(-T // 128) >= SM_COUNT // 2:
             s = _gemm_scratch(x.device)
             _check(_lib("mb_gemm_tc").mb_gemm_tc_persistent(_ptr(x), _ptr(w), _ptr(out), _c_int(mode), _c_int(T), _c_int(N),
                                                            _c_int(K), _c_int(persistent_plan(T, N)), _c_int(SM_COUNT),
