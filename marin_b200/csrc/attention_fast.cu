@@ -294,26 +294,34 @@ __global__ void __launch_bounds__(D) attn_decode_merge_kernel(const float* __res
 #define PF_BM 64
 #define PF_BN 64
 #define PF_LD LDP
-#define PF_SMEM (3 * PF_BM * PF_LD * 2)
+#ifndef PF_BUFFERS
+#define PF_BUFFERS 1                  // 1: one buffer for keys and values (more CTAs per SM); 2: the next block is prefetched
+#endif
+#ifndef PF_MIN_CTAS
+#define PF_MIN_CTAS 3
+#endif
+#define PF_SMEM ((1 + 2 * PF_BUFFERS) * PF_BM * PF_LD * 2)
 
-// Rows of one 64-key block of K or V into shared memory; keys past `k_last` are zero (their pages may not exist).
+// Asks for the rows of one 64-key block of K or V (cp.async); keys past `k_last` are zero (their pages may not exist).
 __device__ __forceinline__ void load_kv_tile(bf16* dst, const bf16* __restrict__ cache, const int* __restrict__ table, int K, int kh,
                                              int page_shift, int key0, int k_last) {
     constexpr int CHUNKS = D / 8;
     const int page_mask = (1 << page_shift) - 1;
+#pragma unroll
     for (int idx = threadIdx.x; idx < PF_BN * CHUNKS; idx += 128) {
         const int row = idx / CHUNKS, c = idx % CHUNKS;
         const int key = key0 + row;
-        uint4 val = make_uint4(0, 0, 0, 0);
+        bf16* d = dst + row * PF_LD + c * 8;
         if (key <= k_last) {
             const size_t at = (((size_t)table[key >> page_shift] * K + kh) << page_shift) + (size_t)(key & page_mask);
-            val = *reinterpret_cast<const uint4*>(cache + at * D + c * 8);
+            cp_async16(d, cache + at * D + c * 8);
+        } else {
+            *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
         }
-        *reinterpret_cast<uint4*>(dst + row * PF_LD + c * 8) = val;
     }
 }
 
-__global__ void __launch_bounds__(128) attn_prefill_kernel(
+__global__ void __launch_bounds__(128, PF_MIN_CTAS) attn_prefill_kernel(
     const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache, bf16* __restrict__ out,
     const int* __restrict__ block_table, int max_pages, const int* __restrict__ cu_tokens, const int* __restrict__ seq_lens,
     int first_req, int K, int page_shift, float scale, int window) {
@@ -321,8 +329,7 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(
     pdl_launch_dependents();
     extern __shared__ __align__(16) uint8_t pf_smem[];
     bf16* sQ = reinterpret_cast<bf16*>(pf_smem);
-    bf16* sK = sQ + PF_BM * PF_LD;
-    bf16* sV = sK + PF_BN * PF_LD;
+    bf16* sKV = sQ + PF_BM * PF_LD;                  // [2 buffers][K then V][64][PF_LD]
     const int H = K * GROUP;
     const int r = first_req + blockIdx.z, h = blockIdx.y, qt = gridDim.x - 1 - blockIdx.x;   // long tiles first
     const int tok0 = cu_tokens[r], n = cu_tokens[r + 1] - tok0;
@@ -335,22 +342,22 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(
     const int* table = block_table + (size_t)r * max_pages;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-    {   // the query tile; rows past the request's tokens are zero
+    const int kb_first = k_lo / PF_BN, kb_last = q_last / PF_BN;
+    {   // the query tile (rows past the request's tokens are zero) and the first block of keys and values
         constexpr int CHUNKS = D / 8;
         for (int idx = threadIdx.x; idx < PF_BM * CHUNKS; idx += 128) {
             const int row = idx / CHUNKS, c = idx % CHUNKS;
-            uint4 val = make_uint4(0, 0, 0, 0);
-            if (row < rows) val = *reinterpret_cast<const uint4*>(q + ((size_t)(tok0 + qt * PF_BM + row) * H + h) * D + c * 8);
-            *reinterpret_cast<uint4*>(sQ + row * PF_LD + c * 8) = val;
+            bf16* d = sQ + row * PF_LD + c * 8;
+            if (row < rows) cp_async16(d, q + ((size_t)(tok0 + qt * PF_BM + row) * H + h) * D + c * 8);
+            else *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
         }
+        load_kv_tile(sKV, k_cache, table, K, kh, page_shift, kb_first * PF_BN, q_last);
+        load_kv_tile(sKV + PF_BN * PF_LD, v_cache, table, K, kh, page_shift, kb_first * PF_BN, q_last);
+        cp_async_commit();
     }
+    cp_async_wait<0>();
     __syncthreads();
-    uint32_t qa[D / 16][4];
-#pragma unroll
-    for (int kk = 0; kk < D / 16; ++kk) {
-        const int row = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
-        ldsm_x4((uint32_t)__cvta_generic_to_shared(sQ + row * PF_LD + kk * 16 + (lane >> 4) * 8), qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3]);
-    }
+    const uint32_t q_addr = (uint32_t)__cvta_generic_to_shared(sQ + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * PF_LD + (lane >> 4) * 8);
 
     float o[D / 8][4];
 #pragma unroll
@@ -361,38 +368,72 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(
     const int qp0 = q_first + row0, qp1 = qp0 + 8;
     const int lo0 = window > 0 ? max(0, qp0 - window + 1) : 0, lo1 = window > 0 ? max(0, qp1 - window + 1) : 0;
 
-    for (int kb = k_lo / PF_BN; kb <= q_last / PF_BN; ++kb) {
+    for (int kb = kb_first; kb <= kb_last; ++kb) {
         const int key0 = kb * PF_BN;
-        __syncthreads();                                       // the previous block's K and V are no longer read
-        load_kv_tile(sK, k_cache, table, K, kh, page_shift, key0, q_last);
-        load_kv_tile(sV, v_cache, table, K, kh, page_shift, key0, q_last);
-        __syncthreads();
+#if PF_BUFFERS == 2
+        const int buf = (kb - kb_first) & 1;
+        bf16* sK = sKV + (size_t)buf * 2 * PF_BN * PF_LD;
+        bf16* sV = sK + PF_BN * PF_LD;
+        if (kb < kb_last) {                                    // ask for the next block while this one is used
+            bf16* nK = sKV + (size_t)(buf ^ 1) * 2 * PF_BN * PF_LD;
+            load_kv_tile(nK, k_cache, table, K, kh, page_shift, key0 + PF_BN, q_last);
+            load_kv_tile(nK + PF_BN * PF_LD, v_cache, table, K, kh, page_shift, key0 + PF_BN, q_last);
+        }
+        cp_async_commit();
+        if (kb > kb_first) {
+            cp_async_wait<1>();                                // this block has arrived (the next may still be on its way)
+            __syncthreads();
+        }
+#else
+        bf16* sK = sKV;
+        bf16* sV = sK + PF_BN * PF_LD;
+        if (kb > kb_first) {                                   // the barrier at the end of the last block freed the buffer
+            load_kv_tile(sK, k_cache, table, K, kh, page_shift, key0, q_last);
+            load_kv_tile(sV, v_cache, table, K, kh, page_shift, key0, q_last);
+            cp_async_commit();
+            cp_async_wait<0>();
+            __syncthreads();
+        }
+#endif
 
         float s[PF_BN / 8][4];
 #pragma unroll
         for (int j = 0; j < PF_BN / 8; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f; }
+        const uint32_t k_addr = (uint32_t)__cvta_generic_to_shared(sK + ((lane & 7) + (lane >> 4) * 8) * PF_LD + ((lane >> 3) & 1) * 8);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
+            uint32_t qa[4];
+            ldsm_x4(q_addr + kk * 32, qa[0], qa[1], qa[2], qa[3]);
 #pragma unroll
             for (int j = 0; j < PF_BN / 8; j += 2) {
                 uint32_t b0, b1, b2, b3;
-                const int key = j * 8 + (lane & 7) + (lane >> 4) * 8;
-                ldsm_x4((uint32_t)__cvta_generic_to_shared(sK + key * PF_LD + kk * 16 + ((lane >> 3) & 1) * 8), b0, b1, b2, b3);
-                mma_bf16_16816(s[j], qa[kk], b0, b1);
-                mma_bf16_16816(s[j + 1], qa[kk], b2, b3);
+                ldsm_x4(k_addr + (uint32_t)(j * 8 * PF_LD * 2 + kk * 32), b0, b1, b2, b3);
+                mma_bf16_16816(s[j], qa, b0, b1);
+                mma_bf16_16816(s[j + 1], qa, b2, b3);
             }
         }
         // mask, online softmax
         float mx0 = -INFINITY, mx1 = -INFINITY;
+        // a block needs masking only if it reaches past the tile's first query or starts before the last query's window
+        const bool interior = key0 + PF_BN - 1 <= q_first && (window <= 0 || key0 >= q_last - window + 1);
+        if (interior) {
 #pragma unroll
-        for (int j = 0; j < PF_BN / 8; ++j) {
-            const int key = key0 + j * 8 + 2 * (lane & 3);
-            s[j][0] = (key <= qp0 && key >= lo0) ? s[j][0] * sl2 : -INFINITY;
-            s[j][1] = (key + 1 <= qp0 && key + 1 >= lo0) ? s[j][1] * sl2 : -INFINITY;
-            s[j][2] = (key <= qp1 && key >= lo1) ? s[j][2] * sl2 : -INFINITY;
-            s[j][3] = (key + 1 <= qp1 && key + 1 >= lo1) ? s[j][3] * sl2 : -INFINITY;
-            mx0 = fmaxf(mx0, fmaxf(s[j][0], s[j][1]));
-            mx1 = fmaxf(mx1, fmaxf(s[j][2], s[j][3]));
+            for (int j = 0; j < PF_BN / 8; ++j) {
+                s[j][0] *= sl2; s[j][1] *= sl2; s[j][2] *= sl2; s[j][3] *= sl2;
+                mx0 = fmaxf(mx0, fmaxf(s[j][0], s[j][1]));
+                mx1 = fmaxf(mx1, fmaxf(s[j][2], s[j][3]));
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < PF_BN / 8; ++j) {
+                const int key = key0 + j * 8 + 2 * (lane & 3);
+                s[j][0] = (key <= qp0 && key >= lo0) ? s[j][0] * sl2 : -INFINITY;
+                s[j][1] = (key + 1 <= qp0 && key + 1 >= lo0) ? s[j][1] * sl2 : -INFINITY;
+                s[j][2] = (key <= qp1 && key >= lo1) ? s[j][2] * sl2 : -INFINITY;
+                s[j][3] = (key + 1 <= qp1 && key + 1 >= lo1) ? s[j][3] * sl2 : -INFINITY;
+                mx0 = fmaxf(mx0, fmaxf(s[j][0], s[j][1]));
+                mx1 = fmaxf(mx1, fmaxf(s[j][2], s[j][3]));
+            }
         }
         mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
         mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
@@ -415,6 +456,7 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(
 #pragma unroll
         for (int i = 0; i < D / 8; ++i) { o[i][0] *= corr0; o[i][1] *= corr0; o[i][2] *= corr1; o[i][3] *= corr1; }
         // O += P V
+        const uint32_t v_addr = (uint32_t)__cvta_generic_to_shared(sV + ((lane & 7) + ((lane >> 3) & 1) * 8) * PF_LD + (lane >> 4) * 8);
 #pragma unroll
         for (int ks = 0; ks < PF_BN / 16; ++ks) {
             uint32_t pa[4];
@@ -425,13 +467,14 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(
 #pragma unroll
             for (int dt = 0; dt < D / 8; dt += 2) {
                 uint32_t b0, b1, b2, b3;
-                const int key = ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
-                ldsm_x4_trans((uint32_t)__cvta_generic_to_shared(sV + key * PF_LD + dt * 8 + (lane >> 4) * 8), b0, b1, b2, b3);
+                ldsm_x4_trans(v_addr + (uint32_t)(ks * 16 * PF_LD * 2 + dt * 16), b0, b1, b2, b3);
                 mma_bf16_16816(o[dt], pa, b0, b1);
                 mma_bf16_16816(o[dt + 1], pa, b2, b3);
             }
         }
+        __syncthreads();                                       // everyone is done with this block's buffers
     }
+    cp_async_wait<0>();
     // row sums live in four lanes each
     l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], 1);
     l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], 2);
