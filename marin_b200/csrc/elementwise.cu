@@ -43,14 +43,59 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
     }
 }
 
+// The same with the row held in registers: 16-byte loads, one pass over memory.  n is a multiple of 4, at most 4096.
+template <typename TO>
+__global__ void __launch_bounds__(256) rmsnorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ w, float eps,
+                                                          int unit_offset, TO* __restrict__ out, int n) {
+    pdl_wait();
+    pdl_launch_dependents();
+    __shared__ float scratch[32];
+    const float4* row = reinterpret_cast<const float4*>(x + (size_t)blockIdx.x * n);
+    const float4* w4 = reinterpret_cast<const float4*>(w);
+    const int n4 = n >> 2;
+    float4 v[4];
+    float ss = 0.0f;
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        const int i = threadIdx.x + r * 256;
+        v[r] = i < n4 ? row[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        ss += v[r].x * v[r].x + v[r].y * v[r].y + v[r].z * v[r].z + v[r].w * v[r].w;
+    }
+    ss = block_sum(ss, scratch);
+    const float scale = 1.0f / sqrtf(ss / (float)n + eps);
+    TO* dst = out + (size_t)blockIdx.x * n;
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        const int i = threadIdx.x + r * 256;
+        if (i < n4) {
+            float4 g = w4[i];
+            if (unit_offset) { g.x += 1.0f; g.y += 1.0f; g.z += 1.0f; g.w += 1.0f; }
+            const float a = v[r].x * scale * g.x, b = v[r].y * scale * g.y, c = v[r].z * scale * g.z, d = v[r].w * scale * g.w;
+            if (sizeof(TO) == 4) {
+                reinterpret_cast<float4*>(dst)[i] = make_float4(a, b, c, d);
+            } else {
+                __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+                uint2 packed;
+                packed.x = *reinterpret_cast<uint32_t*>(&lo);
+                packed.y = *reinterpret_cast<uint32_t*>(&hi);
+                reinterpret_cast<uint2*>(dst)[i] = packed;
+            }
+        }
+    }
+}
+
 MB_API int mb_rmsnorm(const float* x, const float* w, float eps, int unit_offset, void* out, int out_dtype,
                       int rows, int n, cudaStream_t s) {
     if (rows <= 0) return 0;
+    if (out_dtype != MB_F32 && out_dtype != MB_BF16) return MB_ERR_BAD_DTYPE;
+    const bool vec = n % 4 == 0 && n <= 4096 && n >= 512 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0 && ((uintptr_t)out & 15) == 0;
+    if (vec) {
+        if (out_dtype == MB_F32) return launch_kernel(rmsnorm_vec_kernel<float>, rows, 256, 0, s, 0, x, w, eps, unit_offset, (float*)out, n);
+        return launch_kernel(rmsnorm_vec_kernel<bf16>, rows, 256, 0, s, 0, x, w, eps, unit_offset, (bf16*)out, n);
+    }
     const int threads = n >= 1024 ? 256 : 128;
     if (out_dtype == MB_F32) return launch_kernel(rmsnorm_kernel<float>, rows, threads, 0, s, 0, x, w, eps, unit_offset, (float*)out, n);
-    else if (out_dtype == MB_BF16) return launch_kernel(rmsnorm_kernel<bf16>, rows, threads, 0, s, 0, x, w, eps, unit_offset, (bf16*)out, n);
-    else return MB_ERR_BAD_DTYPE;
-    return mb_last_error();
+    return launch_kernel(rmsnorm_kernel<bf16>, rows, threads, 0, s, 0, x, w, eps, unit_offset, (bf16*)out, n);
 }
 
 // ---- per-head RMSNorm of q and k, rotation of q and k, k and v into their pages ---------------------
@@ -62,51 +107,65 @@ __global__ void qk_norm_rope_write_kernel(const T* __restrict__ qkv, int row_str
                                           const int* __restrict__ positions, const float* __restrict__ inv_freq,
                                           int rotary_dim, int interleaved, const int* __restrict__ slot_mapping,
                                           T* __restrict__ k_cache, T* __restrict__ v_cache, int H, int K, int d,
-                                          int page_size, int heads_total) {
+                                          int page_size, int heads_total, int heads_per_warp) {
     pdl_wait();
     pdl_launch_dependents();
     extern __shared__ float smem[];
+    const int warps = blockDim.x >> 5;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x;
-    const int head = blockIdx.y * (blockDim.x >> 5) + warp;
-    if (head >= heads_total) return;
-    float* buf = smem + (size_t)warp * d;
-    const T* src = qkv + (size_t)t * row_stride + (size_t)head * d;
-    const bool is_q = head < H, is_k = !is_q && head < H + K;
-    float ss = 0.0f;
-    for (int i = lane; i < d; i += 32) { float v = to_f32(src[i]); buf[i] = v; ss += v * v; }
-    const float* w = is_q ? q_w : (is_k ? k_w : nullptr);
-    if (w != nullptr) {
-        ss = warp_sum(ss);
-        const float scale = 1.0f / sqrtf(ss / (float)d + eps);
-        __syncwarp();
-        for (int i = lane; i < d; i += 32) buf[i] = buf[i] * scale * w[i];
-    }
-    __syncwarp();
-    if ((is_q || is_k) && inv_freq != nullptr) {
+    const int half = rotary_dim >> 1;
+    float* cs_tab = smem;                                  // [half] cosines then [half] sines of this token's angles
+    float* buf = smem + 2 * half + (size_t)warp * d;
+    if (inv_freq != nullptr) {
         const float pos = (float)positions[t];
-        const int half = rotary_dim >> 1;
-        for (int i = lane; i < half; i += 32) {
-            const int ia = interleaved ? 2 * i : i, ib = interleaved ? 2 * i + 1 : i + half;
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
             float sn, cs;
             sincosf(pos * inv_freq[i], &sn, &cs);
-            const float a = buf[ia], b = buf[ib];
-            buf[ia] = a * cs - b * sn;
-            buf[ib] = b * cs + a * sn;
+            cs_tab[i] = cs;
+            cs_tab[half + i] = sn;
+        }
+    }
+    __syncthreads();
+    const int first = (blockIdx.y * warps + warp) * heads_per_warp;
+    for (int head = first; head < min(heads_total, first + heads_per_warp); ++head) {
+        const T* src = qkv + (size_t)t * row_stride + (size_t)head * d;
+        const bool is_q = head < H, is_k = !is_q && head < H + K;
+        float ss = 0.0f;
+        for (int i = lane; i < d; i += 32) { float v = to_f32(src[i]); buf[i] = v; ss += v * v; }
+        const float* w = is_q ? q_w : (is_k ? k_w : nullptr);
+        if (w != nullptr) {
+            ss = warp_sum(ss);
+            const float scale = 1.0f / sqrtf(ss / (float)d + eps);
+            __syncwarp();
+            for (int i = lane; i < d; i += 32) buf[i] = buf[i] * scale * w[i];
         }
         __syncwarp();
+        if ((is_q || is_k) && inv_freq != nullptr) {
+            for (int i = lane; i < half; i += 32) {
+                const int ia = interleaved ? 2 * i : i, ib = interleaved ? 2 * i + 1 : i + half;
+                const float cs = cs_tab[i], sn = cs_tab[half + i];
+                const float a = buf[ia], b = buf[ib];
+                buf[ia] = a * cs - b * sn;
+                buf[ib] = b * cs + a * sn;
+            }
+            __syncwarp();
+        }
+        T* dst = nullptr;
+        if (is_q) {
+            dst = q_out + ((size_t)t * H + head) * d;
+        } else {
+            const int slot = slot_mapping[t];
+            if (slot >= 0) {
+                const int kh = is_k ? head - H : head - H - K;
+                const size_t page = (size_t)(slot / page_size), off = (size_t)(slot % page_size);
+                dst = (is_k ? k_cache : v_cache) + ((page * K + kh) * page_size + off) * d;
+            }
+        }
+        if (dst != nullptr)
+            for (int i = lane; i < d; i += 32) dst[i] = from_f32<T>(buf[i]);
+        __syncwarp();
     }
-    T* dst;
-    if (is_q) {
-        dst = q_out + ((size_t)t * H + head) * d;
-    } else {
-        const int slot = slot_mapping[t];
-        if (slot < 0) return;
-        const int kh = is_k ? head - H : head - H - K;
-        const size_t page = (size_t)(slot / page_size), off = (size_t)(slot % page_size);
-        dst = (is_k ? k_cache : v_cache) + ((page * K + kh) * page_size + off) * d;
-    }
-    for (int i = lane; i < d; i += 32) dst[i] = from_f32<T>(buf[i]);
 }
 
 MB_API int mb_qk_norm_rope_write(const void* qkv, int dtype, void* q_out, const float* q_w, const float* k_w, float eps,
@@ -118,42 +177,47 @@ MB_API int mb_qk_norm_rope_write(const void* qkv, int dtype, void* q_out, const 
     const int heads_total = write_kv ? H + 2 * K : H;
     const int row_stride = heads_total * d;
     const int warps = 4;
-    dim3 grid(tokens, (heads_total + warps - 1) / warps);
-    const size_t smem = (size_t)warps * d * sizeof(float);
+    // few tokens: a warp per head, the heads spread over CTAs; many tokens: one CTA per token walks all heads and
+    // the token's sines and cosines are computed once
+    const int heads_per_warp = tokens >= 256 ? (heads_total + warps - 1) / warps : 1;
+    dim3 grid(tokens, (heads_total + warps * heads_per_warp - 1) / (warps * heads_per_warp));
+    const size_t smem = (size_t)(warps * d + rotary_dim) * sizeof(float);
     if (smem > 48 * 1024) return MB_ERR_BAD_SIZE;
     if (dtype == MB_F32)
         return launch_kernel(qk_norm_rope_write_kernel<float>, grid, warps * 32, smem, s, 0,
             (const float*)qkv, row_stride, (float*)q_out, q_w, k_w, eps, positions, inv_freq, rotary_dim, interleaved,
-            slot_mapping, (float*)k_cache, (float*)v_cache, H, K, d, page_size, heads_total);
+            slot_mapping, (float*)k_cache, (float*)v_cache, H, K, d, page_size, heads_total, heads_per_warp);
     else if (dtype == MB_BF16)
         return launch_kernel(qk_norm_rope_write_kernel<bf16>, grid, warps * 32, smem, s, 0,
             (const bf16*)qkv, row_stride, (bf16*)q_out, q_w, k_w, eps, positions, inv_freq, rotary_dim, interleaved,
-            slot_mapping, (bf16*)k_cache, (bf16*)v_cache, H, K, d, page_size, heads_total);
-    else return MB_ERR_BAD_DTYPE;
-    return mb_last_error();
+            slot_mapping, (bf16*)k_cache, (bf16*)v_cache, H, K, d, page_size, heads_total, heads_per_warp);
+    return MB_ERR_BAD_DTYPE;
 }
 
-// ---- SwiGLU: out[t, i] = g / (1 + exp(-g)) * u with g = gu[t, i], u = gu[t, I + i] -------------------
+// ---- SwiGLU: out[t, i] = g / (1 + exp(-g)) * u with g = gu[t, i], u = gu[t, I + i]; or, interleaved, with gate and
+// up in alternating blocks of 16 columns: g = gu[t, 32 (i / 16) + i % 16], u = 16 columns further -----------------
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total) {
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total, int interleaved) {
     pdl_wait();
     pdl_launch_dependents();
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (; idx < total; idx += stride) {
         const size_t t = idx / I, i = idx % I;
-        const float g = to_f32(gu[t * 2 * I + i]), u = to_f32(gu[t * 2 * I + I + i]);
+        const size_t gi = interleaved ? (i >> 4) * 32 + (i & 15) : i;
+        const size_t ui = interleaved ? gi + 16 : I + i;
+        const float g = to_f32(gu[t * 2 * I + gi]), u = to_f32(gu[t * 2 * I + ui]);
         out[idx] = from_f32<T>(g / (1.0f + expf(-g)) * u);
     }
 }
 
-MB_API int mb_swiglu(const void* gate_up, void* out, int dtype, int tokens, int I, cudaStream_t s) {
+MB_API int mb_swiglu(const void* gate_up, void* out, int dtype, int tokens, int I, int interleaved, cudaStream_t s) {
     const size_t total = (size_t)tokens * I;
     if (total == 0) return 0;
     const int threads = 256;
     const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
-    if (dtype == MB_F32) return launch_kernel(swiglu_kernel<float>, blocks, threads, 0, s, 0, (const float*)gate_up, (float*)out, I, total);
-    else if (dtype == MB_BF16) return launch_kernel(swiglu_kernel<bf16>, blocks, threads, 0, s, 0, (const bf16*)gate_up, (bf16*)out, I, total);
+    if (dtype == MB_F32) return launch_kernel(swiglu_kernel<float>, blocks, threads, 0, s, 0, (const float*)gate_up, (float*)out, I, total, interleaved);
+    else if (dtype == MB_BF16) return launch_kernel(swiglu_kernel<bf16>, blocks, threads, 0, s, 0, (const bf16*)gate_up, (bf16*)out, I, total, interleaved);
     else return MB_ERR_BAD_DTYPE;
     return mb_last_error();
 }

@@ -28,6 +28,7 @@
 #define TC_OUT_BF16 0
 #define TC_OUT_F32 1
 #define TC_OUT_F32_ACC 2
+#define TC_OUT_SWIGLU 3       // w holds gate and up rows interleaved in blocks of 16; out [T, N/2] bf16 = silu(gate) * up
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -130,6 +131,23 @@ __device__ __forceinline__ void store_chunk(void* out, int mode, int t_first, in
 #pragma unroll
         for (int j = 0; j < 16; ++j)
             if (t_first + j < T) o[(size_t)(t_first + j) * N + n] = v[j];
+    }
+}
+
+// SwiGLU in the epilogue.  The weight rows of a warp's 32 accumulator lanes are 16 gate rows followed by the 16 up
+// rows of the same intermediate indices, so lane l < 16 holds gate(i) and lane l + 16 holds up(i): one shuffle brings
+// them together and out[t, i] = g / (1 + exp(-g)) * u is written in bf16 (crates/tensor/src/silu.rs:18).  All 32
+// lanes must call this; n_base is the warp's first weight row (a multiple of 32).
+__device__ __forceinline__ void store_chunk_swiglu(void* out, int t_first, int n_base, int lane, int T, int N, const float* v) {
+    bf16* o = (bf16*)out;
+    const int half = N >> 1;
+    const int i = (n_base >> 1) + (lane & 15);
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const float u = __shfl_down_sync(0xffffffffu, v[j], 16);
+        const float g = v[j];
+        if (lane < 16 && t_first + j < T && i < half)
+            o[(size_t)(t_first + j) * half + i] = __float2bfloat16_rn(g / (1.0f + expf(-g)) * u);
     }
 }
 
@@ -269,7 +287,9 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
 #pragma unroll
             for (int j = 0; j < 16; ++j) v[j] = 0.0f;
         }
-        if (n < N) {
+        if (direct && mode == TC_OUT_SWIGLU) {
+            if (n0 + warp * 32 < N) store_chunk_swiglu(out, t0 + c0, n0 + warp * 32, lane, T, N, v);
+        } else if (n < N) {
             if (direct) store_chunk(out, mode, t0 + c0, n, T, N, v);
             else {
 #pragma unroll
@@ -413,7 +433,9 @@ __global__ void __launch_bounds__(192) gemm_tc_persistent_kernel(const __grid_co
             for (int c0 = 0; c0 < BN; c0 += 16) {
                 float v[16];
                 tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c0), v);
-                if (n < N) store_chunk(out, mode, t0 + c0, n, T, N, v);
+                if (mode == TC_OUT_SWIGLU) {
+                    if (n0 + quarter * 32 < N) store_chunk_swiglu(out, t0 + c0, n0 + quarter * 32, lane, T, N, v);
+                } else if (n < N) store_chunk(out, mode, t0 + c0, n, T, N, v);
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
@@ -501,7 +523,7 @@ MB_API int mb_gemm_tc_persistent(const void* x, const void* w, void* out, int mo
                                  int* error_flag, cudaStream_t s) {
     if (T <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15) || ctas <= 0) return MB_ERR_BAD_SIZE;
-    if (mode < 0 || mode > 2) return MB_ERR_BAD_DTYPE;
+    if (mode < 0 || mode > 3 || (mode == 3 && N % 32 != 0)) return MB_ERR_BAD_DTYPE;
     CUtensorMap mw, mx;
     int rc = make_map(&mw, w, N, K, TC_BM);
     if (rc) return rc;
@@ -528,7 +550,7 @@ static int gemm_tc_dispatch(const void* x, const void* w, void* out, int mode, i
                             float* partials, int* counters, int* error_flag, int cluster_reduce, cudaStream_t s) {
     if (T <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return MB_ERR_BAD_SIZE;
-    if (mode < 0 || mode > 2) return MB_ERR_BAD_DTYPE;
+    if (mode < 0 || mode > 3 || (mode == 3 && (splits > 1 || N % 32 != 0))) return MB_ERR_BAD_DTYPE;
     const int total_kb = (K + TC_BK - 1) / TC_BK;
     if (splits < 1) splits = 1;
     if (splits > total_kb) splits = total_kb;

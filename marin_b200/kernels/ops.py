@@ -261,11 +261,53 @@ def attention(q, k_cache, v_cache, out, ctx, block_table, H, K, d, scale, window
         _c_float(scale), _c_int(window), _stream()), "attention")
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, interleaved: bool = False) -> None:
+    """``out[t, i] = silu(g) * u``; gate and up are the two halves of a row of ``gate_up``, or (``interleaved``)
+    alternate in blocks of 16 columns."""
     _need_cuda(gate_up, out)
     T, I = out.shape
-    assert gate_up.shape == (T, 2 * I) and gate_up.dtype == out.dtype
-    _check(_lib("mb_elementwise").mb_swiglu(_ptr(gate_up), _ptr(out), _code(out), _c_int(T), _c_int(I), _stream()), "swiglu")
+    assert gate_up.shape == (T, 2 * I) and gate_up.dtype == out.dtype and (not interleaved or I % 16 == 0)
+    _check(_lib("mb_elementwise").mb_swiglu(_ptr(gate_up), _ptr(out), _code(out), _c_int(T), _c_int(I), _c_int(int(interleaved)),
+                                           _stream()), "swiglu")
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """One matrix whose rows alternate 16 gate rows and the 16 up rows of the same indices: the layout the
+    fused SwiGLU epilogue of the matrix product reads (``[I, h]`` twice → ``[2 I, h]``; ``I`` a multiple of 16)."""
+    I, h = gate.shape
+    assert up.shape == gate.shape and I % 16 == 0
+    return torch.stack([gate.view(I // 16, 16, h), up.view(I // 16, 16, h)], dim=1).reshape(2 * I, h)
+
+
+def can_fuse_swiglu(dtype, hidden: int, intermediate: int) -> bool:
+    return dtype == torch.bfloat16 and intermediate % 16 == 0 and hidden % 8 == 0
+
+
+def gemm_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor, out: torch.Tensor, workspace=None) -> None:
+    """``out = silu(x Wg^T) * (x Wu^T)`` with ``w_interleaved = interleave_gate_up(Wg, Wu)``: on the tensor cores the
+    activation is applied to the float32 accumulators in the epilogue and the ``[T, 2 I]`` intermediate never
+    exists; otherwise the product and the activation run as two kernels."""
+    _need_cuda(x, w_interleaved, out)
+    T, K = x.shape
+    N = w_interleaved.shape[0]
+    I = N // 2
+    assert tuple(out.shape) == (T, I) and w_interleaved.shape[1] == K and out.dtype == x.dtype
+    fused = (use_tensor_cores and x.dtype == torch.bfloat16 and w_interleaved.dtype == torch.bfloat16 and K % 8 == 0
+             and N % 32 == 0 and x.data_ptr() % 16 == 0 and w_interleaved.data_ptr() % 16 == 0 and T > 0)
+    if not fused:
+        tmp = workspace.get("gate_up", (T, N), x.dtype) if workspace is not None else torch.empty(T, N, device=x.device, dtype=x.dtype)
+        gemm(x, w_interleaved, tmp)
+        swiglu(tmp, out, interleaved=True)
+        return
+    s = _gemm_scratch(x.device)
+    if T > 128 and -(-N // 128) * -(-T // 128) >= SM_COUNT // 2:
+        _check(_lib("mb_gemm_tc").mb_gemm_tc_persistent(_ptr(x), _ptr(w_interleaved), _ptr(out), _c_int(3), _c_int(T), _c_int(N),
+                                                       _c_int(K), _c_int(persistent_plan(T, N)), _c_int(SM_COUNT),
+                                                       _ptr(s["error"]), _stream()), "gemm+swiglu (tensor cores, persistent)")
+        return
+    bn, _ = gemm_plan(T, N, K)
+    _check(_lib("mb_gemm_tc").mb_gemm_tc_cluster(_ptr(x), _ptr(w_interleaved), _ptr(out), _c_int(3), _c_int(T), _c_int(N), _c_int(K),
+                                                _c_int(bn), _c_int(1), _ptr(s["error"]), _stream()), "gemm+swiglu (tensor cores)")
 
 
 def gather_rows(src: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:

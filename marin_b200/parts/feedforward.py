@@ -41,14 +41,24 @@ class SwiGLU(FeedForward):
     def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
         n = self.name
         gate, up = tensors.pop(f"{n}.gate_proj.weight"), tensors.pop(f"{n}.up_proj.weight")
-        self.w_gate_up = rt.matrix(torch.cat([gate, up], dim=0))
+        # One matrix for both projections.  Where the tensor-core kernel can apply the activation in its epilogue
+        # the rows are interleaved in blocks of 16 (gate, up, gate, ...) so that a gate value and its up value
+        # meet in one warp; otherwise gate rows come first, then up rows.
+        self.fused = ops.can_fuse_swiglu(rt.dtype, self.hidden, self.intermediate)
+        if self.fused:
+            self.w_gate_up = rt.matrix(ops.interleave_gate_up(gate, up))
+        else:
+            self.w_gate_up = rt.matrix(torch.cat([gate, up], dim=0))
         self.w_down = rt.matrix(tensors.pop(f"{n}.down_proj.weight"))
 
     def forward(self, x: torch.Tensor, ctx, residual: torch.Tensor) -> None:
         T = x.shape[0]
         ws = ctx.workspace
-        gate_up = ws.get("gate_up", (T, 2 * self.intermediate), x.dtype)
-        ops.gemm(x, self.w_gate_up, gate_up)
         act = ws.get("ffn_act", (T, self.intermediate), x.dtype)
-        ops.swiglu(gate_up, act)
+        if self.fused:
+            ops.gemm_swiglu(x, self.w_gate_up, act, ws)
+        else:
+            gate_up = ws.get("gate_up", (T, 2 * self.intermediate), x.dtype)
+            ops.gemm(x, self.w_gate_up, gate_up)
+            ops.swiglu(gate_up, act)
         ops.gemm(act, self.w_down, residual, accumulate=True)

@@ -97,10 +97,28 @@ def attention(q, k_cache, v_cache, out, ctx, block_table, H, K, d, scale, window
     out.copy_(res.view(T, H * d).to(out.dtype))
 
 
-def swiglu(gate_up, out):
-    I = out.shape[1]
-    g, u = gate_up[:, :I].float(), gate_up[:, I:].float()
+def swiglu(gate_up, out, interleaved=False):
+    T, I = out.shape
+    if interleaved:
+        blocks = gate_up.float().view(T, I // 16, 2, 16)
+        g, u = blocks[:, :, 0, :].reshape(T, I), blocks[:, :, 1, :].reshape(T, I)
+    else:
+        g, u = gate_up[:, :I].float(), gate_up[:, I:].float()
     out.copy_((g / (1.0 + torch.exp(-g)) * u).to(out.dtype))
+
+
+def interleave_gate_up(gate, up):
+    I, h = gate.shape
+    return torch.stack([gate.view(I // 16, 16, h), up.view(I // 16, 16, h)], dim=1).reshape(2 * I, h)
+
+
+def can_fuse_swiglu(dtype, hidden, intermediate):
+    return dtype == torch.bfloat16 and intermediate % 16 == 0 and hidden % 8 == 0
+
+
+def gemm_swiglu(x, w_interleaved, out, workspace=None):
+    y = x.float() @ w_interleaved.float().t()
+    swiglu(y, out, interleaved=True)
 
 
 def gather_rows(src, rows, out):
@@ -115,7 +133,8 @@ def argmax(logits, usable, out):
     out.copy_(torch.argmax(logits[:, :usable], dim=-1).to(torch.int32))
 
 
-NAMES = ["embed", "rmsnorm", "gemm", "qk_norm_rope_write", "attention", "swiglu", "gather_rows", "add_into", "argmax"]
+NAMES = ["embed", "rmsnorm", "gemm", "qk_norm_rope_write", "attention", "swiglu", "gather_rows", "add_into", "argmax",
+         "interleave_gate_up", "can_fuse_swiglu", "gemm_swiglu"]
 
 
 @contextmanager

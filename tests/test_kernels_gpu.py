@@ -40,7 +40,7 @@ def test_embed(ops, dtype, vocab, h, tokens):
 
 
 @pytest.mark.parametrize("out_dtype", DTYPES)
-@pytest.mark.parametrize("rows,n,eps,unit", [(3, 72, 1e-5, False), (17, 2560, 1e-6, False), (1, 5120, 1e-6, True), (5, 1, 1e-3, False), (2, 1031, 1e-6, False)])
+@pytest.mark.parametrize("rows,n,eps,unit", [(3, 72, 1e-5, False), (17, 2560, 1e-6, False), (300, 4096, 1e-6, True), (9, 512, 1e-5, False), (4, 4092, 1e-6, False), (1, 5120, 1e-6, True), (5, 1, 1e-3, False), (2, 1031, 1e-6, False)])
 def test_rmsnorm(ops, out_dtype, rows, n, eps, unit):
     g = torch.Generator(device=DEV).manual_seed(2)
     x = torch.randn(rows, n, device=DEV, generator=g) * 3.0
@@ -89,7 +89,7 @@ def test_gemm_rows_do_not_depend_on_the_batch(ops):
                                                        (5, 5, 32, 16, True, False, 8), (3, 1, 80, 80, False, True, 2), (2, 2, 256, 256, False, True, 32)])
 def test_qk_norm_rope_write(ops, dtype, H, K, d, rot, inter, norm, page):
     g = torch.Generator(device=DEV).manual_seed(5)
-    T, pages = 23, 12
+    T, pages = (23, 12) if d != 48 else (300, 24)        # many tokens take the one-CTA-per-token path
     qkv = torch.randn(T, (H + 2 * K) * d, device=DEV, generator=g).to(dtype)
     qw = (1 + 0.1 * torch.randn(d, device=DEV, generator=g)) if norm else None
     kw = (1 + 0.1 * torch.randn(d, device=DEV, generator=g)) if norm else None
@@ -342,3 +342,28 @@ def test_attention_long_contexts_bf16(ops, H, K, d, page, window):
     ops.attention(q, kc, vc, out, ctx, table, H, K, d, 1.0 / math.sqrt(d), window)
     ref.attention(q, kc, vc, want, ctx, table, H, K, d, 1.0 / math.sqrt(d), window)
     torch.testing.assert_close(out.float(), want.float(), rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("T,I,K", [(1, 9728, 2560), (8, 320, 96), (40, 144, 72), (300, 1024, 256), (2048, 2048, 512), (64, 4864, 1280)])
+def test_gemm_with_swiglu_epilogue(ops, T, I, K):
+    """silu(x Wg^T) * (x Wu^T) with the activation applied to the float32 accumulators, against float64."""
+    g = torch.Generator(device=DEV).manual_seed(16)
+    x = torch.randn(T, K, device=DEV, generator=g).to(torch.bfloat16)
+    wg = (torch.randn(I, K, device=DEV, generator=g) / math.sqrt(K) * 2).to(torch.bfloat16)
+    wu = (torch.randn(I, K, device=DEV, generator=g) / math.sqrt(K) * 2).to(torch.bfloat16)
+    assert ops.can_fuse_swiglu(torch.bfloat16, K, I)
+    w = ops.interleave_gate_up(wg, wu)
+    out = torch.empty(T, I, device=DEV, dtype=torch.bfloat16)
+    ops.gemm_swiglu(x, w, out)
+    ops.check_device_errors()
+    gd, ud = x.double() @ wg.double().t(), x.double() @ wu.double().t()
+    want = gd / (1 + torch.exp(-gd)) * ud
+    torch.testing.assert_close(out.double(), want, rtol=1e-2, atol=1e-2)
+    # the two-kernel form gives the same up to the rounding of the intermediate
+    ops.use_tensor_cores = False
+    try:
+        out2 = torch.empty_like(out)
+        ops.gemm_swiglu(x, w, out2)
+    finally:
+        ops.use_tensor_cores = True
+    torch.testing.assert_close(out2.double(), want, rtol=3e-2, atol=3e-2)
