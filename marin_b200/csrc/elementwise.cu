@@ -168,6 +168,79 @@ __global__ void qk_norm_rope_write_kernel(const T* __restrict__ qkv, int row_str
     }
 }
 
+// The same for bf16 heads of 64, 128 or 256 elements with the rotation over the whole head (half-split pairs): a
+// head is LPH = d/8 consecutive lanes holding 8 elements each in registers (one 16-byte load, one 16-byte store);
+// the sum of squares and the rotation partner (element i +- d/2 lies LPH/2 lanes away) travel by shuffle; all heads
+// of a token are in flight at once.
+template <int LPH>
+__global__ void __launch_bounds__(256) qk_norm_rope_write_fast_kernel(
+    const bf16* __restrict__ qkv, int row_stride, bf16* __restrict__ q_out, const float* __restrict__ q_w,
+    const float* __restrict__ k_w, float eps, const int* __restrict__ positions, const float* __restrict__ inv_freq,
+    const int* __restrict__ slot_mapping, bf16* __restrict__ k_cache, bf16* __restrict__ v_cache, int H, int K, int page_size,
+    int heads_total) {
+    pdl_wait();
+    pdl_launch_dependents();
+    constexpr int d = LPH * 8, half = d / 2;
+    __shared__ float cs_tab[half], sn_tab[half];
+    const int t = blockIdx.x;
+    if (inv_freq != nullptr) {
+        const float pos = (float)positions[t];
+        for (int i = threadIdx.x; i < half; i += 256) sincosf(pos * inv_freq[i], &sn_tab[i], &cs_tab[i]);
+    }
+    __syncthreads();
+    const int sub = threadIdx.x % LPH;
+    const int slot = slot_mapping[t];
+    for (int base = 0; base < heads_total; base += 256 / LPH) {
+        const int head = base + threadIdx.x / LPH;
+        const bool valid = head < heads_total;
+        const int hh = valid ? head : heads_total - 1;
+        const bool is_q = hh < H, is_k = !is_q && hh < H + K;
+        const uint4 raw = *reinterpret_cast<const uint4*>(qkv + (size_t)t * row_stride + (size_t)hh * d + sub * 8);
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h2[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+        const float* w = is_q ? q_w : (is_k ? k_w : nullptr);
+        float ss = 0.0f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss += v[e] * v[e];
+#pragma unroll
+        for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (w != nullptr) {
+            const float scale = 1.0f / sqrtf(ss / (float)d + eps);
+            const float4 w0 = *reinterpret_cast<const float4*>(w + sub * 8), w1 = *reinterpret_cast<const float4*>(w + sub * 8 + 4);
+            v[0] = v[0] * scale * w0.x; v[1] = v[1] * scale * w0.y; v[2] = v[2] * scale * w0.z; v[3] = v[3] * scale * w0.w;
+            v[4] = v[4] * scale * w1.x; v[5] = v[5] * scale * w1.y; v[6] = v[6] * scale * w1.z; v[7] = v[7] * scale * w1.w;
+        }
+        const bool rotate = (is_q || is_k) && inv_freq != nullptr;
+        const bool first_half = sub < LPH / 2;
+        const int idx0 = (first_half ? sub : sub - LPH / 2) * 8;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const float other = __shfl_xor_sync(0xffffffffu, v[e], LPH / 2);
+            if (rotate) {
+                const float cs = cs_tab[idx0 + e], sn = sn_tab[idx0 + e];
+                v[e] = first_half ? v[e] * cs - other * sn : v[e] * cs + other * sn;
+            }
+        }
+        bf16* dst = nullptr;
+        if (valid) {
+            if (is_q) dst = q_out + ((size_t)t * H + hh) * d;
+            else if (slot >= 0) {
+                const int kh = is_k ? hh - H : hh - H - K;
+                dst = (is_k ? k_cache : v_cache) + (((size_t)(slot / page_size) * K + kh) * page_size + (size_t)(slot % page_size)) * d;
+            }
+        }
+        if (dst != nullptr) {
+            uint4 packed;
+            __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) p2[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+            *reinterpret_cast<uint4*>(dst + sub * 8) = packed;
+        }
+    }
+}
+
 MB_API int mb_qk_norm_rope_write(const void* qkv, int dtype, void* q_out, const float* q_w, const float* k_w, float eps,
                                  const int* positions, const float* inv_freq, int rotary_dim, int interleaved,
                                  const int* slot_mapping, void* k_cache, void* v_cache, int tokens, int H, int K, int d,
@@ -176,6 +249,18 @@ MB_API int mb_qk_norm_rope_write(const void* qkv, int dtype, void* q_out, const 
     if (d <= 0 || rotary_dim > d || (rotary_dim & 1)) return MB_ERR_BAD_SIZE;
     const int heads_total = write_kv ? H + 2 * K : H;
     const int row_stride = heads_total * d;
+    if (dtype == MB_BF16 && (d == 64 || d == 128 || d == 256) && !interleaved && (inv_freq == nullptr || rotary_dim == d) &&
+        ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)q_out & 15) == 0 && ((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0 &&
+        ((uintptr_t)q_w & 15) == 0 && ((uintptr_t)k_w & 15) == 0) {
+        if (d == 64)
+            return launch_kernel(qk_norm_rope_write_fast_kernel<8>, tokens, 256, 0, s, 0, (const bf16*)qkv, row_stride, (bf16*)q_out, q_w, k_w,
+                                 eps, positions, inv_freq, slot_mapping, (bf16*)k_cache, (bf16*)v_cache, H, K, page_size, heads_total);
+        if (d == 128)
+            return launch_kernel(qk_norm_rope_write_fast_kernel<16>, tokens, 256, 0, s, 0, (const bf16*)qkv, row_stride, (bf16*)q_out, q_w, k_w,
+                                 eps, positions, inv_freq, slot_mapping, (bf16*)k_cache, (bf16*)v_cache, H, K, page_size, heads_total);
+        return launch_kernel(qk_norm_rope_write_fast_kernel<32>, tokens, 256, 0, s, 0, (const bf16*)qkv, row_stride, (bf16*)q_out, q_w, k_w,
+                             eps, positions, inv_freq, slot_mapping, (bf16*)k_cache, (bf16*)v_cache, H, K, page_size, heads_total);
+    }
     const int warps = 4;
     // few tokens: a warp per head, the heads spread over CTAs; many tokens: one CTA per token walks all heads and
     // the token's sines and cosines are computed once

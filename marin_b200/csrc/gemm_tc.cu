@@ -136,7 +136,8 @@ __device__ __forceinline__ void store_chunk(void* out, int mode, int t_first, in
 
 // SwiGLU in the epilogue.  The weight rows of a warp's 32 accumulator lanes are 16 gate rows followed by the 16 up
 // rows of the same intermediate indices, so lane l < 16 holds gate(i) and lane l + 16 holds up(i): one shuffle brings
-// them together and out[t, i] = g / (1 + exp(-g)) * u is written in bf16 (crates/tensor/src/silu.rs:18).  All 32
+// them together and out[t, i] = g / (1 + exp(-g)) * u is written in bf16 (crates/tensor/src/silu.rs:18; the fast
+// exponential and division are accurate to a few float32 ulps, far inside the bf16 rounding of the result).  All 32
 // lanes must call this; n_base is the warp's first weight row (a multiple of 32).
 __device__ __forceinline__ void store_chunk_swiglu(void* out, int t_first, int n_base, int lane, int T, int N, const float* v) {
     bf16* o = (bf16*)out;
@@ -147,7 +148,7 @@ __device__ __forceinline__ void store_chunk_swiglu(void* out, int t_first, int n
         const float u = __shfl_down_sync(0xffffffffu, v[j], 16);
         const float g = v[j];
         if (lane < 16 && t_first + j < T && i < half)
-            o[(size_t)(t_first + j) * half + i] = __float2bfloat16_rn(g / (1.0f + expf(-g)) * u);
+            o[(size_t)(t_first + j) * half + i] = __float2bfloat16_rn(__fdividef(g, 1.0f + __expf(-g)) * u);
     }
 }
 
@@ -334,14 +335,14 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
 // ---- the persistent kernel for many tokens -------------------------------------------------------------------------
 // One CTA per SM walks over output tiles (128 weight rows x BN tokens).  Warp 0 feeds the shared-memory ring with
 // TMA and runs ahead into the next tile; warp 1 issues the MMAs into one of two accumulators in tensor memory;
-// warps 2..5 drain the other accumulator (tcgen05.ld, convert, store) meanwhile, so the tensor cores do not wait
+// warps 2..9 drain the other accumulator (tcgen05.ld, convert, store; two warps per 32-lane quarter) meanwhile, so the tensor cores do not wait
 // for the epilogue.
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
 template <int BN, int STAGES>
-__global__ void __launch_bounds__(192) gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w,
+__global__ void __launch_bounds__(320) gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                  const __grid_constant__ CUtensorMap map_x,
                                                                  void* __restrict__ out, int mode, int T, int N, int K,
                                                                  int* __restrict__ error_flag) {
@@ -362,7 +363,7 @@ __global__ void __launch_bounds__(192) gemm_tc_persistent_kernel(const __grid_co
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 8); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
@@ -418,6 +419,8 @@ __global__ void __launch_bounds__(192) gemm_tc_persistent_kernel(const __grid_co
         }
     } else if (warp >= 2) {
         const int quarter = warp & 3;                                 // the 32 TMEM lanes this warp may read
+        const int col_half = (warp - 2) >> 2;                         // two warps share a quarter: each takes half the columns
+        constexpr int HALF_COLS = ((BN / 16 + 1) / 2) * 16;
         int local = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
@@ -430,7 +433,7 @@ __global__ void __launch_bounds__(192) gemm_tc_persistent_kernel(const __grid_co
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int n = n0 + quarter * 32 + lane;
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 16) {
+            for (int c0 = col_half * HALF_COLS; c0 < (col_half == 0 ? HALF_COLS : BN); c0 += 16) {
                 float v[16];
                 tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c0), v);
                 if (mode == TC_OUT_SWIGLU) {
@@ -514,7 +517,7 @@ static int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, void*
         configured = true;
     }
     const int tiles = ((N + TC_BM - 1) / TC_BM) * ((T + BN - 1) / BN);
-    return launch_kernel(gemm_tc_persistent_kernel<BN, STAGES>, dim3(tiles < ctas ? tiles : ctas), dim3(192), smem, s, 0, mw, mx, out,
+    return launch_kernel(gemm_tc_persistent_kernel<BN, STAGES>, dim3(tiles < ctas ? tiles : ctas), dim3(320), smem, s, 0, mw, mx, out,
                          mode, T, N, K, error_flag);
 }
 

@@ -86,7 +86,8 @@ def test_gemm_rows_do_not_depend_on_the_batch(ops):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,K,d,rot,inter,norm,page", [(4, 2, 16, 16, False, True, 4), (6, 3, 48, 48, False, True, 16), (8, 2, 128, 128, False, True, 16),
-                                                       (5, 5, 32, 16, True, False, 8), (3, 1, 80, 80, False, True, 2), (2, 2, 256, 256, False, True, 32)])
+                                                       (5, 5, 32, 16, True, False, 8), (3, 1, 80, 80, False, True, 2), (2, 2, 256, 256, False, True, 32),
+                                                       (7, 1, 64, 64, False, True, 16), (40, 8, 128, 128, False, False, 16), (4, 4, 128, 64, False, True, 16)])
 def test_qk_norm_rope_write(ops, dtype, H, K, d, rot, inter, norm, page):
     g = torch.Generator(device=DEV).manual_seed(5)
     T, pages = (23, 12) if d != 48 else (300, 24)        # many tokens take the one-CTA-per-token path
