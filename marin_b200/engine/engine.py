@@ -83,7 +83,7 @@ class Engine:
     def __init__(self, model: Union[str, None] = None, *, config: Optional[ModelConfig] = None, seed: int = 0,
                  dtype="bfloat16", ctx: Optional[int] = None, page_size: int = 16, num_pages: Optional[int] = None,
                  max_batch: int = 64, token_budget: int = 2048, device="cuda:0", cuda_graphs: bool = True,
-                 _rt: Optional[Runtime] = None):
+                 device_sampling: bool = True, _rt: Optional[Runtime] = None):
         """``model``: a folder with config.json and model.safetensors; or ``config`` + ``seed`` for
         random weights.  ``num_pages``: pages per cache group (default: enough for ``max_batch``
         sequences of ``ctx`` positions)."""
@@ -109,6 +109,8 @@ class Engine:
             sizes = [b for b in (1, 2, 4, 8, 16, 32, 64, 128, 256) if b < max_batch] + [max_batch]
             self.runner.enable_graphs(sizes)
         self.max_batch, self.token_budget = max_batch, token_budget
+        #: False: logits go to the host and the host sampler (the reference's algorithm line by line) picks the token
+        self.device_sampling = device_sampling and self.rt.device.type == "cuda"
         self.scheduler = Scheduler(self.cache, max_batch, token_budget, self.ctx)
         self._requests: Dict[Hashable, Request] = {}
         self._samplers: Dict[Hashable, Sampler] = {}
@@ -184,6 +186,25 @@ class Engine:
         if all(p.request.params.greedy and p.request.params.usable_vocab in (None, vocab) for p in rows):
             ids = torch.empty(len(rows), device=logits.device, dtype=torch.int32)
             ops.argmax(logits, vocab, ids)
+            for p, token in zip(rows, ids.tolist()):
+                out[p.request.req_id] = int(token)
+            return out
+        if self.device_sampling:
+            # the kept set and the draw are computed on the device; each request's own splitmix64 stream gives its u
+            n = len(rows)
+            host = torch.empty(5, n, dtype=torch.float32)
+            ints = host.view(torch.int32)
+            for i, p in enumerate(rows):
+                prm = p.request.params
+                ints[0, i] = prm.usable_vocab or vocab
+                host[1, i] = prm.temperature
+                ints[2, i] = prm.top_k
+                host[3, i] = prm.top_p
+                host[4, i] = 0.0 if prm.greedy else samplers[p.request.req_id].next_unit()
+            dev = host.pin_memory().to(logits.device, non_blocking=True)
+            dint = dev.view(torch.int32)
+            ids = torch.empty(n, device=logits.device, dtype=torch.int32)
+            ops.sample(logits, dint[0], dev[1], dint[2], dev[3], dev[4], ids)
             for p, token in zip(rows, ids.tolist()):
                 out[p.request.req_id] = int(token)
             return out

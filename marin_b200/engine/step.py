@@ -250,19 +250,20 @@ class Runner:
             return g["logits"][: len(entries)]
         return g["logits"][torch.as_tensor(rows, device=self.rt.device, dtype=torch.long)]
 
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], observe=None) -> torch.Tensor:
         """Runs the entries as one batch; returns float32 logits ``[wanted, vocab]`` on the device,
-        in the order of the entries and of each entry's ``want``."""
+        in the order of the entries and of each entry's ``want``.  ``observe`` (see ``Model.forward``) turns
+        graph replay off for this step."""
         self._validate(entries)
         wanted = [(e.req_id, self.cache.length(e.req_id) + len(e.tokens)) for e in entries]
         if not self.cache.can_reserve(wanted):
             raise OutOfPages(f"the step needs more pages than are free ({self.cache.free_pages()} free per group)")
         for req_id, new_len in wanted:
             self.cache.reserve(req_id, new_len)
-        logits = self._step_graph(entries)
+        logits = self._step_graph(entries) if observe is None else None
         if logits is None:
             ctx = self.build_context(entries)
-            logits = self.model.forward(ctx, self.views)
+            logits = self.model.forward(ctx, self.views, observe) if observe is not None else self.model.forward(ctx, self.views)
         for req_id, new_len in wanted:
             self.cache.commit(req_id, new_len)
         self.steps_run += 1

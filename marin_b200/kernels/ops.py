@@ -330,3 +330,16 @@ def argmax(logits: torch.Tensor, usable: int, out: torch.Tensor) -> None:
     rows, vocab = logits.shape
     assert logits.dtype == torch.float32 and out.dtype == torch.int32 and out.numel() == rows
     _check(_lib("mb_sampling").mb_argmax(_ptr(logits), _c_int(rows), _c_int(vocab), _c_int(usable), _ptr(out), _stream()), "argmax")
+
+
+def sample(logits: torch.Tensor, usable: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
+           uniform: torch.Tensor, out: torch.Tensor) -> None:
+    """Draws one token per row from the reference's kept set (temperature, top-k, top-p; temperature 0 = greedy):
+    ``uniform[r]`` in [0, 1) selects the token by walking the kept ids in increasing order."""
+    _need_cuda(logits, usable, temperature, top_k, top_p, uniform, out)
+    rows, vocab = logits.shape
+    assert logits.dtype == torch.float32 and out.dtype == torch.int32 and usable.dtype == torch.int32 and top_k.dtype == torch.int32
+    assert temperature.dtype == torch.float32 and top_p.dtype == torch.float32 and uniform.dtype == torch.float32
+    assert all(t.numel() == rows for t in (usable, temperature, top_k, top_p, uniform, out))
+    _check(_lib("mb_sampling").mb_sample(_ptr(logits), _c_int(rows), _c_int(vocab), _ptr(usable), _ptr(temperature), _ptr(top_k),
+                                        _ptr(top_p), _ptr(uniform), _ptr(out), _stream()), "sample")

@@ -53,15 +53,20 @@ class Model:
         if getattr(self.head, "tied", False):
             self.head.tie(self.embedding.table)
 
-    def forward(self, ctx, caches) -> torch.Tensor:
+    def forward(self, ctx, caches, observe=None) -> torch.Tensor:
         """Runs the step's tokens through every schedule entry; returns float32 logits
-        ``[len(ctx.logit_rows), vocab]`` at the rows asked for."""
+        ``[len(ctx.logit_rows), vocab]`` at the rows asked for.  ``observe(i, hidden)`` is called with the
+        residual stream (float32 ``[T, hidden]``) before the first entry (i = 0) and after entry i - 1."""
         rt, ws = self.rt, ctx.workspace
         T = ctx.num_tokens
         hidden = ws.get("hidden", (T, self.spec.hidden_size), torch.float32)
         self.embedding.forward(ctx.token_ids, hidden)
+        if observe is not None:
+            observe(0, hidden)
         for i, entry in enumerate(self.spec.schedule):
             self.blocks[entry.layer].forward(hidden, ctx, caches.view(i, ctx))
+            if observe is not None:
+                observe(i + 1, hidden)
         W = ctx.num_logit_rows
         if W == 0:
             return torch.empty(0, self.spec.vocab_size, device=rt.device, dtype=torch.float32)

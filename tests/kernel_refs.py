@@ -133,7 +133,25 @@ def argmax(logits, usable, out):
     out.copy_(torch.argmax(logits[:, :usable], dim=-1).to(torch.int32))
 
 
-NAMES = ["embed", "rmsnorm", "gemm", "qk_norm_rope_write", "attention", "swiglu", "gather_rows", "add_into", "argmax",
+def sample(logits, usable, temperature, top_k, top_p, uniform, out):
+    """The host sampler's kept set, walked in id order."""
+    import numpy as np
+
+    from marin_b200.sampling import Sampler, SamplingParams
+    for r in range(logits.shape[0]):
+        t, k, p = float(temperature[r]), int(top_k[r]), float(top_p[r])
+        dist = Sampler(SamplingParams(temperature=t, top_k=k, top_p=p)).distribution(logits[r].float().cpu().numpy(), int(usable[r]))
+        dist.sort()
+        target, run, pick = float(uniform[r]), 0.0, dist[-1][0]
+        for token, prob in dist:
+            if run <= target < run + prob:
+                pick = token
+                break
+            run += prob
+        out[r] = pick
+
+
+NAMES = ["sample", "embed", "rmsnorm", "gemm", "qk_norm_rope_write", "attention", "swiglu", "gather_rows", "add_into", "argmax",
          "interleave_gate_up", "can_fuse_swiglu", "gemm_swiglu"]
 
 

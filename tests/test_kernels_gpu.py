@@ -368,3 +368,33 @@ def test_gemm_with_swiglu_epilogue(ops, T, I, K):
     finally:
         ops.use_tensor_cores = True
     torch.testing.assert_close(out2.double(), want, rtol=3e-2, atol=3e-2)
+
+
+@pytest.mark.parametrize("temperature,top_k,top_p", [(1.0, 0, 1.0), (0.7, 0, 0.9), (1.3, 5, 1.0), (0.5, 40, 0.6), (0.0, 0, 0.9), (2.0, 1, 1.0), (0.8, 300, 0.95)])
+@pytest.mark.parametrize("vocab", [50, 2500])
+def test_device_sampling_follows_the_reference_distribution(ops, temperature, top_k, top_p, vocab):
+    """A grid of u values run through the device sampler: no token outside the host sampler's kept set is ever drawn,
+    and the share of draws each kept token gets equals its probability (the host sampler is the reference's
+    algorithm line by line).  Ties are planted at the head of the ranking."""
+    from marin_b200.sampling import Sampler, SamplingParams
+
+    g = torch.Generator(device=DEV).manual_seed(17)
+    row = torch.randn(vocab, device=DEV, generator=g) * 2.0
+    row[7] = row[3] = row.max() + 0.5                      # two equal best logits
+    row[vocab - 1] = row[11]                               # a tie somewhere in the middle
+    usable = vocab - 1                                     # the last id cannot be drawn
+    N = 4000
+    logits = row.unsqueeze(0).expand(N, vocab).contiguous()
+    u = ((torch.arange(N, device=DEV, dtype=torch.float32) + 0.5) / N)
+    out = torch.empty(N, dtype=torch.int32, device=DEV)
+    ops.sample(logits, torch.full((N,), usable, dtype=torch.int32, device=DEV), torch.full((N,), temperature, device=DEV),
+               torch.full((N,), top_k, dtype=torch.int32, device=DEV), torch.full((N,), top_p, device=DEV), u, out)
+    counts = torch.bincount(out.long().cpu(), minlength=vocab).double() / N
+    want = Sampler(SamplingParams(temperature=temperature, top_k=top_k, top_p=top_p)).distribution(row.cpu().numpy(), usable)
+    probs = torch.zeros(vocab, dtype=torch.double)
+    for token, p in want:
+        probs[token] = p
+    assert set(torch.nonzero(counts).flatten().tolist()) <= {t for t, _ in want}
+    assert float((counts - probs).abs().max()) <= 2.0 / N + 1e-4
+    if temperature == 0.0:
+        assert int(out[0]) == 3 and bool((out == 3).all())       # the lower id of the two equal best
