@@ -212,7 +212,7 @@ __global__ void __launch_bounds__(SP_THREADS) sample_kernel(const float* __restr
         zk = sp_block_sum(zk, fs);
     }
     const float target = uniform[blockIdx.x] * zk;
-    if (threadIdx.x == 0) s_found = -1;
+    if (threadIdx.x == 0) s_found = INT_MAX;
     __syncthreads();
     float run = 0.0f;
     int seen = 0, last_member = -1;
@@ -231,7 +231,7 @@ __global__ void __launch_bounds__(SP_THREADS) sample_kernel(const float* __restr
         if (member) last_member = i;
         run += wtot;
         __syncthreads();
-        if (s_found >= 0) break;
+        if (s_found != INT_MAX) break;
     }
     // rounding may leave target at or past the total: the last member then
     int lm = last_member;
@@ -243,7 +243,7 @@ __global__ void __launch_bounds__(SP_THREADS) sample_kernel(const float* __restr
     if (threadIdx.x == 0) {
         int best = -1;
         for (int w = 0; w < SP_THREADS / 32; ++w) best = max(best, is[w]);
-        out[blockIdx.x] = s_found >= 0 ? s_found : max(best, 0);
+        out[blockIdx.x] = s_found != INT_MAX ? s_found : max(best, 0);
     }
 }
 
