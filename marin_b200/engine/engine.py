@@ -94,6 +94,9 @@ class Engine:
             self.config, self.model = config, random_model(config, seed, self.rt)
         else:
             raise ValueError("give a model folder or a configuration")
+        if self.rt.device.type == "cuda":
+            from ..kernels import build
+            build.build_for(self.model, self.rt.dtype, verbose=True)
         limit = self.config.max_position_embeddings
         self.ctx = min(DEFAULT_CTX, limit) if ctx is None else int(ctx)
         if self.ctx <= 0 or self.ctx > limit:

@@ -139,12 +139,9 @@ LIBRARIES: Dict[str, List[str]] = {
 ATTENTION_LAYOUTS = [(128, 4), (128, 5), (16, 2), (32, 4), (48, 2)]
 
 
-def build_all(verbose: bool = True) -> List[str]:
-    """Compiles every library (in parallel).  Used by the build check and before timing."""
+def build_many(jobs: Dict[str, tuple], verbose: bool = True) -> List[str]:
+    """Compiles ``{name: (sources, defines)}`` in parallel; returns the libraries' paths."""
     results: Dict[str, object] = {}
-    jobs = {n: (src, []) for n, src in LIBRARIES.items()}
-    for d, g in ATTENTION_LAYOUTS:
-        jobs[f"mb_attention_fast_d{d}_g{g}"] = (["attention_fast.cu"], [f"HEAD_DIM={d}", f"GROUP={g}"])
 
     def work(n: str) -> None:
         try:
@@ -161,3 +158,39 @@ def build_all(verbose: bool = True) -> List[str]:
     if errors:
         raise errors[0]
     return [str(results[n]) for n in jobs]
+
+
+def attention_job(d: int, group: int) -> tuple:
+    return (["attention_fast.cu"], [f"HEAD_DIM={d}", f"GROUP={group}"])
+
+
+def build_all(verbose: bool = True) -> List[str]:
+    """Compiles every library and the attention kernels for the layouts in ``ATTENTION_LAYOUTS`` (in parallel).
+    Used by the build check and before timing."""
+    jobs = {n: (src, []) for n, src in LIBRARIES.items()}
+    for d, g in ATTENTION_LAYOUTS:
+        jobs[f"mb_attention_fast_d{d}_g{g}"] = attention_job(d, g)
+    return build_many(jobs, verbose)
+
+
+def build_for(model, dtype, verbose: bool = True) -> List[str]:
+    """Compiles what this model needs and nothing else: the element-wise kernels, the matrix products of its dtype
+    and the attention kernels for its head layouts."""
+    import torch
+
+    jobs = {"mb_elementwise": (LIBRARIES["mb_elementwise"], []), "mb_sampling": (LIBRARIES["mb_sampling"], []),
+            "mb_gemm_simple": (LIBRARIES["mb_gemm_simple"], [])}
+    if dtype == torch.bfloat16:
+        jobs["mb_gemm_tc"] = (LIBRARIES["mb_gemm_tc"], [])
+    from . import ops
+
+    for block in getattr(model, "blocks", []):
+        mixer = block.mixer
+        if not all(hasattr(mixer, a) for a in ("heads", "kv_heads", "head_dim")):
+            continue
+        if ops.fast_attention_supported(dtype, mixer.heads, mixer.kv_heads, mixer.head_dim):
+            jobs[f"mb_attention_fast_d{mixer.head_dim}_g{mixer.heads // mixer.kv_heads}"] = attention_job(
+                mixer.head_dim, mixer.heads // mixer.kv_heads)
+        else:
+            jobs["mb_attention_simple"] = (LIBRARIES["mb_attention_simple"], [])
+    return build_many(jobs, verbose)

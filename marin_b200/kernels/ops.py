@@ -209,8 +209,7 @@ def decode_split(requests: int, kv_heads: int, longest: int):
 
 def _attention_lib(d: int, group: int):
     """The fast attention kernels are compiled for one head size and one group size, at first use."""
-    extra = [x for x in os.environ.get("MARIN_B200_ATTN_DEFINES", "").split(",") if x]
-    return build.load(f"mb_attention_fast_d{d}_g{group}", ["attention_fast.cu"], [f"HEAD_DIM={d}", f"GROUP={group}"] + extra)
+    return build.load(f"mb_attention_fast_d{d}_g{group}", *build.attention_job(d, group))
 
 
 def fast_attention_supported(dtype, H: int, K: int, d: int) -> bool:
