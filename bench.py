@@ -36,6 +36,10 @@ QWEN3_4B = {
     "vocab_size": 151936, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": True,
     "max_position_embeddings": 40960,
 }
+QWEN3_8B = dict(QWEN3_4B, hidden_size=4096, intermediate_size=12288, tie_word_embeddings=False)
+QWEN3_14B = dict(QWEN3_4B, num_hidden_layers=40, hidden_size=5120, num_attention_heads=40, intermediate_size=17408,
+                 tie_word_embeddings=False)
+LAYOUTS = {"4b": QWEN3_4B, "8b": QWEN3_8B, "14b": QWEN3_14B}
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
 PAGE = 16
@@ -249,6 +253,7 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--model", default="4b", choices=sorted(LAYOUTS), help="layer sizes: Qwen3-4B (the default), 8B or 14B layout")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -264,7 +269,7 @@ def main() -> int:
     from marin_b200.kernels import build
 
     build.build_all(verbose=False)
-    raw = dict(QWEN3_4B)
+    raw = dict(LAYOUTS[args.model])
     full_layers = raw["num_hidden_layers"]
     if args.layers:
         raw["num_hidden_layers"] = args.layers
@@ -306,11 +311,11 @@ def main() -> int:
         e2e["value"] = round(e2e["value"], 1)
 
     line = {
-        "metric": "decode tok/s at batch 8 (Qwen3-4B layout, context 4096); prefill tok/s at 2048 tokens; % of roofline",
+        "metric": f"decode tok/s at batch {args.batch} (Qwen3-{args.model.upper()} layout, context 4096); prefill tok/s at 2048 tokens; % of roofline",
         "value": round(main_run["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
         "ms_per_step": round(main_run["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": PUBLISHED, "dtype": "bf16", "data": "synthetic (uniform random token ids, seeded random weights N(0,0.02))",
-        "config": {"model": "Qwen3-4B layout", "layers": cfg.num_hidden_layers, "layers_full": full_layers, "hidden": cfg.hidden_size,
+        "config": {"model": f"Qwen3-{args.model.upper()} layout", "layers": cfg.num_hidden_layers, "layers_full": full_layers, "hidden": cfg.hidden_size,
                    "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
                    "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size, "tied": cfg.tie_word_embeddings,
                    "global_batch": args.batch, "seq_len": CONTEXT, "kv_block": PAGE, "prefill_tokens": PREFILL_TOKENS,

@@ -43,8 +43,9 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
     }
 }
 
-// The same with the row held in registers: 16-byte loads, one pass over memory.  n is a multiple of 4, at most 4096.
-template <typename TO>
+// The same with the row held in registers: 16-byte loads, one pass over memory.  n is a multiple of 4, at most
+// 1024 * R (R float4 per thread).
+template <typename TO, int R>
 __global__ void __launch_bounds__(256) rmsnorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ w, float eps,
                                                           int unit_offset, TO* __restrict__ out, int n) {
     pdl_wait();
@@ -53,10 +54,10 @@ __global__ void __launch_bounds__(256) rmsnorm_vec_kernel(const float* __restric
     const float4* row = reinterpret_cast<const float4*>(x + (size_t)blockIdx.x * n);
     const float4* w4 = reinterpret_cast<const float4*>(w);
     const int n4 = n >> 2;
-    float4 v[4];
+    float4 v[R];
     float ss = 0.0f;
 #pragma unroll
-    for (int r = 0; r < 4; ++r) {
+    for (int r = 0; r < R; ++r) {
         const int i = threadIdx.x + r * 256;
         v[r] = i < n4 ? row[i] : make_float4(0.f, 0.f, 0.f, 0.f);
         ss += v[r].x * v[r].x + v[r].y * v[r].y + v[r].z * v[r].z + v[r].w * v[r].w;
@@ -65,7 +66,7 @@ __global__ void __launch_bounds__(256) rmsnorm_vec_kernel(const float* __restric
     const float scale = 1.0f / sqrtf(ss / (float)n + eps);
     TO* dst = out + (size_t)blockIdx.x * n;
 #pragma unroll
-    for (int r = 0; r < 4; ++r) {
+    for (int r = 0; r < R; ++r) {
         const int i = threadIdx.x + r * 256;
         if (i < n4) {
             float4 g = w4[i];
@@ -88,10 +89,14 @@ MB_API int mb_rmsnorm(const float* x, const float* w, float eps, int unit_offset
                       int rows, int n, cudaStream_t s) {
     if (rows <= 0) return 0;
     if (out_dtype != MB_F32 && out_dtype != MB_BF16) return MB_ERR_BAD_DTYPE;
-    const bool vec = n % 4 == 0 && n <= 4096 && n >= 512 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0 && ((uintptr_t)out & 15) == 0;
+    const bool vec = n % 4 == 0 && n <= 8192 && n >= 512 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0 && ((uintptr_t)out & 15) == 0;
+    if (vec && n <= 4096) {
+        if (out_dtype == MB_F32) return launch_kernel(rmsnorm_vec_kernel<float, 4>, rows, 256, 0, s, 0, x, w, eps, unit_offset, (float*)out, n);
+        return launch_kernel(rmsnorm_vec_kernel<bf16, 4>, rows, 256, 0, s, 0, x, w, eps, unit_offset, (bf16*)out, n);
+    }
     if (vec) {
-        if (out_dtype == MB_F32) return launch_kernel(rmsnorm_vec_kernel<float>, rows, 256, 0, s, 0, x, w, eps, unit_offset, (float*)out, n);
-        return launch_kernel(rmsnorm_vec_kernel<bf16>, rows, 256, 0, s, 0, x, w, eps, unit_offset, (bf16*)out, n);
+        if (out_dtype == MB_F32) return launch_kernel(rmsnorm_vec_kernel<float, 8>, rows, 256, 0, s, 0, x, w, eps, unit_offset, (float*)out, n);
+        return launch_kernel(rmsnorm_vec_kernel<bf16, 8>, rows, 256, 0, s, 0, x, w, eps, unit_offset, (bf16*)out, n);
     }
     const int threads = n >= 1024 ? 256 : 128;
     if (out_dtype == MB_F32) return launch_kernel(rmsnorm_kernel<float>, rows, threads, 0, s, 0, x, w, eps, unit_offset, (float*)out, n);

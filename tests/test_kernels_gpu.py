@@ -40,7 +40,7 @@ def test_embed(ops, dtype, vocab, h, tokens):
 
 
 @pytest.mark.parametrize("out_dtype", DTYPES)
-@pytest.mark.parametrize("rows,n,eps,unit", [(3, 72, 1e-5, False), (17, 2560, 1e-6, False), (300, 4096, 1e-6, True), (9, 512, 1e-5, False), (4, 4092, 1e-6, False), (1, 5120, 1e-6, True), (5, 1, 1e-3, False), (2, 1031, 1e-6, False)])
+@pytest.mark.parametrize("rows,n,eps,unit", [(3, 72, 1e-5, False), (17, 2560, 1e-6, False), (300, 4096, 1e-6, True), (33, 5120, 1e-6, False), (2, 8192, 1e-6, False), (9, 512, 1e-5, False), (4, 4092, 1e-6, False), (1, 5120, 1e-6, True), (5, 1, 1e-3, False), (2, 1031, 1e-6, False)])
 def test_rmsnorm(ops, out_dtype, rows, n, eps, unit):
     g = torch.Generator(device=DEV).manual_seed(2)
     x = torch.randn(rows, n, device=DEV, generator=g) * 3.0
