@@ -39,6 +39,8 @@ class RequestCache:
     slot: int
     length: int = 0
     pages: List[List[int]] = field(default_factory=list)  # per group: logical page → page id or DROPPED
+    dropped: int = 0                                      # how many pages a window has given back so far
+    arrays: Dict[int, tuple] = field(default_factory=dict)
 
 
 @dataclass
@@ -127,7 +129,20 @@ class CacheManager:
         """Per group, how many pages ``reserve(req_id, new_len)`` would take."""
         rc = self.requests[req_id]
         total = -(-new_len // self.page_size)
-        return [max(0, total - len(rc.pages[gi])) for gi in range(len(self.groups))]
+        return [max(0, total - len(pages)) for pages in rc.pages]
+
+    def pages_array(self, rc: RequestCache, group: int):
+        """The request's block table of one group as an int32 array (dropped pages as 0), rebuilt only when
+        the table changed."""
+        import numpy as np
+
+        pages = rc.pages[group]
+        cached = rc.arrays.get(group)
+        if cached is None or cached[0] != len(pages) or cached[1] != rc.dropped:
+            arr = np.maximum(np.asarray(pages, np.int32), 0) if pages else np.zeros(0, np.int32)
+            rc.arrays[group] = (len(pages), rc.dropped, arr)
+            return arr
+        return cached[2]
 
     def can_reserve(self, wanted: Sequence[Tuple[Hashable, int]]) -> bool:
         """Whether all of ``(req_id, new_len)`` could be reserved together."""
@@ -162,6 +177,7 @@ class CacheManager:
                 if table[logical] != DROPPED:
                     g.pool.free([table[logical]])
                     table[logical] = DROPPED
+                    rc.dropped += 1
 
     def release(self, req_id: Hashable) -> None:
         """The request ended (or was preempted): everything it holds goes back."""

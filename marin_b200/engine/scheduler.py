@@ -53,6 +53,20 @@ class Request:
         return self.prompt + self.output
 
     @property
+    def num_tokens(self) -> int:
+        return len(self.prompt) + len(self.output)
+
+    def tokens_from(self, start: int, count: int) -> List[int]:
+        """``tokens[start:start + count]`` without building the whole list."""
+        p = len(self.prompt)
+        end = start + count
+        if end <= p:
+            return self.prompt[start:end]
+        if start >= p:
+            return self.output[start - p:end - p]
+        return self.prompt[start:] + self.output[:end - p]
+
+    @property
     def finished(self) -> bool:
         return self.stop is not None
 
@@ -64,6 +78,7 @@ class Planned:
     request: Request
     tokens: List[int]
     sample: bool                    # the portion ends the known tokens: sample the next one from its last logits
+    missing: List[int] = field(default_factory=list)   # pages per cache group this portion still needs
 
 
 class Scheduler:
@@ -104,10 +119,24 @@ class Scheduler:
 
     # ---- one step's plan --------------------------------------------------------------------------------
     def _pages_fit(self, planned: Sequence[Planned], extra: Optional[Planned] = None) -> bool:
-        wanted = [(p.request.req_id, p.request.computed + len(p.tokens)) for p in planned]
+        """Whether the pages the planned portions (and ``extra``) need are free, in every group."""
+        need = self._need_of(planned)
         if extra is not None:
-            wanted.append((extra.request.req_id, extra.request.computed + len(extra.tokens)))
-        return self.cache.can_reserve(wanted)
+            for g, n in enumerate(self.cache.pages_missing(extra.request.req_id, extra.request.computed + len(extra.tokens))):
+                need[g] += n
+        return all(n <= free for n, free in zip(need, self.cache.free_pages()))
+
+    def _need_of(self, planned: Sequence[Planned]) -> List[int]:
+        need = [0] * len(self.cache.groups)
+        for p in planned:
+            for g, n in enumerate(p.missing):
+                need[g] += n
+        return need
+
+    def _portion(self, request: Request, budget: int) -> Planned:
+        rest = request.num_tokens - request.computed
+        count = min(rest, budget)
+        return Planned(request, request.tokens_from(request.computed, count), sample=rest <= budget)
 
     def _preempt(self, victim: Request) -> None:
         self.cache.release(victim.req_id)
@@ -132,8 +161,7 @@ class Scheduler:
                 continue
             if budget == 0:
                 break
-            rest = request.tokens[request.computed:]
-            portion = Planned(request, rest[:budget], sample=len(rest) <= budget)
+            portion = self._portion(request, budget)
             while not self._pages_fit(plan, portion):
                 victims = [r for r in self.running if r is not request and all(p.request is not r for p in plan)]
                 if not victims:
@@ -143,13 +171,13 @@ class Scheduler:
                 if not plan and len(self.running) == 1:
                     self._finish(request, StopReason.OUT_OF_PAGES)
                 continue
+            portion.missing = self.cache.pages_missing(request.req_id, request.computed + len(portion.tokens))
             plan.append(portion)
             budget -= len(portion.tokens)
         # 2. admit waiting requests while there is room
         while self.waiting and budget > 0 and len(self.running) < self.max_batch:
             request = self.waiting[0]
-            rest = request.tokens
-            portion = Planned(request, rest[:budget], sample=len(rest) <= budget)
+            portion = self._portion(request, budget)
             self.cache.admit(request.req_id)
             if not self._pages_fit(plan, portion):
                 self.cache.release(request.req_id)
@@ -164,6 +192,7 @@ class Scheduler:
             self._clock += 1
             request.admitted_at = self._clock
             self.running.append(request)
+            portion.missing = self.cache.pages_missing(request.req_id, request.computed + len(portion.tokens))
             plan.append(portion)
             budget -= len(portion.tokens)
         return plan

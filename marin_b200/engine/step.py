@@ -135,9 +135,12 @@ class Runner:
             lens[row] = rc.length + n
             slots[row] = rc.slot
             for g in range(G):
-                ids = np.asarray(rc.pages[g], np.int32)
-                tables[g, row, :len(ids)] = np.maximum(ids, 0)
-                slot_maps[g, at:at + n] = ids[p // page] * page + (p % page)
+                ids = cache.pages_array(rc, g)
+                tables[g, row, :len(ids)] = ids
+                if n == 1:
+                    slot_maps[g, at] = ids[rc.length // page] * page + rc.length % page
+                else:
+                    slot_maps[g, at:at + n] = ids[p // page] * page + (p % page)
             spans.append(Span(row, e.req_id, at, n, rc.length, rc.slot))
             at += n
         if pad_to:
