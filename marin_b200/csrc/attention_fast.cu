@@ -84,7 +84,9 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 #define LDP (D + 8)                   // padded row of a tile in shared memory (elements): ldmatrix without bank conflicts
+#ifndef DEC_STAGES
 #define DEC_STAGES 3                  // per-warp ring of 16-key stages
+#endif
 #define DEC_STAGE_KEYS 16
 #define DEC_Q_BYTES (16 * LDP * 2)
 #define DEC_STAGE_BYTES (2 * DEC_STAGE_KEYS * LDP * 2)          // keys then values
@@ -126,21 +128,35 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_split_kernel(
     const int page_mask = (1 << page_shift) - 1;
     const size_t head_rows = (size_t)kh << page_shift;             // rows before this kv head inside a page
     const size_t page_rows = (size_t)K << page_shift;              // rows of a whole page
+    // Where this lane's pieces of a stage lie: piece p of row r (rows 0..15 keys, 16..31 values) for idx = lane + 32 j.
     auto issue = [&](int i) {
         if (i < n_it) {
             bf16* dst = reinterpret_cast<bf16*>(ring + (size_t)(i % DEC_STAGES) * DEC_STAGE_BYTES);
             const int key_base = first + i * DEC_STAGE_KEYS;
+            if (page_shift >= 4 && key_base >= lo && key_base + DEC_STAGE_KEYS <= len) {
+                // the whole stage is valid and lies in one page: one block-table lookup, then constant strides
+                const size_t row0 = (size_t)table[key_base >> page_shift] * page_rows + head_rows + (size_t)(key_base & page_mask);
+                const bf16* ksrc = k_cache + row0 * D;
+                const bf16* vsrc = v_cache + row0 * D;
 #pragma unroll
-            for (int idx = lane; idx < 2 * DEC_STAGE_KEYS * PIECES; idx += 32) {
-                const int row = idx / PIECES, piece = idx % PIECES;           // rows 0..15 keys, 16..31 values
-                const int key = key_base + (row & (DEC_STAGE_KEYS - 1));
-                bf16* d = dst + row * LDP + piece * 8;
-                if (key < len && key >= lo) {
-                    const bf16* cache = row < DEC_STAGE_KEYS ? k_cache : v_cache;
-                    const size_t at = (size_t)table[key >> page_shift] * page_rows + head_rows + (size_t)(key & page_mask);
-                    cp_async16(d, cache + at * D + piece * 8);
-                } else {
-                    *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
+                for (int idx = lane; idx < DEC_STAGE_KEYS * PIECES; idx += 32) {
+                    const int row = idx / PIECES, piece = idx % PIECES;
+                    cp_async16(dst + row * LDP + piece * 8, ksrc + row * D + piece * 8);
+                    cp_async16(dst + (DEC_STAGE_KEYS + row) * LDP + piece * 8, vsrc + row * D + piece * 8);
+                }
+            } else {
+#pragma unroll
+                for (int idx = lane; idx < 2 * DEC_STAGE_KEYS * PIECES; idx += 32) {
+                    const int row = idx / PIECES, piece = idx % PIECES;           // rows 0..15 keys, 16..31 values
+                    const int key = key_base + (row & (DEC_STAGE_KEYS - 1));
+                    bf16* d = dst + row * LDP + piece * 8;
+                    if (key < len && key >= lo) {
+                        const bf16* cache = row < DEC_STAGE_KEYS ? k_cache : v_cache;
+                        const size_t at = (size_t)table[key >> page_shift] * page_rows + head_rows + (size_t)(key & page_mask);
+                        cp_async16(d, cache + at * D + piece * 8);
+                    } else {
+                        *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
+                    }
                 }
             }
         }
@@ -166,9 +182,9 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_split_kernel(
 
     const float sl2 = scale * 1.4426950408889634f;
     float m_run = -INFINITY, l_run = 0.0f;              // of this thread's row (= query head lane / 4)
-    float o[D / 8][2];
+    float o[D / 8][4];                                 // [2] and [3] are rows 8..15 of the tile: they stay zero
 #pragma unroll
-    for (int i = 0; i < D / 8; ++i) { o[i][0] = o[i][1] = 0.0f; }
+    for (int i = 0; i < D / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
 
     for (int it = 0; it < n_it; ++it) {
         cp_async_wait<DEC_STAGES - 1>();
@@ -177,11 +193,11 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_split_kernel(
         const bf16* sV = sK + DEC_STAGE_KEYS * LDP;
         float sc[2][4];
         sc[0][0] = sc[0][1] = sc[0][2] = sc[0][3] = sc[1][0] = sc[1][1] = sc[1][2] = sc[1][3] = 0.0f;
+        const uint32_t k_addr = (uint32_t)__cvta_generic_to_shared(sK + ((lane & 7) + (lane >> 4) * 8) * LDP + ((lane >> 3) & 1) * 8);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
             uint32_t b0, b1, b2, b3;
-            const int key = (lane & 7) + (lane >> 4) * 8;
-            ldsm_x4((uint32_t)__cvta_generic_to_shared(sK + key * LDP + kk * 16 + ((lane >> 3) & 1) * 8), b0, b1, b2, b3);
+            ldsm_x4(k_addr + kk * 32, b0, b1, b2, b3);
             mma_bf16_16816(sc[0], qa[kk], b0, b1);
             mma_bf16_16816(sc[1], qa[kk], b2, b3);
         }
@@ -213,17 +229,14 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_split_kernel(
         pa[1] = 0u;
         pa[2] = pack_bf16(sc[1][0], sc[1][1]);
         pa[3] = 0u;
+        const uint32_t v_addr = (uint32_t)__cvta_generic_to_shared(sV + ((lane & 7) + ((lane >> 3) & 1) * 8) * LDP + (lane >> 4) * 8);
 #pragma unroll
         for (int dt = 0; dt < D / 8; dt += 2) {
             uint32_t b0, b1, b2, b3;
-            const int key = (lane & 7) + ((lane >> 3) & 1) * 8;
-            ldsm_x4_trans((uint32_t)__cvta_generic_to_shared(sV + key * LDP + dt * 8 + (lane >> 4) * 8), b0, b1, b2, b3);
-            float c0[4] = {o[dt][0] * corr, o[dt][1] * corr, 0.0f, 0.0f};
-            float c1[4] = {o[dt + 1][0] * corr, o[dt + 1][1] * corr, 0.0f, 0.0f};
-            mma_bf16_16816(c0, pa, b0, b1);
-            mma_bf16_16816(c1, pa, b2, b3);
-            o[dt][0] = c0[0]; o[dt][1] = c0[1];
-            o[dt + 1][0] = c1[0]; o[dt + 1][1] = c1[1];
+            ldsm_x4_trans(v_addr + dt * 16, b0, b1, b2, b3);
+            o[dt][0] *= corr; o[dt][1] *= corr; o[dt + 1][0] *= corr; o[dt + 1][1] *= corr;
+            mma_bf16_16816(o[dt], pa, b0, b1);
+            mma_bf16_16816(o[dt + 1], pa, b2, b3);
         }
         __syncwarp();                                   // the stage is free: refill it
         issue(it + DEC_STAGES);
@@ -302,21 +315,24 @@ __global__ void __launch_bounds__(D) attn_decode_merge_kernel(const float* __res
 #endif
 #define PF_SMEM ((1 + 2 * PF_BUFFERS) * PF_BM * PF_LD * 2)
 
-// Asks for the rows of one 64-key block of K or V (cp.async); keys past `k_last` are zero (their pages may not exist).
-__device__ __forceinline__ void load_kv_tile(bf16* dst, const bf16* __restrict__ cache, const int* __restrict__ table, int K, int kh,
-                                             int page_shift, int key0, int k_last) {
+// Asks for the rows of one 64-key block of K and of V (cp.async); keys past `k_last` are zero (their pages may not
+// exist).  One address computation per row serves both caches.
+__device__ __forceinline__ void load_kv_tile(bf16* dst_k, bf16* dst_v, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
+                                             const int* __restrict__ table, int K, int kh, int page_shift, int key0, int k_last) {
     constexpr int CHUNKS = D / 8;
     const int page_mask = (1 << page_shift) - 1;
 #pragma unroll
     for (int idx = threadIdx.x; idx < PF_BN * CHUNKS; idx += 128) {
         const int row = idx / CHUNKS, c = idx % CHUNKS;
         const int key = key0 + row;
-        bf16* d = dst + row * PF_LD + c * 8;
+        const int off = row * PF_LD + c * 8;
         if (key <= k_last) {
-            const size_t at = (((size_t)table[key >> page_shift] * K + kh) << page_shift) + (size_t)(key & page_mask);
-            cp_async16(d, cache + at * D + c * 8);
+            const size_t at = ((((size_t)table[key >> page_shift] * K + kh) << page_shift) + (size_t)(key & page_mask)) * D + c * 8;
+            cp_async16(dst_k + off, k_cache + at);
+            cp_async16(dst_v + off, v_cache + at);
         } else {
-            *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
+            *reinterpret_cast<uint4*>(dst_k + off) = make_uint4(0, 0, 0, 0);
+            *reinterpret_cast<uint4*>(dst_v + off) = make_uint4(0, 0, 0, 0);
         }
     }
 }
@@ -351,8 +367,7 @@ __global__ void __launch_bounds__(128, PF_MIN_CTAS) attn_prefill_kernel(
             if (row < rows) cp_async16(d, q + ((size_t)(tok0 + qt * PF_BM + row) * H + h) * D + c * 8);
             else *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
         }
-        load_kv_tile(sKV, k_cache, table, K, kh, page_shift, kb_first * PF_BN, q_last);
-        load_kv_tile(sKV + PF_BN * PF_LD, v_cache, table, K, kh, page_shift, kb_first * PF_BN, q_last);
+        load_kv_tile(sKV, sKV + PF_BN * PF_LD, k_cache, v_cache, table, K, kh, page_shift, kb_first * PF_BN, q_last);
         cp_async_commit();
     }
     cp_async_wait<0>();
@@ -376,8 +391,7 @@ __global__ void __launch_bounds__(128, PF_MIN_CTAS) attn_prefill_kernel(
         bf16* sV = sK + PF_BN * PF_LD;
         if (kb < kb_last) {                                    // ask for the next block while this one is used
             bf16* nK = sKV + (size_t)(buf ^ 1) * 2 * PF_BN * PF_LD;
-            load_kv_tile(nK, k_cache, table, K, kh, page_shift, key0 + PF_BN, q_last);
-            load_kv_tile(nK + PF_BN * PF_LD, v_cache, table, K, kh, page_shift, key0 + PF_BN, q_last);
+            load_kv_tile(nK, nK + PF_BN * PF_LD, k_cache, v_cache, table, K, kh, page_shift, key0 + PF_BN, q_last);
         }
         cp_async_commit();
         if (kb > kb_first) {
@@ -388,8 +402,7 @@ __global__ void __launch_bounds__(128, PF_MIN_CTAS) attn_prefill_kernel(
         bf16* sK = sKV;
         bf16* sV = sK + PF_BN * PF_LD;
         if (kb > kb_first) {                                   // the barrier at the end of the last block freed the buffer
-            load_kv_tile(sK, k_cache, table, K, kh, page_shift, key0, q_last);
-            load_kv_tile(sV, v_cache, table, K, kh, page_shift, key0, q_last);
+            load_kv_tile(sK, sV, k_cache, v_cache, table, K, kh, page_shift, key0, q_last);
             cp_async_commit();
             cp_async_wait<0>();
             __syncthreads();

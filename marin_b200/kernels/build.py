@@ -161,7 +161,10 @@ def build_many(jobs: Dict[str, tuple], verbose: bool = True) -> List[str]:
 
 
 def attention_job(d: int, group: int) -> tuple:
-    return (["attention_fast.cu"], [f"HEAD_DIM={d}", f"GROUP={group}"])
+    """Sources and defines of the attention kernels for one head layout.  MARIN_B200_ATTENTION_DEFINES (comma
+    separated, e.g. ``DEC_STAGES=2,PF_BUFFERS=2``) overrides the kernels' tuning constants for experiments."""
+    extra = [x for x in os.environ.get("MARIN_B200_ATTENTION_DEFINES", "").split(",") if x]
+    return (["attention_fast.cu"], [f"HEAD_DIM={d}", f"GROUP={group}"] + extra)
 
 
 def build_all(verbose: bool = True) -> List[str]:
