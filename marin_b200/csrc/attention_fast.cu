@@ -26,6 +26,14 @@ static_assert(HEAD_DIM % 16 == 0 && HEAD_DIM >= 16 && HEAD_DIM <= 128, "head siz
 static_assert(GROUP >= 1 && GROUP <= 8, "1 to 8 query heads per kv head");
 
 #define D HEAD_DIM
+
+// 2^x for x <= 0 (softmax numerators): one MUFU instruction, a couple of ulps off, flushes denormals to zero;
+// exp2f proper costs several more instructions per element and the probabilities are rounded to bf16 anyway.
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 #define DEC_WARPS 4
 #define DPL (D / 8)                   // dims per lane: 8 lanes share one key
 #define VW (DPL % 8 == 0 ? 8 : (DPL % 4 == 0 ? 4 : 2))   // elements per vector load
@@ -201,26 +209,27 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_split_kernel(
             mma_bf16_16816(sc[0], qa[kk], b0, b1);
             mma_bf16_16816(sc[1], qa[kk], b2, b3);
         }
-        const int key0 = first + it * DEC_STAGE_KEYS + 2 * (lane & 3);
-        float mx = -INFINITY;
+        const int key_base = first + it * DEC_STAGE_KEYS;
+        if (key_base < lo || key_base + DEC_STAGE_KEYS > len) {            // only the ends of the range need masking
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            const int key = key0 + j * 8;
-            sc[j][0] = (key < len && key >= lo) ? sc[j][0] * sl2 : -INFINITY;
-            sc[j][1] = (key + 1 < len && key + 1 >= lo) ? sc[j][1] * sl2 : -INFINITY;
-            mx = fmaxf(mx, fmaxf(sc[j][0], sc[j][1]));
+            for (int j = 0; j < 2; ++j) {
+                const int key = key_base + 2 * (lane & 3) + j * 8;
+                if (!(key < len && key >= lo)) sc[j][0] = -INFINITY;
+                if (!(key + 1 < len && key + 1 >= lo)) sc[j][1] = -INFINITY;
+            }
         }
+        float mx = fmaxf(fmaxf(sc[0][0], sc[0][1]), fmaxf(sc[1][0], sc[1][1]));
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-        const float m_new = fmaxf(m_run, mx);
+        const float m_new = fmaxf(m_run, mx * sl2);                        // log2 units; the scale is positive
         const float base = m_new == -INFINITY ? 0.0f : m_new;
-        const float corr = exp2f(m_run - base);
+        const float corr = fast_exp2(m_run - base);
         m_run = m_new;
         float sum = 0.0f;
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
-            sc[j][0] = exp2f(sc[j][0] - base);
-            sc[j][1] = exp2f(sc[j][1] - base);
+            sc[j][0] = fast_exp2(fmaf(sc[j][0], sl2, -base));
+            sc[j][1] = fast_exp2(fmaf(sc[j][1], sl2, -base));
             sum += sc[j][0] + sc[j][1];
         }
         l_run = l_run * corr + sum;
@@ -429,38 +438,35 @@ __global__ void __launch_bounds__(128, PF_MIN_CTAS) attn_prefill_kernel(
         float mx0 = -INFINITY, mx1 = -INFINITY;
         // a block needs masking only if it reaches past the tile's first query or starts before the last query's window
         const bool interior = key0 + PF_BN - 1 <= q_first && (window <= 0 || key0 >= q_last - window + 1);
-        if (interior) {
-#pragma unroll
-            for (int j = 0; j < PF_BN / 8; ++j) {
-                s[j][0] *= sl2; s[j][1] *= sl2; s[j][2] *= sl2; s[j][3] *= sl2;
-                mx0 = fmaxf(mx0, fmaxf(s[j][0], s[j][1]));
-                mx1 = fmaxf(mx1, fmaxf(s[j][2], s[j][3]));
-            }
-        } else {
+        if (!interior) {
 #pragma unroll
             for (int j = 0; j < PF_BN / 8; ++j) {
                 const int key = key0 + j * 8 + 2 * (lane & 3);
-                s[j][0] = (key <= qp0 && key >= lo0) ? s[j][0] * sl2 : -INFINITY;
-                s[j][1] = (key + 1 <= qp0 && key + 1 >= lo0) ? s[j][1] * sl2 : -INFINITY;
-                s[j][2] = (key <= qp1 && key >= lo1) ? s[j][2] * sl2 : -INFINITY;
-                s[j][3] = (key + 1 <= qp1 && key + 1 >= lo1) ? s[j][3] * sl2 : -INFINITY;
-                mx0 = fmaxf(mx0, fmaxf(s[j][0], s[j][1]));
-                mx1 = fmaxf(mx1, fmaxf(s[j][2], s[j][3]));
+                if (!(key <= qp0 && key >= lo0)) s[j][0] = -INFINITY;
+                if (!(key + 1 <= qp0 && key + 1 >= lo0)) s[j][1] = -INFINITY;
+                if (!(key <= qp1 && key >= lo1)) s[j][2] = -INFINITY;
+                if (!(key + 1 <= qp1 && key + 1 >= lo1)) s[j][3] = -INFINITY;
             }
+        }
+#pragma unroll
+        for (int j = 0; j < PF_BN / 8; ++j) {
+            mx0 = fmaxf(mx0, fmaxf(s[j][0], s[j][1]));
+            mx1 = fmaxf(mx1, fmaxf(s[j][2], s[j][3]));
         }
         mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
         mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-        const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
+        // running maxima are kept in log2 units (raw score * scale * log2 e); the scale is positive
+        const float mn0 = fmaxf(m_run[0], mx0 * sl2), mn1 = fmaxf(m_run[1], mx1 * sl2);
         const float base0 = mn0 == -INFINITY ? 0.0f : mn0, base1 = mn1 == -INFINITY ? 0.0f : mn1;
-        const float corr0 = exp2f(m_run[0] - base0), corr1 = exp2f(m_run[1] - base1);
+        const float corr0 = fast_exp2(m_run[0] - base0), corr1 = fast_exp2(m_run[1] - base1);
         m_run[0] = mn0; m_run[1] = mn1;
         float sum0 = 0.0f, sum1 = 0.0f;
 #pragma unroll
         for (int j = 0; j < PF_BN / 8; ++j) {
-            s[j][0] = exp2f(s[j][0] - base0); s[j][1] = exp2f(s[j][1] - base0);
-            s[j][2] = exp2f(s[j][2] - base1); s[j][3] = exp2f(s[j][3] - base1);
+            s[j][0] = fast_exp2(fmaf(s[j][0], sl2, -base0)); s[j][1] = fast_exp2(fmaf(s[j][1], sl2, -base0));
+            s[j][2] = fast_exp2(fmaf(s[j][2], sl2, -base1)); s[j][3] = fast_exp2(fmaf(s[j][3], sl2, -base1));
             sum0 += s[j][0] + s[j][1];
             sum1 += s[j][2] + s[j][3];
         }
