@@ -4,7 +4,7 @@
 //  * decode: one new token per request.  A CTA takes one kv head of one request and one chunk of 128 keys
 //    (fixed by absolute position, so the arithmetic does not depend on the batch or on the number of SMs);
 //    all GROUP query heads that share the kv head are served from one pass over K and one over V; the
-//    partial (max, sum, accumulator) of every chunk goes to scratch and a merge kernel combines them.
+//    partial (max, sum, accumulator) of every chunk goes to scratch and the CTA that finishes last combines them.
 //    The reference splits decode attention the same way but sizes chunks by SM count
 //    (crates/cuda/src/attention.rs:23-30, attention.cu:224-351,481-494).
 //  * prefill: a CTA takes 64 consecutive query tokens of one request and one query head, walks the keys in
@@ -110,11 +110,13 @@ static_assert(GROUP * D * 4 <= DEC_WARP_BYTES, "a warp's accumulators are writte
 __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_split_kernel(
     const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
     const int* __restrict__ block_table, int max_pages, const int* __restrict__ seq_lens, int K, int page_shift,
-    float scale, int window, float* __restrict__ part_acc, float* __restrict__ part_ml, int max_chunks, int split_keys) {
+    float scale, int window, float* __restrict__ part_acc, float* __restrict__ part_ml, int max_chunks, int split_keys,
+    int* __restrict__ counters, bf16* __restrict__ out) {
     pdl_wait();
     pdl_launch_dependents();
     extern __shared__ __align__(16) uint8_t dec_smem[];
     __shared__ float s_m[DEC_WARPS][8], s_l[DEC_WARPS][8];
+    __shared__ int s_last;
     const int chunk = blockIdx.x, kh = blockIdx.y, r = blockIdx.z;
     const int H = K * GROUP;
     const int len = seq_lens[r];
@@ -284,32 +286,69 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_split_kernel(
         part_acc[at * D + dd] = a;
         if (dd == 0) { part_ml[at * 2] = mm; part_ml[at * 2 + 1] = ll; }
     }
-}
-
-// Combines the chunks of one (request, head): out = sum_c acc_c 2^(m_c - M) / sum_c l_c 2^(m_c - M)
-// (the chunks' maxima are in log2 units).
-__global__ void __launch_bounds__(D) attn_decode_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
-                                                           const int* __restrict__ seq_lens, int H, int window, int max_chunks,
-                                                           int split_keys, bf16* __restrict__ out) {
-    pdl_wait();
-    pdl_launch_dependents();
-    const int h = blockIdx.x, r = blockIdx.y, dd = threadIdx.x;
-    const int len = seq_lens[r];
-    if (len <= 0) return;
-    const int pos = len - 1;
-    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    // The CTA that finishes last among the chunks of this (request, kv head) combines them:
+    // out = sum_c acc_c 2^(m_c - M) / sum_c l_c 2^(m_c - M), chunks in increasing order.  The counter goes back to zero.
     const int c_first = lo / split_keys, c_last = pos / split_keys;
-    const size_t base = ((size_t)r * H + h) * max_chunks;
-    float m = -INFINITY;
-    for (int c = c_first; c <= c_last; ++c) m = fmaxf(m, part_ml[(base + c) * 2]);
-    float a = 0.0f, l = 0.0f;
-    for (int c = c_first; c <= c_last; ++c) {
-        const float mc = part_ml[(base + c) * 2];
-        const float f = mc == -INFINITY ? 0.0f : exp2f(mc - m);
-        a = fmaf(part_acc[(base + c) * D + dd], f, a);
-        l = fmaf(part_ml[(base + c) * 2 + 1], f, l);
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int arrived = atomicAdd(&counters[r * K + kh], 1);
+        s_last = arrived == c_last - c_first;
+        if (s_last) counters[r * K + kh] = 0;
     }
-    out[((size_t)r * H + h) * D + dd] = __float2bfloat16_rn(a / l);
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    // weights of the chunks first (one warp per head, lanes over chunks), then every thread sums its outputs
+    const int n_c = c_last - c_first + 1;
+    float* wgt = reinterpret_cast<float*>(dec_smem);               // [GROUP][n_c]; the rings are free now
+    float* s_total = reinterpret_cast<float*>(s_m);                // [GROUP] sums of l_c * weight
+    const bool fits = (size_t)GROUP * n_c * sizeof(float) <= (size_t)DEC_SMEM;
+    for (int g = warp; g < GROUP && fits; g += DEC_WARPS) {
+        const size_t base = ((size_t)r * H + kh * GROUP + g) * max_chunks + c_first;
+        float mm = -INFINITY;
+        for (int c = lane; c < n_c; c += 32) mm = fmaxf(mm, __ldcg(&part_ml[(base + c) * 2]));
+        mm = warp_max(mm);
+        float ll = 0.0f;
+        for (int c = lane; c < n_c; c += 32) {
+            const float mc = __ldcg(&part_ml[(base + c) * 2]);
+            const float f = mc == -INFINITY ? 0.0f : exp2f(mc - mm);
+            wgt[g * n_c + c] = f;
+            ll = fmaf(__ldcg(&part_ml[(base + c) * 2 + 1]), f, ll);
+        }
+        ll = warp_sum(ll);
+        if (lane == 0) s_total[g] = ll;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < GROUP * D; idx += DEC_WARPS * 32) {
+        const int g = idx / D, dd = idx % D;
+        const size_t base = ((size_t)r * H + kh * GROUP + g) * max_chunks + c_first;
+        float a = 0.0f, ll;
+        if (fits) {
+            float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+            int c = 0;
+            for (; c + 4 <= n_c; c += 4) {
+                a0 = fmaf(__ldcg(&part_acc[(base + c) * D + dd]), wgt[g * n_c + c], a0);
+                a1 = fmaf(__ldcg(&part_acc[(base + c + 1) * D + dd]), wgt[g * n_c + c + 1], a1);
+                a2 = fmaf(__ldcg(&part_acc[(base + c + 2) * D + dd]), wgt[g * n_c + c + 2], a2);
+                a3 = fmaf(__ldcg(&part_acc[(base + c + 3) * D + dd]), wgt[g * n_c + c + 3], a3);
+            }
+            for (; c < n_c; ++c) a0 = fmaf(__ldcg(&part_acc[(base + c) * D + dd]), wgt[g * n_c + c], a0);
+            a = (a0 + a1) + (a2 + a3);
+            ll = s_total[g];
+        } else {                                                   // more chunks than shared memory holds weights for
+            float mm = -INFINITY;
+            for (int c = 0; c < n_c; ++c) mm = fmaxf(mm, __ldcg(&part_ml[(base + c) * 2]));
+            ll = 0.0f;
+            for (int c = 0; c < n_c; ++c) {
+                const float mc = __ldcg(&part_ml[(base + c) * 2]);
+                const float f = mc == -INFINITY ? 0.0f : exp2f(mc - mm);
+                a = fmaf(__ldcg(&part_acc[(base + c) * D + dd]), f, a);
+                ll = fmaf(__ldcg(&part_ml[(base + c) * 2 + 1]), f, ll);
+            }
+        }
+        out[((size_t)r * H + kh * GROUP + g) * D + dd] = __float2bfloat16_rn(a / ll);
+    }
 }
 
 // ---- prefill ------------------------------------------------------------------------------------------------------
@@ -526,10 +565,10 @@ MB_API int mb_attn_head_dim() { return D; }
 MB_API int mb_attn_group() { return GROUP; }
 // Decode: q/out rows 0..requests-1 are the single new tokens of requests 0..requests-1.  A CTA takes split_keys
 // keys (a multiple of 64); part_acc holds requests*H*max_chunks*HEAD_DIM floats and part_ml requests*H*max_chunks*2,
-// with max_chunks >= ceil(longest/split_keys).
+// with max_chunks >= ceil(longest/split_keys); counters holds requests*K ints that are zero between launches.
 MB_API int mb_attn_decode(const void* q, const void* k_cache, const void* v_cache, void* out, const int* block_table,
                           int max_pages, const int* seq_lens, int requests, int K, int page_size, float scale, int window,
-                          float* part_acc, float* part_ml, int max_chunks, int split_keys, cudaStream_t s) {
+                          float* part_acc, float* part_ml, int* counters, int max_chunks, int split_keys, cudaStream_t s) {
     if (requests <= 0) return 0;
     if (max_chunks <= 0 || K <= 0 || split_keys < 64 || split_keys % 64 != 0) return MB_ERR_BAD_SIZE;
     const int page_shift = page_shift_of(page_size);
@@ -541,12 +580,9 @@ MB_API int mb_attn_decode(const void* q, const void* k_cache, const void* v_cach
         configured = true;
     }
     dim3 grid(max_chunks, K, requests);
-    int rc = launch_kernel(attn_decode_split_kernel, grid, DEC_WARPS * 32, DEC_SMEM, s, 0, (const bf16*)q, (const bf16*)k_cache,
-                           (const bf16*)v_cache, block_table, max_pages, seq_lens, K, page_shift, scale, window, part_acc, part_ml,
-                           max_chunks, split_keys);
-    if (rc) return rc;
-    return launch_kernel(attn_decode_merge_kernel, dim3(K * GROUP, requests), D, 0, s, 0, (const float*)part_acc, (const float*)part_ml,
-                         seq_lens, K * GROUP, window, max_chunks, split_keys, (bf16*)out);
+    return launch_kernel(attn_decode_split_kernel, grid, DEC_WARPS * 32, DEC_SMEM, s, 0, (const bf16*)q, (const bf16*)k_cache,
+                         (const bf16*)v_cache, block_table, max_pages, seq_lens, K, page_shift, scale, window, part_acc, part_ml,
+                         max_chunks, split_keys, counters, (bf16*)out);
 }
 
 // Prefill: requests first_req .. first_req+requests-1 of the step, each with its tokens cu_tokens[r]..cu_tokens[r+1].

@@ -211,8 +211,7 @@ class Runner:
         split, chunks = ops.decode_split(bucket, kv_heads, self.max_seq_len)
         g = {"static": (host, dev, torch.cuda.Event()), "workspace": Workspace(self.rt.device), "graph": None, "logits": None,
              "attn_split": (split, chunks),
-             "attn_scratch": (torch.empty(bucket * heads * chunks * hd, device=self.rt.device, dtype=torch.float32),
-                              torch.empty(bucket * heads * chunks * 2, device=self.rt.device, dtype=torch.float32))}
+             "attn_scratch": ops.decode_scratch(self.rt.device, bucket, heads, kv_heads, chunks, hd)}
         self.graphs[bucket] = g
 
         def run():

@@ -200,10 +200,11 @@ DECODE_SPLITS = (4096, 2048, 1024, 512, 256, 128, 64)      # keys per CTA the sp
 
 def decode_split(requests: int, kv_heads: int, longest: int):
     """Keys per CTA and chunks per sequence for decode attention over sequences of up to ``longest`` keys: the
-    largest split that still gives about one CTA per SM (long CTAs amortise their start-up; measured on B200)."""
+    largest split that still gives 128 CTAs (long CTAs amortise their start-up and the merge; measured on B200 at
+    batch 1, 8 and 64 and contexts 1024 and 4096)."""
     for split in DECODE_SPLITS:
         chunks = -(-longest // split)
-        if requests * kv_heads * chunks >= SM_COUNT or split == DECODE_SPLITS[-1]:
+        if requests * kv_heads * chunks >= 128 or split == DECODE_SPLITS[-1]:
             return split, chunks
 
 
@@ -216,13 +217,22 @@ def fast_attention_supported(dtype, H: int, K: int, d: int) -> bool:
     return dtype == torch.bfloat16 and d % 16 == 0 and 16 <= d <= 128 and H % K == 0 and 1 <= H // K <= 8
 
 
-def _decode_scratch(device, requests: int, H: int, chunks: int, d: int):
+def decode_scratch(device, requests: int, H: int, K: int, chunks: int, d: int):
+    """Scratch of the split-KV decode kernel: partial accumulators, partial (max, sum), and one counter per
+    (request, kv head) that is zero between launches."""
+    need = requests * H * chunks
+    return (torch.empty(need * d, device=device, dtype=torch.float32), torch.empty(need * 2, device=device, dtype=torch.float32),
+            torch.zeros(requests * K, device=device, dtype=torch.int32))
+
+
+def _decode_scratch(device, requests: int, H: int, K: int, chunks: int, d: int):
     need = requests * H * chunks
     key = (device.type, device.index)
     held = _attn_scratch.get(key)
-    if held is None or held[0].numel() < need * d or held[1].numel() < need * 2:
-        grow = max(need, 2 * (held[1].numel() // 2) if held else 0)
-        held = (torch.empty(grow * d, device=device, dtype=torch.float32), torch.empty(grow * 2, device=device, dtype=torch.float32))
+    if held is None or held[0].numel() < need * d or held[1].numel() < need * 2 or held[2].numel() < requests * K:
+        grow_r = max(requests, held[2].numel() // K if held else 0)
+        grow_c = max(chunks, (held[1].numel() // 2) // max(1, grow_r * H) if held else 0)
+        held = decode_scratch(device, grow_r, H, K, grow_c, d)
         _attn_scratch[key] = held
     return held
 
@@ -242,12 +252,11 @@ def attention(q, k_cache, v_cache, out, ctx, block_table, H, K, d, scale, window
         nd = ctx.num_decode
         if nd > 0:
             split, chunks = getattr(ctx, "attn_split", None) or decode_split(nd, K, ctx.max_seq_len)
-            part_acc, part_ml = getattr(ctx, "attn_scratch", None) or _decode_scratch(q.device, nd, H, chunks, d)
+            part_acc, part_ml, counters = getattr(ctx, "attn_scratch", None) or _decode_scratch(q.device, nd, H, K, chunks, d)
             _check(lib.mb_attn_decode(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), _c_int(max_pages),
                                       _ptr(ctx.seq_lens), _c_int(nd), _c_int(K), _c_int(page_size), _c_float(scale),
-                                      _c_int(window), _ptr(part_acc), _ptr(part_ml), _c_int(chunks), _c_int(split), _stream()),
-                   "attention (decode)")
-            launches_extra(1)
+                                      _c_int(window), _ptr(part_acc), _ptr(part_ml), _ptr(counters), _c_int(chunks), _c_int(split),
+                                      _stream()), "attention (decode)")
         if ctx.num_requests > nd:
             _check(lib.mb_attn_prefill(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), _c_int(max_pages),
                                        _ptr(ctx.cu_tokens), _ptr(ctx.seq_lens), _c_int(nd), _c_int(ctx.num_requests - nd),
