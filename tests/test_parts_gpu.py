@@ -262,3 +262,165 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
     for rid in tokens:
         torch.testing.assert_close(got[rid].cpu(), want[rid], rtol=1e-4, atol=1e-4)
     cache.check()
+
+
+def test_block_embedding_and_head_parts_alone():
+    """A whole pre-norm block, the embedding and the head, each built from the registries with its own parameters."""
+    from marin_b200.engine import StepEntry
+    from marin_b200.parts import LayerSpec, PartSpec, lookup
+
+    rt = runtime()
+    h, H, K, d, I, V = 72, 6, 3, 48, 136, 333
+    spec = LayerSpec(block="prenorm", norm=PartSpec("rmsnorm", {"dim": h, "eps": 3e-6}),
+                     mixer=PartSpec("gqa_attention", {"hidden": h, "heads": H, "kv_heads": K, "head_dim": d, "norm_eps": 3e-6,
+                                                      "position": PartSpec("rope", {"head_dim": d, "theta": 5e5})}),
+                     feedforward=PartSpec("swiglu", {"hidden": h, "intermediate": I}), prefix="model.layers.0",
+                     names={"norm1": "input_layernorm", "mixer": "self_attn", "norm2": "post_attention_layernorm", "feedforward": "mlp"})
+    block = lookup("block", "prenorm")(spec)
+    g = torch.Generator().manual_seed(5)
+    w = {s.name: torch.randn(s.shape, generator=g) * (0.1 if s.role != "norm" else 0.05) + (1.0 if s.role == "norm" else 0.0)
+         for s in block.tensor_specs()}
+    block.load({k: v.clone() for k, v in w.items()}, rt)
+    runner = harness(block.mixer, rt, page=16, pages=8)
+    T = 21
+    x = torch.randn(T, h, generator=g)
+    runner.begin("r")
+    runner.cache.reserve("r", T)
+    ctx = runner.build_context([StepEntry("r", [0] * T, [])])
+    hidden = x.clone().to(DEV)
+    block.forward(hidden, ctx, runner.views.view(0, ctx))
+    cfg = {"heads": H, "kv_heads": K, "head_dim": d, "eps": 3e-6, "theta": 5e5}
+    want, _ = plain.layer_forward(cfg, w, 0, x)
+    torch.testing.assert_close(hidden.cpu(), want, rtol=1e-4, atol=1e-4)
+
+    emb = lookup("embedding", "token_table")(vocab=V, hidden=h, name="model.embed_tokens")
+    table = torch.randn(V, h, generator=g)
+    emb.load({"model.embed_tokens.weight": table.clone()}, rt)
+    ids = torch.tensor([0, 332, 7, 7], dtype=torch.int32)
+    out = torch.empty(4, h, device=DEV)
+    emb.forward(ids.to(DEV), out)
+    assert torch.equal(out.cpu(), plain.embed(ids.tolist(), table))
+
+    head = lookup("head", "linear")(vocab=V, hidden=h, name="lm_head", tied=True)
+    assert head.tensor_specs() == []
+    head.load({}, rt)
+    head.tie(emb.table)
+    logits = torch.empty(4, V, device=DEV)
+    rows = torch.randn(4, h, generator=g)
+    head.forward(rows.to(DEV), logits)
+    torch.testing.assert_close(logits.cpu(), plain.linear(rows, table), rtol=1e-4, atol=1e-4)
+
+
+def test_other_position_encodings_and_a_routed_feedforward_fit_the_interfaces(tmp_path):
+    """Generality of the parts, shown with toys defined here: partial rotary with interleaved pairs (through the
+    fused kernel's parameters), no position encoding at all, and a feed-forward that routes each token to one of
+    two experts.  None of them is a model of anyone's; each is checked against plain torch written here."""
+    from marin_b200.cache import CacheManager
+    from marin_b200.config.base import ModelConfig
+    from marin_b200.engine import Runner, load_model
+    from marin_b200.models import register_architecture
+    from marin_b200.parts import FeedForward, LayerSpec, ModelSpec, PartSpec, ScheduleEntry, TensorSpec, register_feedforward
+    from marin_b200.weights import write_random_model
+
+    @register_feedforward("toy_top1")
+    class Top1Experts(FeedForward):
+        """y = W2[e] relu(W1[e] x) with e = argmax(router x): routing and experts are the part's own business."""
+
+        def __init__(self, hidden, inner, experts, name):
+            self.hidden, self.inner, self.experts, self.name = hidden, inner, experts, name
+
+        def tensor_specs(self):
+            n = self.name
+            specs = [TensorSpec(f"{n}.router.weight", (self.experts, self.hidden))]
+            for e in range(self.experts):
+                specs.append(TensorSpec(f"{n}.experts.{e}.w1.weight", (self.inner, self.hidden)))
+                specs.append(TensorSpec(f"{n}.experts.{e}.w2.weight", (self.hidden, self.inner)))
+            return specs
+
+        def load(self, tensors, rt):
+            n = self.name
+            self.router = tensors.pop(f"{n}.router.weight").to(rt.device, torch.float32)
+            self.w1 = [tensors.pop(f"{n}.experts.{e}.w1.weight").to(rt.device, torch.float32) for e in range(self.experts)]
+            self.w2 = [tensors.pop(f"{n}.experts.{e}.w2.weight").to(rt.device, torch.float32) for e in range(self.experts)]
+
+        def forward(self, x, ctx, residual):
+            xf = x.float()
+            choice = torch.argmax(xf @ self.router.t(), dim=-1)
+            for e in range(self.experts):
+                rows = torch.nonzero(choice == e).flatten()
+                if rows.numel():
+                    residual[rows] += torch.relu(xf[rows] @ self.w1[e].t()) @ self.w2[e].t()
+
+    @dataclass
+    class Toy2Config(ModelConfig):
+        @classmethod
+        def from_dict(cls, raw, generation=None):
+            return cls(architecture="ToyRoutedLM", model_type="toy_routed", vocab_size=raw["vocab_size"], hidden_size=raw["hidden_size"],
+                       max_position_embeddings=raw["max_position_embeddings"], raw=dict(raw))
+
+        def to_json_dict(self):
+            return dict(self.raw)
+
+    def build_spec(cfg):
+        h = cfg.hidden_size
+        norm = PartSpec("rmsnorm", {"dim": h, "eps": 1e-6})
+        names = {"norm1": "n1", "mixer": "att", "norm2": "n2", "feedforward": "ff"}
+
+        def att(position):
+            return PartSpec("gqa_attention", {"hidden": h, "heads": 2, "kv_heads": 2, "head_dim": 32, "qk_norm": False, "position": position})
+        layers = [
+            LayerSpec("prenorm", norm, att(PartSpec("rope", {"head_dim": 32, "theta": 50.0, "rotary_dim": 16, "interleaved": True})),
+                      PartSpec("toy_top1", {"hidden": h, "inner": 24, "experts": 2}), "t.l0", names),
+            LayerSpec("prenorm", norm, att(PartSpec("none", {})), PartSpec("swiglu", {"hidden": h, "intermediate": 48}), "t.l1", names),
+        ]
+        return ModelSpec(hidden_size=h, vocab_size=cfg.vocab_size,
+                         embedding=PartSpec("token_table", {"vocab": cfg.vocab_size, "hidden": h, "name": "t.embed"}),
+                         final_norm=PartSpec("rmsnorm", {"dim": h, "eps": 1e-6, "name": "t.norm"}),
+                         head=PartSpec("linear", {"vocab": cfg.vocab_size, "hidden": h, "name": "t.head"}),
+                         layers=layers, schedule=[ScheduleEntry(0), ScheduleEntry(1)])
+
+    register_architecture("ToyRoutedLM", "toy_routed", Toy2Config, build_spec)
+    raw = {"architectures": ["ToyRoutedLM"], "model_type": "toy_routed", "vocab_size": 61, "hidden_size": 64, "max_position_embeddings": 80}
+    d = write_random_model(str(tmp_path / "toy2"), Toy2Config.from_dict(raw), seed=9, dtype=torch.float32, matrix_std=0.2)
+    rt = runtime()
+    config, model = load_model(d, rt)
+    cache = CacheManager(model.cache_needs(), [e.cache_of for e in model.spec.schedule], 8, 20, 4)
+    cache.allocate(rt.device, rt.dtype)
+    runner = Runner(model, cache, rt, 80)
+    w = plain.read_weights(d)
+
+    def toy2_plain(ids):
+        T = len(ids)
+        x = plain.embed(ids, w["t.embed.weight"])
+        pos = torch.arange(T)
+        for li in (0, 1):
+            p = f"t.l{li}."
+            n = plain.rms_norm(x, w[p + "n1.weight"], 1e-6)
+            q = plain.linear(n, w[p + "att.q_proj.weight"]).view(T, 2, 32)
+            k = plain.linear(n, w[p + "att.k_proj.weight"]).view(T, 2, 32)
+            v = plain.linear(n, w[p + "att.v_proj.weight"]).view(T, 2, 32)
+            if li == 0:      # partial rotary over the first 16 dims, pairs (2i, 2i+1)
+                ang = pos.float()[:, None] * torch.pow(torch.tensor(50.0), -(torch.arange(8, dtype=torch.float32) * 2.0 / 16))[None, :]
+                cos, sin = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+                for t_ in (q, k):
+                    a, b = t_[..., 0:16:2].clone(), t_[..., 1:16:2].clone()
+                    t_[..., 0:16:2] = a * cos - b * sin
+                    t_[..., 1:16:2] = b * cos + a * sin
+            x = x + plain.linear(plain.attention(q, k, v).reshape(T, 64), w[p + "att.o_proj.weight"])
+            n = plain.rms_norm(x, w[p + "n2.weight"], 1e-6)
+            if li == 0:
+                choice = torch.argmax(n @ w[p + "ff.router.weight"].t(), dim=-1)
+                y = torch.zeros_like(x)
+                for e in range(2):
+                    rows = torch.nonzero(choice == e).flatten()
+                    y[rows] = torch.relu(n[rows] @ w[p + f"ff.experts.{e}.w1.weight"].t()) @ w[p + f"ff.experts.{e}.w2.weight"].t()
+                x = x + y
+            else:
+                x = x + plain.swiglu_mlp(n, w[p + "ff.gate_proj.weight"], w[p + "ff.up_proj.weight"], w[p + "ff.down_proj.weight"])
+        return plain.linear(plain.rms_norm(x, w["t.norm.weight"], 1e-6), w["t.head.weight"])
+
+    rng = random.Random(2)
+    toks = random_prompt(rng, 61, 70)
+    want = toy2_plain(toks)
+    torch.testing.assert_close(run_whole(runner, "w", toks).cpu(), want, rtol=1e-4, atol=1e-4)
+    torch.testing.assert_close(run_portions(runner, "p", toks, portions(70, [9, 1, 2, 17])).cpu(), want, rtol=1e-4, atol=1e-4)
