@@ -1,0 +1,282 @@
+// Prefill attention on the 5th-generation tensor cores (tcgen05 / TMEM), compiled per head size (-DHEAD_DIM=64|128)
+// and group size (-DGROUP).  A CTA takes 128 consecutive query tokens of one request and one query head and
+// walks the keys in blocks of 64:
+//   S = Q K^T      tcgen05.mma, M = 128 queries, N = 64 keys, K = HEAD_DIM; Q and K tiles in shared memory (TMA,
+//                  128-byte swizzle, K-major); the accumulator S is 64 columns of tensor memory;
+//   softmax        thread t owns query row t (TMEM lane t): it reads its 64 scores with tcgen05.ld, masks, keeps the
+//                  running maximum and sum in float32 (exp2 domain) — no shuffles — and writes P in bf16 to shared
+//                  memory in the swizzled K-major layout the next MMA reads;
+//   PV             tcgen05.mma, M = 128, N = HEAD_DIM, K = 64 keys; V stays as it lies in the cache ([key][d], d
+//                  contiguous), i.e. an MN-major B operand; the product lands in HEAD_DIM more TMEM columns and each
+//                  thread folds it into its own float32 output row: o = o * correction + PV.
+// K and V blocks arrive by TMA straight from the paged cache (one 16-key box per page piece and 64-column half) into
+// two buffers, so the next block is on its way while this one is used.  Two CTAs fit an SM: one's softmax overlaps the
+// other's MMAs.  Needs pages of at least 16 positions.  Waits are bounded and record a code in *error_flag.
+// The mma.sync kernel in attention_fast.cu is the fallback and the plain twin (the reference's counterpart:
+// crates/cuda/src/attention_mma.cu:43-180).
+#include "tc_common.cuh"
+#include "launch.cuh"
+
+#ifndef HEAD_DIM
+#error "compile with -DHEAD_DIM=64 or 128"
+#endif
+#ifndef GROUP
+#error "compile with -DGROUP=<query heads per kv head>"
+#endif
+static_assert(HEAD_DIM == 64 || HEAD_DIM == 128, "the tcgen05 attention kernel takes heads of 64 or 128");
+
+#define D HEAD_DIM
+#define NH (D / 64)                    // 64-column halves of a head: one 128-byte swizzle row each
+#define TA_BM 128
+#define TA_BN 64
+#define TA_Q_BYTES (NH * TA_BM * 128)
+#define TA_KV_BYTES (NH * TA_BN * 128)  // one of K or V, one buffer
+#define TA_P_BYTES (TA_BM * 128)
+#define TA_SMEM (TA_Q_BYTES + 4 * TA_KV_BYTES + TA_P_BYTES + 128)
+#define TA_TMEM_COLS 256               // S: 64 columns, PV: HEAD_DIM columns
+
+__device__ __forceinline__ float ta_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// MN-major B operand (V: rows are keys, 64 head columns contiguous per 128-byte swizzled row): 8-key groups 1024 bytes
+// apart (stride offset), 64-column halves `half_bytes` apart (leading offset).
+__device__ __forceinline__ uint64_t umma_desc_mn(uint32_t smem_addr, uint32_t half_bytes) {
+    const uint32_t lo = ((smem_addr & 0x3FFFFu) >> 4) | ((half_bytes >> 4) << 16);
+    const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);
+    return ((uint64_t)hi << 32) | lo;
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+__global__ void __launch_bounds__(128, 2) attn_prefill_tc_kernel(
+    const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+    bf16* __restrict__ out, const int* __restrict__ block_table, int max_pages, const int* __restrict__ cu_tokens,
+    const int* __restrict__ seq_lens, int first_req, int K, int page_shift, float scale, int window, int* __restrict__ error_flag) {
+    extern __shared__ __align__(1024) uint8_t smem[];     // the swizzled tiles need 1024-byte alignment (checked below)
+    uint8_t* sQ = smem;
+    uint8_t* sKV = sQ + TA_Q_BYTES;                       // [buffer][K then V][half][64 rows][128 B]
+    uint8_t* sP = sKV + 4 * TA_KV_BYTES;
+    uint64_t* bars = (uint64_t*)(sP + TA_P_BYTES);        // q_full, kv_full[2], s_done, pv_done
+    uint64_t* q_full = bars, *kv_full = bars + 1, *s_done = bars + 3, *pv_done = bars + 4;
+    uint32_t* tmem_slot = (uint32_t*)(bars + 5);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    pdl_wait();
+    pdl_launch_dependents();
+    const int H = K * GROUP;
+    const int r = first_req + blockIdx.z, h = blockIdx.y, qt = gridDim.x - 1 - blockIdx.x;   // long tiles first
+    const int tok0 = cu_tokens[r], n = cu_tokens[r + 1] - tok0;
+    if (qt * TA_BM >= n) return;                           // nothing to do here (before any tensor memory is taken)
+    if ((smem_u32(smem) & 1023u) != 0) { if (threadIdx.x == 0) atomicExch(error_flag, 20); return; }
+    const bool active = true;
+    const int len = seq_lens[r], pos0 = len - n;
+    const int rows = min(TA_BM, n - qt * TA_BM);
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1); mbar_init(&kv_full[0], 1); mbar_init(&kv_full[1], 1); mbar_init(s_done, 1); mbar_init(pv_done, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TA_TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+    const int q_first = pos0 + qt * TA_BM, q_last = q_first + rows - 1;
+    const int k_lo = window > 0 ? max(0, q_first - window + 1) : 0;
+    const int kh = h / GROUP;
+    const int* table = block_table + (size_t)r * max_pages;
+    const int page_mask = (1 << page_shift) - 1;
+    const int kb_first = k_lo / TA_BN, kb_last = q_last / TA_BN;
+    const int row_t = threadIdx.x;                         // this thread's query row
+    const int qp = q_first + row_t;
+    const int lo_t = window > 0 ? max(0, qp - window + 1) : 0;
+    const float sl2 = scale * 1.4426950408889634f;
+    constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TA_BN >> 3) << 17) | ((uint32_t)(TA_BM >> 4) << 24);
+    constexpr uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(TA_BM >> 4) << 24);
+
+    // leader: asks for one block of keys and values (16-key boxes, one per page piece and half)
+    auto load_kv = [&](int kb, int buf) {
+        uint8_t* dk = sKV + (size_t)buf * 2 * TA_KV_BYTES;
+        uint8_t* dv = dk + TA_KV_BYTES;
+        mbar_expect_tx(&kv_full[buf], 2 * TA_KV_BYTES);
+#pragma unroll
+        for (int g = 0; g < TA_BN / 16; ++g) {
+            const int key = kb * TA_BN + g * 16;
+            const int row = (int)((((size_t)table[key >> page_shift] * K + kh) << page_shift) + (size_t)(key & page_mask));
+#pragma unroll
+            for (int hf = 0; hf < NH; ++hf) {
+                tma_load_2d(dk + hf * (TA_BN * 128) + g * 2048, &map_k, hf * 64, row, &kv_full[buf]);
+                tma_load_2d(dv + hf * (TA_BN * 128) + g * 2048, &map_v, hf * 64, row, &kv_full[buf]);
+            }
+        }
+    };
+
+    float o[D];
+#pragma unroll
+    for (int i = 0; i < D; ++i) o[i] = 0.0f;
+    float m_run = -INFINITY, l_run = 0.0f;
+    bool ok = true;
+
+    if (active && threadIdx.x == 0) {
+        mbar_expect_tx(q_full, TA_Q_BYTES);
+#pragma unroll
+        for (int hf = 0; hf < NH; ++hf) tma_load_2d(sQ + hf * (TA_BM * 128), &map_q, h * D + hf * 64, tok0 + qt * TA_BM, q_full);
+        load_kv(kb_first, 0);
+    }
+    for (int kb = kb_first, i = 0; kb <= kb_last; ++kb, ++i) {
+        const int buf = i & 1;
+        const uint32_t sk = smem_u32(sKV + (size_t)buf * 2 * TA_KV_BYTES), sv = sk + TA_KV_BYTES;
+        if (threadIdx.x == 0) {
+            if (kb < kb_last) load_kv(kb + 1, buf ^ 1);    // that buffer's last reader (the PV product two blocks ago) is done
+            if (i == 0 && !mbar_wait(q_full, 0)) { atomicExch(error_flag, 21); ok = false; }
+            if (ok && !mbar_wait(&kv_full[buf], (i >> 1) & 1)) { atomicExch(error_flag, 22); ok = false; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t sq = smem_u32(sQ);
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk) {
+                const uint64_t adesc = umma_desc(sq + (kk / 4) * (TA_BM * 128)) + 2 * (kk % 4);
+                const uint64_t bdesc = umma_desc(sk + (kk / 4) * (TA_BN * 128)) + 2 * (kk % 4);
+                umma_bf16(tmem_base, adesc, bdesc, idesc_s, kk > 0 ? 1u : 0u);
+            }
+            umma_commit(s_done);
+        }
+        // ---- softmax of this thread's row ----
+        if (!mbar_wait(s_done, i & 1)) { if (lane == 0) atomicExch(error_flag, 23); ok = false; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        float s[TA_BN];
+        tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16), s);
+        tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + 32, s + 32);
+        const int key0 = kb * TA_BN;
+        const bool interior = key0 + TA_BN - 1 <= q_first && (window <= 0 || key0 >= q_last - window + 1);
+        if (!interior) {
+#pragma unroll
+            for (int j = 0; j < TA_BN; ++j)
+                if (!(key0 + j <= qp && key0 + j >= lo_t)) s[j] = -INFINITY;
+        }
+        float mx = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < TA_BN; ++j) mx = fmaxf(mx, s[j]);
+        const float m_new = fmaxf(m_run, mx * sl2);
+        const float base = m_new == -INFINITY ? 0.0f : m_new;
+        const float corr = ta_exp2(m_run - base);
+        m_run = m_new;
+        float sum = 0.0f;
+        uint4* prow = reinterpret_cast<uint4*>(sP + row_t * 128);
+#pragma unroll
+        for (int c = 0; c < TA_BN / 8; ++c) {
+            float p[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) { p[e] = ta_exp2(fmaf(s[c * 8 + e], sl2, -base)); sum += p[e]; }
+            uint4 packed;
+            __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) p2[e] = __floats2bfloat162_rn(p[2 * e], p[2 * e + 1]);
+            prow[c ^ (row_t & 7)] = packed;                 // the 128-byte swizzle: 16-byte piece index xor (row mod 8)
+        }
+        l_run = l_run * corr + sum;
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // P was written by ordinary stores; the MMA reads it through the async proxy
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        if (__syncthreads_or(!ok)) break;                   // a wait gave up somewhere: everyone leaves together
+        if (threadIdx.x == 0) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t sp = smem_u32(sP);
+#pragma unroll
+            for (int kk = 0; kk < TA_BN / 16; ++kk) {
+                const uint64_t adesc = umma_desc(sp) + 2 * kk;
+                const uint64_t bdesc = umma_desc_mn(sv + kk * 2048, TA_BN * 128);
+                umma_bf16(tmem_base + TA_BN, adesc, bdesc, idesc_pv, kk > 0 ? 1u : 0u);
+            }
+            umma_commit(pv_done);
+        }
+        if (!mbar_wait(pv_done, i & 1)) { if (lane == 0) atomicExch(error_flag, 24); ok = false; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+            float pv[32];
+            tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + TA_BN + c * 32, pv);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) o[c * 32 + j] = fmaf(o[c * 32 + j], corr, pv[j]);
+        }
+    }
+    if (active && row_t < rows) {
+        const float inv = 1.0f / l_run;
+        bf16* dst = out + ((size_t)(tok0 + qt * TA_BM + row_t) * H + h) * D;
+#pragma unroll
+        for (int c = 0; c < D / 8; ++c) {
+            uint4 packed;
+            __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) p2[e] = __floats2bfloat162_rn(o[c * 8 + 2 * e] * inv, o[c * 8 + 2 * e + 1] * inv);
+            reinterpret_cast<uint4*>(dst)[c] = packed;
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TA_TMEM_COLS) : "memory");
+    }
+}
+
+// ---- host side ------------------------------------------------------------------------------------------------------
+static int map_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+    EncodeTiled enc = encode_tiled();
+    if (enc == nullptr) return MB_ERR_BAD_SIZE;
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {cols * 2};
+    cuuint32_t box[2] = {64, box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult rc = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return rc == CUDA_SUCCESS ? 0 : 1000 + (int)rc;
+}
+
+// Prefill attention of requests first_req .. first_req+requests-1 (tokens cu_tokens[r]..cu_tokens[r+1], all `tokens`
+// rows of q and out belong to the step); cache_pages pages of page_size (>= 16) positions.
+MB_API int mb_attn_prefill_tc(const void* q, const void* k_cache, const void* v_cache, void* out, const int* block_table,
+                              int max_pages, const int* cu_tokens, const int* seq_lens, int first_req, int requests,
+                              int max_query_len, int tokens, int K, int page_size, long long cache_pages, float scale,
+                              int window, int* error_flag, cudaStream_t s) {
+    if (requests <= 0 || max_query_len <= 0) return 0;
+    int page_shift = -1;
+    for (int b = 4; b < 16; ++b)
+        if ((1 << b) == page_size) page_shift = b;
+    if (page_shift < 0) return MB_ERR_BAD_SIZE;
+    if (((uintptr_t)q & 15) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15)) return MB_ERR_BAD_SIZE;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TA_SMEM);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    CUtensorMap mq, mk, mv;
+    int rc = map_2d(&mq, q, (uint64_t)tokens, (uint64_t)K * GROUP * D, TA_BM);
+    if (rc) return rc;
+    const uint64_t cache_rows = (uint64_t)cache_pages * K * page_size;
+    rc = map_2d(&mk, k_cache, cache_rows, D, 16);
+    if (rc) return rc;
+    rc = map_2d(&mv, v_cache, cache_rows, D, 16);
+    if (rc) return rc;
+    dim3 grid((max_query_len + TA_BM - 1) / TA_BM, K * GROUP, requests);
+    return launch_kernel(attn_prefill_tc_kernel, grid, 128, TA_SMEM, s, 0, mq, mk, mv, (bf16*)out, block_table, max_pages, cu_tokens,
+                         seq_lens, first_req, K, page_shift, scale, window, error_flag);
+}

@@ -167,12 +167,18 @@ def attention_job(d: int, group: int) -> tuple:
     return (["attention_fast.cu"], [f"HEAD_DIM={d}", f"GROUP={group}"] + extra)
 
 
+def attention_tc_job(d: int, group: int) -> tuple:
+    return (["attention_tc.cu"], [f"HEAD_DIM={d}", f"GROUP={group}"])
+
+
 def build_all(verbose: bool = True) -> List[str]:
     """Compiles every library and the attention kernels for the layouts in ``ATTENTION_LAYOUTS`` (in parallel).
     Used by the build check and before timing."""
     jobs = {n: (src, []) for n, src in LIBRARIES.items()}
     for d, g in ATTENTION_LAYOUTS:
         jobs[f"mb_attention_fast_d{d}_g{g}"] = attention_job(d, g)
+        if d in (64, 128):
+            jobs[f"mb_attention_tc_d{d}_g{g}"] = attention_tc_job(d, g)
     return build_many(jobs, verbose)
 
 
@@ -194,6 +200,9 @@ def build_for(model, dtype, verbose: bool = True) -> List[str]:
         if ops.fast_attention_supported(dtype, mixer.heads, mixer.kv_heads, mixer.head_dim):
             jobs[f"mb_attention_fast_d{mixer.head_dim}_g{mixer.heads // mixer.kv_heads}"] = attention_job(
                 mixer.head_dim, mixer.heads // mixer.kv_heads)
+            if mixer.head_dim in (64, 128):
+                jobs[f"mb_attention_tc_d{mixer.head_dim}_g{mixer.heads // mixer.kv_heads}"] = attention_tc_job(
+                    mixer.head_dim, mixer.heads // mixer.kv_heads)
         else:
             jobs["mb_attention_simple"] = (LIBRARIES["mb_attention_simple"], [])
     return build_many(jobs, verbose)

@@ -194,6 +194,8 @@ def qk_norm_rope_write(qkv, q_out, q_weight, k_weight, eps, positions, inv_freq,
 
 #: bf16 attention goes to the tensor-core / split-KV kernels when the head layout allows (False: the plain kernel)
 use_fast_attention = True
+#: prompt portions go to the tcgen05 attention kernel where it applies (heads of 64 or 128, pages >= 16)
+use_tc_attention = True
 _attn_scratch = {}
 DECODE_SPLITS = (4096, 2048, 1024, 512, 256, 128, 64)      # keys per CTA the split-KV decode kernel may be given
 
@@ -257,7 +259,14 @@ def attention(q, k_cache, v_cache, out, ctx, block_table, H, K, d, scale, window
                                       _ptr(ctx.seq_lens), _c_int(nd), _c_int(K), _c_int(page_size), _c_float(scale),
                                       _c_int(window), _ptr(part_acc), _ptr(part_ml), _ptr(counters), _c_int(chunks), _c_int(split),
                                       _stream()), "attention (decode)")
-        if ctx.num_requests > nd:
+        if ctx.num_requests > nd and use_tc_attention and d in (64, 128) and page_size >= 16:
+            tc = build.load(f"mb_attention_tc_d{d}_g{H // K}", *build.attention_tc_job(d, H // K))
+            _check(tc.mb_attn_prefill_tc(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), _c_int(max_pages),
+                                         _ptr(ctx.cu_tokens), _ptr(ctx.seq_lens), _c_int(nd), _c_int(ctx.num_requests - nd),
+                                         _c_int(ctx.max_query_len), _c_int(T), _c_int(K), _c_int(page_size),
+                                         ctypes.c_longlong(k_cache.shape[0]), _c_float(scale), _c_int(window),
+                                         _ptr(_gemm_scratch(q.device)["error"]), _stream()), "attention (prefill, tensor cores)")
+        elif ctx.num_requests > nd:
             _check(lib.mb_attn_prefill(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), _c_int(max_pages),
                                        _ptr(ctx.cu_tokens), _ptr(ctx.seq_lens), _c_int(nd), _c_int(ctx.num_requests - nd),
                                        _c_int(ctx.max_query_len), _c_int(K), _c_int(page_size), _c_float(scale),

@@ -398,3 +398,26 @@ def test_device_sampling_follows_the_reference_distribution(ops, temperature, to
     assert float((counts - probs).abs().max()) <= 2.0 / N + 1e-4
     if temperature == 0.0:
         assert int(out[0]) == 3 and bool((out == 3).all())       # the lower id of the two equal best
+
+
+@pytest.mark.parametrize("H,K,d,page", [(32, 8, 128, 16), (8, 2, 64, 16), (5, 1, 64, 32), (40, 8, 128, 64)])
+@pytest.mark.parametrize("window", [0, 300])
+def test_attention_tensor_core_prefill_matches_the_mma_kernel(ops, H, K, d, page, window):
+    """The tcgen05 prefill kernel against its plain twin and against the mma.sync kernel, on portions at several
+    cached lengths, with ragged tile and block edges."""
+    g = torch.Generator(device=DEV).manual_seed(18)
+    lens_new = [(0, 1), (900, 150), (0, 200), (511, 2), (63, 129), (1000, 128), (17, 64)]
+    pages = sum(-(-(c + n) // page) for c, n in lens_new) + 3
+    q, kc, vc, table, ctx = paged_case(g, torch.bfloat16, lens_new, H, K, d, page, pages)
+    got, mma, want = torch.empty_like(q), torch.empty_like(q), torch.empty_like(q)
+    scale = 1.0 / math.sqrt(d)
+    ops.attention(q, kc, vc, got, ctx, table, H, K, d, scale, window)
+    ops.check_device_errors()
+    ops.use_tc_attention = False
+    try:
+        ops.attention(q, kc, vc, mma, ctx, table, H, K, d, scale, window)
+    finally:
+        ops.use_tc_attention = True
+    ref.attention(q, kc, vc, want, ctx, table, H, K, d, scale, window)
+    torch.testing.assert_close(mma.float(), want.float(), rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(got.float(), want.float(), rtol=2e-2, atol=2e-2)
