@@ -32,7 +32,7 @@ static_assert(HEAD_DIM == 64 || HEAD_DIM == 128, "the tcgen05 attention kernel t
 #define TA_Q_BYTES (NH * TA_BM * 128)
 #define TA_KV_BYTES (NH * TA_BN * 128)  // one of K or V, one buffer
 #define TA_P_BYTES (TA_BM * 128)
-#define TA_SMEM (TA_Q_BYTES + 4 * TA_KV_BYTES + TA_P_BYTES + 128)
+#define TA_SMEM (TA_Q_BYTES + 4 * TA_KV_BYTES + TA_P_BYTES + 256)
 #define TA_TMEM_COLS 256               // S: 64 columns, PV: HEAD_DIM columns
 
 __device__ __forceinline__ float ta_exp2(float x) {
@@ -64,7 +64,32 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
-__global__ void __launch_bounds__(128, 2) attn_prefill_tc_kernel(
+// Waits for a phase; gives up at once if another thread of the CTA already gave up (`*abort`), and says so itself when
+// its own time limit passes.
+__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort, int* error_flag, int code) {
+    const uint32_t addr = smem_u32(bar);
+    const long long start = clock64();
+    for (;;) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+        if (*abort) return false;
+        if (clock64() - start > TC_WAIT_LIMIT) { *abort = 1; atomicExch(error_flag, code); return false; }
+    }
+}
+
+__device__ __forceinline__ void mbar_arrive_one(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// 160 threads: warps 0..3 own the 128 query rows (softmax, output); warp 4 asks for keys and values and issues the MMAs.
+__global__ void __launch_bounds__(160, 2) attn_prefill_tc_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
     bf16* __restrict__ out, const int* __restrict__ block_table, int max_pages, const int* __restrict__ cu_tokens,
     const int* __restrict__ seq_lens, int first_req, int K, int page_shift, float scale, int window, int* __restrict__ error_flag) {
@@ -72,9 +97,17 @@ __global__ void __launch_bounds__(128, 2) attn_prefill_tc_kernel(
     uint8_t* sQ = smem;
     uint8_t* sKV = sQ + TA_Q_BYTES;                       // [buffer][K then V][half][64 rows][128 B]
     uint8_t* sP = sKV + 4 * TA_KV_BYTES;
-    uint64_t* bars = (uint64_t*)(sP + TA_P_BYTES);        // q_full, kv_full[2], s_done, pv_done
-    uint64_t* q_full = bars, *kv_full = bars + 1, *s_done = bars + 3, *pv_done = bars + 4;
-    uint32_t* tmem_slot = (uint32_t*)(bars + 5);
+    uint64_t* bars = (uint64_t*)(sP + TA_P_BYTES);
+    uint64_t* q_full = bars;              // Q tile has landed
+    uint64_t* kv_full = bars + 1;         // [2] a block of K and V has landed
+    uint64_t* kv_free = bars + 3;         // [2] the MMAs that read the buffer are done
+    uint64_t* s_done = bars + 5;          // S = Q K^T is in tensor memory
+    uint64_t* s_free = bars + 6;          // every row has read its scores (4 warps arrive)
+    uint64_t* p_ready = bars + 7;         // P is in shared memory (4 warps arrive)
+    uint64_t* pv_done = bars + 8;         // P V is in tensor memory
+    uint64_t* pv_free = bars + 9;         // every row has read its part of P V (4 warps arrive)
+    uint32_t* tmem_slot = (uint32_t*)(bars + 10);
+    volatile int* abort = (volatile int*)(tmem_slot + 1);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     pdl_wait();
     pdl_launch_dependents();
@@ -83,11 +116,13 @@ __global__ void __launch_bounds__(128, 2) attn_prefill_tc_kernel(
     const int tok0 = cu_tokens[r], n = cu_tokens[r + 1] - tok0;
     if (qt * TA_BM >= n) return;                           // nothing to do here (before any tensor memory is taken)
     if ((smem_u32(smem) & 1023u) != 0) { if (threadIdx.x == 0) atomicExch(error_flag, 20); return; }
-    const bool active = true;
     const int len = seq_lens[r], pos0 = len - n;
     const int rows = min(TA_BM, n - qt * TA_BM);
     if (threadIdx.x == 0) {
-        mbar_init(q_full, 1); mbar_init(&kv_full[0], 1); mbar_init(&kv_full[1], 1); mbar_init(s_done, 1); mbar_init(pv_done, 1);
+        mbar_init(q_full, 1);
+        for (int b = 0; b < 2; ++b) { mbar_init(&kv_full[b], 1); mbar_init(&kv_free[b], 1); }
+        mbar_init(s_done, 1); mbar_init(s_free, 4); mbar_init(p_ready, 4); mbar_init(pv_done, 1); mbar_init(pv_free, 4);
+        *abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
@@ -102,130 +137,170 @@ __global__ void __launch_bounds__(128, 2) attn_prefill_tc_kernel(
     const int q_first = pos0 + qt * TA_BM, q_last = q_first + rows - 1;
     const int k_lo = window > 0 ? max(0, q_first - window + 1) : 0;
     const int kh = h / GROUP;
-    const int* table = block_table + (size_t)r * max_pages;
-    const int page_mask = (1 << page_shift) - 1;
     const int kb_first = k_lo / TA_BN, kb_last = q_last / TA_BN;
-    const int row_t = threadIdx.x;                         // this thread's query row
-    const int qp = q_first + row_t;
-    const int lo_t = window > 0 ? max(0, qp - window + 1) : 0;
-    const float sl2 = scale * 1.4426950408889634f;
-    constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TA_BN >> 3) << 17) | ((uint32_t)(TA_BM >> 4) << 24);
-    constexpr uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(TA_BM >> 4) << 24);
+    const int nblk = kb_last - kb_first + 1;
 
-    // leader: asks for one block of keys and values (16-key boxes, one per page piece and half)
-    auto load_kv = [&](int kb, int buf) {
-        uint8_t* dk = sKV + (size_t)buf * 2 * TA_KV_BYTES;
-        uint8_t* dv = dk + TA_KV_BYTES;
-        mbar_expect_tx(&kv_full[buf], 2 * TA_KV_BYTES);
+    if (warp == 4) {
+        if (lane == 0) {
+            // ---- the issuer: TMA for Q, K, V and all MMAs ----
+            const int* table = block_table + (size_t)r * max_pages;
+            const int page_mask = (1 << page_shift) - 1;
+            constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TA_BN >> 3) << 17) | ((uint32_t)(TA_BM >> 4) << 24);
+            constexpr uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(TA_BM >> 4) << 24);
+            auto load_kv = [&](int kb, int buf) {           // 16-key boxes, one per page piece and 64-column half
+                uint8_t* dk = sKV + (size_t)buf * 2 * TA_KV_BYTES;
+                uint8_t* dv = dk + TA_KV_BYTES;
+                mbar_expect_tx(&kv_full[buf], 2 * TA_KV_BYTES);
 #pragma unroll
-        for (int g = 0; g < TA_BN / 16; ++g) {
-            const int key = kb * TA_BN + g * 16;
-            const int row = (int)((((size_t)table[key >> page_shift] * K + kh) << page_shift) + (size_t)(key & page_mask));
+                for (int g = 0; g < TA_BN / 16; ++g) {
+                    const int key = kb * TA_BN + g * 16;
+                    const int row = (int)((((size_t)table[key >> page_shift] * K + kh) << page_shift) + (size_t)(key & page_mask));
 #pragma unroll
-            for (int hf = 0; hf < NH; ++hf) {
-                tma_load_2d(dk + hf * (TA_BN * 128) + g * 2048, &map_k, hf * 64, row, &kv_full[buf]);
-                tma_load_2d(dv + hf * (TA_BN * 128) + g * 2048, &map_v, hf * 64, row, &kv_full[buf]);
+                    for (int hf = 0; hf < NH; ++hf) {
+                        tma_load_2d(dk + hf * (TA_BN * 128) + g * 2048, &map_k, hf * 64, row, &kv_full[buf]);
+                        tma_load_2d(dv + hf * (TA_BN * 128) + g * 2048, &map_v, hf * 64, row, &kv_full[buf]);
+                    }
+                }
+            };
+            auto issue_s = [&](int i) {                     // S(i) = Q K(i)^T into TMEM columns [0, 64)
+                const uint32_t sq = smem_u32(sQ), sk = smem_u32(sKV + (size_t)(i & 1) * 2 * TA_KV_BYTES);
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint64_t adesc = umma_desc(sq + (kk / 4) * (TA_BM * 128)) + 2 * (kk % 4);
+                    const uint64_t bdesc = umma_desc(sk + (kk / 4) * (TA_BN * 128)) + 2 * (kk % 4);
+                    umma_bf16(tmem_base, adesc, bdesc, idesc_s, kk > 0 ? 1u : 0u);
+                }
+                umma_commit(s_done);
+            };
+            mbar_expect_tx(q_full, TA_Q_BYTES);
+#pragma unroll
+            for (int hf = 0; hf < NH; ++hf) tma_load_2d(sQ + hf * (TA_BM * 128), &map_q, h * D + hf * 64, tok0 + qt * TA_BM, q_full);
+            load_kv(kb_first, 0);
+            bool ok = wait_or_abort(q_full, 0, abort, error_flag, 21) && wait_or_abort(&kv_full[0], 0, abort, error_flag, 22);
+            if (ok) issue_s(0);
+            for (int i = 0; i < nblk && ok; ++i) {
+                const int buf = i & 1;
+                if (i + 1 < nblk) {
+                    // the other buffer was read by the MMAs of block i - 1
+                    if (i >= 1) ok = ok && wait_or_abort(&kv_free[buf ^ 1], ((i - 1) >> 1) & 1, abort, error_flag, 25);
+                    if (ok) load_kv(kb_first + i + 1, buf ^ 1);
+                    // S(i + 1) can start as soon as every row has read S(i)
+                    ok = ok && wait_or_abort(&kv_full[buf ^ 1], ((i + 1) >> 1) & 1, abort, error_flag, 22);
+                    ok = ok && wait_or_abort(s_free, i & 1, abort, error_flag, 26);
+                    if (ok) issue_s(i + 1);
+                }
+                // P V(i) into TMEM columns [64, 64 + D): needs P(i) in shared memory and the rows done with P V(i - 1)
+                ok = ok && wait_or_abort(p_ready, i & 1, abort, error_flag, 27);
+                if (i >= 1) ok = ok && wait_or_abort(pv_free, (i - 1) & 1, abort, error_flag, 28);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t sp = smem_u32(sP), sv = smem_u32(sKV + (size_t)buf * 2 * TA_KV_BYTES) + TA_KV_BYTES;
+#pragma unroll
+                for (int kk = 0; kk < TA_BN / 16; ++kk)
+                    umma_bf16(tmem_base + TA_BN, umma_desc(sp) + 2 * kk, umma_desc_mn(sv + kk * 2048, TA_BN * 128), idesc_pv, kk > 0 ? 1u : 0u);
+                umma_commit(pv_done);
+                umma_commit(&kv_free[buf]);
             }
         }
-    };
-
-    float o[D];
+    } else {
+        // ---- the rows: thread t owns query row t ----
+        const int row_t = threadIdx.x;
+        const int qp = q_first + row_t;
+        const int lo_t = window > 0 ? max(0, qp - window + 1) : 0;
+        const float sl2 = scale * 1.4426950408889634f;
+        const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
+        float o[D];
 #pragma unroll
-    for (int i = 0; i < D; ++i) o[i] = 0.0f;
-    float m_run = -INFINITY, l_run = 0.0f;
-    bool ok = true;
-
-    if (active && threadIdx.x == 0) {
-        mbar_expect_tx(q_full, TA_Q_BYTES);
-#pragma unroll
-        for (int hf = 0; hf < NH; ++hf) tma_load_2d(sQ + hf * (TA_BM * 128), &map_q, h * D + hf * 64, tok0 + qt * TA_BM, q_full);
-        load_kv(kb_first, 0);
-    }
-    for (int kb = kb_first, i = 0; kb <= kb_last; ++kb, ++i) {
-        const int buf = i & 1;
-        const uint32_t sk = smem_u32(sKV + (size_t)buf * 2 * TA_KV_BYTES), sv = sk + TA_KV_BYTES;
-        if (threadIdx.x == 0) {
-            if (kb < kb_last) load_kv(kb + 1, buf ^ 1);    // that buffer's last reader (the PV product two blocks ago) is done
-            if (i == 0 && !mbar_wait(q_full, 0)) { atomicExch(error_flag, 21); ok = false; }
-            if (ok && !mbar_wait(&kv_full[buf], (i >> 1) & 1)) { atomicExch(error_flag, 22); ok = false; }
+        for (int i = 0; i < D; ++i) o[i] = 0.0f;
+        float m_run = -INFINITY, l_run = 0.0f;
+        bool ok = true;
+        for (int i = 0; i < nblk; ++i) {
+            const int key0 = (kb_first + i) * TA_BN;
+            ok = ok && wait_or_abort(s_done, i & 1, abort, error_flag, 23);
+            ok = __all_sync(0xffffffffu, ok);              // tcgen05.ld is warp-wide: the warp takes one path
+            if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t sq = smem_u32(sQ);
+            // two passes over the 64 scores, 32 at a time (tensor memory is cheap to read twice; registers are not):
+            // the row maximum first, then the probabilities
+            const bool interior = key0 + TA_BN - 1 <= q_first && (window <= 0 || key0 >= q_last - window + 1);
+            float mx = -INFINITY;
 #pragma unroll
-            for (int kk = 0; kk < D / 16; ++kk) {
-                const uint64_t adesc = umma_desc(sq + (kk / 4) * (TA_BM * 128)) + 2 * (kk % 4);
-                const uint64_t bdesc = umma_desc(sk + (kk / 4) * (TA_BN * 128)) + 2 * (kk % 4);
-                umma_bf16(tmem_base, adesc, bdesc, idesc_s, kk > 0 ? 1u : 0u);
+            for (int hf = 0; hf < 2; ++hf) {
+                float s[32];
+                tmem_ld32(lane_base + hf * 32, s);
+                if (!interior) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (!(key0 + hf * 32 + j <= qp && key0 + hf * 32 + j >= lo_t)) s[j] = -INFINITY;
+                }
+#pragma unroll
+                for (int j = 0; j < 32; ++j) mx = fmaxf(mx, s[j]);
             }
-            umma_commit(s_done);
-        }
-        // ---- softmax of this thread's row ----
-        if (!mbar_wait(s_done, i & 1)) { if (lane == 0) atomicExch(error_flag, 23); ok = false; }
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        float s[TA_BN];
-        tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16), s);
-        tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + 32, s + 32);
-        const int key0 = kb * TA_BN;
-        const bool interior = key0 + TA_BN - 1 <= q_first && (window <= 0 || key0 >= q_last - window + 1);
-        if (!interior) {
+            const float m_new = fmaxf(m_run, mx * sl2);
+            const float base = m_new == -INFINITY ? 0.0f : m_new;
+            const float corr = ta_exp2(m_run - base);
+            m_run = m_new;
+            float sum = 0.0f;
+            // P(i - 1) was consumed before it is overwritten: P V(i - 1) was done when pv_done(i - 1) fired, which this
+            // thread waited for at the end of the last iteration.
+            uint4* prow = reinterpret_cast<uint4*>(sP + row_t * 128);
 #pragma unroll
-            for (int j = 0; j < TA_BN; ++j)
-                if (!(key0 + j <= qp && key0 + j >= lo_t)) s[j] = -INFINITY;
-        }
-        float mx = -INFINITY;
+            for (int hf = 0; hf < 2; ++hf) {
+                float s[32];
+                tmem_ld32(lane_base + hf * 32, s);
+                if (hf == 1) {                                  // the scores are in registers: S(i + 1) may overwrite them
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_one(s_free);
+                }
+                if (!interior) {
 #pragma unroll
-        for (int j = 0; j < TA_BN; ++j) mx = fmaxf(mx, s[j]);
-        const float m_new = fmaxf(m_run, mx * sl2);
-        const float base = m_new == -INFINITY ? 0.0f : m_new;
-        const float corr = ta_exp2(m_run - base);
-        m_run = m_new;
-        float sum = 0.0f;
-        uint4* prow = reinterpret_cast<uint4*>(sP + row_t * 128);
+                    for (int j = 0; j < 32; ++j)
+                        if (!(key0 + hf * 32 + j <= qp && key0 + hf * 32 + j >= lo_t)) s[j] = -INFINITY;
+                }
 #pragma unroll
-        for (int c = 0; c < TA_BN / 8; ++c) {
-            float p[8];
+                for (int c = 0; c < 4; ++c) {
+                    float p[8];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) { p[e] = ta_exp2(fmaf(s[c * 8 + e], sl2, -base)); sum += p[e]; }
-            uint4 packed;
-            __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&packed);
+                    for (int e = 0; e < 8; ++e) { p[e] = ta_exp2(fmaf(s[c * 8 + e], sl2, -base)); sum += p[e]; }
+                    uint4 packed;
+                    __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&packed);
 #pragma unroll
-            for (int e = 0; e < 4; ++e) p2[e] = __floats2bfloat162_rn(p[2 * e], p[2 * e + 1]);
-            prow[c ^ (row_t & 7)] = packed;                 // the 128-byte swizzle: 16-byte piece index xor (row mod 8)
-        }
-        l_run = l_run * corr + sum;
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // P was written by ordinary stores; the MMA reads it through the async proxy
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        if (__syncthreads_or(!ok)) break;                   // a wait gave up somewhere: everyone leaves together
-        if (threadIdx.x == 0) {
+                    for (int e = 0; e < 4; ++e) p2[e] = __floats2bfloat162_rn(p[2 * e], p[2 * e + 1]);
+                    prow[(hf * 4 + c) ^ (row_t & 7)] = packed;   // the 128-byte swizzle: 16-byte piece index xor (row mod 8)
+                }
+            }
+            l_run = l_run * corr + sum;
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // ordinary stores, read by the MMA through the async proxy
+            __syncwarp();
+            if (lane == 0) mbar_arrive_one(p_ready);
+            ok = wait_or_abort(pv_done, i & 1, abort, error_flag, 24);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t sp = smem_u32(sP);
 #pragma unroll
-            for (int kk = 0; kk < TA_BN / 16; ++kk) {
-                const uint64_t adesc = umma_desc(sp) + 2 * kk;
-                const uint64_t bdesc = umma_desc_mn(sv + kk * 2048, TA_BN * 128);
-                umma_bf16(tmem_base + TA_BN, adesc, bdesc, idesc_pv, kk > 0 ? 1u : 0u);
+            for (int c = 0; c < D / 32; ++c) {
+                float pv[32];
+                tmem_ld32(lane_base + TA_BN + c * 32, pv);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) o[c * 32 + j] = fmaf(o[c * 32 + j], corr, pv[j]);
             }
-            umma_commit(pv_done);
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive_one(pv_free);
         }
-        if (!mbar_wait(pv_done, i & 1)) { if (lane == 0) atomicExch(error_flag, 24); ok = false; }
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (ok && row_t < rows) {
+            const float inv = 1.0f / l_run;
+            bf16* dst = out + ((size_t)(tok0 + qt * TA_BM + row_t) * H + h) * D;
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-            float pv[32];
-            tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + TA_BN + c * 32, pv);
+            for (int c = 0; c < D / 8; ++c) {
+                uint4 packed;
+                __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&packed);
 #pragma unroll
-            for (int j = 0; j < 32; ++j) o[c * 32 + j] = fmaf(o[c * 32 + j], corr, pv[j]);
-        }
-    }
-    if (active && row_t < rows) {
-        const float inv = 1.0f / l_run;
-        bf16* dst = out + ((size_t)(tok0 + qt * TA_BM + row_t) * H + h) * D;
-#pragma unroll
-        for (int c = 0; c < D / 8; ++c) {
-            uint4 packed;
-            __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&packed);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) p2[e] = __floats2bfloat162_rn(o[c * 8 + 2 * e] * inv, o[c * 8 + 2 * e + 1] * inv);
-            reinterpret_cast<uint4*>(dst)[c] = packed;
+                for (int e = 0; e < 4; ++e) p2[e] = __floats2bfloat162_rn(o[c * 8 + 2 * e] * inv, o[c * 8 + 2 * e + 1] * inv);
+                reinterpret_cast<uint4*>(dst)[c] = packed;
+            }
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -277,6 +352,6 @@ MB_API int mb_attn_prefill_tc(const void* q, const void* k_cache, const void* v_
     rc = map_2d(&mv, v_cache, cache_rows, D, 16);
     if (rc) return rc;
     dim3 grid((max_query_len + TA_BM - 1) / TA_BM, K * GROUP, requests);
-    return launch_kernel(attn_prefill_tc_kernel, grid, 128, TA_SMEM, s, 0, mq, mk, mv, (bf16*)out, block_table, max_pages, cu_tokens,
+    return launch_kernel(attn_prefill_tc_kernel, grid, 160, TA_SMEM, s, 0, mq, mk, mv, (bf16*)out, block_table, max_pages, cu_tokens,
                          seq_lens, first_req, K, page_shift, scale, window, error_flag);
 }
