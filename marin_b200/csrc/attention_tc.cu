@@ -7,8 +7,10 @@
 //                  running maximum and sum in float32 (exp2 domain) — no shuffles — and writes P in bf16 to shared
 //                  memory in the swizzled K-major layout the next MMA reads;
 //   PV             tcgen05.mma, M = 128, N = HEAD_DIM, K = 64 keys; V stays as it lies in the cache ([key][d], d
-//                  contiguous), i.e. an MN-major B operand; the product lands in HEAD_DIM more TMEM columns and each
-//                  thread folds it into its own float32 output row: o = o * correction + PV.
+//                  contiguous), i.e. an MN-major B operand; the product accumulates in HEAD_DIM more TMEM columns.  The
+//                  running maximum a row's O is scaled by is only raised when the true maximum has moved by more than
+//                  8 (a factor 256, harmless in float32): then the row's O is read, rescaled and written back
+//                  (tcgen05.ld/st); otherwise O is never touched until the end.
 // K and V blocks arrive by TMA straight from the paged cache (one 16-key box per page piece and 64-column half) into
 // two buffers, so the next block is on its way while this one is used.  Two CTAs fit an SM: one's softmax overlaps the
 // other's MMAs.  Needs pages of at least 16 positions.  Waits are bounded and record a code in *error_flag.
@@ -33,7 +35,8 @@ static_assert(HEAD_DIM == 64 || HEAD_DIM == 128, "the tcgen05 attention kernel t
 #define TA_KV_BYTES (NH * TA_BN * 128)  // one of K or V, one buffer
 #define TA_P_BYTES (TA_BM * 128)
 #define TA_SMEM (TA_Q_BYTES + 4 * TA_KV_BYTES + TA_P_BYTES + 256)
-#define TA_TMEM_COLS 256               // S: 64 columns, PV: HEAD_DIM columns
+#define TA_TMEM_COLS 256               // two S buffers of 64 columns, then O: HEAD_DIM columns
+#define TA_O_COL (2 * TA_BN)
 
 __device__ __forceinline__ float ta_exp2(float x) {
     float y;
@@ -69,6 +72,7 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort, int* error_flag, int code) {
     const uint32_t addr = smem_u32(bar);
     const long long start = clock64();
+    unsigned polls = 0;
     for (;;) {
         uint32_t done;
         asm volatile(
@@ -79,9 +83,24 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, vo
             : "r"(addr), "r"(parity)
             : "memory");
         if (done) return true;
-        if (*abort) return false;
-        if (clock64() - start > TC_WAIT_LIMIT) { *abort = 1; atomicExch(error_flag, code); return false; }
+        if ((++polls & 31) == 0) {
+            if (*abort) return false;
+            if (clock64() - start > TC_WAIT_LIMIT) { *abort = 1; atomicExch(error_flag, code); return false; }
+        }
     }
+}
+
+// Has the phase with this parity completed?  Does not block.
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return done != 0;
 }
 
 __device__ __forceinline__ void mbar_arrive_one(uint64_t* bar) {
@@ -89,6 +108,22 @@ __device__ __forceinline__ void mbar_arrive_one(uint64_t* bar) {
 }
 
 // 160 threads: warps 0..3 own the 128 query rows (softmax, output); warp 4 asks for keys and values and issues the MMAs.
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+          "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+          "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+          "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+          "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+          "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+          "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
+          "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
 __global__ void __launch_bounds__(160, 2) attn_prefill_tc_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
     bf16* __restrict__ out, const int* __restrict__ block_table, int max_pages, const int* __restrict__ cu_tokens,
@@ -101,12 +136,11 @@ __global__ void __launch_bounds__(160, 2) attn_prefill_tc_kernel(
     uint64_t* q_full = bars;              // Q tile has landed
     uint64_t* kv_full = bars + 1;         // [2] a block of K and V has landed
     uint64_t* kv_free = bars + 3;         // [2] the MMAs that read the buffer are done
-    uint64_t* s_done = bars + 5;          // S = Q K^T is in tensor memory
-    uint64_t* s_free = bars + 6;          // every row has read its scores (4 warps arrive)
-    uint64_t* p_ready = bars + 7;         // P is in shared memory (4 warps arrive)
-    uint64_t* pv_done = bars + 8;         // P V is in tensor memory
-    uint64_t* pv_free = bars + 9;         // every row has read its part of P V (4 warps arrive)
-    uint32_t* tmem_slot = (uint32_t*)(bars + 10);
+    uint64_t* s_done = bars + 5;          // [2] S = Q K^T is in its tensor-memory buffer
+    uint64_t* s_free = bars + 7;          // [2] every row has read its scores from the buffer (4 warps arrive)
+    uint64_t* p_ready = bars + 9;         // P is in shared memory (4 warps arrive)
+    uint64_t* pv_done = bars + 10;        // O += P V has been added
+    uint32_t* tmem_slot = (uint32_t*)(bars + 11);
     volatile int* abort = (volatile int*)(tmem_slot + 1);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     pdl_wait();
@@ -121,7 +155,8 @@ __global__ void __launch_bounds__(160, 2) attn_prefill_tc_kernel(
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
         for (int b = 0; b < 2; ++b) { mbar_init(&kv_full[b], 1); mbar_init(&kv_free[b], 1); }
-        mbar_init(s_done, 1); mbar_init(s_free, 4); mbar_init(p_ready, 4); mbar_init(pv_done, 1); mbar_init(pv_free, 4);
+        for (int b = 0; b < 2; ++b) { mbar_init(&s_done[b], 1); mbar_init(&s_free[b], 4); }
+        mbar_init(p_ready, 4); mbar_init(pv_done, 1);
         *abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -162,16 +197,16 @@ __global__ void __launch_bounds__(160, 2) attn_prefill_tc_kernel(
                     }
                 }
             };
-            auto issue_s = [&](int i) {                     // S(i) = Q K(i)^T into TMEM columns [0, 64)
+            auto issue_s = [&](int i) {                     // S(i) = Q K(i)^T into S buffer i & 1
                 const uint32_t sq = smem_u32(sQ), sk = smem_u32(sKV + (size_t)(i & 1) * 2 * TA_KV_BYTES);
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
                     const uint64_t adesc = umma_desc(sq + (kk / 4) * (TA_BM * 128)) + 2 * (kk % 4);
                     const uint64_t bdesc = umma_desc(sk + (kk / 4) * (TA_BN * 128)) + 2 * (kk % 4);
-                    umma_bf16(tmem_base, adesc, bdesc, idesc_s, kk > 0 ? 1u : 0u);
+                    umma_bf16(tmem_base + (uint32_t)((i & 1) * TA_BN), adesc, bdesc, idesc_s, kk > 0 ? 1u : 0u);
                 }
-                umma_commit(s_done);
+                umma_commit(&s_done[i & 1]);
             };
             mbar_expect_tx(q_full, TA_Q_BYTES);
 #pragma unroll
@@ -179,28 +214,44 @@ __global__ void __launch_bounds__(160, 2) attn_prefill_tc_kernel(
             load_kv(kb_first, 0);
             bool ok = wait_or_abort(q_full, 0, abort, error_flag, 21) && wait_or_abort(&kv_full[0], 0, abort, error_flag, 22);
             if (ok) issue_s(0);
-            for (int i = 0; i < nblk && ok; ++i) {
-                const int buf = i & 1;
-                if (i + 1 < nblk) {
-                    // the other buffer was read by the MMAs of block i - 1
-                    if (i >= 1) ok = ok && wait_or_abort(&kv_free[buf ^ 1], ((i - 1) >> 1) & 1, abort, error_flag, 25);
-                    if (ok) load_kv(kb_first + i + 1, buf ^ 1);
-                    // S(i + 1) can start as soon as every row has read S(i)
-                    ok = ok && wait_or_abort(&kv_full[buf ^ 1], ((i + 1) >> 1) & 1, abort, error_flag, 22);
-                    ok = ok && wait_or_abort(s_free, i & 1, abort, error_flag, 26);
-                    if (ok) issue_s(i + 1);
+            // From here on the issuer does whichever of three things is possible next, never blocking on one while
+            // another is ready: ask for the next block of K and V (its buffer held block i - 2), start S of the next
+            // block (its K has landed, the rows are done with that S buffer), add P V of the oldest block whose P is
+            // in shared memory.
+            int next_load = 1, next_s = 1, next_pv = 0;
+            unsigned idle = 0;
+            const long long start = clock64();
+            while (ok && next_pv < nblk) {
+                bool progressed = false;
+                if (next_load < nblk && (next_load < 2 || mbar_test(&kv_free[next_load & 1], ((next_load - 2) >> 1) & 1))) {
+                    load_kv(kb_first + next_load, next_load & 1);
+                    ++next_load;
+                    progressed = true;
                 }
-                // P V(i) into TMEM columns [64, 64 + D): needs P(i) in shared memory and the rows done with P V(i - 1)
-                ok = ok && wait_or_abort(p_ready, i & 1, abort, error_flag, 27);
-                if (i >= 1) ok = ok && wait_or_abort(pv_free, (i - 1) & 1, abort, error_flag, 28);
-                if (!ok) break;
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t sp = smem_u32(sP), sv = smem_u32(sKV + (size_t)buf * 2 * TA_KV_BYTES) + TA_KV_BYTES;
+                if (next_s < next_load && mbar_test(&kv_full[next_s & 1], (next_s >> 1) & 1) &&
+                    (next_s < 2 || mbar_test(&s_free[next_s & 1], ((next_s - 2) >> 1) & 1))) {
+                    issue_s(next_s);
+                    ++next_s;
+                    progressed = true;
+                }
+                if (mbar_test(p_ready, next_pv & 1)) {
+                    // O += P(i) V(i) in TMEM columns [128, 128 + D); any rescaling of O by the rows happened before they arrived
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const int buf = next_pv & 1;
+                    const uint32_t sp = smem_u32(sP), sv = smem_u32(sKV + (size_t)buf * 2 * TA_KV_BYTES) + TA_KV_BYTES;
 #pragma unroll
-                for (int kk = 0; kk < TA_BN / 16; ++kk)
-                    umma_bf16(tmem_base + TA_BN, umma_desc(sp) + 2 * kk, umma_desc_mn(sv + kk * 2048, TA_BN * 128), idesc_pv, kk > 0 ? 1u : 0u);
-                umma_commit(pv_done);
-                umma_commit(&kv_free[buf]);
+                    for (int kk = 0; kk < TA_BN / 16; ++kk)
+                        umma_bf16(tmem_base + TA_O_COL, umma_desc(sp) + 2 * kk, umma_desc_mn(sv + kk * 2048, TA_BN * 128), idesc_pv,
+                                  (next_pv > 0 || kk > 0) ? 1u : 0u);
+                    umma_commit(pv_done);
+                    umma_commit(&kv_free[buf]);
+                    ++next_pv;
+                    progressed = true;
+                }
+                if (!progressed && (++idle & 63) == 0) {
+                    if (*abort) ok = false;
+                    else if (clock64() - start > 8 * TC_WAIT_LIMIT) { *abort = 1; atomicExch(error_flag, 29); ok = false; }
+                }
             }
         }
     } else {
@@ -210,14 +261,12 @@ __global__ void __launch_bounds__(160, 2) attn_prefill_tc_kernel(
         const int lo_t = window > 0 ? max(0, qp - window + 1) : 0;
         const float sl2 = scale * 1.4426950408889634f;
         const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
-        float o[D];
-#pragma unroll
-        for (int i = 0; i < D; ++i) o[i] = 0.0f;
-        float m_run = -INFINITY, l_run = 0.0f;
+        float m_used = -INFINITY, l_run = 0.0f;           // the maximum O and l are currently scaled by (log2 units)
         bool ok = true;
         for (int i = 0; i < nblk; ++i) {
             const int key0 = (kb_first + i) * TA_BN;
-            ok = ok && wait_or_abort(s_done, i & 1, abort, error_flag, 23);
+            const uint32_t s_col = lane_base + (uint32_t)((i & 1) * TA_BN);
+            ok = ok && wait_or_abort(&s_done[i & 1], (i >> 1) & 1, abort, error_flag, 23);
             ok = __all_sync(0xffffffffu, ok);              // tcgen05.ld is warp-wide: the warp takes one path
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -228,7 +277,7 @@ __global__ void __launch_bounds__(160, 2) attn_prefill_tc_kernel(
 #pragma unroll
             for (int hf = 0; hf < 2; ++hf) {
                 float s[32];
-                tmem_ld32(lane_base + hf * 32, s);
+                tmem_ld32(s_col + hf * 32, s);
                 if (!interior) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j)
@@ -237,22 +286,40 @@ __global__ void __launch_bounds__(160, 2) attn_prefill_tc_kernel(
 #pragma unroll
                 for (int j = 0; j < 32; ++j) mx = fmaxf(mx, s[j]);
             }
-            const float m_new = fmaxf(m_run, mx * sl2);
-            const float base = m_new == -INFINITY ? 0.0f : m_new;
-            const float corr = ta_exp2(m_run - base);
-            m_run = m_new;
+            // raise the scaling maximum only when the true one has moved by more than 8 (or from -inf)
+            const float m_true = fmaxf(m_used, mx * sl2);
+            const bool raise = m_true > m_used + 8.0f || (m_used == -INFINITY && m_true != -INFINITY);
+            const float m_new = raise ? m_true : m_used;
+            const float corr = raise ? ta_exp2(m_used - m_new) : 1.0f;      // exp2(-inf) = 0 on the first raise
+            bool pv_waited = i == 0;
+            if (__any_sync(0xffffffffu, raise) && i >= 1) {
+                // O is being added to by the MMAs of block i - 1 until pv_done(i - 1)
+                ok = wait_or_abort(pv_done, (i - 1) & 1, abort, error_flag, 24);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                pv_waited = true;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                for (int c = 0; c < D / 32; ++c) {
+                    float ov[32];
+                    tmem_ld32(lane_base + TA_O_COL + c * 32, ov);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) ov[j] *= corr;
+                    tmem_st32(lane_base + TA_O_COL + c * 32, ov);
+                }
+            }
+            m_used = m_new;
+            const float base = m_used == -INFINITY ? 0.0f : m_used;
             float sum = 0.0f;
-            // P(i - 1) was consumed before it is overwritten: P V(i - 1) was done when pv_done(i - 1) fired, which this
-            // thread waited for at the end of the last iteration.
-            uint4* prow = reinterpret_cast<uint4*>(sP + row_t * 128);
+            uint4 packed[TA_BN / 8];                           // the row of P, kept until the last block's P has been consumed
 #pragma unroll
             for (int hf = 0; hf < 2; ++hf) {
                 float s[32];
-                tmem_ld32(lane_base + hf * 32, s);
-                if (hf == 1) {                                  // the scores are in registers: S(i + 1) may overwrite them
+                tmem_ld32(s_col + hf * 32, s);
+                if (hf == 1) {                                  // the scores are in registers: this S buffer may be overwritten
                     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                     __syncwarp();
-                    if (lane == 0) mbar_arrive_one(s_free);
+                    if (lane == 0) mbar_arrive_one(&s_free[i & 1]);
                 }
                 if (!interior) {
 #pragma unroll
@@ -264,42 +331,47 @@ __global__ void __launch_bounds__(160, 2) attn_prefill_tc_kernel(
                     float p[8];
 #pragma unroll
                     for (int e = 0; e < 8; ++e) { p[e] = ta_exp2(fmaf(s[c * 8 + e], sl2, -base)); sum += p[e]; }
-                    uint4 packed;
-                    __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&packed);
+                    __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&packed[hf * 4 + c]);
 #pragma unroll
                     for (int e = 0; e < 4; ++e) p2[e] = __floats2bfloat162_rn(p[2 * e], p[2 * e + 1]);
-                    prow[(hf * 4 + c) ^ (row_t & 7)] = packed;   // the 128-byte swizzle: 16-byte piece index xor (row mod 8)
                 }
             }
             l_run = l_run * corr + sum;
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // ordinary stores, read by the MMA through the async proxy
-            __syncwarp();
-            if (lane == 0) mbar_arrive_one(p_ready);
-            ok = wait_or_abort(pv_done, i & 1, abort, error_flag, 24);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-            for (int c = 0; c < D / 32; ++c) {
-                float pv[32];
-                tmem_ld32(lane_base + TA_BN + c * 32, pv);
-#pragma unroll
-                for (int j = 0; j < 32; ++j) o[c * 32 + j] = fmaf(o[c * 32 + j], corr, pv[j]);
+            if (!pv_waited) {                                   // P(i - 1) is read by the MMAs of block i - 1 until pv_done(i - 1)
+                ok = wait_or_abort(pv_done, (i - 1) & 1, abort, error_flag, 24);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
             }
+            uint4* prow = reinterpret_cast<uint4*>(sP + row_t * 128);
+#pragma unroll
+            for (int c = 0; c < TA_BN / 8; ++c) prow[c ^ (row_t & 7)] = packed[c];   // 128-byte swizzle: piece index xor (row mod 8)
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // ordinary stores, read by the MMA through the async proxy
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
-            if (lane == 0) mbar_arrive_one(pv_free);
+            if (lane == 0) mbar_arrive_one(p_ready);
         }
-        if (ok && row_t < rows) {
+        if (ok) {
+            ok = wait_or_abort(pv_done, (nblk - 1) & 1, abort, error_flag, 24);
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        if (ok) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const float inv = 1.0f / l_run;
             bf16* dst = out + ((size_t)(tok0 + qt * TA_BM + row_t) * H + h) * D;
 #pragma unroll
-            for (int c = 0; c < D / 8; ++c) {
-                uint4 packed;
-                __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&packed);
+            for (int c = 0; c < D / 32; ++c) {
+                float ov[32];
+                tmem_ld32(lane_base + TA_O_COL + c * 32, ov);
+                if (row_t < rows) {
 #pragma unroll
-                for (int e = 0; e < 4; ++e) p2[e] = __floats2bfloat162_rn(o[c * 8 + 2 * e] * inv, o[c * 8 + 2 * e + 1] * inv);
-                reinterpret_cast<uint4*>(dst)[c] = packed;
+                    for (int q8 = 0; q8 < 4; ++q8) {
+                        uint4 packed;
+                        __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) p2[e] = __floats2bfloat162_rn(ov[q8 * 8 + 2 * e] * inv, ov[q8 * 8 + 2 * e + 1] * inv);
+                        reinterpret_cast<uint4*>(dst)[c * 4 + q8] = packed;
+                    }
+                }
             }
         }
     }
