@@ -12,7 +12,7 @@
 //                  8 (a factor 256, harmless in float32): then the row's O is read, rescaled and written back
 //                  (tcgen05.ld/st); otherwise O is never touched until the end.
 // K and V blocks arrive by TMA straight from the paged cache (one 16-key box per page piece and 64-column half) into
-// two buffers, so the next block is on its way while this one is used.  Two CTAs fit an SM: one's softmax overlaps the
+// two buffers each; keys run two blocks ahead of the rows, values one.  Two CTAs fit an SM: one's softmax overlaps the
 // other's MMAs.  Needs pages of at least 16 positions.  Waits are bounded and record a code in *error_flag.
 // The mma.sync kernel in attention_fast.cu is the fallback and the plain twin (the reference's counterpart:
 // crates/cuda/src/attention_mma.cu:43-180).
@@ -127,20 +127,22 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
 __global__ void __launch_bounds__(160, 2) attn_prefill_tc_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
     bf16* __restrict__ out, const int* __restrict__ block_table, int max_pages, const int* __restrict__ cu_tokens,
-    const int* __restrict__ seq_lens, int first_req, int K, int page_shift, float scale, int window, int* __restrict__ error_flag) {
+    const int* __restrict__ seq_lens, int first_req, int K, int page_shift, float scale, int window, int* __restrict__ error_flag,
+    int box_rows) {
     extern __shared__ __align__(1024) uint8_t smem[];     // the swizzled tiles need 1024-byte alignment (checked below)
     uint8_t* sQ = smem;
     uint8_t* sKV = sQ + TA_Q_BYTES;                       // [buffer][K then V][half][64 rows][128 B]
     uint8_t* sP = sKV + 4 * TA_KV_BYTES;
     uint64_t* bars = (uint64_t*)(sP + TA_P_BYTES);
     uint64_t* q_full = bars;              // Q tile has landed
-    uint64_t* kv_full = bars + 1;         // [2] a block of K and V has landed
-    uint64_t* kv_free = bars + 3;         // [2] the MMAs that read the buffer are done
-    uint64_t* s_done = bars + 5;          // [2] S = Q K^T is in its tensor-memory buffer
-    uint64_t* s_free = bars + 7;          // [2] every row has read its scores from the buffer (4 warps arrive)
-    uint64_t* p_ready = bars + 9;         // P is in shared memory (4 warps arrive)
-    uint64_t* pv_done = bars + 10;        // O += P V has been added
-    uint32_t* tmem_slot = (uint32_t*)(bars + 11);
+    uint64_t* k_full = bars + 1;          // [2] a block of K has landed
+    uint64_t* v_full = bars + 3;          // [2] a block of V has landed
+    uint64_t* v_free = bars + 5;          // [2] the P V product that read the V buffer is done
+    uint64_t* s_done = bars + 7;          // [2] S = Q K^T is in its tensor-memory buffer (and its K buffer is free again)
+    uint64_t* s_free = bars + 9;          // [2] every row has read its scores from the buffer (4 warps arrive)
+    uint64_t* p_ready = bars + 11;        // P is in shared memory (4 warps arrive)
+    uint64_t* pv_done = bars + 12;        // O += P V has been added
+    uint32_t* tmem_slot = (uint32_t*)(bars + 13);
     volatile int* abort = (volatile int*)(tmem_slot + 1);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     pdl_wait();
@@ -154,7 +156,7 @@ __global__ void __launch_bounds__(160, 2) attn_prefill_tc_kernel(
     const int rows = min(TA_BM, n - qt * TA_BM);
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
-        for (int b = 0; b < 2; ++b) { mbar_init(&kv_full[b], 1); mbar_init(&kv_free[b], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&k_full[b], 1); mbar_init(&v_full[b], 1); mbar_init(&v_free[b], 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(&s_done[b], 1); mbar_init(&s_free[b], 4); }
         mbar_init(p_ready, 4); mbar_init(pv_done, 1);
         *abort = 0;
@@ -174,30 +176,37 @@ __global__ void __launch_bounds__(160, 2) attn_prefill_tc_kernel(
     const int kh = h / GROUP;
     const int kb_first = k_lo / TA_BN, kb_last = q_last / TA_BN;
     const int nblk = kb_last - kb_first + 1;
+    // The online softmax does not care about the order of the key blocks.  Every CTA starts at another block, so that
+    // the many CTAs that read the same keys and values (the query tiles of a request, the heads of a group) do not
+    // all ask the L2 for the same lines at the same moment.
+    const int rot = (int)(((unsigned)(h * gridDim.x + qt) * 37u) % (unsigned)nblk);
+    auto block_of = [&](int i) { const int j = i + rot; return kb_first + (j >= nblk ? j - nblk : j); };
 
     if (warp == 4) {
-        if (lane == 0) {
-            // ---- the issuer: TMA for Q, K, V and all MMAs ----
+        {
+            // ---- the issuer warp: lane 0 starts the MMAs and arms the barriers; lanes 0..3 each ask for one box of a
+            // block of K or V, so that one instruction starts four TMA copies ----
             const int* table = block_table + (size_t)r * max_pages;
             const int page_mask = (1 << page_shift) - 1;
             constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TA_BN >> 3) << 17) | ((uint32_t)(TA_BM >> 4) << 24);
             constexpr uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(TA_BM >> 4) << 24);
-            auto load_kv = [&](int kb, int buf) {           // 16-key boxes, one per page piece and 64-column half
-                uint8_t* dk = sKV + (size_t)buf * 2 * TA_KV_BYTES;
-                uint8_t* dv = dk + TA_KV_BYTES;
-                mbar_expect_tx(&kv_full[buf], 2 * TA_KV_BYTES);
-#pragma unroll
-                for (int g = 0; g < TA_BN / 16; ++g) {
-                    const int key = kb * TA_BN + g * 16;
+            // one block of keys, or of values: 16-key boxes, one per page piece and 64-column half
+            auto load_block = [&](const CUtensorMap* map, uint8_t* dst, uint64_t* bar, int kb) {
+                if (lane == 0) mbar_expect_tx(bar, TA_KV_BYTES);
+                __syncwarp();
+                const int g = lane * box_rows;                  // box_rows keys per box: 16, 32 or 64 (at most a page)
+                if (g < TA_BN) {
+                    const int key = kb * TA_BN + g;
                     const int row = (int)((((size_t)table[key >> page_shift] * K + kh) << page_shift) + (size_t)(key & page_mask));
 #pragma unroll
-                    for (int hf = 0; hf < NH; ++hf) {
-                        tma_load_2d(dk + hf * (TA_BN * 128) + g * 2048, &map_k, hf * 64, row, &kv_full[buf]);
-                        tma_load_2d(dv + hf * (TA_BN * 128) + g * 2048, &map_v, hf * 64, row, &kv_full[buf]);
-                    }
+                    for (int hf = 0; hf < NH; ++hf) tma_load_2d(dst + hf * (TA_BN * 128) + g * 128, map, hf * 64, row, bar);
                 }
+                __syncwarp();
             };
+            auto load_k = [&](int j) { load_block(&map_k, sKV + (size_t)(j & 1) * 2 * TA_KV_BYTES, &k_full[j & 1], block_of(j)); };
+            auto load_v = [&](int j) { load_block(&map_v, sKV + (size_t)(j & 1) * 2 * TA_KV_BYTES + TA_KV_BYTES, &v_full[j & 1], block_of(j)); };
             auto issue_s = [&](int i) {                     // S(i) = Q K(i)^T into S buffer i & 1
+                if (lane != 0) return;
                 const uint32_t sq = smem_u32(sQ), sk = smem_u32(sKV + (size_t)(i & 1) * 2 * TA_KV_BYTES);
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
@@ -208,49 +217,61 @@ __global__ void __launch_bounds__(160, 2) attn_prefill_tc_kernel(
                 }
                 umma_commit(&s_done[i & 1]);
             };
-            mbar_expect_tx(q_full, TA_Q_BYTES);
+            if (lane == 0) {
+                mbar_expect_tx(q_full, TA_Q_BYTES);
 #pragma unroll
-            for (int hf = 0; hf < NH; ++hf) tma_load_2d(sQ + hf * (TA_BM * 128), &map_q, h * D + hf * 64, tok0 + qt * TA_BM, q_full);
-            load_kv(kb_first, 0);
-            bool ok = wait_or_abort(q_full, 0, abort, error_flag, 21) && wait_or_abort(&kv_full[0], 0, abort, error_flag, 22);
+                for (int hf = 0; hf < NH; ++hf) tma_load_2d(sQ + hf * (TA_BM * 128), &map_q, h * D + hf * 64, tok0 + qt * TA_BM, q_full);
+            }
+            load_k(0);
+            load_v(0);
+            bool ok = wait_or_abort(q_full, 0, abort, error_flag, 21) && wait_or_abort(&k_full[0], 0, abort, error_flag, 22);
+            ok = __all_sync(0xffffffffu, ok);
             if (ok) issue_s(0);
-            // From here on the issuer does whichever of three things is possible next, never blocking on one while
-            // another is ready: ask for the next block of K and V (its buffer held block i - 2), start S of the next
-            // block (its K has landed, the rows are done with that S buffer), add P V of the oldest block whose P is
-            // in shared memory.
-            int next_load = 1, next_s = 1, next_pv = 0;
+            // From here on the issuer does whichever of these is possible next, never blocking on one while another is
+            // ready: ask for the next block of K (its buffer is free once S of two blocks ago is done: keys run two
+            // blocks ahead), ask for the next block of V (free once P V of two blocks ago is done), start S of the next
+            // block (K landed, the rows done with that S buffer), add P V of the oldest block whose P is in shared memory.
+            int next_k = 1, next_v = 1, next_s = 1, next_pv = 0;
             unsigned idle = 0;
             const long long start = clock64();
             while (ok && next_pv < nblk) {
                 bool progressed = false;
-                if (next_load < nblk && (next_load < 2 || mbar_test(&kv_free[next_load & 1], ((next_load - 2) >> 1) & 1))) {
-                    load_kv(kb_first + next_load, next_load & 1);
-                    ++next_load;
+                if (__shfl_sync(0xffffffffu, (int)(next_k < nblk && (next_k < 2 || mbar_test(&s_done[next_k & 1], ((next_k - 2) >> 1) & 1))), 0)) {
+                    load_k(next_k);
+                    ++next_k;
                     progressed = true;
                 }
-                if (next_s < next_load && mbar_test(&kv_full[next_s & 1], (next_s >> 1) & 1) &&
-                    (next_s < 2 || mbar_test(&s_free[next_s & 1], ((next_s - 2) >> 1) & 1))) {
+                if (__shfl_sync(0xffffffffu, (int)(next_v < nblk && (next_v < 2 || mbar_test(&v_free[next_v & 1], ((next_v - 2) >> 1) & 1))), 0)) {
+                    load_v(next_v);
+                    ++next_v;
+                    progressed = true;
+                }
+                if (__shfl_sync(0xffffffffu, (int)(next_s < next_k && mbar_test(&k_full[next_s & 1], (next_s >> 1) & 1) &&
+                                                   (next_s < 2 || mbar_test(&s_free[next_s & 1], ((next_s - 2) >> 1) & 1))), 0)) {
                     issue_s(next_s);
                     ++next_s;
                     progressed = true;
                 }
-                if (mbar_test(p_ready, next_pv & 1)) {
+                if (__shfl_sync(0xffffffffu, (int)(next_pv < next_v && mbar_test(p_ready, next_pv & 1) && mbar_test(&v_full[next_pv & 1], (next_pv >> 1) & 1)), 0)) {
                     // O += P(i) V(i) in TMEM columns [128, 128 + D); any rescaling of O by the rows happened before they arrived
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const int buf = next_pv & 1;
-                    const uint32_t sp = smem_u32(sP), sv = smem_u32(sKV + (size_t)buf * 2 * TA_KV_BYTES) + TA_KV_BYTES;
+                    if (lane == 0) {
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        const uint32_t sp = smem_u32(sP), sv = smem_u32(sKV + (size_t)buf * 2 * TA_KV_BYTES) + TA_KV_BYTES;
 #pragma unroll
-                    for (int kk = 0; kk < TA_BN / 16; ++kk)
-                        umma_bf16(tmem_base + TA_O_COL, umma_desc(sp) + 2 * kk, umma_desc_mn(sv + kk * 2048, TA_BN * 128), idesc_pv,
-                                  (next_pv > 0 || kk > 0) ? 1u : 0u);
-                    umma_commit(pv_done);
-                    umma_commit(&kv_free[buf]);
+                        for (int kk = 0; kk < TA_BN / 16; ++kk)
+                            umma_bf16(tmem_base + TA_O_COL, umma_desc(sp) + 2 * kk, umma_desc_mn(sv + kk * 2048, TA_BN * 128), idesc_pv,
+                                      (next_pv > 0 || kk > 0) ? 1u : 0u);
+                        umma_commit(pv_done);
+                        umma_commit(&v_free[buf]);
+                    }
                     ++next_pv;
                     progressed = true;
                 }
                 if (!progressed && (++idle & 63) == 0) {
                     if (*abort) ok = false;
                     else if (clock64() - start > 8 * TC_WAIT_LIMIT) { *abort = 1; atomicExch(error_flag, 29); ok = false; }
+                    ok = __all_sync(0xffffffffu, ok);
                 }
             }
         }
@@ -264,7 +285,7 @@ __global__ void __launch_bounds__(160, 2) attn_prefill_tc_kernel(
         float m_used = -INFINITY, l_run = 0.0f;           // the maximum O and l are currently scaled by (log2 units)
         bool ok = true;
         for (int i = 0; i < nblk; ++i) {
-            const int key0 = (kb_first + i) * TA_BN;
+            const int key0 = block_of(i) * TA_BN;
             const uint32_t s_col = lane_base + (uint32_t)((i & 1) * TA_BN);
             ok = ok && wait_or_abort(&s_done[i & 1], (i >> 1) & 1, abort, error_flag, 23);
             ok = __all_sync(0xffffffffu, ok);              // tcgen05.ld is warp-wide: the warp takes one path
@@ -419,11 +440,12 @@ MB_API int mb_attn_prefill_tc(const void* q, const void* k_cache, const void* v_
     int rc = map_2d(&mq, q, (uint64_t)tokens, (uint64_t)K * GROUP * D, TA_BM);
     if (rc) return rc;
     const uint64_t cache_rows = (uint64_t)cache_pages * K * page_size;
-    rc = map_2d(&mk, k_cache, cache_rows, D, 16);
+    const int box_rows = page_size < TA_BN ? page_size : TA_BN;
+    rc = map_2d(&mk, k_cache, cache_rows, D, box_rows);
     if (rc) return rc;
-    rc = map_2d(&mv, v_cache, cache_rows, D, 16);
+    rc = map_2d(&mv, v_cache, cache_rows, D, box_rows);
     if (rc) return rc;
     dim3 grid((max_query_len + TA_BM - 1) / TA_BM, K * GROUP, requests);
     return launch_kernel(attn_prefill_tc_kernel, grid, 160, TA_SMEM, s, 0, mq, mk, mv, (bf16*)out, block_table, max_pages, cu_tokens,
-                         seq_lens, first_req, K, page_shift, scale, window, error_flag);
+                         seq_lens, first_req, K, page_shift, scale, window, error_flag, box_rows);
 }

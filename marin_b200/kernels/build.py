@@ -168,7 +168,8 @@ def attention_job(d: int, group: int) -> tuple:
 
 
 def attention_tc_job(d: int, group: int) -> tuple:
-    return (["attention_tc.cu"], [f"HEAD_DIM={d}", f"GROUP={group}"])
+    extra = [x for x in os.environ.get("MARIN_B200_ATTENTION_DEFINES", "").split(",") if x]
+    return (["attention_tc.cu"], [f"HEAD_DIM={d}", f"GROUP={group}"] + extra)
 
 
 def build_all(verbose: bool = True) -> List[str]:
