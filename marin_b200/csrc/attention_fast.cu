@@ -34,7 +34,9 @@ __device__ __forceinline__ float fast_exp2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+#ifndef DEC_WARPS
 #define DEC_WARPS 4
+#endif
 #define DPL (D / 8)                   // dims per lane: 8 lanes share one key
 #define VW (DPL % 8 == 0 ? 8 : (DPL % 4 == 0 ? 4 : 2))   // elements per vector load
 #define NV (DPL / VW)                 // vector loads per lane and key
@@ -112,8 +114,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_split_kernel(
     const int* __restrict__ block_table, int max_pages, const int* __restrict__ seq_lens, int K, int page_shift,
     float scale, int window, float* __restrict__ part_acc, float* __restrict__ part_ml, int max_chunks, int split_keys,
     int* __restrict__ counters, bf16* __restrict__ out) {
-    pdl_wait();
-    pdl_launch_dependents();
+    PDL_ENTER();
     extern __shared__ __align__(16) uint8_t dec_smem[];
     __shared__ float s_m[DEC_WARPS][8], s_l[DEC_WARPS][8];
     __shared__ int s_last;
@@ -389,8 +390,7 @@ __global__ void __launch_bounds__(128, PF_MIN_CTAS) attn_prefill_kernel(
     const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache, bf16* __restrict__ out,
     const int* __restrict__ block_table, int max_pages, const int* __restrict__ cu_tokens, const int* __restrict__ seq_lens,
     int first_req, int K, int page_shift, float scale, int window) {
-    pdl_wait();
-    pdl_launch_dependents();
+    PDL_ENTER_EARLY();
     extern __shared__ __align__(16) uint8_t pf_smem[];
     bf16* sQ = reinterpret_cast<bf16*>(pf_smem);
     bf16* sKV = sQ + PF_BM * PF_LD;                  // [2 buffers][K then V][64][PF_LD]

@@ -14,8 +14,7 @@ __global__ void __launch_bounds__(AS_THREADS) attention_simple_kernel(
     const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache, T* __restrict__ out,
     const int* __restrict__ block_table, int max_pages, const int* __restrict__ req_index,
     const int* __restrict__ positions, int H, int K, int d, int page_size, float scale, int window) {
-    pdl_wait();
-    pdl_launch_dependents();
+    PDL_ENTER();
     extern __shared__ float smem[];
     float* qs = smem;                 // [d]
     float* ps = smem + d;             // [AS_THREADS]

@@ -145,8 +145,7 @@ __global__ void __launch_bounds__(160, 2) attn_prefill_tc_kernel(
     uint32_t* tmem_slot = (uint32_t*)(bars + 13);
     volatile int* abort = (volatile int*)(tmem_slot + 1);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    pdl_wait();
-    pdl_launch_dependents();
+    PDL_ENTER_EARLY();
     const int H = K * GROUP;
     const int r = first_req + blockIdx.z, h = blockIdx.y, qt = gridDim.x - 1 - blockIdx.x;   // long tiles first
     const int tok0 = cu_tokens[r], n = cu_tokens[r + 1] - tok0;

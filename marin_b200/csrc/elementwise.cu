@@ -8,8 +8,7 @@
 // ---- embedding: out[t, :] = float(table[ids[t], :]) -------------------------------------------------
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ ids, const TW* __restrict__ table, float* __restrict__ out, int h) {
-    pdl_wait();
-    pdl_launch_dependents();
+    PDL_ENTER();
     const int t = blockIdx.x;
     const TW* row = table + (size_t)ids[t] * h;
     float* dst = out + (size_t)t * h;
@@ -28,8 +27,7 @@ MB_API int mb_embed(const int* ids, const void* table, int table_dtype, float* o
 template <typename TO>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, float eps, int unit_offset,
                                TO* __restrict__ out, int n) {
-    pdl_wait();
-    pdl_launch_dependents();
+    PDL_ENTER();
     __shared__ float scratch[32];
     const float* row = x + (size_t)blockIdx.x * n;
     TO* dst = out + (size_t)blockIdx.x * n;
@@ -48,8 +46,7 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
 template <typename TO, int R>
 __global__ void __launch_bounds__(256) rmsnorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ w, float eps,
                                                           int unit_offset, TO* __restrict__ out, int n) {
-    pdl_wait();
-    pdl_launch_dependents();
+    PDL_ENTER();
     __shared__ float scratch[32];
     const float4* row = reinterpret_cast<const float4*>(x + (size_t)blockIdx.x * n);
     const float4* w4 = reinterpret_cast<const float4*>(w);
@@ -113,8 +110,7 @@ __global__ void qk_norm_rope_write_kernel(const T* __restrict__ qkv, int row_str
                                           int rotary_dim, int interleaved, const int* __restrict__ slot_mapping,
                                           T* __restrict__ k_cache, T* __restrict__ v_cache, int H, int K, int d,
                                           int page_size, int heads_total, int heads_per_warp) {
-    pdl_wait();
-    pdl_launch_dependents();
+    PDL_ENTER();
     extern __shared__ float smem[];
     const int warps = blockDim.x >> 5;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -183,8 +179,7 @@ __global__ void __launch_bounds__(256) qk_norm_rope_write_fast_kernel(
     const float* __restrict__ k_w, float eps, const int* __restrict__ positions, const float* __restrict__ inv_freq,
     const int* __restrict__ slot_mapping, bf16* __restrict__ k_cache, bf16* __restrict__ v_cache, int H, int K, int page_size,
     int heads_total) {
-    pdl_wait();
-    pdl_launch_dependents();
+    PDL_ENTER();
     constexpr int d = LPH * 8, half = d / 2;
     __shared__ float cs_tab[half], sn_tab[half];
     const int t = blockIdx.x;
@@ -288,8 +283,7 @@ MB_API int mb_qk_norm_rope_write(const void* qkv, int dtype, void* q_out, const 
 // up in alternating blocks of 16 columns: g = gu[t, 32 (i / 16) + i % 16], u = 16 columns further -----------------
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total, int interleaved) {
-    pdl_wait();
-    pdl_launch_dependents();
+    PDL_ENTER();
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (; idx < total; idx += stride) {
@@ -314,8 +308,7 @@ MB_API int mb_swiglu(const void* gate_up, void* out, int dtype, int tokens, int 
 
 // ---- rows of the residual stream whose logits are wanted ----------------------------------------------
 __global__ void gather_rows_kernel(const float* __restrict__ src, const int* __restrict__ rows, float* __restrict__ out, int h) {
-    pdl_wait();
-    pdl_launch_dependents();
+    PDL_ENTER();
     const float* row = src + (size_t)rows[blockIdx.x] * h;
     float* dst = out + (size_t)blockIdx.x * h;
     for (int i = threadIdx.x; i < h; i += blockDim.x) dst[i] = row[i];
@@ -329,8 +322,7 @@ MB_API int mb_gather_rows(const float* src, const int* rows, float* out, int cou
 // ---- y += x (float32 residual, x in the activation dtype) ---------------------------------------------
 template <typename T>
 __global__ void add_into_kernel(float* __restrict__ y, const T* __restrict__ x, size_t total) {
-    pdl_wait();
-    pdl_launch_dependents();
+    PDL_ENTER();
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (; idx < total; idx += stride) y[idx] += to_f32(x[idx]);

@@ -305,8 +305,7 @@ __global__ void __launch_bounds__(320) gemm_tc_persistent_kernel(const __grid_co
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
-    pdl_wait();
-    pdl_launch_dependents();
+    PDL_ENTER_EARLY();
 
     if (warp == 0 && lane == 0) {
         int it = 0;                                                   // k-blocks issued so far, over all tiles

@@ -11,6 +11,24 @@
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// The start of a kernel that needs nothing before its inputs.  PDL_ENTER() lets the kernels behind it be scheduled
+// once its own inputs are there; PDL_ENTER_EARLY() lets them be scheduled at once, so that their CTAs sit on the
+// SMs, set up and waiting, while this kernel runs.  Measured on B200: early scheduling gains 3 % on a prompt of 2,048
+// tokens when the long kernels (the persistent matrix product, prefill attention) do it, and loses 5 % in decode
+// steps when the short kernels do it too.  -DPDL_WAIT_FIRST or -DPDL_LAUNCH_FIRST force one order everywhere.
+#define PDL_ENTER_LATE() do { pdl_wait(); pdl_launch_dependents(); } while (0)
+#define PDL_ENTER_AT_ONCE() do { pdl_launch_dependents(); pdl_wait(); } while (0)
+#if defined(PDL_WAIT_FIRST)
+#define PDL_ENTER() PDL_ENTER_LATE()
+#define PDL_ENTER_EARLY() PDL_ENTER_LATE()
+#elif defined(PDL_LAUNCH_FIRST)
+#define PDL_ENTER() PDL_ENTER_AT_ONCE()
+#define PDL_ENTER_EARLY() PDL_ENTER_AT_ONCE()
+#else
+#define PDL_ENTER() PDL_ENTER_LATE()
+#define PDL_ENTER_EARLY() PDL_ENTER_AT_ONCE()
+#endif
+
 static inline bool pdl_enabled() {
     static int state = -1;
     if (state < 0) {

@@ -8,8 +8,7 @@
 
 __global__ void __launch_bounds__(AM_THREADS) argmax_kernel(const float* __restrict__ logits, int vocab, int usable,
                                                             int* __restrict__ out) {
-    pdl_wait();
-    pdl_launch_dependents();
+    PDL_ENTER();
     __shared__ float best_v[AM_THREADS / 32];
     __shared__ int best_i[AM_THREADS / 32];
     const float* row = logits + (size_t)blockIdx.x * vocab;
@@ -102,8 +101,7 @@ __global__ void __launch_bounds__(SP_THREADS) sample_kernel(const float* __restr
                                                             const float* __restrict__ temperature, const int* __restrict__ top_k,
                                                             const float* __restrict__ top_p, const float* __restrict__ uniform,
                                                             int* __restrict__ out) {
-    pdl_wait();
-    pdl_launch_dependents();
+    PDL_ENTER();
     __shared__ float fs[32];
     __shared__ int is[32];
     __shared__ int s_found;

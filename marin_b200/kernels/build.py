@@ -85,8 +85,11 @@ def library_path(name: str, sources: Sequence[str], defines: Sequence[str] = ())
 
 
 def build(name: str, sources: Sequence[str], defines: Sequence[str] = (), verbose: bool = True) -> str:
-    """Compiles ``sources`` (names inside csrc/) into one shared library unless it is already built."""
-    flags = ARCH_FLAGS + BASE_FLAGS + [f"-D{d}" for d in defines]
+    """Compiles ``sources`` (names inside csrc/) into one shared library unless it is already built.
+    MARIN_B200_DEFINES in the environment (comma separated, e.g. ``DEC_STAGES=2,PDL_WAIT_FIRST``) adds defines to
+    every library: the kernels' tuning constants can be overridden for experiments without touching the sources."""
+    extra = [x for x in os.environ.get("MARIN_B200_DEFINES", "").split(",") if x]
+    flags = ARCH_FLAGS + BASE_FLAGS + [f"-D{d}" for d in list(defines) + extra]
     out = os.path.join(_build_dir(), f"{name}-{_digest(sources, flags)}.so")
     if os.path.exists(out):
         return out
@@ -161,15 +164,13 @@ def build_many(jobs: Dict[str, tuple], verbose: bool = True) -> List[str]:
 
 
 def attention_job(d: int, group: int) -> tuple:
-    """Sources and defines of the attention kernels for one head layout.  MARIN_B200_ATTENTION_DEFINES (comma
-    separated, e.g. ``DEC_STAGES=2,PF_BUFFERS=2``) overrides the kernels' tuning constants for experiments."""
-    extra = [x for x in os.environ.get("MARIN_B200_ATTENTION_DEFINES", "").split(",") if x]
-    return (["attention_fast.cu"], [f"HEAD_DIM={d}", f"GROUP={group}"] + extra)
+    """Sources and defines of the attention kernels for one head layout."""
+    return (["attention_fast.cu"], [f"HEAD_DIM={d}", f"GROUP={group}"])
 
 
 def attention_tc_job(d: int, group: int) -> tuple:
-    extra = [x for x in os.environ.get("MARIN_B200_ATTENTION_DEFINES", "").split(",") if x]
-    return (["attention_tc.cu"], [f"HEAD_DIM={d}", f"GROUP={group}"] + extra)
+    """Sources and defines of the tensor-core prefill attention kernel for one head layout."""
+    return (["attention_tc.cu"], [f"HEAD_DIM={d}", f"GROUP={group}"])
 
 
 def build_all(verbose: bool = True) -> List[str]:
