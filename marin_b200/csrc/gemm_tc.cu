@@ -82,13 +82,61 @@ __device__ __forceinline__ void store_chunk_swiglu(void* out, int t_first, int n
     }
 }
 
+// Two optional couplings of a product with the RMS norm next to it, so that the norm needs no kernel of its own
+// (y = norm(h) W^T = rstd(h) * ((h * g) W^T): the per-token factor commutes with the product).
+//   TcNormOut, on a "+=" into the residual stream h: the updated rows times the norm's weight g are also written in
+//   bf16, and the sums of their squares over each group of at most 32 weight rows go to sumsq[slot][T]
+//   (slot = tile * max(4, splits) + group, written without atomics: the sum over slots has a fixed order).
+//   TcRowScale, on the product that consumes those rows: the accumulator of token t is multiplied by
+//   1 / sqrt(sum_slots sumsq[slot][t] / dim + eps) in float32 before it is written (crates/tensor/src/norm.rs:16-22).
+struct TcNormOut {
+    const float* weight;      // [N]; nullptr: none of this
+    bf16* scaled;             // [T, N]
+    float* sumsq;             // [slots][T]
+    int unit_offset;          // 1: the factor is 1 + weight
+};
+struct TcRowScale {
+    const float* sumsq;       // [slots][T]; nullptr: no scaling
+    int slots;
+    int dim;
+    float eps;
+};
+
+__device__ __forceinline__ float group_sum(float v, int width) {       // over aligned groups of `width` lanes (<= 32)
+    for (int o = width >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// "+=" of sixteen tokens of weight row n with the norm's side outputs; all 32 lanes call it (valid: n < N).
+__device__ __forceinline__ void store_chunk_norm(void* out, int t_first, int n, bool valid, int T, int N, const float* v,
+                                                 const TcNormOut& norm, float* sumsq_slot, int lane) {
+    float* o = (float*)out;
+    float nv[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) nv[j] = (valid && t_first + j < T) ? o[(size_t)(t_first + j) * N + n] : 0.0f;
+    float g = valid ? norm.weight[n] : 0.0f;
+    if (norm.unit_offset) g += 1.0f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        nv[j] = (valid && t_first + j < T) ? nv[j] + v[j] : 0.0f;
+        if (valid && t_first + j < T) {
+            o[(size_t)(t_first + j) * N + n] = nv[j];
+            norm.scaled[(size_t)(t_first + j) * N + n] = __float2bfloat16_rn(nv[j] * g);
+        }
+        const float sq = group_sum(nv[j] * nv[j], 32);
+        if (lane == 0 && t_first + j < T) sumsq_slot[t_first + j] = sq;
+    }
+}
+
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,
                                                       const __grid_constant__ CUtensorMap map_x, void* __restrict__ out,
                                                       int mode, int T, int N, int K, int kb_per_split,
                                                       float* __restrict__ partials, int* __restrict__ counters,
-                                                      int* __restrict__ error_flag, int cluster_reduce) {
+                                                      int* __restrict__ error_flag, int cluster_reduce,
+                                                      const TcNormOut norm, const TcRowScale scale) {
     extern __shared__ uint8_t smem_raw[];
+    __shared__ float s_scale[BN];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     using L = TcSmem<BN>;
     uint64_t* full = (uint64_t*)(smem + STAGES * L::STAGE_BYTES);
@@ -159,8 +207,37 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
             umma_commit(&empty[s]);
         }
         umma_commit(accum);
+    } else if (warp >= 2 && scale.sumsq != nullptr) {
+        // ---- the per-token factors of the norm ahead of this product: warps 2 and 3 add the slots, in slot order ----
+        pdl_wait();
+        // warps 2 and 3: `tpt` threads per token (a power of two, at most 32), each adds its share of the slots in
+        // slot order, up to 24 loads in flight at a time; then the shares are added in a fixed tree
+        const int here = min(BN, T - t0);
+        int tpt = 32;
+        while (tpt * here > 64 && tpt > 1) tpt >>= 1;
+        const int local = threadIdx.x - 64, part = local % tpt;
+        const int per = (scale.slots + tpt - 1) / tpt;
+        const int trips = (BN * tpt + 63) / 64;                       // the same for every thread: shuffles below
+        for (int trip = 0; trip < trips; ++trip) {
+            const int tt = trip * (64 / tpt) + local / tpt;
+            const int t = t0 + tt;
+            float sum = 0.0f;
+            if (tt < BN && t < T) {
+                const int s_end = min(scale.slots, (part + 1) * per);
+                for (int s0 = part * per; s0 < s_end; s0 += 24) {
+                    float v[24];
+#pragma unroll
+                    for (int i = 0; i < 24; ++i) v[i] = s0 + i < s_end ? __ldcg(&scale.sumsq[(size_t)(s0 + i) * T + t]) : 0.0f;
+#pragma unroll
+                    for (int i = 0; i < 24; ++i) sum += v[i];
+                }
+            }
+            sum = group_sum(sum, tpt);
+            if (part == 0 && tt < BN) s_scale[tt] = t < T ? 1.0f / sqrtf(sum / (float)scale.dim + scale.eps) : 0.0f;
+        }
     }
     __syncwarp();
+    if (scale.sumsq != nullptr) __syncthreads();
 
     // ---- epilogue: every warp reads its 32 lanes of the accumulator ----
     pdl_wait();                                   // out may be read (+=) and is written: only after the kernels ahead
@@ -190,22 +267,60 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
 #pragma unroll
             for (int j = 0; j < 16; ++j) red[(c0 + j) * TC_BM + warp * 32 + lane] = v[j];
         }
-        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
         const int rows_per = TC_BM / splits;                         // splits is 2, 4 or 8
         const int row_first = blockIdx.z * rows_per;
         const int t_count = min(BN, T - t0);
-        const uint32_t red_addr = smem_u32(red);
-        for (int idx = threadIdx.x; idx < t_count * rows_per; idx += 128) {
-            const int tt = idx / rows_per, row = row_first + idx % rows_per;
-            float sum = 0.0f;
-            for (int z = 0; z < splits; ++z) {
-                uint32_t remote;
-                float pv;
-                asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(red_addr + (uint32_t)(tt * TC_BM + row) * 4u), "r"(z));
-                asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(pv) : "r"(remote) : "memory");
-                sum += pv;
+        // what the first trip below needs from global memory is asked for before the cluster meets
+        float old0 = 0.0f, g0 = 0.0f;
+        {
+            const int tt = threadIdx.x / rows_per, row = row_first + threadIdx.x % rows_per;
+            if (threadIdx.x < t_count * rows_per && n0 + row < N) {
+                if (mode == TC_OUT_F32_ACC) old0 = ((const float*)out)[(size_t)(t0 + tt) * N + n0 + row];
+                if (norm.weight != nullptr) g0 = norm.weight[n0 + row];
             }
-            if (n0 + row < N) store_out(out, mode, (size_t)(t0 + tt) * N + n0 + row, sum);
+        }
+        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+        const uint32_t red_addr = smem_u32(red);
+        const int group = rows_per < 32 ? rows_per : 32;             // rows whose squares are added into one slot
+        const int slots_per_tile = splits < 4 ? 4 : splits;
+        for (int base = 0; base < t_count * rows_per; base += 128) {  // every thread makes every trip (shuffles below)
+            const int idx = base + threadIdx.x;
+            const bool active = idx < t_count * rows_per;
+            const int tt = idx / rows_per, in_slice = idx % rows_per, row = row_first + in_slice;
+            float sum = 0.0f;
+            if (active) {
+                for (int z = 0; z < splits; ++z) {
+                    uint32_t remote;
+                    float pv;
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(red_addr + (uint32_t)(tt * TC_BM + row) * 4u), "r"(z));
+                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(pv) : "r"(remote) : "memory");
+                    sum += pv;
+                }
+                if (scale.sumsq != nullptr) sum *= s_scale[tt];
+            }
+            const bool valid = active && n0 + row < N;
+            const size_t at = (size_t)(t0 + tt) * N + n0 + row;
+            float nv = 0.0f;
+            if (valid) {
+                if (mode == TC_OUT_F32_ACC) {
+                    nv = (base == 0 ? old0 : ((const float*)out)[at]) + sum;
+                    ((float*)out)[at] = nv;
+                    if (norm.weight != nullptr) {
+                        float g = base == 0 ? g0 : norm.weight[n0 + row];
+                        if (norm.unit_offset) g += 1.0f;
+                        norm.scaled[at] = __float2bfloat16_rn(nv * g);
+                    }
+                } else {
+                    store_out(out, mode, at, sum);
+                }
+            }
+            if (norm.weight != nullptr) {
+                const float sq = group_sum(nv * nv, group);
+                if (active && in_slice % group == 0) {
+                    const int slot = blockIdx.x * slots_per_tile + blockIdx.z * (slots_per_tile / splits) + in_slice / group;
+                    norm.sumsq[(size_t)slot * T + t0 + tt] = sq;
+                }
+            }
         }
         // nobody leaves while a peer may still read its tile
         asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
@@ -218,7 +333,13 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
 #pragma unroll
             for (int j = 0; j < 16; ++j) v[j] = 0.0f;
         }
-        if (direct && mode == TC_OUT_SWIGLU) {
+        if (direct && scale.sumsq != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] *= s_scale[c0 + j];
+        }
+        if (direct && norm.weight != nullptr) {
+            store_chunk_norm(out, t0 + c0, n, n < N, T, N, v, norm, norm.sumsq + (size_t)(blockIdx.x * 4 + warp) * T, lane);
+        } else if (direct && mode == TC_OUT_SWIGLU) {
             if (n0 + warp * 32 < N) store_chunk_swiglu(out, t0 + c0, n0 + warp * 32, lane, T, N, v);
         } else if (n < N) {
             if (direct) store_chunk(out, mode, t0 + c0, n, T, N, v);
@@ -400,7 +521,8 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int K, int box
 
 template <int BN, int STAGES>
 static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int mode, int T, int N, int K, int splits,
-                     int kb_per_split, float* partials, int* counters, int* error_flag, int cluster_reduce, cudaStream_t s) {
+                     int kb_per_split, float* partials, int* counters, int* error_flag, int cluster_reduce,
+                     const TcNormOut& norm, const TcRowScale& scale, cudaStream_t s) {
     constexpr int smem = STAGES * TcSmem<BN>::STAGE_BYTES + 1024 + 256;
     static_assert(STAGES * TcSmem<BN>::STAGE_BYTES >= BN * TC_BM * 4, "the cluster reduction reuses the pipeline buffers");
     static bool configured = false;
@@ -412,7 +534,7 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* out, in
     const bool clustered = cluster_reduce && splits > 1;
     return launch_kernel(gemm_tc_kernel<BN, STAGES>, dim3((N + TC_BM - 1) / TC_BM, (T + BN - 1) / BN, splits), dim3(128), smem, s,
                          clustered ? splits : 0, mw, mx, out, mode, T, N, K, kb_per_split, partials, counters, error_flag,
-                         clustered ? 1 : 0);
+                         clustered ? 1 : 0, norm, scale);
 }
 
 // Tiles a launch with `bn` tokens per CTA would have (for the caller's choice of split).
@@ -463,8 +585,13 @@ MB_API int mb_gemm_tc_persistent(const void* x, const void* w, void* out, int mo
 // of 8 and both pointers 16-byte aligned (TMA).  splits > 1 needs partials (splits*T*N floats) and counters
 // (one zeroed int per tile).  bn in {16, 32, 64, 128, 256}.
 static int gemm_tc_dispatch(const void* x, const void* w, void* out, int mode, int T, int N, int K, int bn, int splits,
-                            float* partials, int* counters, int* error_flag, int cluster_reduce, cudaStream_t s) {
+                            float* partials, int* counters, int* error_flag, int cluster_reduce, const TcNormOut& norm,
+                            const TcRowScale& scale, cudaStream_t s) {
     if (T <= 0 || N <= 0) return 0;
+    // the norm's side outputs exist for "+=" without global split-K scratch
+    if (norm.weight != nullptr && (mode != TC_OUT_F32_ACC || norm.scaled == nullptr || norm.sumsq == nullptr)) return MB_ERR_BAD_DTYPE;
+    if (norm.weight != nullptr && !cluster_reduce && splits > 1) return MB_ERR_BAD_SIZE;
+    if (scale.sumsq != nullptr && (scale.slots <= 0 || scale.dim <= 0 || (!cluster_reduce && splits > 1))) return MB_ERR_BAD_SIZE;
     if (K <= 0 || K % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return MB_ERR_BAD_SIZE;
     if (mode < 0 || mode > 3 || (mode == 3 && (splits > 1 || N % 32 != 0))) return MB_ERR_BAD_DTYPE;
     const int total_kb = (K + TC_BK - 1) / TC_BK;
@@ -485,11 +612,11 @@ static int gemm_tc_dispatch(const void* x, const void* w, void* out, int mode, i
     rc = make_map(&mx, x, T, K, bn);
     if (rc) return rc;
     switch (bn) {
-        case 16: return launch_tc<16, 6>(mw, mx, out, mode, T, N, K, splits, kb_per_split, partials, counters, error_flag, cluster_reduce, s);
-        case 32: return launch_tc<32, 5>(mw, mx, out, mode, T, N, K, splits, kb_per_split, partials, counters, error_flag, cluster_reduce, s);
-        case 64: return launch_tc<64, 4>(mw, mx, out, mode, T, N, K, splits, kb_per_split, partials, counters, error_flag, cluster_reduce, s);
-        case 128: return launch_tc<128, 3>(mw, mx, out, mode, T, N, K, splits, kb_per_split, partials, counters, error_flag, cluster_reduce, s);
-        case 256: return launch_tc<256, 4>(mw, mx, out, mode, T, N, K, splits, kb_per_split, partials, counters, error_flag, cluster_reduce, s);
+        case 16: return launch_tc<16, 6>(mw, mx, out, mode, T, N, K, splits, kb_per_split, partials, counters, error_flag, cluster_reduce, norm, scale, s);
+        case 32: return launch_tc<32, 5>(mw, mx, out, mode, T, N, K, splits, kb_per_split, partials, counters, error_flag, cluster_reduce, norm, scale, s);
+        case 64: return launch_tc<64, 4>(mw, mx, out, mode, T, N, K, splits, kb_per_split, partials, counters, error_flag, cluster_reduce, norm, scale, s);
+        case 128: return launch_tc<128, 3>(mw, mx, out, mode, T, N, K, splits, kb_per_split, partials, counters, error_flag, cluster_reduce, norm, scale, s);
+        case 256: return launch_tc<256, 4>(mw, mx, out, mode, T, N, K, splits, kb_per_split, partials, counters, error_flag, cluster_reduce, norm, scale, s);
         default: return MB_ERR_BAD_SIZE;
     }
 }
@@ -499,14 +626,30 @@ static int gemm_tc_dispatch(const void* x, const void* w, void* out, int mode, i
 // (one zeroed int per tile).  bn in {16, 32, 64, 128, 256}.
 MB_API int mb_gemm_tc(const void* x, const void* w, void* out, int mode, int T, int N, int K, int bn, int splits,
                       float* partials, int* counters, int* error_flag, cudaStream_t s) {
-    return gemm_tc_dispatch(x, w, out, mode, T, N, K, bn, splits, partials, counters, error_flag, 0, s);
+    return gemm_tc_dispatch(x, w, out, mode, T, N, K, bn, splits, partials, counters, error_flag, 0, TcNormOut{}, TcRowScale{}, s);
 }
 
 // The same product with the K slices of a tile as one thread-block cluster (splits in {1, 2, 4, 8}): the slices
 // are added through distributed shared memory, no global scratch is touched.
 MB_API int mb_gemm_tc_cluster(const void* x, const void* w, void* out, int mode, int T, int N, int K, int bn, int splits,
                               int* error_flag, cudaStream_t s) {
-    return gemm_tc_dispatch(x, w, out, mode, T, N, K, bn, splits, nullptr, nullptr, error_flag, 1, s);
+    return gemm_tc_dispatch(x, w, out, mode, T, N, K, bn, splits, nullptr, nullptr, error_flag, 1, TcNormOut{}, TcRowScale{}, s);
+}
+
+// Slots of sums of squares per token that a "+=" product over N weight rows with `splits` K slices writes.
+MB_API int mb_gemm_tc_norm_slots(int N, int splits) { return ((N + TC_BM - 1) / TC_BM) * (splits < 4 ? 4 : splits); }
+
+// mb_gemm_tc_cluster coupled with the RMS norms around it (either coupling may be absent: null pointers).
+//   norm_weight [N] float32, scaled_out [T, N] bf16, sumsq_out [mb_gemm_tc_norm_slots(N, splits)][T] float32: with
+//   mode 2, the updated rows times the norm weight (1 + weight with unit_offset) and their sums of squares.
+//   scale_sumsq [scale_slots][T]: token t of the product is multiplied by 1 / sqrt(sum of its slots / scale_dim + eps).
+MB_API int mb_gemm_tc_coupled(const void* x, const void* w, void* out, int mode, int T, int N, int K, int bn, int splits,
+                              const float* norm_weight, int norm_unit_offset, void* scaled_out, float* sumsq_out,
+                              const float* scale_sumsq, int scale_slots, int scale_dim, float scale_eps, int* error_flag,
+                              cudaStream_t s) {
+    TcNormOut norm{norm_weight, (bf16*)scaled_out, sumsq_out, norm_unit_offset};
+    TcRowScale scale{scale_sumsq, scale_slots, scale_dim, scale_eps};
+    return gemm_tc_dispatch(x, w, out, mode, T, N, K, bn, splits, nullptr, nullptr, error_flag, 1, norm, scale, s);
 }
 
 // ---- the entry point that allocates nothing (see gemm_tc_noalloc.h) --------------------------------------------

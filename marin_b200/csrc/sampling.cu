@@ -1,20 +1,38 @@
 // Sampling on the device.  arg-max: the largest logit among the first `usable`, the lowest id among
-// equals (the reference's greedy rule, crates/sampler/src/lib.rs:40-48); one block per row.
+// equals (the reference's greedy rule, crates/sampler/src/lib.rs:40-48).  A row is shared by several blocks; each
+// folds its best (value, id) into one 64-bit key per row with atomicMax, and the block that arrives last writes
+// the id and clears the row's key and counter for the next launch.  NaN is never chosen; a row without any
+// comparable value gives id 0.
 #include "common.cuh"
 #include "launch.cuh"
 #include <limits.h>
 
 #define AM_THREADS 512
+#define AM_MAX_ROWS 4096
+
+// Scratch of the arg-max kernel, zero between launches.  One launch at a time may use it (the engine has one stream).
+static __device__ unsigned long long am_keys[AM_MAX_ROWS];
+static __device__ int am_count[AM_MAX_ROWS];
+
+// Larger value first, then lower id: the value's bits made monotonic in the high word, the inverted id in the low.
+__device__ __forceinline__ unsigned long long am_key(float v, int idx) {
+    v += 0.0f;                                               // -0 and +0 are equal: one key for both
+    unsigned int b = __float_as_uint(v);
+    b = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+    return ((unsigned long long)b << 32) | (unsigned long long)(0xffffffffu - (unsigned int)idx);
+}
 
 __global__ void __launch_bounds__(AM_THREADS) argmax_kernel(const float* __restrict__ logits, int vocab, int usable,
-                                                            int* __restrict__ out) {
+                                                            int per_block, int* __restrict__ out) {
     PDL_ENTER();
     __shared__ float best_v[AM_THREADS / 32];
     __shared__ int best_i[AM_THREADS / 32];
-    const float* row = logits + (size_t)blockIdx.x * vocab;
+    const int r = blockIdx.y;
+    const float* row = logits + (size_t)r * vocab;
+    const int begin = blockIdx.x * per_block, end = min(usable, begin + per_block);
     float v = -INFINITY;
     int idx = 0x7fffffff;
-    for (int i = threadIdx.x; i < usable; i += AM_THREADS) {
+    for (int i = begin + threadIdx.x; i < end; i += AM_THREADS) {
         const float x = row[i];
         if (x > v || (x == v && i < idx)) { v = x; idx = i; }
     }
@@ -36,14 +54,34 @@ __global__ void __launch_bounds__(AM_THREADS) argmax_kernel(const float* __restr
             const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
             if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; }
         }
-        if (lane == 0) out[blockIdx.x] = idx == 0x7fffffff ? 0 : idx;
+        if (lane == 0) {
+            if (idx != 0x7fffffff) atomicMax(&am_keys[r], am_key(v, idx));
+            __threadfence();
+            if (atomicAdd(&am_count[r], 1) == (int)gridDim.x - 1) {
+                __threadfence();
+                const unsigned long long key = atomicExch(&am_keys[r], 0ull);
+                am_count[r] = 0;
+                out[r] = key == 0ull ? 0 : (int)(0xffffffffu - (unsigned int)(key & 0xffffffffull));
+            }
+        }
     }
 }
 
 MB_API int mb_argmax(const float* logits, int rows, int vocab, int usable, int* out, cudaStream_t s) {
     if (rows <= 0) return 0;
     if (usable <= 0 || usable > vocab) return MB_ERR_BAD_SIZE;
-    return launch_kernel(argmax_kernel, rows, AM_THREADS, 0, s, 0, logits, vocab, usable, out);
+    for (int r0 = 0; r0 < rows; r0 += AM_MAX_ROWS) {
+        const int n = rows - r0 < AM_MAX_ROWS ? rows - r0 : AM_MAX_ROWS;
+        int blocks = (296 + n - 1) / n;                                  // about two blocks per SM in all
+        const int most = (usable + 4 * AM_THREADS - 1) / (4 * AM_THREADS);  // at least four values per thread
+        if (blocks > most) blocks = most;
+        const int per_block = (usable + blocks - 1) / blocks;
+        blocks = (usable + per_block - 1) / per_block;
+        const int rc = launch_kernel(argmax_kernel, dim3(blocks, n), AM_THREADS, 0, s, 0, logits + (size_t)r0 * vocab, vocab, usable,
+                                     per_block, out + r0);
+        if (rc) return rc;
+    }
+    return 0;
 }
 
 // ---- temperature / top-k / top-p sampling on the device ---------------------------------------------------------------

@@ -63,8 +63,16 @@ class Model:
         self.embedding.forward(ctx.token_ids, hidden)
         if observe is not None:
             observe(0, hidden)
-        for i, entry in enumerate(self.spec.schedule):
-            self.blocks[entry.layer].forward(hidden, ctx, caches.view(i, ctx))
+        carried = None            # the next block's first norm, if the block before could carry it on its last product
+        schedule = self.spec.schedule
+        for i, entry in enumerate(schedule):
+            block = self.blocks[entry.layer]
+            if getattr(block, "chains_norm", False):
+                following = self.blocks[schedule[i + 1].layer] if i + 1 < len(schedule) else None
+                carried = block.forward(hidden, ctx, caches.view(i, ctx), x_in=carried, next_block=following)
+            else:
+                block.forward(hidden, ctx, caches.view(i, ctx))
+                carried = None
             if observe is not None:
                 observe(i + 1, hidden)
         W = ctx.num_logit_rows

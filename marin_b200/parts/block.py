@@ -35,10 +35,30 @@ class PreNormBlock(Part):
             p.load(tensors, rt)
         self.rt = rt
 
-    def forward(self, hidden: torch.Tensor, ctx, cache) -> None:
+    #: ``forward`` takes ``x_in`` / ``next_block`` and returns the next block's input (see there)
+    chains_norm = True
+
+    def _rider(self, norm, producer, consumer, out):
+        """``norm`` as a rider on ``producer``'s last product, if both parts around it can couple."""
+        if getattr(producer, "couples_norm", False) and getattr(consumer, "couples_norm", False) and hasattr(norm, "coupling"):
+            return norm.coupling(out)
+        return None
+
+    def forward(self, hidden: torch.Tensor, ctx, cache, x_in=None, next_block=None):
+        """``x_in``: this block's first norm of ``hidden``, already there or carried by the block before (what that
+        block returned).  ``next_block``: the block that runs next; if its first norm can ride on this block's last
+        product, its input is returned, else None."""
         ws = ctx.workspace
         normed = ws.get("normed", tuple(hidden.shape), self.rt.dtype)
-        self.norm1.forward(hidden, normed)
-        self.mixer.forward(normed, ctx, cache, hidden)
-        self.norm2.forward(hidden, normed)
-        self.feedforward.forward(normed, ctx, hidden)
+        x = x_in if x_in is not None else self.norm1.forward(hidden, normed)
+        rider = self._rider(self.norm2, self.mixer, self.feedforward, normed)
+        x = self.mixer.forward(x, ctx, cache, hidden, then_norm=rider) if rider is not None else self.mixer.forward(x, ctx, cache, hidden)
+        if x is None:
+            x = self.norm2.forward(hidden, normed)
+        rider = None
+        if next_block is not None and getattr(next_block, "chains_norm", False):
+            rider = self._rider(next_block.norm1, self.feedforward, next_block.mixer, normed)
+        if rider is not None:
+            return self.feedforward.forward(x, ctx, hidden, then_norm=rider)
+        self.feedforward.forward(x, ctx, hidden)
+        return None

@@ -17,6 +17,10 @@ from .spec import TensorSpec
 
 
 class FeedForward(Part):
+    #: True if ``forward`` takes ``x`` as ``ops.NormedRows`` too, and a keyword ``then_norm`` (an ``ops.NormOut``),
+    #: returning ``ops.NormedRows`` if its last product carried that norm and None otherwise (see ``Mixer``).
+    couples_norm = False
+
     def forward(self, x: torch.Tensor, ctx, residual: torch.Tensor) -> None:
         raise NotImplementedError
 
@@ -51,7 +55,9 @@ class SwiGLU(FeedForward):
             self.w_gate_up = rt.matrix(torch.cat([gate, up], dim=0))
         self.w_down = rt.matrix(tensors.pop(f"{n}.down_proj.weight"))
 
-    def forward(self, x: torch.Tensor, ctx, residual: torch.Tensor) -> None:
+    couples_norm = True
+
+    def forward(self, x, ctx, residual: torch.Tensor, then_norm=None):
         T = x.shape[0]
         ws = ctx.workspace
         act = ws.get("ffn_act", (T, self.intermediate), x.dtype)
@@ -61,4 +67,4 @@ class SwiGLU(FeedForward):
             gate_up = ws.get("gate_up", (T, 2 * self.intermediate), x.dtype)
             ops.gemm(x, self.w_gate_up, gate_up)
             ops.swiglu(gate_up, act)
-        ops.gemm(act, self.w_down, residual, accumulate=True)
+        return ops.gemm(act, self.w_down, residual, accumulate=True, then_norm=then_norm)

@@ -45,6 +45,11 @@ class StateNeed:
 
 
 class Mixer(Part):
+    #: True if ``forward`` takes ``x`` as ``ops.NormedRows`` too, and a keyword ``then_norm`` (an ``ops.NormOut``:
+    #: the norm wanted of the updated residual), returning ``ops.NormedRows`` if its last product carried that norm
+    #: and None otherwise.  A block couples norms only between parts that both say so.
+    couples_norm = False
+
     def cache_need(self):
         return None
 
@@ -104,7 +109,9 @@ class GQAttention(Mixer):
         self.position.load(tensors, rt)
         self.rt = rt
 
-    def forward(self, x: torch.Tensor, ctx, cache, residual: torch.Tensor) -> None:
+    couples_norm = True
+
+    def forward(self, x, ctx, cache, residual: torch.Tensor, then_norm=None):
         T = x.shape[0]
         ws = ctx.workspace
         writes = cache.owner
@@ -125,4 +132,4 @@ class GQAttention(Mixer):
         out = ws.get("attn_out", (T, self.q_dim), x.dtype)
         ops.attention(q, cache.k, cache.v, out, ctx, cache.block_table, self.heads, self.kv_heads,
                       self.head_dim, self.scale, self.window or 0)
-        ops.gemm(out, self.w_o, residual, accumulate=True)
+        return ops.gemm(out, self.w_o, residual, accumulate=True, then_norm=then_norm)

@@ -34,3 +34,7 @@ class RMSNorm(Part):
         """``x`` float32 ``[rows, dim]`` → ``out`` (float32 or bfloat16) ``[rows, dim]``."""
         ops.rmsnorm(x, self.weight, self.eps, out, self.unit_offset)
         return out
+
+    def coupling(self, out: torch.Tensor) -> "ops.NormOut":
+        """This norm as a rider on the product that last updates its input (``ops.gemm(..., then_norm=...)``)."""
+        return ops.NormOut(self.weight, self.unit_offset, self.eps, out)

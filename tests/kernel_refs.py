@@ -24,7 +24,7 @@ def rmsnorm(x, weight, eps, out, unit_offset=False):
     out.copy_((xf * (1.0 / torch.sqrt(ms + eps)) * w).to(out.dtype))
 
 
-def gemm(x, w, out, accumulate=False):
+def gemm(x, w, out, accumulate=False, then_norm=None):
     y = x.float() @ w.float().t()
     if accumulate:
         out.add_(y.to(out.dtype))

@@ -317,6 +317,67 @@ def test_gemm_tensor_cores(ops, T, N, K):
     ops.check_device_errors()
 
 
+@pytest.mark.parametrize("T,N,K,N2,unit", [(8, 2560, 4096, 6144, False), (1, 320, 512, 384, False), (13, 200, 264, 96, True),
+                                            (33, 1024, 9728, 2048, False), (64, 2560, 512, 640, False), (16, 128, 64, 64, True)])
+def test_gemm_carries_the_norm_that_follows(ops, monkeypatch, T, N, K, N2, unit):
+    """h += x W^T with the RMS norm of the new h riding on it, finished by the next product (plain and with
+    SwiGLU): against float64, and against the same three steps with the norm as a kernel of its own."""
+    g = torch.Generator(device=DEV).manual_seed(21)
+    x = torch.randn(T, K, device=DEV, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    h0 = torch.randn(T, N, device=DEV, generator=g) * torch.linspace(0.2, 30.0, T, device=DEV)[:, None]   # rows of very different size
+    gain = 1 + 0.2 * torch.randn(N, device=DEV, generator=g)
+    w2 = (torch.randn(N2, N, device=DEV, generator=g) / math.sqrt(N)).to(torch.bfloat16)
+    eps = 1e-5
+    monkeypatch.setattr(ops, "COUPLED_NORM_MAX_TOKENS", 64)         # every tile width the kernel couples at
+    for _ in range(2):
+        h = h0.clone()
+        normed = torch.full((T, N), float("nan"), device=DEV, dtype=torch.bfloat16)
+        carried = ops.gemm(x, w, h, accumulate=True, then_norm=ops.NormOut(gain, unit, eps, normed))
+        assert isinstance(carried, ops.NormedRows)
+        want_h = h0.double() + x.double() @ w.double().t()
+        assert float((h.double() - want_h).abs().max()) <= 2e-5 * float(want_h.abs().max()) + 1e-4
+        y = torch.empty(T, N2, device=DEV, dtype=torch.bfloat16)
+        ops.gemm(carried, w2, y)
+        ops.check_device_errors()
+        gg = (1 + gain.double()) if unit else gain.double()
+        want_n = want_h / torch.sqrt((want_h ** 2).mean(dim=1, keepdim=True) + eps) * gg
+        want_y = want_n @ w2.double().t()
+        scale = float(want_y.abs().max())
+        assert float((y.double() - want_y).abs().max()) <= 2e-2 * scale
+        # the same with the norm as its own kernel
+        h_b = h0.clone()
+        ops.gemm(x, w, h_b, accumulate=True)
+        n_b = torch.empty(T, N, device=DEV, dtype=torch.bfloat16)
+        ops.rmsnorm(h_b, gain, eps, n_b, unit)
+        y_b = torch.empty(T, N2, device=DEV, dtype=torch.bfloat16)
+        ops.gemm(n_b, w2, y_b)
+        assert torch.equal(h, h_b)
+        assert float((y.float() - y_b.float()).abs().max()) <= 1.6e-2 * scale
+        if N2 % 32 == 0:
+            act, act_b = (torch.empty(T, N2 // 2, device=DEV, dtype=torch.bfloat16) for _ in range(2))
+            ops.gemm_swiglu(carried, w2, act)
+            ops.gemm_swiglu(n_b, w2, act_b)
+            yy = want_y.float()
+            blocks = yy.view(T, N2 // 32, 2, 16)
+            gate, up = blocks[:, :, 0].reshape(T, -1), blocks[:, :, 1].reshape(T, -1)
+            want_act = gate / (1 + torch.exp(-gate)) * up
+            lim = 2e-2 * float(want_act.abs().max()) + 1e-3
+            assert float((act.float() - want_act).abs().max()) <= lim
+            assert float((act.float() - act_b.float()).abs().max()) <= lim
+    ops.check_device_errors()
+
+
+def test_gemm_with_many_tokens_leaves_the_norm_to_the_caller(ops):
+    g = torch.Generator(device=DEV).manual_seed(22)
+    x = torch.randn(200, 256, device=DEV, generator=g).to(torch.bfloat16)
+    w = torch.randn(384, 256, device=DEV, generator=g).to(torch.bfloat16)
+    h = torch.zeros(200, 384, device=DEV)
+    normed = torch.empty(200, 384, device=DEV, dtype=torch.bfloat16)
+    assert ops.gemm(x, w, h, accumulate=True, then_norm=ops.NormOut(torch.ones(384, device=DEV), False, 1e-6, normed)) is None
+    assert float((h.double() - x.double() @ w.double().t()).abs().max()) <= 1e-2
+
+
 def test_gemm_tensor_cores_match_the_plain_kernel(ops):
     g = torch.Generator(device=DEV).manual_seed(14)
     x = torch.randn(40, 512, device=DEV, generator=g).to(torch.bfloat16)
