@@ -392,6 +392,18 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+// The order of tiles.  CTAs that run at the same time take consecutive tiles, so what is fastest decides what they
+// share: with TC_TOKENS_FASTEST (the default) a wave holds few weight tiles, each under all token tiles, and the
+// weight matrix comes from HBM once (x, much smaller, stays in L2); the other order streams all of w once per
+// token tile.
+#ifndef TC_WEIGHTS_FASTEST
+__device__ __forceinline__ int tile_rows(int tile, int tiles_n, int tiles_t) { return tile / tiles_t; }
+__device__ __forceinline__ int tile_tokens(int tile, int tiles_n, int tiles_t) { return tile % tiles_t; }
+#else
+__device__ __forceinline__ int tile_rows(int tile, int tiles_n, int tiles_t) { return tile % tiles_n; }
+__device__ __forceinline__ int tile_tokens(int tile, int tiles_n, int tiles_t) { return tile / tiles_n; }
+#endif
+
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(320) gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                  const __grid_constant__ CUtensorMap map_x,
@@ -432,7 +444,7 @@ __global__ void __launch_bounds__(320) gemm_tc_persistent_kernel(const __grid_co
         int it = 0;                                                   // k-blocks issued so far, over all tiles
         bool ok = true;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-            const int n0 = (tile % tiles_n) * TC_BM, t0 = (tile / tiles_n) * BN;
+            const int n0 = tile_rows(tile, tiles_n, tiles_t) * TC_BM, t0 = tile_tokens(tile, tiles_n, tiles_t) * BN;
             for (int kb = 0; kb < nkb; ++kb, ++it) {
                 const int s = it % STAGES;
                 const uint32_t phase = (it / STAGES) & 1;
@@ -474,7 +486,7 @@ __global__ void __launch_bounds__(320) gemm_tc_persistent_kernel(const __grid_co
         int local = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
-            const int n0 = (tile % tiles_n) * TC_BM, t0 = (tile / tiles_n) * BN;
+            const int n0 = tile_rows(tile, tiles_n, tiles_t) * TC_BM, t0 = tile_tokens(tile, tiles_n, tiles_t) * BN;
             const int buf = local & 1;
             const uint32_t acc_phase = (local >> 1) & 1;
             if (ok && !mbar_wait(&acc_full[buf], acc_phase)) { if (lane == 0) atomicExch(error_flag, 14); ok = false; }
