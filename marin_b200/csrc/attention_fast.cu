@@ -13,7 +13,7 @@
 //    (The reference's counterpart: crates/cuda/src/attention_mma.cu:43-180, f16, whole prompts.)
 //
 // Page layout: [page][kv_head][offset in page][HEAD_DIM]; block_table[request][logical page] -> page.
-#include "common.cuh"
+#include "tc_common.cuh"
 #include "launch.cuh"
 
 #ifndef HEAD_DIM
@@ -93,47 +93,84 @@ __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
+// A float from the shared memory of CTA `rank` of this cluster, at the address `addr` has in this CTA.
+__device__ __forceinline__ float ld_cluster_f32(uint32_t addr, int rank) {
+    uint32_t remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+
 #define LDP (D + 8)                   // padded row of a tile in shared memory (elements): ldmatrix without bank conflicts
 #ifndef DEC_STAGES
 #define DEC_STAGES 3                  // per-warp ring of 16-key stages
 #endif
 #define DEC_STAGE_KEYS 16
+#ifndef DEC_MAX_CLUSTER
+#define DEC_MAX_CLUSTER 8             // most chunks of one sequence that merge as one thread-block cluster
+#endif
 #define DEC_Q_BYTES (16 * LDP * 2)
 #define DEC_STAGE_BYTES (2 * DEC_STAGE_KEYS * LDP * 2)          // keys then values
 #define DEC_WARP_BYTES (DEC_STAGES * DEC_STAGE_BYTES)
 #define DEC_SMEM (DEC_Q_BYTES + DEC_WARPS * DEC_WARP_BYTES)
 static_assert(GROUP * D * 4 <= DEC_WARP_BYTES, "a warp's accumulators are written over its stage buffers");
+// With TMA a stage is dense: per 64 dims one tile of 16 rows x 128 bytes in the 128-byte swizzle (keys, then values).
+#define DEC_TMA (D % 64 == 0)
+#define DEC_TMA_STAGE_BYTES (2 * DEC_STAGE_KEYS * D * 2)
+#define DEC_TMA_SMEM (DEC_Q_BYTES + DEC_WARPS * DEC_STAGES * DEC_TMA_STAGE_BYTES + 1024)
+static_assert(!DEC_TMA || GROUP * D * 4 <= DEC_STAGES * DEC_TMA_STAGE_BYTES, "a warp's accumulators are written over its stage buffers");
 
 // Decode.  A CTA takes `split_keys` consecutive keys (by absolute position) of one kv head of one request; each of
-// its four warps takes a quarter of them and walks it in stages of 16 keys through its own ring of cp.async
-// buffers (three stages in flight per warp, no block-wide barrier in the loop).  The GROUP query heads are rows
+// its four warps takes a quarter of them and walks it in stages of 16 keys through its own ring of buffers
+// (three stages in flight per warp, no block-wide barrier in the loop).  The GROUP query heads are rows
 // 0..GROUP-1 of a 16-row tile (the other rows are zero); S = Q K^T and O = P V are mma.sync.m16n8k16, the
 // softmax runs online in float32 in the exp2 domain.  Partial (m, l, acc) per CTA: m is in log2 units.
+// TMA = true (heads of 64 or 128, pages of at least 16 positions): a stage lies inside one page and one lane
+// fetches it with two or four tensor copies onto the warp's mbarrier, instead of sixteen cp.async per lane.
+template <bool TMA>
 __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_split_kernel(
+    const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
     const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
     const int* __restrict__ block_table, int max_pages, const int* __restrict__ seq_lens, int K, int page_shift,
     float scale, int window, float* __restrict__ part_acc, float* __restrict__ part_ml, int max_chunks, int split_keys,
-    int* __restrict__ counters, bf16* __restrict__ out) {
+    int* __restrict__ counters, bf16* __restrict__ out, int* __restrict__ error_flag, int cluster_merge) {
     PDL_ENTER();
-    extern __shared__ __align__(16) uint8_t dec_smem[];
+    extern __shared__ __align__(16) uint8_t dec_smem_raw[];
+    constexpr int STAGE_BYTES = TMA ? DEC_TMA_STAGE_BYTES : DEC_STAGE_BYTES;
+    constexpr int WARP_BYTES = DEC_STAGES * STAGE_BYTES;
+    uint8_t* dec_smem = TMA ? (uint8_t*)(((uintptr_t)dec_smem_raw + 1023) & ~(uintptr_t)1023) : dec_smem_raw;
     __shared__ float s_m[DEC_WARPS][8], s_l[DEC_WARPS][8];
     __shared__ int s_last;
+    __shared__ uint64_t s_full[DEC_WARPS][DEC_STAGES];
+    __shared__ float c_m[8], c_l[8];                   // this CTA's (max, sum) per query head, for its cluster
     const int chunk = blockIdx.x, kh = blockIdx.y, r = blockIdx.z;
     const int H = K * GROUP;
     const int len = seq_lens[r];
     const int pos = len - 1;
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
     const int c_begin = chunk * split_keys, c_end = min(len, c_begin + split_keys);
-    if (c_begin >= len || c_end <= lo) return;
+    const bool has_work = c_begin < len && c_end > lo;
+    if (!has_work && !cluster_merge) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int* table = block_table + (size_t)r * max_pages;
-    bf16* sQ = reinterpret_cast<bf16*>(dec_smem);
-    uint8_t* ring = dec_smem + DEC_Q_BYTES + (size_t)warp * DEC_WARP_BYTES;
+    uint8_t* ring = dec_smem + (size_t)warp * WARP_BYTES;
+    bf16* sQ = reinterpret_cast<bf16*>(dec_smem + (size_t)DEC_WARPS * WARP_BYTES);
+    float* c_acc = reinterpret_cast<float*>(sQ);       // [GROUP][D] for the cluster, once the query tile is in registers
+    static_assert(GROUP * D * 4 <= DEC_Q_BYTES, "the CTA's partial result is written over the query tile");
+    if (has_work) {
     const int kpw = split_keys / DEC_WARPS;
     const int w_begin = c_begin + warp * kpw, w_stop = min(len, w_begin + kpw);
     const int first = max(w_begin, (lo / DEC_STAGE_KEYS) * DEC_STAGE_KEYS);
     const int n_it = w_stop > first ? (w_stop - first + DEC_STAGE_KEYS - 1) / DEC_STAGE_KEYS : 0;
     constexpr int PIECES = D / 8;
+    if (TMA) {
+        if (lane == 0) {
+            for (int st = 0; st < DEC_STAGES; ++st) mbar_init(&s_full[warp][st], 1);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
+        __syncwarp();
+    }
 
     // stage i: keys first + 16 i .. + 16, K rows then V rows; rows outside [lo, len) are zero
     const int page_mask = (1 << page_shift) - 1;
@@ -141,6 +178,23 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_split_kernel(
     const size_t page_rows = (size_t)K << page_shift;              // rows of a whole page
     // Where this lane's pieces of a stage lie: piece p of row r (rows 0..15 keys, 16..31 values) for idx = lane + 32 j.
     auto issue = [&](int i) {
+        if (TMA) {
+            // the whole stage lies in one page (pages hold at least 16 positions); rows outside [lo, len) come along
+            // and are masked (keys) or cleared (values) when the stage is used
+            if (i < n_it && lane == 0) {
+                uint8_t* dst = ring + (size_t)(i % DEC_STAGES) * STAGE_BYTES;
+                uint64_t* bar = &s_full[warp][i % DEC_STAGES];
+                const int key_base = first + i * DEC_STAGE_KEYS;
+                const int row0 = (int)(((size_t)table[key_base >> page_shift] * K + kh) << page_shift) + (key_base & page_mask);
+                mbar_expect_tx(bar, STAGE_BYTES);
+#pragma unroll
+                for (int hf = 0; hf < D / 64; ++hf) {
+                    tma_load_2d(dst + hf * 2048, &map_k, hf * 64, row0, bar);
+                    tma_load_2d(dst + STAGE_BYTES / 2 + hf * 2048, &map_v, hf * 64, row0, bar);
+                }
+            }
+            return;
+        }
         if (i < n_it) {
             bf16* dst = reinterpret_cast<bf16*>(ring + (size_t)(i % DEC_STAGES) * DEC_STAGE_BYTES);
             const int key_base = first + i * DEC_STAGE_KEYS;
@@ -197,22 +251,50 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_split_kernel(
 #pragma unroll
     for (int i = 0; i < D / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
 
+    // where this lane's ldmatrix rows lie in a swizzled tile: 16-byte chunk c of row r is at r * 128 + ((c ^ (r & 7)) << 4)
+    uint32_t offk[4], offv[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        offk[j] = (uint32_t)(((((lane >> 3) & 1) + 2 * j) ^ (lane & 7)) << 4);
+        offv[j] = (uint32_t)((((lane >> 4) + 2 * j) ^ (lane & 7)) << 4);
+    }
     for (int it = 0; it < n_it; ++it) {
-        cp_async_wait<DEC_STAGES - 1>();
-        __syncwarp();
-        const bf16* sK = reinterpret_cast<const bf16*>(ring + (size_t)(it % DEC_STAGES) * DEC_STAGE_BYTES);
+        const int key_base = first + it * DEC_STAGE_KEYS;
+        const uint8_t* stage = ring + (size_t)(it % DEC_STAGES) * STAGE_BYTES;
+        if (TMA) {
+            const bool arrived = mbar_wait(&s_full[warp][it % DEC_STAGES], (uint32_t)(it / DEC_STAGES) & 1u);
+            if (!__all_sync(0xffffffffu, arrived)) {
+                if (lane == 0) atomicExch(error_flag, 31);
+                break;
+            }
+            if (key_base < lo || key_base + DEC_STAGE_KEYS > len) {
+                // values of positions outside [lo, len) may be anything (0 * NaN is NaN): clear their rows
+                for (int idx = lane; idx < DEC_STAGE_KEYS * PIECES; idx += 32) {
+                    const int row = idx / PIECES, c = idx % PIECES;
+                    const int key = key_base + row;
+                    if (!(key < len && key >= lo))
+                        *reinterpret_cast<uint4*>(const_cast<uint8_t*>(stage) + STAGE_BYTES / 2 + (c >> 3) * 2048 + row * 128 + (c & 7) * 16) = make_uint4(0, 0, 0, 0);
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+            }
+        } else {
+            cp_async_wait<DEC_STAGES - 1>();
+            __syncwarp();
+        }
+        const bf16* sK = reinterpret_cast<const bf16*>(stage);
         const bf16* sV = sK + DEC_STAGE_KEYS * LDP;
         float sc[2][4];
         sc[0][0] = sc[0][1] = sc[0][2] = sc[0][3] = sc[1][0] = sc[1][1] = sc[1][2] = sc[1][3] = 0.0f;
-        const uint32_t k_addr = (uint32_t)__cvta_generic_to_shared(sK + ((lane & 7) + (lane >> 4) * 8) * LDP + ((lane >> 3) & 1) * 8);
+        const uint32_t k_addr = TMA ? smem_u32(stage) + (uint32_t)(((lane & 7) + (lane >> 4) * 8) * 128)
+                                    : (uint32_t)__cvta_generic_to_shared(sK + ((lane & 7) + (lane >> 4) * 8) * LDP + ((lane >> 3) & 1) * 8);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
             uint32_t b0, b1, b2, b3;
-            ldsm_x4(k_addr + kk * 32, b0, b1, b2, b3);
+            ldsm_x4(TMA ? k_addr + (uint32_t)((kk >> 2) * 2048) + offk[kk & 3] : k_addr + kk * 32, b0, b1, b2, b3);
             mma_bf16_16816(sc[0], qa[kk], b0, b1);
             mma_bf16_16816(sc[1], qa[kk], b2, b3);
         }
-        const int key_base = first + it * DEC_STAGE_KEYS;
         if (key_base < lo || key_base + DEC_STAGE_KEYS > len) {            // only the ends of the range need masking
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
@@ -241,11 +323,12 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_split_kernel(
         pa[1] = 0u;
         pa[2] = pack_bf16(sc[1][0], sc[1][1]);
         pa[3] = 0u;
-        const uint32_t v_addr = (uint32_t)__cvta_generic_to_shared(sV + ((lane & 7) + ((lane >> 3) & 1) * 8) * LDP + (lane >> 4) * 8);
+        const uint32_t v_addr = TMA ? smem_u32(stage) + (uint32_t)(STAGE_BYTES / 2 + ((lane & 7) + ((lane >> 3) & 1) * 8) * 128)
+                                    : (uint32_t)__cvta_generic_to_shared(sV + ((lane & 7) + ((lane >> 3) & 1) * 8) * LDP + (lane >> 4) * 8);
 #pragma unroll
         for (int dt = 0; dt < D / 8; dt += 2) {
             uint32_t b0, b1, b2, b3;
-            ldsm_x4_trans(v_addr + dt * 16, b0, b1, b2, b3);
+            ldsm_x4_trans(TMA ? v_addr + (uint32_t)((dt >> 3) * 2048) + offv[(dt >> 1) & 3] : v_addr + dt * 16, b0, b1, b2, b3);
             o[dt][0] *= corr; o[dt][1] *= corr; o[dt + 1][0] *= corr; o[dt + 1][1] *= corr;
             mma_bf16_16816(o[dt], pa, b0, b1);
             mma_bf16_16816(o[dt + 1], pa, b2, b3);
@@ -253,7 +336,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_split_kernel(
         __syncwarp();                                   // the stage is free: refill it
         issue(it + DEC_STAGES);
     }
-    cp_async_wait<0>();
+    if (!TMA) cp_async_wait<0>();
     l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
     l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
 
@@ -279,13 +362,50 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_split_kernel(
 #pragma unroll
         for (int w = 0; w < DEC_WARPS; ++w) {
             const float f = s_m[w][g] == -INFINITY ? 0.0f : exp2f(s_m[w][g] - mm);
-            const float* wacc = reinterpret_cast<const float*>(dec_smem + DEC_Q_BYTES + (size_t)w * DEC_WARP_BYTES);
+            const float* wacc = reinterpret_cast<const float*>(dec_smem + (size_t)w * WARP_BYTES);
             a = fmaf(wacc[g * D + dd], f, a);
             ll = fmaf(s_l[w][g], f, ll);
         }
-        const size_t at = ((size_t)r * H + kh * GROUP + g) * max_chunks + chunk;
-        part_acc[at * D + dd] = a;
-        if (dd == 0) { part_ml[at * 2] = mm; part_ml[at * 2 + 1] = ll; }
+        if (cluster_merge) {
+            c_acc[idx] = a;
+            if (dd == 0) { c_m[g] = mm; c_l[g] = ll; }
+        } else {
+            const size_t at = ((size_t)r * H + kh * GROUP + g) * max_chunks + chunk;
+            part_acc[at * D + dd] = a;
+            if (dd == 0) { part_ml[at * 2] = mm; part_ml[at * 2 + 1] = ll; }
+        }
+    }
+    } else if (threadIdx.x < 8) {
+        c_m[threadIdx.x] = -INFINITY;                  // a chunk outside the sequence (or the window) adds nothing
+        c_l[threadIdx.x] = 0.0f;
+    }
+    if (cluster_merge) {
+        // The chunks of this (request, kv head) are the CTAs of one cluster: after a cluster barrier every CTA combines
+        // its share of the outputs from all partial results, read through distributed shared memory, chunks in
+        // increasing order: out = sum_c acc_c 2^(m_c - M) / sum_c l_c 2^(m_c - M).
+        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+        const int ranks = gridDim.x;
+        const int per = (GROUP * D + ranks - 1) / ranks;
+        const int i_end = min(GROUP * D, (chunk + 1) * per);
+        const uint32_t a_acc = smem_u32(c_acc), a_m = smem_u32(c_m), a_l = smem_u32(c_l);
+        for (int idx = chunk * per + threadIdx.x; idx < i_end; idx += DEC_WARPS * 32) {
+            const int g = idx / D;
+            float mm = -INFINITY;
+            for (int c = 0; c < ranks; ++c) mm = fmaxf(mm, ld_cluster_f32(a_m + g * 4, c));
+            float a = 0.0f, ll = 0.0f;
+            for (int c = 0; c < ranks; ++c) {
+                const float mc = ld_cluster_f32(a_m + g * 4, c);
+                if (mc != -INFINITY) {
+                    const float f = exp2f(mc - mm);
+                    a = fmaf(ld_cluster_f32(a_acc + idx * 4, c), f, a);
+                    ll = fmaf(ld_cluster_f32(a_l + g * 4, c), f, ll);
+                }
+            }
+            out[((size_t)r * H + kh * GROUP) * D + idx] = __float2bfloat16_rn(a / ll);
+        }
+        // nobody leaves while a peer may still read its partial result
+        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+        return;
     }
     // The CTA that finishes last among the chunks of this (request, kv head) combines them:
     // out = sum_c acc_c 2^(m_c - M) / sum_c l_c 2^(m_c - M), chunks in increasing order.  The counter goes back to zero.
@@ -304,7 +424,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_split_kernel(
     const int n_c = c_last - c_first + 1;
     float* wgt = reinterpret_cast<float*>(dec_smem);               // [GROUP][n_c]; the rings are free now
     float* s_total = reinterpret_cast<float*>(s_m);                // [GROUP] sums of l_c * weight
-    const bool fits = (size_t)GROUP * n_c * sizeof(float) <= (size_t)DEC_SMEM;
+    const bool fits = (size_t)GROUP * n_c * sizeof(float) <= (size_t)DEC_WARPS * WARP_BYTES;
     for (int g = warp; g < GROUP && fits; g += DEC_WARPS) {
         const size_t base = ((size_t)r * H + kh * GROUP + g) * max_chunks + c_first;
         float mm = -INFINITY;
@@ -565,24 +685,61 @@ MB_API int mb_attn_head_dim() { return D; }
 MB_API int mb_attn_group() { return GROUP; }
 // Decode: q/out rows 0..requests-1 are the single new tokens of requests 0..requests-1.  A CTA takes split_keys
 // keys (a multiple of 64); part_acc holds requests*H*max_chunks*HEAD_DIM floats and part_ml requests*H*max_chunks*2,
-// with max_chunks >= ceil(longest/split_keys); counters holds requests*K ints that are zero between launches.
+// with max_chunks >= ceil(longest/split_keys); counters holds requests*K ints that are zero between launches;
+// cache_pages pages in each cache; error_flag receives a code if a wait on a copy gives up.
+static int decode_map(CUtensorMap* map, const void* base, uint64_t rows) {
+    EncodeTiled enc = encode_tiled();
+    if (enc == nullptr) return MB_ERR_BAD_SIZE;
+    cuuint64_t dims[2] = {(cuuint64_t)D, rows};
+    cuuint64_t strides[1] = {(cuuint64_t)D * 2};
+    cuuint32_t box[2] = {64, DEC_STAGE_KEYS};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult rc = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return rc == CUDA_SUCCESS ? 0 : 1000 + (int)rc;
+}
+
 MB_API int mb_attn_decode(const void* q, const void* k_cache, const void* v_cache, void* out, const int* block_table,
-                          int max_pages, const int* seq_lens, int requests, int K, int page_size, float scale, int window,
-                          float* part_acc, float* part_ml, int* counters, int max_chunks, int split_keys, cudaStream_t s) {
+                          int max_pages, const int* seq_lens, int requests, int K, int page_size, long long cache_pages,
+                          float scale, int window, float* part_acc, float* part_ml, int* counters, int max_chunks,
+                          int split_keys, int* error_flag, cudaStream_t s) {
     if (requests <= 0) return 0;
-    if (max_chunks <= 0 || K <= 0 || split_keys < 64 || split_keys % 64 != 0) return MB_ERR_BAD_SIZE;
+    if (max_chunks <= 0 || K <= 0 || split_keys < 16 * DEC_WARPS || split_keys % (16 * DEC_WARPS) != 0) return MB_ERR_BAD_SIZE;
     const int page_shift = page_shift_of(page_size);
     if (page_shift < 0) return MB_ERR_BAD_SIZE;
+    dim3 grid(max_chunks, K, requests);
+    // up to eight chunks: they are one cluster and merge through distributed shared memory, without scratch
+    const int cluster_merge = (max_chunks >= 2 && max_chunks <= DEC_MAX_CLUSTER) ? 1 : 0;
+    const int cluster = cluster_merge ? -max_chunks : 0;
+    const uint64_t rows = (uint64_t)cache_pages * K * page_size;
+    const bool tma = DEC_TMA && page_shift >= 4 && error_flag != nullptr && rows > 0 && rows < (1ull << 31) &&
+                     ((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0;
+    CUtensorMap mk = {}, mv = {};
+    if (tma) {
+        int rc = decode_map(&mk, k_cache, rows);
+        if (rc) return rc;
+        rc = decode_map(&mv, v_cache, rows);
+        if (rc) return rc;
+        static bool configured = false;
+        if (!configured) {
+            cudaError_t e = cudaFuncSetAttribute(attn_decode_split_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_TMA_SMEM);
+            if (e != cudaSuccess) return (int)e;
+            configured = true;
+        }
+        return launch_kernel(attn_decode_split_kernel<true>, grid, DEC_WARPS * 32, DEC_TMA_SMEM, s, cluster, mk, mv, (const bf16*)q,
+                             (const bf16*)k_cache, (const bf16*)v_cache, block_table, max_pages, seq_lens, K, page_shift, scale,
+                             window, part_acc, part_ml, max_chunks, split_keys, counters, (bf16*)out, error_flag, cluster_merge);
+    }
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM);
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_split_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_SMEM);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    dim3 grid(max_chunks, K, requests);
-    return launch_kernel(attn_decode_split_kernel, grid, DEC_WARPS * 32, DEC_SMEM, s, 0, (const bf16*)q, (const bf16*)k_cache,
-                         (const bf16*)v_cache, block_table, max_pages, seq_lens, K, page_shift, scale, window, part_acc, part_ml,
-                         max_chunks, split_keys, counters, (bf16*)out);
+    return launch_kernel(attn_decode_split_kernel<false>, grid, DEC_WARPS * 32, DEC_SMEM, s, cluster, mk, mv, (const bf16*)q,
+                         (const bf16*)k_cache, (const bf16*)v_cache, block_table, max_pages, seq_lens, K, page_shift, scale, window,
+                         part_acc, part_ml, max_chunks, split_keys, counters, (bf16*)out, error_flag, cluster_merge);
 }
 
 // Prefill: requests first_req .. first_req+requests-1 of the step, each with its tokens cu_tokens[r]..cu_tokens[r+1].

@@ -38,7 +38,7 @@ static inline bool pdl_enabled() {
     return state == 1;
 }
 
-// cluster_z > 1 launches thread-block clusters of (1, 1, cluster_z).
+// cluster_z > 1 launches thread-block clusters of (1, 1, cluster_z); cluster_z < -1 clusters of (-cluster_z, 1, 1).
 template <typename... KArgs, typename... Args>
 static inline int launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, int cluster_z,
                                 Args... args) {
@@ -54,11 +54,11 @@ static inline int launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block,
         attr[n].val.programmaticStreamSerializationAllowed = 1;
         ++n;
     }
-    if (cluster_z > 1) {
+    if (cluster_z > 1 || cluster_z < -1) {
         attr[n].id = cudaLaunchAttributeClusterDimension;
-        attr[n].val.clusterDim.x = 1;
+        attr[n].val.clusterDim.x = cluster_z < 0 ? (unsigned)(-cluster_z) : 1;
         attr[n].val.clusterDim.y = 1;
-        attr[n].val.clusterDim.z = (unsigned)cluster_z;
+        attr[n].val.clusterDim.z = cluster_z > 0 ? (unsigned)cluster_z : 1;
         ++n;
     }
     cfg.attrs = attr;

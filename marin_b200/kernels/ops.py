@@ -255,15 +255,30 @@ use_fast_attention = True
 use_tc_attention = True
 _attn_scratch = {}
 DECODE_SPLITS = (4096, 2048, 1024, 512, 256, 128, 64)      # keys per CTA the split-KV decode kernel may be given
+DECODE_CLUSTER_CHUNKS = 8                                   # most chunks the kernel merges as one cluster
 
 
 def decode_split(requests: int, kv_heads: int, longest: int):
-    """Keys per CTA and chunks per sequence for decode attention over sequences of up to ``longest`` keys: the
-    largest split that still gives 128 CTAs (long CTAs amortise their start-up and the merge; measured on B200 at
-    batch 1, 8 and 64 and contexts 1024 and 4096)."""
+    """Keys per CTA and chunks per sequence for decode attention over sequences of up to ``longest`` keys.
+
+    Up to eight chunks of one (request, kv head) run as one thread-block cluster and merge through distributed shared
+    memory; that is preferred, with chunks as long as still give 256 CTAs (measured on B200 at batch 1, 8 and 64 and
+    contexts 1024 and 4096).  A few long sequences would leave most SMs idle that way: they get more chunks, merged
+    through scratch memory, as long as still give 128 CTAs."""
+    pairs = requests * kv_heads
+    best = None
     for split in DECODE_SPLITS:
         chunks = -(-longest // split)
-        if requests * kv_heads * chunks >= 128 or split == DECODE_SPLITS[-1]:
+        if chunks > DECODE_CLUSTER_CHUNKS:
+            break
+        best = (split, chunks)
+        if pairs * chunks >= 256:
+            break
+    if best is not None and (pairs * best[1] >= 128 or best[0] <= 1024):
+        return best
+    for split in DECODE_SPLITS:
+        chunks = -(-longest // split)
+        if pairs * chunks >= 128 or split == DECODE_SPLITS[-1]:
             return split, chunks
 
 
@@ -313,9 +328,10 @@ def attention(q, k_cache, v_cache, out, ctx, block_table, H, K, d, scale, window
             split, chunks = getattr(ctx, "attn_split", None) or decode_split(nd, K, ctx.max_seq_len)
             part_acc, part_ml, counters = getattr(ctx, "attn_scratch", None) or _decode_scratch(q.device, nd, H, K, chunks, d)
             _check(lib.mb_attn_decode(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), _c_int(max_pages),
-                                      _ptr(ctx.seq_lens), _c_int(nd), _c_int(K), _c_int(page_size), _c_float(scale),
-                                      _c_int(window), _ptr(part_acc), _ptr(part_ml), _ptr(counters), _c_int(chunks), _c_int(split),
-                                      _stream()), "attention (decode)")
+                                      _ptr(ctx.seq_lens), _c_int(nd), _c_int(K), _c_int(page_size),
+                                      ctypes.c_longlong(k_cache.shape[0]), _c_float(scale), _c_int(window), _ptr(part_acc),
+                                      _ptr(part_ml), _ptr(counters), _c_int(chunks), _c_int(split),
+                                      _ptr(_gemm_scratch(q.device)["error"]), _stream()), "attention (decode)")
         if ctx.num_requests > nd and use_tc_attention and d in (64, 128) and page_size >= 16:
             tc = build.load(f"mb_attention_tc_d{d}_g{H // K}", *build.attention_tc_job(d, H // K))
             _check(tc.mb_attn_prefill_tc(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), _c_int(max_pages),
