@@ -102,6 +102,23 @@ struct TcRowScale {
     float eps;
 };
 
+// A third coupling, for the product that makes queries, keys and values with heads of 128 = one tile of weight rows:
+// instead of writing q|k|v rows, each head is finished where its sums are (per-head RMS norm with weight, half-split
+// rotation by the token's position, crates/model/src/qwen3/layer.rs:59-75) and goes straight to the query buffer or
+// into the paged caches.  Head h < H is a query head, the next K are key heads, the last K value heads (stored as is).
+struct TcHeadsOut {
+    bf16* q_out;              // [T, H * 128]; nullptr: none of this
+    bf16* k_cache;            // [page][K][page_size][128]
+    bf16* v_cache;
+    const float* q_weight;    // [128] or nullptr: no norm
+    const float* k_weight;
+    const int* positions;     // [T]
+    const float* inv_freq;    // [64] or nullptr: no rotation
+    const int* slot_mapping;  // [T]: page * page_size + offset, negative: a padded token, nothing is stored
+    float eps;
+    int H, K, page_size;
+};
+
 __device__ __forceinline__ float group_sum(float v, int width) {       // over aligned groups of `width` lanes (<= 32)
     for (int o = width >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     return v;
@@ -134,9 +151,10 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
                                                       int mode, int T, int N, int K, int kb_per_split,
                                                       float* __restrict__ partials, int* __restrict__ counters,
                                                       int* __restrict__ error_flag, int cluster_reduce,
-                                                      const TcNormOut norm, const TcRowScale scale) {
+                                                      const TcNormOut norm, const TcRowScale scale, const TcHeadsOut heads) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ float s_scale[BN];
+    __shared__ float s_head[TC_BM], s_part[4];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     using L = TcSmem<BN>;
     uint64_t* full = (uint64_t*)(smem + STAGES * L::STAGE_BYTES);
@@ -270,6 +288,59 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
         const int rows_per = TC_BM / splits;                         // splits is 2, 4 or 8
         const int row_first = blockIdx.z * rows_per;
         const int t_count = min(BN, T - t0);
+        if (heads.q_out != nullptr) {
+            // ---- this tile is one head: CTA z finishes tokens z, z + splits, ...; a thread is one element of the head
+            const int head = blockIdx.x, i = threadIdx.x;
+            const bool is_q = head < heads.H, is_k = !is_q && head < heads.H + heads.K;
+            const float* hw = is_q ? heads.q_weight : (is_k ? heads.k_weight : nullptr);
+            const float wi = hw != nullptr ? hw[i] : 1.0f;
+            const bool rotate = (is_q || is_k) && heads.inv_freq != nullptr;
+            const float freq = rotate ? heads.inv_freq[i & 63] : 0.0f;
+            asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+            const uint32_t red_addr = smem_u32(red);
+            for (int tt = blockIdx.z; tt < t_count; tt += splits) {
+                const int t = t0 + tt;
+                float sum = 0.0f;
+                for (int z = 0; z < splits; ++z) {
+                    uint32_t remote;
+                    float pv;
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(red_addr + (uint32_t)(tt * TC_BM + i) * 4u), "r"(z));
+                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(pv) : "r"(remote) : "memory");
+                    sum += pv;
+                }
+                if (scale.sumsq != nullptr) sum *= s_scale[tt];
+                // rounded to bf16 here, as the q|k|v rows are when they are written out and normed by a second kernel
+                float v = __bfloat162float(__float2bfloat16_rn(sum));
+                if (hw != nullptr) {
+                    const float ss = group_sum(v * v, 32);
+                    if (lane == 0) s_part[warp] = ss;
+                    __syncthreads();
+                    const float total = ((s_part[0] + s_part[1]) + s_part[2]) + s_part[3];
+                    v = v * (1.0f / sqrtf(total / (float)TC_BM + heads.eps)) * wi;
+                }
+                if (rotate) {
+                    s_head[i] = v;
+                    __syncthreads();
+                    const float other = s_head[i ^ 64];
+                    float sn, cs;
+                    sincosf((float)heads.positions[t] * freq, &sn, &cs);
+                    v = i < 64 ? v * cs - other * sn : v * cs + other * sn;
+                }
+                if (is_q) {
+                    heads.q_out[((size_t)t * heads.H + head) * TC_BM + i] = __float2bfloat16_rn(v);
+                } else {
+                    const int slot = heads.slot_mapping[t];
+                    if (slot >= 0) {
+                        const int kh = is_k ? head - heads.H : head - heads.H - heads.K;
+                        bf16* cache = is_k ? heads.k_cache : heads.v_cache;
+                        cache[(((size_t)(slot / heads.page_size) * heads.K + kh) * heads.page_size + (size_t)(slot % heads.page_size)) * TC_BM + i] =
+                            __float2bfloat16_rn(v);
+                    }
+                }
+                __syncthreads();                                      // s_part and s_head are used again
+            }
+            asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+        } else {
         // what the first trip below needs from global memory is asked for before the cluster meets
         float old0 = 0.0f, g0 = 0.0f;
         {
@@ -324,6 +395,7 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
         }
         // nobody leaves while a peer may still read its tile
         asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+        }
     } else {
 #pragma unroll 1
     for (int c0 = 0; c0 < BN; c0 += 16) {
@@ -534,7 +606,7 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int K, int box
 template <int BN, int STAGES>
 static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int mode, int T, int N, int K, int splits,
                      int kb_per_split, float* partials, int* counters, int* error_flag, int cluster_reduce,
-                     const TcNormOut& norm, const TcRowScale& scale, cudaStream_t s) {
+                     const TcNormOut& norm, const TcRowScale& scale, const TcHeadsOut& heads, cudaStream_t s) {
     constexpr int smem = STAGES * TcSmem<BN>::STAGE_BYTES + 1024 + 256;
     static_assert(STAGES * TcSmem<BN>::STAGE_BYTES >= BN * TC_BM * 4, "the cluster reduction reuses the pipeline buffers");
     static bool configured = false;
@@ -546,7 +618,7 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* out, in
     const bool clustered = cluster_reduce && splits > 1;
     return launch_kernel(gemm_tc_kernel<BN, STAGES>, dim3((N + TC_BM - 1) / TC_BM, (T + BN - 1) / BN, splits), dim3(128), smem, s,
                          clustered ? splits : 0, mw, mx, out, mode, T, N, K, kb_per_split, partials, counters, error_flag,
-                         clustered ? 1 : 0, norm, scale);
+                         clustered ? 1 : 0, norm, scale, heads);
 }
 
 // Tiles a launch with `bn` tokens per CTA would have (for the caller's choice of split).
@@ -598,8 +670,10 @@ MB_API int mb_gemm_tc_persistent(const void* x, const void* w, void* out, int mo
 // (one zeroed int per tile).  bn in {16, 32, 64, 128, 256}.
 static int gemm_tc_dispatch(const void* x, const void* w, void* out, int mode, int T, int N, int K, int bn, int splits,
                             float* partials, int* counters, int* error_flag, int cluster_reduce, const TcNormOut& norm,
-                            const TcRowScale& scale, cudaStream_t s) {
+                            const TcRowScale& scale, const TcHeadsOut& heads, cudaStream_t s) {
     if (T <= 0 || N <= 0) return 0;
+    // heads are finished only where the K slices of a tile meet as a cluster
+    if (heads.q_out != nullptr && (!cluster_reduce || splits < 2 || N % TC_BM != 0 || bn > 16 || T > bn)) return MB_ERR_BAD_SIZE;
     // the norm's side outputs exist for "+=" without global split-K scratch
     if (norm.weight != nullptr && (mode != TC_OUT_F32_ACC || norm.scaled == nullptr || norm.sumsq == nullptr)) return MB_ERR_BAD_DTYPE;
     if (norm.weight != nullptr && !cluster_reduce && splits > 1) return MB_ERR_BAD_SIZE;
@@ -624,11 +698,11 @@ static int gemm_tc_dispatch(const void* x, const void* w, void* out, int mode, i
     rc = make_map(&mx, x, T, K, bn);
     if (rc) return rc;
     switch (bn) {
-        case 16: return launch_tc<16, 6>(mw, mx, out, mode, T, N, K, splits, kb_per_split, partials, counters, error_flag, cluster_reduce, norm, scale, s);
-        case 32: return launch_tc<32, 5>(mw, mx, out, mode, T, N, K, splits, kb_per_split, partials, counters, error_flag, cluster_reduce, norm, scale, s);
-        case 64: return launch_tc<64, 4>(mw, mx, out, mode, T, N, K, splits, kb_per_split, partials, counters, error_flag, cluster_reduce, norm, scale, s);
-        case 128: return launch_tc<128, 3>(mw, mx, out, mode, T, N, K, splits, kb_per_split, partials, counters, error_flag, cluster_reduce, norm, scale, s);
-        case 256: return launch_tc<256, 4>(mw, mx, out, mode, T, N, K, splits, kb_per_split, partials, counters, error_flag, cluster_reduce, norm, scale, s);
+        case 16: return launch_tc<16, 6>(mw, mx, out, mode, T, N, K, splits, kb_per_split, partials, counters, error_flag, cluster_reduce, norm, scale, heads, s);
+        case 32: return launch_tc<32, 5>(mw, mx, out, mode, T, N, K, splits, kb_per_split, partials, counters, error_flag, cluster_reduce, norm, scale, heads, s);
+        case 64: return launch_tc<64, 4>(mw, mx, out, mode, T, N, K, splits, kb_per_split, partials, counters, error_flag, cluster_reduce, norm, scale, heads, s);
+        case 128: return launch_tc<128, 3>(mw, mx, out, mode, T, N, K, splits, kb_per_split, partials, counters, error_flag, cluster_reduce, norm, scale, heads, s);
+        case 256: return launch_tc<256, 4>(mw, mx, out, mode, T, N, K, splits, kb_per_split, partials, counters, error_flag, cluster_reduce, norm, scale, heads, s);
         default: return MB_ERR_BAD_SIZE;
     }
 }
@@ -638,14 +712,14 @@ static int gemm_tc_dispatch(const void* x, const void* w, void* out, int mode, i
 // (one zeroed int per tile).  bn in {16, 32, 64, 128, 256}.
 MB_API int mb_gemm_tc(const void* x, const void* w, void* out, int mode, int T, int N, int K, int bn, int splits,
                       float* partials, int* counters, int* error_flag, cudaStream_t s) {
-    return gemm_tc_dispatch(x, w, out, mode, T, N, K, bn, splits, partials, counters, error_flag, 0, TcNormOut{}, TcRowScale{}, s);
+    return gemm_tc_dispatch(x, w, out, mode, T, N, K, bn, splits, partials, counters, error_flag, 0, TcNormOut{}, TcRowScale{}, TcHeadsOut{}, s);
 }
 
 // The same product with the K slices of a tile as one thread-block cluster (splits in {1, 2, 4, 8}): the slices
 // are added through distributed shared memory, no global scratch is touched.
 MB_API int mb_gemm_tc_cluster(const void* x, const void* w, void* out, int mode, int T, int N, int K, int bn, int splits,
                               int* error_flag, cudaStream_t s) {
-    return gemm_tc_dispatch(x, w, out, mode, T, N, K, bn, splits, nullptr, nullptr, error_flag, 1, TcNormOut{}, TcRowScale{}, s);
+    return gemm_tc_dispatch(x, w, out, mode, T, N, K, bn, splits, nullptr, nullptr, error_flag, 1, TcNormOut{}, TcRowScale{}, TcHeadsOut{}, s);
 }
 
 // Slots of sums of squares per token that a "+=" product over N weight rows with `splits` K slices writes.
@@ -661,7 +735,22 @@ MB_API int mb_gemm_tc_coupled(const void* x, const void* w, void* out, int mode,
                               cudaStream_t s) {
     TcNormOut norm{norm_weight, (bf16*)scaled_out, sumsq_out, norm_unit_offset};
     TcRowScale scale{scale_sumsq, scale_slots, scale_dim, scale_eps};
-    return gemm_tc_dispatch(x, w, out, mode, T, N, K, bn, splits, nullptr, nullptr, error_flag, 1, norm, scale, s);
+    return gemm_tc_dispatch(x, w, out, mode, T, N, K, bn, splits, nullptr, nullptr, error_flag, 1, norm, scale, TcHeadsOut{}, s);
+}
+
+// The q|k|v product of at most 16 tokens with heads of 128 elements, each head finished in the epilogue (see
+// TcHeadsOut): w is [(H + 2 K) * 128, Kdim] (or [H * 128, Kdim]: queries only, when k_cache is null); splits >= 2.
+// q_weight / k_weight null: no norm; inv_freq null: no rotation.  scale_*: as for mb_gemm_tc_coupled.
+MB_API int mb_gemm_tc_heads(const void* x, const void* w, int T, int N, int K, int splits, void* q_out, void* k_cache, void* v_cache,
+                            const float* q_weight, const float* k_weight, float eps, const int* positions, const float* inv_freq,
+                            const int* slot_mapping, int H, int KV, int page_size, const float* scale_sumsq, int scale_slots,
+                            int scale_dim, float scale_eps, int* error_flag, cudaStream_t s) {
+    if (q_out == nullptr || H <= 0 || KV < 0 || (N != H * TC_BM && N != (H + 2 * KV) * TC_BM)) return MB_ERR_BAD_SIZE;
+    if (N != H * TC_BM && (k_cache == nullptr || v_cache == nullptr || slot_mapping == nullptr || page_size <= 0)) return MB_ERR_BAD_SIZE;
+    if (inv_freq != nullptr && positions == nullptr) return MB_ERR_BAD_SIZE;
+    TcHeadsOut heads{(bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, q_weight, k_weight, positions, inv_freq, slot_mapping, eps, H, KV, page_size};
+    TcRowScale scale{scale_sumsq, scale_slots, scale_dim, scale_eps};
+    return gemm_tc_dispatch(x, w, nullptr, TC_OUT_BF16, T, N, K, 16, splits, nullptr, nullptr, error_flag, 1, TcNormOut{}, scale, heads, s);
 }
 
 // ---- the entry point that allocates nothing (see gemm_tc_noalloc.h) --------------------------------------------

@@ -233,6 +233,45 @@ def gemm(x, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False, then_n
     return None
 
 
+#: with few tokens the q|k|v product finishes its heads itself (norm, rotation, cache write) where the layout allows
+fuse_heads = True
+FUSED_HEADS_MAX_TOKENS = 16
+
+
+def gemm_qkv_heads(x, w: torch.Tensor, q_out: torch.Tensor, q_weight, k_weight, eps: float, positions, inv_freq, rotary_dim: int,
+                   interleaved: bool, slot_mapping, k_cache, v_cache, H: int, K: int, d: int, write_kv: bool = True) -> bool:
+    """The product ``x w^T`` of a few tokens with ``w`` = query, key and value rows (or query rows only), each head
+    normed, rotated and stored by the product's own epilogue: queries to ``q_out``, keys and values into the paged
+    caches at ``slot_mapping``.  Returns False, having done nothing, where this does not apply (many tokens, heads
+    that are not 128 wide, a partial or interleaved rotation, float32): the caller then runs ``gemm`` and
+    ``qk_norm_rope_write``."""
+    scaled = x if isinstance(x, NormedRows) else None
+    rows = scaled.rows if scaled is not None else x
+    T, Kdim = rows.shape
+    N = w.shape[0]
+    heads_total = H + 2 * K if write_kv else H
+    if not (fuse_heads and use_tensor_cores and rows.is_cuda and rows.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+            and q_out.dtype == torch.bfloat16 and d == 128 and 0 < T <= FUSED_HEADS_MAX_TOKENS and N == heads_total * d
+            and Kdim % 8 == 0 and not interleaved and (inv_freq is None or rotary_dim == d)
+            and rows.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and (not write_kv or k_cache.dtype == torch.bfloat16)):
+        return False
+    bn, splits = gemm_plan(T, N, Kdim)
+    if bn != 16 or splits < 2:
+        return False
+    _need_cuda(rows, w, q_out)
+    assert tuple(q_out.shape) == (T, H * d) and w.shape[1] == Kdim
+    s = _gemm_scratch(rows.device)
+    page_size = k_cache.shape[2] if write_kv else 0
+    _check(_lib("mb_gemm_tc").mb_gemm_tc_heads(
+        _ptr(rows), _ptr(w), _c_int(T), _c_int(N), _c_int(Kdim), _c_int(splits), _ptr(q_out),
+        _ptr(k_cache) if write_kv else None, _ptr(v_cache) if write_kv else None, _ptr(q_weight), _ptr(k_weight), _c_float(eps),
+        _ptr(positions), _ptr(inv_freq), _ptr(slot_mapping) if write_kv else None, _c_int(H), _c_int(K), _c_int(page_size),
+        _ptr(scaled.sumsq) if scaled is not None else None, _c_int(scaled.slots if scaled is not None else 0),
+        _c_int(scaled.dim if scaled is not None else 0), _c_float(scaled.eps if scaled is not None else 0.0),
+        _ptr(s["error"]), _stream()), "gemm with heads finished in the epilogue")
+    return True
+
+
 def qk_norm_rope_write(qkv, q_out, q_weight, k_weight, eps, positions, inv_freq, rotary_dim, interleaved,
                        slot_mapping, k_cache, v_cache, H, K, d, write_kv=True) -> None:
     _need_cuda(qkv, q_out, q_weight, k_weight, positions, inv_freq, slot_mapping, k_cache, v_cache)

@@ -115,20 +115,20 @@ class GQAttention(Mixer):
         T = x.shape[0]
         ws = ctx.workspace
         writes = cache.owner
-        if writes:
-            qkv = ws.get("qkv", (T, self.q_dim + 2 * self.kv_dim), x.dtype)
-            ops.gemm(x, self.w_qkv, qkv)
-        else:
-            # This run reads another run's cache: only the queries are computed.
-            qkv = ws.get("qkv", (T, self.q_dim), x.dtype)
-            ops.gemm(x, self.w_qkv[: self.q_dim], qkv)
-        q = ws.get("q", (T, self.q_dim), x.dtype)
         pos = self.position
-        ops.qk_norm_rope_write(
-            qkv, q, self.q_weight, self.k_weight, self.norm_eps, ctx.positions,
-            pos.inv_freq, pos.rotary_dim, pos.interleaved, cache.slot_mapping,
-            cache.k, cache.v, self.heads, self.kv_heads, self.head_dim, writes,
-        )
+        q = ws.get("q", (T, self.q_dim), x.dtype)
+        # A run that reads another run's cache computes only the queries.
+        w = self.w_qkv if writes else self.w_qkv[: self.q_dim]
+        if not ops.gemm_qkv_heads(x, w, q, self.q_weight, self.k_weight, self.norm_eps, ctx.positions, pos.inv_freq,
+                                  pos.rotary_dim, pos.interleaved, cache.slot_mapping, cache.k, cache.v, self.heads,
+                                  self.kv_heads, self.head_dim, writes):
+            qkv = ws.get("qkv", (T, w.shape[0]), x.dtype)
+            ops.gemm(x, w, qkv)
+            ops.qk_norm_rope_write(
+                qkv, q, self.q_weight, self.k_weight, self.norm_eps, ctx.positions,
+                pos.inv_freq, pos.rotary_dim, pos.interleaved, cache.slot_mapping,
+                cache.k, cache.v, self.heads, self.kv_heads, self.head_dim, writes,
+            )
         out = ws.get("attn_out", (T, self.q_dim), x.dtype)
         ops.attention(q, cache.k, cache.v, out, ctx, cache.block_table, self.heads, self.kv_heads,
                       self.head_dim, self.scale, self.window or 0)

@@ -32,6 +32,10 @@ def gemm(x, w, out, accumulate=False, then_norm=None):
         out.copy_(y.to(out.dtype))
 
 
+def gemm_qkv_heads(*args, **kwargs):
+    return False
+
+
 def qk_norm_rope_write(qkv, q_out, q_weight, k_weight, eps, positions, inv_freq, rotary_dim, interleaved,
                        slot_mapping, k_cache, v_cache, H, K, d, write_kv=True):
     T = qkv.shape[0]
@@ -152,7 +156,7 @@ def sample(logits, usable, temperature, top_k, top_p, uniform, out):
 
 
 NAMES = ["sample", "embed", "rmsnorm", "gemm", "qk_norm_rope_write", "attention", "swiglu", "gather_rows", "add_into", "argmax",
-         "interleave_gate_up", "can_fuse_swiglu", "gemm_swiglu"]
+         "interleave_gate_up", "can_fuse_swiglu", "gemm_swiglu", "gemm_qkv_heads"]
 
 
 @contextmanager

@@ -378,6 +378,59 @@ def test_gemm_with_many_tokens_leaves_the_norm_to_the_caller(ops):
     assert float((h.double() - x.double() @ w.double().t()).abs().max()) <= 1e-2
 
 
+@pytest.mark.parametrize("T,H,K,hidden,norm,rope,write", [(8, 32, 8, 2560, True, True, True), (1, 4, 2, 512, True, True, True),
+                                                         (16, 6, 3, 1024, False, True, True), (5, 8, 1, 768, True, False, True),
+                                                         (3, 4, 4, 512, True, True, False)])
+def test_qkv_product_finishes_its_heads(ops, T, H, K, hidden, norm, rope, write):
+    """The q|k|v product with norm, rotation and cache write in its epilogue, against the product followed by the
+    kernel that does the same on its own."""
+    d, page = 128, 16
+    g = torch.Generator(device=DEV).manual_seed(31)
+    heads_total = H + 2 * K if write else H
+    x = torch.randn(T, hidden, device=DEV, generator=g).to(torch.bfloat16)
+    w = (torch.randn(heads_total * d, hidden, device=DEV, generator=g) / math.sqrt(hidden)).to(torch.bfloat16)
+    w[:, 0] += (torch.arange(heads_total * d, device=DEV) % 128).to(torch.bfloat16) * 0.03       # rows distinguishable
+    qw = (1 + 0.1 * torch.randn(d, device=DEV, generator=g)) if norm else None
+    kw = (1 + 0.1 * torch.randn(d, device=DEV, generator=g)) if norm else None
+    positions = torch.randint(0, 40000, (T,), device=DEV, generator=g, dtype=torch.int32)
+    inv_freq = torch.pow(torch.tensor(1e6), -(torch.arange(d // 2, dtype=torch.float32) * 2.0 / d)).to(DEV) if rope else None
+    pages = 8
+    slots = torch.randperm(pages * page, device=DEV, generator=g)[:T].to(torch.int32)
+    if T > 2:
+        slots[2] = -1
+    caches = [torch.zeros(pages, K, page, d, device=DEV, dtype=torch.bfloat16) for _ in range(4)]
+    q1 = torch.full((T, H * d), float("nan"), device=DEV, dtype=torch.bfloat16)
+    q2 = torch.empty_like(q1)
+    for _ in range(2):
+        done = ops.gemm_qkv_heads(x, w, q1, qw, kw, 1e-6, positions, inv_freq, d if rope else 0, False, slots, caches[0], caches[1],
+                                  H, K, d, write)
+        ops.check_device_errors()
+    bn, splits = ops.gemm_plan(T, heads_total * d, hidden)
+    assert done == (splits > 1)
+    if not done:
+        pytest.skip("this shape keeps K whole: no cluster to finish the heads in")
+    qkv = torch.empty(T, heads_total * d, device=DEV, dtype=torch.bfloat16)
+    ops.gemm(x, w, qkv)
+    ops.qk_norm_rope_write(qkv, q2, qw, kw, 1e-6, positions, inv_freq, d if rope else 0, False, slots, caches[2], caches[3], H, K, d, write)
+    tol = dict(rtol=1.6e-2, atol=2e-2)
+    torch.testing.assert_close(q1.float(), q2.float(), **tol)
+    torch.testing.assert_close(caches[0].float(), caches[2].float(), **tol)
+    torch.testing.assert_close(caches[1].float(), caches[3].float(), **tol)
+    if write:
+        assert float(caches[0].float().abs().sum()) > 0 and float(caches[1].float().abs().sum()) > 0
+
+
+def test_qkv_product_declines_what_it_cannot_finish(ops):
+    x = torch.zeros(40, 256, device=DEV, dtype=torch.bfloat16)
+    w = torch.zeros(4 * 128, 256, device=DEV, dtype=torch.bfloat16)
+    q = torch.zeros(40, 2 * 128, device=DEV, dtype=torch.bfloat16)
+    cache = torch.zeros(4, 1, 16, 128, device=DEV, dtype=torch.bfloat16)
+    slots = torch.zeros(40, device=DEV, dtype=torch.int32)
+    assert not ops.gemm_qkv_heads(x, w, q, None, None, 1e-6, slots, None, 0, False, slots, cache, cache, 2, 1, 128, True)       # many tokens
+    assert not ops.gemm_qkv_heads(x[:4], w[:, :], q[:4, :128].contiguous(), None, None, 1e-6, slots, None, 0, False, slots, cache,
+                                  cache, 2, 1, 64, True)                                                                      # heads of 64
+
+
 def test_gemm_tensor_cores_match_the_plain_kernel(ops):
     g = torch.Generator(device=DEV).manual_seed(14)
     x = torch.randn(40, 512, device=DEV, generator=g).to(torch.bfloat16)
