@@ -139,7 +139,7 @@ LIBRARIES: Dict[str, List[str]] = {
 
 #: (head size, query heads per kv head) the fast attention kernels are built for by ``build_all``; any other
 #: layout a model brings is compiled when that model first runs
-ATTENTION_LAYOUTS = [(128, 4), (128, 5), (16, 2), (32, 4), (48, 2)]
+ATTENTION_LAYOUTS = [(128, 4), (128, 5), (128, 2), (16, 2), (32, 4), (48, 2)]
 
 
 def build_many(jobs: Dict[str, tuple], verbose: bool = True) -> List[str]:

@@ -28,8 +28,18 @@ TINY_C = {
     "num_key_value_heads": 3, "head_dim": 48, "intermediate_size": 136, "vocab_size": 333, "rope_theta": 500000.0,
     "rms_norm_eps": 3e-6, "tie_word_embeddings": False, "max_position_embeddings": 192,
 }
-PAGE = {"A": 4, "B": 8, "C": 16}
-CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+# Heads of 128 and a width that lets the matrix products cut K: the layout the tensor-core attention kernels, the TMA
+# decode kernel and the fused epilogues (heads finished by the q|k|v product, norms riding on products) are made for.
+TINY_D = {
+    "model_type": "qwen3", "num_hidden_layers": 2, "hidden_size": 512, "num_attention_heads": 4,
+    "num_key_value_heads": 2, "head_dim": 128, "intermediate_size": 640, "vocab_size": 500, "rope_theta": 1000000.0,
+    "rms_norm_eps": 1e-6, "tie_word_embeddings": True, "max_position_embeddings": 160,
+}
+PAGE = {"A": 4, "B": 8, "C": 16, "D": 16}
+# Standard deviation of the random matrices: about 1 / sqrt(width), so that logits keep a standard deviation near 1
+# (the bfloat16 tolerances are absolute and stated for such logits).
+MATRIX_STD = {"A": 0.1, "B": 0.1, "C": 0.1, "D": 0.05}
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
 
 
 def make_model_dir(path: str, raw: dict, seed: int, dtype=torch.float32, matrix_std: float = 0.02) -> str:

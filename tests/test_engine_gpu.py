@@ -15,14 +15,15 @@ import pytest
 import torch
 
 import plain_qwen3 as plain
-from helpers import CONFIGS, PAGE, make_model_dir, mixed_schedule, portions, random_prompt, run_mixed, run_portions, run_whole
+from helpers import MATRIX_STD, CONFIGS, PAGE, make_model_dir, mixed_schedule, portions, random_prompt, run_mixed, run_portions, run_whole
 
 pytestmark = pytest.mark.gpu
 
 DTYPES = ["float32", "bfloat16"]
 LENGTHS = {"A": {"a": 37, "b": 9, "c": 120, "d": 1, "e": 64, "f": 40, "g": 33},
            "B": {"a": 100, "b": 1, "c": 250, "d": 17, "e": 64, "f": 129, "g": 48},
-           "C": {"a": 50, "b": 180, "c": 16, "d": 97, "e": 2, "f": 33}}
+           "C": {"a": 50, "b": 180, "c": 16, "d": 97, "e": 2, "f": 33},
+           "D": {"a": 150, "b": 21, "c": 64, "d": 3, "e": 129, "f": 40}}
 
 
 def close(got: torch.Tensor, want: torch.Tensor, dtype: str, what=""):
@@ -49,7 +50,7 @@ class Case:
 
         raw = CONFIGS[name]
         self.name, self.dtype, self.raw = name, dtype, raw
-        self.dir = make_model_dir(str(tmp / f"{name}-{dtype}"), raw, seed=11, dtype=parse_dtype(dtype), matrix_std=0.1)
+        self.dir = make_model_dir(str(tmp / f"{name}-{dtype}"), raw, seed=11, dtype=parse_dtype(dtype), matrix_std=MATRIX_STD[name])
         self.cfg, self.w = plain.read_config(self.dir), plain.read_weights(self.dir)
         rng = random.Random(5)
         self.tokens = {rid: random_prompt(rng, raw["vocab_size"], n) for rid, n in LENGTHS[name].items()}
@@ -71,7 +72,7 @@ class Case:
         return runner
 
 
-@pytest.fixture(scope="module", params=[(n, d) for n in "ABC" for d in DTYPES], ids=lambda p: f"{p[0]}-{p[1]}")
+@pytest.fixture(scope="module", params=[(n, d) for n in "ABCD" for d in DTYPES], ids=lambda p: f"{p[0]}-{p[1]}")
 def case(request, tmp_path_factory):
     return Case(tmp_path_factory.mktemp("models"), *request.param)
 

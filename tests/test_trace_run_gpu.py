@@ -12,7 +12,7 @@ import pytest
 import torch
 
 import plain_qwen3 as plain
-from helpers import CONFIGS, make_model_dir, mixed_schedule, portions, random_prompt
+from helpers import MATRIX_STD, CONFIGS, make_model_dir, mixed_schedule, portions, random_prompt
 from test_engine_gpu import close
 
 pytestmark = pytest.mark.gpu
@@ -43,11 +43,11 @@ def replay(model_dir, dtype, out_dir, max_tokens, steps, vocab):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "D"])
 def test_trace_replay_modes(tmp_path, name, dtype):
     raw = CONFIGS[name]
     vocab = raw["vocab_size"]
-    d = make_model_dir(str(tmp_path / "model"), raw, seed=21, dtype=torch.float32 if dtype == "float32" else torch.bfloat16, matrix_std=0.1)
+    d = make_model_dir(str(tmp_path / "model"), raw, seed=21, dtype=torch.float32 if dtype == "float32" else torch.bfloat16, matrix_std=MATRIX_STD[name])
     cfg, w = plain.read_config(d), plain.read_weights(d)
     rng = random.Random(2)
     cap = raw["max_position_embeddings"]
