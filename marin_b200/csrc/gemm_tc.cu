@@ -341,55 +341,79 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
             }
             asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
         } else {
-        // what the first trip below needs from global memory is asked for before the cluster meets
-        float old0 = 0.0f, g0 = 0.0f;
-        {
-            const int tt = threadIdx.x / rows_per, row = row_first + threadIdx.x % rows_per;
-            if (threadIdx.x < t_count * rows_per && n0 + row < N) {
-                if (mode == TC_OUT_F32_ACC) old0 = ((const float*)out)[(size_t)(t0 + tt) * N + n0 + row];
-                if (norm.weight != nullptr) g0 = norm.weight[n0 + row];
-            }
+        // Trips of 128 (token, row) pairs, four at a time: all loads of the four (the old values from global memory,
+        // then the slices from the peers' shared memory) are asked for before any is used, so their latencies overlap.
+        // What the first four need from global memory is asked for before the cluster meets.
+        constexpr int U = BN >= 64 ? 4 : (BN >= 32 ? 2 : 1);
+        const int total = t_count * rows_per;
+        const bool acc_mode = mode == TC_OUT_F32_ACC;
+        float old[U], gain[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int idx = u * 128 + threadIdx.x;
+            const int tt = idx / rows_per, row = row_first + idx % rows_per;
+            const bool valid = idx < total && n0 + row < N;
+            old[u] = (acc_mode && valid) ? ((const float*)out)[(size_t)(t0 + tt) * N + n0 + row] : 0.0f;
+            gain[u] = (norm.weight != nullptr && valid) ? norm.weight[n0 + row] : 0.0f;
         }
         asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
         const uint32_t red_addr = smem_u32(red);
         const int group = rows_per < 32 ? rows_per : 32;             // rows whose squares are added into one slot
         const int slots_per_tile = splits < 4 ? 4 : splits;
-        for (int base = 0; base < t_count * rows_per; base += 128) {  // every thread makes every trip (shuffles below)
-            const int idx = base + threadIdx.x;
-            const bool active = idx < t_count * rows_per;
-            const int tt = idx / rows_per, in_slice = idx % rows_per, row = row_first + in_slice;
-            float sum = 0.0f;
-            if (active) {
-                for (int z = 0; z < splits; ++z) {
-                    uint32_t remote;
-                    float pv;
-                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(red_addr + (uint32_t)(tt * TC_BM + row) * 4u), "r"(z));
-                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(pv) : "r"(remote) : "memory");
-                    sum += pv;
+        for (int base = 0; base < total; base += 128 * U) {           // every thread makes every trip (shuffles below)
+            if (base > 0) {
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const int idx = base + u * 128 + threadIdx.x;
+                    const int tt = idx / rows_per, row = row_first + idx % rows_per;
+                    const bool valid = idx < total && n0 + row < N;
+                    old[u] = (acc_mode && valid) ? ((const float*)out)[(size_t)(t0 + tt) * N + n0 + row] : 0.0f;
+                    gain[u] = (norm.weight != nullptr && valid) ? norm.weight[n0 + row] : 0.0f;
                 }
-                if (scale.sumsq != nullptr) sum *= s_scale[tt];
             }
-            const bool valid = active && n0 + row < N;
-            const size_t at = (size_t)(t0 + tt) * N + n0 + row;
-            float nv = 0.0f;
-            if (valid) {
-                if (mode == TC_OUT_F32_ACC) {
-                    nv = (base == 0 ? old0 : ((const float*)out)[at]) + sum;
-                    ((float*)out)[at] = nv;
-                    if (norm.weight != nullptr) {
-                        float g = base == 0 ? g0 : norm.weight[n0 + row];
-                        if (norm.unit_offset) g += 1.0f;
-                        norm.scaled[at] = __float2bfloat16_rn(nv * g);
+            float pv[U][8];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int idx = base + u * 128 + threadIdx.x;
+                const int tt = idx / rows_per, row = row_first + idx % rows_per;
+#pragma unroll
+                for (int z = 0; z < 8; ++z) {
+                    pv[u][z] = 0.0f;
+                    if (z < splits && idx < total) {
+                        uint32_t remote;
+                        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(red_addr + (uint32_t)(tt * TC_BM + row) * 4u), "r"(z));
+                        asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(pv[u][z]) : "r"(remote) : "memory");
                     }
-                } else {
-                    store_out(out, mode, at, sum);
                 }
             }
-            if (norm.weight != nullptr) {
-                const float sq = group_sum(nv * nv, group);
-                if (active && in_slice % group == 0) {
-                    const int slot = blockIdx.x * slots_per_tile + blockIdx.z * (slots_per_tile / splits) + in_slice / group;
-                    norm.sumsq[(size_t)slot * T + t0 + tt] = sq;
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                if (base + u * 128 >= total) break;                   // the same for every thread
+                const int idx = base + u * 128 + threadIdx.x;
+                const bool active = idx < total;
+                const int tt = idx / rows_per, in_slice = idx % rows_per, row = row_first + in_slice;
+                float sum = 0.0f;
+#pragma unroll
+                for (int z = 0; z < 8; ++z) sum += pv[u][z];          // slices beyond `splits` are zero
+                if (scale.sumsq != nullptr && active) sum *= s_scale[tt];
+                const bool valid = active && n0 + row < N;
+                const size_t at = (size_t)(t0 + tt) * N + n0 + row;
+                float nv = 0.0f;
+                if (valid) {
+                    if (acc_mode) {
+                        nv = old[u] + sum;
+                        ((float*)out)[at] = nv;
+                        if (norm.weight != nullptr) norm.scaled[at] = __float2bfloat16_rn(nv * (norm.unit_offset ? gain[u] + 1.0f : gain[u]));
+                    } else {
+                        store_out(out, mode, at, sum);
+                    }
+                }
+                if (norm.weight != nullptr) {
+                    const float sq = group_sum(nv * nv, group);
+                    if (active && in_slice % group == 0) {
+                        const int slot = blockIdx.x * slots_per_tile + blockIdx.z * (slots_per_tile / splits) + in_slice / group;
+                        norm.sumsq[(size_t)slot * T + t0 + tt] = sq;
+                    }
                 }
             }
         }
