@@ -14,33 +14,78 @@ one (page, kv head) tile is contiguous.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+import ctypes
+from dataclasses import dataclass
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
 import torch
 
 from ..parts.mixer import PagedKV, StateNeed
-from .pages import OutOfPages, PagePool, SlotPool
+from .pages import (BAD_ARG, NO_SLOT, OK, OUT_OF_PAGES, OutOfPages, PageAccountingError, checked, host_lib)
 
 DROPPED = -1
+
+
+class GroupPool:
+    """One group's page pool inside the C++ cache: what the tests and the scheduler read of it."""
+
+    def __init__(self, lib, core, group: int, num_pages: int):
+        self._lib, self._core, self._group, self.num_pages = lib, core, group, num_pages
+
+    @property
+    def num_free(self) -> int:
+        return self._lib.mbh_group_free(self._core(), self._group)
+
+    @property
+    def num_held(self) -> int:
+        return self._lib.mbh_group_held(self._core(), self._group)
+
+    def check(self) -> None:
+        checked(self._lib.mbh_group_check, self._core(), self._group)
+
+
+class SlotsView:
+    """The state slots inside the C++ cache."""
+
+    def __init__(self, lib, core, count: int):
+        self._lib, self._core, self.num_pages = lib, core, count
+
+    @property
+    def num_free(self) -> int:
+        return self._lib.mbh_slots_free(self._core())
+
+    @property
+    def num_held(self) -> int:
+        return self._lib.mbh_slots_held(self._core())
+
+    def check(self) -> None:
+        checked(self._lib.mbh_slots_check, self._core())
 
 
 @dataclass
 class PagedGroup:
     need: PagedKV
     entries: List[int]          # schedule indices that own a cache in this group
-    pool: PagePool
+    pool: GroupPool
     k: Optional[torch.Tensor] = None
     v: Optional[torch.Tensor] = None
 
 
-@dataclass
 class RequestCache:
-    slot: int
-    length: int = 0
-    pages: List[List[int]] = field(default_factory=list)  # per group: logical page → page id or DROPPED
-    dropped: int = 0                                      # how many pages a window has given back so far
-    arrays: Dict[int, tuple] = field(default_factory=dict)
+    """A live request as the cache sees it: its handle in the C++ core, its state slot, and (read from the core) its
+    length and its block tables."""
+
+    def __init__(self, manager: "CacheManager", handle: int, slot: int):
+        self._manager, self.handle, self.slot = manager, int(handle), int(slot)
+
+    @property
+    def length(self) -> int:
+        return self._manager._lib.mbh_length(self._manager._core(), self.handle)
+
+    @property
+    def pages(self) -> List[List[int]]:
+        """Per group: logical page -> page id, or DROPPED where a window has given the page back."""
+        return [self._manager._table(self.handle, g) for g in range(len(self._manager.groups))]
 
 
 @dataclass
@@ -71,7 +116,11 @@ class CacheManager:
         ``cache_of[i]``'s cache); ``num_pages`` pages are given to every group."""
         if page_size <= 0 or page_size > 64 or (page_size & (page_size - 1)) != 0:
             raise ValueError(f"page_size must be a power of two up to 64, got {page_size}")
+        if num_pages <= 0:
+            raise ValueError("a page pool needs at least one page")
         self.page_size, self.num_pages, self.max_requests = int(page_size), int(num_pages), int(max_requests)
+        self._lib = host_lib()
+        self._handle = None
         self.groups: List[PagedGroup] = []
         self.place: Dict[int, Tuple[int, int]] = {}     # schedule index → (group, index inside group)
         self.state_needs: Dict[int, StateNeed] = {}
@@ -82,7 +131,7 @@ class CacheManager:
             if isinstance(need, PagedKV):
                 if need not in by_need:
                     by_need[need] = len(self.groups)
-                    self.groups.append(PagedGroup(need, [], PagePool(self.num_pages)))
+                    self.groups.append(PagedGroup(need, [], GroupPool(self._lib, self._core, len(self.groups), self.num_pages)))
                 g = by_need[need]
                 self.place[i] = (g, len(self.groups[g].entries))
                 self.groups[g].entries.append(i)
@@ -90,8 +139,28 @@ class CacheManager:
                 self.state_needs[i] = need
             elif need is not None:
                 raise TypeError(f"schedule entry {i}: unknown cache need {need!r}")
-        self.slots = SlotPool(self.max_requests)
+        windows = (ctypes.c_int * max(1, len(self.groups)))(*[g.need.window if g.need.window else -1 for g in self.groups])
+        self._handle = self._lib.mbh_cache_create(self.page_size, self.num_pages, self.max_requests, len(self.groups), windows)
+        if not self._handle:
+            raise ValueError("the cache core refused these sizes")
+        self.slots = SlotsView(self._lib, self._core, self.max_requests)
         self.requests: Dict[Hashable, RequestCache] = {}
+
+    def _core(self):
+        return self._handle
+
+    def __del__(self):
+        handle, self._handle = getattr(self, "_handle", None), None
+        if handle:
+            self._lib.mbh_cache_destroy(handle)
+
+    def _table(self, handle: int, group: int) -> List[int]:
+        n = self._lib.mbh_block_table(self._handle, handle, group, None, 0)
+        if n < 0:
+            raise KeyError(f"the cache core knows no request with handle {handle}")
+        out = (ctypes.c_int * max(n, 1))()
+        self._lib.mbh_block_table(self._handle, handle, group, out, n)
+        return list(out[:n])
 
     # ---- device memory -------------------------------------------------------------------------
     def bytes_per_page(self, dtype: torch.dtype) -> int:
@@ -110,102 +179,71 @@ class CacheManager:
     def admit(self, req_id: Hashable) -> RequestCache:
         if req_id in self.requests:
             raise KeyError(f"request {req_id!r} is already live")
-        (slot,) = self.slots.alloc(1)
-        rc = RequestCache(slot=slot, pages=[[] for _ in self.groups])
-        self.requests[req_id] = rc
+        handle, slot = ctypes.c_int64(), ctypes.c_int()
+        rc = self._lib.mbh_admit(self._handle, ctypes.byref(handle), ctypes.byref(slot))
+        if rc == NO_SLOT:
+            raise OutOfPages(f"1 pages wanted, 0 of {self.max_requests} free")
+        req = RequestCache(self, handle.value, slot.value)
+        self.requests[req_id] = req
         for tensor in self.state.values():
-            tensor[slot].zero_()
-        return rc
+            tensor[req.slot].zero_()
+        return req
 
     def length(self, req_id: Hashable) -> int:
         return self.requests[req_id].length
 
-    def _first_needed_page(self, g: PagedGroup, first_query_pos: int) -> int:
-        if g.need.window is None:
-            return 0
-        return max(0, first_query_pos - g.need.window + 1) // self.page_size
-
     def pages_missing(self, req_id: Hashable, new_len: int) -> List[int]:
         """Per group, how many pages ``reserve(req_id, new_len)`` would take."""
-        rc = self.requests[req_id]
-        total = -(-new_len // self.page_size)
-        return [max(0, total - len(pages)) for pages in rc.pages]
+        out = (ctypes.c_int * max(1, len(self.groups)))()
+        self._lib.mbh_pages_missing(self._handle, self.requests[req_id].handle, int(new_len), out)
+        return list(out[:len(self.groups)])
 
     def pages_array(self, rc: RequestCache, group: int):
-        """The request's block table of one group as an int32 array (dropped pages as 0), rebuilt only when
-        the table changed."""
+        """The request's block table of one group as an int32 array (dropped pages as 0)."""
         import numpy as np
 
-        pages = rc.pages[group]
-        cached = rc.arrays.get(group)
-        if cached is None or cached[0] != len(pages) or cached[1] != rc.dropped:
-            arr = np.maximum(np.asarray(pages, np.int32), 0) if pages else np.zeros(0, np.int32)
-            rc.arrays[group] = (len(pages), rc.dropped, arr)
-            return arr
-        return cached[2]
+        return np.maximum(np.asarray(self._table(rc.handle, group), np.int32), 0)
 
     def can_reserve(self, wanted: Sequence[Tuple[Hashable, int]]) -> bool:
         """Whether all of ``(req_id, new_len)`` could be reserved together."""
-        need = [0] * len(self.groups)
-        for req_id, new_len in wanted:
-            for gi, n in enumerate(self.pages_missing(req_id, new_len)):
-                need[gi] += n
-        return all(n <= g.pool.num_free for n, g in zip(need, self.groups))
+        n = len(wanted)
+        handles = (ctypes.c_int64 * max(n, 1))(*[self.requests[r].handle for r, _ in wanted])
+        lens = (ctypes.c_int * max(n, 1))(*[int(x) for _, x in wanted])
+        return self._lib.mbh_can_reserve(self._handle, n, handles, lens) == 1
 
     def reserve(self, req_id: Hashable, new_len: int) -> None:
         """Pages so that positions ``< new_len`` have a place, in every group, or OutOfPages
         with nothing taken."""
-        rc = self.requests[req_id]
-        missing = self.pages_missing(req_id, new_len)
-        for n, g in zip(missing, self.groups):
-            if n > g.pool.num_free:
-                raise OutOfPages(f"request {req_id!r} needs {n} more pages, {g.pool.num_free} free")
-        for gi, (n, g) in enumerate(zip(missing, self.groups)):
-            rc.pages[gi].extend(g.pool.alloc(n))
+        rc = self._lib.mbh_reserve(self._handle, self.requests[req_id].handle, int(new_len))
+        if rc == OUT_OF_PAGES:
+            raise OutOfPages(f"request {req_id!r} needs {self.pages_missing(req_id, new_len)} more pages, {self.free_pages()} free")
+        if rc != OK:
+            raise PageAccountingError(f"reserve failed with code {rc}")
 
     def commit(self, req_id: Hashable, new_len: int) -> None:
         """The step succeeded: the request now holds ``new_len`` positions.  Pages that a window
         has passed go back to their pool."""
-        rc = self.requests[req_id]
-        if new_len < rc.length:
+        rc = self._lib.mbh_commit(self._handle, self.requests[req_id].handle, int(new_len))
+        if rc == BAD_ARG:
             raise ValueError("a request's length cannot shrink on commit")
-        rc.length = new_len
-        for gi, g in enumerate(self.groups):
-            first = self._first_needed_page(g, new_len)
-            table = rc.pages[gi]
-            for logical in range(min(first, len(table))):
-                if table[logical] != DROPPED:
-                    g.pool.free([table[logical]])
-                    table[logical] = DROPPED
-                    rc.dropped += 1
+        if rc != OK:
+            raise PageAccountingError(f"commit failed with code {rc}")
 
     def release(self, req_id: Hashable) -> None:
         """The request ended (or was preempted): everything it holds goes back."""
-        rc = self.requests.pop(req_id)
-        for gi, g in enumerate(self.groups):
-            g.pool.free([p for p in rc.pages[gi] if p != DROPPED])
-        self.slots.free([rc.slot])
+        req = self.requests.pop(req_id)
+        rc = self._lib.mbh_release(self._handle, req.handle)
+        if rc != OK:
+            raise PageAccountingError(f"release failed with code {rc}")
 
     def block_table(self, req_id: Hashable, group: int) -> List[int]:
-        return self.requests[req_id].pages[group]
+        return self._table(self.requests[req_id].handle, group)
 
     def free_pages(self) -> List[int]:
         return [g.pool.num_free for g in self.groups]
 
     def check(self) -> None:
         """No page lost, held twice or freed twice: pools consistent with the block tables."""
-        for gi, g in enumerate(self.groups):
-            g.pool.check()
-            seen = set()
-            for req_id, rc in self.requests.items():
-                for page in rc.pages[gi]:
-                    if page == DROPPED:
-                        continue
-                    if page in seen:
-                        raise AssertionError(f"page {page} of group {gi} is in two block tables")
-                    seen.add(page)
-            if len(seen) != g.pool.num_held:
-                raise AssertionError(f"group {gi}: {g.pool.num_held} pages held, {len(seen)} in block tables")
-        self.slots.check()
+        checked(self._lib.mbh_check, self._handle)
         if self.slots.num_held != len(self.requests):
-            raise AssertionError("slots held and live requests differ")
+            raise PageAccountingError("slots held and live requests differ")

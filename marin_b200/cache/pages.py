@@ -1,12 +1,48 @@
 """Page and slot bookkeeping (host side, no device memory here).
 
-The reference keeps one private page pool per sequence and reuses freed pages LIFO
-(crates/cuda/src/pages.rs:20-65).  Here one pool is shared by all requests of a cache
-group, so pages a finished request gives back are the next ones handed out.
+The accounting itself is C++ (``csrc/host/cache_core.cpp``, built at first use like the kernels); the classes
+here are its handles.  The reference keeps one private page pool per sequence and reuses freed pages LIFO
+(crates/cuda/src/pages.rs:20-65).  Here one pool is shared by all requests of a cache group, so pages a
+finished request gives back are the next ones handed out.
 """
 from __future__ import annotations
 
-from typing import Iterable, List, Set
+import ctypes
+from typing import Iterable, List
+
+from ..kernels import build
+
+OK, OUT_OF_PAGES, NOT_HELD, BAD_ARG, UNKNOWN_REQUEST, NO_SLOT, INCONSISTENT, TOO_SMALL = range(8)
+
+_lib = None
+
+
+def host_lib() -> ctypes.CDLL:
+    """The host library, with the argument and result types of its functions declared."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    lib = build.load("mb_host", build.LIBRARIES["mb_host"])
+    vp, i32, i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64
+    pi32, pi64, text = ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int64), ctypes.c_char_p
+    signatures = {
+        "mbh_pool_create": (vp, [i32]), "mbh_pool_destroy": (None, [vp]), "mbh_pool_num_free": (i32, [vp]),
+        "mbh_pool_num_held": (i32, [vp]), "mbh_pool_alloc": (i32, [vp, i32, pi32]), "mbh_pool_free": (i32, [vp, i32]),
+        "mbh_pool_check": (i32, [vp, text, i32]),
+        "mbh_cache_create": (vp, [i32, i32, i32, i32, pi32]), "mbh_cache_destroy": (None, [vp]),
+        "mbh_admit": (i32, [vp, pi64, pi32]), "mbh_length": (i32, [vp, i64]), "mbh_pages_missing": (i32, [vp, i64, i32, pi32]),
+        "mbh_can_reserve": (i32, [vp, i32, pi64, pi32]), "mbh_reserve": (i32, [vp, i64, i32]), "mbh_commit": (i32, [vp, i64, i32]),
+        "mbh_release": (i32, [vp, i64]), "mbh_block_table": (i32, [vp, i64, i32, pi32, i32]),
+        "mbh_group_free": (i32, [vp, i32]), "mbh_group_held": (i32, [vp, i32]), "mbh_group_check": (i32, [vp, i32, text, i32]),
+        "mbh_slots_free": (i32, [vp]), "mbh_slots_held": (i32, [vp]), "mbh_slots_check": (i32, [vp, text, i32]),
+        "mbh_check": (i32, [vp, text, i32]),
+        "mbh_pack_step": (i32, [vp, i32, vp, vp, vp, vp, vp, i32, i32, vp, i32, vp, vp]),
+    }
+    for name, (res, args) in signatures.items():
+        fn = getattr(lib, name)
+        fn.restype, fn.argtypes = res, args
+    _lib = lib
+    return lib
 
 
 class OutOfPages(RuntimeError):
@@ -17,6 +53,13 @@ class PageAccountingError(AssertionError):
     """A page was freed twice, freed without being held, or lost."""
 
 
+def checked(call, *args) -> None:
+    """Runs one of the library's ``check`` functions and raises what it found."""
+    msg = ctypes.create_string_buffer(256)
+    if call(*args, msg, len(msg)) != OK:
+        raise PageAccountingError(msg.value.decode() or "the page accounting is inconsistent")
+
+
 class PagePool:
     """``num_pages`` page ids handed out and taken back; LIFO reuse."""
 
@@ -24,42 +67,38 @@ class PagePool:
         if num_pages <= 0:
             raise ValueError("a page pool needs at least one page")
         self.num_pages = int(num_pages)
-        self._free: List[int] = list(range(self.num_pages - 1, -1, -1))
-        self._held: Set[int] = set()
+        self._lib = host_lib()
+        self._pool = self._lib.mbh_pool_create(self.num_pages)
+
+    def __del__(self):
+        pool, self._pool = getattr(self, "_pool", None), None
+        if pool:
+            self._lib.mbh_pool_destroy(pool)
 
     @property
     def num_free(self) -> int:
-        return len(self._free)
+        return self._lib.mbh_pool_num_free(self._pool)
 
     @property
     def num_held(self) -> int:
-        return len(self._held)
+        return self._lib.mbh_pool_num_held(self._pool)
 
     def alloc(self, count: int) -> List[int]:
         if count < 0:
             raise ValueError("cannot allocate a negative number of pages")
-        if count > len(self._free):
-            raise OutOfPages(f"{count} pages wanted, {len(self._free)} of {self.num_pages} free")
-        taken = [self._free.pop() for _ in range(count)]
-        self._held.update(taken)
-        return taken
+        out = (ctypes.c_int * max(count, 1))()
+        if self._lib.mbh_pool_alloc(self._pool, count, out) == OUT_OF_PAGES:
+            raise OutOfPages(f"{count} pages wanted, {self.num_free} of {self.num_pages} free")
+        return list(out[:count])
 
     def free(self, pages: Iterable[int]) -> None:
         for page in pages:
-            if page not in self._held:
+            if self._lib.mbh_pool_free(self._pool, int(page)) != OK:
                 raise PageAccountingError(f"page {page} is freed but not held")
-            self._held.remove(page)
-            self._free.append(page)
 
     def check(self) -> None:
         """Every page is either free or held, exactly once."""
-        free = set(self._free)
-        if len(free) != len(self._free):
-            raise PageAccountingError("a page is on the free list twice")
-        if free & self._held:
-            raise PageAccountingError(f"pages both free and held: {sorted(free & self._held)}")
-        if len(free) + len(self._held) != self.num_pages:
-            raise PageAccountingError("a page was lost")
+        checked(self._lib.mbh_pool_check, self._pool)
 
 
 class SlotPool(PagePool):

@@ -103,61 +103,39 @@ class Runner:
         """Flattens the entries (single tokens first) into the arrays the kernels read, and copies
         them to the device in one transfer.  ``pad_to`` (decode batches only) pads the batch with empty
         requests up to a fixed size; ``static`` is then the device buffer a captured graph reads."""
-        cache, page = self.cache, self.cache.page_size
-        order = sorted(range(len(entries)), key=lambda i: (len(entries[i].tokens) != 1, i))
-        num_decode = sum(1 for e in entries if len(e.tokens) == 1)
-        real_R = len(entries)
-        real_T = sum(len(e.tokens) for e in entries)
-        R, T = (pad_to, pad_to) if pad_to else (real_R, real_T)
+        cache = self.cache
+        n = len(entries)
+        counts = np.fromiter((len(e.tokens) for e in entries), np.int32, n)
+        want_counts = np.fromiter((len(e.want) for e in entries), np.int32, n)
+        tokens = np.concatenate([np.asarray(e.tokens, np.int32) for e in entries]) if n > 1 else np.asarray(entries[0].tokens, np.int32)
+        wants = np.fromiter((w for e in entries for w in e.want), np.int32, int(want_counts.sum()))
+        handles = np.fromiter((cache.requests[e.req_id].handle for e in entries), np.int64, n)
+        real_T = int(counts.sum())
+        R, T = (pad_to, pad_to) if pad_to else (n, real_T)
+        W = pad_to if pad_to else int(want_counts.sum())
         maxb = self.max_pages_per_seq
         G = len(cache.groups)
-        tok = np.zeros(T, np.int32)
-        pos = np.zeros(T, np.int32)
-        req = np.arange(T, dtype=np.int32) if pad_to else np.zeros(T, np.int32)
-        cu = np.arange(R + 1, dtype=np.int32) if pad_to else np.zeros(R + 1, np.int32)
-        lens = np.zeros(R, np.int32)
-        slots = np.zeros(R, np.int32)
-        tables = np.zeros((G, R, maxb), np.int32)
-        slot_maps = np.full((G, T), -1, np.int32)
-        spans: List[Span] = []
-        flat_start: Dict[int, int] = {}
-        at = 0
-        for row, i in enumerate(order):
-            e = entries[i]
-            rc = cache.requests[e.req_id]
-            n = len(e.tokens)
-            flat_start[i] = at
-            tok[at:at + n] = np.asarray(e.tokens, np.int32)
-            p = np.arange(rc.length, rc.length + n, dtype=np.int32)
-            pos[at:at + n] = p
-            req[at:at + n] = row
-            cu[row + 1] = at + n
-            lens[row] = rc.length + n
-            slots[row] = rc.slot
-            for g in range(G):
-                ids = cache.pages_array(rc, g)
-                tables[g, row, :len(ids)] = ids
-                if n == 1:
-                    slot_maps[g, at] = ids[rc.length // page] * page + rc.length % page
-                else:
-                    slot_maps[g, at:at + n] = ids[p // page] * page + (p % page)
-            spans.append(Span(row, e.req_id, at, n, rc.length, rc.slot))
-            at += n
-        if pad_to:
-            logit_rows = np.arange(pad_to, dtype=np.int32)
-            num_rows = pad_to
-        else:
-            rows: List[int] = []
-            for i, e in enumerate(entries):
-                rows.extend(flat_start[i] + int(w) for w in e.want)
-            logit_rows = np.asarray(rows, np.int32)
-            num_rows = len(rows)
-        parts = [tok, pos, req, cu, lens, slots, logit_rows, tables.reshape(-1), slot_maps.reshape(-1)]
-        packed = np.concatenate(parts)
+        sizes = [T, T, T, R + 1, R, R, W, G * R * maxb, G * T]
+        total = sum(sizes)
         if static is not None:
             host, dev, copied = static
             copied.synchronize()                 # the last step's copy has left the pinned buffer
-            host.numpy()[:] = packed
+            packed = host.numpy()
+        else:
+            packed = np.empty(total, np.int32)
+        info = np.zeros(8, np.int32)
+        span_rows = np.zeros((n, 5), np.int32)
+        # the C++ side walks the block tables and writes the arrays in place (csrc/host/cache_core.cpp)
+        wrote = cache._lib.mbh_pack_step(cache._core(), n, handles.ctypes.data, counts.ctypes.data, tokens.ctypes.data,
+                                        want_counts.ctypes.data, wants.ctypes.data, int(pad_to), maxb, packed.ctypes.data,
+                                        int(packed.size), info.ctypes.data, span_rows.ctypes.data)
+        if wrote != total:
+            raise StepError(f"packing the step failed (code {wrote}, {total} values expected)")
+        num_decode, max_query_len, max_seq_len = int(info[3]), int(info[4]), int(info[5])
+        spans = [Span(row, entries[int(i)].req_id, int(at), int(cnt), int(first), int(slot))
+                 for row, (i, at, cnt, first, slot) in enumerate(span_rows.tolist())]
+        num_rows = W
+        if static is not None:
             dev.copy_(host, non_blocking=True)
             copied.record()
         else:
@@ -166,13 +144,13 @@ class Runner:
                 host = host.pin_memory()
             dev = host.to(self.rt.device, non_blocking=True)
         views, at = [], 0
-        for p in parts:
-            views.append(dev[at:at + p.size])
-            at += p.size
+        for size in sizes:
+            views.append(dev[at:at + size])
+            at += size
         d_tok, d_pos, d_req, d_cu, d_lens, d_slots, d_rows, d_tables, d_maps = views
         return StepContext(
             num_tokens=T, num_requests=R, num_decode=R if pad_to else num_decode, num_logit_rows=num_rows,
-            max_query_len=max(len(e.tokens) for e in entries), max_seq_len=int(lens.max()),
+            max_query_len=max_query_len, max_seq_len=max_seq_len,
             token_ids=d_tok, positions=d_pos, req_index=d_req, cu_tokens=d_cu, seq_lens=d_lens,
             state_slots=d_slots, logit_rows=d_rows,
             group_block_tables=[d_tables.view(G, R, maxb)[g] for g in range(G)] if G else [],

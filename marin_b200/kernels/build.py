@@ -1,4 +1,5 @@
-"""Compiles the CUDA sources of ``csrc/`` for sm_100a into shared libraries, at first use.
+"""Compiles the CUDA sources of ``csrc/`` for sm_100a (and the C++ host sources of ``csrc/host/``) into shared
+libraries, at first use.
 
 Each library is built with ``nvcc`` directly (no framework headers, so a file compiles in
 seconds) into ``marin_b200/csrc/_build/`` beside the sources, named by a hash of its sources
@@ -38,6 +39,20 @@ def _nvcc() -> str:
             return cand
     raise KernelBuildError("nvcc was not found (looked at $MARIN_B200_NVCC, PATH and /usr/local/cuda/bin); "
                            "the CUDA kernels of marin_b200 cannot be built and there is no other path")
+
+
+HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden"]
+
+
+def _host_compiler() -> str:
+    for cand in (os.environ.get("CXX"), shutil.which("g++"), shutil.which("c++"), shutil.which("clang++")):
+        if cand and (os.path.exists(cand) or shutil.which(cand)):
+            return cand
+    raise KernelBuildError("no C++ compiler was found (looked at $CXX, g++, c++, clang++): the host code of marin_b200 cannot be built")
+
+
+def _is_host(sources: Sequence[str]) -> bool:
+    return all(s.endswith(".cpp") for s in sources)
 
 
 _build_dir_cache: Optional[str] = None
@@ -89,14 +104,15 @@ def build(name: str, sources: Sequence[str], defines: Sequence[str] = (), verbos
     MARIN_B200_DEFINES in the environment (comma separated, e.g. ``DEC_STAGES=2,PDL_WAIT_FIRST``) adds defines to
     every library: the kernels' tuning constants can be overridden for experiments without touching the sources."""
     extra = [x for x in os.environ.get("MARIN_B200_DEFINES", "").split(",") if x]
-    flags = ARCH_FLAGS + BASE_FLAGS + [f"-D{d}" for d in list(defines) + extra]
+    host = _is_host(sources)
+    flags = (HOST_FLAGS if host else ARCH_FLAGS + BASE_FLAGS) + [f"-D{d}" for d in list(defines) + extra]
     out = os.path.join(_build_dir(), f"{name}-{_digest(sources, flags)}.so")
     if os.path.exists(out):
         return out
-    tmp = f"{out}.{os.getpid()}.tmp"
-    cmd = [_nvcc()] + flags + ["-I", CSRC, "-o", tmp] + [os.path.join(CSRC, s) for s in sources]
+    tmp = f"{out}.{os.getpid()}.{threading.get_ident()}.tmp"
+    cmd = [_host_compiler() if host else _nvcc()] + flags + ["-I", CSRC, "-o", tmp] + [os.path.join(CSRC, s) for s in sources]
     if verbose:
-        print(f"[marin_b200] compiling {name} for sm_100a ({', '.join(sources)}) ...", file=sys.stderr, flush=True)
+        print(f"[marin_b200] compiling {name} {'(host code)' if host else 'for sm_100a'} ({', '.join(sources)}) ...", file=sys.stderr, flush=True)
     started = time.time()
     proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     while True:
@@ -134,6 +150,7 @@ LIBRARIES: Dict[str, List[str]] = {
     "mb_attention_simple": ["attention_simple.cu"],
     "mb_sampling": ["sampling.cu"],
     "mb_gemm_tc": ["gemm_tc.cu"],
+    "mb_host": ["host/cache_core.cpp"],
 }
 
 
