@@ -12,7 +12,7 @@ from typing import Iterable, List
 
 from ..kernels import build
 
-OK, OUT_OF_PAGES, NOT_HELD, BAD_ARG, UNKNOWN_REQUEST, NO_SLOT, INCONSISTENT, TOO_SMALL = range(8)
+OK, OUT_OF_PAGES, NOT_HELD, BAD_ARG, UNKNOWN_REQUEST, NO_SLOT, INCONSISTENT, TOO_SMALL, CONTEXT_FULL = range(9)
 
 _lib = None
 
@@ -36,6 +36,7 @@ def host_lib() -> ctypes.CDLL:
         "mbh_group_free": (i32, [vp, i32]), "mbh_group_held": (i32, [vp, i32]), "mbh_group_check": (i32, [vp, i32, text, i32]),
         "mbh_slots_free": (i32, [vp]), "mbh_slots_held": (i32, [vp]), "mbh_slots_check": (i32, [vp, text, i32]),
         "mbh_check": (i32, [vp, text, i32]),
+        "mbh_step_reserve": (i32, [vp, i32, vp, vp, i32, pi32]), "mbh_step_commit": (i32, [vp, i32, vp, vp]),
         "mbh_pack_step": (i32, [vp, i32, vp, vp, vp, vp, vp, i32, i32, vp, i32, vp, vp]),
     }
     for name, (res, args) in signatures.items():

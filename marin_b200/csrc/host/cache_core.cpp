@@ -25,6 +25,7 @@ enum {
     MBH_NO_SLOT = 5,
     MBH_INCONSISTENT = 6,       // check() found a page lost or held twice
     MBH_TOO_SMALL = 7,          // the caller's buffer is too small
+    MBH_CONTEXT_FULL = 8,       // a request would grow past the context capacity
 };
 
 static const int DROPPED = -1;  // a block-table entry whose page a window has given back
@@ -303,6 +304,45 @@ MBH_API int mbh_check(void* c, char* msg, int cap) {
     const int rc = static_cast<Cache*>(c)->check(&why);
     put_message(why, msg, cap);
     return rc;
+}
+
+// ---- a whole step's accounting in one call each -----------------------------------------------------------------------
+// Before the step: every entry (handle, number of new tokens) must stay within max_seq_len positions and all of them
+// together must find their pages, which are then taken; otherwise nothing is taken and *bad names the entry at fault
+// (for MBH_OUT_OF_PAGES: -1, the step as a whole does not fit).
+MBH_API int mbh_step_reserve(void* c, int n, const int64_t* handles, const int* counts, int max_seq_len, int* bad) {
+    Cache* cache = static_cast<Cache*>(c);
+    std::vector<Request*> reqs(n);
+    std::vector<int> need(cache->groups(), 0), one(cache->groups(), 0);
+    *bad = -1;
+    for (int i = 0; i < n; ++i) {
+        reqs[i] = cache->find(handles[i]);
+        *bad = i;
+        if (reqs[i] == nullptr) return MBH_UNKNOWN_REQUEST;
+        if (counts[i] <= 0) return MBH_BAD_ARG;
+        if (reqs[i]->length + counts[i] > max_seq_len) return MBH_CONTEXT_FULL;
+        cache->missing(*reqs[i], reqs[i]->length + counts[i], one.data());
+        for (int g = 0; g < cache->groups(); ++g) need[g] += one[g];
+    }
+    *bad = -1;
+    for (int g = 0; g < cache->groups(); ++g)
+        if (need[g] > cache->pool(g).num_free()) return MBH_OUT_OF_PAGES;
+    for (int i = 0; i < n; ++i) {
+        const int rc = cache->reserve(*reqs[i], reqs[i]->length + counts[i]);
+        if (rc != MBH_OK) return rc;          // cannot happen: the sum was checked above
+    }
+    return MBH_OK;
+}
+// After the step: every entry's request now holds its new tokens.
+MBH_API int mbh_step_commit(void* c, int n, const int64_t* handles, const int* counts) {
+    Cache* cache = static_cast<Cache*>(c);
+    for (int i = 0; i < n; ++i) {
+        Request* r = cache->find(handles[i]);
+        if (r == nullptr) return MBH_UNKNOWN_REQUEST;
+        const int rc = cache->commit(*r, r->length + counts[i]);
+        if (rc != MBH_OK) return rc;
+    }
+    return MBH_OK;
 }
 
 // ---- packing a step ---------------------------------------------------------------------------------------------------

@@ -187,8 +187,10 @@ class Engine:
             return {}
         out: Dict[Hashable, int] = {}
         if all(p.request.params.greedy and p.request.params.usable_vocab in (None, vocab) for p in rows):
-            ids = torch.empty(len(rows), device=logits.device, dtype=torch.int32)
-            ops.argmax(logits, vocab, ids)
+            ids = self.runner.greedy_ids if len(rows) == len(plan) else None
+            if ids is None or ids.numel() != len(rows):
+                ids = torch.empty(len(rows), device=logits.device, dtype=torch.int32)
+                ops.argmax(logits, vocab, ids)
             for p, token in zip(rows, ids.tolist()):
                 out[p.request.req_id] = int(token)
             return out

@@ -152,9 +152,30 @@ class Scheduler:
             self.cache.release(request.req_id)
         self.finished.append(request)
 
-    def schedule(self) -> List[Planned]:
+    def _plan_without_contest(self) -> Optional[List[Planned]]:
+        """The common step: nobody can be admitted (no one waits, or every place is taken) and the running requests'
+        portions all find their pages.  One question to the cache instead of one per request; None if it does not
+        apply, and the careful path below decides."""
+        if not self.running or (self.waiting and len(self.running) < self.max_batch):
+            return None
         budget = self.token_budget
         plan: List[Planned] = []
+        for request in sorted(self.running, key=lambda r: r.admitted_at):
+            if budget == 0:
+                break
+            portion = self._portion(request, budget)
+            plan.append(portion)
+            budget -= len(portion.tokens)
+        if not self.cache.can_reserve([(p.request.req_id, p.request.computed + len(p.tokens)) for p in plan]):
+            return None
+        return plan
+
+    def schedule(self) -> List[Planned]:
+        plan = self._plan_without_contest()
+        if plan is not None:
+            return plan
+        budget = self.token_budget
+        plan = []
         # 1. running requests, oldest first: decodes take one token, prompts a portion
         for request in sorted(self.running, key=lambda r: r.admitted_at):
             if request not in self.running:      # preempted while making room for an older one

@@ -13,11 +13,13 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence
 
+import ctypes
+
 import numpy as np
 import torch
 
 from ..cache.manager import DROPPED, CacheManager, PagedView, StateView
-from ..cache.pages import OutOfPages
+from ..cache.pages import CONTEXT_FULL, OK, OUT_OF_PAGES, OutOfPages
 from ..models.model import Model
 from ..parts.base import Runtime
 from .context import Span, StepContext, Workspace
@@ -64,6 +66,9 @@ class Runner:
         self.views = CacheViews(cache)
         self.vocab = model.spec.vocab_size
         self.steps_run = 0
+        #: after a step replayed from a graph: int32 ids of the largest logit of each returned row (lowest id among
+        #: equals), computed inside the graph; None after any other step
+        self.greedy_ids: Optional[torch.Tensor] = None
 
     # ---- requests ----------------------------------------------------------------------------------
     def begin(self, req_id: Hashable) -> None:
@@ -95,14 +100,12 @@ class Runner:
             for w in e.want:
                 if not 0 <= int(w) < n:
                     raise StepError(f"request {e.req_id!r}: wanted place {w} is outside its {n} tokens")
-            new_len = self.cache.length(e.req_id) + n
-            if new_len > self.max_seq_len:
-                raise StepError(f"request {e.req_id!r}: context full ({new_len} positions needed, capacity {self.max_seq_len})")
 
-    def build_context(self, entries: Sequence[StepEntry], pad_to: int = 0, static=None) -> StepContext:
+    def build_context(self, entries: Sequence[StepEntry], pad_to: int = 0, static=None, refresh_only: bool = False):
         """Flattens the entries (single tokens first) into the arrays the kernels read, and copies
         them to the device in one transfer.  ``pad_to`` (decode batches only) pads the batch with empty
-        requests up to a fixed size; ``static`` is then the device buffer a captured graph reads."""
+        requests up to a fixed size; ``static`` is then the device buffer a captured graph reads, and with
+        ``refresh_only`` nothing but that buffer is wanted (a replay follows): no context is built."""
         cache = self.cache
         n = len(entries)
         counts = np.fromiter((len(e.tokens) for e in entries), np.int32, n)
@@ -132,17 +135,19 @@ class Runner:
         if wrote != total:
             raise StepError(f"packing the step failed (code {wrote}, {total} values expected)")
         num_decode, max_query_len, max_seq_len = int(info[3]), int(info[4]), int(info[5])
-        spans = [Span(row, entries[int(i)].req_id, int(at), int(cnt), int(first), int(slot))
-                 for row, (i, at, cnt, first, slot) in enumerate(span_rows.tolist())]
         num_rows = W
         if static is not None:
             dev.copy_(host, non_blocking=True)
             copied.record()
+            if refresh_only:
+                return None
         else:
             host = torch.from_numpy(packed)
             if self.rt.device.type == "cuda":
                 host = host.pin_memory()
             dev = host.to(self.rt.device, non_blocking=True)
+        spans = [Span(row, entries[int(i)].req_id, int(at), int(cnt), int(first), int(slot))
+                 for row, (i, at, cnt, first, slot) in enumerate(span_rows.tolist())]
         views, at = [], 0
         for size in sizes:
             views.append(dev[at:at + size])
@@ -206,8 +211,10 @@ class Runner:
         ctx.attn_split, ctx.attn_scratch = g["attn_split"], g["attn_scratch"]
         torch.cuda.synchronize()
         launches = ops.launches
+        g["best"] = torch.zeros(bucket, device=self.rt.device, dtype=torch.int32)
         with torch.cuda.graph(graph):
             g["logits"] = self.model.forward(ctx, self.views)
+            ops.argmax(g["logits"], self.vocab, g["best"])        # greedy sampling rides in the same graph
         g["launches"] = ops.launches - launches
         g["graph"] = graph
         return g
@@ -222,11 +229,12 @@ class Runner:
         from ..kernels import ops
 
         g = self._graph_for(bucket, entries)
-        self.build_context(entries, pad_to=bucket, static=g["static"])      # refresh the static buffer
+        self.build_context(entries, pad_to=bucket, static=g["static"], refresh_only=True)
         g["graph"].replay()
         ops.launches_extra(g["launches"])
         rows = [i for i, e in enumerate(entries) for _ in e.want]
         if rows == list(range(len(entries))):
+            self.greedy_ids = g["best"][: len(entries)]      # the largest logit of each returned row, already found
             return g["logits"][: len(entries)]
         return g["logits"][torch.as_tensor(rows, device=self.rt.device, dtype=torch.long)]
 
@@ -235,16 +243,27 @@ class Runner:
         in the order of the entries and of each entry's ``want``.  ``observe`` (see ``Model.forward``) turns
         graph replay off for this step."""
         self._validate(entries)
-        wanted = [(e.req_id, self.cache.length(e.req_id) + len(e.tokens)) for e in entries]
-        if not self.cache.can_reserve(wanted):
-            raise OutOfPages(f"the step needs more pages than are free ({self.cache.free_pages()} free per group)")
-        for req_id, new_len in wanted:
-            self.cache.reserve(req_id, new_len)
+        self.greedy_ids = None
+        cache, n = self.cache, len(entries)
+        handles = np.fromiter((cache.requests[e.req_id].handle for e in entries), np.int64, n)
+        counts = np.fromiter((len(e.tokens) for e in entries), np.int32, n)
+        # one call checks the context capacity and takes every entry's pages, or takes none
+        bad = ctypes.c_int(-1)
+        rc = cache._lib.mbh_step_reserve(cache._core(), n, handles.ctypes.data, counts.ctypes.data, self.max_seq_len, ctypes.byref(bad))
+        if rc == CONTEXT_FULL:
+            e = entries[bad.value]
+            raise StepError(f"request {e.req_id!r}: context full ({cache.length(e.req_id) + len(e.tokens)} positions needed, "
+                            f"capacity {self.max_seq_len})")
+        if rc == OUT_OF_PAGES:
+            raise OutOfPages(f"the step needs more pages than are free ({cache.free_pages()} free per group)")
+        if rc != OK:
+            raise StepError(f"reserving the step's pages failed (code {rc})")
         logits = self._step_graph(entries) if observe is None else None
         if logits is None:
             ctx = self.build_context(entries)
             logits = self.model.forward(ctx, self.views, observe) if observe is not None else self.model.forward(ctx, self.views)
-        for req_id, new_len in wanted:
-            self.cache.commit(req_id, new_len)
+        rc = cache._lib.mbh_step_commit(cache._core(), n, handles.ctypes.data, counts.ctypes.data)
+        if rc != OK:
+            raise StepError(f"recording the step failed (code {rc})")
         self.steps_run += 1
         return logits
