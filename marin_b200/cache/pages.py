@@ -37,6 +37,11 @@ def host_lib() -> ctypes.CDLL:
         "mbh_slots_free": (i32, [vp]), "mbh_slots_held": (i32, [vp]), "mbh_slots_check": (i32, [vp, text, i32]),
         "mbh_check": (i32, [vp, text, i32]),
         "mbh_step_reserve": (i32, [vp, i32, vp, vp, i32, pi32]), "mbh_step_commit": (i32, [vp, i32, vp, vp]),
+        "mbs_create": (vp, [vp, i32, i32, i32]), "mbs_destroy": (None, [vp]),
+        "mbs_add": (i32, [vp, vp, i32, i32, vp, i32, pi64]), "mbs_cancel": (i32, [vp, i64]), "mbs_forget": (i32, [vp, i64]),
+        "mbs_has_work": (i32, [vp]), "mbs_schedule": (i32, [vp, vp, i32, vp, i32, pi32]),
+        "mbs_update": (i32, [vp, vp, i32, vp, vp, pi32]), "mbs_states": (i32, [vp, i32, vp, vp]),
+        "mbs_output": (i32, [vp, i64, vp, i32]), "mbs_list": (i32, [vp, i32, vp, i32]),
         "mbh_pack_step": (i32, [vp, i32, vp, vp, vp, vp, vp, i32, i32, vp, i32, vp, vp]),
     }
     for name, (res, args) in signatures.items():

@@ -152,6 +152,7 @@ class Engine:
         return Generation(r.req_id, len(r.prompt), list(r.output), r.stop, r.preemptions)
 
     def forget(self, req_id: Hashable) -> None:
+        self.scheduler.forget(req_id)
         self._requests.pop(req_id, None)
         self._samplers.pop(req_id, None)
 

@@ -1,4 +1,5 @@
-"""The scheduler: which requests run in the next step, and with how many tokens.
+"""The scheduler: which requests run in the next step, and with how many tokens.  The decisions are made in C++
+(``csrc/host/scheduler.cpp``); this module holds its Python face.
 
 Policy (host bookkeeping only).  Each step has a token budget.  Requests that are decoding
 come first with one token each; what is left of the budget goes to prompt portions, running
@@ -16,10 +17,12 @@ crates/runtime/src/generate.rs:38-44.)
 """
 from __future__ import annotations
 
+import ctypes
 import enum
-from collections import deque
 from dataclasses import dataclass, field
-from typing import Deque, Dict, Hashable, List, Optional, Sequence
+from typing import Dict, Hashable, List, Optional, Sequence
+
+import numpy as np
 
 from ..cache.manager import CacheManager
 from ..sampling.sampler import SamplingParams
@@ -82,161 +85,153 @@ class Planned:
 
 
 class Scheduler:
+    """The handle of the C++ scheduler (``csrc/host/scheduler.cpp``), which holds the queues, the requests' tokens
+    and counters and decides every step; the ``Request`` objects here mirror what it says about them."""
+
+    _STOPS = [StopReason.MAX_TOKENS, StopReason.END_OF_TEXT, StopReason.CONTEXT_FULL, StopReason.CANCELLED, StopReason.OUT_OF_PAGES]
+
     def __init__(self, cache: CacheManager, max_batch: int, token_budget: int, max_seq_len: int):
         if token_budget < 1 or max_batch < 1:
             raise ValueError("token_budget and max_batch must be at least 1")
         self.cache, self.max_batch, self.token_budget, self.max_seq_len = cache, max_batch, token_budget, max_seq_len
-        self.waiting: Deque[Request] = deque()
-        self.running: List[Request] = []
-        self.finished: List[Request] = []
-        self._clock = 0
+        self._lib = cache._lib
+        self._core = self._lib.mbs_create(cache._core(), int(max_batch), int(token_budget), int(max_seq_len))
+        if not self._core:
+            raise ValueError("the scheduler core refused these sizes")
+        self._by_sid: Dict[int, Request] = {}
+        self._sid_of: Dict[Hashable, int] = {}
+        self._in_cache: Dict[Hashable, int] = {}                  # requests this scheduler has put into cache.requests
+        self._items = np.zeros((max_batch + 1, 6), np.int64)
+        self._tokens = np.zeros(token_budget, np.int32)
+        self._emitted_ids = np.zeros(max_batch + 1, np.int64)
+        self._emitted_tokens = np.zeros(max_batch + 1, np.int32)
+
+    def __del__(self):
+        core, self._core = getattr(self, "_core", None), None
+        if core:
+            self._lib.mbs_destroy(core)
+
+    # ---- what the core says about the requests -----------------------------------------------------------
+    def _refresh(self, requests: Sequence[Request]) -> None:
+        """Brings the mirrors of these requests up to date, and ``cache.requests`` with who is running."""
+        requests = [r for r in requests if r.req_id in self._sid_of]
+        if not requests:
+            return
+        ids = np.fromiter((self._sid_of[r.req_id] for r in requests), np.int64, len(requests))
+        out = np.zeros((len(requests), 8), np.int64)
+        if self._lib.mbs_states(self._core, len(requests), ids.ctypes.data, out.ctypes.data) != 0:
+            raise KeyError("the scheduler core does not know one of its requests")
+        for r, (computed, n_out, stop, preemptions, admitted_at, where, handle, slot) in zip(requests, out.tolist()):
+            r.computed, r.preemptions, r.admitted_at = computed, preemptions, admitted_at
+            r.stop = None if stop < 0 else self._STOPS[stop]
+            if n_out != len(r.output):
+                buf = np.zeros(max(n_out, 1), np.int32)
+                self._lib.mbs_output(self._core, self._sid_of[r.req_id], buf.ctypes.data, n_out)
+                r.output[:] = buf[:n_out].tolist()
+            known = self._in_cache.get(r.req_id)
+            if where == 1 and known != handle:
+                self._enter_cache(r.req_id, handle, slot)
+            elif where != 1 and known is not None:
+                self.cache.requests.pop(r.req_id, None)
+                del self._in_cache[r.req_id]
+
+    def _enter_cache(self, req_id: Hashable, handle: int, slot: int) -> None:
+        from ..cache.manager import RequestCache
+
+        self.cache.requests[req_id] = RequestCache(self.cache, handle, slot)
+        self._in_cache[req_id] = handle
+        for tensor in self.cache.state.values():
+            tensor[slot].zero_()
+
+    def _listed(self, which: int) -> List[Request]:
+        n = self._lib.mbs_list(self._core, which, None, 0)
+        buf = np.zeros(max(n, 1), np.int64)
+        self._lib.mbs_list(self._core, which, buf.ctypes.data, n)
+        return [self._by_sid[i] for i in buf[:n].tolist() if i in self._by_sid]
+
+    @property
+    def waiting(self) -> List[Request]:
+        return self._listed(0)
+
+    @property
+    def running(self) -> List[Request]:
+        return self._listed(1)
+
+    @property
+    def finished(self) -> List[Request]:
+        return self._listed(2)
 
     # ---- admission ------------------------------------------------------------------------------------
     def add(self, request: Request) -> None:
         request.params.validate()
-        if not request.prompt:
+        prompt = np.asarray(request.prompt, np.int32).reshape(-1)
+        stops = np.asarray(list(request.params.stop_tokens), np.int32).reshape(-1)
+        sid = ctypes.c_int64()
+        rc = self._lib.mbs_add(self._core, prompt.ctypes.data, int(prompt.size), int(request.params.max_tokens),
+                               stops.ctypes.data, int(stops.size), ctypes.byref(sid))
+        if rc == 20:
             raise RequestError("the prompt is empty")
-        if len(request.prompt) > self.max_seq_len:
+        if rc == 21:
             raise RequestError(f"the prompt has {len(request.prompt)} tokens, the context holds {self.max_seq_len}")
-        if request.params.max_tokens == 0:
-            request.stop = StopReason.MAX_TOKENS
-            self.finished.append(request)
-            return
-        self.waiting.append(request)
+        if rc != 0:
+            raise RequestError(f"the scheduler refused the request (code {rc})")
+        self._by_sid[sid.value] = request
+        self._sid_of[request.req_id] = sid.value
+        self._refresh([request])
 
     def has_work(self) -> bool:
-        return bool(self.waiting or self.running)
+        return self._lib.mbs_has_work(self._core) == 1
 
     def cancel(self, req_id: Hashable) -> None:
-        for r in list(self.running):
-            if r.req_id == req_id:
-                self._finish(r, StopReason.CANCELLED)
-        for r in list(self.waiting):
-            if r.req_id == req_id:
-                self.waiting.remove(r)
-                r.stop = StopReason.CANCELLED
-                self.finished.append(r)
+        sid = self._sid_of.get(req_id)
+        if sid is None:
+            return
+        self._lib.mbs_cancel(self._core, sid)
+        self._refresh([self._by_sid[sid]])
+
+    def forget(self, req_id: Hashable) -> None:
+        """Drops a finished request from the scheduler's memory."""
+        sid = self._sid_of.get(req_id)
+        if sid is not None and self._lib.mbs_forget(self._core, sid) == 0:
+            del self._sid_of[req_id]
+            del self._by_sid[sid]
 
     # ---- one step's plan --------------------------------------------------------------------------------
-    def _pages_fit(self, planned: Sequence[Planned], extra: Optional[Planned] = None) -> bool:
-        """Whether the pages the planned portions (and ``extra``) need are free, in every group."""
-        need = self._need_of(planned)
-        if extra is not None:
-            for g, n in enumerate(self.cache.pages_missing(extra.request.req_id, extra.request.computed + len(extra.tokens))):
-                need[g] += n
-        return all(n <= free for n, free in zip(need, self.cache.free_pages()))
-
-    def _need_of(self, planned: Sequence[Planned]) -> List[int]:
-        need = [0] * len(self.cache.groups)
-        for p in planned:
-            for g, n in enumerate(p.missing):
-                need[g] += n
-        return need
-
-    def _portion(self, request: Request, budget: int) -> Planned:
-        rest = request.num_tokens - request.computed
-        count = min(rest, budget)
-        return Planned(request, request.tokens_from(request.computed, count), sample=rest <= budget)
-
-    def _preempt(self, victim: Request) -> None:
-        self.cache.release(victim.req_id)
-        self.running.remove(victim)
-        victim.computed = 0
-        victim.preemptions += 1
-        self.waiting.appendleft(victim)
-
-    def _finish(self, request: Request, reason: StopReason) -> None:
-        request.stop = reason
-        if request in self.running:
-            self.running.remove(request)
-            self.cache.release(request.req_id)
-        self.finished.append(request)
-
-    def _plan_without_contest(self) -> Optional[List[Planned]]:
-        """The common step: nobody can be admitted (no one waits, or every place is taken) and the running requests'
-        portions all find their pages.  One question to the cache instead of one per request; None if it does not
-        apply, and the careful path below decides."""
-        if not self.running or (self.waiting and len(self.running) < self.max_batch):
-            return None
-        budget = self.token_budget
-        plan: List[Planned] = []
-        for request in sorted(self.running, key=lambda r: r.admitted_at):
-            if budget == 0:
-                break
-            portion = self._portion(request, budget)
-            plan.append(portion)
-            budget -= len(portion.tokens)
-        if not self.cache.can_reserve([(p.request.req_id, p.request.computed + len(p.tokens)) for p in plan]):
-            return None
-        return plan
-
     def schedule(self) -> List[Planned]:
-        plan = self._plan_without_contest()
-        if plan is not None:
-            return plan
-        budget = self.token_budget
-        plan = []
-        # 1. running requests, oldest first: decodes take one token, prompts a portion
-        for request in sorted(self.running, key=lambda r: r.admitted_at):
-            if request not in self.running:      # preempted while making room for an older one
-                continue
-            if budget == 0:
-                break
-            portion = self._portion(request, budget)
-            while not self._pages_fit(plan, portion):
-                victims = [r for r in self.running if r is not request and all(p.request is not r for p in plan)]
-                if not victims:
-                    break
-                self._preempt(max(victims, key=lambda r: r.admitted_at))
-            if not self._pages_fit(plan, portion):
-                if not plan and len(self.running) == 1:
-                    self._finish(request, StopReason.OUT_OF_PAGES)
-                continue
-            portion.missing = self.cache.pages_missing(request.req_id, request.computed + len(portion.tokens))
-            plan.append(portion)
-            budget -= len(portion.tokens)
-        # 2. admit waiting requests while there is room
-        while self.waiting and budget > 0 and len(self.running) < self.max_batch:
-            request = self.waiting[0]
-            portion = self._portion(request, budget)
-            self.cache.admit(request.req_id)
-            if not self._pages_fit(plan, portion):
-                self.cache.release(request.req_id)
-                if not self.running:
-                    # alone and still too large for the pool: it can never run
-                    self.waiting.popleft()
-                    request.stop = StopReason.OUT_OF_PAGES
-                    self.finished.append(request)
-                    continue
-                break
-            self.waiting.popleft()
-            self._clock += 1
-            request.admitted_at = self._clock
-            self.running.append(request)
-            portion.missing = self.cache.pages_missing(request.req_id, request.computed + len(portion.tokens))
-            plan.append(portion)
-            budget -= len(portion.tokens)
+        changed = ctypes.c_int(0)
+        n = self._lib.mbs_schedule(self._core, self._items.ctypes.data, len(self._items), self._tokens.ctypes.data,
+                                   len(self._tokens), ctypes.byref(changed))
+        if n < 0:
+            raise RuntimeError(f"the scheduler core failed (code {n})")
+        if changed.value:
+            self._refresh(list(self._by_sid.values()))
+        plan: List[Planned] = []
+        at = 0
+        flat = self._tokens[: int(self._items[:n, 2].sum())].tolist()
+        for sid, start, count, sample, handle, slot in self._items[:n].tolist():
+            request = self._by_sid[sid]
+            request.computed = start
+            plan.append(Planned(request, flat[at:at + count], bool(sample)))
+            at += count
         return plan
 
     # ---- after the step ----------------------------------------------------------------------------------
     def update(self, plan: Sequence[Planned], sampled: Dict[Hashable, int]) -> List[tuple]:
         """Records what ran and the tokens sampled for the requests whose portion ended their known
         tokens; returns ``[(req_id, token)]`` for the tokens that were emitted (a stop token is not)."""
+        tokens = np.asarray([sampled[p.request.req_id] for p in plan if p.sample], np.int32).reshape(-1)
+        changed = ctypes.c_int(0)
+        n = self._lib.mbs_update(self._core, tokens.ctypes.data, int(tokens.size), self._emitted_ids.ctypes.data,
+                                 self._emitted_tokens.ctypes.data, ctypes.byref(changed))
+        if n < 0:
+            raise RuntimeError(f"the scheduler core failed (code {n})")
         emitted: List[tuple] = []
+        for sid, token in zip(self._emitted_ids[:n].tolist(), self._emitted_tokens[:n].tolist()):
+            request = self._by_sid[sid]
+            request.output.append(token)
+            emitted.append((request.req_id, token))
         for p in plan:
-            r = p.request
-            r.computed += len(p.tokens)
-            if not p.sample:
-                continue
-            token = sampled[r.req_id]
-            if token in r.params.stop_tokens:
-                self._finish(r, StopReason.END_OF_TEXT)      # the stop token is not emitted
-                continue
-            r.output.append(token)
-            emitted.append((r.req_id, token))
-            if len(r.output) >= r.params.max_tokens:
-                self._finish(r, StopReason.MAX_TOKENS)
-            elif r.computed >= self.max_seq_len:
-                # the cache is full: the token just emitted cannot be fed (generate.rs:217-221)
-                self._finish(r, StopReason.CONTEXT_FULL)
+            p.request.computed += len(p.tokens)
+        if changed.value:
+            self._refresh([p.request for p in plan])
         return emitted

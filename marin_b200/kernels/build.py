@@ -83,10 +83,12 @@ def _build_dir() -> str:
 
 def _digest(sources: Sequence[str], flags: Sequence[str]) -> str:
     h = hashlib.sha256()
-    for name in sorted(os.listdir(CSRC)):
-        if name.endswith((".cuh", ".h")):
-            with open(os.path.join(CSRC, name), "rb") as fh:
-                h.update(name.encode() + b"\0" + fh.read())
+    folders = sorted({""} | {os.path.dirname(s) for s in sources})       # headers beside the sources count too
+    for folder in folders:
+        for name in sorted(os.listdir(os.path.join(CSRC, folder))):
+            if name.endswith((".cuh", ".h")):
+                with open(os.path.join(CSRC, folder, name), "rb") as fh:
+                    h.update(os.path.join(folder, name).encode() + b"\0" + fh.read())
     for src in sources:
         with open(os.path.join(CSRC, src), "rb") as fh:
             h.update(src.encode() + b"\0" + fh.read())
@@ -150,7 +152,7 @@ LIBRARIES: Dict[str, List[str]] = {
     "mb_attention_simple": ["attention_simple.cu"],
     "mb_sampling": ["sampling.cu"],
     "mb_gemm_tc": ["gemm_tc.cu"],
-    "mb_host": ["host/cache_core.cpp"],
+    "mb_host": ["host/cache_core.cpp", "host/scheduler.cpp"],
 }
 
 
