@@ -42,6 +42,9 @@ def host_lib() -> ctypes.CDLL:
         "mbs_has_work": (i32, [vp]), "mbs_schedule": (i32, [vp, vp, i32, vp, i32, pi32]),
         "mbs_update": (i32, [vp, vp, i32, vp, vp, pi32]), "mbs_states": (i32, [vp, i32, vp, vp]),
         "mbs_output": (i32, [vp, i64, vp, i32]), "mbs_list": (i32, [vp, i32, vp, i32]),
+        "mbp_best_index": (i32, [vp, i32]), "mbp_distribution": (i32, [vp, i32, i32, ctypes.c_float, i32, ctypes.c_float, vp, vp, i32]),
+        "mbp_next_unit": (ctypes.c_float, [ctypes.POINTER(ctypes.c_uint64)]),
+        "mbp_sample": (i32, [vp, i32, i32, ctypes.c_float, i32, ctypes.c_float, ctypes.POINTER(ctypes.c_uint64)]),
         "mbh_pack_step": (i32, [vp, i32, vp, vp, vp, vp, vp, i32, i32, vp, i32, vp, vp]),
     }
     for name, (res, args) in signatures.items():

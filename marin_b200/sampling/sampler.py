@@ -12,6 +12,7 @@ tokens as this plain algorithm by construction and are not repeated here.
 """
 from __future__ import annotations
 
+import ctypes
 import math
 from dataclasses import dataclass, field
 from typing import List, Optional, Sequence, Tuple
@@ -54,67 +55,65 @@ class SamplingParams:
         return self.temperature == 0.0
 
 
-def _total_order_key(values: np.ndarray) -> np.ndarray:
-    """int32 keys that sort float32 values the way IEEE total order does (-0.0 below +0.0)."""
-    bits = np.ascontiguousarray(values, dtype=np.float32).view(np.int32)
-    return bits ^ ((bits >> 31) & np.int32(0x7FFFFFFF))
+def _host():
+    from ..cache.pages import host_lib
+
+    return host_lib()
+
+
+def _row(values) -> np.ndarray:
+    return np.ascontiguousarray(np.asarray(values, dtype=np.float32).reshape(-1))
 
 
 def best_index(values: np.ndarray) -> int:
-    """Largest value, lowest index among equals (lib.rs:40-48)."""
-    return int(np.argmax(_total_order_key(values)))
+    """Largest value under IEEE total order (-0.0 below +0.0), lowest index among equals (lib.rs:40-48)."""
+    row = _row(values)
+    return int(_host().mbp_best_index(row.ctypes.data, int(row.size)))
 
 
 class Sampler:
+    """One request's sampler: its parameters and its own splitmix64 stream.  The arithmetic is C++
+    (``csrc/host/sampler.cpp``)."""
+
     def __init__(self, params: SamplingParams):
         params.validate()
         self.params = params
-        self.state = int(params.seed) & MASK64
+        self._state = ctypes.c_uint64(int(params.seed) & MASK64)
+        self._lib = _host()
+
+    @property
+    def state(self) -> int:
+        return int(self._state.value)
 
     def next_unit(self) -> float:
-        self.state = (self.state + 0x9E3779B97F4A7C15) & MASK64
-        z = self.state
-        z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & MASK64
-        z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & MASK64
-        z ^= z >> 31
-        return float(np.float32(z >> 40) / np.float32(16777216.0))
+        return float(self._lib.mbp_next_unit(ctypes.byref(self._state)))
+
+    @staticmethod
+    def _raise(code: int, usable: int, size: int) -> None:
+        if code == -1:
+            raise SamplerError(f"cannot sample from {usable} candidates out of {size} logits")
+        if code == -2:
+            raise SamplerError("logits contain NaN or infinity")
+        raise SamplerError(f"the sampler failed (code {code})")
 
     def distribution(self, logits: np.ndarray, usable: Optional[int] = None) -> List[Tuple[int, float]]:
-        logits = np.asarray(logits, dtype=np.float32).reshape(-1)
-        usable = len(logits) if usable is None else usable
-        if usable <= 0 or usable > len(logits):
-            raise SamplerError(f"cannot sample from {usable} candidates out of {len(logits)} logits")
-        cand = logits[:usable]
-        if not np.all(np.isfinite(cand)):
-            raise SamplerError("logits contain NaN or infinity")
+        row = _row(logits)
+        usable = int(row.size) if usable is None else int(usable)
         p = self.params
-        if p.temperature == 0.0:
-            return [(best_index(cand), 1.0)]
-        key = _total_order_key(cand).astype(np.int64)
-        order = np.argsort(-key, kind="stable")      # logit descending, id ascending among equals
-        if p.top_k > 0:
-            order = order[: p.top_k]
-        ranked = cand[order]
-        temperature = np.float32(p.temperature)
-        weights = np.exp((ranked - ranked[0]) / temperature, dtype=np.float32)
-        total = np.cumsum(weights, dtype=np.float32)[-1]
-        probs = weights / total
-        mass = np.cumsum(probs, dtype=np.float32)
-        reached = np.nonzero(mass >= np.float32(p.top_p))[0]
-        keep = int(reached[0]) + 1 if len(reached) else len(probs)
-        kept = probs[:keep]
-        kept_mass = np.cumsum(kept, dtype=np.float32)[-1]
-        kept = kept / kept_mass
-        return [(int(i), float(q)) for i, q in zip(order[:keep], kept)]
+        cap = max(1, min(int(row.size), usable if usable > 0 else 1))
+        ids, probs = np.zeros(cap, np.int32), np.zeros(cap, np.float32)
+        kept = self._lib.mbp_distribution(row.ctypes.data, int(row.size), usable, float(p.temperature), int(p.top_k), float(p.top_p),
+                                          ids.ctypes.data, probs.ctypes.data, cap)
+        if kept < 0:
+            self._raise(kept, usable, int(row.size))
+        return [(int(i), float(q)) for i, q in zip(ids[:kept], probs[:kept])]
 
     def sample(self, logits: np.ndarray, usable: Optional[int] = None) -> int:
-        dist = self.distribution(logits, usable)
-        if self.params.temperature == 0.0:
-            return dist[0][0]
-        draw = np.float32(self.next_unit())
-        cumulative = np.float32(0.0)
-        for token, prob in dist:
-            cumulative = np.float32(cumulative + np.float32(prob))
-            if draw < cumulative:
-                return token
-        return dist[-1][0]
+        row = _row(logits)
+        usable = int(row.size) if usable is None else int(usable)
+        p = self.params
+        token = self._lib.mbp_sample(row.ctypes.data, int(row.size), usable, float(p.temperature), int(p.top_k), float(p.top_p),
+                                     ctypes.byref(self._state))
+        if token < 0:
+            self._raise(token, usable, int(row.size))
+        return int(token)
