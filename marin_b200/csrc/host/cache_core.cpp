@@ -119,23 +119,25 @@ MBH_API int mbh_check(void* c, char* msg, int cap) {
 
 // ---- a whole step's accounting in one call each -----------------------------------------------------------------------
 // Before the step: every entry (handle, number of new tokens) must stay within max_seq_len positions and all of them
-// together must find their pages, which are then taken; otherwise nothing is taken and *bad names the entry at fault
-// (for MBH_OUT_OF_PAGES: -1, the step as a whole does not fit).
-MBH_API int mbh_step_reserve(void* c, int n, const int64_t* handles, const int* counts, int max_seq_len, int* bad) {
+// together must find their pages, which are then taken; otherwise nothing is taken.  info[0] names the entry at fault
+// (-1 for MBH_OUT_OF_PAGES: the step as a whole does not fit), info[1] receives the longest sequence after the step.
+MBH_API int mbh_step_reserve(void* c, int n, const int64_t* handles, const int* counts, int max_seq_len, int* info) {
     Cache* cache = static_cast<Cache*>(c);
     std::vector<Request*> reqs(n);
     std::vector<int> need(cache->groups(), 0), one(cache->groups(), 0);
-    *bad = -1;
+    info[0] = -1;
+    info[1] = 0;
     for (int i = 0; i < n; ++i) {
         reqs[i] = cache->find(handles[i]);
-        *bad = i;
+        info[0] = i;
         if (reqs[i] == nullptr) return MBH_UNKNOWN_REQUEST;
         if (counts[i] <= 0) return MBH_BAD_ARG;
         if (reqs[i]->length + counts[i] > max_seq_len) return MBH_CONTEXT_FULL;
+        info[1] = std::max(info[1], reqs[i]->length + counts[i]);
         cache->missing(*reqs[i], reqs[i]->length + counts[i], one.data());
         for (int g = 0; g < cache->groups(); ++g) need[g] += one[g];
     }
-    *bad = -1;
+    info[0] = -1;
     for (int g = 0; g < cache->groups(); ++g)
         if (need[g] > cache->pool(g).num_free()) return MBH_OUT_OF_PAGES;
     for (int i = 0; i < n; ++i) {

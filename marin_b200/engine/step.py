@@ -66,6 +66,7 @@ class Runner:
         self.views = CacheViews(cache)
         self.vocab = model.spec.vocab_size
         self.steps_run = 0
+        self._longest = 1
         #: after a step replayed from a graph: int32 ids of the largest logit of each returned row (lowest id among
         #: equals), computed inside the graph; None after any other step
         self.greedy_ids: Optional[torch.Tensor] = None
@@ -175,10 +176,22 @@ class Runner:
         if self.cache.state_needs:
             return
         self.graph_sizes = sorted(set(int(b) for b in batch_sizes))
-        self.graphs: Dict[int, dict] = {}
+        self.graphs: Dict[tuple, dict] = {}
+
+    #: sequences up to this long share the shortest graph; longer ones take the next power of two
+    GRAPH_MIN_SPAN = 1024
 
     def _graph_for(self, bucket: int, entries: Sequence[StepEntry]) -> dict:
-        g = self.graphs.get(bucket)
+        # A graph is captured per padded batch size and per span of sequence lengths (a power of two, at most the
+        # context capacity): the split of the keys over CTAs is part of the captured grid, and a split made for the
+        # whole capacity would leave short sequences to one CTA each.
+        longest = self._longest
+        span = self.GRAPH_MIN_SPAN
+        while span < longest:
+            span *= 2
+        span = min(span, self.max_seq_len)
+        key = (bucket, span)
+        g = self.graphs.get(key)
         if g is not None:
             return g
         from ..kernels import ops
@@ -190,12 +203,14 @@ class Runner:
         heads = max((m.heads for m in mixers), default=1)
         kv_heads = min((m.kv_heads for m in mixers), default=1)
         hd = max((m.head_dim for m in mixers), default=1)
-        # the split of the keys is fixed by the context capacity, so that the captured grid fits every step
-        split, chunks = ops.decode_split(bucket, kv_heads, self.max_seq_len)
-        g = {"static": (host, dev, torch.cuda.Event()), "workspace": Workspace(self.rt.device), "graph": None, "logits": None,
+        # the split of the keys is fixed by the span, so that the captured grid fits every step of this graph
+        split, chunks = ops.decode_split(bucket, kv_heads, span)
+        shared = next((o for (b, _), o in self.graphs.items() if b == bucket), None)
+        g = {"static": (host, dev, torch.cuda.Event()), "workspace": shared["workspace"] if shared else Workspace(self.rt.device),
+             "graph": None, "logits": None,
              "attn_split": (split, chunks),
              "attn_scratch": ops.decode_scratch(self.rt.device, bucket, heads, kv_heads, chunks, hd)}
-        self.graphs[bucket] = g
+        self.graphs[key] = g
 
         def run():
             ctx = self.build_context(entries, pad_to=bucket, static=g["static"])
@@ -248,10 +263,11 @@ class Runner:
         handles = np.fromiter((cache.requests[e.req_id].handle for e in entries), np.int64, n)
         counts = np.fromiter((len(e.tokens) for e in entries), np.int32, n)
         # one call checks the context capacity and takes every entry's pages, or takes none
-        bad = ctypes.c_int(-1)
-        rc = cache._lib.mbh_step_reserve(cache._core(), n, handles.ctypes.data, counts.ctypes.data, self.max_seq_len, ctypes.byref(bad))
+        info = (ctypes.c_int * 2)()
+        rc = cache._lib.mbh_step_reserve(cache._core(), n, handles.ctypes.data, counts.ctypes.data, self.max_seq_len, info)
+        self._longest = int(info[1])
         if rc == CONTEXT_FULL:
-            e = entries[bad.value]
+            e = entries[info[0]]
             raise StepError(f"request {e.req_id!r}: context full ({cache.length(e.req_id) + len(e.tokens)} positions needed, "
                             f"capacity {self.max_seq_len})")
         if rc == OUT_OF_PAGES:

@@ -127,7 +127,9 @@ def test_long_decoding(case):
     toks = random_prompt(random.Random(9), case.raw["vocab_size"], n)
     want = plain.forward(case.cfg, case.w, toks)
     runner = case.runner(num_pages=-(-n // case.page), graphs=True)
+    runner.GRAPH_MIN_SPAN = 32           # several graphs on the way: one per span of lengths (32, 64, 128, ...)
     close(run_portions(runner, "long", toks, [5] + [1] * (n - 5)), want, case.dtype, "long decoding")
+    assert len(runner.graphs) >= 3
 
 
 def test_first_tokens_of_a_sequence(case):
