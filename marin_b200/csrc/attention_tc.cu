@@ -4,15 +4,19 @@
 //   S = Q K^T      tcgen05.mma, M = 128 queries, N = 64 keys, K = HEAD_DIM; Q and K tiles in shared memory (TMA,
 //                  128-byte swizzle, K-major); the accumulator S is 64 columns of tensor memory;
 //   softmax        thread t owns query row t (TMEM lane t): it reads its 64 scores with tcgen05.ld, masks, keeps the
-//                  running maximum and sum in float32 (exp2 domain) — no shuffles — and writes P in bf16 to shared
-//                  memory in the swizzled K-major layout the next MMA reads;
-//   PV             tcgen05.mma, M = 128, N = HEAD_DIM, K = 64 keys; V stays as it lies in the cache ([key][d], d
+//                  running maximum and sum in float32 (exp2 domain) — no shuffles — and writes its row of P in bf16
+//                  back into tensor memory, over the first half of its own scores (tcgen05.st);
+//   PV             tcgen05.mma with P as the A operand straight from tensor memory, M = 128, N = HEAD_DIM, K = 64
+//                  keys; V stays as it lies in the cache ([key][d], d
 //                  contiguous), i.e. an MN-major B operand; the product accumulates in HEAD_DIM more TMEM columns.  The
 //                  running maximum a row's O is scaled by is only raised when the true maximum has moved by more than
 //                  8 (a factor 256, harmless in float32): then the row's O is read, rescaled and written back
 //                  (tcgen05.ld/st); otherwise O is never touched until the end.
 // K and V blocks arrive by TMA straight from the paged cache (one 16-key box per page piece and 64-column half) into
-// two buffers each; keys run two blocks ahead of the rows, values one.  Two CTAs fit an SM: one's softmax overlaps the
+// two buffers each; keys run two blocks ahead of the rows, values one.  S (and with it P) has two buffers as well; the
+// MMAs run in the order they are issued, so S of block i + 2 may follow P V of block i without a barrier.  Every
+// barrier used once per block exists per buffer parity, since the rows may run a block ahead of the issuer.
+// Two CTAs fit an SM: one's softmax overlaps the
 // other's MMAs.  Needs pages of at least 16 positions.  Waits are bounded and record a code in *error_flag.
 // The mma.sync kernel in attention_fast.cu is the fallback and the plain twin (the reference's counterpart:
 // crates/cuda/src/attention_mma.cu:43-180).
@@ -33,8 +37,8 @@ static_assert(HEAD_DIM == 64 || HEAD_DIM == 128, "the tcgen05 attention kernel t
 #define TA_BN 64
 #define TA_Q_BYTES (NH * TA_BM * 128)
 #define TA_KV_BYTES (NH * TA_BN * 128)  // one of K or V, one buffer
-#define TA_P_BYTES (TA_BM * 128)
-#define TA_SMEM (TA_Q_BYTES + 4 * TA_KV_BYTES + TA_P_BYTES + 256)
+#define TA_PAGE_CACHE 1024            // page ids of a tile's keys kept in shared memory (more are read from global memory)
+#define TA_SMEM (TA_Q_BYTES + 4 * TA_KV_BYTES + 256)
 #define TA_TMEM_COLS 256               // two S buffers of 64 columns, then O: HEAD_DIM columns
 #define TA_O_COL (2 * TA_BN)
 
@@ -107,6 +111,16 @@ __device__ __forceinline__ void mbar_arrive_one(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+// The MMA with its A operand in tensor memory (row m in lane m, two bf16 per 32-bit column) and B in shared memory.
+__device__ __forceinline__ void umma_bf16_tmem_a(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
 // 160 threads: warps 0..3 own the 128 query rows (softmax, output); warp 4 asks for keys and values and issues the MMAs.
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
     asm volatile(
@@ -124,6 +138,18 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ void tmem_st32_bits(uint32_t taddr, const uint32_t* v) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]),
+          "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]),
+          "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]),
+          "r"(v[30]), "r"(v[31])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
 __global__ void __launch_bounds__(160, 2) attn_prefill_tc_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
     bf16* __restrict__ out, const int* __restrict__ block_table, int max_pages, const int* __restrict__ cu_tokens,
@@ -132,16 +158,16 @@ __global__ void __launch_bounds__(160, 2) attn_prefill_tc_kernel(
     extern __shared__ __align__(1024) uint8_t smem[];     // the swizzled tiles need 1024-byte alignment (checked below)
     uint8_t* sQ = smem;
     uint8_t* sKV = sQ + TA_Q_BYTES;                       // [buffer][K then V][half][64 rows][128 B]
-    uint8_t* sP = sKV + 4 * TA_KV_BYTES;
-    uint64_t* bars = (uint64_t*)(sP + TA_P_BYTES);
+    uint64_t* bars = (uint64_t*)(sKV + 4 * TA_KV_BYTES);
     uint64_t* q_full = bars;              // Q tile has landed
     uint64_t* k_full = bars + 1;          // [2] a block of K has landed
     uint64_t* v_full = bars + 3;          // [2] a block of V has landed
     uint64_t* v_free = bars + 5;          // [2] the P V product that read the V buffer is done
     uint64_t* s_done = bars + 7;          // [2] S = Q K^T is in its tensor-memory buffer (and its K buffer is free again)
-    uint64_t* s_free = bars + 9;          // [2] every row has read its scores from the buffer (4 warps arrive)
-    uint64_t* p_ready = bars + 11;        // P is in shared memory (4 warps arrive)
-    uint64_t* pv_done = bars + 12;        // O += P V has been added
+    uint64_t* p_ready = bars + 9;         // [2] P is in tensor memory, over the first half of its S buffer (4 warps arrive)
+    // Every barrier that is used once per key block exists twice, one per buffer parity: a waiter may be a block behind
+    // or ahead of the other side, and a single barrier's phase parity would then be taken for the wrong block.
+    // v_free[b] also tells the rows that O += P V of a block with parity b has been added.
     uint32_t* tmem_slot = (uint32_t*)(bars + 13);
     volatile int* abort = (volatile int*)(tmem_slot + 1);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -156,8 +182,8 @@ __global__ void __launch_bounds__(160, 2) attn_prefill_tc_kernel(
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
         for (int b = 0; b < 2; ++b) { mbar_init(&k_full[b], 1); mbar_init(&v_full[b], 1); mbar_init(&v_free[b], 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(&s_done[b], 1); mbar_init(&s_free[b], 4); }
-        mbar_init(p_ready, 4); mbar_init(pv_done, 1);
+        for (int b = 0; b < 2; ++b) mbar_init(&s_done[b], 1);
+        mbar_init(&p_ready[0], 4); mbar_init(&p_ready[1], 4);
         *abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -166,15 +192,23 @@ __global__ void __launch_bounds__(160, 2) attn_prefill_tc_kernel(
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TA_TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t tmem_base = *tmem_slot;
     const int q_first = pos0 + qt * TA_BM, q_last = q_first + rows - 1;
     const int k_lo = window > 0 ? max(0, q_first - window + 1) : 0;
     const int kh = h / GROUP;
     const int kb_first = k_lo / TA_BN, kb_last = q_last / TA_BN;
     const int nblk = kb_last - kb_first + 1;
+    // the page ids of this tile's keys, copied once: the issuer must not wait for global memory between two MMAs
+    __shared__ int s_pages[TA_PAGE_CACHE];
+    const int page_first = (kb_first * TA_BN) >> page_shift;
+    {
+        const int* table = block_table + (size_t)r * max_pages;
+        const int count = min(TA_PAGE_CACHE, (((kb_last + 1) * TA_BN - 1) >> page_shift) - page_first + 1);
+        for (int i = threadIdx.x; i < count; i += blockDim.x) s_pages[i] = table[min(page_first + i, max_pages - 1)];
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
     // The online softmax does not care about the order of the key blocks.  Every CTA starts at another block, so that
     // the many CTAs that read the same keys and values (the query tiles of a request, the heads of a group) do not
     // all ask the L2 for the same lines at the same moment.
@@ -196,7 +230,9 @@ __global__ void __launch_bounds__(160, 2) attn_prefill_tc_kernel(
                 const int g = lane * box_rows;                  // box_rows keys per box: 16, 32 or 64 (at most a page)
                 if (g < TA_BN) {
                     const int key = kb * TA_BN + g;
-                    const int row = (int)((((size_t)table[key >> page_shift] * K + kh) << page_shift) + (size_t)(key & page_mask));
+                    const int pg = (key >> page_shift) - page_first;
+                    const int page_id = pg < TA_PAGE_CACHE ? s_pages[pg] : table[min(key >> page_shift, max_pages - 1)];
+                    const int row = (int)((((size_t)page_id * K + kh) << page_shift) + (size_t)(key & page_mask));
 #pragma unroll
                     for (int hf = 0; hf < NH; ++hf) tma_load_2d(dst + hf * (TA_BN * 128) + g * 128, map, hf * 64, row, bar);
                 }
@@ -245,23 +281,25 @@ __global__ void __launch_bounds__(160, 2) attn_prefill_tc_kernel(
                     ++next_v;
                     progressed = true;
                 }
-                if (__shfl_sync(0xffffffffu, (int)(next_s < next_k && mbar_test(&k_full[next_s & 1], (next_s >> 1) & 1) &&
-                                                   (next_s < 2 || mbar_test(&s_free[next_s & 1], ((next_s - 2) >> 1) & 1))), 0)) {
+                // S(i) goes where P(i - 2) lies: the MMAs run in the order they are issued, so it is enough that
+                // P(i - 2) V(i - 2) has been issued before
+                if (__shfl_sync(0xffffffffu, (int)(next_s < next_k && next_s < next_pv + 2 && mbar_test(&k_full[next_s & 1], (next_s >> 1) & 1)), 0)) {
                     issue_s(next_s);
                     ++next_s;
                     progressed = true;
                 }
-                if (__shfl_sync(0xffffffffu, (int)(next_pv < next_v && mbar_test(p_ready, next_pv & 1) && mbar_test(&v_full[next_pv & 1], (next_pv >> 1) & 1)), 0)) {
+                if (__shfl_sync(0xffffffffu, (int)(next_pv < next_v && mbar_test(&p_ready[next_pv & 1], (next_pv >> 1) & 1) && mbar_test(&v_full[next_pv & 1], (next_pv >> 1) & 1)), 0)) {
                     // O += P(i) V(i) in TMEM columns [128, 128 + D); any rescaling of O by the rows happened before they arrived
                     const int buf = next_pv & 1;
                     if (lane == 0) {
                         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                        const uint32_t sp = smem_u32(sP), sv = smem_u32(sKV + (size_t)buf * 2 * TA_KV_BYTES) + TA_KV_BYTES;
+                        // P is the A operand straight from tensor memory: row = lane, two bf16 per 32-bit column
+                        const uint32_t tp = tmem_base + (uint32_t)(buf * TA_BN);
+                        const uint32_t sv = smem_u32(sKV + (size_t)buf * 2 * TA_KV_BYTES) + TA_KV_BYTES;
 #pragma unroll
                         for (int kk = 0; kk < TA_BN / 16; ++kk)
-                            umma_bf16(tmem_base + TA_O_COL, umma_desc(sp) + 2 * kk, umma_desc_mn(sv + kk * 2048, TA_BN * 128), idesc_pv,
-                                      (next_pv > 0 || kk > 0) ? 1u : 0u);
-                        umma_commit(pv_done);
+                            umma_bf16_tmem_a(tmem_base + TA_O_COL, tp + (uint32_t)(kk * 8), umma_desc_mn(sv + kk * 2048, TA_BN * 128), idesc_pv,
+                                             (next_pv > 0 || kk > 0) ? 1u : 0u);
                         umma_commit(&v_free[buf]);
                     }
                     ++next_pv;
@@ -311,13 +349,11 @@ __global__ void __launch_bounds__(160, 2) attn_prefill_tc_kernel(
             const bool raise = m_true > m_used + 8.0f || (m_used == -INFINITY && m_true != -INFINITY);
             const float m_new = raise ? m_true : m_used;
             const float corr = raise ? ta_exp2(m_used - m_new) : 1.0f;      // exp2(-inf) = 0 on the first raise
-            bool pv_waited = i == 0;
             if (__any_sync(0xffffffffu, raise) && i >= 1) {
-                // O is being added to by the MMAs of block i - 1 until pv_done(i - 1)
-                ok = wait_or_abort(pv_done, (i - 1) & 1, abort, error_flag, 24);
+                // O is being added to by the MMAs of block i - 1 until they are done (blocks up to i - 2 are: S(i) came after them)
+                ok = wait_or_abort(&v_free[(i - 1) & 1], ((i - 1) >> 1) & 1, abort, error_flag, 24);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
-                pv_waited = true;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
                 for (int c = 0; c < D / 32; ++c) {
@@ -336,11 +372,6 @@ __global__ void __launch_bounds__(160, 2) attn_prefill_tc_kernel(
             for (int hf = 0; hf < 2; ++hf) {
                 float s[32];
                 tmem_ld32(s_col + hf * 32, s);
-                if (hf == 1) {                                  // the scores are in registers: this S buffer may be overwritten
-                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive_one(&s_free[i & 1]);
-                }
                 if (!interior) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j)
@@ -357,21 +388,14 @@ __global__ void __launch_bounds__(160, 2) attn_prefill_tc_kernel(
                 }
             }
             l_run = l_run * corr + sum;
-            if (!pv_waited) {                                   // P(i - 1) is read by the MMAs of block i - 1 until pv_done(i - 1)
-                ok = wait_or_abort(pv_done, (i - 1) & 1, abort, error_flag, 24);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-            }
-            uint4* prow = reinterpret_cast<uint4*>(sP + row_t * 128);
-#pragma unroll
-            for (int c = 0; c < TA_BN / 8; ++c) prow[c ^ (row_t & 7)] = packed[c];   // 128-byte swizzle: piece index xor (row mod 8)
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // ordinary stores, read by the MMA through the async proxy
+            // the row of P goes over the first 32 columns of its own scores (all 64 are in registers by now)
+            tmem_st32_bits(s_col, reinterpret_cast<const uint32_t*>(packed));
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
-            if (lane == 0) mbar_arrive_one(p_ready);
+            if (lane == 0) mbar_arrive_one(&p_ready[i & 1]);
         }
         if (ok) {
-            ok = wait_or_abort(pv_done, (nblk - 1) & 1, abort, error_flag, 24);
+            ok = wait_or_abort(&v_free[(nblk - 1) & 1], ((nblk - 1) >> 1) & 1, abort, error_flag, 24);
             ok = __all_sync(0xffffffffu, ok);
         }
         if (ok) {
