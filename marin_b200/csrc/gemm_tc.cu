@@ -504,8 +504,10 @@ template <int BN, int STAGES>
 __global__ void __launch_bounds__(320) gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                  const __grid_constant__ CUtensorMap map_x,
                                                                  void* __restrict__ out, int mode, int T, int N, int K,
-                                                                 int* __restrict__ error_flag) {
+                                                                 int* __restrict__ error_flag, const TcNormOut norm,
+                                                                 const TcRowScale scale) {
     extern __shared__ uint8_t smem_raw[];
+    __shared__ float s_pscale[2][BN];          // the per-token factors of a coupled norm, for the tile in each accumulator
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     using L = TcSmem<BN>;
     uint64_t* full = (uint64_t*)(smem + STAGES * L::STAGE_BYTES);
@@ -582,19 +584,46 @@ __global__ void __launch_bounds__(320) gemm_tc_persistent_kernel(const __grid_co
         int local = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
-            const int n0 = tile_rows(tile, tiles_n, tiles_t) * TC_BM, t0 = tile_tokens(tile, tiles_n, tiles_t) * BN;
+            const int tile_row = tile_rows(tile, tiles_n, tiles_t);
+            const int n0 = tile_row * TC_BM, t0 = tile_tokens(tile, tiles_n, tiles_t) * BN;
             const int buf = local & 1;
             const uint32_t acc_phase = (local >> 1) & 1;
+            if (scale.sumsq != nullptr) {
+                // while the MMAs of this tile run: each of the 256 epilogue threads adds the slots of one token, in slot
+                // order, up to 24 loads in flight; the eight warps then meet at a barrier of their own
+                for (int e = (warp - 2) * 32 + lane; e < BN; e += 256) {
+                    const int t = t0 + e;
+                    float sum = 0.0f;
+                    if (t < T) {
+                        for (int s0 = 0; s0 < scale.slots; s0 += 24) {
+                            float part[24];
+#pragma unroll
+                            for (int i = 0; i < 24; ++i) part[i] = s0 + i < scale.slots ? __ldcg(&scale.sumsq[(size_t)(s0 + i) * T + t]) : 0.0f;
+#pragma unroll
+                            for (int i = 0; i < 24; ++i) sum += part[i];
+                        }
+                    }
+                    s_pscale[buf][e] = t < T ? 1.0f / sqrtf(sum / (float)scale.dim + scale.eps) : 0.0f;
+                }
+                asm volatile("bar.sync 1, 256;" ::: "memory");
+            }
+            // a warp whose wait gave up keeps walking the tiles (the barrier above counts on it) but touches nothing
             if (ok && !mbar_wait(&acc_full[buf], acc_phase)) { if (lane == 0) atomicExch(error_flag, 14); ok = false; }
             ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
+            if (!ok) continue;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int n = n0 + quarter * 32 + lane;
 #pragma unroll 1
             for (int c0 = col_half * HALF_COLS; c0 < (col_half == 0 ? HALF_COLS : BN); c0 += 16) {
                 float v[16];
                 tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c0), v);
-                if (mode == TC_OUT_SWIGLU) {
+                if (scale.sumsq != nullptr) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) v[j] *= s_pscale[buf][c0 + j];
+                }
+                if (norm.weight != nullptr) {
+                    store_chunk_norm(out, t0 + c0, n, n < N, T, N, v, norm, norm.sumsq + (size_t)(tile_row * 4 + quarter) * T, lane);
+                } else if (mode == TC_OUT_SWIGLU) {
                     if (n0 + quarter * 32 < N) store_chunk_swiglu(out, t0 + c0, n0 + quarter * 32, lane, T, N, v);
                 } else if (n < N) store_chunk(out, mode, t0 + c0, n, T, N, v);
             }
@@ -650,7 +679,7 @@ MB_API int mb_gemm_tc_tiles(int T, int N, int bn) { return ((N + TC_BM - 1) / TC
 
 template <int BN, int STAGES>
 static int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int mode, int T, int N, int K, int ctas,
-                             int* error_flag, cudaStream_t s) {
+                             int* error_flag, const TcNormOut& norm, const TcRowScale& scale, cudaStream_t s) {
     constexpr int smem = STAGES * TcSmem<BN>::STAGE_BYTES + 1024 + 256;
     static_assert(smem <= 227 * 1024, "the ring does not fit shared memory");
     static bool configured = false;
@@ -661,32 +690,49 @@ static int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, void*
     }
     const int tiles = ((N + TC_BM - 1) / TC_BM) * ((T + BN - 1) / BN);
     return launch_kernel(gemm_tc_persistent_kernel<BN, STAGES>, dim3(tiles < ctas ? tiles : ctas), dim3(320), smem, s, 0, mw, mx, out,
-                         mode, T, N, K, error_flag);
+                         mode, T, N, K, error_flag, norm, scale);
 }
 
-// The persistent kernel: bn tokens per tile (a multiple of 16 from 128 to 256), `ctas` CTAs (one per SM).
-MB_API int mb_gemm_tc_persistent(const void* x, const void* w, void* out, int mode, int T, int N, int K, int bn, int ctas,
-                                 int* error_flag, cudaStream_t s) {
+static int persistent_dispatch(const void* x, const void* w, void* out, int mode, int T, int N, int K, int bn, int ctas,
+                               int* error_flag, const TcNormOut& norm, const TcRowScale& scale, cudaStream_t s) {
     if (T <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15) || ctas <= 0) return MB_ERR_BAD_SIZE;
     if (mode < 0 || mode > 3 || (mode == 3 && N % 32 != 0)) return MB_ERR_BAD_DTYPE;
+    if (norm.weight != nullptr && (mode != TC_OUT_F32_ACC || norm.scaled == nullptr || norm.sumsq == nullptr)) return MB_ERR_BAD_DTYPE;
+    if (scale.sumsq != nullptr && (scale.slots <= 0 || scale.dim <= 0)) return MB_ERR_BAD_SIZE;
     CUtensorMap mw, mx;
     int rc = make_map(&mw, w, N, K, TC_BM);
     if (rc) return rc;
     rc = make_map(&mx, x, T, K, bn);
     if (rc) return rc;
     switch (bn) {
-        case 128: return launch_persistent<128, 6>(mw, mx, out, mode, T, N, K, ctas, error_flag, s);
-        case 144: return launch_persistent<144, 6>(mw, mx, out, mode, T, N, K, ctas, error_flag, s);
-        case 160: return launch_persistent<160, 5>(mw, mx, out, mode, T, N, K, ctas, error_flag, s);
-        case 176: return launch_persistent<176, 5>(mw, mx, out, mode, T, N, K, ctas, error_flag, s);
-        case 192: return launch_persistent<192, 5>(mw, mx, out, mode, T, N, K, ctas, error_flag, s);
-        case 208: return launch_persistent<208, 4>(mw, mx, out, mode, T, N, K, ctas, error_flag, s);
-        case 224: return launch_persistent<224, 4>(mw, mx, out, mode, T, N, K, ctas, error_flag, s);
-        case 240: return launch_persistent<240, 4>(mw, mx, out, mode, T, N, K, ctas, error_flag, s);
-        case 256: return launch_persistent<256, 4>(mw, mx, out, mode, T, N, K, ctas, error_flag, s);
+        case 128: return launch_persistent<128, 6>(mw, mx, out, mode, T, N, K, ctas, error_flag, norm, scale, s);
+        case 144: return launch_persistent<144, 6>(mw, mx, out, mode, T, N, K, ctas, error_flag, norm, scale, s);
+        case 160: return launch_persistent<160, 5>(mw, mx, out, mode, T, N, K, ctas, error_flag, norm, scale, s);
+        case 176: return launch_persistent<176, 5>(mw, mx, out, mode, T, N, K, ctas, error_flag, norm, scale, s);
+        case 192: return launch_persistent<192, 5>(mw, mx, out, mode, T, N, K, ctas, error_flag, norm, scale, s);
+        case 208: return launch_persistent<208, 4>(mw, mx, out, mode, T, N, K, ctas, error_flag, norm, scale, s);
+        case 224: return launch_persistent<224, 4>(mw, mx, out, mode, T, N, K, ctas, error_flag, norm, scale, s);
+        case 240: return launch_persistent<240, 4>(mw, mx, out, mode, T, N, K, ctas, error_flag, norm, scale, s);
+        case 256: return launch_persistent<256, 4>(mw, mx, out, mode, T, N, K, ctas, error_flag, norm, scale, s);
         default: return MB_ERR_BAD_SIZE;
     }
+}
+
+// The persistent kernel: bn tokens per tile (a multiple of 16 from 128 to 256), `ctas` CTAs (one per SM).
+MB_API int mb_gemm_tc_persistent(const void* x, const void* w, void* out, int mode, int T, int N, int K, int bn, int ctas,
+                                 int* error_flag, cudaStream_t s) {
+    return persistent_dispatch(x, w, out, mode, T, N, K, bn, ctas, error_flag, TcNormOut{}, TcRowScale{}, s);
+}
+
+// The same coupled with the RMS norms around it (see mb_gemm_tc_coupled; the slots are mb_gemm_tc_norm_slots(N, 1)).
+MB_API int mb_gemm_tc_persistent_coupled(const void* x, const void* w, void* out, int mode, int T, int N, int K, int bn, int ctas,
+                                         const float* norm_weight, int norm_unit_offset, void* scaled_out, float* sumsq_out,
+                                         const float* scale_sumsq, int scale_slots, int scale_dim, float scale_eps,
+                                         int* error_flag, cudaStream_t s) {
+    TcNormOut norm{norm_weight, (bf16*)scaled_out, sumsq_out, norm_unit_offset};
+    TcRowScale scale{scale_sumsq, scale_slots, scale_dim, scale_eps};
+    return persistent_dispatch(x, w, out, mode, T, N, K, bn, ctas, error_flag, norm, scale, s);
 }
 
 // x [T, K] bf16, w [N, K] bf16, out [T, N]: bf16 (mode 0), float32 (1), float32 += (2).  K must be a multiple

@@ -94,6 +94,10 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
 use_tensor_cores = True
 #: with few tokens an RMS norm rides on the products around it instead of running as a kernel of its own
 couple_norms = True
+#: the same with many tokens, in the persistent kernel.  Off: measured on B200 at 2,048 tokens (Qwen3-4B layers) the
+#: per-token factors that every tile's epilogue has to gather cost the gate/up product 39 us where the norm's own
+#: kernel costs 7.
+couple_norms_in_prefill = False
 SM_COUNT = 148
 _scratch = {}
 
@@ -106,7 +110,7 @@ def _gemm_scratch(device):
         s = {"partials": torch.empty(8 << 20, device=device, dtype=torch.float32),
              "counters": torch.zeros(1 << 16, device=device, dtype=torch.int32),
              "error": torch.zeros(1, device=device, dtype=torch.int32),
-             "sumsq": torch.empty(1 << 20, device=device, dtype=torch.float32)}
+             "sumsq": torch.empty(1 << 22, device=device, dtype=torch.float32)}
         _scratch[key] = s
     return s
 
@@ -200,12 +204,27 @@ def gemm(x, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False, then_n
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and T > 0):
         mode = 2 if accumulate else (0 if out.dtype == torch.bfloat16 else 1)
         if T > 128 and -(-N // 128) * -(-T // 128) >= SM_COUNT // 2:
-            assert scaled is None
             s = _gemm_scratch(x.device)
-            _check(_lib("mb_gemm_tc").mb_gemm_tc_persistent(_ptr(x), _ptr(w), _ptr(out), _c_int(mode), _c_int(T), _c_int(N),
-                                                           _c_int(K), _c_int(persistent_plan(T, N)), _c_int(SM_COUNT),
-                                                           _ptr(s["error"]), _stream()), "gemm (tensor cores, persistent)")
-            return None
+            lib = _lib("mb_gemm_tc")
+            carried = None
+            if (then_norm is not None and accumulate and couple_norms and couple_norms_in_prefill and N % 8 == 0
+                    and then_norm.rows.dtype == torch.bfloat16 and then_norm.rows.data_ptr() % 16 == 0):
+                slots = int(lib.mb_gemm_tc_norm_slots(_c_int(N), _c_int(1)))
+                if slots * T <= s["sumsq"].numel():
+                    carried = NormedRows(then_norm.rows, s["sumsq"], slots, N, then_norm.eps)
+            if carried is None and scaled is None:
+                _check(lib.mb_gemm_tc_persistent(_ptr(x), _ptr(w), _ptr(out), _c_int(mode), _c_int(T), _c_int(N),
+                                                 _c_int(K), _c_int(persistent_plan(T, N)), _c_int(SM_COUNT),
+                                                 _ptr(s["error"]), _stream()), "gemm (tensor cores, persistent)")
+                return None
+            _check(lib.mb_gemm_tc_persistent_coupled(
+                _ptr(x), _ptr(w), _ptr(out), _c_int(mode), _c_int(T), _c_int(N), _c_int(K), _c_int(persistent_plan(T, N)), _c_int(SM_COUNT),
+                _ptr(then_norm.weight) if carried is not None else None, _c_int(int(then_norm.unit_offset)) if carried is not None else _c_int(0),
+                _ptr(carried.rows) if carried is not None else None, _ptr(carried.sumsq) if carried is not None else None,
+                _ptr(scaled.sumsq) if scaled is not None else None, _c_int(scaled.slots if scaled is not None else 0),
+                _c_int(scaled.dim if scaled is not None else 0), _c_float(scaled.eps if scaled is not None else 0.0),
+                _ptr(s["error"]), _stream()), "gemm (tensor cores, persistent, coupled with a norm)")
+            return carried
         bn, splits = gemm_plan(T, N, K)
         s = _gemm_scratch(x.device)
         lib = _lib("mb_gemm_tc")
@@ -438,6 +457,12 @@ def gemm_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor, out: torch.Tensor,
         return
     s = _gemm_scratch(x.device)
     if T > 128 and -(-N // 128) * -(-T // 128) >= SM_COUNT // 2:
+        if scaled is not None:
+            _check(_lib("mb_gemm_tc").mb_gemm_tc_persistent_coupled(
+                _ptr(x), _ptr(w_interleaved), _ptr(out), _c_int(3), _c_int(T), _c_int(N), _c_int(K), _c_int(persistent_plan(T, N)),
+                _c_int(SM_COUNT), None, _c_int(0), None, None, _ptr(scaled.sumsq), _c_int(scaled.slots), _c_int(scaled.dim),
+                _c_float(scaled.eps), _ptr(s["error"]), _stream()), "gemm+swiglu (tensor cores, persistent, coupled with a norm)")
+            return
         _check(_lib("mb_gemm_tc").mb_gemm_tc_persistent(_ptr(x), _ptr(w_interleaved), _ptr(out), _c_int(3), _c_int(T), _c_int(N),
                                                        _c_int(K), _c_int(persistent_plan(T, N)), _c_int(SM_COUNT),
                                                        _ptr(s["error"]), _stream()), "gemm+swiglu (tensor cores, persistent)")

@@ -318,7 +318,8 @@ def test_gemm_tensor_cores(ops, T, N, K):
 
 
 @pytest.mark.parametrize("T,N,K,N2,unit", [(8, 2560, 4096, 6144, False), (1, 320, 512, 384, False), (13, 200, 264, 96, True),
-                                            (33, 1024, 9728, 2048, False), (64, 2560, 512, 640, False), (16, 128, 64, 64, True)])
+                                            (33, 1024, 9728, 2048, False), (64, 2560, 512, 640, False), (16, 128, 64, 64, True),
+                                            (1000, 2560, 512, 2560, False), (2048, 2560, 1024, 6144, True), (777, 1536, 320, 96, False)])
 def test_gemm_carries_the_norm_that_follows(ops, monkeypatch, T, N, K, N2, unit):
     """h += x W^T with the RMS norm of the new h riding on it, finished by the next product (plain and with
     SwiGLU): against float64, and against the same three steps with the norm as a kernel of its own."""
@@ -330,6 +331,7 @@ def test_gemm_carries_the_norm_that_follows(ops, monkeypatch, T, N, K, N2, unit)
     w2 = (torch.randn(N2, N, device=DEV, generator=g) / math.sqrt(N)).to(torch.bfloat16)
     eps = 1e-5
     monkeypatch.setattr(ops, "COUPLED_NORM_MAX_TOKENS", 64)         # every tile width the kernel couples at
+    monkeypatch.setattr(ops, "couple_norms_in_prefill", True)       # and the persistent kernel, for many tokens
     for _ in range(2):
         h = h0.clone()
         normed = torch.full((T, N), float("nan"), device=DEV, dtype=torch.bfloat16)
