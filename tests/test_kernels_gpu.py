@@ -461,6 +461,26 @@ def test_attention_long_contexts_bf16(ops, H, K, d, page, window):
     torch.testing.assert_close(out.float(), want.float(), rtol=2e-2, atol=2e-2)
 
 
+@pytest.mark.parametrize("H,K,d,page,split", [(32, 8, 128, 16, 64), (8, 2, 64, 16, 128), (6, 3, 48, 8, 64), (4, 4, 128, 32, 64)])
+def test_attention_decode_with_more_chunks_than_a_cluster_holds(ops, H, K, d, page, split):
+    """Sequences cut into more than eight chunks merge through scratch memory (the last CTA combines them) instead of
+    through a cluster; run twice: the arrival counters must be back at zero."""
+    g = torch.Generator(device=DEV).manual_seed(23)
+    lens_new = [(1500, 1), (70, 1), (0, 1), (1023, 1), (640, 1)]
+    pages = sum(-(-(c + n) // page) for c, n in lens_new) + 2
+    q, kc, vc, table, ctx = paged_case(g, torch.bfloat16, lens_new, H, K, d, page, pages)
+    chunks = -(-1501 // split)
+    assert chunks > 8
+    ctx.attn_split = (split, chunks)
+    want = torch.empty_like(q)
+    ref.attention(q, kc, vc, want, ctx, table, H, K, d, 1.0 / math.sqrt(d), 0)
+    for _ in range(2):
+        out = torch.full_like(q, float("nan"))
+        ops.attention(q, kc, vc, out, ctx, table, H, K, d, 1.0 / math.sqrt(d), 0)
+        ops.check_device_errors()
+        torch.testing.assert_close(out.float(), want.float(), rtol=2e-2, atol=2e-2)
+
+
 @pytest.mark.parametrize("T,I,K", [(1, 9728, 2560), (8, 320, 96), (40, 144, 72), (300, 1024, 256), (2048, 2048, 512), (64, 4864, 1280)])
 def test_gemm_with_swiglu_epilogue(ops, T, I, K):
     """silu(x Wg^T) * (x Wu^T) with the activation applied to the float32 accumulators, against float64."""
