@@ -239,7 +239,7 @@ def prefill_device(engine, tokens, runs, warmup):
 
 def reference_arm():
     """The reference is a Rust workspace (cargo, rustc); neither exists in this image, so it cannot be
-    built or installed offline, and `pip install /root/reference` has nothing to install (no Python package)."""
+    built or installed offline, and a pip install of its source tree has nothing to install (no Python package)."""
     print(json.dumps({"impl": "reference", "unavailable": "Kayleexx/marin is a Rust workspace; no cargo/rustc in this image and no Python package to pip-install"}))
     return 0
 
