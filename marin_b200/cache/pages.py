@@ -45,6 +45,10 @@ def host_lib() -> ctypes.CDLL:
         "mbp_best_index": (i32, [vp, i32]), "mbp_distribution": (i32, [vp, i32, i32, ctypes.c_float, i32, ctypes.c_float, vp, vp, i32]),
         "mbp_next_unit": (ctypes.c_float, [ctypes.POINTER(ctypes.c_uint64)]),
         "mbp_sample": (i32, [vp, i32, i32, ctypes.c_float, i32, ctypes.c_float, ctypes.POINTER(ctypes.c_uint64)]),
+        "mbl_open": (vp, [text, text, i32]), "mbl_close": (None, [vp]), "mbl_count": (i32, [vp]),
+        "mbl_data_start": (ctypes.c_longlong, [vp]),
+        "mbl_entry": (i32, [vp, i32, text, i32, text, i32, ctypes.POINTER(ctypes.c_longlong), i32,
+                            ctypes.POINTER(ctypes.c_longlong), ctypes.POINTER(ctypes.c_longlong)]),
         "mbh_pack_step": (i32, [vp, i32, vp, vp, vp, vp, vp, i32, i32, vp, i32, vp, vp]),
     }
     for name, (res, args) in signatures.items():

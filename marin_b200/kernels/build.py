@@ -152,7 +152,7 @@ LIBRARIES: Dict[str, List[str]] = {
     "mb_attention_simple": ["attention_simple.cu"],
     "mb_sampling": ["sampling.cu"],
     "mb_gemm_tc": ["gemm_tc.cu"],
-    "mb_host": ["host/cache_core.cpp", "host/scheduler.cpp", "host/sampler.cpp"],
+    "mb_host": ["host/cache_core.cpp", "host/scheduler.cpp", "host/sampler.cpp", "host/safetensors.cpp"],
 }
 
 

@@ -8,6 +8,7 @@ tensors are views until they are copied to the device.
 """
 from __future__ import annotations
 
+import ctypes
 import json
 import mmap
 import os
@@ -52,45 +53,32 @@ class SafetensorsFile:
     """One memory-mapped safetensors file."""
 
     def __init__(self, path: str):
+        """The header is read and checked by the C++ host library (``csrc/host/safetensors.cpp``); the bytes are
+        mapped here."""
+        from ..cache.pages import host_lib
+
         self.path = path
-        size = os.path.getsize(path)
-        if size < 8:
-            raise SafetensorsError(f"{path}: too short to hold a safetensors header (partial download?)")
-        self._fh = open(path, "rb")
-        (header_len,) = struct.unpack("<Q", self._fh.read(8))
-        if header_len > MAX_HEADER_BYTES or 8 + header_len > size:
-            raise SafetensorsError(f"{path}: header of {header_len} bytes does not fit the file (partial download?)")
+        lib = host_lib()
+        err = ctypes.create_string_buffer(1024)
+        handle = lib.mbl_open(os.fsencode(path), err, len(err))
+        if not handle:
+            raise SafetensorsError(err.value.decode("utf-8", "replace"))
         try:
-            header = json.loads(self._fh.read(header_len).decode("utf-8"))
-        except (UnicodeDecodeError, json.JSONDecodeError) as err:
-            raise SafetensorsError(f"{path}: header is not valid JSON: {err}") from err
-        if not isinstance(header, dict):
-            raise SafetensorsError(f"{path}: header must be a JSON object")
-        self.data_start = 8 + header_len
-        data_bytes = size - self.data_start
-        self.tensors: Dict[str, TensorInfo] = {}
-        for name, entry in header.items():
-            if name == "__metadata__":
-                continue
-            try:
-                dtype = entry["dtype"]
-                shape = tuple(int(s) for s in entry["shape"])
-                begin, end = (int(v) for v in entry["data_offsets"])
-            except (KeyError, TypeError, ValueError) as err:
-                raise SafetensorsError(f"{path}: malformed entry for tensor `{name}`") from err
-            if dtype not in _DTYPES:
-                raise SafetensorsError(f"{path}: tensor `{name}` has unsupported dtype {dtype}")
-            count = 1
-            for s in shape:
-                if s < 0:
-                    raise SafetensorsError(f"{path}: tensor `{name}` has a negative size")
-                count *= s
-            if begin < 0 or end < begin or end - begin != count * _DTYPES[dtype][1]:
-                raise SafetensorsError(f"{path}: tensor `{name}`: offsets {begin}..{end} do not match shape {shape} {dtype}")
-            if end > data_bytes:
-                raise SafetensorsError(f"{path}: tensor `{name}` ends at byte {end} but the file holds {data_bytes} (partial download?)")
-            self.tensors[name] = TensorInfo(name, dtype, shape, begin, end)
-        self._map = mmap.mmap(self._fh.fileno(), 0, access=mmap.ACCESS_READ) if size > 0 else None
+            self.data_start = int(lib.mbl_data_start(handle))
+            self.tensors: Dict[str, TensorInfo] = {}
+            name, dtype = ctypes.create_string_buffer(4096), ctypes.create_string_buffer(16)
+            shape = (ctypes.c_longlong * 16)()
+            begin, end = ctypes.c_longlong(), ctypes.c_longlong()
+            for i in range(lib.mbl_count(handle)):
+                ndim = lib.mbl_entry(handle, i, name, len(name), dtype, len(dtype), shape, len(shape), ctypes.byref(begin), ctypes.byref(end))
+                if ndim < 0:
+                    raise SafetensorsError(f"{path}: entry {i} of the header has a name or a shape too long to take")
+                key = name.value.decode("utf-8")
+                self.tensors[key] = TensorInfo(key, dtype.value.decode(), tuple(int(shape[k]) for k in range(ndim)), begin.value, end.value)
+        finally:
+            lib.mbl_close(handle)
+        self._fh = open(path, "rb")
+        self._map = mmap.mmap(self._fh.fileno(), 0, access=mmap.ACCESS_READ) if os.path.getsize(path) > 0 else None
 
     def names(self) -> List[str]:
         return list(self.tensors)
