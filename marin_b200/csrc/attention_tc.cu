@@ -121,7 +121,7 @@ __device__ __forceinline__ void umma_bf16_tmem_a(uint32_t tmem_d, uint32_t tmem_
         : "memory");
 }
 
-// 160 threads: warps 0..3 own the 128 query rows (softmax, output); warp 4 asks for keys and values and issues the MMAs.
+// 192 threads: warps 0..3 own the 128 query rows (softmax, output); warp 4 issues the MMAs; warp 5 asks for keys and values.
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
@@ -150,7 +150,7 @@ __device__ __forceinline__ void tmem_st32_bits(uint32_t taddr, const uint32_t* v
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
-__global__ void __launch_bounds__(160, 2) attn_prefill_tc_kernel(
+__global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
     bf16* __restrict__ out, const int* __restrict__ block_table, int max_pages, const int* __restrict__ cu_tokens,
     const int* __restrict__ seq_lens, int first_req, int K, int page_shift, float scale, int window, int* __restrict__ error_flag,
@@ -215,34 +215,70 @@ __global__ void __launch_bounds__(160, 2) attn_prefill_tc_kernel(
     const int rot = (int)(((unsigned)(h * gridDim.x + qt) * 37u) % (unsigned)nblk);
     auto block_of = [&](int i) { const int j = i + rot; return kb_first + (j >= nblk ? j - nblk : j); };
 
-    if (warp == 4) {
-        {
-            // ---- the issuer warp: lane 0 starts the MMAs and arms the barriers; lanes 0..3 each ask for one box of a
-            // block of K or V, so that one instruction starts four TMA copies ----
-            const int* table = block_table + (size_t)r * max_pages;
-            const int page_mask = (1 << page_shift) - 1;
+    if (warp == 5) {
+        // ---- the loader warp: asks for Q once, then for every block of K and of V as soon as its buffer is free.  Lanes
+        // 0..3 each ask for one box of a block, so that one instruction starts four TMA copies.  (Measured: one warp
+        // that both loads and issues the MMAs spends about 900 cycles on each of its four jobs per block, and that
+        // sum, not the tensor cores or the softmax, set the pace; two warps halve it.) ----
+        const int* table = block_table + (size_t)r * max_pages;
+        const int page_mask = (1 << page_shift) - 1;
+        // one block of keys, or of values: 16-key boxes, one per page piece and 64-column half
+        auto load_block = [&](const CUtensorMap* map, uint8_t* dst, uint64_t* bar, int kb) {
+            if (lane == 0) mbar_expect_tx(bar, TA_KV_BYTES);
+            __syncwarp();
+            const int g = lane * box_rows;                  // box_rows keys per box: 16, 32 or 64 (at most a page)
+            if (g < TA_BN) {
+                const int key = kb * TA_BN + g;
+                const int pg = (key >> page_shift) - page_first;
+                const int page_id = pg < TA_PAGE_CACHE ? s_pages[pg] : table[min(key >> page_shift, max_pages - 1)];
+                const int row = (int)((((size_t)page_id * K + kh) << page_shift) + (size_t)(key & page_mask));
+#pragma unroll
+                for (int hf = 0; hf < NH; ++hf) tma_load_2d(dst + hf * (TA_BN * 128) + g * 128, map, hf * 64, row, bar);
+            }
+            __syncwarp();
+        };
+        auto load_k = [&](int j) { load_block(&map_k, sKV + (size_t)(j & 1) * 2 * TA_KV_BYTES, &k_full[j & 1], block_of(j)); };
+        auto load_v = [&](int j) { load_block(&map_v, sKV + (size_t)(j & 1) * 2 * TA_KV_BYTES + TA_KV_BYTES, &v_full[j & 1], block_of(j)); };
+        if (lane == 0) {
+            mbar_expect_tx(q_full, TA_Q_BYTES);
+#pragma unroll
+            for (int hf = 0; hf < NH; ++hf) tma_load_2d(sQ + hf * (TA_BM * 128), &map_q, h * D + hf * 64, tok0 + qt * TA_BM, q_full);
+        }
+        load_k(0);
+        load_v(0);
+        // the K buffer of block j is free once S of block j - 2 is done, the V buffer once P V of block j - 2 is
+        int next_k = 1, next_v = 1;
+        bool ok = true;
+        unsigned idle = 0;
+        const long long start = clock64();
+        while (ok && (next_k < nblk || next_v < nblk)) {
+            bool progressed = false;
+            if (__shfl_sync(0xffffffffu, (int)(next_k < nblk && (next_k < 2 || mbar_test(&s_done[next_k & 1], ((next_k - 2) >> 1) & 1))), 0)) {
+                load_k(next_k);
+                ++next_k;
+                progressed = true;
+            }
+            if (__shfl_sync(0xffffffffu, (int)(next_v < nblk && (next_v < 2 || mbar_test(&v_free[next_v & 1], ((next_v - 2) >> 1) & 1))), 0)) {
+                load_v(next_v);
+                ++next_v;
+                progressed = true;
+            }
+            if (!progressed && (++idle & 63) == 0) {
+                if (*abort) ok = false;
+                else if (clock64() - start > 8 * TC_WAIT_LIMIT) { *abort = 1; atomicExch(error_flag, 28); ok = false; }
+                ok = __all_sync(0xffffffffu, ok);
+            }
+        }
+    } else if (warp == 4) {
+        // ---- the MMA warp: one lane issues S = Q K^T of the next block as soon as its keys have landed (and P V of two
+        // blocks ago has been issued: S(i) goes where P(i - 2) lies, and the MMAs run in the order they are issued),
+        // and O += P V of the oldest block whose P is in tensor memory and whose values have landed ----
+        if (lane == 0) {
             constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TA_BN >> 3) << 17) | ((uint32_t)(TA_BM >> 4) << 24);
             constexpr uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(TA_BM >> 4) << 24);
-            // one block of keys, or of values: 16-key boxes, one per page piece and 64-column half
-            auto load_block = [&](const CUtensorMap* map, uint8_t* dst, uint64_t* bar, int kb) {
-                if (lane == 0) mbar_expect_tx(bar, TA_KV_BYTES);
-                __syncwarp();
-                const int g = lane * box_rows;                  // box_rows keys per box: 16, 32 or 64 (at most a page)
-                if (g < TA_BN) {
-                    const int key = kb * TA_BN + g;
-                    const int pg = (key >> page_shift) - page_first;
-                    const int page_id = pg < TA_PAGE_CACHE ? s_pages[pg] : table[min(key >> page_shift, max_pages - 1)];
-                    const int row = (int)((((size_t)page_id * K + kh) << page_shift) + (size_t)(key & page_mask));
-#pragma unroll
-                    for (int hf = 0; hf < NH; ++hf) tma_load_2d(dst + hf * (TA_BN * 128) + g * 128, map, hf * 64, row, bar);
-                }
-                __syncwarp();
-            };
-            auto load_k = [&](int j) { load_block(&map_k, sKV + (size_t)(j & 1) * 2 * TA_KV_BYTES, &k_full[j & 1], block_of(j)); };
-            auto load_v = [&](int j) { load_block(&map_v, sKV + (size_t)(j & 1) * 2 * TA_KV_BYTES + TA_KV_BYTES, &v_full[j & 1], block_of(j)); };
+            const uint32_t sq = smem_u32(sQ);
             auto issue_s = [&](int i) {                     // S(i) = Q K(i)^T into S buffer i & 1
-                if (lane != 0) return;
-                const uint32_t sq = smem_u32(sQ), sk = smem_u32(sKV + (size_t)(i & 1) * 2 * TA_KV_BYTES);
+                const uint32_t sk = smem_u32(sKV + (size_t)(i & 1) * 2 * TA_KV_BYTES);
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
@@ -252,63 +288,35 @@ __global__ void __launch_bounds__(160, 2) attn_prefill_tc_kernel(
                 }
                 umma_commit(&s_done[i & 1]);
             };
-            if (lane == 0) {
-                mbar_expect_tx(q_full, TA_Q_BYTES);
-#pragma unroll
-                for (int hf = 0; hf < NH; ++hf) tma_load_2d(sQ + hf * (TA_BM * 128), &map_q, h * D + hf * 64, tok0 + qt * TA_BM, q_full);
-            }
-            load_k(0);
-            load_v(0);
-            bool ok = wait_or_abort(q_full, 0, abort, error_flag, 21) && wait_or_abort(&k_full[0], 0, abort, error_flag, 22);
-            ok = __all_sync(0xffffffffu, ok);
-            if (ok) issue_s(0);
-            // From here on the issuer does whichever of these is possible next, never blocking on one while another is
-            // ready: ask for the next block of K (its buffer is free once S of two blocks ago is done: keys run two
-            // blocks ahead), ask for the next block of V (free once P V of two blocks ago is done), start S of the next
-            // block (K landed, the rows done with that S buffer), add P V of the oldest block whose P is in shared memory.
-            int next_k = 1, next_v = 1, next_s = 1, next_pv = 0;
+            bool ok = wait_or_abort(q_full, 0, abort, error_flag, 21);
+            int next_s = 0, next_pv = 0;
             unsigned idle = 0;
             const long long start = clock64();
             while (ok && next_pv < nblk) {
                 bool progressed = false;
-                if (__shfl_sync(0xffffffffu, (int)(next_k < nblk && (next_k < 2 || mbar_test(&s_done[next_k & 1], ((next_k - 2) >> 1) & 1))), 0)) {
-                    load_k(next_k);
-                    ++next_k;
-                    progressed = true;
-                }
-                if (__shfl_sync(0xffffffffu, (int)(next_v < nblk && (next_v < 2 || mbar_test(&v_free[next_v & 1], ((next_v - 2) >> 1) & 1))), 0)) {
-                    load_v(next_v);
-                    ++next_v;
-                    progressed = true;
-                }
-                // S(i) goes where P(i - 2) lies: the MMAs run in the order they are issued, so it is enough that
-                // P(i - 2) V(i - 2) has been issued before
-                if (__shfl_sync(0xffffffffu, (int)(next_s < next_k && next_s < next_pv + 2 && mbar_test(&k_full[next_s & 1], (next_s >> 1) & 1)), 0)) {
+                if (next_s < nblk && next_s < next_pv + 2 && mbar_test(&k_full[next_s & 1], (next_s >> 1) & 1)) {
                     issue_s(next_s);
                     ++next_s;
                     progressed = true;
                 }
-                if (__shfl_sync(0xffffffffu, (int)(next_pv < next_v && mbar_test(&p_ready[next_pv & 1], (next_pv >> 1) & 1) && mbar_test(&v_full[next_pv & 1], (next_pv >> 1) & 1)), 0)) {
+                if (next_pv < next_s && mbar_test(&p_ready[next_pv & 1], (next_pv >> 1) & 1) && mbar_test(&v_full[next_pv & 1], (next_pv >> 1) & 1)) {
                     // O += P(i) V(i) in TMEM columns [128, 128 + D); any rescaling of O by the rows happened before they arrived
                     const int buf = next_pv & 1;
-                    if (lane == 0) {
-                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                        // P is the A operand straight from tensor memory: row = lane, two bf16 per 32-bit column
-                        const uint32_t tp = tmem_base + (uint32_t)(buf * TA_BN);
-                        const uint32_t sv = smem_u32(sKV + (size_t)buf * 2 * TA_KV_BYTES) + TA_KV_BYTES;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    // P is the A operand straight from tensor memory: row = lane, two bf16 per 32-bit column
+                    const uint32_t tp = tmem_base + (uint32_t)(buf * TA_BN);
+                    const uint32_t sv = smem_u32(sKV + (size_t)buf * 2 * TA_KV_BYTES) + TA_KV_BYTES;
 #pragma unroll
-                        for (int kk = 0; kk < TA_BN / 16; ++kk)
-                            umma_bf16_tmem_a(tmem_base + TA_O_COL, tp + (uint32_t)(kk * 8), umma_desc_mn(sv + kk * 2048, TA_BN * 128), idesc_pv,
-                                             (next_pv > 0 || kk > 0) ? 1u : 0u);
-                        umma_commit(&v_free[buf]);
-                    }
+                    for (int kk = 0; kk < TA_BN / 16; ++kk)
+                        umma_bf16_tmem_a(tmem_base + TA_O_COL, tp + (uint32_t)(kk * 8), umma_desc_mn(sv + kk * 2048, TA_BN * 128), idesc_pv,
+                                         (next_pv > 0 || kk > 0) ? 1u : 0u);
+                    umma_commit(&v_free[buf]);
                     ++next_pv;
                     progressed = true;
                 }
                 if (!progressed && (++idle & 63) == 0) {
                     if (*abort) ok = false;
                     else if (clock64() - start > 8 * TC_WAIT_LIMIT) { *abort = 1; atomicExch(error_flag, 29); ok = false; }
-                    ok = __all_sync(0xffffffffu, ok);
                 }
             }
         }
@@ -469,6 +477,6 @@ MB_API int mb_attn_prefill_tc(const void* q, const void* k_cache, const void* v_
     rc = map_2d(&mv, v_cache, cache_rows, D, box_rows);
     if (rc) return rc;
     dim3 grid((max_query_len + TA_BM - 1) / TA_BM, K * GROUP, requests);
-    return launch_kernel(attn_prefill_tc_kernel, grid, 160, TA_SMEM, s, 0, mq, mk, mv, (bf16*)out, block_table, max_pages, cu_tokens,
+    return launch_kernel(attn_prefill_tc_kernel, grid, 192, TA_SMEM, s, 0, mq, mk, mv, (bf16*)out, block_table, max_pages, cu_tokens,
                          seq_lens, first_req, K, page_shift, scale, window, error_flag, box_rows);
 }
