@@ -121,7 +121,7 @@ __device__ __forceinline__ void umma_bf16_tmem_a(uint32_t tmem_d, uint32_t tmem_
         : "memory");
 }
 
-// 192 threads: warps 0..3 own the 128 query rows (softmax, output); warp 4 issues the MMAs; warp 5 asks for keys and values.
+// 224 threads: warps 0..3 own the 128 query rows (softmax, output); warp 4 issues the MMAs; warp 5 asks for keys, warp 6 for values.
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
@@ -150,7 +150,7 @@ __device__ __forceinline__ void tmem_st32_bits(uint32_t taddr, const uint32_t* v
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
-__global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(
+__global__ void __launch_bounds__(224, 2) attn_prefill_tc_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
     bf16* __restrict__ out, const int* __restrict__ block_table, int max_pages, const int* __restrict__ cu_tokens,
     const int* __restrict__ seq_lens, int first_req, int K, int page_shift, float scale, int window, int* __restrict__ error_flag,
@@ -215,15 +215,20 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(
     const int rot = (int)(((unsigned)(h * gridDim.x + qt) * 37u) % (unsigned)nblk);
     auto block_of = [&](int i) { const int j = i + rot; return kb_first + (j >= nblk ? j - nblk : j); };
 
-    if (warp == 5) {
-        // ---- the loader warp: asks for Q once, then for every block of K and of V as soon as its buffer is free.  Lanes
-        // 0..3 each ask for one box of a block, so that one instruction starts four TMA copies.  (Measured: one warp
-        // that both loads and issues the MMAs spends about 900 cycles on each of its four jobs per block, and that
-        // sum, not the tensor cores or the softmax, set the pace; two warps halve it.) ----
+    if (warp >= 5) {
+        // ---- the loader warps: warp 5 asks for Q once and then for every block of K, warp 6 for every block of V, each
+        // as soon as the block's buffer is free.  Lanes 0..3 each ask for one box of a block, so that one instruction
+        // starts four TMA copies.  (Measured with cycle stamps: asking for a block takes a warp about 900 cycles, issuing
+        // a block's MMAs about as long; one warp doing all of it set the pace of the whole kernel.) ----
+        const bool keys = warp == 5;
         const int* table = block_table + (size_t)r * max_pages;
         const int page_mask = (1 << page_shift) - 1;
+        const CUtensorMap* map = keys ? &map_k : &map_v;
         // one block of keys, or of values: 16-key boxes, one per page piece and 64-column half
-        auto load_block = [&](const CUtensorMap* map, uint8_t* dst, uint64_t* bar, int kb) {
+        auto load_block = [&](int j) {
+            uint8_t* dst = sKV + (size_t)(j & 1) * 2 * TA_KV_BYTES + (keys ? 0 : TA_KV_BYTES);
+            uint64_t* bar = keys ? &k_full[j & 1] : &v_full[j & 1];
+            const int kb = block_of(j);
             if (lane == 0) mbar_expect_tx(bar, TA_KV_BYTES);
             __syncwarp();
             const int g = lane * box_rows;                  // box_rows keys per box: 16, 32 or 64 (at most a page)
@@ -237,33 +242,22 @@ __global__ void __launch_bounds__(192, 2) attn_prefill_tc_kernel(
             }
             __syncwarp();
         };
-        auto load_k = [&](int j) { load_block(&map_k, sKV + (size_t)(j & 1) * 2 * TA_KV_BYTES, &k_full[j & 1], block_of(j)); };
-        auto load_v = [&](int j) { load_block(&map_v, sKV + (size_t)(j & 1) * 2 * TA_KV_BYTES + TA_KV_BYTES, &v_full[j & 1], block_of(j)); };
-        if (lane == 0) {
+        if (keys && lane == 0) {
             mbar_expect_tx(q_full, TA_Q_BYTES);
 #pragma unroll
             for (int hf = 0; hf < NH; ++hf) tma_load_2d(sQ + hf * (TA_BM * 128), &map_q, h * D + hf * 64, tok0 + qt * TA_BM, q_full);
         }
-        load_k(0);
-        load_v(0);
+        load_block(0);
         // the K buffer of block j is free once S of block j - 2 is done, the V buffer once P V of block j - 2 is
-        int next_k = 1, next_v = 1;
+        uint64_t* freed = keys ? s_done : v_free;
         bool ok = true;
         unsigned idle = 0;
         const long long start = clock64();
-        while (ok && (next_k < nblk || next_v < nblk)) {
-            bool progressed = false;
-            if (__shfl_sync(0xffffffffu, (int)(next_k < nblk && (next_k < 2 || mbar_test(&s_done[next_k & 1], ((next_k - 2) >> 1) & 1))), 0)) {
-                load_k(next_k);
-                ++next_k;
-                progressed = true;
-            }
-            if (__shfl_sync(0xffffffffu, (int)(next_v < nblk && (next_v < 2 || mbar_test(&v_free[next_v & 1], ((next_v - 2) >> 1) & 1))), 0)) {
-                load_v(next_v);
-                ++next_v;
-                progressed = true;
-            }
-            if (!progressed && (++idle & 63) == 0) {
+        for (int next = 1; ok && next < nblk;) {
+            if (__shfl_sync(0xffffffffu, (int)(next < 2 || mbar_test(&freed[next & 1], ((next - 2) >> 1) & 1)), 0)) {
+                load_block(next);
+                ++next;
+            } else if ((++idle & 63) == 0) {
                 if (*abort) ok = false;
                 else if (clock64() - start > 8 * TC_WAIT_LIMIT) { *abort = 1; atomicExch(error_flag, 28); ok = false; }
                 ok = __all_sync(0xffffffffu, ok);
@@ -477,6 +471,6 @@ MB_API int mb_attn_prefill_tc(const void* q, const void* k_cache, const void* v_
     rc = map_2d(&mv, v_cache, cache_rows, D, box_rows);
     if (rc) return rc;
     dim3 grid((max_query_len + TA_BM - 1) / TA_BM, K * GROUP, requests);
-    return launch_kernel(attn_prefill_tc_kernel, grid, 192, TA_SMEM, s, 0, mq, mk, mv, (bf16*)out, block_table, max_pages, cu_tokens,
+    return launch_kernel(attn_prefill_tc_kernel, grid, 224, TA_SMEM, s, 0, mq, mk, mv, (bf16*)out, block_table, max_pages, cu_tokens,
                          seq_lens, first_req, K, page_shift, scale, window, error_flag, box_rows);
 }
