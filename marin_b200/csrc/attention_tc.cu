@@ -224,39 +224,44 @@ __global__ void __launch_bounds__(224, 2) attn_prefill_tc_kernel(
         const int* table = block_table + (size_t)r * max_pages;
         const int page_mask = (1 << page_shift) - 1;
         const CUtensorMap* map = keys ? &map_k : &map_v;
-        // one block of keys, or of values: 16-key boxes, one per page piece and 64-column half
-        auto load_block = [&](int j) {
+        // One block of keys, or of values: 16-key boxes, one per page piece and 64-column half.  Where a block's boxes
+        // lie in the cache is worked out one block ahead (row_of), while the warp waits for the buffer anyway: once
+        // the buffer is free only the copies themselves remain to be started.
+        const int g = lane * box_rows;                      // box_rows keys per box: 16, 32 or 64 (at most a page)
+        auto row_of = [&](int j) {
+            if (g >= TA_BN || j >= nblk) return 0;
+            const int key = block_of(j) * TA_BN + g;
+            const int pg = (key >> page_shift) - page_first;
+            const int page_id = pg < TA_PAGE_CACHE ? s_pages[pg] : table[min(key >> page_shift, max_pages - 1)];
+            return (int)((((size_t)page_id * K + kh) << page_shift) + (size_t)(key & page_mask));
+        };
+        auto load_block = [&](int j, int row) {
             uint8_t* dst = sKV + (size_t)(j & 1) * 2 * TA_KV_BYTES + (keys ? 0 : TA_KV_BYTES);
             uint64_t* bar = keys ? &k_full[j & 1] : &v_full[j & 1];
-            const int kb = block_of(j);
             if (lane == 0) mbar_expect_tx(bar, TA_KV_BYTES);
             __syncwarp();
-            const int g = lane * box_rows;                  // box_rows keys per box: 16, 32 or 64 (at most a page)
             if (g < TA_BN) {
-                const int key = kb * TA_BN + g;
-                const int pg = (key >> page_shift) - page_first;
-                const int page_id = pg < TA_PAGE_CACHE ? s_pages[pg] : table[min(key >> page_shift, max_pages - 1)];
-                const int row = (int)((((size_t)page_id * K + kh) << page_shift) + (size_t)(key & page_mask));
 #pragma unroll
                 for (int hf = 0; hf < NH; ++hf) tma_load_2d(dst + hf * (TA_BN * 128) + g * 128, map, hf * 64, row, bar);
             }
-            __syncwarp();
         };
         if (keys && lane == 0) {
             mbar_expect_tx(q_full, TA_Q_BYTES);
 #pragma unroll
             for (int hf = 0; hf < NH; ++hf) tma_load_2d(sQ + hf * (TA_BM * 128), &map_q, h * D + hf * 64, tok0 + qt * TA_BM, q_full);
         }
-        load_block(0);
+        load_block(0, row_of(0));
         // the K buffer of block j is free once S of block j - 2 is done, the V buffer once P V of block j - 2 is
         uint64_t* freed = keys ? s_done : v_free;
         bool ok = true;
         unsigned idle = 0;
         const long long start = clock64();
+        int row_next = row_of(1);
         for (int next = 1; ok && next < nblk;) {
             if (__shfl_sync(0xffffffffu, (int)(next < 2 || mbar_test(&freed[next & 1], ((next - 2) >> 1) & 1)), 0)) {
-                load_block(next);
+                load_block(next, row_next);
                 ++next;
+                row_next = row_of(next);
             } else if ((++idle & 63) == 0) {
                 if (*abort) ok = false;
                 else if (clock64() - start > 8 * TC_WAIT_LIMIT) { *abort = 1; atomicExch(error_flag, 28); ok = false; }
@@ -270,15 +275,29 @@ __global__ void __launch_bounds__(224, 2) attn_prefill_tc_kernel(
         if (lane == 0) {
             constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TA_BN >> 3) << 17) | ((uint32_t)(TA_BM >> 4) << 24);
             constexpr uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(TA_BM >> 4) << 24);
+            // the descriptors of every MMA of a block, for either buffer, worked out once
             const uint32_t sq = smem_u32(sQ);
-            auto issue_s = [&](int i) {                     // S(i) = Q K(i)^T into S buffer i & 1
-                const uint32_t sk = smem_u32(sKV + (size_t)(i & 1) * 2 * TA_KV_BYTES);
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            uint64_t qdesc[D / 16], kdesc[2][D / 16], vdesc[2][TA_BN / 16];
 #pragma unroll
-                for (int kk = 0; kk < D / 16; ++kk) {
-                    const uint64_t adesc = umma_desc(sq + (kk / 4) * (TA_BM * 128)) + 2 * (kk % 4);
-                    const uint64_t bdesc = umma_desc(sk + (kk / 4) * (TA_BN * 128)) + 2 * (kk % 4);
-                    umma_bf16(tmem_base + (uint32_t)((i & 1) * TA_BN), adesc, bdesc, idesc_s, kk > 0 ? 1u : 0u);
+            for (int kk = 0; kk < D / 16; ++kk) {
+                qdesc[kk] = umma_desc(sq + (kk / 4) * (TA_BM * 128)) + 2 * (kk % 4);
+#pragma unroll
+                for (int b = 0; b < 2; ++b)
+                    kdesc[b][kk] = umma_desc(smem_u32(sKV + (size_t)b * 2 * TA_KV_BYTES) + (kk / 4) * (TA_BN * 128)) + 2 * (kk % 4);
+            }
+#pragma unroll
+            for (int kk = 0; kk < TA_BN / 16; ++kk)
+#pragma unroll
+                for (int b = 0; b < 2; ++b)
+                    vdesc[b][kk] = umma_desc_mn(smem_u32(sKV + (size_t)b * 2 * TA_KV_BYTES) + TA_KV_BYTES + kk * 2048, TA_BN * 128);
+            auto issue_s = [&](int i) {                     // S(i) = Q K(i)^T into S buffer i & 1
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                if (i & 1) {
+#pragma unroll
+                    for (int kk = 0; kk < D / 16; ++kk) umma_bf16(tmem_base + (uint32_t)TA_BN, qdesc[kk], kdesc[1][kk], idesc_s, kk > 0 ? 1u : 0u);
+                } else {
+#pragma unroll
+                    for (int kk = 0; kk < D / 16; ++kk) umma_bf16(tmem_base, qdesc[kk], kdesc[0][kk], idesc_s, kk > 0 ? 1u : 0u);
                 }
                 umma_commit(&s_done[i & 1]);
             };
@@ -299,11 +318,15 @@ __global__ void __launch_bounds__(224, 2) attn_prefill_tc_kernel(
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     // P is the A operand straight from tensor memory: row = lane, two bf16 per 32-bit column
                     const uint32_t tp = tmem_base + (uint32_t)(buf * TA_BN);
-                    const uint32_t sv = smem_u32(sKV + (size_t)buf * 2 * TA_KV_BYTES) + TA_KV_BYTES;
+                    if (buf) {
 #pragma unroll
-                    for (int kk = 0; kk < TA_BN / 16; ++kk)
-                        umma_bf16_tmem_a(tmem_base + TA_O_COL, tp + (uint32_t)(kk * 8), umma_desc_mn(sv + kk * 2048, TA_BN * 128), idesc_pv,
-                                         (next_pv > 0 || kk > 0) ? 1u : 0u);
+                        for (int kk = 0; kk < TA_BN / 16; ++kk)
+                            umma_bf16_tmem_a(tmem_base + TA_O_COL, tp + (uint32_t)(kk * 8), vdesc[1][kk], idesc_pv, (next_pv > 0 || kk > 0) ? 1u : 0u);
+                    } else {
+#pragma unroll
+                        for (int kk = 0; kk < TA_BN / 16; ++kk)
+                            umma_bf16_tmem_a(tmem_base + TA_O_COL, tp + (uint32_t)(kk * 8), vdesc[0][kk], idesc_pv, (next_pv > 0 || kk > 0) ? 1u : 0u);
+                    }
                     umma_commit(&v_free[buf]);
                     ++next_pv;
                     progressed = true;
