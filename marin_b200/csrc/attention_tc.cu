@@ -13,11 +13,15 @@
 //                  8 (a factor 256, harmless in float32): then the row's O is read, rescaled and written back
 //                  (tcgen05.ld/st); otherwise O is never touched until the end.
 // K and V blocks arrive by TMA straight from the paged cache (one 16-key box per page piece and 64-column half) into
-// two buffers each; keys run two blocks ahead of the rows, values one.  S (and with it P) has two buffers as well; the
-// MMAs run in the order they are issued, so S of block i + 2 may follow P V of block i without a barrier.  Every
-// barrier used once per block exists per buffer parity, since the rows may run a block ahead of the issuer.
-// Two CTAs fit an SM: one's softmax overlaps the
-// other's MMAs.  Needs pages of at least 16 positions.  Waits are bounded and record a code in *error_flag.
+// two buffers each.  S (and with it P) has two buffers as well; the MMAs run in the order they are issued, so S of
+// block i + 2 may follow P V of block i without a barrier.  Every barrier used once per block exists per buffer parity,
+// since the rows may run a block ahead of the MMA warp.
+// Seven warps: four own the 128 query rows (softmax, output), one issues the MMAs, one asks for keys and one for values.
+// (A cycle-stamped timeline of one CTA showed that asking for a block of K or V, or issuing a block's MMAs, takes a
+// warp 700 to 900 cycles each; one warp doing all four jobs set the pace of the kernel at 3,400 cycles a block, three
+// warps bring it to 1,800, where the latency of the K copy plus S, and the rows' softmax, are about level.)
+// Two CTAs fit an SM: one's softmax overlaps the other's MMAs.  Needs pages of at least 16 positions.  Waits are
+// bounded and record a code in *error_flag.
 // The mma.sync kernel in attention_fast.cu is the fallback and the plain twin (the reference's counterpart:
 // crates/cuda/src/attention_mma.cu:43-180).
 #include "tc_common.cuh"
