@@ -169,11 +169,16 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
     const int kb_begin = blockIdx.z * kb_per_split;
     const int kb_end = min(total_kb, kb_begin + kb_per_split);
     const int nkb = kb_end - kb_begin;
-    constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+    // Starting an MMA costs the issuing thread on the order of a hundred cycles, whatever its size, and with few tokens
+    // that, not the data, sets the pace once the weights have landed: up to 64 tokens two threads issue, even k-blocks
+    // into one accumulator and odd ones into a second, and the epilogue adds the two.
+    constexpr bool DUAL = BN <= 64;
+    constexpr int NSC = DUAL ? 32 : 64;                               // threads that work out the per-token factors
+    constexpr uint32_t TMEM_COLS = (DUAL ? 2 * BN : BN) < 32 ? 32 : (DUAL ? 2 * BN : BN);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        mbar_init(accum, 1);
+        mbar_init(accum, DUAL ? 2 : 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
@@ -208,11 +213,13 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
             tma_load_2d(a, &map_w, k, n0, &full[s]);
             tma_load_2d(a + L::A_BYTES, &map_x, k, t0, &full[s]);
         }
-    } else if (warp == 1 && lane == 0) {
-        // ---- MMA issuer ----
+    } else if ((warp == 1 || (DUAL && warp == 3)) && lane == 0) {
+        // ---- MMA issuers: thread `which` takes the k-blocks i = which, which + step, ... into accumulator `which` ----
         constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+        const int which = warp == 1 ? 0 : 1, step = DUAL ? 2 : 1;
+        const uint32_t tmem_d = tmem_base + (uint32_t)(which * BN);
         bool ok = true;
-        for (int i = 0; i < nkb && ok; ++i) {
+        for (int i = which; i < nkb && ok; i += step) {
             const int s = i % STAGES;
             const uint32_t phase = (i / STAGES) & 1;
             if (!mbar_wait(&full[s], phase)) { atomicExch(error_flag, 2); ok = false; break; }
@@ -221,23 +228,23 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
             const uint64_t adesc = umma_desc(a), bdesc = umma_desc(a + L::A_BYTES);
 #pragma unroll
             for (int kk = 0; kk < TC_BK / 16; ++kk)
-                umma_bf16(tmem_base, adesc + 2 * kk, bdesc + 2 * kk, idesc, (i > 0 || kk > 0) ? 1u : 0u);
-            umma_commit(&empty[s]);
+                umma_bf16(tmem_d, adesc + 2 * kk, bdesc + 2 * kk, idesc, (i > which || kk > 0) ? 1u : 0u);
+            if (i + STAGES < nkb) umma_commit(&empty[s]);             // only a stage that is filled again needs to be given back
         }
         umma_commit(accum);
-    } else if (warp >= 2 && scale.sumsq != nullptr) {
-        // ---- the per-token factors of the norm ahead of this product: warps 2 and 3 add the slots, in slot order ----
+    } else if ((DUAL ? warp == 2 : warp >= 2) && scale.sumsq != nullptr) {
+        // ---- the per-token factors of the norm ahead of this product: warp 2 (and 3, with one issuer) adds the slots, in slot order ----
         pdl_wait();
         // warps 2 and 3: `tpt` threads per token (a power of two, at most 32), each adds its share of the slots in
         // slot order, up to 24 loads in flight at a time; then the shares are added in a fixed tree
         const int here = min(BN, T - t0);
         int tpt = 32;
-        while (tpt * here > 64 && tpt > 1) tpt >>= 1;
+        while (tpt * here > NSC && tpt > 1) tpt >>= 1;
         const int local = threadIdx.x - 64, part = local % tpt;
         const int per = (scale.slots + tpt - 1) / tpt;
-        const int trips = (BN * tpt + 63) / 64;                       // the same for every thread: shuffles below
+        const int trips = (BN * tpt + NSC - 1) / NSC;                 // the same for every thread: shuffles below
         for (int trip = 0; trip < trips; ++trip) {
-            const int tt = trip * (64 / tpt) + local / tpt;
+            const int tt = trip * (NSC / tpt) + local / tpt;
             const int t = t0 + tt;
             float sum = 0.0f;
             if (tt < BN && t < T) {
@@ -277,7 +284,15 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 16) {
             float v[16];
-            if (have) tmem_ld16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, v);
+            if (have) {
+                tmem_ld16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, v);
+                if (DUAL && nkb >= 2) {                               // the odd k-blocks' accumulator
+                    float v2[16];
+                    tmem_ld16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(BN + c0), v2);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) v[j] += v2[j];
+                }
+            }
             else {
 #pragma unroll
                 for (int j = 0; j < 16; ++j) v[j] = 0.0f;
@@ -424,7 +439,15 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
 #pragma unroll 1
     for (int c0 = 0; c0 < BN; c0 += 16) {
         float v[16];
-        if (have) tmem_ld16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, v);
+        if (have) {
+            tmem_ld16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, v);
+            if (DUAL && nkb >= 2) {                                   // the odd k-blocks' accumulator
+                float v2[16];
+                tmem_ld16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(BN + c0), v2);
+#pragma unroll
+                for (int j = 0; j < 16; ++j) v[j] += v2[j];
+            }
+        }
         else {
 #pragma unroll
             for (int j = 0; j < 16; ++j) v[j] = 0.0f;
