@@ -403,8 +403,8 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_split_kernel(
             }
             out[((size_t)r * H + kh * GROUP) * D + idx] = __float2bfloat16_rn(a / ll);
         }
-        // nobody leaves while a peer may still read its partial result
-        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+        // nobody leaves while a peer may still read its partial result (nothing is published: a relaxed arrival)
+        asm volatile("barrier.cluster.arrive.relaxed.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
         return;
     }
     // The CTA that finishes last among the chunks of this (request, kv head) combines them:

@@ -300,6 +300,8 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
 #pragma unroll
             for (int j = 0; j < 16; ++j) red[(c0 + j) * TC_BM + warp * 32 + lane] = v[j];
         }
+        // this CTA's tile is in place: say so to the cluster now, and wait for the peers only when their tiles are needed
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
         const int rows_per = TC_BM / splits;                         // splits is 2, 4 or 8
         const int row_first = blockIdx.z * rows_per;
         const int t_count = min(BN, T - t0);
@@ -311,7 +313,7 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
             const float wi = hw != nullptr ? hw[i] : 1.0f;
             const bool rotate = (is_q || is_k) && heads.inv_freq != nullptr;
             const float freq = rotate ? heads.inv_freq[i & 63] : 0.0f;
-            asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+            asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
             const uint32_t red_addr = smem_u32(red);
             for (int tt = blockIdx.z; tt < t_count; tt += splits) {
                 const int t = t0 + tt;
@@ -354,7 +356,7 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
                 }
                 __syncthreads();                                      // s_part and s_head are used again
             }
-            asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+            asm volatile("barrier.cluster.arrive.relaxed.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
         } else {
         // Trips of 128 (token, row) pairs, four at a time: all loads of the four (the old values from global memory,
         // then the slices from the peers' shared memory) are asked for before any is used, so their latencies overlap.
@@ -371,7 +373,7 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
             old[u] = (acc_mode && valid) ? ((const float*)out)[(size_t)(t0 + tt) * N + n0 + row] : 0.0f;
             gain[u] = (norm.weight != nullptr && valid) ? norm.weight[n0 + row] : 0.0f;
         }
-        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
         const uint32_t red_addr = smem_u32(red);
         const int group = rows_per < 32 ? rows_per : 32;             // rows whose squares are added into one slot
         const int slots_per_tile = splits < 4 ? 4 : splits;
@@ -432,8 +434,9 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
                 }
             }
         }
-        // nobody leaves while a peer may still read its tile
-        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+        // nobody leaves while a peer may still read its tile (nothing is published here: a relaxed arrival does not wait
+        // for this CTA's own stores to drain)
+        asm volatile("barrier.cluster.arrive.relaxed.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
         }
     } else {
 #pragma unroll 1
