@@ -135,7 +135,9 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_split_kernel(
     const int* __restrict__ block_table, int max_pages, const int* __restrict__ seq_lens, int K, int page_shift,
     float scale, int window, float* __restrict__ part_acc, float* __restrict__ part_ml, int max_chunks, int split_keys,
     int* __restrict__ counters, bf16* __restrict__ out, int* __restrict__ error_flag, int cluster_merge) {
-    PDL_ENTER();
+    // The dependency wait comes later: sequence lengths and block tables were copied before the step began, and every
+    // key and value but the newest token's was written by earlier steps, so most of the cache may be asked for while
+    // the kernels ahead are still running.
     extern __shared__ __align__(16) uint8_t dec_smem_raw[];
     constexpr int STAGE_BYTES = TMA ? DEC_TMA_STAGE_BYTES : DEC_STAGE_BYTES;
     constexpr int WARP_BYTES = DEC_STAGES * STAGE_BYTES;
@@ -151,7 +153,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_split_kernel(
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
     const int c_begin = chunk * split_keys, c_end = min(len, c_begin + split_keys);
     const bool has_work = c_begin < len && c_end > lo;
-    if (!has_work && !cluster_merge) return;
+    if (!has_work && !cluster_merge) { PDL_ENTER(); return; }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int* table = block_table + (size_t)r * max_pages;
     uint8_t* ring = dec_smem + (size_t)warp * WARP_BYTES;
@@ -227,8 +229,15 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_split_kernel(
         }
         cp_async_commit();
     };
+    // only the stage that holds the newest position (written by the kernel just ahead) has to wait for that kernel
+    bool waited = false;
 #pragma unroll
-    for (int i = 0; i < DEC_STAGES; ++i) issue(i);
+    for (int i = 0; i < DEC_STAGES; ++i) {
+        const int key_base = first + i * DEC_STAGE_KEYS;
+        if (!waited && i < n_it && key_base + DEC_STAGE_KEYS > pos) { PDL_ENTER(); waited = true; }
+        issue(i);
+    }
+    if (!waited) PDL_ENTER();
 
     // the query tile: GROUP heads, the rest of the 16 rows zero
     for (int idx = threadIdx.x; idx < 16 * PIECES; idx += DEC_WARPS * 32) {
@@ -375,9 +384,12 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_split_kernel(
             if (dd == 0) { part_ml[at * 2] = mm; part_ml[at * 2 + 1] = ll; }
         }
     }
-    } else if (threadIdx.x < 8) {
-        c_m[threadIdx.x] = -INFINITY;                  // a chunk outside the sequence (or the window) adds nothing
-        c_l[threadIdx.x] = 0.0f;
+    } else {
+        PDL_ENTER();                                   // it still writes its share of the outputs below
+        if (threadIdx.x < 8) {
+            c_m[threadIdx.x] = -INFINITY;              // a chunk outside the sequence (or the window) adds nothing
+            c_l[threadIdx.x] = 0.0f;
+        }
     }
     if (cluster_merge) {
         // The chunks of this (request, kv head) are the CTAs of one cluster: after a cluster barrier every CTA combines
