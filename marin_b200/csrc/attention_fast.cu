@@ -239,19 +239,20 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_split_kernel(
     }
     if (!waited) PDL_ENTER();
 
-    // the query tile: GROUP heads, the rest of the 16 rows zero
-    for (int idx = threadIdx.x; idx < 16 * PIECES; idx += DEC_WARPS * 32) {
-        const int row = idx / PIECES, piece = idx % PIECES;
-        uint4 val = make_uint4(0, 0, 0, 0);
-        if (row < GROUP) val = *reinterpret_cast<const uint4*>(q + ((size_t)r * H + kh * GROUP + row) * D + piece * 8);
-        *reinterpret_cast<uint4*>(sQ + row * LDP + piece * 8) = val;
-    }
-    __syncthreads();
+    // The query tile, GROUP heads in rows 0..GROUP-1 of 16 (the rest zero), straight into the MMA's A fragments: lane l
+    // holds row l / 4, columns 2 (l % 4) + {0, 1} and + 8 of every 16-column step; rows 8..15 (a1, a3) are zero since at
+    // most 8 heads share a kv head.  Every warp loads its own copy: no shared memory, no block-wide barrier.
     uint32_t qa[D / 16][4];
+    {
+        const int qrow = lane >> 2;
+        const bf16* qsrc = q + ((size_t)r * H + kh * GROUP + (qrow < GROUP ? qrow : 0)) * D + 2 * (lane & 3);
 #pragma unroll
-    for (int kk = 0; kk < D / 16; ++kk) {
-        const int row = (lane & 7) + ((lane >> 3) & 1) * 8;
-        ldsm_x4((uint32_t)__cvta_generic_to_shared(sQ + row * LDP + kk * 16 + (lane >> 4) * 8), qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3]);
+        for (int kk = 0; kk < D / 16; ++kk) {
+            qa[kk][0] = qrow < GROUP ? *reinterpret_cast<const uint32_t*>(qsrc + kk * 16) : 0u;
+            qa[kk][2] = qrow < GROUP ? *reinterpret_cast<const uint32_t*>(qsrc + kk * 16 + 8) : 0u;
+            qa[kk][1] = 0u;
+            qa[kk][3] = 0u;
+        }
     }
 
     const float sl2 = scale * 1.4426950408889634f;
@@ -400,20 +401,33 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_split_kernel(
         const int per = (GROUP * D + ranks - 1) / ranks;
         const int i_end = min(GROUP * D, (chunk + 1) * per);
         const uint32_t a_acc = smem_u32(c_acc), a_m = smem_u32(c_m), a_l = smem_u32(c_l);
+        // the chunks' weights 2^(m_c - M) and the inverse of the total sum, once per head (ranks <= 8), then every
+        // output is one weighted sum over the chunks
+        __shared__ float wgt[8 * 8], inv_total[8];                   // [head][chunk], [head]
+        if (threadIdx.x < GROUP) {
+            const int g = threadIdx.x;
+            float mc[8], mm = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) { mc[c] = c < ranks ? ld_cluster_f32(a_m + g * 4, c) : -INFINITY; mm = fmaxf(mm, mc[c]); }
+            float ll = 0.0f;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                const float f = mc[c] == -INFINITY ? 0.0f : exp2f(mc[c] - mm);
+                wgt[g * 8 + c] = f;
+                if (c < ranks && f != 0.0f) ll = fmaf(ld_cluster_f32(a_l + g * 4, c), f, ll);
+            }
+            inv_total[g] = 1.0f / ll;
+        }
+        __syncthreads();
         for (int idx = chunk * per + threadIdx.x; idx < i_end; idx += DEC_WARPS * 32) {
             const int g = idx / D;
-            float mm = -INFINITY;
-            for (int c = 0; c < ranks; ++c) mm = fmaxf(mm, ld_cluster_f32(a_m + g * 4, c));
-            float a = 0.0f, ll = 0.0f;
-            for (int c = 0; c < ranks; ++c) {
-                const float mc = ld_cluster_f32(a_m + g * 4, c);
-                if (mc != -INFINITY) {
-                    const float f = exp2f(mc - mm);
-                    a = fmaf(ld_cluster_f32(a_acc + idx * 4, c), f, a);
-                    ll = fmaf(ld_cluster_f32(a_l + g * 4, c), f, ll);
-                }
-            }
-            out[((size_t)r * H + kh * GROUP) * D + idx] = __float2bfloat16_rn(a / ll);
+            float part[8];
+#pragma unroll
+            for (int c = 0; c < 8; ++c) part[c] = (c < ranks && wgt[g * 8 + c] != 0.0f) ? ld_cluster_f32(a_acc + idx * 4, c) : 0.0f;
+            float a = 0.0f;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) a = fmaf(part[c], wgt[g * 8 + c], a);
+            out[((size_t)r * H + kh * GROUP) * D + idx] = __float2bfloat16_rn(a * inv_total[g]);
         }
         // nobody leaves while a peer may still read its partial result (nothing is published: a relaxed arrival)
         asm volatile("barrier.cluster.arrive.relaxed.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
