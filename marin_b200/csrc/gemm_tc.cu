@@ -526,12 +526,55 @@ __device__ __forceinline__ int tile_rows(int tile, int tiles_n, int tiles_t) { r
 __device__ __forceinline__ int tile_tokens(int tile, int tiles_n, int tiles_t) { return tile / tiles_n; }
 #endif
 
-template <int BN, int STAGES>
+// What a CTA of the persistent kernel works on, piece by piece.  Tile by tile (units_per_group = 0): tiles blockIdx.x,
+// blockIdx.x + gridDim.x, ... each over all of k.  Stream-K (units_per_group > 0): the CTAs form groups of tiles_t,
+// one CTA for each token tile; the weight-row tiles laid end to end are tiles_n * nkb k-blocks, and group g takes
+// k-blocks [g * units_per_group, (g + 1) * units_per_group) of them, whatever row tiles they fall into.  Every SM
+// gets the same amount of work however many tiles there are, and the CTAs of a group walk the same weight k-blocks
+// at the same time (one copy from HBM, the others from L2), which dealing k-blocks to single CTAs would lose.  With
+// units_per_group >= nkb (the launcher sees to it) a tile is shared by two CTAs at most: CTA c + tiles_t starts with
+// the tile's last k-blocks (its first piece), CTA c ends with the tile's first k-blocks (its last piece).
+struct TcStreamK {
+    float* partials;        // [ctas][BN][128] float32: the piece a CTA began with, if it began inside a tile
+    int* flags;             // [ctas][8]: one per epilogue warp; 1 while that warp's part of the piece is there
+    int units_per_group;
+};
+
+struct TcWalk {
+    int nkb, limit, step, at, token_tile, tiles_t;
+    bool streamk;
+    __device__ TcWalk(const TcStreamK& sk, bool streamk_, int tiles_n, int tiles_t_, int nkb_) : nkb(nkb_), tiles_t(tiles_t_), streamk(streamk_) {
+        if (streamk) {
+            const int group = blockIdx.x / tiles_t_;
+            token_tile = blockIdx.x - group * tiles_t_;
+            const long long total = (long long)tiles_n * nkb_;
+            const long long from = (long long)group * sk.units_per_group, to = from + sk.units_per_group;
+            at = (int)(from < total ? from : total);
+            limit = (int)(to < total ? to : total);
+            step = 0;
+        } else {
+            at = blockIdx.x; limit = tiles_n * tiles_t_; step = gridDim.x; token_tile = 0;
+        }
+    }
+    // the next piece: k-blocks [kb0, kb1) of `tile` (numbered with the token tiles fastest)
+    __device__ bool next(int& tile, int& kb0, int& kb1) {
+        if (at >= limit) return false;
+        if (!streamk) { tile = at; kb0 = 0; kb1 = nkb; at += step; return true; }
+        const int row = at / nkb;
+        tile = row * tiles_t + token_tile;
+        kb0 = at - row * nkb;
+        kb1 = kb0 + (limit - at) < nkb ? kb0 + (limit - at) : nkb;
+        at += kb1 - kb0;
+        return true;
+    }
+};
+
+template <int BN, int STAGES, bool SK>
 __global__ void __launch_bounds__(320) gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                  const __grid_constant__ CUtensorMap map_x,
                                                                  void* __restrict__ out, int mode, int T, int N, int K,
                                                                  int* __restrict__ error_flag, const TcNormOut norm,
-                                                                 const TcRowScale scale) {
+                                                                 const TcRowScale scale, const TcStreamK sk) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ float s_pscale[2][BN];          // the per-token factors of a coupled norm, for the tile in each accumulator
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -567,9 +610,10 @@ __global__ void __launch_bounds__(320) gemm_tc_persistent_kernel(const __grid_co
     if (warp == 0 && lane == 0) {
         int it = 0;                                                   // k-blocks issued so far, over all tiles
         bool ok = true;
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        TcWalk walk(sk, SK, tiles_n, tiles_t, nkb);
+        for (int tile, kb0, kb1; ok && walk.next(tile, kb0, kb1);) {
             const int n0 = tile_rows(tile, tiles_n, tiles_t) * TC_BM, t0 = tile_tokens(tile, tiles_n, tiles_t) * BN;
-            for (int kb = 0; kb < nkb; ++kb, ++it) {
+            for (int kb = kb0; kb < kb1; ++kb, ++it) {
                 const int s = it % STAGES;
                 const uint32_t phase = (it / STAGES) & 1;
                 if (!mbar_wait(&empty[s], phase ^ 1)) { atomicExch(error_flag, 11); ok = false; break; }
@@ -583,13 +627,14 @@ __global__ void __launch_bounds__(320) gemm_tc_persistent_kernel(const __grid_co
         constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
         int it = 0, local = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+        TcWalk walk(sk, SK, tiles_n, tiles_t, nkb);
+        for (int tile, kb0, kb1; ok && walk.next(tile, kb0, kb1); ++local) {
             const int buf = local & 1;
             const uint32_t acc_phase = (local >> 1) & 1;
             if (!mbar_wait(&acc_empty[buf], acc_phase ^ 1)) { atomicExch(error_flag, 12); ok = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
-            for (int kb = 0; kb < nkb; ++kb, ++it) {
+            for (int kb = kb0; kb < kb1; ++kb, ++it) {
                 const int s = it % STAGES;
                 const uint32_t phase = (it / STAGES) & 1;
                 if (!mbar_wait(&full[s], phase)) { atomicExch(error_flag, 13); ok = false; break; }
@@ -598,7 +643,7 @@ __global__ void __launch_bounds__(320) gemm_tc_persistent_kernel(const __grid_co
                 const uint64_t adesc = umma_desc(a), bdesc = umma_desc(a + L::A_BYTES);
 #pragma unroll
                 for (int kk = 0; kk < TC_BK / 16; ++kk)
-                    umma_bf16(tmem_d, adesc + 2 * kk, bdesc + 2 * kk, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+                    umma_bf16(tmem_d, adesc + 2 * kk, bdesc + 2 * kk, idesc, (kb > kb0 || kk > 0) ? 1u : 0u);
                 umma_commit(&empty[s]);
             }
             umma_commit(&acc_full[buf]);
@@ -609,7 +654,10 @@ __global__ void __launch_bounds__(320) gemm_tc_persistent_kernel(const __grid_co
         constexpr int HALF_COLS = ((BN / 16 + 1) / 2) * 16;
         int local = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++local) {
+        TcWalk walk(sk, SK, tiles_n, tiles_t, nkb);
+        for (int tile, kb0, kb1; walk.next(tile, kb0, kb1); ++local) {
+            const bool is_tail = SK && kb0 > 0;    // the tile's last k-blocks: parked for the CTA that has its first ones
+            const bool is_head = SK && kb1 < nkb;  // the tile's first k-blocks: the next CTA's parked piece is added
             const int tile_row = tile_rows(tile, tiles_n, tiles_t);
             const int n0 = tile_row * TC_BM, t0 = tile_tokens(tile, tiles_n, tiles_t) * BN;
             const int buf = local & 1;
@@ -633,16 +681,10 @@ __global__ void __launch_bounds__(320) gemm_tc_persistent_kernel(const __grid_co
                 }
                 asm volatile("bar.sync 1, 256;" ::: "memory");
             }
-            // a warp whose wait gave up keeps walking the tiles (the barrier above counts on it) but touches nothing
-            if (ok && !mbar_wait(&acc_full[buf], acc_phase)) { if (lane == 0) atomicExch(error_flag, 14); ok = false; }
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) continue;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int c_begin = col_half * HALF_COLS, c_end = col_half == 0 ? HALF_COLS : BN;
             const int n = n0 + quarter * 32 + lane;
-#pragma unroll 1
-            for (int c0 = col_half * HALF_COLS; c0 < (col_half == 0 ? HALF_COLS : BN); c0 += 16) {
-                float v[16];
-                tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c0), v);
+            // what happens to 16 finished columns of this thread's row
+            auto finish_chunk = [&](float* v, int c0) {
                 if (scale.sumsq != nullptr) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j) v[j] *= s_pscale[buf][c0 + j];
@@ -652,10 +694,87 @@ __global__ void __launch_bounds__(320) gemm_tc_persistent_kernel(const __grid_co
                 } else if (mode == TC_OUT_SWIGLU) {
                     if (n0 + quarter * 32 < N) store_chunk_swiglu(out, t0 + c0, n0 + quarter * 32, lane, T, N, v);
                 } else if (n < N) store_chunk(out, mode, t0 + c0, n, T, N, v);
+            };
+            // the parked piece: [BN columns][128 rows], so that a warp's 32 lanes store and load 128 contiguous bytes;
+            // this warp reads exactly what the warp of the same number wrote in the other CTA
+            float* parked = SK ? sk.partials + (size_t)(blockIdx.x + (is_head ? tiles_t : 0)) * BN * TC_BM + quarter * 32 + lane : nullptr;
+            int* parked_flag = SK ? sk.flags + (blockIdx.x + (is_head ? tiles_t : 0)) * 8 + (warp - 2) : nullptr;
+            if (SK && is_head) {
+                // The other CTA parked its piece first thing and this is our last piece: the wait is short or none.
+                // The piece comes from L2 a microsecond after it is asked for, and nothing runs beside this last
+                // epilogue: its first chunks are asked for here, while the MMAs of the piece still run, and each
+                // later chunk as soon as a register set is free.
+                constexpr int AHEAD = 4;
+                float pre[AHEAD][16];
+                bool there = false;
+                if (ok && lane == 0) {
+                    for (int spin = 0; spin < (1 << 22) && !there; ++spin) {
+                        int seen;
+                        asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(parked_flag) : "memory");
+                        there = seen == 1;
+                        if (!there) __nanosleep(64);
+                    }
+                    if (!there) atomicExch(error_flag, 15);
+                }
+                there = __shfl_sync(0xffffffffu, there, 0);
+                __syncwarp();
+                if (!there) ok = false;
+                if (ok) {
+#pragma unroll
+                    for (int c = 0; c < AHEAD; ++c) {
+                        if (c_begin + c * 16 < c_end) {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) pre[c][j] = __ldcg(parked + (size_t)(c_begin + c * 16 + j) * TC_BM);
+                        }
+                    }
+                }
+                if (ok && !mbar_wait(&acc_full[buf], acc_phase)) { if (lane == 0) atomicExch(error_flag, 14); ok = false; }
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) continue;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+                for (int cg = c_begin; cg < c_end; cg += AHEAD * 16) {
+#pragma unroll
+                    for (int c = 0; c < AHEAD; ++c) {
+                        const int c0 = cg + c * 16;
+                        if (c0 >= c_end) break;
+                        float v[16];
+                        tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c0), v);
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) v[j] += pre[c][j];
+                        if (c0 + AHEAD * 16 < c_end) {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) pre[c][j] = __ldcg(parked + (size_t)(c0 + AHEAD * 16 + j) * TC_BM);
+                        }
+                        finish_chunk(v, c0);
+                    }
+                }
+            } else {
+                // a warp whose wait gave up keeps walking the tiles (the barrier above counts on it) but touches nothing
+                if (ok && !mbar_wait(&acc_full[buf], acc_phase)) { if (lane == 0) atomicExch(error_flag, 14); ok = false; }
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) continue;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+                for (int c0 = c_begin; c0 < c_end; c0 += 16) {
+                    float v[16];
+                    tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c0), v);
+                    if (SK && is_tail) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) __stcg(parked + (size_t)(c0 + j) * TC_BM, v[j]);
+                    } else {
+                        finish_chunk(v, c0);
+                    }
+                }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            if (is_tail) __threadfence();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_empty[buf]);
+            if (lane == 0) {
+                mbar_arrive(&acc_empty[buf]);
+                if (is_tail) asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(parked_flag), "r"(1) : "memory");
+                if (is_head) asm volatile("st.relaxed.gpu.global.s32 [%0], %1;" ::"l"(parked_flag), "r"(0) : "memory");   // for the next launch
+            }
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -703,24 +822,32 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* out, in
 // Tiles a launch with `bn` tokens per CTA would have (for the caller's choice of split).
 MB_API int mb_gemm_tc_tiles(int T, int N, int bn) { return ((N + TC_BM - 1) / TC_BM) * ((T + bn - 1) / bn); }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool SK>
 static int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int mode, int T, int N, int K, int ctas,
-                             int* error_flag, const TcNormOut& norm, const TcRowScale& scale, cudaStream_t s) {
+                             int* error_flag, const TcNormOut& norm, const TcRowScale& scale, TcStreamK sk, cudaStream_t s) {
     constexpr int smem = STAGES * TcSmem<BN>::STAGE_BYTES + 1024 + 256;
     static_assert(smem <= 227 * 1024, "the ring does not fit shared memory");
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel<BN, STAGES, SK>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    const int tiles = ((N + TC_BM - 1) / TC_BM) * ((T + BN - 1) / BN);
-    return launch_kernel(gemm_tc_persistent_kernel<BN, STAGES>, dim3(tiles < ctas ? tiles : ctas), dim3(320), smem, s, 0, mw, mx, out,
-                         mode, T, N, K, error_flag, norm, scale);
+    const int tiles_n = (N + TC_BM - 1) / TC_BM, tiles_t = (T + BN - 1) / BN, tiles = tiles_n * tiles_t;
+    int grid = tiles < ctas ? tiles : ctas;
+    if (SK) {
+        // every group the same number of k-blocks; at least a tile's worth each, so that a tile has two owners at most
+        const int groups = ctas / tiles_t;
+        const long long units = (long long)tiles_n * ((K + TC_BK - 1) / TC_BK);
+        sk.units_per_group = (int)((units + groups - 1) / groups);
+        grid = groups * tiles_t;
+    }
+    return launch_kernel(gemm_tc_persistent_kernel<BN, STAGES, SK>, dim3(grid), dim3(320), smem, s, 0, mw, mx, out, mode, T, N, K,
+                         error_flag, norm, scale, sk);
 }
 
 static int persistent_dispatch(const void* x, const void* w, void* out, int mode, int T, int N, int K, int bn, int ctas,
-                               int* error_flag, const TcNormOut& norm, const TcRowScale& scale, cudaStream_t s) {
+                               int* error_flag, const TcNormOut& norm, const TcRowScale& scale, const TcStreamK& sk, cudaStream_t s) {
     if (T <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15) || ctas <= 0) return MB_ERR_BAD_SIZE;
     if (mode < 0 || mode > 3 || (mode == 3 && N % 32 != 0)) return MB_ERR_BAD_DTYPE;
@@ -731,16 +858,24 @@ static int persistent_dispatch(const void* x, const void* w, void* out, int mode
     if (rc) return rc;
     rc = make_map(&mx, x, T, K, bn);
     if (rc) return rc;
+    if (sk.partials != nullptr) {
+        switch (bn) {                                   // stream-K: three widths
+            case 128: return launch_persistent<128, 6, true>(mw, mx, out, mode, T, N, K, ctas, error_flag, norm, scale, sk, s);
+            case 192: return launch_persistent<192, 5, true>(mw, mx, out, mode, T, N, K, ctas, error_flag, norm, scale, sk, s);
+            case 256: return launch_persistent<256, 4, true>(mw, mx, out, mode, T, N, K, ctas, error_flag, norm, scale, sk, s);
+            default: return MB_ERR_BAD_SIZE;
+        }
+    }
     switch (bn) {
-        case 128: return launch_persistent<128, 6>(mw, mx, out, mode, T, N, K, ctas, error_flag, norm, scale, s);
-        case 144: return launch_persistent<144, 6>(mw, mx, out, mode, T, N, K, ctas, error_flag, norm, scale, s);
-        case 160: return launch_persistent<160, 5>(mw, mx, out, mode, T, N, K, ctas, error_flag, norm, scale, s);
-        case 176: return launch_persistent<176, 5>(mw, mx, out, mode, T, N, K, ctas, error_flag, norm, scale, s);
-        case 192: return launch_persistent<192, 5>(mw, mx, out, mode, T, N, K, ctas, error_flag, norm, scale, s);
-        case 208: return launch_persistent<208, 4>(mw, mx, out, mode, T, N, K, ctas, error_flag, norm, scale, s);
-        case 224: return launch_persistent<224, 4>(mw, mx, out, mode, T, N, K, ctas, error_flag, norm, scale, s);
-        case 240: return launch_persistent<240, 4>(mw, mx, out, mode, T, N, K, ctas, error_flag, norm, scale, s);
-        case 256: return launch_persistent<256, 4>(mw, mx, out, mode, T, N, K, ctas, error_flag, norm, scale, s);
+        case 128: return launch_persistent<128, 6, false>(mw, mx, out, mode, T, N, K, ctas, error_flag, norm, scale, sk, s);
+        case 144: return launch_persistent<144, 6, false>(mw, mx, out, mode, T, N, K, ctas, error_flag, norm, scale, sk, s);
+        case 160: return launch_persistent<160, 5, false>(mw, mx, out, mode, T, N, K, ctas, error_flag, norm, scale, sk, s);
+        case 176: return launch_persistent<176, 5, false>(mw, mx, out, mode, T, N, K, ctas, error_flag, norm, scale, sk, s);
+        case 192: return launch_persistent<192, 5, false>(mw, mx, out, mode, T, N, K, ctas, error_flag, norm, scale, sk, s);
+        case 208: return launch_persistent<208, 4, false>(mw, mx, out, mode, T, N, K, ctas, error_flag, norm, scale, sk, s);
+        case 224: return launch_persistent<224, 4, false>(mw, mx, out, mode, T, N, K, ctas, error_flag, norm, scale, sk, s);
+        case 240: return launch_persistent<240, 4, false>(mw, mx, out, mode, T, N, K, ctas, error_flag, norm, scale, sk, s);
+        case 256: return launch_persistent<256, 4, false>(mw, mx, out, mode, T, N, K, ctas, error_flag, norm, scale, sk, s);
         default: return MB_ERR_BAD_SIZE;
     }
 }
@@ -748,7 +883,26 @@ static int persistent_dispatch(const void* x, const void* w, void* out, int mode
 // The persistent kernel: bn tokens per tile (a multiple of 16 from 128 to 256), `ctas` CTAs (one per SM).
 MB_API int mb_gemm_tc_persistent(const void* x, const void* w, void* out, int mode, int T, int N, int K, int bn, int ctas,
                                  int* error_flag, cudaStream_t s) {
-    return persistent_dispatch(x, w, out, mode, T, N, K, bn, ctas, error_flag, TcNormOut{}, TcRowScale{}, s);
+    return persistent_dispatch(x, w, out, mode, T, N, K, bn, ctas, error_flag, TcNormOut{}, TcRowScale{}, TcStreamK{}, s);
+}
+
+// The same with the k-blocks dealt out evenly (stream-K, see TcStreamK): no last round of tiles that fills a part of
+// the SMs.  bn is 128, 192 or 256.  ctas must not exceed the SMs of the device (a CTA may wait for its neighbour's
+// piece); there must be no more token tiles than CTAs and at least as many weight-row tiles as groups (ctas / token tiles).  partials:
+// ctas * bn * 128 floats; flags: ctas * 8 ints, zero before the first call (the kernel leaves them at zero).  Two
+// launches that share them must not overlap.
+MB_API int mb_gemm_tc_persistent_streamk(const void* x, const void* w, void* out, int mode, int T, int N, int K, int bn, int ctas,
+                                         float* partials, long long partials_floats, int* flags, int* error_flag, cudaStream_t s) {
+    if (T <= 0 || N <= 0) return 0;
+    if (partials == nullptr || flags == nullptr || bn <= 0 || ctas <= 0) return MB_ERR_BAD_SIZE;
+    static int sms = 0;                                            // of the device of the first call: all devices of a box are alike
+    if (sms == 0) {
+        int device = 0;
+        if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return MB_ERR_BAD_SIZE;
+    }
+    const int tiles_n = (N + TC_BM - 1) / TC_BM, tiles_t = (T + bn - 1) / bn;
+    if (ctas > sms || tiles_t > ctas || tiles_n < ctas / tiles_t || partials_floats < (long long)ctas * bn * TC_BM) return MB_ERR_BAD_SIZE;
+    return persistent_dispatch(x, w, out, mode, T, N, K, bn, ctas, error_flag, TcNormOut{}, TcRowScale{}, TcStreamK{partials, flags, 0}, s);
 }
 
 // The same coupled with the RMS norms around it (see mb_gemm_tc_coupled; the slots are mb_gemm_tc_norm_slots(N, 1)).
@@ -758,7 +912,7 @@ MB_API int mb_gemm_tc_persistent_coupled(const void* x, const void* w, void* out
                                          int* error_flag, cudaStream_t s) {
     TcNormOut norm{norm_weight, (bf16*)scaled_out, sumsq_out, norm_unit_offset};
     TcRowScale scale{scale_sumsq, scale_slots, scale_dim, scale_eps};
-    return persistent_dispatch(x, w, out, mode, T, N, K, bn, ctas, error_flag, norm, scale, s);
+    return persistent_dispatch(x, w, out, mode, T, N, K, bn, ctas, error_flag, norm, scale, TcStreamK{}, s);
 }
 
 // x [T, K] bf16, w [N, K] bf16, out [T, N]: bf16 (mode 0), float32 (1), float32 += (2).  K must be a multiple

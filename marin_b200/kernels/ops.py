@@ -104,13 +104,18 @@ _scratch = {}
 
 def _gemm_scratch(device):
     """Split-K partials, per-tile counters (zeroed once; the kernel leaves them at zero) and the error flag."""
+    global SM_COUNT
     key = (device.type, device.index)
     s = _scratch.get(key)
     if s is None:
+        SM_COUNT = torch.cuda.get_device_properties(device).multi_processor_count
         s = {"partials": torch.empty(8 << 20, device=device, dtype=torch.float32),
              "counters": torch.zeros(1 << 16, device=device, dtype=torch.int32),
              "error": torch.zeros(1, device=device, dtype=torch.int32),
-             "sumsq": torch.empty(1 << 22, device=device, dtype=torch.float32)}
+             "sumsq": torch.empty(1 << 22, device=device, dtype=torch.float32),
+             # stream-K: the partial tile each CTA may park (the widest tile), and a flag per epilogue warp
+             "parked": torch.empty(SM_COUNT * 256 * 128, device=device, dtype=torch.float32),
+             "parked_flags": torch.zeros(SM_COUNT * 8, device=device, dtype=torch.int32)}
         _scratch[key] = s
     return s
 
@@ -141,18 +146,71 @@ def gemm_plan(T: int, N: int, K: int):
 
 
 PERSISTENT_TILES = (128, 144, 160, 176, 192, 208, 224, 240, 256)
+STREAM_K_TILES = (128, 192, 256)
 
 
 def persistent_plan(T: int, N: int) -> int:
     """Tokens per tile for the persistent kernel: the tile width whose rounds over the SMs waste the least.
     A tile's time grows with its width plus a fixed part (ramp-up of the ring, the epilogue's tail)."""
+    return _tile_by_tile(T, N)[1]
+
+
+def _tile_by_tile(T: int, N: int):
     best = None
     for bn in PERSISTENT_TILES:
         tiles = -(-N // 128) * -(-T // bn)
         cost = -(-tiles // SM_COUNT) * (bn + 24)
         if best is None or cost < best[0]:
             best = (cost, bn)
-    return best[1]
+    return best
+
+
+#: the persistent kernel deals k-blocks instead of tiles over the SMs where whole tiles would leave SMs idle
+stream_k = True
+
+
+#: Stream-K against tile by tile, fitted to timings on B200 (2,048 and 1,024 tokens, layer sizes of 4B to 14B models):
+#: a k-block of a 128 x bn tile costs about bn + 138 (the weight tile is fetched whatever the width), and stream-K
+#: pays a fixed part worth 7,700 such units (about 8 us: every CTA parks a partial tile at the start and the last
+#: epilogue, which nothing overlaps, is longer).  Measured times came out up to 0.1 above the predicted ratio, hence
+#: the margin.  Groups walk different k at the same time, so x has to stay in L2 (at 71 MB stream-K lost 6 % where
+#: the fit promised 9 %), and with fewer than four token tiles the fit did not hold (0.98 and 1.07 for 0.75 and 0.91).
+_KBLOCK_FIXED, _STREAM_K_FIXED, _STREAM_K_MARGIN, _STREAM_K_MAX_X_BYTES = 138, 7700, 0.87, 48 << 20
+
+
+def stream_k_plan(T: int, N: int, K: int) -> Optional[int]:
+    """Tokens per tile if the product should run stream-K, else None.  The CTAs form groups, one CTA per token tile,
+    and every group gets the same number of k-blocks of the weight-row tiles laid end to end: the time goes with
+    row tiles / groups, without rounding up to whole rounds of tiles.  It needs at least one row tile per group."""
+    if not stream_k:
+        return None
+    best = None
+    rows, nkb = -(-N // 128), -(-K // 64)
+    for bn in STREAM_K_TILES:
+        across = -(-T // bn)
+        if across > SM_COUNT or rows < SM_COUNT // across or (_STREAM_K_FIXED > 0 and (across < 4 or T * K * 2 > _STREAM_K_MAX_X_BYTES)):
+            continue
+        cost = rows / (SM_COUNT // across) * nkb * (bn + _KBLOCK_FIXED) + _STREAM_K_FIXED
+        if best is None or cost <= best[0]:
+            best = (cost, bn)
+    if best is None:
+        return None
+    bn = persistent_plan(T, N)
+    whole = -(-(rows * -(-T // bn)) // SM_COUNT) * nkb * (bn + _KBLOCK_FIXED)
+    return best[1] if best[0] < _STREAM_K_MARGIN * whole else None
+
+
+def _persistent_product(x, w, out, mode: int, T: int, N: int, K: int, s, what: str) -> None:
+    lib = _lib("mb_gemm_tc")
+    bn = stream_k_plan(T, N, K)
+    if bn is not None:
+        _check(lib.mb_gemm_tc_persistent_streamk(
+            _ptr(x), _ptr(w), _ptr(out), _c_int(mode), _c_int(T), _c_int(N), _c_int(K), _c_int(bn), _c_int(SM_COUNT),
+            _ptr(s["parked"]), ctypes.c_longlong(s["parked"].numel()), _ptr(s["parked_flags"]), _ptr(s["error"]), _stream()),
+            what + ", stream-K")
+        return
+    _check(lib.mb_gemm_tc_persistent(_ptr(x), _ptr(w), _ptr(out), _c_int(mode), _c_int(T), _c_int(N), _c_int(K),
+                                     _c_int(persistent_plan(T, N)), _c_int(SM_COUNT), _ptr(s["error"]), _stream()), what)
 
 
 class NormOut:
@@ -213,9 +271,7 @@ def gemm(x, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False, then_n
                 if slots * T <= s["sumsq"].numel():
                     carried = NormedRows(then_norm.rows, s["sumsq"], slots, N, then_norm.eps)
             if carried is None and scaled is None:
-                _check(lib.mb_gemm_tc_persistent(_ptr(x), _ptr(w), _ptr(out), _c_int(mode), _c_int(T), _c_int(N),
-                                                 _c_int(K), _c_int(persistent_plan(T, N)), _c_int(SM_COUNT),
-                                                 _ptr(s["error"]), _stream()), "gemm (tensor cores, persistent)")
+                _persistent_product(x, w, out, mode, T, N, K, s, "gemm (tensor cores, persistent)")
                 return None
             _check(lib.mb_gemm_tc_persistent_coupled(
                 _ptr(x), _ptr(w), _ptr(out), _c_int(mode), _c_int(T), _c_int(N), _c_int(K), _c_int(persistent_plan(T, N)), _c_int(SM_COUNT),
@@ -463,9 +519,7 @@ def gemm_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor, out: torch.Tensor,
                 _c_int(SM_COUNT), None, _c_int(0), None, None, _ptr(scaled.sumsq), _c_int(scaled.slots), _c_int(scaled.dim),
                 _c_float(scaled.eps), _ptr(s["error"]), _stream()), "gemm+swiglu (tensor cores, persistent, coupled with a norm)")
             return
-        _check(_lib("mb_gemm_tc").mb_gemm_tc_persistent(_ptr(x), _ptr(w_interleaved), _ptr(out), _c_int(3), _c_int(T), _c_int(N),
-                                                       _c_int(K), _c_int(persistent_plan(T, N)), _c_int(SM_COUNT),
-                                                       _ptr(s["error"]), _stream()), "gemm+swiglu (tensor cores, persistent)")
+        _persistent_product(x, w_interleaved, out, 3, T, N, K, s, "gemm+swiglu (tensor cores, persistent)")
         return
     bn, _ = gemm_plan(T, N, K)
     if scaled is not None:

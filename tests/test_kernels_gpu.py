@@ -317,6 +317,50 @@ def test_gemm_tensor_cores(ops, T, N, K):
     ops.check_device_errors()
 
 
+@pytest.mark.parametrize("T,N,K", [(2048, 2560, 4096), (1000, 3000, 1032), (1999, 2560, 9728), (777, 6144, 72), (5000, 1152, 64), (600, 4864, 520)])
+def test_gemm_stream_k(ops, monkeypatch, T, N, K):
+    """Shapes for which the k-blocks, not the tiles, are dealt over the SMs: the pieces of a tile that two CTAs share
+    must add up.  Against float64, against the tile-by-tile kernel, and twice (the flags must be back at zero).
+    Column 0 of x and w carry ramps, and the first and the last k-block differ in size, so that a piece added
+    to the wrong tile, added twice or left out shows."""
+    monkeypatch.setattr(ops, "_STREAM_K_FIXED", -1e12)            # stream-K wherever it can run, not only where it pays
+    assert ops.stream_k_plan(T, N, K) is not None
+    g = torch.Generator(device=DEV).manual_seed(29)
+    x = torch.randn(T, K, device=DEV, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    x[:, 0] += torch.arange(T, device=DEV).to(torch.bfloat16) * 0.125
+    w[:, 0] += (torch.arange(N, device=DEV) % 64).to(torch.bfloat16) * 0.0625
+    x[:, K - 1] += (torch.arange(T, device=DEV) % 7).to(torch.bfloat16)
+    want = x.double() @ w.double().t()
+    scale = float(want.abs().max())
+    for _ in range(2):
+        out32 = torch.full((T, N), float("nan"), device=DEV)
+        ops.gemm(x, w, out32)
+        ops.check_device_errors()
+        assert float((out32.double() - want).abs().max()) <= 2e-5 * scale + 1e-4
+        base = torch.randn(T, N, device=DEV, generator=g)
+        acc = base.clone()
+        ops.gemm(x, w, acc, accumulate=True)
+        assert float((acc.double() - base.double() - want).abs().max()) <= 2e-5 * scale + 1e-4
+        out16 = torch.empty(T, N, device=DEV, dtype=torch.bfloat16)
+        ops.gemm(x, w, out16)
+    ops.check_device_errors()
+    monkeypatch.setattr(ops, "stream_k", False)
+    plain16 = torch.empty_like(out16)
+    ops.gemm(x, w, plain16)
+    # float32 sums of the same products in another order, rounded to bf16: one step of bf16 apart at most
+    torch.testing.assert_close(out16.float(), plain16.float(), rtol=2 ** -7, atol=1e-3 * scale)
+    if N % 32 == 0:
+        monkeypatch.setattr(ops, "stream_k", True)
+        a = torch.empty(T, N // 2, device=DEV, dtype=torch.bfloat16)
+        ops.gemm_swiglu(x, w, a)
+        ops.check_device_errors()
+        monkeypatch.setattr(ops, "stream_k", False)
+        b = torch.empty_like(a)
+        ops.gemm_swiglu(x, w, b)
+        torch.testing.assert_close(a.float(), b.float(), rtol=2 ** -6, atol=1e-3 * scale * scale)
+
+
 @pytest.mark.parametrize("T,N,K,N2,unit", [(8, 2560, 4096, 6144, False), (1, 320, 512, 384, False), (13, 200, 264, 96, True),
                                             (33, 1024, 9728, 2048, False), (64, 2560, 512, 640, False), (16, 128, 64, 64, True),
                                             (1000, 2560, 512, 2560, False), (2048, 2560, 1024, 6144, True), (777, 1536, 320, 96, False)])
@@ -332,6 +376,7 @@ def test_gemm_carries_the_norm_that_follows(ops, monkeypatch, T, N, K, N2, unit)
     eps = 1e-5
     monkeypatch.setattr(ops, "COUPLED_NORM_MAX_TOKENS", 64)         # every tile width the kernel couples at
     monkeypatch.setattr(ops, "couple_norms_in_prefill", True)       # and the persistent kernel, for many tokens
+    monkeypatch.setattr(ops, "stream_k", False)                     # the coupled product runs tile by tile: so must its twin, for equal bits
     for _ in range(2):
         h = h0.clone()
         normed = torch.full((T, N), float("nan"), device=DEV, dtype=torch.bfloat16)
