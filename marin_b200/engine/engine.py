@@ -114,6 +114,8 @@ class Engine:
         self.max_batch, self.token_budget = max_batch, token_budget
         #: False: logits go to the host and the host sampler (the reference's algorithm line by line) picks the token
         self.device_sampling = device_sampling and self.rt.device.type == "cuda"
+        #: pack the next decode step's inputs while the GPU runs the current one (Runner.prepare_next)
+        self.prepare_ahead = True
         self.scheduler = Scheduler(self.cache, max_batch, token_budget, self.ctx)
         self._requests: Dict[Hashable, Request] = {}
         self._samplers: Dict[Hashable, Sampler] = {}
@@ -144,6 +146,11 @@ class Engine:
             return []
         entries = [StepEntry(p.request.req_id, p.tokens, [len(p.tokens) - 1] if p.sample else []) for p in plan]
         logits = self.runner.step(entries)
+        if self.prepare_ahead and all(p.sample and len(p.tokens) == 1 and len(p.request.output) + 1 < p.request.params.max_tokens
+                                      for p in plan):
+            # every request decodes and none reaches its length limit: most likely the next step is this one over
+            # again, one position on; its inputs are packed now, while the GPU is busy, instead of after the wait below
+            self.runner.prepare_next(entries)
         sampled = self._sample(plan, logits, self._samplers, self.config.vocab_size)
         return self.scheduler.update(plan, sampled)
 

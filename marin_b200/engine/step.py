@@ -14,6 +14,7 @@ from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence
 
 import ctypes
+import gc
 
 import numpy as np
 import torch
@@ -70,6 +71,8 @@ class Runner:
         #: after a step replayed from a graph: int32 ids of the largest logit of each returned row (lowest id among
         #: equals), computed inside the graph; None after any other step
         self.greedy_ids: Optional[torch.Tensor] = None
+        self._replayed: Optional[dict] = None      # the graph the last step was replayed from, if it was
+        self._prepared: Optional[dict] = None      # the next step's inputs, packed ahead (see prepare_next)
 
     # ---- requests ----------------------------------------------------------------------------------
     def begin(self, req_id: Hashable) -> None:
@@ -102,11 +105,13 @@ class Runner:
                 if not 0 <= int(w) < n:
                     raise StepError(f"request {e.req_id!r}: wanted place {w} is outside its {n} tokens")
 
-    def build_context(self, entries: Sequence[StepEntry], pad_to: int = 0, static=None, refresh_only: bool = False):
+    def build_context(self, entries: Sequence[StepEntry], pad_to: int = 0, static=None, refresh_only: bool = False,
+                      pack_only: bool = False):
         """Flattens the entries (single tokens first) into the arrays the kernels read, and copies
         them to the device in one transfer.  ``pad_to`` (decode batches only) pads the batch with empty
         requests up to a fixed size; ``static`` is then the device buffer a captured graph reads, and with
-        ``refresh_only`` nothing but that buffer is wanted (a replay follows): no context is built."""
+        ``refresh_only`` nothing but that buffer is wanted (a replay follows): no context is built; with ``pack_only``
+        the pinned host buffer is filled and not copied (the device buffer may still be read by the step that runs)."""
         cache = self.cache
         n = len(entries)
         counts = np.fromiter((len(e.tokens) for e in entries), np.int32, n)
@@ -138,6 +143,8 @@ class Runner:
         num_decode, max_query_len, max_seq_len = int(info[3]), int(info[4]), int(info[5])
         num_rows = W
         if static is not None:
+            if pack_only:
+                return None
             dev.copy_(host, non_blocking=True)
             copied.record()
             if refresh_only:
@@ -181,16 +188,18 @@ class Runner:
     #: sequences up to this long share the shortest graph; longer ones take the next power of two
     GRAPH_MIN_SPAN = 1024
 
+    def _span_of(self, longest: int) -> int:
+        span = self.GRAPH_MIN_SPAN
+        while span < longest:
+            span *= 2
+        return min(span, self.max_seq_len)
+
     def _graph_for(self, bucket: int, entries: Sequence[StepEntry]) -> dict:
         # A graph is captured per padded batch size and per span of sequence lengths (a power of two, at most the
         # context capacity): the split of the keys over CTAs is part of the captured grid, and a split made for the
         # whole capacity would leave short sequences to one CTA each.
-        longest = self._longest
-        span = self.GRAPH_MIN_SPAN
-        while span < longest:
-            span *= 2
-        span = min(span, self.max_seq_len)
-        key = (bucket, span)
+        key = (bucket, self._span_of(self._longest))
+        span = key[1]
         g = self.graphs.get(key)
         if g is not None:
             return g
@@ -206,7 +215,7 @@ class Runner:
         # the split of the keys is fixed by the span, so that the captured grid fits every step of this graph
         split, chunks = ops.decode_split(bucket, kv_heads, span)
         shared = next((o for (b, _), o in self.graphs.items() if b == bucket), None)
-        g = {"static": (host, dev, torch.cuda.Event()), "workspace": shared["workspace"] if shared else Workspace(self.rt.device),
+        g = {"key": key, "static": (host, dev, torch.cuda.Event()), "workspace": shared["workspace"] if shared else Workspace(self.rt.device),
              "graph": None, "logits": None,
              "attn_split": (split, chunks),
              "attn_scratch": ops.decode_scratch(self.rt.device, bucket, heads, kv_heads, chunks, hd)}
@@ -227,9 +236,18 @@ class Runner:
         torch.cuda.synchronize()
         launches = ops.launches
         g["best"] = torch.zeros(bucket, device=self.rt.device, dtype=torch.int32)
-        with torch.cuda.graph(graph):
-            g["logits"] = self.model.forward(ctx, self.views)
-            ops.argmax(g["logits"], self.vocab, g["best"])        # greedy sampling rides in the same graph
+        # No garbage collection while the stream is capturing: an engine or a tensor dropped earlier that is freed now
+        # (pinned memory, events, older graphs) would make a CUDA call that a capture does not allow, and the capture
+        # would be lost.  (torch.cuda.graph collects once before it begins.)
+        collecting = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(graph):
+                g["logits"] = self.model.forward(ctx, self.views)
+                ops.argmax(g["logits"], self.vocab, g["best"])    # greedy sampling rides in the same graph
+        finally:
+            if collecting:
+                gc.enable()
         g["launches"] = ops.launches - launches
         g["graph"] = graph
         return g
@@ -247,6 +265,7 @@ class Runner:
         self.build_context(entries, pad_to=bucket, static=g["static"], refresh_only=True)
         g["graph"].replay()
         ops.launches_extra(g["launches"])
+        self._replayed = g
         rows = [i for i, e in enumerate(entries) for _ in e.want]
         if rows == list(range(len(entries))):
             self.greedy_ids = g["best"][: len(entries)]      # the largest logit of each returned row, already found
@@ -259,6 +278,9 @@ class Runner:
         graph replay off for this step."""
         self._validate(entries)
         self.greedy_ids = None
+        prepared, self._prepared, self._replayed = self._prepared, None, None
+        if prepared is not None and observe is None and self._is_the_prepared_step(prepared, entries):
+            return self._run_prepared(prepared, entries)
         cache, n = self.cache, len(entries)
         handles = np.fromiter((cache.requests[e.req_id].handle for e in entries), np.int64, n)
         counts = np.fromiter((len(e.tokens) for e in entries), np.int32, n)
@@ -283,3 +305,58 @@ class Runner:
             raise StepError(f"recording the step failed (code {rc})")
         self.steps_run += 1
         return logits
+
+    # ---- the next step, packed while this one runs -------------------------------------------------------------
+    def prepare_next(self, entries: Sequence[StepEntry]) -> bool:
+        """To be called right after a step that was replayed from a graph, while the GPU runs it.  Supposes that the
+        same requests bring one token each to the next step too (no request ends, none joins): takes their pages and
+        packs that step's inputs, all but the token ids, into the graph's pinned buffer.  If the next call of
+        ``step`` brings exactly that, only the ids are filled in and copied; if it brings anything else the packed
+        buffer is forgotten (the pages taken are the requests' own either way).  Returns whether it prepared."""
+        g, self._prepared = self._replayed, None
+        if g is None or any(len(e.tokens) != 1 for e in entries):
+            return False
+        cache, n = self.cache, len(entries)
+        try:
+            handles = np.fromiter((cache.requests[e.req_id].handle for e in entries), np.int64, n)
+        except KeyError:
+            return False
+        counts = np.ones(n, np.int32)
+        info = (ctypes.c_int * 2)()
+        if cache._lib.mbh_step_reserve(cache._core(), n, handles.ctypes.data, counts.ctypes.data, self.max_seq_len, info) != OK:
+            return False                          # full context or no pages: the step itself will say so
+        longest = int(info[1])
+        if (g["key"][0], self._span_of(longest)) != g["key"]:
+            return False                          # the sequences grow into the next graph
+        ahead = [StepEntry(e.req_id, [0], [0]) for e in entries]
+        self.build_context(ahead, pad_to=g["key"][0], static=g["static"], pack_only=True)
+        self._prepared = {"graph": g, "ids": [e.req_id for e in entries], "handles": handles, "counts": counts, "longest": longest}
+        return True
+
+    def _is_the_prepared_step(self, prepared: dict, entries: Sequence[StepEntry]) -> bool:
+        ids, handles, requests = prepared["ids"], prepared["handles"], self.cache.requests
+        if len(entries) != len(ids):
+            return False
+        for e, rid, handle in zip(entries, ids, handles.tolist()):
+            if e.req_id != rid or len(e.tokens) != 1 or list(e.want) != [0] or requests[e.req_id].handle != handle:
+                return False
+        return True
+
+    def _run_prepared(self, prepared: dict, entries: Sequence[StepEntry]) -> torch.Tensor:
+        from ..kernels import ops
+
+        g, n = prepared["graph"], len(entries)
+        host, dev, copied = g["static"]
+        host.numpy()[:n] = [e.tokens[0] for e in entries]      # the token ids lead the packed buffer
+        dev.copy_(host, non_blocking=True)
+        copied.record()
+        g["graph"].replay()
+        ops.launches_extra(g["launches"])
+        self._longest = prepared["longest"]
+        rc = self.cache._lib.mbh_step_commit(self.cache._core(), n, prepared["handles"].ctypes.data, prepared["counts"].ctypes.data)
+        if rc != OK:
+            raise StepError(f"recording the step failed (code {rc})")
+        self.steps_run += 1
+        self._replayed = g
+        self.greedy_ids = g["best"][:n]
+        return g["logits"][:n]

@@ -167,6 +167,55 @@ def test_greedy_generation_through_the_entry_point(case):
     assert not engine.cache.requests
 
 
+def test_steps_packed_ahead_change_nothing(case):
+    """While a decode step runs the engine packs the next one on the supposition that the same requests go on.  The
+    supposition fails when a request ends on a stop token, is cancelled or another joins: requests of different
+    lengths, one that stops on a token it is known to produce, one added and one cancelled half way, run with and
+    without packing ahead, must give the same tokens, and the packed steps must really have been used."""
+    from marin_b200 import Engine, SamplingParams
+
+    rng = random.Random(31)
+    prompts = [random_prompt(rng, case.raw["vocab_size"], n) for n in (9, 3, 17, 6)]
+
+    def run(ahead: bool):
+        engine = Engine(case.dir, dtype=case.dtype, ctx=case.raw["max_position_embeddings"], page_size=case.page,
+                        max_batch=4, token_budget=32)
+        engine.prepare_ahead = ahead
+        used = [0]
+        inner = engine.runner._run_prepared
+        engine.runner._run_prepared = lambda *a: (used.__setitem__(0, used[0] + 1), inner(*a))[1]
+        first = engine.generate([prompts[0]], SamplingParams(temperature=0.0, max_tokens=10))[0].tokens
+        stop = first[6]                                       # request 0 run again ends when it produces this token
+        ids = [engine.add_request(prompts[0], SamplingParams(temperature=0.0, max_tokens=30, stop_tokens=(stop,))),
+               engine.add_request(prompts[1], SamplingParams(temperature=0.0, max_tokens=14)),
+               engine.add_request(prompts[2], SamplingParams(temperature=0.0, max_tokens=25))]
+        out = {i: [] for i in ids}
+        steps = 0
+        while engine.scheduler.has_work():
+            for rid, tok in engine.step():
+                out[rid].append(tok)
+            steps += 1
+            if steps == 8:
+                late = engine.add_request(prompts[3], SamplingParams(temperature=0.0, max_tokens=9))
+                ids.append(late)
+                out[late] = []
+            if steps == 16:
+                engine.scheduler.cancel(ids[2])
+            assert steps < 200
+        for i in ids:
+            engine.forget(i)
+        engine.cache.check()
+        assert not engine.cache.requests
+        return first, [out[i] for i in ids], used[0]
+
+    first_a, with_ahead, used = run(True)
+    first_b, without, unused = run(False)
+    assert used >= 10 and unused == 0
+    assert first_a == first_b and with_ahead == without
+    assert len(with_ahead[0]) == first_a.index(first_a[6])   # the stop token itself is not emitted
+    assert len(with_ahead[1]) == 14 and len(with_ahead[3]) == 9
+
+
 def test_schedule_may_repeat_a_layer_and_share_a_cache(case):
     """The order layers run in is data: layer 0 twice, the second run reading the first run's cache."""
     if case.name != "A":
