@@ -245,7 +245,8 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_split_kernel(
     uint32_t qa[D / 16][4];
     {
         const int qrow = lane >> 2;
-        const bf16* qsrc = q + ((size_t)r * H + kh * GROUP + (qrow < GROUP ? qrow : 0)) * D + 2 * (lane & 3);
+        // (the queries were written by the kernel just ahead: see pdl_fresh)
+        const bf16* qsrc = pdl_fresh(q) + ((size_t)r * H + kh * GROUP + (qrow < GROUP ? qrow : 0)) * D + 2 * (lane & 3);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
             qa[kk][0] = qrow < GROUP ? *reinterpret_cast<const uint32_t*>(qsrc + kk * 16) : 0u;
@@ -537,6 +538,7 @@ __global__ void __launch_bounds__(128, PF_MIN_CTAS) attn_prefill_kernel(
     const int* __restrict__ block_table, int max_pages, const int* __restrict__ cu_tokens, const int* __restrict__ seq_lens,
     int first_req, int K, int page_shift, float scale, int window) {
     PDL_ENTER_EARLY();
+    q = pdl_fresh(q); k_cache = pdl_fresh(k_cache); v_cache = pdl_fresh(v_cache);
     extern __shared__ __align__(16) uint8_t pf_smem[];
     bf16* sQ = reinterpret_cast<bf16*>(pf_smem);
     bf16* sKV = sQ + PF_BM * PF_LD;                  // [2 buffers][K then V][64][PF_LD]

@@ -15,6 +15,7 @@ __global__ void __launch_bounds__(AS_THREADS) attention_simple_kernel(
     const int* __restrict__ block_table, int max_pages, const int* __restrict__ req_index,
     const int* __restrict__ positions, int H, int K, int d, int page_size, float scale, int window) {
     PDL_ENTER();
+    q = pdl_fresh(q); k_cache = pdl_fresh(k_cache); v_cache = pdl_fresh(v_cache);
     extern __shared__ float smem[];
     float* qs = smem;                 // [d]
     float* ps = smem + d;             // [AS_THREADS]

@@ -28,6 +28,7 @@ template <typename TO>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, float eps, int unit_offset,
                                TO* __restrict__ out, int n) {
     PDL_ENTER();
+    x = pdl_fresh(x);
     __shared__ float scratch[32];
     const float* row = x + (size_t)blockIdx.x * n;
     TO* dst = out + (size_t)blockIdx.x * n;
@@ -47,6 +48,7 @@ template <typename TO, int R>
 __global__ void __launch_bounds__(256) rmsnorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ w, float eps,
                                                           int unit_offset, TO* __restrict__ out, int n) {
     PDL_ENTER();
+    x = pdl_fresh(x);
     __shared__ float scratch[32];
     const float4* row = reinterpret_cast<const float4*>(x + (size_t)blockIdx.x * n);
     const float4* w4 = reinterpret_cast<const float4*>(w);
@@ -111,6 +113,7 @@ __global__ void qk_norm_rope_write_kernel(const T* __restrict__ qkv, int row_str
                                           T* __restrict__ k_cache, T* __restrict__ v_cache, int H, int K, int d,
                                           int page_size, int heads_total, int heads_per_warp) {
     PDL_ENTER();
+    qkv = pdl_fresh(qkv);
     extern __shared__ float smem[];
     const int warps = blockDim.x >> 5;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -180,6 +183,7 @@ __global__ void __launch_bounds__(256) qk_norm_rope_write_fast_kernel(
     const int* __restrict__ slot_mapping, bf16* __restrict__ k_cache, bf16* __restrict__ v_cache, int H, int K, int page_size,
     int heads_total) {
     PDL_ENTER();
+    qkv = pdl_fresh(qkv);
     constexpr int d = LPH * 8, half = d / 2;
     __shared__ float cs_tab[half], sn_tab[half];
     const int t = blockIdx.x;
@@ -284,6 +288,7 @@ MB_API int mb_qk_norm_rope_write(const void* qkv, int dtype, void* q_out, const 
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total, int interleaved) {
     PDL_ENTER();
+    gu = pdl_fresh(gu);
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (; idx < total; idx += stride) {
@@ -309,6 +314,7 @@ MB_API int mb_swiglu(const void* gate_up, void* out, int dtype, int tokens, int 
 // ---- rows of the residual stream whose logits are wanted ----------------------------------------------
 __global__ void gather_rows_kernel(const float* __restrict__ src, const int* __restrict__ rows, float* __restrict__ out, int h) {
     PDL_ENTER();
+    src = pdl_fresh(src);
     const float* row = src + (size_t)rows[blockIdx.x] * h;
     float* dst = out + (size_t)blockIdx.x * h;
     for (int i = threadIdx.x; i < h; i += blockDim.x) dst[i] = row[i];
@@ -323,6 +329,7 @@ MB_API int mb_gather_rows(const float* src, const int* rows, float* out, int cou
 template <typename T>
 __global__ void add_into_kernel(float* __restrict__ y, const T* __restrict__ x, size_t total) {
     PDL_ENTER();
+    x = pdl_fresh(x);
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (; idx < total; idx += stride) y[idx] += to_f32(x[idx]);

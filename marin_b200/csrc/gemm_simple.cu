@@ -13,6 +13,7 @@ template <typename TX, typename TW, typename TO, bool ACC>
 __global__ void __launch_bounds__(256) gemm_simple_kernel(const TX* __restrict__ x, const TW* __restrict__ w,
                                                           TO* __restrict__ out, int T, int N, int K) {
     PDL_ENTER();
+    x = pdl_fresh(x);
     __shared__ float sx[GS_BK][GS_TILE + 1];
     __shared__ float sw[GS_BK][GS_TILE + 1];
     const int t0 = blockIdx.y * GS_TILE, n0 = blockIdx.x * GS_TILE;

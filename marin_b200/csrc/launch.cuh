@@ -1,7 +1,8 @@
 // Launching with programmatic dependent launch (PDL): a kernel may be scheduled while the kernel before it in the
 // stream is still running, so that its start-up (and, for the matrix product, the first weight tiles, which no
 // earlier kernel writes) overlaps the predecessor's tail.  Rules every kernel of this package follows:
-//   * nothing that an earlier kernel may write is read, and no global memory is written, before pdl_wait();
+//   * nothing that an earlier kernel may write is read, and no global memory is written, before pdl_wait(); pointers
+//     to such data are renewed with pdl_fresh() after the wait, so that the compiler cannot move their loads up;
 //   * pdl_wait() returns once every earlier kernel in the stream has finished and its writes are visible.
 // Without the launch attribute both instructions do nothing.  MARIN_B200_PDL=0 in the environment turns it off.
 #pragma once
@@ -10,6 +11,17 @@
 
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// A pointer to what a kernel ahead in the stream has written goes through this after the wait, before anything is
+// loaded through it.  A load through a `const __restrict__` pointer is an invariant load to the compiler, which a
+// memory clobber does not hold in place: it may be moved above the wait, and was, once (decode attention read its
+// queries before the kernel ahead had written them).  The empty volatile asm makes the pointer's value, and with
+// it every load through it, come after the wait.
+template <typename T>
+__device__ __forceinline__ T* pdl_fresh(T* p) {
+    asm volatile("" : "+l"(p) : : "memory");
+    return p;
+}
 
 // The start of a kernel that needs nothing before its inputs.  PDL_ENTER() lets the kernels behind it be scheduled
 // once its own inputs are there; PDL_ENTER_EARLY() lets them be scheduled at once, so that their CTAs sit on the

@@ -25,6 +25,7 @@ __device__ __forceinline__ unsigned long long am_key(float v, int idx) {
 __global__ void __launch_bounds__(AM_THREADS) argmax_kernel(const float* __restrict__ logits, int vocab, int usable,
                                                             int per_block, int* __restrict__ out) {
     PDL_ENTER();
+    logits = pdl_fresh(logits);
     __shared__ float best_v[AM_THREADS / 32];
     __shared__ int best_i[AM_THREADS / 32];
     const int r = blockIdx.y;
@@ -140,6 +141,7 @@ __global__ void __launch_bounds__(SP_THREADS) sample_kernel(const float* __restr
                                                             const float* __restrict__ top_p, const float* __restrict__ uniform,
                                                             int* __restrict__ out) {
     PDL_ENTER();
+    logits = pdl_fresh(logits);
     __shared__ float fs[32];
     __shared__ int is[32];
     __shared__ int s_found;

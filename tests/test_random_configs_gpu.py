@@ -27,7 +27,20 @@ def draw(rng: random.Random) -> tuple:
     return raw, rng.choice([2, 4, 8, 16, 16, 32, 64]), rng.choice([37, 70, 130, 190])
 
 
-@pytest.mark.parametrize("seed", range(6))
+#: Configurations that once went wrong.  One query head per kv head with heads that are not 128 wide, decoded from
+#: graphs: the compiler had moved the loads of the queries above the wait for the kernel that writes them (it showed
+#: only in graphs, where kernels really overlap, and only in the build for groups of one).
+PINNED = [
+    ({"model_type": "qwen3", "num_hidden_layers": 1, "hidden_size": 136, "num_attention_heads": 2, "num_key_value_heads": 2,
+      "head_dim": 112, "intermediate_size": 48, "vocab_size": 300, "rope_theta": 1e4, "rms_norm_eps": 1e-5,
+      "tie_word_embeddings": True, "max_position_embeddings": 200}, 64, 37),
+    ({"model_type": "qwen3", "num_hidden_layers": 2, "hidden_size": 200, "num_attention_heads": 4, "num_key_value_heads": 4,
+      "head_dim": 48, "intermediate_size": 144, "vocab_size": 333, "rope_theta": 1e6, "rms_norm_eps": 1e-6,
+      "tie_word_embeddings": False, "max_position_embeddings": 200}, 16, 130),
+]
+
+
+@pytest.mark.parametrize("seed", list(range(6)) + [f"pinned{i}" for i in range(len(PINNED))])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_a_random_configuration(tmp_path, seed, dtype):
     from marin_b200.cache import CacheManager
@@ -35,8 +48,13 @@ def test_a_random_configuration(tmp_path, seed, dtype):
     from marin_b200.kernels import ops
     from marin_b200.parts import Runtime
 
-    rng = random.Random(100 + seed)
-    raw, page, n = draw(rng)
+    if isinstance(seed, str):
+        raw, page, n = PINNED[int(seed[len("pinned"):])]
+        seed = 26
+        rng = random.Random(3)
+    else:
+        rng = random.Random(100 + seed)
+        raw, page, n = draw(rng)
     std = min(0.1, 1.2 / raw["hidden_size"] ** 0.5)              # logits of standard deviation near 1
     folder = make_model_dir(str(tmp_path / "m"), raw, seed=seed, dtype=parse_dtype(dtype), matrix_std=std)
     cfg, w = plain.read_config(folder), plain.read_weights(folder)
