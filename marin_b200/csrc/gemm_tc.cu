@@ -4,14 +4,18 @@
 // (BN = 16..256 tokens per CTA), so that a decode step with a handful of tokens still fills the 128-row
 // datapath and streams every weight exactly once.  Both operands are K-major in global memory (w is
 // [N, K], x is [T, K]) and are brought into shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle,
-// no multicast) through a ring of STAGES buffers guarded by mbarriers; one thread issues the MMAs, whose
-// float32 accumulator lives in tensor memory; four warps read it back with tcgen05.ld and write
-// out[t, n] (32 consecutive n per warp and token: coalesced).
+// no multicast) through a ring of STAGES buffers guarded by mbarriers; one thread issues the MMAs (two, into two
+// accumulators that the epilogue adds, with up to 64 tokens), whose float32 accumulator lives in tensor memory; four
+// warps read it back with tcgen05.ld and write out[t, n] (32 consecutive n per warp and token: coalesced).
 //
 // Split-K: with few tokens and few weight rows there are fewer tiles than SMs, so blockIdx.z cuts K into
-// slices.  Each slice writes its float32 partial tile to scratch memory; the CTA that arrives last at the
-// tile's counter adds the slices in slice order (so the sum does not depend on which CTA was last) and
-// writes the result.  The counter is left at zero for the next launch.
+// slices.  The slices of a tile are the CTAs of one thread-block cluster and add their partial tiles through
+// distributed shared memory, in slice order (gemm_tc_kernel with cluster_reduce); without clusters each slice writes
+// its float32 partial tile to scratch memory and the CTA that arrives last at the tile's counter adds them, again in
+// slice order, and leaves the counter at zero for the next launch.
+//
+// Many tokens: gemm_tc_persistent_kernel, one CTA per SM walking over tiles, or over equal runs of k-blocks
+// (stream-K in groups, see TcStreamK).
 //
 // Every wait on an mbarrier has a time limit; a wait that gives up records a code in *error_flag and the
 // kernel winds down (tensor memory is freed on every path).  The reference's counterpart is its mma.sync
