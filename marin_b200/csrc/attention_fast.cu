@@ -15,6 +15,7 @@
 // Page layout: [page][kv_head][offset in page][HEAD_DIM]; block_table[request][logical page] -> page.
 #include "tc_common.cuh"
 #include "launch.cuh"
+#include <type_traits>
 
 #ifndef HEAD_DIM
 #error "compile with -DHEAD_DIM=<multiple of 16, at most 128>"
@@ -108,7 +109,8 @@ __device__ __forceinline__ float ld_cluster_f32(uint32_t addr, int rank) {
 #endif
 #define DEC_STAGE_KEYS 16
 #ifndef DEC_MAX_CLUSTER
-#define DEC_MAX_CLUSTER 8             // most chunks of one sequence that merge as one thread-block cluster
+#define DEC_MAX_CLUSTER 16            // most chunks of one sequence that merge as one thread-block cluster (more than 8 is
+                                      // a non-portable size: the launcher asks for it and the caller falls back if refused)
 #endif
 #define DEC_Q_BYTES (16 * LDP * 2)
 #define DEC_STAGE_BYTES (2 * DEC_STAGE_KEYS * LDP * 2)          // keys then values
@@ -402,34 +404,40 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attn_decode_split_kernel(
         const int per = (GROUP * D + ranks - 1) / ranks;
         const int i_end = min(GROUP * D, (chunk + 1) * per);
         const uint32_t a_acc = smem_u32(c_acc), a_m = smem_u32(c_m), a_l = smem_u32(c_l);
-        // the chunks' weights 2^(m_c - M) and the inverse of the total sum, once per head (ranks <= 8), then every
+        // the chunks' weights 2^(m_c - M) and the inverse of the total sum, once per head (ranks <= MC), then every
         // output is one weighted sum over the chunks
-        __shared__ float wgt[8 * 8], inv_total[8];                   // [head][chunk], [head]
-        if (threadIdx.x < GROUP) {
-            const int g = threadIdx.x;
-            float mc[8], mm = -INFINITY;
+        __shared__ float wgt[8 * DEC_MAX_CLUSTER], inv_total[8];     // [head][chunk], [head]
+        // (written for 8 and for 16 chunks: the loops are unrolled, and the common small clusters do not pay for the wide ones)
+        auto merge = [&](auto width) {
+            constexpr int MC = decltype(width)::value;
+            if (threadIdx.x < GROUP) {
+                const int g = threadIdx.x;
+                float mc[MC], mm = -INFINITY;
 #pragma unroll
-            for (int c = 0; c < 8; ++c) { mc[c] = c < ranks ? ld_cluster_f32(a_m + g * 4, c) : -INFINITY; mm = fmaxf(mm, mc[c]); }
-            float ll = 0.0f;
+                for (int c = 0; c < MC; ++c) { mc[c] = c < ranks ? ld_cluster_f32(a_m + g * 4, c) : -INFINITY; mm = fmaxf(mm, mc[c]); }
+                float ll = 0.0f;
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                const float f = mc[c] == -INFINITY ? 0.0f : exp2f(mc[c] - mm);
-                wgt[g * 8 + c] = f;
-                if (c < ranks && f != 0.0f) ll = fmaf(ld_cluster_f32(a_l + g * 4, c), f, ll);
+                for (int c = 0; c < MC; ++c) {
+                    const float f = mc[c] == -INFINITY ? 0.0f : exp2f(mc[c] - mm);
+                    wgt[g * MC + c] = f;
+                    if (c < ranks && f != 0.0f) ll = fmaf(ld_cluster_f32(a_l + g * 4, c), f, ll);
+                }
+                inv_total[g] = 1.0f / ll;
             }
-            inv_total[g] = 1.0f / ll;
-        }
-        __syncthreads();
-        for (int idx = chunk * per + threadIdx.x; idx < i_end; idx += DEC_WARPS * 32) {
-            const int g = idx / D;
-            float part[8];
+            __syncthreads();
+            for (int idx = chunk * per + threadIdx.x; idx < i_end; idx += DEC_WARPS * 32) {
+                const int g = idx / D;
+                float part[MC];
 #pragma unroll
-            for (int c = 0; c < 8; ++c) part[c] = (c < ranks && wgt[g * 8 + c] != 0.0f) ? ld_cluster_f32(a_acc + idx * 4, c) : 0.0f;
-            float a = 0.0f;
+                for (int c = 0; c < MC; ++c) part[c] = (c < ranks && wgt[g * MC + c] != 0.0f) ? ld_cluster_f32(a_acc + idx * 4, c) : 0.0f;
+                float a = 0.0f;
 #pragma unroll
-            for (int c = 0; c < 8; ++c) a = fmaf(part[c], wgt[g * 8 + c], a);
-            out[((size_t)r * H + kh * GROUP) * D + idx] = __float2bfloat16_rn(a * inv_total[g]);
-        }
+                for (int c = 0; c < MC; ++c) a = fmaf(part[c], wgt[g * MC + c], a);
+                out[((size_t)r * H + kh * GROUP) * D + idx] = __float2bfloat16_rn(a * inv_total[g]);
+            }
+        };
+        if (DEC_MAX_CLUSTER <= 8 || ranks <= 8) merge(std::integral_constant<int, DEC_MAX_CLUSTER < 8 ? DEC_MAX_CLUSTER : 8>{});
+        else merge(std::integral_constant<int, DEC_MAX_CLUSTER>{});
         // nobody leaves while a peer may still read its partial result (nothing is published: a relaxed arrival)
         asm volatile("barrier.cluster.arrive.relaxed.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
         return;
@@ -728,6 +736,41 @@ static int decode_map(CUtensorMap* map, const void* base, uint64_t rows) {
     return rc == CUDA_SUCCESS ? 0 : 1000 + (int)rc;
 }
 
+// Clusters of more than 8 CTAs are a non-portable size: the kernels are allowed it once, and whether the device can
+// place such a cluster at all (16 CTAs with this kernel's shared memory inside one GPC) is asked, not assumed.
+template <bool TMA>
+static bool decode_wide_clusters() {
+    static int state = -1;
+    if (state < 0) {
+        state = 0;
+        const int smem = TMA ? DEC_TMA_SMEM : DEC_SMEM;
+        if (DEC_MAX_CLUSTER > 8 &&
+            cudaFuncSetAttribute(attn_decode_split_kernel<TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) == cudaSuccess &&
+            cudaFuncSetAttribute(attn_decode_split_kernel<TMA>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(DEC_MAX_CLUSTER, 1, 1);
+            cfg.blockDim = dim3(DEC_WARPS * 32);
+            cfg.dynamicSmemBytes = smem;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = DEC_MAX_CLUSTER;
+            attr[0].val.clusterDim.y = 1;
+            attr[0].val.clusterDim.z = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            int clusters = 0;
+            if (cudaOccupancyMaxActiveClusters(&clusters, attn_decode_split_kernel<TMA>, &cfg) == cudaSuccess && clusters >= 1) state = 1;
+            else (void)cudaGetLastError();
+        }
+    }
+    return state == 1;
+}
+
+// The most chunks of a sequence that the decode kernel merges as one cluster on this device (8 or DEC_MAX_CLUSTER).
+MB_API int mb_attn_decode_max_cluster() {
+    return (DEC_TMA ? decode_wide_clusters<true>() : decode_wide_clusters<false>()) ? DEC_MAX_CLUSTER : (DEC_MAX_CLUSTER < 8 ? DEC_MAX_CLUSTER : 8);
+}
+
 MB_API int mb_attn_decode(const void* q, const void* k_cache, const void* v_cache, void* out, const int* block_table,
                           int max_pages, const int* seq_lens, int requests, int K, int page_size, long long cache_pages,
                           float scale, int window, float* part_acc, float* part_ml, int* counters, int max_chunks,
@@ -737,12 +780,14 @@ MB_API int mb_attn_decode(const void* q, const void* k_cache, const void* v_cach
     const int page_shift = page_shift_of(page_size);
     if (page_shift < 0) return MB_ERR_BAD_SIZE;
     dim3 grid(max_chunks, K, requests);
-    // up to eight chunks: they are one cluster and merge through distributed shared memory, without scratch
-    const int cluster_merge = (max_chunks >= 2 && max_chunks <= DEC_MAX_CLUSTER) ? 1 : 0;
-    const int cluster = cluster_merge ? -max_chunks : 0;
     const uint64_t rows = (uint64_t)cache_pages * K * page_size;
     const bool tma = DEC_TMA && page_shift >= 4 && error_flag != nullptr && rows > 0 && rows < (1ull << 31) &&
                      ((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0;
+    // a few chunks (up to 8, or 16 where the device places such clusters): they are one cluster and merge through
+    // distributed shared memory, without scratch
+    const int widest = max_chunks <= 8 ? 8 : ((tma ? decode_wide_clusters<true>() : decode_wide_clusters<false>()) ? DEC_MAX_CLUSTER : 8);
+    const int cluster_merge = (max_chunks >= 2 && max_chunks <= widest) ? 1 : 0;
+    const int cluster = cluster_merge ? -max_chunks : 0;
     CUtensorMap mk = {}, mv = {};
     if (tma) {
         int rc = decode_map(&mk, k_cache, rows);

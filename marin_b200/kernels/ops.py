@@ -369,14 +369,15 @@ use_fast_attention = True
 use_tc_attention = True
 _attn_scratch = {}
 DECODE_SPLITS = (4096, 2048, 1024, 512, 256, 128, 64)      # keys per CTA the split-KV decode kernel may be given
-DECODE_CLUSTER_CHUNKS = 8                                   # most chunks the kernel merges as one cluster
+DECODE_CLUSTER_CHUNKS = 8                                   # most chunks the kernel merges as one cluster (see _attention_lib)
+_cluster_asked = set()
 
 
 def decode_split(requests: int, kv_heads: int, longest: int):
     """Keys per CTA and chunks per sequence for decode attention over sequences of up to ``longest`` keys.
 
-    Up to eight chunks of one (request, kv head) run as one thread-block cluster and merge through distributed shared
-    memory; that is preferred, with chunks as long as still give 256 CTAs (measured on B200 at batch 1, 8 and 64 and
+    Up to eight chunks of one (request, kv head), sixteen where the device allows (``DECODE_CLUSTER_CHUNKS``), run as
+    one thread-block cluster and merge through distributed shared memory; that is preferred, with chunks as long as still give 256 CTAs (measured on B200 at batch 1, 8 and 64 and
     contexts 1024 and 4096).  A few long sequences would leave most SMs idle that way: they get more chunks, merged
     through scratch memory, as long as still give 128 CTAs."""
     pairs = requests * kv_heads
@@ -402,8 +403,16 @@ def decode_split(requests: int, kv_heads: int, longest: int):
 
 
 def _attention_lib(d: int, group: int):
-    """The fast attention kernels are compiled for one head size and one group size, at first use."""
-    return build.load(f"mb_attention_fast_d{d}_g{group}", *build.attention_job(d, group))
+    """The fast attention kernels are compiled for one head size and one group size, at first use.  A library also
+    says how many chunks the device lets the decode kernel merge as one cluster (8, or 16 where clusters of a
+    non-portable size can be placed): ``decode_split`` plans with the smallest answer so far."""
+    global DECODE_CLUSTER_CHUNKS, _cluster_asked
+    lib = build.load(f"mb_attention_fast_d{d}_g{group}", *build.attention_job(d, group))
+    if (d, group) not in _cluster_asked and torch.cuda.is_available():
+        widest = int(lib.mb_attn_decode_max_cluster())
+        DECODE_CLUSTER_CHUNKS = widest if not _cluster_asked else min(DECODE_CLUSTER_CHUNKS, widest)
+        _cluster_asked.add((d, group))
+    return lib
 
 
 def fast_attention_supported(dtype, H: int, K: int, d: int) -> bool:

@@ -506,16 +506,37 @@ def test_attention_long_contexts_bf16(ops, H, K, d, page, window):
     torch.testing.assert_close(out.float(), want.float(), rtol=2e-2, atol=2e-2)
 
 
-@pytest.mark.parametrize("H,K,d,page,split", [(32, 8, 128, 16, 64), (8, 2, 64, 16, 128), (6, 3, 48, 8, 64), (4, 4, 128, 32, 64)])
+@pytest.mark.parametrize("H,K,d,page,split,longest", [(32, 8, 128, 16, 128, 1500), (8, 2, 64, 16, 64, 1000), (4, 4, 48, 8, 64, 1023),
+                                                      (5, 1, 128, 64, 64, 600)])
+def test_attention_decode_in_clusters_of_more_than_eight(ops, H, K, d, page, split, longest):
+    """Nine to sixteen chunks of a sequence are still one cluster where the device places clusters of that (non-portable)
+    size, and merge through scratch memory where it does not: either way the result is the reference's."""
+    g = torch.Generator(device=DEV).manual_seed(24)
+    lens_new = [(longest, 1), (70, 1), (0, 1), (longest // 2, 1), (longest - 300, 1)]
+    pages = sum(-(-(c + n) // page) for c, n in lens_new) + 2
+    q, kc, vc, table, ctx = paged_case(g, torch.bfloat16, lens_new, H, K, d, page, pages)
+    chunks = -(-(longest + 1) // split)
+    assert 8 < chunks <= 16
+    ctx.attn_split = (split, chunks)
+    want = torch.empty_like(q)
+    ref.attention(q, kc, vc, want, ctx, table, H, K, d, 1.0 / math.sqrt(d), 0)
+    for _ in range(2):
+        out = torch.full_like(q, float("nan"))
+        ops.attention(q, kc, vc, out, ctx, table, H, K, d, 1.0 / math.sqrt(d), 0)
+        ops.check_device_errors()
+        torch.testing.assert_close(out.float(), want.float(), rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("H,K,d,page,split", [(32, 8, 128, 16, 64), (8, 2, 64, 16, 64), (6, 3, 48, 8, 64), (4, 4, 128, 32, 64)])
 def test_attention_decode_with_more_chunks_than_a_cluster_holds(ops, H, K, d, page, split):
-    """Sequences cut into more than eight chunks merge through scratch memory (the last CTA combines them) instead of
-    through a cluster; run twice: the arrival counters must be back at zero."""
+    """Sequences cut into more chunks than a cluster holds merge through scratch memory (the last CTA combines them);
+    run twice: the arrival counters must be back at zero."""
     g = torch.Generator(device=DEV).manual_seed(23)
     lens_new = [(1500, 1), (70, 1), (0, 1), (1023, 1), (640, 1)]
     pages = sum(-(-(c + n) // page) for c, n in lens_new) + 2
     q, kc, vc, table, ctx = paged_case(g, torch.bfloat16, lens_new, H, K, d, page, pages)
     chunks = -(-1501 // split)
-    assert chunks > 8
+    assert chunks > 16
     ctx.attn_split = (split, chunks)
     want = torch.empty_like(q)
     ref.attention(q, kc, vc, want, ctx, table, H, K, d, 1.0 / math.sqrt(d), 0)
