@@ -506,6 +506,64 @@ def test_attention_long_contexts_bf16(ops, H, K, d, page, window):
     torch.testing.assert_close(out.float(), want.float(), rtol=2e-2, atol=2e-2)
 
 
+@pytest.mark.parametrize("H,K,d,page", [(2, 2, 112, 64), (4, 4, 48, 16), (1, 1, 128, 16), (3, 3, 64, 16), (8, 2, 80, 8), (6, 2, 96, 32),
+                                        (32, 8, 128, 16)])
+def test_decode_chain_replayed_from_a_graph(ops, H, K, d, page):
+    """The kernel that writes the new token's queries, keys and values and the decode attention behind it, captured
+    in one graph and replayed over several positions.  Launched one by one the host's gaps keep kernels apart;
+    replayed from a graph the attention really starts while its producer runs, and anything it reads too early (it
+    asks for the older keys before it waits) is stale: the queries, keys and values change with every replay."""
+    g = torch.Generator(device=DEV).manual_seed(41)
+    B, first, steps = 3, [130, 17, 63], 7
+    maxb = -(-(max(first) + steps + 1) // page) + 1
+    pages = B * maxb + 2
+    perm = torch.randperm(pages, generator=g, device=DEV)[: B * maxb].to(torch.int32).view(B, maxb)
+    kc = torch.randn(pages, K, page, d, device=DEV, generator=g).to(torch.bfloat16)
+    vc = torch.randn(pages, K, page, d, device=DEV, generator=g).to(torch.bfloat16)
+    qw, kw = (1 + 0.1 * torch.randn(d, device=DEV, generator=g) for _ in range(2))
+    inv_freq = (1e4 ** (-torch.arange(0, d, 2, device=DEV).float() / d)).contiguous()
+    qkv = torch.zeros(B, (H + 2 * K) * d, device=DEV, dtype=torch.bfloat16)
+    q = torch.zeros(B, H * d, device=DEV, dtype=torch.bfloat16)
+    out = torch.zeros_like(q)
+    positions = torch.zeros(B, dtype=torch.int32, device=DEV)
+    slots = torch.zeros(B, dtype=torch.int32, device=DEV)
+    ctx = SimpleNamespace(positions=positions, req_index=torch.arange(B, dtype=torch.int32, device=DEV),
+                          cu_tokens=torch.arange(B + 1, dtype=torch.int32, device=DEV), seq_lens=torch.zeros(B, dtype=torch.int32, device=DEV),
+                          num_tokens=B, num_requests=B, num_decode=B, max_query_len=1, max_seq_len=max(first) + steps + 1)
+    ctx.attn_split = ops.decode_split(B, K, 256)
+
+    def chain():
+        ops.qk_norm_rope_write(qkv, q, qw, kw, 1e-6, positions, inv_freq, d, False, slots, kc, vc, H, K, d)
+        ops.attention(q, kc, vc, out, ctx, perm, H, K, d, 1.0 / math.sqrt(d), 0)
+
+    def set_step(i):
+        pos = torch.tensor([f + i for f in first], dtype=torch.int32, device=DEV)
+        positions.copy_(pos)
+        ctx.seq_lens.copy_(pos + 1)
+        page_of = perm[torch.arange(B, device=DEV), (pos // page).long()]
+        slots.copy_(page_of * page + pos % page)
+        qkv.copy_(torch.randn(qkv.shape, device=DEV, generator=g).to(torch.bfloat16))
+
+    set_step(0)
+    chain()                                              # builds what is needed before the capture
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        chain()
+    for i in range(1, steps):
+        set_step(i)
+        graph.replay()
+        torch.cuda.synchronize()
+        ops.check_device_errors()
+        want_q, want = torch.empty_like(q), torch.empty_like(out)
+        kc2, vc2 = kc.clone(), vc.clone()
+        ref.qk_norm_rope_write(qkv, want_q, qw, kw, 1e-6, positions, inv_freq, d, False, slots, kc2, vc2, H, K, d)
+        torch.testing.assert_close(q.float(), want_q.float(), rtol=2e-2, atol=2e-2)
+        torch.testing.assert_close(kc.float(), kc2.float(), rtol=2e-2, atol=2e-2)
+        ref.attention(want_q, kc2, vc2, want, ctx, perm, H, K, d, 1.0 / math.sqrt(d), 0)
+        torch.testing.assert_close(out.float(), want.float(), rtol=3e-2, atol=3e-2, msg=lambda m: f"replay {i}: {m}")
+
+
 @pytest.mark.parametrize("H,K,d,page,split,longest", [(32, 8, 128, 16, 128, 1500), (8, 2, 64, 16, 64, 1000), (4, 4, 48, 8, 64, 1023),
                                                       (5, 1, 128, 64, 64, 600)])
 def test_attention_decode_in_clusters_of_more_than_eight(ops, H, K, d, page, split, longest):
