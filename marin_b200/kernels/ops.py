@@ -126,6 +126,8 @@ def check_device_errors(device=None) -> None:
         code = int(s["error"].item())
         if code != 0:
             s["error"].zero_()
+            s["counters"].zero_()                 # a kernel that gave up may have left its counters and flags set
+            s["parked_flags"].zero_()
             raise KernelError(f"a tensor-core kernel's wait on an mbarrier gave up (code {code})")
 
 
