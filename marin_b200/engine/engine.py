@@ -120,6 +120,7 @@ class Engine:
         self._requests: Dict[Hashable, Request] = {}
         self._samplers: Dict[Hashable, Sampler] = {}
         self._next_id = 0
+        self._steps_unchecked = 0
 
     # ---- requests, one step at a time ------------------------------------------------------------------
     def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None,
@@ -152,7 +153,19 @@ class Engine:
             # again, one position on; its inputs are packed now, while the GPU is busy, instead of after the wait below
             self.runner.prepare_next(entries)
         sampled = self._sample(plan, logits, self._samplers, self.config.vocab_size)
+        self._steps_unchecked += 1
+        if self._steps_unchecked >= self.CHECK_EVERY:
+            self.check_device()
         return self.scheduler.update(plan, sampled)
+
+    #: a kernel whose bounded wait gave up leaves a code on the device; it is read every so many steps (one small copy)
+    #: and when a generation ends, and raises ``KernelError``
+    CHECK_EVERY = 32
+
+    def check_device(self) -> None:
+        self._steps_unchecked = 0
+        if self.rt.device.type == "cuda":
+            ops.check_device_errors()
 
     def result(self, req_id: Hashable) -> Generation:
         r = self._requests[req_id]
@@ -183,6 +196,7 @@ class Engine:
             if on_token is not None:
                 for rid, token in emitted:
                     on_token(rid, token)
+        self.check_device()
         out = [self.result(i) for i in ids]
         for i in ids:
             self.forget(i)
