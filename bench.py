@@ -327,6 +327,8 @@ def main() -> int:
     }
     if e2e is not None:
         line["e2e"] = e2e
+    from marin_b200.kernels import ops
+    ops.check_device_errors()            # a kernel whose bounded wait gave up would make the numbers above worthless: raise
     print(json.dumps(line))
     return 0
 
