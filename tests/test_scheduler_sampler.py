@@ -15,8 +15,20 @@ def sched(num_pages=16, page=4, max_batch=3, budget=8, ctx=32):
     return Scheduler(cache, max_batch, budget, ctx), cache
 
 
-def run(s, cache, next_token=lambda r: len(r.tokens) % 50 + 1, max_steps=500):
-    """Drives the scheduler with a fake step that only does the cache bookkeeping."""
+def reserve_ahead(cache, plan, ctx) -> bool:
+    """What the engine does while a decode step runs: the same requests' next token gets its pages now, all or none."""
+    import ctypes
+
+    n = len(plan)
+    handles = np.fromiter((cache.requests[p.request.req_id].handle for p in plan), np.int64, n)
+    counts = np.ones(n, np.int32)
+    info = (ctypes.c_int * 2)()
+    return cache._lib.mbh_step_reserve(cache._core(), n, handles.ctypes.data, counts.ctypes.data, ctx, info) == 0
+
+
+def run(s, cache, next_token=lambda r: len(r.tokens) % 50 + 1, max_steps=500, ahead_ctx=0):
+    """Drives the scheduler with a fake step that only does the cache bookkeeping.  ``ahead_ctx`` > 0: after every
+    step in which all requests decode, pages for their next tokens are taken ahead (context capacity ``ahead_ctx``)."""
     log = []
     for _ in range(max_steps):
         if not s.has_work():
@@ -30,6 +42,9 @@ def run(s, cache, next_token=lambda r: len(r.tokens) % 50 + 1, max_steps=500):
             cache.commit(p.request.req_id, new_len)
         cache.check()
         log.append([(p.request.req_id, len(p.tokens), p.sample) for p in plan])
+        if ahead_ctx and all(p.sample and len(p.tokens) == 1 for p in plan):
+            reserve_ahead(cache, plan, ahead_ctx)
+            cache.check()
         s.update(plan, {p.request.req_id: next_token(p.request) for p in plan if p.sample})
     assert not s.has_work()
     return log
@@ -127,6 +142,26 @@ def test_random_arrivals_finish_everything():
     for r in s.finished:
         assert len(r.output) == want[r.req_id], (r.req_id, r.stop)
     assert cache.free_pages() == [10]
+
+
+@pytest.mark.parametrize("pages", [6, 7, 10, 40])
+def test_pages_taken_ahead_for_the_next_decode_step_change_no_outcome(pages):
+    """The engine reserves the next decode step's pages while the current one runs.  Whatever the pool (so tight that
+    requests are preempted, or roomy), every request ends as it does without that, with the same tokens, and every
+    page comes back."""
+    outcomes = []
+    for ahead in (0, 32):
+        rng = random.Random(11)
+        s, cache = sched(num_pages=pages, budget=9, max_batch=3, ctx=32)
+        for i in range(10):
+            n, m = rng.randint(1, 18), rng.randint(1, 12)
+            stop = (7,) if i % 3 == 0 else ()
+            s.add(Request(i, [rng.randint(1, 40) for _ in range(n)], greedy(m, stop)))
+        run(s, cache, next_token=lambda r: (len(r.prompt) * 7 + len(r.output) * 3) % 11 + 1, max_steps=3000, ahead_ctx=ahead)
+        assert cache.free_pages() == [pages] and not cache.requests
+        outcomes.append(sorted((r.req_id, r.stop, tuple(r.output)) for r in s.finished))
+    assert outcomes[0] == outcomes[1]
+    assert len(outcomes[0]) == 10
 
 
 # ---- sampler ---------------------------------------------------------------------------------------------
