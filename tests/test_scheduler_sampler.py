@@ -164,6 +164,55 @@ def test_pages_taken_ahead_for_the_next_decode_step_change_no_outcome(pages):
     assert len(outcomes[0]) == 10
 
 
+@pytest.mark.parametrize("seed", range(8))
+def test_requests_added_and_cancelled_at_random_times_with_and_without_pages_taken_ahead(seed):
+    """A random programme of arrivals and cancellations over a tight pool, run twice: the second time pages for the next
+    decode step are taken ahead after every all-decode step, as the engine does.  The accounting holds at every step,
+    every page comes back, and every request ends the same way with the same tokens."""
+    rng = random.Random(100 + seed)
+    pages, ctx = rng.choice([5, 8, 12, 30]), 40
+    programme = []                                            # (step, "add", id, prompt, max_tokens, stop) / (step, "cancel", id)
+    for i in range(14):
+        at = rng.randint(0, 40)
+        programme.append((at, "add", i, [rng.randint(1, 30) for _ in range(rng.randint(1, 22))], rng.randint(1, 14),
+                          (5,) if rng.random() < 0.3 else ()))
+        if rng.random() < 0.35:
+            programme.append((at + rng.randint(1, 12), "cancel", i))
+    outcomes = []
+    for ahead in (False, True):
+        s, cache = sched(num_pages=pages, page=4, max_batch=3, budget=10, ctx=ctx)
+        known = {}
+        for step in range(400):
+            for ev in programme:
+                if ev[0] != step:
+                    continue
+                if ev[1] == "add":
+                    known[ev[2]] = Request(ev[2], ev[3], greedy(ev[4], ev[5]))
+                    s.add(known[ev[2]])
+                elif ev[2] in known:
+                    s.cancel(ev[2])
+            if not s.has_work():
+                if step > 60:
+                    break
+                continue
+            plan = s.schedule()
+            for p in plan:
+                new_len = p.request.computed + len(p.tokens)
+                cache.reserve(p.request.req_id, new_len)
+                cache.commit(p.request.req_id, new_len)
+            cache.check()
+            if ahead and plan and all(p.sample and len(p.tokens) == 1 for p in plan):
+                reserve_ahead(cache, plan, ctx)
+                cache.check()
+            if plan:
+                s.update(plan, {p.request.req_id: (len(p.request.prompt) * 5 + len(p.request.output) * 3 + p.request.req_id) % 9 + 1
+                                for p in plan if p.sample})
+        assert not s.has_work()
+        assert cache.free_pages() == [pages] and not cache.requests
+        outcomes.append(sorted((r.req_id, r.stop, tuple(r.output)) for r in s.finished))
+    assert outcomes[0] == outcomes[1] and len(outcomes[0]) == 14
+
+
 # ---- sampler ---------------------------------------------------------------------------------------------
 
 def plain_distribution(logits, temperature, top_k, top_p):
