@@ -99,29 +99,17 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-def model_bytes_and_flops(engine, tokens):
-    """Bytes of every weight a decode step reads once, and the flops of a `tokens`-long prefill."""
-    import torch
-
-    cfg = engine.config
-    weight_bytes, matrix_params = 0, 0
-    for block in engine.model.blocks:
-        for t in (block.mixer.w_qkv, block.mixer.w_o, block.feedforward.w_gate_up, block.feedforward.w_down):
-            weight_bytes += t.numel() * t.element_size()
-            matrix_params += t.numel()
-        for t in (block.norm1.weight, block.norm2.weight, block.mixer.q_weight, block.mixer.k_weight):
-            weight_bytes += t.numel() * t.element_size()
-    head = engine.model.head.weight
-    weight_bytes += head.numel() * head.element_size() + engine.model.final_norm.weight.numel() * 4
-    layers = len(engine.model.blocks)
-    attn = 2.0 * tokens * tokens * cfg.head_dim * cfg.num_attention_heads * layers
-    flops = 2.0 * tokens * matrix_params + 2.0 * head.numel() + attn
-    return weight_bytes, flops
+def model_bytes_and_flops(engine, batch, tokens):
+    """Bytes of weights a decode step of `batch` tokens reads (what the model's parts say they read), and the flops
+    of a `tokens`-long prompt with one row of logits (causal: every token looks at itself and what came before)."""
+    dtype = engine.rt.dtype
+    pairs = tokens * (tokens + 1) // 2
+    return engine.model.bytes_read(batch, dtype), engine.model.flops(tokens, pairs, 1)
 
 
 def kv_bytes_per_token(engine):
-    cfg = engine.config
-    return len(engine.model.blocks) * 2 * cfg.num_key_value_heads * cfg.head_dim * 2
+    """Bytes one cached position holds over all layers (what a decoded token reads per position of its sequence)."""
+    return engine.model.cache_bytes_read(1, engine.rt.dtype)
 
 
 def fill_cache(engine, seed=1):
@@ -153,12 +141,13 @@ def decode_device(engine, batch, steps, warmup, context):
         engine.cache.commit(rid, start_len)
     vocab = engine.config.vocab_size
     tokens = torch.randint(0, vocab, (batch,), dtype=torch.int32).tolist()
-    out = torch.empty(batch, device=engine.rt.device, dtype=torch.int32)
+    out = runner.scratch.ids(batch)
 
     def one_step(tokens):
         logits = runner.step([StepEntry(rid, [tok], [0]) for rid, tok in zip(ids, tokens)])
         if runner.greedy_ids is None:                       # a replayed graph has found the largest logits already
-            ops.argmax(logits, vocab, out)
+            with ops.using(runner.scratch):
+                ops.argmax(logits, vocab, out)
 
     for _ in range(warmup):
         one_step(tokens)
@@ -280,7 +269,7 @@ def main() -> int:
     engine = Engine(config=cfg, seed=0, dtype="bfloat16", ctx=CONTEXT, page_size=PAGE, max_batch=max_batch,
                     token_budget=PREFILL_TOKENS)
     fill_cache(engine)
-    weight_bytes, prefill_flops = model_bytes_and_flops(engine, PREFILL_TOKENS)
+    weight_bytes, prefill_flops = model_bytes_and_flops(engine, args.batch, PREFILL_TOKENS)
     kv_tok = kv_bytes_per_token(engine)
 
     clocks = ClockSampler()
@@ -303,7 +292,7 @@ def main() -> int:
         for b in (1, 64):
             r = decode_device(engine, b, min(args.steps, 32), 3, CONTEXT)
             points[f"decode_b{b}"] = round(r["tok_s"], 1)
-            bytes_b = weight_bytes + b * r["mean_context"] * kv_tok
+            bytes_b = model_bytes_and_flops(engine, b, PREFILL_TOKENS)[0] + b * r["mean_context"] * kv_tok
             points[f"decode_b{b}_hbm_frac"] = round(bytes_b / (r["ms_per_step"] / 1e3) / 1e9 / pk["hbm_gbs"], 4)
 
     e2e = None
@@ -327,8 +316,7 @@ def main() -> int:
     }
     if e2e is not None:
         line["e2e"] = e2e
-    from marin_b200.kernels import ops
-    ops.check_device_errors()            # a kernel whose bounded wait gave up would make the numbers above worthless: raise
+    engine.check_device()                # a kernel whose bounded wait gave up would make the numbers above worthless: raise
     print(json.dumps(line))
     return 0
 

@@ -104,7 +104,7 @@ class PagedView:
 class StateView:
     """What a stateful mixer sees: ``state[slot]`` for each of the step's requests."""
 
-    state: torch.Tensor           # [max_requests, *shape]
+    state: torch.Tensor           # [max_requests + 1, *shape]; the last slot is a spare for rows that pad a batch
     slots: torch.Tensor           # int32 [requests]
     owner: bool = True
 
@@ -164,16 +164,20 @@ class CacheManager:
 
     # ---- device memory -------------------------------------------------------------------------
     def bytes_per_page(self, dtype: torch.dtype) -> int:
-        size = torch.empty(0, dtype=dtype).element_size()
-        return sum(2 * len(g.entries) * g.need.kv_heads * self.page_size * g.need.head_dim * size for g in self.groups)
+        """Bytes one page takes in every group together (``num_pages`` of them are allocated per group)."""
+        return sum(len(g.entries) * self.page_size * g.need.bytes_per_token(dtype) for g in self.groups)
+
+    def state_bytes(self) -> int:
+        return sum((self.max_requests + 1) * need.bytes() for need in self.state_needs.values())
 
     def allocate(self, device, dtype: torch.dtype) -> None:
         for g in self.groups:
             shape = (len(g.entries), self.num_pages, g.need.kv_heads, self.page_size, g.need.head_dim)
             g.k = torch.zeros(shape, device=device, dtype=dtype)
             g.v = torch.zeros(shape, device=device, dtype=dtype)
+        # one slot more than there can be requests: the rows that pad a captured batch read and write the spare slot
         for i, need in self.state_needs.items():
-            self.state[i] = torch.zeros((self.max_requests, *need.shape), device=device, dtype=need.dtype)
+            self.state[i] = torch.zeros((self.max_requests + 1, *need.shape), device=device, dtype=need.dtype)
 
     # ---- requests ------------------------------------------------------------------------------
     def admit(self, req_id: Hashable) -> RequestCache:

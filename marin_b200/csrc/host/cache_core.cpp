@@ -165,8 +165,8 @@ MBH_API int mbh_step_commit(void* c, int n, const int64_t* handles, const int* c
 //   step [R], state slots [R], rows whose logits are wanted [W], block tables [G][R][max_pages], and for each group
 //   where each new token is written [G][T] (page * page_size + offset, -1: nowhere).
 // Entries with a single token come first (the decode kernels take rows 0 .. num_decode - 1), otherwise in the order
-// given.  pad_to > 0 (single-token steps only) pads to pad_to rows that stand for empty requests, so that a captured
-// graph sees one shape.  info receives T, R, W, the number of single-token rows, the longest entry and the longest
+// given.  pad_to > 0 (single-token steps only) pads to pad_to rows that stand for empty requests (length 0, state slot
+// max_requests: a spare slot no request ever holds), so that a captured graph sees one shape.  info receives T, R, W, the number of single-token rows, the longest entry and the longest
 // sequence; spans[row] = (entry, first token, count, first position, slot).  Returns the number of ints written or a
 // negative code.
 MBH_API int mbh_pack_step(void* c, int n, const int64_t* handles, const int* counts, const int* tokens, const int* want_counts,
@@ -249,6 +249,8 @@ MBH_API int mbh_pack_step(void* c, int n, const int64_t* handles, const int* cou
         spans[row * 5 + 4] = r->slot;
         at += cnt;
     }
+    // rows that pad a captured batch stand for empty requests: length 0, and the spare state slot behind the real ones
+    for (int row = n; row < R; ++row) slots[row] = cache->slots().size();
     if (pad_to <= 0) {
         int w = 0;
         for (int i = 0; i < n; ++i)

@@ -249,11 +249,23 @@ bool read_header(const char* path, Header* out, std::string* err) {
         entry.end = offsets->items[1].integer;
         const int width = dtype_bytes(entry.dtype);
         if (width == 0) { *err = where + ": tensor `" + name + "` has unsupported dtype " + entry.dtype; return false; }
+        // the number of elements, refusing a product that would not fit: no tensor holds more elements than the file
+        // has bytes, so a size that pushes the product past that is a lie (and would overflow if multiplied on)
         long long count = 1;
+        bool empty = false;
         for (long long s : entry.shape) {
             if (s < 0) { *err = where + ": tensor `" + name + "` has a negative size"; return false; }
-            count *= s;
+            if (s == 0) empty = true;
         }
+        if (empty) count = 0;
+        else
+            for (long long s : entry.shape) {
+                if (count > (data_bytes > 0 ? data_bytes : 0) / s) {
+                    *err = where + ": tensor `" + name + "`: its shape holds more elements than the file has bytes";
+                    return false;
+                }
+                count *= s;
+            }
         if (entry.begin < 0 || entry.end < entry.begin || entry.end - entry.begin != count * width) {
             *err = where + ": tensor `" + name + "`: offsets " + std::to_string(entry.begin) + ".." + std::to_string(entry.end) +
                    " do not match its shape and dtype " + entry.dtype;

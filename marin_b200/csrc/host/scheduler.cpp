@@ -17,7 +17,8 @@ using namespace mbh;
 
 namespace {
 
-enum Stop { STOP_NONE = -1, STOP_MAX_TOKENS = 0, STOP_END_OF_TEXT = 1, STOP_CONTEXT_FULL = 2, STOP_CANCELLED = 3, STOP_OUT_OF_PAGES = 4 };
+enum Stop { STOP_NONE = -1, STOP_MAX_TOKENS = 0, STOP_END_OF_TEXT = 1, STOP_CONTEXT_FULL = 2, STOP_CANCELLED = 3, STOP_OUT_OF_PAGES = 4,
+            STOP_NON_FINITE = 5 };
 enum Where { WAITING = 0, RUNNING = 1, FINISHED = 2 };
 enum { MBS_EMPTY_PROMPT = 20, MBS_PROMPT_TOO_LONG = 21, MBS_UNKNOWN = 22 };
 
@@ -157,7 +158,8 @@ class Scheduler {
     }
 
     // ---- after the step -------------------------------------------------------------------------------------------
-    // tokens[k] is the token sampled for the k-th plan item that asked for one; emitted receives (id, token) pairs.
+    // tokens[k] is the token sampled for the k-th plan item that asked for one (negative: its logits were not finite, the
+    // request ends with STOP_NON_FINITE and emits nothing); emitted receives (id, token) pairs.
     int update(const int* tokens, int n_tokens, int64_t* emitted_ids, int* emitted_tokens) {
         membership_changed_ = false;
         int k = 0, out = 0;
@@ -169,6 +171,10 @@ class Scheduler {
             if (k >= n_tokens) return -MBH_BAD_ARG;
             const int token = tokens[k++];
             if (!live) continue;
+            if (token < 0) {                                        // the sampler refused the row: its logits were not finite
+                finish(*r, STOP_NON_FINITE);
+                continue;
+            }
             if (std::find(r->stop_tokens.begin(), r->stop_tokens.end(), token) != r->stop_tokens.end()) {
                 finish(*r, STOP_END_OF_TEXT);                       // the stop token is not emitted
                 continue;

@@ -1,18 +1,21 @@
 // Sampling on the device.  arg-max: the largest logit among the first `usable`, the lowest id among
 // equals (the reference's greedy rule, crates/sampler/src/lib.rs:40-48).  A row is shared by several blocks; each
 // folds its best (value, id) into one 64-bit key per row with atomicMax, and the block that arrives last writes
-// the id and clears the row's key and counter for the next launch.  NaN is never chosen; a row without any
-// comparable value gives id 0.
+// the id and clears the row's key and counter for the next launch.
+//
+// A logit that is NaN or infinite among the usable ones is an error, as in the reference (crates/sampler/src/lib.rs:
+// 135-137): both kernels write the id -1 for such a row.  report[0] receives the code another kernel left in
+// `error_flag` when one of its bounded waits gave up (untouched otherwise), so that the host learns of both with the
+// ids it reads anyway; the host clears it after it has seen a non-zero value.
 #include "common.cuh"
 #include "launch.cuh"
 #include <limits.h>
 
 #define AM_THREADS 512
-#define AM_MAX_ROWS 4096
 
-// Scratch of the arg-max kernel, zero between launches.  One launch at a time may use it (the engine has one stream).
-static __device__ unsigned long long am_keys[AM_MAX_ROWS];
-static __device__ int am_count[AM_MAX_ROWS];
+__device__ __forceinline__ bool not_finite(float x) { return !(fabsf(x) <= 3.402823466e+38f); }
+
+#define AM_BAD_ROW 0xffffffffffffffffull      // no key of a value that can win looks like this (its high word would be a NaN's)
 
 // Larger value first, then lower id: the value's bits made monotonic in the high word, the inverted id in the low.
 __device__ __forceinline__ unsigned long long am_key(float v, int idx) {
@@ -22,8 +25,10 @@ __device__ __forceinline__ unsigned long long am_key(float v, int idx) {
     return ((unsigned long long)b << 32) | (unsigned long long)(0xffffffffu - (unsigned int)idx);
 }
 
+// keys, count: one entry per row of this launch, zero between launches (the caller's scratch memory).
 __global__ void __launch_bounds__(AM_THREADS) argmax_kernel(const float* __restrict__ logits, int vocab, int usable,
-                                                            int per_block, int* __restrict__ out) {
+                                                            int per_block, int* __restrict__ out, unsigned long long* keys,
+                                                            int* count, int* report, const int* error_flag) {
     PDL_ENTER();
     logits = pdl_fresh(logits);
     __shared__ float best_v[AM_THREADS / 32];
@@ -33,9 +38,16 @@ __global__ void __launch_bounds__(AM_THREADS) argmax_kernel(const float* __restr
     const int begin = blockIdx.x * per_block, end = min(usable, begin + per_block);
     float v = -INFINITY;
     int idx = 0x7fffffff;
+    bool bad = false;
     for (int i = begin + threadIdx.x; i < end; i += AM_THREADS) {
         const float x = row[i];
+        bad |= not_finite(x);
         if (x > v || (x == v && i < idx)) { v = x; idx = i; }
+    }
+    if (__any_sync(0xffffffffu, bad) && (threadIdx.x & 31) == 0) atomicMax(&keys[r], AM_BAD_ROW);
+    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0 && report != nullptr && error_flag != nullptr) {
+        const int code = *(const volatile int*)error_flag;   // every earlier kernel of the stream has ended
+        if (code != 0) report[0] = code;
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -56,30 +68,34 @@ __global__ void __launch_bounds__(AM_THREADS) argmax_kernel(const float* __restr
             if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; }
         }
         if (lane == 0) {
-            if (idx != 0x7fffffff) atomicMax(&am_keys[r], am_key(v, idx));
+            if (idx != 0x7fffffff) atomicMax(&keys[r], am_key(v, idx));
             __threadfence();
-            if (atomicAdd(&am_count[r], 1) == (int)gridDim.x - 1) {
+            if (atomicAdd(&count[r], 1) == (int)gridDim.x - 1) {
                 __threadfence();
-                const unsigned long long key = atomicExch(&am_keys[r], 0ull);
-                am_count[r] = 0;
-                out[r] = key == 0ull ? 0 : (int)(0xffffffffu - (unsigned int)(key & 0xffffffffull));
+                const unsigned long long key = atomicExch(&keys[r], 0ull);
+                count[r] = 0;
+                out[r] = key == AM_BAD_ROW ? -1 : key == 0ull ? 0 : (int)(0xffffffffu - (unsigned int)(key & 0xffffffffull));
             }
         }
     }
 }
 
-MB_API int mb_argmax(const float* logits, int rows, int vocab, int usable, int* out, cudaStream_t s) {
+// keys/count hold `key_rows` entries; `blocks_wanted` is about how many blocks the launch should have in all (the
+// caller knows the device: two per SM).  report and error_flag may be null.
+MB_API int mb_argmax(const float* logits, int rows, int vocab, int usable, int* out, unsigned long long* keys, int* count,
+                     int key_rows, int blocks_wanted, int* report, const int* error_flag, cudaStream_t s) {
     if (rows <= 0) return 0;
-    if (usable <= 0 || usable > vocab) return MB_ERR_BAD_SIZE;
-    for (int r0 = 0; r0 < rows; r0 += AM_MAX_ROWS) {
-        const int n = rows - r0 < AM_MAX_ROWS ? rows - r0 : AM_MAX_ROWS;
-        int blocks = (296 + n - 1) / n;                                  // about two blocks per SM in all
+    if (usable <= 0 || usable > vocab || key_rows <= 0 || keys == nullptr || count == nullptr) return MB_ERR_BAD_SIZE;
+    if (blocks_wanted <= 0) blocks_wanted = 1;
+    for (int r0 = 0; r0 < rows; r0 += key_rows) {
+        const int n = rows - r0 < key_rows ? rows - r0 : key_rows;
+        int blocks = (blocks_wanted + n - 1) / n;
         const int most = (usable + 4 * AM_THREADS - 1) / (4 * AM_THREADS);  // at least four values per thread
         if (blocks > most) blocks = most;
         const int per_block = (usable + blocks - 1) / blocks;
         blocks = (usable + per_block - 1) / per_block;
         const int rc = launch_kernel(argmax_kernel, dim3(blocks, n), AM_THREADS, 0, s, 0, logits + (size_t)r0 * vocab, vocab, usable,
-                                     per_block, out + r0);
+                                     per_block, out + r0, keys, count, report, error_flag);
         if (rc) return rc;
     }
     return 0;
@@ -139,7 +155,7 @@ __device__ __forceinline__ float sp_block_scan(float v, float* scratch, float* t
 __global__ void __launch_bounds__(SP_THREADS) sample_kernel(const float* __restrict__ logits, int vocab, const int* __restrict__ usable_of,
                                                             const float* __restrict__ temperature, const int* __restrict__ top_k,
                                                             const float* __restrict__ top_p, const float* __restrict__ uniform,
-                                                            int* __restrict__ out) {
+                                                            int* __restrict__ out, int* report, const int* error_flag) {
     PDL_ENTER();
     logits = pdl_fresh(logits);
     __shared__ float fs[32];
@@ -153,10 +169,23 @@ __global__ void __launch_bounds__(SP_THREADS) sample_kernel(const float* __restr
     if (temp == 0.0f) { k = 1; p = 1.0f; }
     const float inv_t = temp == 0.0f ? 1.0f : 1.0f / temp;
 
-    // the largest logit
+    // the largest logit; a row with a value that is not finite gets the id -1
     float m = -INFINITY;
-    for (int i = threadIdx.x; i < n; i += SP_THREADS) m = fmaxf(m, row[i]);
+    bool bad = false;
+    for (int i = threadIdx.x; i < n; i += SP_THREADS) {
+        const float x = row[i];
+        bad |= not_finite(x);
+        m = fmaxf(m, x);
+    }
     m = block_max(m, fs);
+    if (blockIdx.x == 0 && threadIdx.x == 0 && report != nullptr && error_flag != nullptr) {
+        const int code = *(const volatile int*)error_flag;
+        if (code != 0) report[0] = code;
+    }
+    if (__syncthreads_or(bad)) {
+        if (threadIdx.x == 0) out[blockIdx.x] = -1;
+        return;
+    }
 
     // top-k: the k-th largest key, how many lie above it, how many of its ties are kept
     int tk = INT_MIN, ties_k = INT_MAX;                       // keep key > tk, and the first ties_k ids with key == tk
@@ -286,7 +315,8 @@ __global__ void __launch_bounds__(SP_THREADS) sample_kernel(const float* __restr
 }
 
 MB_API int mb_sample(const float* logits, int rows, int vocab, const int* usable, const float* temperature, const int* top_k,
-                     const float* top_p, const float* uniform, int* out, cudaStream_t s) {
+                     const float* top_p, const float* uniform, int* out, int* report, const int* error_flag, cudaStream_t s) {
     if (rows <= 0) return 0;
-    return launch_kernel(sample_kernel, rows, SP_THREADS, 0, s, 0, logits, vocab, usable, temperature, top_k, top_p, uniform, out);
+    return launch_kernel(sample_kernel, rows, SP_THREADS, 0, s, 0, logits, vocab, usable, temperature, top_k, top_p, uniform, out,
+                         report, error_flag);
 }

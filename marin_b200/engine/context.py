@@ -58,6 +58,6 @@ class StepContext:
     spans: List[Span]
     workspace: Workspace
     extras: Dict[str, object] = field(default_factory=dict)
-    #: set for captured decode steps: fixed number of key chunks and the scratch the capture owns
-    attn_split: object = None     # (keys per CTA, chunks per sequence)
-    attn_scratch: object = None
+    #: set for captured single-token steps: what each kind of mixer fixed ahead for them (``Mixer.decode_plan``), by
+    #: the mixers' ``decode_plan_key()``; the capture owns the plans' scratch memory
+    decode_plans: Dict[object, object] = field(default_factory=dict)

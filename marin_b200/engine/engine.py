@@ -21,9 +21,10 @@ from ..config.base import ModelConfig, load_config
 from ..kernels import ops
 from ..models import Model, architecture_of
 from ..parts.base import Runtime
-from ..sampling.sampler import Sampler, SamplingParams
+from ..sampling.sampler import Sampler, SamplerError, SamplingParams
 from ..weights.loader import load_tensors
 from ..weights.random_init import random_tensor
+from .memory import Footprint, OutOfDeviceMemory, plan as plan_memory
 from .scheduler import Planned, Request, Scheduler, StopReason
 from .step import Runner, StepEntry
 
@@ -50,24 +51,37 @@ def build_model(config: ModelConfig) -> Model:
     return Model(architecture_of(config).build_spec(config))
 
 
-def load_model(model_dir: str, rt: Runtime) -> (ModelConfig, Model):
+def load_model(model_dir: str, rt: Runtime, extra_tensors: str = "error") -> (ModelConfig, Model):
     """config.json chooses the model class; safetensors are read by name and checked as a whole."""
     config = load_config(model_dir)
     model = build_model(config)
-    tensors = load_tensors(model_dir, model.tensor_specs(), model.spec.ignorable)
+    tensors = load_tensors(model_dir, model.tensor_specs(), model.spec.ignorable, extra_tensors)
     model.load(tensors, rt)
     return config, model
 
 
-def random_model(config: ModelConfig, seed: int, rt: Runtime) -> Model:
+def load_random(model: Model, seed: int, rt: Runtime) -> None:
     """Random weights made directly on the device (no folder is written)."""
-    model = build_model(config)
     dev = rt.device if rt.device.type == "cuda" else "cpu"
     tensors = {}
     for spec in model.tensor_specs():
         tensors[spec.name] = random_tensor(spec, seed, rt.dtype if spec.role != "norm" else torch.float32, dev)
     model.load(tensors, rt)
+
+
+def random_model(config: ModelConfig, seed: int, rt: Runtime) -> Model:
+    model = build_model(config)
+    load_random(model, seed, rt)
     return model
+
+
+class GenerationError(RuntimeError):
+    """A request whose logits were not finite: it has ended with ``StopReason.NON_FINITE_LOGITS`` (its pages are free
+    again); ``req_id`` names it."""
+
+    def __init__(self, req_id, message: str):
+        super().__init__(message)
+        self.req_id = req_id
 
 
 @dataclass
@@ -83,44 +97,65 @@ class Engine:
     def __init__(self, model: Union[str, None] = None, *, config: Optional[ModelConfig] = None, seed: int = 0,
                  dtype="bfloat16", ctx: Optional[int] = None, page_size: int = 16, num_pages: Optional[int] = None,
                  max_batch: int = 64, token_budget: int = 2048, device="cuda:0", cuda_graphs: bool = True,
-                 device_sampling: bool = True, _rt: Optional[Runtime] = None):
+                 device_sampling: bool = True, extra_tensors: str = "error", _rt: Optional[Runtime] = None,
+                 _free_bytes: Optional[int] = None):
         """``model``: a folder with config.json and model.safetensors; or ``config`` + ``seed`` for
         random weights.  ``num_pages``: pages per cache group (default: enough for ``max_batch``
-        sequences of ``ctx`` positions)."""
+        sequences of ``ctx`` positions, or as many as the device has room for if that is fewer).
+        ``extra_tensors``: ``"error"`` lists tensors of the folder that the model does not know in the one
+        error with everything else that is wrong; ``"warn"`` loads without them and keeps their names in
+        ``self.ignored_tensors`` (the reference ignores extras: crates/model/src/qwen3/weight_bytes.rs:9-10).
+
+        Before anything is loaded the weights, the page pool and the working memory are added up from the
+        parts' own figures and compared with the device's free memory (``self.footprint``,
+        ``engine/memory.py``); what does not fit raises ``OutOfDeviceMemory`` with the numbers."""
         self.rt = _rt or Runtime(require_cuda(device), parse_dtype(dtype))
         if model is not None:
-            self.config, self.model = load_model(model, self.rt)
+            self.config = load_config(model)
         elif config is not None:
-            self.config, self.model = config, random_model(config, seed, self.rt)
+            self.config = config
         else:
             raise ValueError("give a model folder or a configuration")
-        if self.rt.device.type == "cuda":
-            from ..kernels import build
-            build.build_for(self.model, self.rt.dtype, verbose=True)
+        self.model = build_model(self.config)
         limit = self.config.max_position_embeddings
         self.ctx = min(DEFAULT_CTX, limit) if ctx is None else int(ctx)
         if self.ctx <= 0 or self.ctx > limit:
             raise ValueError(f"ctx {self.ctx} is outside 1..{limit} (max_position_embeddings)")
-        pages_per_seq = -(-self.ctx // page_size)
-        self.num_pages = int(num_pages) if num_pages is not None else pages_per_seq * max_batch
+        on_gpu = self.rt.device.type == "cuda"
+        graph_sizes = []
+        if cuda_graphs and on_gpu and self.model.capturable():
+            graph_sizes = [b for b in (1, 2, 4, 8, 16, 32, 64, 128, 256) if b < max_batch] + [max_batch]
+        free = _free_bytes
+        if free is None and on_gpu:
+            free = int(torch.cuda.mem_get_info(self.rt.device)[0])
+        self.footprint = plan_memory(self.model, self.rt.dtype, page_size, self.ctx, max_batch, token_budget, num_pages,
+                                     graph_sizes, free)
+        self.num_pages = self.footprint.num_pages
+        self.ignored_tensors: List[str] = []
+        if model is not None:
+            tensors = load_tensors(model, self.model.tensor_specs(), self.model.spec.ignorable, extra_tensors, self.ignored_tensors)
+            self.model.load(tensors, self.rt)
+        else:
+            load_random(self.model, seed, self.rt)
+        if on_gpu:
+            from ..kernels import build
+            build.build_for(self.model, self.rt.dtype, verbose=True)
         needs = self.model.cache_needs()
         self.cache = CacheManager(needs, [e.cache_of for e in self.model.spec.schedule], page_size,
                                   self.num_pages, max_requests=max_batch)
         self.cache.allocate(self.rt.device, self.rt.dtype)
         self.runner = Runner(self.model, self.cache, self.rt, self.ctx)
-        if cuda_graphs and self.rt.device.type == "cuda":
-            sizes = [b for b in (1, 2, 4, 8, 16, 32, 64, 128, 256) if b < max_batch] + [max_batch]
-            self.runner.enable_graphs(sizes)
+        if graph_sizes:
+            self.runner.enable_graphs(graph_sizes)
         self.max_batch, self.token_budget = max_batch, token_budget
         #: False: logits go to the host and the host sampler (the reference's algorithm line by line) picks the token
-        self.device_sampling = device_sampling and self.rt.device.type == "cuda"
+        self.device_sampling = device_sampling and on_gpu
         #: pack the next decode step's inputs while the GPU runs the current one (Runner.prepare_next)
         self.prepare_ahead = True
         self.scheduler = Scheduler(self.cache, max_batch, token_budget, self.ctx)
         self._requests: Dict[Hashable, Request] = {}
         self._samplers: Dict[Hashable, Sampler] = {}
         self._next_id = 0
-        self._steps_unchecked = 0
 
     # ---- requests, one step at a time ------------------------------------------------------------------
     def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None,
@@ -141,7 +176,12 @@ class Engine:
 
     def step(self) -> List[tuple]:
         """One scheduler decision and one model step.  Returns ``[(req_id, token)]`` for the requests
-        that produced a token in this step (host ints)."""
+        that produced a token in this step (host ints).
+
+        Every step learns, with the sampled ids it reads anyway, whether a kernel's bounded wait gave up
+        (``KernelError``).  A request whose logits are NaN or infinite is ended, the others' tokens are
+        recorded, and ``GenerationError`` is raised naming it (the reference fails such a pass:
+        crates/model/src/qwen3/model.rs:128, crates/sampler/src/lib.rs:135-137)."""
         plan = self.scheduler.schedule()
         if not plan:
             return []
@@ -153,19 +193,19 @@ class Engine:
             # again, one position on; its inputs are packed now, while the GPU is busy, instead of after the wait below
             self.runner.prepare_next(entries)
         sampled = self._sample(plan, logits, self._samplers, self.config.vocab_size)
-        self._steps_unchecked += 1
-        if self._steps_unchecked >= self.CHECK_EVERY:
-            self.check_device()
-        return self.scheduler.update(plan, sampled)
-
-    #: a kernel whose bounded wait gave up leaves a code on the device; it is read every so many steps (one small copy)
-    #: and when a generation ends, and raises ``KernelError``
-    CHECK_EVERY = 32
+        emitted = self.scheduler.update(plan, sampled)          # a negative id ends its request (NON_FINITE_LOGITS)
+        bad = [rid for rid, token in sampled.items() if token < 0]
+        if bad:
+            raise GenerationError(bad[0], f"request {bad[0]!r}: the logits hold a value that is not finite"
+                                  + (f" (and those of {len(bad) - 1} more requests)" if len(bad) > 1 else "")
+                                  + "; ended, the other requests' tokens of this step are recorded")
+        return emitted
 
     def check_device(self) -> None:
-        self._steps_unchecked = 0
-        if self.rt.device.type == "cuda":
-            ops.check_device_errors()
+        """Raises ``KernelError`` if a kernel's bounded wait gave up since the last look (one small copy, one wait).
+        ``step`` learns of it by itself when it samples; this is for callers that drive ``runner`` directly."""
+        if self.runner.scratch is not None:
+            self.runner.scratch.check()
 
     def result(self, req_id: Hashable) -> Generation:
         r = self._requests[req_id]
@@ -189,14 +229,19 @@ class Engine:
         ids = [self.add_request(prompt, p) for prompt, p in zip(prompts, plist)]
         idle = 0
         while self.scheduler.has_work():
-            emitted = self.step()
+            try:
+                emitted = self.step()
+            except Exception:
+                for i in ids:                                  # a failed generation leaves nothing behind
+                    self.scheduler.cancel(i)
+                    self.forget(i)
+                raise
             idle = 0 if emitted or self.scheduler.running else idle + 1
             if idle > 2:
                 raise RuntimeError("the scheduler made no progress")
             if on_token is not None:
                 for rid, token in emitted:
                     on_token(rid, token)
-        self.check_device()
         out = [self.result(i) for i in ids]
         for i in ids:
             self.forget(i)
@@ -204,21 +249,22 @@ class Engine:
 
     def _sample(self, plan: Sequence[Planned], logits: torch.Tensor, samplers: Dict[Hashable, Sampler],
                 vocab: int) -> Dict[Hashable, int]:
+        """The next token of every request of the plan that wants one; -1 where the logits were not finite."""
         rows = [p for p in plan if p.sample]
         if not rows:
             return {}
         out: Dict[Hashable, int] = {}
-        if all(p.request.params.greedy and p.request.params.usable_vocab in (None, vocab) for p in rows):
-            ids = self.runner.greedy_ids if len(rows) == len(plan) else None
-            if ids is None or ids.numel() != len(rows):
-                ids = torch.empty(len(rows), device=logits.device, dtype=torch.int32)
-                ops.argmax(logits, vocab, ids)
-            for p, token in zip(rows, ids.tolist()):
+        scratch = self.runner.scratch
+        n = len(rows)
+        if self.device_sampling and all(p.request.params.greedy and p.request.params.usable_vocab in (None, vocab) for p in rows):
+            if not (self.runner.greedy_ids is not None and len(rows) == len(plan) and self.runner.greedy_ids.numel() == n):
+                with ops.using(scratch):                      # a replayed graph has found the largest logits already
+                    ops.argmax(logits, vocab, scratch.ids(n))
+            for p, token in zip(rows, scratch.read(n)):
                 out[p.request.req_id] = int(token)
             return out
         if self.device_sampling:
             # the kept set and the draw are computed on the device; each request's own splitmix64 stream gives its u
-            n = len(rows)
             host = torch.empty(5, n, dtype=torch.float32)
             ints = host.view(torch.int32)
             for i, p in enumerate(rows):
@@ -230,13 +276,20 @@ class Engine:
                 host[4, i] = 0.0 if prm.greedy else samplers[p.request.req_id].next_unit()
             dev = host.pin_memory().to(logits.device, non_blocking=True)
             dint = dev.view(torch.int32)
-            ids = torch.empty(n, device=logits.device, dtype=torch.int32)
-            ops.sample(logits, dint[0], dev[1], dint[2], dev[3], dev[4], ids)
-            for p, token in zip(rows, ids.tolist()):
+            with ops.using(scratch):
+                ops.sample(logits, dint[0], dev[1], dint[2], dev[3], dev[4], scratch.ids(n))
+            for p, token in zip(rows, scratch.read(n)):
                 out[p.request.req_id] = int(token)
             return out
         host = logits.float().cpu().numpy()
+        if scratch is not None:
+            scratch.check()
         for i, p in enumerate(rows):
             usable = p.request.params.usable_vocab or vocab
-            out[p.request.req_id] = samplers[p.request.req_id].sample(host[i], usable)
+            try:
+                out[p.request.req_id] = samplers[p.request.req_id].sample(host[i], usable)
+            except SamplerError as err:
+                if "NaN" not in str(err):
+                    raise
+                out[p.request.req_id] = -1
         return out

@@ -34,6 +34,7 @@ class StopReason(enum.Enum):
     CONTEXT_FULL = "context_full"
     CANCELLED = "cancelled"
     OUT_OF_PAGES = "out_of_pages"
+    NON_FINITE_LOGITS = "non_finite_logits"      # the model produced NaN or infinity for this request: it was ended
 
 
 class RequestError(ValueError):
@@ -88,7 +89,8 @@ class Scheduler:
     """The handle of the C++ scheduler (``csrc/host/scheduler.cpp``), which holds the queues, the requests' tokens
     and counters and decides every step; the ``Request`` objects here mirror what it says about them."""
 
-    _STOPS = [StopReason.MAX_TOKENS, StopReason.END_OF_TEXT, StopReason.CONTEXT_FULL, StopReason.CANCELLED, StopReason.OUT_OF_PAGES]
+    _STOPS = [StopReason.MAX_TOKENS, StopReason.END_OF_TEXT, StopReason.CONTEXT_FULL, StopReason.CANCELLED, StopReason.OUT_OF_PAGES,
+              StopReason.NON_FINITE_LOGITS]
 
     def __init__(self, cache: CacheManager, max_batch: int, token_budget: int, max_seq_len: int):
         if token_budget < 1 or max_batch < 1:
@@ -218,7 +220,8 @@ class Scheduler:
     # ---- after the step ----------------------------------------------------------------------------------
     def update(self, plan: Sequence[Planned], sampled: Dict[Hashable, int]) -> List[tuple]:
         """Records what ran and the tokens sampled for the requests whose portion ended their known
-        tokens; returns ``[(req_id, token)]`` for the tokens that were emitted (a stop token is not)."""
+        tokens; returns ``[(req_id, token)]`` for the tokens that were emitted (a stop token is not).  A negative token says the request's logits were not finite:
+        it ends with ``StopReason.NON_FINITE_LOGITS``."""
         tokens = np.asarray([sampled[p.request.req_id] for p in plan if p.sample], np.int32).reshape(-1)
         changed = ctypes.c_int(0)
         n = self._lib.mbs_update(self._core, tokens.ctypes.data, int(tokens.size), self._emitted_ids.ctypes.data,

@@ -21,6 +21,7 @@ import torch
 
 from ..cache.manager import DROPPED, CacheManager, PagedView, StateView
 from ..cache.pages import CONTEXT_FULL, OK, OUT_OF_PAGES, OutOfPages
+from ..kernels import ops
 from ..models.model import Model
 from ..parts.base import Runtime
 from .context import Span, StepContext, Workspace
@@ -66,6 +67,12 @@ class Runner:
         self.workspace = Workspace(rt.device)
         self.views = CacheViews(cache)
         self.vocab = model.spec.vocab_size
+        #: the kernels' scratch memory, error flag and result buffer of this runner alone (see ``ops.Scratch``)
+        self.scratch = None
+        if rt.device.type == "cuda":
+            self.scratch = ops.Scratch(rt.device)
+        self._pinned: Optional[torch.Tensor] = None           # host side of the packed inputs of steps run without a graph
+        self._pinned_free = None                               # the event after which it may be written again
         self.steps_run = 0
         self._longest = 1
         #: after a step replayed from a graph: int32 ids of the largest logit of each returned row (lowest id among
@@ -98,9 +105,16 @@ class Runner:
             n = len(e.tokens)
             if n == 0:
                 raise StepError(f"request {e.req_id!r} brings no tokens")
-            for t in e.tokens:
-                if not 0 <= int(t) < self.vocab:
-                    raise StepError(f"request {e.req_id!r}: token id {t} is outside the vocabulary of {self.vocab}")
+            if n == 1:
+                low = high = int(e.tokens[0])
+            else:
+                ids = np.asarray(e.tokens)
+                if ids.dtype.kind not in "iu":
+                    raise StepError(f"request {e.req_id!r}: token ids must be integers")
+                low, high = int(ids.min()), int(ids.max())
+            if low < 0 or high >= self.vocab:
+                bad = next(t for t in e.tokens if not 0 <= int(t) < self.vocab)
+                raise StepError(f"request {e.req_id!r}: token id {bad} is outside the vocabulary of {self.vocab}")
             for w in e.want:
                 if not 0 <= int(w) < n:
                     raise StepError(f"request {e.req_id!r}: wanted place {w} is outside its {n} tokens")
@@ -130,6 +144,14 @@ class Runner:
             host, dev, copied = static
             copied.synchronize()                 # the last step's copy has left the pinned buffer
             packed = host.numpy()
+        elif self.rt.device.type == "cuda":
+            # one pinned buffer serves every step that runs without a graph; it grows when a step needs more
+            if self._pinned is None or self._pinned.numel() < total:
+                self._pinned = torch.empty(max(total, 1 << 16), dtype=torch.int32).pin_memory()
+                self._pinned_free = torch.cuda.Event()
+            else:
+                self._pinned_free.synchronize()
+            packed = self._pinned.numpy()[:total]
         else:
             packed = np.empty(total, np.int32)
         info = np.zeros(8, np.int32)
@@ -149,11 +171,11 @@ class Runner:
             copied.record()
             if refresh_only:
                 return None
+        elif self.rt.device.type == "cuda":
+            dev = self._pinned[:total].to(self.rt.device, non_blocking=True)
+            self._pinned_free.record()
         else:
-            host = torch.from_numpy(packed)
-            if self.rt.device.type == "cuda":
-                host = host.pin_memory()
-            dev = host.to(self.rt.device, non_blocking=True)
+            dev = torch.from_numpy(packed)
         spans = [Span(row, entries[int(i)].req_id, int(at), int(cnt), int(first), int(slot))
                  for row, (i, at, cnt, first, slot) in enumerate(span_rows.tolist())]
         views, at = [], 0
@@ -179,8 +201,10 @@ class Runner:
     def enable_graphs(self, batch_sizes: Sequence[int] = (1, 2, 4, 8, 16, 32, 64)) -> None:
         """Steps in which every request brings exactly one token are replayed from a CUDA graph captured per
         padded batch size: the kernels' arguments live in one static device buffer that each step overwrites.
-        Mixers that keep their state through Python-side loops cannot be captured; graphs are then left off."""
-        if self.cache.state_needs:
+        Whether a model's single-token steps can be captured is its parts' answer (``Mixer.capturable``,
+        ``FeedForward.capturable``); if one of them says no, graphs are left off."""
+        capturable = getattr(self.model, "capturable", None)
+        if capturable is None or not capturable():
             return
         self.graph_sizes = sorted(set(int(b) for b in batch_sizes))
         self.graphs: Dict[tuple, dict] = {}
@@ -203,46 +227,39 @@ class Runner:
         g = self.graphs.get(key)
         if g is not None:
             return g
-        from ..kernels import ops
-
         size = self.packed_size(bucket)
         host = torch.zeros(size, dtype=torch.int32).pin_memory()
         dev = torch.zeros(size, dtype=torch.int32, device=self.rt.device)
-        mixers = [b.mixer for b in self.model.blocks if hasattr(b.mixer, "kv_heads")]
-        heads = max((m.heads for m in mixers), default=1)
-        kv_heads = min((m.kv_heads for m in mixers), default=1)
-        hd = max((m.head_dim for m in mixers), default=1)
-        # the split of the keys is fixed by the span, so that the captured grid fits every step of this graph
-        split, chunks = ops.decode_split(bucket, kv_heads, span)
+        # what each kind of mixer fixes ahead for this batch size and span (for attention: the split of the keys, which
+        # is part of the captured grid, and scratch of the capture's own), asked of the mixers themselves
         shared = next((o for (b, _), o in self.graphs.items() if b == bucket), None)
         g = {"key": key, "static": (host, dev, torch.cuda.Event()), "workspace": shared["workspace"] if shared else Workspace(self.rt.device),
-             "graph": None, "logits": None,
-             "attn_split": (split, chunks),
-             "attn_scratch": ops.decode_scratch(self.rt.device, bucket, heads, kv_heads, chunks, hd)}
+             "graph": None, "logits": None, "plans": self.model.decode_plans(bucket, span)}
         self.graphs[key] = g
 
         def run():
             ctx = self.build_context(entries, pad_to=bucket, static=g["static"])
             ctx.workspace = g["workspace"]
-            ctx.attn_split, ctx.attn_scratch = g["attn_split"], g["attn_scratch"]
+            ctx.decode_plans = g["plans"]
             return self.model.forward(ctx, self.views)
 
-        run()                                    # warm up: builds kernels, sizes the workspace
+        with ops.using(self.scratch):
+            run()                                # warm up: builds kernels, sizes the workspace
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         ctx = self.build_context(entries, pad_to=bucket, static=g["static"])
         ctx.workspace = g["workspace"]
-        ctx.attn_split, ctx.attn_scratch = g["attn_split"], g["attn_scratch"]
+        ctx.decode_plans = g["plans"]
         torch.cuda.synchronize()
         launches = ops.launches
-        g["best"] = torch.zeros(bucket, device=self.rt.device, dtype=torch.int32)
+        g["best"] = self.scratch.ids(bucket)     # behind the scratch's report: the host reads both in one copy
         # No garbage collection while the stream is capturing: an engine or a tensor dropped earlier that is freed now
         # (pinned memory, events, older graphs) would make a CUDA call that a capture does not allow, and the capture
         # would be lost.  (torch.cuda.graph collects once before it begins.)
         collecting = gc.isenabled()
         gc.disable()
         try:
-            with torch.cuda.graph(graph):
+            with ops.using(self.scratch), torch.cuda.graph(graph):
                 g["logits"] = self.model.forward(ctx, self.views)
                 ops.argmax(g["logits"], self.vocab, g["best"])    # greedy sampling rides in the same graph
         finally:
@@ -259,8 +276,6 @@ class Runner:
         bucket = next((b for b in sizes if b >= len(entries)), None)
         if bucket is None:
             return None
-        from ..kernels import ops
-
         g = self._graph_for(bucket, entries)
         self.build_context(entries, pad_to=bucket, static=g["static"], refresh_only=True)
         g["graph"].replay()
@@ -299,7 +314,8 @@ class Runner:
         logits = self._step_graph(entries) if observe is None else None
         if logits is None:
             ctx = self.build_context(entries)
-            logits = self.model.forward(ctx, self.views, observe) if observe is not None else self.model.forward(ctx, self.views)
+            with ops.using(self.scratch):
+                logits = self.model.forward(ctx, self.views, observe) if observe is not None else self.model.forward(ctx, self.views)
         rc = cache._lib.mbh_step_commit(cache._core(), n, handles.ctypes.data, counts.ctypes.data)
         if rc != OK:
             raise StepError(f"recording the step failed (code {rc})")
@@ -343,8 +359,6 @@ class Runner:
         return True
 
     def _run_prepared(self, prepared: dict, entries: Sequence[StepEntry]) -> torch.Tensor:
-        from ..kernels import ops
-
         g, n = prepared["graph"], len(entries)
         host, dev, copied = g["static"]
         host.numpy()[:n] = [e.tokens[0] for e in entries]      # the token ids lead the packed buffer

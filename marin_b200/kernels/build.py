@@ -204,26 +204,14 @@ def build_all(verbose: bool = True) -> List[str]:
 
 
 def build_for(model, dtype, verbose: bool = True) -> List[str]:
-    """Compiles what this model needs and nothing else: the element-wise kernels, the matrix products of its dtype
-    and the attention kernels for its head layouts."""
+    """Compiles what this model needs and nothing else: the element-wise and sampling kernels, the matrix products of
+    its dtype, and whatever its parts ask for themselves (``Part.kernel_jobs``: attention for its head layouts)."""
     import torch
 
     jobs = {"mb_elementwise": (LIBRARIES["mb_elementwise"], []), "mb_sampling": (LIBRARIES["mb_sampling"], []),
             "mb_gemm_simple": (LIBRARIES["mb_gemm_simple"], [])}
     if dtype == torch.bfloat16:
         jobs["mb_gemm_tc"] = (LIBRARIES["mb_gemm_tc"], [])
-    from . import ops
-
-    for block in getattr(model, "blocks", []):
-        mixer = block.mixer
-        if not all(hasattr(mixer, a) for a in ("heads", "kv_heads", "head_dim")):
-            continue
-        if ops.fast_attention_supported(dtype, mixer.heads, mixer.kv_heads, mixer.head_dim):
-            jobs[f"mb_attention_fast_d{mixer.head_dim}_g{mixer.heads // mixer.kv_heads}"] = attention_job(
-                mixer.head_dim, mixer.heads // mixer.kv_heads)
-            if mixer.head_dim in (64, 128):
-                jobs[f"mb_attention_tc_d{mixer.head_dim}_g{mixer.heads // mixer.kv_heads}"] = attention_tc_job(
-                    mixer.head_dim, mixer.heads // mixer.kv_heads)
-        else:
-            jobs["mb_attention_simple"] = (LIBRARIES["mb_attention_simple"], [])
+    if hasattr(model, "kernel_jobs"):
+        jobs.update(model.kernel_jobs(dtype))
     return build_many(jobs, verbose)

@@ -10,6 +10,7 @@ from __future__ import annotations
 
 import ctypes
 import os
+import weakref
 from typing import Optional
 
 import torch
@@ -99,36 +100,134 @@ couple_norms = True
 #: kernel costs 7.
 couple_norms_in_prefill = False
 SM_COUNT = 148
-_scratch = {}
 
 
-def _gemm_scratch(device):
-    """Split-K partials, per-tile counters (zeroed once; the kernel leaves them at zero) and the error flag."""
-    global SM_COUNT
+class NonFiniteLogits(KernelError):
+    """Logits that are NaN or infinite among the values a token may be chosen from; the sampling kernels give such
+    rows the id -1 (the reference refuses them: crates/sampler/src/lib.rs:135-137, crates/model/src/qwen3/model.rs:128)."""
+
+
+class Scratch:
+    """Device memory the kernels use besides their inputs and outputs, for ONE stream of work at a time: an engine
+    owns one (``Runner.scratch``) and makes it current around its steps (``using``), so that two engines in one
+    process, each on a stream of its own, never share a counter or a flag.  Calls outside any ``using`` block
+    take a default per device.
+
+    ``error``        one int: the code a kernel leaves when a bounded wait gives up (zero otherwise);
+    ``report``       four ints, of which a sampling kernel fills the first with a copy of ``error`` when that is not
+                     zero; the sampled ids of a step lie right behind it (``ids``), so that one copy brings both
+                     to the host (``read``) and every step learns of a wait that gave up without a wait of its own;
+    ``sumsq``        per-token sums of squares that ride from one product to the next (coupled norms);
+    ``parked``, ``parked_flags``  stream-K: the partial tile each CTA may park, and a flag per epilogue warp;
+    ``argmax_keys``, ``argmax_count``  arg-max over several blocks per row; zero between launches;
+    decode attention's partial results grow on demand (``decode_buffers``) unless a captured graph brings its own.
+    """
+
+    ARGMAX_ROWS = 4096
+    RESULT_ROWS = 4096
+
+    def __init__(self, device):
+        global SM_COUNT
+        self.device = torch.device(device)
+        SM_COUNT = torch.cuda.get_device_properties(self.device).multi_processor_count
+        self.sm_count = SM_COUNT
+        i32, f32 = dict(device=self.device, dtype=torch.int32), dict(device=self.device, dtype=torch.float32)
+        self.error = torch.zeros(1, **i32)
+        self.result = torch.zeros(4 + self.RESULT_ROWS, **i32)      # the report, then the sampled ids: one copy reads both
+        self.report = self.result[:4]
+        self.sumsq = torch.empty(1 << 22, **f32)
+        self.parked = torch.empty(self.sm_count * 256 * 128, **f32)
+        self.parked_flags = torch.zeros(self.sm_count * 8, **i32)
+        self.argmax_keys = torch.zeros(self.ARGMAX_ROWS, device=self.device, dtype=torch.int64)
+        self.argmax_count = torch.zeros(self.ARGMAX_ROWS, **i32)
+        self._decode = None
+        _all_scratch.add(self)
+
+    def decode_buffers(self, requests: int, H: int, K: int, chunks: int, d: int):
+        """Partial accumulators, partial (max, sum) and arrival counters of the split-KV decode kernel, at least as
+        large as this call needs; they only ever grow, so layers of different head layouts share them."""
+        need = requests * H * chunks
+        sizes = (need * d, need * 2, requests * K)
+        held = self._decode
+        if held is None or any(t.numel() < n for t, n in zip(held, sizes)):
+            sizes = tuple(max(n, t.numel()) for t, n in zip(held, sizes)) if held is not None else sizes
+            held = (torch.empty(sizes[0], device=self.device, dtype=torch.float32),
+                    torch.empty(sizes[1], device=self.device, dtype=torch.float32),
+                    torch.zeros(sizes[2], device=self.device, dtype=torch.int32))
+            self._decode = held
+        return held
+
+    def ids(self, rows: int) -> torch.Tensor:
+        """Where a step's sampled ids go (int32 ``[rows]``), right behind the report."""
+        if rows > self.RESULT_ROWS:
+            raise KernelError(f"{rows} rows are sampled in one step; the result buffer holds {self.RESULT_ROWS}")
+        return self.result[4:4 + rows]
+
+    def read(self, rows: int):
+        """The ids of ``ids(rows)`` as host ints (-1: that row's logits were not finite), read together with the
+        report (one copy, one wait): raises ``KernelError`` if a kernel's wait gave up."""
+        both = self.result[:4 + rows].tolist()
+        if both[0]:
+            self.clear()
+            raise KernelError(f"a tensor-core kernel's wait on an mbarrier gave up (code {both[0]})")
+        return both[4:]
+
+    def check(self) -> None:
+        """Raises if a kernel's bounded wait gave up since the last check (reads one int: synchronises)."""
+        code = int(self.error.item())
+        if code != 0:
+            self.clear()
+            raise KernelError(f"a tensor-core kernel's wait on an mbarrier gave up (code {code})")
+
+    def clear(self) -> None:
+        """After an error: a kernel that gave up may have left its counters and flags set."""
+        self.error.zero_()
+        self.report.zero_()
+        self.parked_flags.zero_()
+        self.argmax_keys.zero_()
+        self.argmax_count.zero_()
+        if self._decode is not None:
+            self._decode[2].zero_()
+
+
+_default_scratch = {}
+_all_scratch = weakref.WeakSet()
+_current_scratch: Optional[Scratch] = None
+
+
+def _scratch_for(device) -> Scratch:
+    if _current_scratch is not None and _current_scratch.device == device:
+        return _current_scratch
     key = (device.type, device.index)
-    s = _scratch.get(key)
+    s = _default_scratch.get(key)
     if s is None:
-        SM_COUNT = torch.cuda.get_device_properties(device).multi_processor_count
-        s = {"partials": torch.empty(8 << 20, device=device, dtype=torch.float32),
-             "counters": torch.zeros(1 << 16, device=device, dtype=torch.int32),
-             "error": torch.zeros(1, device=device, dtype=torch.int32),
-             "sumsq": torch.empty(1 << 22, device=device, dtype=torch.float32),
-             # stream-K: the partial tile each CTA may park (the widest tile), and a flag per epilogue warp
-             "parked": torch.empty(SM_COUNT * 256 * 128, device=device, dtype=torch.float32),
-             "parked_flags": torch.zeros(SM_COUNT * 8, device=device, dtype=torch.int32)}
-        _scratch[key] = s
+        s = _default_scratch[key] = Scratch(device)
     return s
 
 
+class using:
+    """``with ops.using(scratch): ...`` — the kernels launched inside take their scratch memory from ``scratch``."""
+
+    def __init__(self, scratch: Optional[Scratch]):
+        self.scratch = scratch
+
+    def __enter__(self):
+        global _current_scratch
+        self.before, _current_scratch = _current_scratch, self.scratch
+        return self.scratch
+
+    def __exit__(self, *exc):
+        global _current_scratch
+        _current_scratch = self.before
+        return False
+
+
 def check_device_errors(device=None) -> None:
-    """Raises if a kernel's bounded wait gave up since the last check (reads one int: synchronises)."""
-    for s in _scratch.values():
-        code = int(s["error"].item())
-        if code != 0:
-            s["error"].zero_()
-            s["counters"].zero_()                 # a kernel that gave up may have left its counters and flags set
-            s["parked_flags"].zero_()
-            raise KernelError(f"a tensor-core kernel's wait on an mbarrier gave up (code {code})")
+    """Raises if a kernel's bounded wait gave up since the last check, under any scratch of this process (on
+    ``device`` if one is given).  Reads one int per scratch: synchronises."""
+    for s in list(_all_scratch):
+        if device is None or s.device == torch.device(device):
+            s.check()
 
 
 def gemm_plan(T: int, N: int, K: int):
@@ -208,11 +307,11 @@ def _persistent_product(x, w, out, mode: int, T: int, N: int, K: int, s, what: s
     if bn is not None:
         _check(lib.mb_gemm_tc_persistent_streamk(
             _ptr(x), _ptr(w), _ptr(out), _c_int(mode), _c_int(T), _c_int(N), _c_int(K), _c_int(bn), _c_int(SM_COUNT),
-            _ptr(s["parked"]), ctypes.c_longlong(s["parked"].numel()), _ptr(s["parked_flags"]), _ptr(s["error"]), _stream()),
+            _ptr(s.parked), ctypes.c_longlong(s.parked.numel()), _ptr(s.parked_flags), _ptr(s.error), _stream()),
             what + ", stream-K")
         return
     _check(lib.mb_gemm_tc_persistent(_ptr(x), _ptr(w), _ptr(out), _c_int(mode), _c_int(T), _c_int(N), _c_int(K),
-                                     _c_int(persistent_plan(T, N)), _c_int(SM_COUNT), _ptr(s["error"]), _stream()), what)
+                                     _c_int(persistent_plan(T, N)), _c_int(SM_COUNT), _ptr(s.error), _stream()), what)
 
 
 class NormOut:
@@ -264,14 +363,14 @@ def gemm(x, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False, then_n
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and T > 0):
         mode = 2 if accumulate else (0 if out.dtype == torch.bfloat16 else 1)
         if T > 128 and -(-N // 128) * -(-T // 128) >= SM_COUNT // 2:
-            s = _gemm_scratch(x.device)
+            s = _scratch_for(x.device)
             lib = _lib("mb_gemm_tc")
             carried = None
             if (then_norm is not None and accumulate and couple_norms and couple_norms_in_prefill and N % 8 == 0
                     and then_norm.rows.dtype == torch.bfloat16 and then_norm.rows.data_ptr() % 16 == 0):
                 slots = int(lib.mb_gemm_tc_norm_slots(_c_int(N), _c_int(1)))
-                if slots * T <= s["sumsq"].numel():
-                    carried = NormedRows(then_norm.rows, s["sumsq"], slots, N, then_norm.eps)
+                if slots * T <= s.sumsq.numel():
+                    carried = NormedRows(then_norm.rows, s.sumsq, slots, N, then_norm.eps)
             if carried is None and scaled is None:
                 _persistent_product(x, w, out, mode, T, N, K, s, "gemm (tensor cores, persistent)")
                 return None
@@ -281,20 +380,20 @@ def gemm(x, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False, then_n
                 _ptr(carried.rows) if carried is not None else None, _ptr(carried.sumsq) if carried is not None else None,
                 _ptr(scaled.sumsq) if scaled is not None else None, _c_int(scaled.slots if scaled is not None else 0),
                 _c_int(scaled.dim if scaled is not None else 0), _c_float(scaled.eps if scaled is not None else 0.0),
-                _ptr(s["error"]), _stream()), "gemm (tensor cores, persistent, coupled with a norm)")
+                _ptr(s.error), _stream()), "gemm (tensor cores, persistent, coupled with a norm)")
             return carried
         bn, splits = gemm_plan(T, N, K)
-        s = _gemm_scratch(x.device)
+        s = _scratch_for(x.device)
         lib = _lib("mb_gemm_tc")
         carried = None
         if (then_norm is not None and accumulate and couple_norms and T <= COUPLED_NORM_MAX_TOKENS and N % 8 == 0
                 and then_norm.rows.dtype == torch.bfloat16 and then_norm.rows.data_ptr() % 16 == 0):
             slots = int(lib.mb_gemm_tc_norm_slots(_c_int(N), _c_int(splits)))
-            if slots * T <= s["sumsq"].numel():
-                carried = NormedRows(then_norm.rows, s["sumsq"], slots, N, then_norm.eps)
+            if slots * T <= s.sumsq.numel():
+                carried = NormedRows(then_norm.rows, s.sumsq, slots, N, then_norm.eps)
         if carried is None and scaled is None:
             _check(lib.mb_gemm_tc_cluster(_ptr(x), _ptr(w), _ptr(out), _c_int(mode), _c_int(T), _c_int(N), _c_int(K),
-                                          _c_int(bn), _c_int(splits), _ptr(s["error"]), _stream()), "gemm (tensor cores)")
+                                          _c_int(bn), _c_int(splits), _ptr(s.error), _stream()), "gemm (tensor cores)")
             return None
         _check(lib.mb_gemm_tc_coupled(
             _ptr(x), _ptr(w), _ptr(out), _c_int(mode), _c_int(T), _c_int(N), _c_int(K), _c_int(bn), _c_int(splits),
@@ -302,7 +401,7 @@ def gemm(x, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False, then_n
             _ptr(carried.rows) if carried is not None else None, _ptr(carried.sumsq) if carried is not None else None,
             _ptr(scaled.sumsq) if scaled is not None else None, _c_int(scaled.slots if scaled is not None else 0),
             _c_int(scaled.dim if scaled is not None else 0), _c_float(scaled.eps if scaled is not None else 0.0),
-            _ptr(s["error"]), _stream()), "gemm (tensor cores, coupled with a norm)")
+            _ptr(s.error), _stream()), "gemm (tensor cores, coupled with a norm)")
         return carried
     assert scaled is None, "rows with a pending norm reach only the tensor-core product"
     _check(_lib("mb_gemm_simple").mb_gemm_simple(_ptr(x), _code(x), _ptr(w), _code(w), _ptr(out), _code(out), _c_int(T),
@@ -337,7 +436,7 @@ def gemm_qkv_heads(x, w: torch.Tensor, q_out: torch.Tensor, q_weight, k_weight, 
         return False
     _need_cuda(rows, w, q_out)
     assert tuple(q_out.shape) == (T, H * d) and w.shape[1] == Kdim
-    s = _gemm_scratch(rows.device)
+    s = _scratch_for(rows.device)
     page_size = k_cache.shape[2] if write_kv else 0
     _check(_lib("mb_gemm_tc").mb_gemm_tc_heads(
         _ptr(rows), _ptr(w), _c_int(T), _c_int(N), _c_int(Kdim), _c_int(splits), _ptr(q_out),
@@ -345,7 +444,7 @@ def gemm_qkv_heads(x, w: torch.Tensor, q_out: torch.Tensor, q_weight, k_weight, 
         _ptr(positions), _ptr(inv_freq), _ptr(slot_mapping) if write_kv else None, _c_int(H), _c_int(K), _c_int(page_size),
         _ptr(scaled.sumsq) if scaled is not None else None, _c_int(scaled.slots if scaled is not None else 0),
         _c_int(scaled.dim if scaled is not None else 0), _c_float(scaled.eps if scaled is not None else 0.0),
-        _ptr(s["error"]), _stream()), "gemm with heads finished in the epilogue")
+        _ptr(s.error), _stream()), "gemm with heads finished in the epilogue")
     return True
 
 
@@ -369,7 +468,6 @@ def qk_norm_rope_write(qkv, q_out, q_weight, k_weight, eps, positions, inv_freq,
 use_fast_attention = True
 #: prompt portions go to the tcgen05 attention kernel where it applies (heads of 64 or 128, pages >= 16)
 use_tc_attention = True
-_attn_scratch = {}
 DECODE_SPLITS = (4096, 2048, 1024, 512, 256, 128, 64)      # keys per CTA the split-KV decode kernel may be given
 DECODE_CLUSTER_CHUNKS = 8                                   # most chunks the kernel merges as one cluster (see _attention_lib)
 _cluster_asked = set()
@@ -429,21 +527,40 @@ def decode_scratch(device, requests: int, H: int, K: int, chunks: int, d: int):
             torch.zeros(requests * K, device=device, dtype=torch.int32))
 
 
-def _decode_scratch(device, requests: int, H: int, K: int, chunks: int, d: int):
-    need = requests * H * chunks
-    key = (device.type, device.index)
-    held = _attn_scratch.get(key)
-    if held is None or held[0].numel() < need * d or held[1].numel() < need * 2 or held[2].numel() < requests * K:
-        grow_r = max(requests, held[2].numel() // K if held else 0)
-        grow_c = max(chunks, (held[1].numel() // 2) // max(1, grow_r * H) if held else 0)
-        held = decode_scratch(device, grow_r, H, K, grow_c, d)
-        _attn_scratch[key] = held
-    return held
+class DecodePlan:
+    """How single-token attention splits its keys, fixed ahead for a captured graph: keys per CTA, chunks per
+    sequence, and scratch memory of the capture's own (partial accumulators, partial (max, sum), counters)."""
+    __slots__ = ("split", "chunks", "buffers")
+
+    def __init__(self, split: int, chunks: int, buffers=None):
+        self.split, self.chunks, self.buffers = int(split), int(chunks), buffers
 
 
-def attention(q, k_cache, v_cache, out, ctx, block_table, H, K, d, scale, window=0) -> None:
+def decode_plan(device, dtype, requests: int, H: int, K: int, d: int, span: int) -> Optional[DecodePlan]:
+    """The plan for ``requests`` single-token requests over sequences of up to ``span`` keys, with scratch sized for
+    exactly this head layout; None where the split-KV kernel does not apply (the plain kernel needs no plan)."""
+    if not (use_fast_attention and fast_attention_supported(dtype, H, K, d)):
+        return None
+    _attention_lib(d, H // K)                        # the library says how wide a cluster may be: plan after asking
+    split, chunks = decode_split(requests, K, span)
+    return DecodePlan(split, chunks, decode_scratch(device, requests, H, K, chunks, d))
+
+
+def attention_jobs(dtype, H: int, K: int, d: int) -> dict:
+    """``{library: (sources, defines)}`` of the attention kernels a mixer of this head layout runs."""
+    if not fast_attention_supported(dtype, H, K, d):
+        return {"mb_attention_simple": (build.LIBRARIES["mb_attention_simple"], [])}
+    jobs = {f"mb_attention_fast_d{d}_g{H // K}": build.attention_job(d, H // K)}
+    if d in (64, 128):
+        jobs[f"mb_attention_tc_d{d}_g{H // K}"] = build.attention_tc_job(d, H // K)
+    return jobs
+
+
+def attention(q, k_cache, v_cache, out, ctx, block_table, H, K, d, scale, window=0, plan: Optional[DecodePlan] = None) -> None:
     """Causal attention of the step's tokens over the paged cache (their own keys included).  The first
-    ``ctx.num_decode`` requests bring one token each (rows 0..num_decode-1); the rest bring portions."""
+    ``ctx.num_decode`` requests bring one token each (rows 0..num_decode-1); the rest bring portions.  ``plan``
+    fixes the split of the single-token rows' keys (a captured graph brings it); without one the split follows the
+    longest sequence of the step."""
     _need_cuda(q, k_cache, v_cache, out, block_table)
     T = q.shape[0]
     page_size = k_cache.shape[2]
@@ -455,20 +572,21 @@ def attention(q, k_cache, v_cache, out, ctx, block_table, H, K, d, scale, window
         max_pages = block_table.shape[1]
         nd = ctx.num_decode
         if nd > 0:
-            split, chunks = getattr(ctx, "attn_split", None) or decode_split(nd, K, ctx.max_seq_len)
-            part_acc, part_ml, counters = getattr(ctx, "attn_scratch", None) or _decode_scratch(q.device, nd, H, K, chunks, d)
+            split, chunks = (plan.split, plan.chunks) if plan is not None else decode_split(nd, K, ctx.max_seq_len)
+            buffers = plan.buffers if plan is not None and plan.buffers is not None else None
+            part_acc, part_ml, counters = buffers or _scratch_for(q.device).decode_buffers(nd, H, K, chunks, d)
             _check(lib.mb_attn_decode(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), _c_int(max_pages),
                                       _ptr(ctx.seq_lens), _c_int(nd), _c_int(K), _c_int(page_size),
                                       ctypes.c_longlong(k_cache.shape[0]), _c_float(scale), _c_int(window), _ptr(part_acc),
                                       _ptr(part_ml), _ptr(counters), _c_int(chunks), _c_int(split),
-                                      _ptr(_gemm_scratch(q.device)["error"]), _stream()), "attention (decode)")
+                                      _ptr(_scratch_for(q.device).error), _stream()), "attention (decode)")
         if ctx.num_requests > nd and use_tc_attention and d in (64, 128) and page_size >= 16:
             tc = build.load(f"mb_attention_tc_d{d}_g{H // K}", *build.attention_tc_job(d, H // K))
             _check(tc.mb_attn_prefill_tc(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), _c_int(max_pages),
                                          _ptr(ctx.cu_tokens), _ptr(ctx.seq_lens), _c_int(nd), _c_int(ctx.num_requests - nd),
                                          _c_int(ctx.max_query_len), _c_int(T), _c_int(K), _c_int(page_size),
                                          ctypes.c_longlong(k_cache.shape[0]), _c_float(scale), _c_int(window),
-                                         _ptr(_gemm_scratch(q.device)["error"]), _stream()), "attention (prefill, tensor cores)")
+                                         _ptr(_scratch_for(q.device).error), _stream()), "attention (prefill, tensor cores)")
         elif ctx.num_requests > nd:
             _check(lib.mb_attn_prefill(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), _c_int(max_pages),
                                        _ptr(ctx.cu_tokens), _ptr(ctx.seq_lens), _c_int(nd), _c_int(ctx.num_requests - nd),
@@ -522,13 +640,13 @@ def gemm_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor, out: torch.Tensor,
         gemm(scaled if scaled is not None else x, w_interleaved, tmp)
         swiglu(tmp, out, interleaved=True)
         return
-    s = _gemm_scratch(x.device)
+    s = _scratch_for(x.device)
     if T > 128 and -(-N // 128) * -(-T // 128) >= SM_COUNT // 2:
         if scaled is not None:
             _check(_lib("mb_gemm_tc").mb_gemm_tc_persistent_coupled(
                 _ptr(x), _ptr(w_interleaved), _ptr(out), _c_int(3), _c_int(T), _c_int(N), _c_int(K), _c_int(persistent_plan(T, N)),
                 _c_int(SM_COUNT), None, _c_int(0), None, None, _ptr(scaled.sumsq), _c_int(scaled.slots), _c_int(scaled.dim),
-                _c_float(scaled.eps), _ptr(s["error"]), _stream()), "gemm+swiglu (tensor cores, persistent, coupled with a norm)")
+                _c_float(scaled.eps), _ptr(s.error), _stream()), "gemm+swiglu (tensor cores, persistent, coupled with a norm)")
             return
         _persistent_product(x, w_interleaved, out, 3, T, N, K, s, "gemm+swiglu (tensor cores, persistent)")
         return
@@ -537,10 +655,10 @@ def gemm_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor, out: torch.Tensor,
         _check(_lib("mb_gemm_tc").mb_gemm_tc_coupled(
             _ptr(x), _ptr(w_interleaved), _ptr(out), _c_int(3), _c_int(T), _c_int(N), _c_int(K), _c_int(bn), _c_int(1),
             None, _c_int(0), None, None, _ptr(scaled.sumsq), _c_int(scaled.slots), _c_int(scaled.dim), _c_float(scaled.eps),
-            _ptr(s["error"]), _stream()), "gemm+swiglu (tensor cores, coupled with a norm)")
+            _ptr(s.error), _stream()), "gemm+swiglu (tensor cores, coupled with a norm)")
         return
     _check(_lib("mb_gemm_tc").mb_gemm_tc_cluster(_ptr(x), _ptr(w_interleaved), _ptr(out), _c_int(3), _c_int(T), _c_int(N), _c_int(K),
-                                                _c_int(bn), _c_int(1), _ptr(s["error"]), _stream()), "gemm+swiglu (tensor cores)")
+                                                _c_int(bn), _c_int(1), _ptr(s.error), _stream()), "gemm+swiglu (tensor cores)")
 
 
 def gather_rows(src: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:
@@ -558,21 +676,27 @@ def add_into(y: torch.Tensor, x: torch.Tensor) -> None:
 
 
 def argmax(logits: torch.Tensor, usable: int, out: torch.Tensor) -> None:
-    """``out[r]`` = id of the largest of the first ``usable`` logits of row ``r`` (lowest id among equals)."""
+    """``out[r]`` = id of the largest of the first ``usable`` logits of row ``r`` (lowest id among equals); -1 for a
+    row that holds a NaN or an infinity among them."""
     _need_cuda(logits, out)
     rows, vocab = logits.shape
     assert logits.dtype == torch.float32 and out.dtype == torch.int32 and out.numel() == rows
-    _check(_lib("mb_sampling").mb_argmax(_ptr(logits), _c_int(rows), _c_int(vocab), _c_int(usable), _ptr(out), _stream()), "argmax")
+    s = _scratch_for(logits.device)
+    _check(_lib("mb_sampling").mb_argmax(_ptr(logits), _c_int(rows), _c_int(vocab), _c_int(usable), _ptr(out), _ptr(s.argmax_keys),
+                                        _ptr(s.argmax_count), _c_int(s.ARGMAX_ROWS), _c_int(2 * s.sm_count), _ptr(s.report),
+                                        _ptr(s.error), _stream()), "argmax")
 
 
 def sample(logits: torch.Tensor, usable: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
            uniform: torch.Tensor, out: torch.Tensor) -> None:
     """Draws one token per row from the reference's kept set (temperature, top-k, top-p; temperature 0 = greedy):
-    ``uniform[r]`` in [0, 1) selects the token by walking the kept ids in increasing order."""
+    ``uniform[r]`` in [0, 1) selects the token by walking the kept ids in increasing order.  Rows with a logit that is
+    not finite get the id -1."""
     _need_cuda(logits, usable, temperature, top_k, top_p, uniform, out)
     rows, vocab = logits.shape
     assert logits.dtype == torch.float32 and out.dtype == torch.int32 and usable.dtype == torch.int32 and top_k.dtype == torch.int32
     assert temperature.dtype == torch.float32 and top_p.dtype == torch.float32 and uniform.dtype == torch.float32
     assert all(t.numel() == rows for t in (usable, temperature, top_k, top_p, uniform, out))
+    s = _scratch_for(logits.device)
     _check(_lib("mb_sampling").mb_sample(_ptr(logits), _c_int(rows), _c_int(vocab), _ptr(usable), _ptr(temperature), _ptr(top_k),
-                                        _ptr(top_p), _ptr(uniform), _ptr(out), _stream()), "sample")
+                                        _ptr(top_p), _ptr(uniform), _ptr(out), _ptr(s.report), _ptr(s.error), _stream()), "sample")

@@ -43,6 +43,66 @@ class Model:
             needs.append(need if entry.cache_of is None else None)
         return needs
 
+    # ---- what the code around the model asks of it: every answer is the sum of the parts' own answers ----------------
+    def parts(self) -> List[object]:
+        """Every part of the model once: embedding, the blocks' parts in layer order, final norm, head."""
+        out = [self.embedding]
+        for block in self.blocks:
+            out += block.parts() if hasattr(block, "parts") else [block]
+        return out + [self.final_norm, self.head]
+
+    def weight_bytes(self, dtype: torch.dtype) -> int:
+        """Bytes the weights hold on the device (a tied head holds none of its own)."""
+        return sum(p.weight_bytes(dtype) for p in self.parts())
+
+    def bytes_read(self, tokens: int, dtype: torch.dtype) -> int:
+        """Bytes of weights a step over ``tokens`` tokens has to read: every layer run as often as the schedule names
+        it, the embedding's rows, the whole head."""
+        total = self.embedding.bytes_read(tokens, dtype) + self.final_norm.bytes_read(tokens, dtype) + self.head.bytes_read(tokens, dtype)
+        for entry in self.spec.schedule:
+            total += self.blocks[entry.layer].bytes_read(tokens, dtype)
+        return total
+
+    def flops(self, tokens: int, pairs: int, logit_rows: int) -> float:
+        """Floating-point operations of a step over ``tokens`` tokens in which every mixer looks at ``pairs``
+        (query, key) pairs and ``logit_rows`` rows go through the head."""
+        total = self.head.flops(logit_rows)
+        for entry in self.spec.schedule:
+            total += self.blocks[entry.layer].flops(tokens, pairs)
+        return total
+
+    def cache_bytes_read(self, context: int, dtype: torch.dtype) -> int:
+        """Bytes of the cache one decoded token of a sequence of ``context`` positions reads, over all schedule entries."""
+        total = 0
+        for entry in self.spec.schedule:
+            need = self.blocks[entry.layer].mixer.cache_need()
+            if need is not None:
+                total += need.bytes_read(context, dtype)
+        return total
+
+    def kernel_jobs(self, dtype: torch.dtype) -> Dict[str, tuple]:
+        """``{library: (sources, defines)}`` of the kernels specialised for this model's parts."""
+        jobs: Dict[str, tuple] = {}
+        for p in self.parts():
+            jobs.update(p.kernel_jobs(dtype))
+        return jobs
+
+    def capturable(self) -> bool:
+        """Whether single-token steps of this model may be captured in CUDA graphs: every mixer and feed-forward says so."""
+        return all(getattr(p, "capturable", True) for p in self.parts())
+
+    def decode_plans(self, requests: int, span: int) -> Dict[object, object]:
+        """One decode plan per kind of mixer (``Mixer.decode_plan_key``), for a captured graph of ``requests`` rows
+        over sequences of up to ``span`` positions."""
+        plans: Dict[object, object] = {}
+        for p in self.parts():
+            key = p.decode_plan_key() if hasattr(p, "decode_plan_key") else None
+            if key is not None and key not in plans:
+                plan = p.decode_plan(requests, span, self.rt)
+                if plan is not None:
+                    plans[key] = plan
+        return plans
+
     def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
         self.rt = rt
         self.embedding.load(tensors, rt)

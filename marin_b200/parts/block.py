@@ -35,6 +35,21 @@ class PreNormBlock(Part):
             p.load(tensors, rt)
         self.rt = rt
 
+    def weight_bytes(self, dtype) -> int:
+        return sum(p.weight_bytes(dtype) for p in self.parts())
+
+    def bytes_read(self, tokens: int, dtype) -> int:
+        return sum(p.bytes_read(tokens, dtype) for p in self.parts())
+
+    def flops(self, tokens: int, pairs: int = 0) -> float:
+        return sum(p.flops(tokens, pairs) for p in self.parts())
+
+    def kernel_jobs(self, dtype) -> Dict[str, tuple]:
+        jobs: Dict[str, tuple] = {}
+        for p in self.parts():
+            jobs.update(p.kernel_jobs(dtype))
+        return jobs
+
     #: ``forward`` takes ``x_in`` / ``next_block`` and returns the next block's input (see there)
     chains_norm = True
 

@@ -6,7 +6,7 @@ from typing import Dict, List, Optional
 import torch
 
 from ..kernels import ops
-from .base import Part, Runtime
+from .base import Part, Runtime, element_size
 from .registry import register_embedding, register_head
 from .spec import TensorSpec
 
@@ -25,6 +25,9 @@ class TokenEmbedding(Part):
 
     def load(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
         self.table = rt.matrix(tensors.pop(f"{self.name}.weight"))
+
+    def bytes_read(self, tokens: int, dtype: torch.dtype) -> int:
+        return tokens * self.hidden * element_size(dtype)          # only the rows asked for leave memory
 
     def forward(self, ids: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         ops.embed(ids, self.table, out)
@@ -49,6 +52,13 @@ class LinearHead(Part):
 
     def tie(self, table: torch.Tensor) -> None:
         self.weight = table
+
+    def bytes_read(self, tokens: int, dtype: torch.dtype) -> int:
+        return self.vocab * self.hidden * element_size(dtype)      # tied or not, the whole matrix is read
+
+    def flops(self, tokens: int, pairs: int = 0) -> float:
+        """``tokens`` counts the rows whose logits are wanted."""
+        return 2.0 * tokens * self.vocab * self.hidden
 
     def forward(self, rows: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         ops.gemm(rows, self.weight, out)

@@ -20,6 +20,9 @@ class FeedForward(Part):
     #: True if ``forward`` takes ``x`` as ``ops.NormedRows`` too, and a keyword ``then_norm`` (an ``ops.NormOut``),
     #: returning ``ops.NormedRows`` if its last product carried that norm and None otherwise (see ``Mixer``).
     couples_norm = False
+    #: as ``Mixer.capturable``: single-token steps launch the same kernels whatever the batch holds, without a wait
+    #: on the host (a routed feed-forward that reads its routing back to the host says False)
+    capturable = True
 
     def forward(self, x: torch.Tensor, ctx, residual: torch.Tensor) -> None:
         raise NotImplementedError

@@ -21,7 +21,7 @@ from typing import Dict, List, Optional, Tuple
 import torch
 
 from ..kernels import ops
-from .base import Part, Runtime
+from .base import Part, Runtime, element_size
 from .registry import lookup, register_mixer
 from .spec import PartSpec, TensorSpec
 
@@ -35,6 +35,15 @@ class PagedKV:
     head_dim: int
     window: Optional[int] = None
 
+    def bytes_per_token(self, dtype: torch.dtype) -> int:
+        """Bytes one position of one layer holds in the cache (keys and values)."""
+        return 2 * self.kv_heads * self.head_dim * element_size(dtype)
+
+    def bytes_read(self, context: int, dtype: torch.dtype) -> int:
+        """Bytes one decoded token reads of a sequence of ``context`` positions."""
+        kept = context if self.window is None else min(context, self.window)
+        return kept * self.bytes_per_token(dtype)
+
 
 @dataclass(frozen=True)
 class StateNeed:
@@ -43,14 +52,39 @@ class StateNeed:
     shape: Tuple[int, ...]
     dtype: torch.dtype = torch.float32
 
+    def bytes(self) -> int:
+        count = 1
+        for s in self.shape:
+            count *= int(s)
+        return count * element_size(self.dtype)
+
+    def bytes_read(self, context: int, dtype: torch.dtype) -> int:
+        return self.bytes()
+
 
 class Mixer(Part):
     #: True if ``forward`` takes ``x`` as ``ops.NormedRows`` too, and a keyword ``then_norm`` (an ``ops.NormOut``:
     #: the norm wanted of the updated residual), returning ``ops.NormedRows`` if its last product carried that norm
     #: and None otherwise.  A block couples norms only between parts that both say so.
     couples_norm = False
+    #: True if a step in which every request brings one token may be captured in a CUDA graph and replayed for other
+    #: requests of the same number: ``forward`` then launches the same kernels whatever the lengths and slots are,
+    #: reads them from ``ctx``'s device tensors only (never ``ctx.spans`` or another host value), and waits for
+    #: nothing on the host.  The step function captures graphs only for models whose parts all say so.  Rows that
+    #: pad a captured batch stand for empty requests: length 0, the spare state slot (see ``CacheManager``).
+    capturable = True
 
     def cache_need(self):
+        return None
+
+    def decode_plan_key(self):
+        """Mixers that answer the same (hashable) key share one decode plan per captured graph; None: no plan."""
+        return None
+
+    def decode_plan(self, requests: int, span: int, rt: Runtime):
+        """What this mixer fixes ahead for single-token steps of ``requests`` requests whose sequences are at most
+        ``span`` long: how it splits the work and the scratch memory it then needs.  A captured graph owns the plan;
+        ``forward`` finds it as ``ctx.decode_plans[self.decode_plan_key()]``."""
         return None
 
     def forward(self, x: torch.Tensor, ctx, cache, residual: torch.Tensor) -> None:
@@ -111,6 +145,19 @@ class GQAttention(Mixer):
 
     couples_norm = True
 
+    def flops(self, tokens: int, pairs: int = 0) -> float:
+        """The four projections, and per (query, key) pair a score and a weighted value of ``head_dim`` each."""
+        return super().flops(tokens, pairs) + 4.0 * pairs * self.heads * self.head_dim
+
+    def kernel_jobs(self, dtype) -> Dict[str, tuple]:
+        return ops.attention_jobs(dtype, self.heads, self.kv_heads, self.head_dim)
+
+    def decode_plan_key(self):
+        return ("paged_attention", self.heads, self.kv_heads, self.head_dim)
+
+    def decode_plan(self, requests: int, span: int, rt: Runtime):
+        return ops.decode_plan(rt.device, rt.dtype, requests, self.heads, self.kv_heads, self.head_dim, span)
+
     def forward(self, x, ctx, cache, residual: torch.Tensor, then_norm=None):
         T = x.shape[0]
         ws = ctx.workspace
@@ -130,6 +177,7 @@ class GQAttention(Mixer):
                 cache.k, cache.v, self.heads, self.kv_heads, self.head_dim, writes,
             )
         out = ws.get("attn_out", (T, self.q_dim), x.dtype)
+        plans = ctx.decode_plans
         ops.attention(q, cache.k, cache.v, out, ctx, cache.block_table, self.heads, self.kv_heads,
-                      self.head_dim, self.scale, self.window or 0)
+                      self.head_dim, self.scale, self.window or 0, plans.get(self.decode_plan_key()) if plans else None)
         return ops.gemm(out, self.w_o, residual, accumulate=True, then_norm=then_norm)

@@ -13,7 +13,8 @@ from __future__ import annotations
 
 import json
 import os
-from typing import Dict, Iterable, List, Sequence, Tuple
+import sys
+from typing import Dict, Iterable, List, Optional, Sequence, Tuple
 
 import torch
 
@@ -85,8 +86,10 @@ class Checkpoint:
             f.close()
 
 
-def check(ckpt: Checkpoint, expected: Iterable[TensorSpec], ignorable: Sequence[str] = ()) -> List[str]:
-    """Every mismatch between the checkpoint and the expected tensors, as readable lines."""
+def check(ckpt: Checkpoint, expected: Iterable[TensorSpec], ignorable: Sequence[str] = (),
+          extras: Optional[List[str]] = None) -> List[str]:
+    """Every mismatch between the checkpoint and the expected tensors, as readable lines.  Tensors of the checkpoint
+    that the model does not know are problems too, unless ``extras`` is a list: their names then go there."""
     problems: List[str] = []
     wanted = {}
     for spec in expected:
@@ -103,17 +106,34 @@ def check(ckpt: Checkpoint, expected: Iterable[TensorSpec], ignorable: Sequence[
         if info.dtype not in ok:
             problems.append(f"tensor `{name}` is {info.dtype} but expected one of {sorted(ok)}")
     for name in sorted(have - set(wanted) - set(ignorable)):
-        problems.append(f"unexpected tensor `{name}` {list(ckpt.info(name).shape)}")
+        if extras is not None:
+            extras.append(name)
+        else:
+            problems.append(f"unexpected tensor `{name}` {list(ckpt.info(name).shape)}")
     return problems
 
 
-def load_tensors(model_dir: str, expected: Sequence[TensorSpec], ignorable: Sequence[str] = ()) -> Dict[str, torch.Tensor]:
-    """name → CPU tensor in its stored dtype (ints as int32), after the checkpoint passed ``check``."""
+def load_tensors(model_dir: str, expected: Sequence[TensorSpec], ignorable: Sequence[str] = (), extra_tensors: str = "error",
+                 ignored: Optional[List[str]] = None) -> Dict[str, torch.Tensor]:
+    """name → CPU tensor in its stored dtype (ints as int32), after the checkpoint passed ``check``.
+
+    ``extra_tensors`` says what tensors the model does not know are: ``"error"`` (the default) lists them in the one
+    ``WeightError`` with everything else that is wrong; ``"warn"`` leaves them unread, appends their names to
+    ``ignored`` if a list is given and says so once on stderr (the reference reads only what it expects and ignores
+    the rest: crates/model/src/qwen3/weight_bytes.rs:9-10)."""
+    if extra_tensors not in ("error", "warn"):
+        raise ValueError(f"extra_tensors must be 'error' or 'warn', got {extra_tensors!r}")
     ckpt = Checkpoint(model_dir)
     try:
-        problems = check(ckpt, expected, ignorable)
+        extras: Optional[List[str]] = [] if extra_tensors == "warn" else None
+        problems = check(ckpt, expected, ignorable, extras)
         if problems:
             raise WeightError(problems, model_dir)
+        if extras:
+            shown = ", ".join(f"`{n}`" for n in extras[:MAX_LISTED]) + (f" and {len(extras) - MAX_LISTED} more" if len(extras) > MAX_LISTED else "")
+            print(f"[marin_b200] {model_dir}: {len(extras)} tensor(s) the model does not know were left unread: {shown}", file=sys.stderr)
+            if ignored is not None:
+                ignored.extend(extras)
         out: Dict[str, torch.Tensor] = {}
         for spec in expected:
             t = ckpt.read(spec.name)

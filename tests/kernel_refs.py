@@ -79,7 +79,7 @@ def qk_norm_rope_write(qkv, q_out, q_weight, k_weight, eps, positions, inv_freq,
     v_cache[page, :, off, :] = v[ok].to(v_cache.dtype)
 
 
-def attention(q, k_cache, v_cache, out, ctx, block_table, H, K, d, scale, window=0):
+def attention(q, k_cache, v_cache, out, ctx, block_table, H, K, d, scale, window=0, plan=None):
     T = q.shape[0]
     page_size = k_cache.shape[2]
     group = H // K

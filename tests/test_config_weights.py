@@ -141,6 +141,52 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
     assert "unexpected tensor `model.layers.7.extra.weight` [3]" in text
 
 
+def test_unknown_tensors_may_be_left_unread_on_request(tmp_path, capsys):
+    """``extra_tensors="warn"``: tensors the model does not know are named once and skipped (the reference ignores
+    them: crates/model/src/qwen3/weight_bytes.rs:9-10); what is missing or mis-shaped is an error all the same."""
+    from marin_b200.config import Qwen3Config
+    from marin_b200.models import Model, architecture_of
+    from marin_b200.weights import WeightError, load_tensors, random_tensors, write_safetensors
+
+    cfg = Qwen3Config.from_dict(TINY_A)
+    model = Model(architecture_of(cfg).build_spec(cfg))
+    d = str(tmp_path / "extras")
+    os.makedirs(d)
+    tensors = dict(random_tensors(cfg, 1))
+    tensors["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.zeros(8, dtype=torch.float32)
+    write_safetensors(os.path.join(d, "model.safetensors"), tensors.items())
+    with pytest.raises(WeightError, match="unexpected tensor `model.layers.0.self_attn.rotary_emb.inv_freq`"):
+        load_tensors(d, model.tensor_specs(), model.spec.ignorable)
+    ignored = []
+    got = load_tensors(d, model.tensor_specs(), model.spec.ignorable, "warn", ignored)
+    assert ignored == ["model.layers.0.self_attn.rotary_emb.inv_freq"] and ignored[0] not in got
+    assert "1 tensor(s) the model does not know were left unread" in capsys.readouterr().err
+    del tensors["model.norm.weight"]
+    write_safetensors(os.path.join(d, "model.safetensors"), tensors.items())
+    with pytest.raises(WeightError, match="1 problem"):
+        load_tensors(d, model.tensor_specs(), model.spec.ignorable, "warn")
+    with pytest.raises(ValueError, match="extra_tensors"):
+        load_tensors(d, model.tensor_specs(), model.spec.ignorable, "ignore")
+
+
+def test_a_shape_whose_product_overflows_is_refused(tmp_path):
+    """A crafted header whose sizes multiply past 64 bits must not wrap around into a product that matches its bytes."""
+    from marin_b200.weights import SafetensorsError
+    from marin_b200.weights.safetensors_io import SafetensorsFile
+
+    path = str(tmp_path / "overflow.safetensors")
+    for shape in ([1 << 33, 1 << 33, 4], [1 << 59, 8], [3, 1 << 40], [1 << 32, 1 << 32]):
+        header = json.dumps({"w": {"dtype": "F32", "shape": shape, "data_offsets": [0, 64]}}).encode()
+        with open(path, "wb") as fh:
+            fh.write(struct.pack("<Q", len(header)) + header + b"\0" * 64)
+        with pytest.raises(SafetensorsError, match="more elements than the file has bytes"):
+            SafetensorsFile(path)
+    header = json.dumps({"w": {"dtype": "F32", "shape": [0, 1 << 59], "data_offsets": [0, 0]}}).encode()     # empty: fine
+    with open(path, "wb") as fh:
+        fh.write(struct.pack("<Q", len(header)) + header)
+    assert tuple(SafetensorsFile(path).tensors["w"].shape) == (0, 1 << 59)
+
+
 def test_tied_model_may_carry_an_unused_head(tmp_path):
     from marin_b200.config import Qwen3Config
     from marin_b200.models import Model, architecture_of

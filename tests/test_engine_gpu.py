@@ -217,30 +217,31 @@ def test_steps_packed_ahead_change_nothing(case):
 
 
 def test_a_wait_that_gave_up_is_reported(case):
-    """Kernels bound their waits and leave a code on the device when one gives up; the engine reads it every few
-    steps and at the end of a generation and raises.  The code is planted here (nothing on the GPU is made to fail)."""
-    if case.name != "A" or case.dtype != "bfloat16":
-        pytest.skip("one configuration is enough")
+    """Kernels bound their waits and leave a code on the device when one gives up; the sampling kernel that ends a step
+    copies it beside the sampled ids, so the engine learns of it with the very step it happened in and raises.  The
+    code is planted here (nothing on the GPU is made to fail)."""
+    if case.name not in "AD" or case.dtype != "bfloat16":
+        pytest.skip("two configurations are enough")
     from marin_b200 import Engine, SamplingParams
-    from marin_b200.kernels import ops
     from marin_b200.kernels.ops import KernelError
 
     engine = Engine(case.dir, dtype=case.dtype, ctx=case.raw["max_position_embeddings"], page_size=case.page, max_batch=2, token_budget=16)
     engine.generate([[1, 2, 3]], SamplingParams(temperature=0.0, max_tokens=3))
-    flag = ops._gemm_scratch(engine.rt.device)["error"]
+    flag = engine.runner.scratch.error
     flag.fill_(13)
     with pytest.raises(KernelError, match="13"):
         engine.generate([[1, 2, 3]], SamplingParams(temperature=0.0, max_tokens=3))
-    assert int(flag.item()) == 0                              # read and cleared
-    for rid in list(engine.cache.requests):                   # the failed generation's request is still live: end it
-        engine.scheduler.cancel(rid)
-    engine.CHECK_EVERY = 2
-    rid = engine.add_request([4, 5, 6], SamplingParams(temperature=0.0, max_tokens=8))
+    assert int(flag.item()) == 0 and int(engine.runner.scratch.report[0].item()) == 0      # read and cleared
+    engine.cache.check()
+    assert not engine.cache.requests                          # the failed generation left nothing behind
+    # the add_request / step way: the step after the flag is raised sees it, whether it samples eagerly or from a graph
+    engine.add_request([4, 5, 6], SamplingParams(temperature=0.0, max_tokens=8))
+    engine.step()
     engine.step()
     flag.fill_(14)
     with pytest.raises(KernelError, match="14"):
-        for _ in range(4):
-            engine.step()
+        engine.step()
+    engine.check_device()                                     # nothing is left to report
 
 
 def test_schedule_may_repeat_a_layer_and_share_a_cache(case):

@@ -530,11 +530,11 @@ def test_decode_chain_replayed_from_a_graph(ops, H, K, d, page):
     ctx = SimpleNamespace(positions=positions, req_index=torch.arange(B, dtype=torch.int32, device=DEV),
                           cu_tokens=torch.arange(B + 1, dtype=torch.int32, device=DEV), seq_lens=torch.zeros(B, dtype=torch.int32, device=DEV),
                           num_tokens=B, num_requests=B, num_decode=B, max_query_len=1, max_seq_len=max(first) + steps + 1)
-    ctx.attn_split = ops.decode_split(B, K, 256)
+    plan = ops.DecodePlan(*ops.decode_split(B, K, 256))
 
     def chain():
         ops.qk_norm_rope_write(qkv, q, qw, kw, 1e-6, positions, inv_freq, d, False, slots, kc, vc, H, K, d)
-        ops.attention(q, kc, vc, out, ctx, perm, H, K, d, 1.0 / math.sqrt(d), 0)
+        ops.attention(q, kc, vc, out, ctx, perm, H, K, d, 1.0 / math.sqrt(d), 0, plan)
 
     def set_step(i):
         pos = torch.tensor([f + i for f in first], dtype=torch.int32, device=DEV)
@@ -575,12 +575,12 @@ def test_attention_decode_in_clusters_of_more_than_eight(ops, H, K, d, page, spl
     q, kc, vc, table, ctx = paged_case(g, torch.bfloat16, lens_new, H, K, d, page, pages)
     chunks = -(-(longest + 1) // split)
     assert 8 < chunks <= 16
-    ctx.attn_split = (split, chunks)
+    plan = ops.DecodePlan(split, chunks)
     want = torch.empty_like(q)
     ref.attention(q, kc, vc, want, ctx, table, H, K, d, 1.0 / math.sqrt(d), 0)
     for _ in range(2):
         out = torch.full_like(q, float("nan"))
-        ops.attention(q, kc, vc, out, ctx, table, H, K, d, 1.0 / math.sqrt(d), 0)
+        ops.attention(q, kc, vc, out, ctx, table, H, K, d, 1.0 / math.sqrt(d), 0, plan)
         ops.check_device_errors()
         torch.testing.assert_close(out.float(), want.float(), rtol=2e-2, atol=2e-2)
 
@@ -595,12 +595,12 @@ def test_attention_decode_with_more_chunks_than_a_cluster_holds(ops, H, K, d, pa
     q, kc, vc, table, ctx = paged_case(g, torch.bfloat16, lens_new, H, K, d, page, pages)
     chunks = -(-1501 // split)
     assert chunks > 16
-    ctx.attn_split = (split, chunks)
+    plan = ops.DecodePlan(split, chunks)
     want = torch.empty_like(q)
     ref.attention(q, kc, vc, want, ctx, table, H, K, d, 1.0 / math.sqrt(d), 0)
     for _ in range(2):
         out = torch.full_like(q, float("nan"))
-        ops.attention(q, kc, vc, out, ctx, table, H, K, d, 1.0 / math.sqrt(d), 0)
+        ops.attention(q, kc, vc, out, ctx, table, H, K, d, 1.0 / math.sqrt(d), 0, plan)
         ops.check_device_errors()
         torch.testing.assert_close(out.float(), want.float(), rtol=2e-2, atol=2e-2)
 

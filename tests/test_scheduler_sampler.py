@@ -284,3 +284,18 @@ def test_sampler_errors():
         s.sample(np.array([1.0, float("nan")], np.float32))
     with pytest.raises(SamplerError, match="candidates"):
         s.sample(np.array([1.0, 2.0], np.float32), usable=0)
+
+
+def test_a_negative_token_ends_its_request_as_non_finite_and_the_others_go_on():
+    """The sampler answers -1 for a row whose logits were not finite: that request ends, nothing is emitted for it,
+    its pages go back, and the requests beside it are untouched."""
+    s, cache = sched()
+    s.add(Request("a", [1, 2, 3], greedy(6)))
+    s.add(Request("b", [4, 5], greedy(4)))
+    run(s, cache, next_token=lambda r: -1 if r.req_id == "a" and len(r.output) == 2 else len(r.tokens))
+    a = next(r for r in s.finished if r.req_id == "a")
+    b = next(r for r in s.finished if r.req_id == "b")
+    assert a.stop == StopReason.NON_FINITE_LOGITS and len(a.output) == 2
+    assert b.stop == StopReason.MAX_TOKENS and len(b.output) == 4
+    cache.check()
+    assert all(g.pool.num_held == 0 for g in cache.groups)
