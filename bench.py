@@ -62,13 +62,26 @@ class ClockSampler:
     QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self):
-        self.rows, self.proc = [], None
+    def __init__(self, gpu="0"):
+        self.rows, self.proc, self.gpu = [], None, str(gpu)
+
+    @staticmethod
+    def gpu_in_use():
+        """What nvidia-smi should be asked about: the device this process computes on (its UUID), not index 0 of the
+        box, which may be another job's GPU."""
+        import torch
+
+        try:
+            uuid = str(torch.cuda.get_device_properties(torch.cuda.current_device()).uuid)
+            return uuid if uuid.startswith("GPU-") else "GPU-" + uuid
+        except Exception:  # noqa: BLE001 - an older torch without the field: the first visible device
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES", "").split(",")[0].strip()
+            return visible or "0"
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", self.gpu, f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
             self.proc = None
@@ -96,7 +109,7 @@ class ClockSampler:
                     reasons.add(name)
         busy = [c for c in sm if smax and c > 0.5 * smax] or sm
         return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": smax, "reasons": sorted(reasons),
-                "samples": len(sm)}
+                "samples": len(sm), "samples_under_load": len(busy), "gpu": self.gpu}
 
 
 def model_bytes_and_flops(engine, batch, tokens):
@@ -272,9 +285,14 @@ def main() -> int:
     weight_bytes, prefill_flops = model_bytes_and_flops(engine, args.batch, PREFILL_TOKENS)
     kv_tok = kv_bytes_per_token(engine)
 
-    clocks = ClockSampler()
+    clocks = ClockSampler(ClockSampler.gpu_in_use())
     clocks.start()
     main_run = decode_device(engine, args.batch, args.steps, warmup, CONTEXT)
+    # the timed steps last a fraction of a second; the same steps run on (untimed) until the sampler has seen about two
+    # seconds of this load, so that the median clock rests on tens of readings
+    load_until = time.perf_counter() + 2.0
+    while time.perf_counter() < load_until:
+        decode_device(engine, args.batch, args.steps, 3, CONTEXT)
     clock_record = clocks.stop()
 
     step_bytes = weight_bytes + args.batch * main_run["mean_context"] * kv_tok

@@ -884,6 +884,19 @@ static int persistent_dispatch(const void* x, const void* w, void* out, int mode
     }
 }
 
+// The number of SMs of the device that is current, asked once per device.
+static int sm_count_of_current_device() {
+    static int known[64];
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return 0;
+    if (known[device] == 0) {
+        int sms = 0;
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return 0;
+        known[device] = sms;
+    }
+    return known[device];
+}
+
 // The persistent kernel: bn tokens per tile (a multiple of 16 from 128 to 256), `ctas` CTAs (one per SM).
 MB_API int mb_gemm_tc_persistent(const void* x, const void* w, void* out, int mode, int T, int N, int K, int bn, int ctas,
                                  int* error_flag, cudaStream_t s) {
@@ -899,11 +912,8 @@ MB_API int mb_gemm_tc_persistent_streamk(const void* x, const void* w, void* out
                                          float* partials, long long partials_floats, int* flags, int* error_flag, cudaStream_t s) {
     if (T <= 0 || N <= 0) return 0;
     if (partials == nullptr || flags == nullptr || bn <= 0 || ctas <= 0) return MB_ERR_BAD_SIZE;
-    static int sms = 0;                                            // of the device of the first call: all devices of a box are alike
-    if (sms == 0) {
-        int device = 0;
-        if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return MB_ERR_BAD_SIZE;
-    }
+    const int sms = sm_count_of_current_device();                  // a CTA may wait for its neighbour: all must be resident
+    if (sms <= 0) return MB_ERR_BAD_SIZE;
     const int tiles_n = (N + TC_BM - 1) / TC_BM, tiles_t = (T + bn - 1) / bn;
     if (ctas > sms || tiles_t > ctas || tiles_n < ctas / tiles_t || partials_floats < (long long)ctas * bn * TC_BM) return MB_ERR_BAD_SIZE;
     return persistent_dispatch(x, w, out, mode, T, N, K, bn, ctas, error_flag, TcNormOut{}, TcRowScale{}, TcStreamK{partials, flags, 0}, s);
@@ -1017,10 +1027,13 @@ MB_API int mb_gemm_tc_heads(const void* x, const void* w, int T, int N, int K, i
 static __device__ __align__(256) unsigned char mb_noalloc_scratch[MB_NOALLOC_SCRATCH_BYTES];
 
 #define MB_NOALLOC_MAX_DEVICES 64
-static unsigned char* noalloc_base[MB_NOALLOC_MAX_DEVICES];     // per device, filled at its first call
+// Per device, filled at its first call.  Nothing guards these: two threads that make a device's first call at the same
+// time both write the same values, which is harmless, but the header asks callers to make that first call alone.
+static unsigned char* noalloc_base[MB_NOALLOC_MAX_DEVICES];
+static int noalloc_sms[MB_NOALLOC_MAX_DEVICES];
 static thread_local char noalloc_message[256] = "";
 
-static int noalloc_setup(unsigned char** base) {
+static int noalloc_setup(unsigned char** base, int* sms = nullptr) {
     int device = -1;
     cudaError_t e = cudaGetDevice(&device);
     if (e != cudaSuccess) return (int)e;
@@ -1036,9 +1049,17 @@ static int noalloc_setup(unsigned char** base) {
                      cudaGetErrorString(e));
             return e != cudaSuccess ? (int)e : MB_ERR_NOALLOC_SETUP;
         }
+        int count = 0;
+        e = cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device);
+        if (e != cudaSuccess || count <= 0) {
+            snprintf(noalloc_message, sizeof noalloc_message, "the SM count of device %d could not be read: %s", device, cudaGetErrorString(e));
+            return e != cudaSuccess ? (int)e : MB_ERR_NOALLOC_SETUP;
+        }
+        noalloc_sms[device] = count;
         noalloc_base[device] = (unsigned char*)p;
     }
     *base = noalloc_base[device];
+    if (sms != nullptr) *sms = noalloc_sms[device];
     return 0;
 }
 
@@ -1048,9 +1069,12 @@ MB_API int mb_gemm_tc_noalloc_device_error(void) {
     unsigned char* base = nullptr;
     if (noalloc_setup(&base) != 0) return -1;
     int* flag = (int*)(base + (size_t)MB_NOALLOC_MAX_PARTIALS * 4 + (size_t)MB_NOALLOC_MAX_TILES * 4);
+    // Wait for the whole device, not for the legacy default stream alone: a copy on that stream does not wait for
+    // kernels on streams created as non-blocking, which is what most callers' streams are.
+    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
     int value = 0;
     if (cudaMemcpy(&value, flag, sizeof value, cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
-    if (value != 0) cudaMemset(flag, 0, sizeof value);
+    if (value != 0 && cudaMemset(flag, 0, sizeof value) != cudaSuccess) return -1;   // the device is idle: nothing races with this
     return value;
 }
 
@@ -1058,13 +1082,20 @@ MB_API int mb_gemm_tc_noalloc(const void* x, const void* w, void* out, int mode,
     noalloc_message[0] = 0;
     if (T <= 0 || N <= 0) return 0;
     if (K <= 0) return MB_ERR_BAD_SIZE;
-    // the same plan the Python wrapper makes: tokens per CTA, then K slices if there are fewer tiles than SMs
+    unsigned char* base = nullptr;
+    int sms = 0;
+    int rc = noalloc_setup(&base, &sms);
+    if (rc != 0) return rc;
+    // A plan of this entry point's own (the Python wrapper plans for clusters of 2, 4 or 8 CTAs that reduce through
+    // shared memory; here the slices reduce through the built-in scratch, so up to 16 are taken): tokens per CTA by
+    // the number of tokens, then K slices while there are fewer tiles than SMs, about two CTAs per SM in all, each
+    // slice at least four k-blocks long.
     const int bn = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : 128;
     const long long tiles = (long long)((N + TC_BM - 1) / TC_BM) * ((T + bn - 1) / bn);
     const int total_kb = (K + TC_BK - 1) / TC_BK;
     int splits = 1;
-    if (tiles < 148) {
-        splits = (int)(296 / tiles);
+    if (tiles < sms) {
+        splits = (int)(2 * sms / tiles);
         if (splits > total_kb / 4) splits = total_kb / 4;
         if (splits > 16) splits = 16;
         if (splits < 1) splits = 1;
@@ -1083,9 +1114,6 @@ MB_API int mb_gemm_tc_noalloc(const void* x, const void* w, void* out, int mode,
             return MB_ERR_NOALLOC_TOO_LARGE;
         }
     }
-    unsigned char* base = nullptr;
-    int rc = noalloc_setup(&base);
-    if (rc != 0) return rc;
     float* partials = (float*)base;
     int* counters = (int*)(base + (size_t)MB_NOALLOC_MAX_PARTIALS * 4);
     int* error_flag = counters + MB_NOALLOC_MAX_TILES;

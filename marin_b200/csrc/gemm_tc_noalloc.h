@@ -21,7 +21,9 @@
 //    MB_ERR_NOALLOC_TOO_LARGE before anything is launched; mb_gemm_tc_noalloc_last_error() says
 //    which limit and by how much.  (With one K slice no scratch is used and any size is accepted.)
 //  * The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
-//    that device current).  Make that first call outside any stream capture.
+//    that device current) and the device's SM count.  Make that first call outside any stream
+//    capture, and from one thread: nothing guards the per-device set-up against two first calls
+//    at the same time (both would store the same values).
 //  * All calls share the one array, and it keeps what the last call left.  The tile counters are
 //    cleared on the call's stream before each launch.  Two calls that overlap on the GPU (different
 //    streams without an ordering between them) race on the scratch and give wrong results: order them.
@@ -48,7 +50,9 @@ int mb_gemm_tc_noalloc(const void* x, const void* w, void* out, int mode, int T,
 const char* mb_gemm_tc_noalloc_last_error(void);
 
 // Non-zero if a kernel launched through mb_gemm_tc_noalloc on the current device gave up a wait since the
-// last call of this function (synchronises the device to read the flag, then clears it).
+// last call of this function; -1 if the device could not be asked.  It waits for ALL work on the device
+// (cudaDeviceSynchronize), whatever streams the products ran on, reads the flag and clears it; do not
+// call it while other threads launch products on the same device.
 int mb_gemm_tc_noalloc_device_error(void);
 
 #ifdef __cplusplus

@@ -243,9 +243,15 @@ class Runner:
             ctx.decode_plans = g["plans"]
             return self.model.forward(ctx, self.views)
 
+        # Warm up: builds kernels, sizes the workspace.  The step runs for real here and once more when the captured
+        # graph is first replayed.  Keys and values are written to the same places with the same values both times;
+        # per-request state is not like that (a recurrence would advance twice), so it is put back after the warm-up.
+        kept = {i: t.clone() for i, t in self.cache.state.items()}
         with ops.using(self.scratch):
-            run()                                # warm up: builds kernels, sizes the workspace
+            run()
         torch.cuda.synchronize()
+        for i, t in kept.items():
+            self.cache.state[i].copy_(t)
         graph = torch.cuda.CUDAGraph()
         ctx = self.build_context(entries, pad_to=bucket, static=g["static"])
         ctx.workspace = g["workspace"]

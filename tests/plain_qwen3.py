@@ -46,6 +46,15 @@ def read_weights(model_dir: str, dtype=torch.float32) -> Dict[str, torch.Tensor]
     return {k: v.to(dtype) for k, v in load_file(os.path.join(model_dir, "model.safetensors")).items()}
 
 
+def as_bf16(x: torch.Tensor) -> torch.Tensor:
+    """Rounds to bfloat16 and back: what a value loses when it is stored in 16 bits between two kernels."""
+    return x.to(torch.bfloat16).to(torch.float32)
+
+
+def same(x: torch.Tensor) -> torch.Tensor:
+    return x
+
+
 def embed(ids: Sequence[int], table: torch.Tensor) -> torch.Tensor:
     """hidden[t] = table[ids[t]], no scaling (crates/model/src/qwen3/model.rs:133-153)."""
     return table[torch.as_tensor(list(ids), dtype=torch.long)]
@@ -83,10 +92,11 @@ def softmax(scores: torch.Tensor) -> torch.Tensor:
     return e / e.sum(dim=-1, keepdim=True)
 
 
-def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window: Optional[int] = None) -> torch.Tensor:
+def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window: Optional[int] = None, stored=same) -> torch.Tensor:
     """q: [T, H, d], k/v: [T, K, d].  Query head h reads kv head h // (H/K); scale 1/sqrt(d);
     token t sees positions 0..=t (crates/tensor/src/attention.rs:148-169).  ``window`` (not part
-    of Qwen3) limits this to the last ``window`` positions."""
+    of Qwen3) limits this to the last ``window`` positions.  ``stored`` is applied to the terms of
+    the softmax before they meet the values (see ``forward``)."""
     T, H, d = q.shape
     K = k.shape[1]
     group = H // K
@@ -100,56 +110,69 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window: Optiona
         if window is not None:
             mask |= idx[None, :] < (idx[:, None] - window + 1)
         scores = scores.masked_fill(mask, float("-inf"))
-        out[:, h, :] = softmax(scores) @ v[:, kh, :]
+        if stored is same:
+            out[:, h, :] = softmax(scores) @ v[:, kh, :]
+        else:
+            # a 16-bit engine sums exp(s - m) in float32 but hands the terms to the value product in 16 bits
+            e = torch.exp(scores - scores.max(dim=-1, keepdim=True).values)
+            out[:, h, :] = (stored(e) @ v[:, kh, :]) / e.sum(dim=-1, keepdim=True)
     return out
 
 
-def swiglu_mlp(x: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor) -> torch.Tensor:
+def swiglu_mlp(x: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor, stored=same) -> torch.Tensor:
     """down( g / (1 + exp(-g)) * u ) (crates/model/src/qwen3/mlp.rs:22-37, crates/tensor/src/silu.rs:18)."""
     g, u = linear(x, gate), linear(x, up)
-    return linear(g / (1.0 + torch.exp(-g)) * u, down)
+    return linear(stored(g / (1.0 + torch.exp(-g)) * u), down)
 
 
 def layer_forward(cfg: dict, w: Dict[str, torch.Tensor], n: int, hidden: torch.Tensor,
-                  window: Optional[int] = None, kv_from=None):
+                  window: Optional[int] = None, kv_from=None, stored=same):
     """One pre-norm block (crates/model/src/qwen3/layer.rs:56-103): norm, q/k/v, per-head q/k norm
     before the rotation, causal attention, o_proj + residual, norm, SwiGLU + residual.  Returns the
-    new hidden state and the (k, v) it attended over; ``kv_from`` makes it attend over given k, v."""
+    new hidden state and the (k, v) it attended over; ``kv_from`` makes it attend over given k, v.
+    ``stored`` is applied to every value that a 16-bit engine keeps in 16 bits between two kernels (see ``forward``)."""
     p = f"model.layers.{n}."
     T = hidden.shape[0]
     H, K, d = cfg["heads"], cfg["kv_heads"], cfg["head_dim"]
     pos = torch.arange(T)
-    normed = rms_norm(hidden, w[p + "input_layernorm.weight"], cfg["eps"])
-    q = linear(normed, w[p + "self_attn.q_proj.weight"]).view(T, H, d)
-    q = rope(rms_norm(q, w[p + "self_attn.q_norm.weight"], cfg["eps"]), pos, cfg["theta"])
+    normed = stored(rms_norm(hidden, w[p + "input_layernorm.weight"], cfg["eps"]))
+    q = stored(linear(normed, w[p + "self_attn.q_proj.weight"])).view(T, H, d)
+    q = stored(rope(rms_norm(q, w[p + "self_attn.q_norm.weight"], cfg["eps"]), pos, cfg["theta"]))
     if kv_from is None:
-        k = linear(normed, w[p + "self_attn.k_proj.weight"]).view(T, K, d)
-        v = linear(normed, w[p + "self_attn.v_proj.weight"]).view(T, K, d)
-        k = rope(rms_norm(k, w[p + "self_attn.k_norm.weight"], cfg["eps"]), pos, cfg["theta"])
+        k = stored(linear(normed, w[p + "self_attn.k_proj.weight"])).view(T, K, d)
+        v = stored(linear(normed, w[p + "self_attn.v_proj.weight"])).view(T, K, d)
+        k = stored(rope(rms_norm(k, w[p + "self_attn.k_norm.weight"], cfg["eps"]), pos, cfg["theta"]))
     else:
         k, v = kv_from
-    ctx = attention(q, k, v, window).reshape(T, H * d)
+    ctx = stored(attention(q, k, v, window, stored).reshape(T, H * d))
     hidden = hidden + linear(ctx, w[p + "self_attn.o_proj.weight"])
-    normed = rms_norm(hidden, w[p + "post_attention_layernorm.weight"], cfg["eps"])
+    normed = stored(rms_norm(hidden, w[p + "post_attention_layernorm.weight"], cfg["eps"]))
     hidden = hidden + swiglu_mlp(normed, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"],
-                                 w[p + "mlp.down_proj.weight"])
+                                 w[p + "mlp.down_proj.weight"], stored)
     return hidden, (k, v)
 
 
 def forward(cfg: dict, w: Dict[str, torch.Tensor], ids: Sequence[int], schedule: Optional[List[tuple]] = None,
-            window: Optional[int] = None, return_hidden: bool = False):
+            window: Optional[int] = None, return_hidden: bool = False, stored=same):
     """Logits [T, vocab] after every token of one whole sequence
     (crates/model/src/qwen3/model.rs:81-131; the reference keeps only the last row).
-    ``schedule`` = [(layer, cache_of or None), ...] runs layers in another order (default 0..L-1)."""
+    ``schedule`` = [(layer, cache_of or None), ...] runs layers in another order (default 0..L-1).
+
+    ``stored=as_bf16`` gives the model as an engine computes it that keeps activations in bfloat16 between
+    kernels and everything else (sums, norms, softmax, the residual stream) in float32: the values the reference
+    formulas produce are rounded where such an engine stores them (after each norm, the q/k/v projections, the
+    per-head norm and rotation, the softmax terms, the attention output, the SwiGLU output).  Comparing a
+    bfloat16 engine with this leaves only the differences of summation order and of where exactly a factor is
+    applied, an order of magnitude less than the rounding itself."""
     hidden = embed(ids, w["model.embed_tokens.weight"])
     states = [hidden]
     schedule = schedule or [(n, None) for n in range(cfg["layers"])]
     kvs = []
     for layer, cache_of in schedule:
-        hidden, kv = layer_forward(cfg, w, layer, hidden, window, kvs[cache_of] if cache_of is not None else None)
+        hidden, kv = layer_forward(cfg, w, layer, hidden, window, kvs[cache_of] if cache_of is not None else None, stored)
         kvs.append(kv)
         states.append(hidden)
-    normed = rms_norm(hidden, w["model.norm.weight"], cfg["eps"])
+    normed = stored(rms_norm(hidden, w["model.norm.weight"], cfg["eps"]))
     head = w["model.embed_tokens.weight"] if cfg["tied"] else w["lm_head.weight"]
     logits = linear(normed, head)
     return (logits, states) if return_hidden else logits

@@ -681,3 +681,68 @@ def test_attention_tensor_core_prefill_matches_the_mma_kernel(ops, H, K, d, page
     ref.attention(q, kc, vc, want, ctx, table, H, K, d, scale, window)
     torch.testing.assert_close(mma.float(), want.float(), rtol=2e-2, atol=2e-2)
     torch.testing.assert_close(got.float(), want.float(), rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("H,K,d,page", [(8, 2, 128, 16), (4, 1, 64, 16), (6, 3, 128, 32)])
+def test_attention_tensor_core_prefill_of_long_portions_against_the_plain_twin(ops, H, K, d, page):
+    """The tcgen05 prefill kernel against the plain torch twin (not another kernel of the package) where a query tile
+    walks many 64-key blocks: portions of 300 to 2,000 tokens over 0 to 2,048 cached ones, so that the running maximum
+    moves and the accumulator is rescaled many times, and one portion behind 16,600 cached positions, whose keys lie on
+    more pages than the kernel's page-id cache in shared memory holds (1,024; the rest is read from global memory).
+    One key far back is made to stand out in each long request, so that a block skipped or weighted wrongly shows."""
+    g = torch.Generator(device=DEV).manual_seed(29)
+    lens_new = [(0, 2000), (2048, 300), (1500, 700), (0, 300)]
+    if page == 16:
+        lens_new.append((16600, 300))
+    pages = sum(-(-(c + n) // page) for c, n in lens_new) + 3
+    q, kc, vc, table, ctx = paged_case(g, torch.bfloat16, lens_new, H, K, d, page, pages)
+    # in every request, the key at position 5 of kv head 0 gets the direction of that request's last query (head 0),
+    # scaled so that its score towers over the others: the last rows must then return (nearly) that position's value
+    starts = ctx.cu_tokens.tolist()
+    for r in range(len(lens_new)):
+        last = q[starts[r + 1] - 1, :d].float()
+        page_id = int(table[r, 5 // page])
+        kc[page_id, 0, 5 % page] = (last / last.norm() * 16.0).to(torch.bfloat16)
+    got, want = torch.empty_like(q), torch.empty_like(q)
+    scale = 1.0 / math.sqrt(d)
+    ops.attention(q, kc, vc, got, ctx, table, H, K, d, scale, 0)
+    ops.check_device_errors()
+    ref.attention(q, kc, vc, want, ctx, table, H, K, d, scale, 0)
+    torch.testing.assert_close(got.float(), want.float(), rtol=2e-2, atol=2e-2)
+    for r in range(len(lens_new)):
+        row, page_id = starts[r + 1] - 1, int(table[r, 5 // page])
+        weight_on_far_key = float((got[row, :d].float() * vc[page_id, 0, 5 % page].float()).sum() / (vc[page_id, 0, 5 % page].float() ** 2).sum())
+        assert weight_on_far_key > 0.5, f"request {r}: the far key carries {weight_on_far_key:.2f} of the weight"
+
+
+def test_sampling_kernels_mark_rows_that_are_not_finite(ops):
+    """A NaN or an infinity among the usable logits of a row: arg-max and the sampler write the id -1 for that row
+    (the reference refuses it: crates/sampler/src/lib.rs:135-137); rows beside it are untouched, a bad value beyond
+    ``usable`` does not count, and the next launch finds the scratch clean."""
+    g = torch.Generator(device=DEV).manual_seed(33)
+    rows, vocab = 7, 50021
+    logits = torch.randn(rows, vocab, device=DEV, generator=g)
+    want = torch.argmax(logits[:, :50000], dim=-1).tolist()
+    logits[1, 49999] = float("nan")                 # the last usable value, seen by the last block of the row
+    logits[3, 0] = float("inf")                     # an infinity would win the comparison: it is refused all the same
+    logits[4, 31000] = float("-inf")
+    logits[5, 50010] = float("nan")                 # beyond usable: ignored
+    ids = torch.full((rows,), -7, dtype=torch.int32, device=DEV)
+    for _ in range(2):
+        ops.argmax(logits, 50000, ids)
+        got = ids.tolist()
+        assert [got[i] for i in (1, 3, 4)] == [-1, -1, -1]
+        assert [got[i] for i in (0, 2, 5, 6)] == [want[i] for i in (0, 2, 5, 6)]
+    clean = torch.randn(rows, vocab, device=DEV, generator=g)
+    ops.argmax(clean, 50000, ids)
+    assert ids.tolist() == torch.argmax(clean[:, :50000], dim=-1).tolist()
+    n = rows
+    usable = torch.full((n,), 50000, dtype=torch.int32, device=DEV)
+    temperature = torch.tensor([0.0, 0.8, 1.0, 0.0, 1.2, 0.7, 1.0], device=DEV)
+    top_k = torch.tensor([0, 5, 0, 0, 40, 0, 3], dtype=torch.int32, device=DEV)
+    top_p = torch.tensor([1.0, 0.9, 0.5, 1.0, 1.0, 0.9, 1.0], device=DEV)
+    u = torch.full((n,), 0.37, device=DEV)
+    ops.sample(logits, usable, temperature, top_k, top_p, u, ids)
+    got = ids.tolist()
+    assert [got[i] for i in (1, 3, 4)] == [-1, -1, -1] and got[0] == want[0] and all(0 <= got[i] < 50000 for i in (2, 5, 6))
+    ops.check_device_errors()

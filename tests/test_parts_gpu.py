@@ -156,8 +156,18 @@ def define_toy():
             self.w_in = tensors.pop(f"{self.name}.in_proj.weight").to(rt.device, torch.float32)
             self.w_out = tensors.pop(f"{self.name}.out_proj.weight").to(rt.device, torch.float32)
 
+        # single-token steps do the same work whatever the batch holds, all of it on the device and addressed through
+        # ctx's device tensors: such steps may be captured in a graph (rows that pad a batch use the spare slot)
+        capturable = True
+
         def forward(self, x, ctx, cache, residual):
             u = x.float() @ self.w_in.t()
+            if ctx.num_decode == ctx.num_requests:
+                slots = ctx.state_slots.long()
+                s = self.decay * cache.state.index_select(0, slots) + u
+                cache.state.index_copy_(0, slots, s)
+                residual += s @ self.w_out.t()
+                return
             y = torch.empty_like(u)
             for span in ctx.spans:
                 s = cache.state[span.slot].clone()
@@ -262,6 +272,22 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped(tmp_path):
     for rid in tokens:
         torch.testing.assert_close(got[rid].cpu(), want[rid], rtol=1e-4, atol=1e-4)
     cache.check()
+    # the same from captured graphs: whether a hybrid model's single-token steps can be captured is its mixers' answer
+    assert model.capturable()
+    runner.enable_graphs((1, 2, 4))
+    got = run_mixed(runner, tokens, mixed_schedule(random.Random(5), lengths, max_live=3, decode_tail=12))
+    assert any(g["graph"] is not None for g in runner.graphs.values()) and {b for b, _ in runner.graphs} >= {1, 2, 4}
+    for rid in tokens:
+        torch.testing.assert_close(got[rid].cpu(), want[rid], rtol=1e-4, atol=1e-4)
+    cache.check()
+    # a mixer that says it cannot be captured turns graphs off for its model, and only for its model
+    model.blocks[0].mixer.capturable = False
+    try:
+        plain_runner = Runner(model, cache, rt, 96)
+        plain_runner.enable_graphs((1, 2, 4))
+        assert not getattr(plain_runner, "graph_sizes", None)
+    finally:
+        del model.blocks[0].mixer.capturable
 
 
 def test_block_embedding_and_head_parts_alone():
@@ -424,3 +450,92 @@ def test_other_position_encodings_and_a_routed_feedforward_fit_the_interfaces(tm
     want = toy2_plain(toks)
     torch.testing.assert_close(run_whole(runner, "w", toks).cpu(), want, rtol=1e-4, atol=1e-4)
     torch.testing.assert_close(run_portions(runner, "p", toks, portions(70, [9, 1, 2, 17])).cpu(), want, rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_two_attention_layouts_in_one_model_decode_from_graphs(tmp_path, dtype):
+    """A toy model whose two layers attend with different head counts, kv-head counts and head sizes: two cache groups,
+    and for captured single-token steps one decode plan per layout (its own split of the keys, its own scratch and
+    counters), asked of the mixers.  Several requests decode together from graphs against plain torch written here."""
+    from marin_b200.cache import CacheManager
+    from marin_b200.config.base import ModelConfig
+    from marin_b200.engine import Runner, load_model
+    from marin_b200.models import register_architecture
+    from marin_b200.parts import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+    from marin_b200.weights import write_random_model
+
+    layouts = [(8, 4, 64), (2, 1, 128)]            # (heads, kv heads, head size) of layer 0 and layer 1
+
+    @dataclass
+    class Toy3Config(ModelConfig):
+        @classmethod
+        def from_dict(cls, raw, generation=None):
+            return cls(architecture="ToyTwoLayoutsLM", model_type="toy_two_layouts", vocab_size=raw["vocab_size"],
+                       hidden_size=raw["hidden_size"], max_position_embeddings=raw["max_position_embeddings"], raw=dict(raw))
+
+        def to_json_dict(self):
+            return dict(self.raw)
+
+    def build_spec(cfg):
+        h = cfg.hidden_size
+        norm = PartSpec("rmsnorm", {"dim": h, "eps": 1e-6})
+        names = {"norm1": "n1", "mixer": "att", "norm2": "n2", "feedforward": "ff"}
+        layers = [LayerSpec("prenorm", norm,
+                            PartSpec("gqa_attention", {"hidden": h, "heads": H, "kv_heads": K, "head_dim": d, "qk_norm": True, "norm_eps": 1e-6,
+                                                       "position": PartSpec("rope", {"head_dim": d, "theta": 1e4})}),
+                            PartSpec("swiglu", {"hidden": h, "intermediate": 384}), f"t.l{i}", names)
+                  for i, (H, K, d) in enumerate(layouts)]
+        return ModelSpec(hidden_size=h, vocab_size=cfg.vocab_size,
+                         embedding=PartSpec("token_table", {"vocab": cfg.vocab_size, "hidden": h, "name": "t.embed"}),
+                         final_norm=PartSpec("rmsnorm", {"dim": h, "eps": 1e-6, "name": "t.norm"}),
+                         head=PartSpec("linear", {"vocab": cfg.vocab_size, "hidden": h, "name": "t.head"}),
+                         layers=layers, schedule=[ScheduleEntry(0), ScheduleEntry(1)])
+
+    register_architecture("ToyTwoLayoutsLM", "toy_two_layouts", Toy3Config, build_spec)
+    raw = {"architectures": ["ToyTwoLayoutsLM"], "model_type": "toy_two_layouts", "vocab_size": 211, "hidden_size": 256,
+           "max_position_embeddings": 512}
+    d = write_random_model(str(tmp_path / "toy3"), Toy3Config.from_dict(raw), seed=3, dtype=dtype, matrix_std=0.06)
+    rt = runtime(dtype)
+    config, model = load_model(d, rt)
+    cache = CacheManager(model.cache_needs(), [e.cache_of for e in model.spec.schedule], 16, 80, 4)
+    cache.allocate(rt.device, rt.dtype)
+    assert len(cache.groups) == 2
+    runner = Runner(model, cache, rt, 512)
+    runner.GRAPH_MIN_SPAN = 64
+    runner.enable_graphs((1, 2, 4))
+    w = plain.read_weights(d)
+
+    def twin(ids):
+        T = len(ids)
+        x = plain.embed(ids, w["t.embed.weight"])
+        pos = torch.arange(T)
+        for i, (H, K, hd) in enumerate(layouts):
+            p = f"t.l{i}."
+            n = plain.rms_norm(x, w[p + "n1.weight"], 1e-6)
+            q = plain.rope(plain.rms_norm(plain.linear(n, w[p + "att.q_proj.weight"]).view(T, H, hd), w[p + "att.q_norm.weight"], 1e-6), pos, 1e4)
+            k = plain.rope(plain.rms_norm(plain.linear(n, w[p + "att.k_proj.weight"]).view(T, K, hd), w[p + "att.k_norm.weight"], 1e-6), pos, 1e4)
+            v = plain.linear(n, w[p + "att.v_proj.weight"]).view(T, K, hd)
+            x = x + plain.linear(plain.attention(q, k, v).reshape(T, H * hd), w[p + "att.o_proj.weight"])
+            n = plain.rms_norm(x, w[p + "n2.weight"], 1e-6)
+            x = x + plain.swiglu_mlp(n, w[p + "ff.gate_proj.weight"], w[p + "ff.up_proj.weight"], w[p + "ff.down_proj.weight"])
+        return plain.linear(plain.rms_norm(x, w["t.norm.weight"], 1e-6), w["t.head.weight"])
+
+    rng = random.Random(6)
+    lengths = {"a": 300, "b": 90, "c": 170, "d": 41}
+    tokens = {rid: random_prompt(rng, 211, n) for rid, n in lengths.items()}
+    # short prompts, then long decoding side by side: the sequences grow through several spans, each with its own graphs
+    steps = mixed_schedule(rng, lengths, max_live=4, decode_tail=150, sizes=(23, 2, 9))
+    got = run_mixed(runner, tokens, steps)
+    keys = {key for g in runner.graphs.values() for key in g["plans"]}
+    if dtype == torch.bfloat16:
+        assert len(keys) == 2, keys                  # one plan per layout, each with counters for its own kv heads
+        for g in runner.graphs.values():
+            bucket = g["key"][0]
+            for (_, H, K, hd), plan in g["plans"].items():
+                assert plan.buffers[2].numel() == bucket * K and plan.buffers[0].numel() == bucket * H * plan.chunks * hd
+    assert len({span for _, span in runner.graphs}) >= 2
+    tol = dict(rtol=1e-4, atol=1e-4) if dtype == torch.float32 else dict(rtol=0.0, atol=0.15)
+    for rid in tokens:
+        torch.testing.assert_close(got[rid].cpu().float(), twin(tokens[rid]), **tol)
+    cache.check()
+    runner.scratch.check()

@@ -5,7 +5,8 @@ scratch is a fixed array inside the library, so the caller passes only inputs an
 
 The test calls it through its exported C symbol, twice in a row (the scratch is shared between calls and
 keeps what the last call left), and compares each result with the ordinary entry point's, at the
-tolerance the other matrix-product tests use.  Sizes beyond the built-in scratch must be refused with a
+tolerance the other matrix-product tests use, and with a float64 product of the same inputs, so that the
+check does not rest on another kernel of the same family.  Sizes beyond the built-in scratch must be refused with a
 message, before anything is launched.  This file sorts last on purpose: a run that stops at the first
 failure has then already run every other test.
 """
@@ -55,9 +56,32 @@ def test_no_alloc_entry_matches_the_ordinary_one_twice_in_a_row(T, N, K):
         torch.cuda.synchronize()
         scale = float(want32.abs().max())
         assert float((got32 - want32).abs().max()) <= 2e-5 * scale + 1e-4, f"call {call}"
+        exact = x.double() @ w.double().t()                  # bfloat16 products are exact in float64: only the sums round
+        assert float((got32.double() - exact).abs().max()) <= 2e-5 * scale + 1e-4, f"call {call} against float64"
         torch.testing.assert_close(got16.float(), want16.float(), rtol=1e-2, atol=1e-2 * scale)
         assert float((acc - base - want32).abs().max()) <= 2e-5 * scale + 1e-4
     assert lib.mb_gemm_tc_noalloc_device_error() == 0
+
+
+def test_no_alloc_entry_on_a_stream_of_the_callers_own():
+    """Callers run the product on streams of their own, which do not wait for the legacy default stream nor it for
+    them.  The flag reader has to wait for the whole device by itself: here nothing synchronises before it is
+    called, and afterwards the result is complete and right."""
+    lib, fn = entry()
+    g = torch.Generator(device=DEV).manual_seed(22)
+    T, N, K = 8, 2560, 4096
+    x = torch.randn(T, K, device=DEV, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    exact = x.double() @ w.double().t()
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    got = torch.full((T, N), float("nan"), device=DEV)
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            assert fn(x.data_ptr(), w.data_ptr(), got.data_ptr(), 1, T, N, K, ctypes.c_void_p(side.cuda_stream)) == 0
+    assert lib.mb_gemm_tc_noalloc_device_error() == 0         # waits for the side stream too
+    assert side.query()                                       # ... so nothing is left running on it
+    assert float((got.double() - exact).abs().max()) <= 2e-5 * float(exact.abs().max()) + 1e-4
 
 
 def test_no_alloc_entry_refuses_what_its_scratch_cannot_hold():
