@@ -239,6 +239,50 @@ def prefill_device(engine, tokens, runs, warmup):
     return statistics.median(times)
 
 
+def profile_mode(engine, args, pk):
+    """Where the time of a decode step (batch 1, 8 and 64) and of a 2,048-token prompt goes, stage by stage
+    (marin_b200/engine/profile.py).  Text to stdout; no JSON line: nothing measured here is a throughput figure."""
+    import torch
+
+    from marin_b200.engine import StepEntry
+    from marin_b200.engine.profile import format_table, profile_steps
+    from marin_b200.kernels import ops
+
+    runner, vocab = engine.runner, engine.config.vocab_size
+    layers = len(engine.model.blocks)
+    where = f"Qwen3-{args.model.upper()} layout, {layers} of {LAYOUTS[args.model]['num_hidden_layers']} layers, bfloat16, page {PAGE}"
+    peaks_line = f"peaks ({pk['source']}): {pk['hbm_gbs']:.0f} GB/s copy, {pk['bf16_tflops']:.0f} TFLOP/s bf16"
+    print(f"{where}; {peaks_line}; in-step times under the CUDA profiling interface (medians of 6 steps)\n")
+    steps, warmup = 6, 4
+    for batch in (1, 8, 64):
+        ids = [f"prof{batch}_{i}" for i in range(batch)]
+        for rid in ids:
+            runner.begin(rid)
+            engine.cache.reserve(rid, CONTEXT - steps - warmup)
+            engine.cache.commit(rid, CONTEXT - steps - warmup)
+        rows = profile_steps(runner, lambda i: [StepEntry(rid, [5 + i], [0]) for rid in ids], steps, warmup)
+        print(format_table(rows, pk["hbm_gbs"], pk["bf16_tflops"], f"decode step, batch {batch}, sequences of about {CONTEXT} positions"))
+        print()
+        for rid in ids:
+            runner.end(rid)
+    prompt = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=torch.Generator().manual_seed(5)).tolist()
+    out = runner.scratch.ids(1)
+
+    def entries(i):
+        runner.begin(f"prefill{i}")
+        return [StepEntry(f"prefill{i}", prompt, [PREFILL_TOKENS - 1])]
+
+    def after(logits):
+        ops.stage_name = "sampling"
+        ops.argmax(logits, vocab, out)
+        runner.end(next(iter(runner.cache.requests)))
+
+    rows = profile_steps(runner, entries, steps, warmup, after_step=after)
+    print(format_table(rows, pk["hbm_gbs"], pk["bf16_tflops"], f"prompt of {PREFILL_TOKENS} tokens in one step"))
+    engine.check_device()
+    return 0
+
+
 def reference_arm():
     """The reference is a Rust workspace (cargo, rustc); neither exists in this image, so it cannot be
     built or installed offline, and a pip install of its source tree has nothing to install (no Python package)."""
@@ -257,6 +301,7 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--model", default="4b", choices=sorted(LAYOUTS), help="layer sizes: Qwen3-4B (the default), 8B or 14B layout")
+    ap.add_argument("--profile", action="store_true", help="print where a step's time goes, stage by stage, instead of the JSON line")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -282,6 +327,8 @@ def main() -> int:
     engine = Engine(config=cfg, seed=0, dtype="bfloat16", ctx=CONTEXT, page_size=PAGE, max_batch=max_batch,
                     token_budget=PREFILL_TOKENS)
     fill_cache(engine)
+    if args.profile:
+        return profile_mode(engine, args, pk)
     weight_bytes, prefill_flops = model_bytes_and_flops(engine, args.batch, PREFILL_TOKENS)
     kv_tok = kv_bytes_per_token(engine)
 

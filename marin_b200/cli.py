@@ -2,12 +2,12 @@
 
     marin-run MODEL_DIR -p TEXT | --prompt-ids 1,2,3 [--ctx N] [--max-tokens 128] [--temp 0.7] [--top-k 0]
                         [--top-p 0.9] [--seed N] [--metrics] [--dtype bfloat16|float32]
-    marin-run bench MODEL_DIR [--prompt-tokens 128] [--tokens 64] [--runs 3] [--warmup 1] [--temp 0] [--json FILE]
+    marin-run bench MODEL_DIR [--prompt-tokens 128] [--tokens 64] [--runs 3] [--warmup 1] [--temp 0] [--json FILE] [--profile]
     marin-run verify MODEL_DIR --reference REF.json
     marin-run random --config CONFIG.json --seed S --out DIR [--dtype bfloat16|float32]
 
 Option names and defaults are the reference's where it has them (``--temp``, ``--top-k``, ``--top-p``, ``--seed``,
-``--max-tokens``, ``--ctx``, ``--prompt-tokens``, ``--tokens``, ``--runs``, ``--warmup``, ``--json``).  ``-p`` needs
+``--max-tokens``, ``--ctx``, ``--prompt-tokens``, ``--tokens``, ``--runs``, ``--warmup``, ``--json``, ``--profile``).  ``-p`` needs
 ``tokenizer.json`` in the model folder and the ``tokenizers`` package; ``--prompt-ids`` takes token ids and prints
 token ids.  The reply goes to stdout, everything else to stderr.  ``random`` (random-weights mode) and ``--dtype``
 have no counterpart in the reference; its ``--backend``, ``--quantize``, ``--kv-type``, ``--speculate`` are not taken.
@@ -128,7 +128,45 @@ def cmd_bench(args) -> int:
         with open(tmp, "w") as fh:
             json.dump(record, fh, indent=2)
         os.replace(tmp, args.json)
+    if args.profile:
+        print(profile_text(engine, prompt, args.tokens))
     return 0
+
+
+def profile_text(engine, prompt: List[int], tokens: int, hbm_gbs: float = 6500.0, peak_tflops: float = 1600.0) -> str:
+    """``bench --profile``: where the time of the prompt step and of a decode step goes, stage by stage (the reference's
+    flag: crates/cli/src/args.rs:70-91; its stages: crates/metrics/src/stage.rs:5-19).  Fractions are of a B200's
+    measured copy bandwidth and library bf16 product rate, about 6.5 TB/s and 1.6 PFLOP/s."""
+    from .engine import StepEntry
+    from .engine.profile import format_table, profile_steps
+    from .kernels import ops
+
+    runner, vocab = engine.runner, engine.config.vocab_size
+    out = runner.scratch.ids(1)
+    live = []
+
+    def sample(logits):
+        ops.stage_name = "sampling"
+        ops.argmax(logits, vocab, out)
+
+    def prompt_step(i):
+        for rid in live:
+            runner.end(rid)
+        live[:] = [f"profile{i}"]
+        runner.begin(live[0])
+        return [StepEntry(live[0], prompt, [len(prompt) - 1])]
+
+    rows = profile_steps(runner, prompt_step, steps=4, warmup=2, after_step=sample)
+    text = format_table(rows, hbm_gbs, peak_tflops, f"prompt of {len(prompt)} tokens in one step")
+    room = engine.ctx - len(prompt)
+    steps = max(1, min(6, room - 3))
+    if room >= 2:
+        rows = profile_steps(runner, lambda i: [StepEntry(live[0], [prompt[i % len(prompt)]], [0])], steps=steps, warmup=min(3, room - steps),
+                             after_step=None if getattr(runner, "graph_sizes", None) else sample)
+        text += "\n\n" + format_table(rows, hbm_gbs, peak_tflops, f"decode step, one sequence of about {len(prompt) + tokens} positions")
+    for rid in live:
+        runner.end(rid)
+    return text
 
 
 def verify(model_dir: str, reference: str, dtype: str = "float32", ctx: Optional[int] = None) -> List[str]:
@@ -212,6 +250,7 @@ def main(argv: Optional[List[str]] = None) -> int:
             ap.add_argument("--runs", type=int, default=3)
             ap.add_argument("--warmup", type=int, default=1)
             ap.add_argument("--json", default=None)
+            ap.add_argument("--profile", action="store_true", help="also print where a step's time goes, stage by stage")
             _add_sampling(ap, temp=0.0, top_p=1.0)
             return cmd_bench(ap.parse_args(argv[1:]))
         if argv[0] == "verify":

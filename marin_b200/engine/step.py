@@ -264,11 +264,14 @@ class Runner:
         # would be lost.  (torch.cuda.graph collects once before it begins.)
         collecting = gc.isenabled()
         gc.disable()
+        logging, ops.launch_log = ops.launch_log, []      # what the graph's kernels are, in order (engine/profile.py)
         try:
             with ops.using(self.scratch), torch.cuda.graph(graph):
                 g["logits"] = self.model.forward(ctx, self.views)
+                ops.stage_name = "sampling"
                 ops.argmax(g["logits"], self.vocab, g["best"])    # greedy sampling rides in the same graph
         finally:
+            g["labels"], ops.launch_log = ops.launch_log, logging
             if collecting:
                 gc.enable()
         g["launches"] = ops.launches - launches

@@ -40,7 +40,13 @@ def _ptr(t: Optional[torch.Tensor]):
     return _c_void_p(t.data_ptr()) if t is not None else _c_void_p(0)
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream():
+    """The current stream's handle (asked of torch on every launch: streams change under graph capture)."""
+    if _raw_stream is not None:
+        return _c_void_p(_raw_stream(torch.cuda.current_device()))
     return _c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
@@ -62,10 +68,37 @@ def launches_extra(n: int) -> None:
     launches += n
 
 
+#: While this is a list, every launch appends what it was and what it had to move and compute (``engine/profile.py``
+#: reads it: the stages of a step with their bytes and flops, in launch order).  ``stage_name`` is set by the parts
+#: before their calls ("qkv", "attention", "o", ...) and names the launches that follow.
+launch_log: Optional[list] = None
+stage_name = ""
+_pending_cost: Optional[dict] = None
+
+
+def _cost(nbytes: float = 0, flops: float = 0.0, bytes_per_key: float = 0, flops_per_pair: float = 0.0) -> None:
+    """What the next launch has to read and write (bytes) and compute (flops), as the algorithm needs it: every input
+    and output once.  Attention's share that grows with the cache is given per cached key read and per (query, key)
+    pair, because a captured graph is replayed at other lengths than it was captured at."""
+    global _pending_cost
+    if launch_log is not None:
+        _pending_cost = {"bytes": float(nbytes), "flops": float(flops), "bytes_per_key": float(bytes_per_key),
+                         "flops_per_pair": float(flops_per_pair)}
+
+
+def _size(t) -> int:
+    return t.numel() * t.element_size()
+
+
 def _check(rc: int, what: str) -> None:
-    global launches
+    global launches, _pending_cost
     if rc == 0:
         launches += 1
+        if launch_log is not None:
+            entry = _pending_cost or {"bytes": 0.0, "flops": 0.0, "bytes_per_key": 0.0, "flops_per_pair": 0.0}
+            entry["stage"], entry["kernel"] = stage_name, what
+            launch_log.append(entry)
+            _pending_cost = None
         return
     if rc in _ERRORS:
         raise KernelError(f"{what}: {_ERRORS[rc]}")
@@ -80,6 +113,7 @@ def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> None:
     _need_cuda(ids, table, out)
     T, h = out.shape
     assert ids.dtype == torch.int32 and ids.numel() == T and table.shape[1] == h and out.dtype == torch.float32
+    _cost(T * h * table.element_size() + _size(out) + _size(ids))
     _check(_lib("mb_elementwise").mb_embed(_ptr(ids), _ptr(table), _code(table), _ptr(out), _c_int(T), _c_int(h), _stream()), "embed")
 
 
@@ -87,6 +121,7 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
     _need_cuda(x, weight, out)
     rows, n = x.shape
     assert x.dtype == torch.float32 and weight.dtype == torch.float32 and weight.numel() == n and out.shape == x.shape
+    _cost(_size(x) + _size(out) + _size(weight), 4.0 * rows * n)
     _check(_lib("mb_elementwise").mb_rmsnorm(_ptr(x), _ptr(weight), _c_float(eps), _c_int(int(unit_offset)), _ptr(out),
                                             _code(out), _c_int(rows), _c_int(n), _stream()), "rmsnorm")
 
@@ -359,6 +394,7 @@ def gemm(x, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False, then_n
     assert w.shape[1] == K and tuple(out.shape) == (T, N), (x.shape, w.shape, out.shape)
     if accumulate and out.dtype != torch.float32:
         raise KernelError("gemm: accumulate needs a float32 output")
+    _cost(_size(w) + _size(x) + _size(out) * (2 if accumulate else 1) + (_size(then_norm.rows) if then_norm is not None else 0), 2.0 * T * N * K)
     if (use_tensor_cores and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and K % 8 == 0
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and T > 0):
         mode = 2 if accumulate else (0 if out.dtype == torch.bfloat16 else 1)
@@ -436,6 +472,7 @@ def gemm_qkv_heads(x, w: torch.Tensor, q_out: torch.Tensor, q_weight, k_weight, 
         return False
     _need_cuda(rows, w, q_out)
     assert tuple(q_out.shape) == (T, H * d) and w.shape[1] == Kdim
+    _cost(_size(w) + _size(rows) + T * N * 2, 2.0 * T * N * Kdim)
     s = _scratch_for(rows.device)
     page_size = k_cache.shape[2] if write_kv else 0
     _check(_lib("mb_gemm_tc").mb_gemm_tc_heads(
@@ -457,6 +494,7 @@ def qk_norm_rope_write(qkv, q_out, q_weight, k_weight, eps, positions, inv_freq,
     assert k_cache.dtype == qkv.dtype and v_cache.dtype == qkv.dtype
     assert k_cache.shape[1] == K and k_cache.shape[3] == d
     page_size = k_cache.shape[2]
+    _cost(2 * _size(qkv), 8.0 * T * heads_total * d)
     _check(_lib("mb_elementwise").mb_qk_norm_rope_write(
         _ptr(qkv), _code(qkv), _ptr(q_out), _ptr(q_weight), _ptr(k_weight), _c_float(eps), _ptr(positions),
         _ptr(inv_freq), _c_int(rotary_dim if inv_freq is not None else 0), _c_int(int(interleaved)), _ptr(slot_mapping),
@@ -556,6 +594,16 @@ def attention_jobs(dtype, H: int, K: int, d: int) -> dict:
     return jobs
 
 
+def _attention_cost(q, rows: int, H: int, K: int, d: int, which: str) -> None:
+    """Queries in, results out; per cached key read, its key and value over all kv heads; per (query, key) pair a
+    score and a weighted value for every head.  ``which`` says whose keys and pairs count: the single-token rows'
+    ("decode"), the portions' ("prefill") or everyone's ("all")."""
+    if launch_log is not None:
+        size = q.element_size()
+        _cost(2 * rows * H * d * size, 0.0, 2 * K * d * size, 4.0 * H * d)
+        _pending_cost["rows"] = which
+
+
 def attention(q, k_cache, v_cache, out, ctx, block_table, H, K, d, scale, window=0, plan: Optional[DecodePlan] = None) -> None:
     """Causal attention of the step's tokens over the paged cache (their own keys included).  The first
     ``ctx.num_decode`` requests bring one token each (rows 0..num_decode-1); the rest bring portions.  ``plan``
@@ -575,6 +623,7 @@ def attention(q, k_cache, v_cache, out, ctx, block_table, H, K, d, scale, window
             split, chunks = (plan.split, plan.chunks) if plan is not None else decode_split(nd, K, ctx.max_seq_len)
             buffers = plan.buffers if plan is not None and plan.buffers is not None else None
             part_acc, part_ml, counters = buffers or _scratch_for(q.device).decode_buffers(nd, H, K, chunks, d)
+            _attention_cost(q, nd, H, K, d, "decode")
             _check(lib.mb_attn_decode(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), _c_int(max_pages),
                                       _ptr(ctx.seq_lens), _c_int(nd), _c_int(K), _c_int(page_size),
                                       ctypes.c_longlong(k_cache.shape[0]), _c_float(scale), _c_int(window), _ptr(part_acc),
@@ -582,17 +631,20 @@ def attention(q, k_cache, v_cache, out, ctx, block_table, H, K, d, scale, window
                                       _ptr(_scratch_for(q.device).error), _stream()), "attention (decode)")
         if ctx.num_requests > nd and use_tc_attention and d in (64, 128) and page_size >= 16:
             tc = build.load(f"mb_attention_tc_d{d}_g{H // K}", *build.attention_tc_job(d, H // K))
+            _attention_cost(q, T - nd, H, K, d, "prefill")
             _check(tc.mb_attn_prefill_tc(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), _c_int(max_pages),
                                          _ptr(ctx.cu_tokens), _ptr(ctx.seq_lens), _c_int(nd), _c_int(ctx.num_requests - nd),
                                          _c_int(ctx.max_query_len), _c_int(T), _c_int(K), _c_int(page_size),
                                          ctypes.c_longlong(k_cache.shape[0]), _c_float(scale), _c_int(window),
                                          _ptr(_scratch_for(q.device).error), _stream()), "attention (prefill, tensor cores)")
         elif ctx.num_requests > nd:
+            _attention_cost(q, T - nd, H, K, d, "prefill")
             _check(lib.mb_attn_prefill(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), _c_int(max_pages),
                                        _ptr(ctx.cu_tokens), _ptr(ctx.seq_lens), _c_int(nd), _c_int(ctx.num_requests - nd),
                                        _c_int(ctx.max_query_len), _c_int(K), _c_int(page_size), _c_float(scale),
                                        _c_int(window), _stream()), "attention (prefill)")
         return
+    _attention_cost(q, T, H, K, d, "all")
     _check(_lib("mb_attention_simple").mb_attention_simple(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _code(q), _ptr(block_table), _c_int(block_table.shape[1]),
         _ptr(ctx.req_index), _ptr(ctx.positions), _c_int(T), _c_int(H), _c_int(K), _c_int(d), _c_int(page_size),
@@ -605,6 +657,7 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor, interleaved: bool = False) 
     _need_cuda(gate_up, out)
     T, I = out.shape
     assert gate_up.shape == (T, 2 * I) and gate_up.dtype == out.dtype and (not interleaved or I % 16 == 0)
+    _cost(_size(gate_up) + _size(out), 8.0 * T * I)
     _check(_lib("mb_elementwise").mb_swiglu(_ptr(gate_up), _ptr(out), _code(out), _c_int(T), _c_int(I), _c_int(int(interleaved)),
                                            _stream()), "swiglu")
 
@@ -641,6 +694,7 @@ def gemm_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor, out: torch.Tensor,
         swiglu(tmp, out, interleaved=True)
         return
     s = _scratch_for(x.device)
+    _cost(_size(w_interleaved) + _size(x) + _size(out), 2.0 * T * N * K)
     if T > 128 and -(-N // 128) * -(-T // 128) >= SM_COUNT // 2:
         if scaled is not None:
             _check(_lib("mb_gemm_tc").mb_gemm_tc_persistent_coupled(
@@ -665,6 +719,7 @@ def gather_rows(src: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> Non
     _need_cuda(src, rows, out)
     W, h = out.shape
     assert src.dtype == torch.float32 and out.dtype == torch.float32 and rows.dtype == torch.int32 and rows.numel() == W
+    _cost(2 * _size(out))
     _check(_lib("mb_elementwise").mb_gather_rows(_ptr(src), _ptr(rows), _ptr(out), _c_int(W), _c_int(h), _stream()), "gather_rows")
 
 
@@ -672,6 +727,7 @@ def add_into(y: torch.Tensor, x: torch.Tensor) -> None:
     """``y += x`` with ``y`` float32 (the residual stream)."""
     _need_cuda(y, x)
     assert y.dtype == torch.float32 and y.numel() == x.numel()
+    _cost(2 * _size(y) + _size(x), float(y.numel()))
     _check(_lib("mb_elementwise").mb_add_into(_ptr(y), _ptr(x), _code(x), _c_size_t(y.numel()), _stream()), "add_into")
 
 
@@ -682,6 +738,7 @@ def argmax(logits: torch.Tensor, usable: int, out: torch.Tensor) -> None:
     rows, vocab = logits.shape
     assert logits.dtype == torch.float32 and out.dtype == torch.int32 and out.numel() == rows
     s = _scratch_for(logits.device)
+    _cost(rows * usable * 4)
     _check(_lib("mb_sampling").mb_argmax(_ptr(logits), _c_int(rows), _c_int(vocab), _c_int(usable), _ptr(out), _ptr(s.argmax_keys),
                                         _ptr(s.argmax_count), _c_int(s.ARGMAX_ROWS), _c_int(2 * s.sm_count), _ptr(s.report),
                                         _ptr(s.error), _stream()), "argmax")
@@ -698,5 +755,6 @@ def sample(logits: torch.Tensor, usable: torch.Tensor, temperature: torch.Tensor
     assert temperature.dtype == torch.float32 and top_p.dtype == torch.float32 and uniform.dtype == torch.float32
     assert all(t.numel() == rows for t in (usable, temperature, top_k, top_p, uniform, out))
     s = _scratch_for(logits.device)
+    _cost(_size(logits))
     _check(_lib("mb_sampling").mb_sample(_ptr(logits), _c_int(rows), _c_int(vocab), _ptr(usable), _ptr(temperature), _ptr(top_k),
                                         _ptr(top_p), _ptr(uniform), _ptr(out), _ptr(s.report), _ptr(s.error), _stream()), "sample")

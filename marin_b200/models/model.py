@@ -120,6 +120,7 @@ class Model:
         rt, ws = self.rt, ctx.workspace
         T = ctx.num_tokens
         hidden = ws.get("hidden", (T, self.spec.hidden_size), torch.float32)
+        ops.stage_name = "embedding"
         self.embedding.forward(ctx.token_ids, hidden)
         if observe is not None:
             observe(0, hidden)
@@ -138,10 +139,12 @@ class Model:
         W = ctx.num_logit_rows
         if W == 0:
             return torch.empty(0, self.spec.vocab_size, device=rt.device, dtype=torch.float32)
+        ops.stage_name = "final norm"
         rows = ws.get("logit_hidden", (W, self.spec.hidden_size), torch.float32)
         ops.gather_rows(hidden, ctx.logit_rows, rows)
         normed = ws.get("logit_normed", (W, self.spec.hidden_size), rt.dtype)
         self.final_norm.forward(rows, normed)
+        ops.stage_name = "head"
         logits = ws.get("logits", (W, self.spec.vocab_size), torch.float32)
         self.head.forward(normed, logits)
         return logits

@@ -5,6 +5,7 @@ from typing import Dict, List
 
 import torch
 
+from ..kernels import ops
 from .base import Part, Runtime
 from .registry import lookup, register_block
 from .spec import LayerSpec, TensorSpec
@@ -65,10 +66,13 @@ class PreNormBlock(Part):
         product, its input is returned, else None."""
         ws = ctx.workspace
         normed = ws.get("normed", tuple(hidden.shape), self.rt.dtype)
+        if x_in is None:
+            ops.stage_name = "norm"
         x = x_in if x_in is not None else self.norm1.forward(hidden, normed)
         rider = self._rider(self.norm2, self.mixer, self.feedforward, normed)
         x = self.mixer.forward(x, ctx, cache, hidden, then_norm=rider) if rider is not None else self.mixer.forward(x, ctx, cache, hidden)
         if x is None:
+            ops.stage_name = "norm"
             x = self.norm2.forward(hidden, normed)
         rider = None
         if next_block is not None and getattr(next_block, "chains_norm", False):

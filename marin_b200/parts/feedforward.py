@@ -64,10 +64,12 @@ class SwiGLU(FeedForward):
         T = x.shape[0]
         ws = ctx.workspace
         act = ws.get("ffn_act", (T, self.intermediate), x.dtype)
+        ops.stage_name = "gate|up, SwiGLU"
         if self.fused:
             ops.gemm_swiglu(x, self.w_gate_up, act, ws)
         else:
             gate_up = ws.get("gate_up", (T, 2 * self.intermediate), x.dtype)
             ops.gemm(x, self.w_gate_up, gate_up)
             ops.swiglu(gate_up, act)
+        ops.stage_name = "down"
         return ops.gemm(act, self.w_down, residual, accumulate=True, then_norm=then_norm)

@@ -166,6 +166,7 @@ class GQAttention(Mixer):
         q = ws.get("q", (T, self.q_dim), x.dtype)
         # A run that reads another run's cache computes only the queries.
         w = self.w_qkv if writes else self.w_qkv[: self.q_dim]
+        ops.stage_name = "q|k|v, heads"
         if not ops.gemm_qkv_heads(x, w, q, self.q_weight, self.k_weight, self.norm_eps, ctx.positions, pos.inv_freq,
                                   pos.rotary_dim, pos.interleaved, cache.slot_mapping, cache.k, cache.v, self.heads,
                                   self.kv_heads, self.head_dim, writes):
@@ -177,7 +178,9 @@ class GQAttention(Mixer):
                 cache.k, cache.v, self.heads, self.kv_heads, self.head_dim, writes,
             )
         out = ws.get("attn_out", (T, self.q_dim), x.dtype)
+        ops.stage_name = "attention"
         plans = ctx.decode_plans
         ops.attention(q, cache.k, cache.v, out, ctx, cache.block_table, self.heads, self.kv_heads,
                       self.head_dim, self.scale, self.window or 0, plans.get(self.decode_plan_key()) if plans else None)
+        ops.stage_name = "o"
         return ops.gemm(out, self.w_o, residual, accumulate=True, then_norm=then_norm)

@@ -12,10 +12,13 @@ ends in a minute) and a context of 4,096, under every way of cutting the work:
     python tests/check_layout_equality.py [--model 4b|8b|14b] [--layers 2] [--context 4096] [--dtypes float32,bfloat16]
 
 float32 must agree within 1e-4 + 1e-4 |x| at every position, bfloat16 within the tolerances of the tests
-(tests/test_engine_gpu.py: close).  Too slow for the test suite (a minute of CPU per model); the tests hold the same
-comparisons on tiny configurations.  Prints one line per comparison and exits non-zero if any fails.
+(tests/test_engine_gpu.py: close, against the plain result rounded where a 16-bit engine stores).  Too slow for the
+test suite (a minute or two of CPU per model); the suite holds the same comparisons on one layer of the same widths
+with a cut vocabulary and a context of 1,100 (tests/test_real_widths_gpu.py).  Prints one line per comparison and
+exits non-zero if any fails.
 """
 import argparse
+import math
 import os
 import random
 import sys
@@ -41,7 +44,7 @@ def main() -> int:
     import bench
     import plain_qwen3 as plain
     from helpers import make_model_dir, mixed_schedule, portions, random_prompt, run_mixed, run_portions, run_whole
-    from test_engine_gpu import close
+    from test_engine_gpu import close, plain_forward
 
     from marin_b200.cache import CacheManager
     from marin_b200.engine import Runner, load_model, parse_dtype
@@ -57,16 +60,20 @@ def main() -> int:
     with tempfile.TemporaryDirectory() as tmp:
         t0 = time.time()
         # written once, in bfloat16: the float32 run reads the same values, so one plain result serves both
-        folder = make_model_dir(os.path.join(tmp, "m"), raw, seed=args.seed, dtype=torch.bfloat16)
+        # matrices of standard deviation 1 / sqrt(width), so that logits have a standard deviation near 1 at every
+        # layout (the bfloat16 tolerance is absolute and supposes that)
+        folder = make_model_dir(os.path.join(tmp, "m"), raw, seed=args.seed, dtype=torch.bfloat16,
+                                matrix_std=1.0 / math.sqrt(raw["hidden_size"]))
         cfg, w = plain.read_config(folder), plain.read_weights(folder)
         print(f"[{time.time() - t0:6.1f} s] {args.model} layout, {args.layers} layers: weights written and read", flush=True)
         prompt = random_prompt(rng, vocab, n)
         lengths = {"a": n, "b": 1000, "c": 300, "d": 2000, "e": 600}
         others = {rid: random_prompt(rng, vocab, min(L, n)) for rid, L in lengths.items() if rid != "a"}
         others["a"] = prompt
-        want = {rid: plain.forward(cfg, w, toks) for rid, toks in others.items()}
-        print(f"[{time.time() - t0:6.1f} s] plain implementation done (logits of standard deviation {float(want['a'].std()):.2f})", flush=True)
         for dtype in args.dtypes.split(","):
+            # bfloat16 is held to the plain result rounded where a 16-bit engine stores its activations
+            want = {rid: plain_forward(cfg, w, toks, dtype) for rid, toks in others.items()}
+            print(f"[{time.time() - t0:6.1f} s] plain implementation for {dtype} done (logits of standard deviation {float(want['a'].std()):.2f})", flush=True)
             rt = Runtime(torch.device("cuda:0"), parse_dtype(dtype))
             _, model = load_model(folder, rt)
             per_seq = -(-n // page)

@@ -52,9 +52,13 @@ def test_run_random_and_bench_commands(tmp_path):
     d = subprocess.run(RUN + [model, "--prompt-ids", "5,6,7", "--temp", "0.9", "--seed", "1", "--max-tokens", "6"], capture_output=True, text=True)
     assert c.stdout == d.stdout
     j = str(tmp_path / "bench.json")
-    e = subprocess.run(RUN + ["bench", model, "--prompt-tokens", "16", "--tokens", "8", "--runs", "2", "--warmup", "1", "--json", j],
-                       capture_output=True, text=True)
+    e = subprocess.run(RUN + ["bench", model, "--prompt-tokens", "16", "--tokens", "8", "--runs", "2", "--warmup", "1", "--json", j,
+                              "--profile"], capture_output=True, text=True)
     assert e.returncode == 0, e.stderr
+    # --profile: the stages of the prompt step and of a decode step, each with its time inside the step
+    assert "prompt of 16 tokens in one step" in e.stdout and "decode step, one sequence" in e.stdout
+    for stage in ("embedding", "q|k|v", "attention", "gate|up", "down", "head", "sampling", "(between steps)"):
+        assert stage in e.stdout, stage
     rec = json.load(open(j))
     assert rec["prompt_tokens"] == 16 and rec["decode_tokens_per_s"] > 0 and rec["batch_size"] == 1
     f = subprocess.run(RUN + [model, "--max-tokens", "6"], capture_output=True, text=True)

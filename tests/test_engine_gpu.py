@@ -5,9 +5,14 @@ live requests with so few pages that they are used again.  Also long decoding, t
 a sequence and greedy generation through the entry point.
 
 Tolerances (fixed; the reference's chunking gate is 1e-4 (1 + |x|), crates/model/tests/kv_append.rs:27-60):
-float32: |diff| <= 1e-4 + 1e-4 |ref|.  bfloat16 (activations rounded to 8 bits of mantissa between
-kernels, logits of standard deviation ~1): max |diff| <= 0.15 and mean |diff| <= 0.02 against the plain
-float32 result computed from the same bfloat16 weights.
+float32: |diff| <= 1e-4 + 1e-4 |ref|.  bfloat16 (logits of standard deviation ~1): max |diff| <= 0.08 and
+mean |diff| <= 0.01 against the plain implementation computed from the same bfloat16 weights and rounded to
+bfloat16 where a 16-bit engine stores its activations (``plain.forward(..., stored=plain.as_bf16)``).  Measured
+on B200 over the four tiny configurations and one layer of the Qwen3-4B, 8B and 14B widths, in every way of
+cutting: max 0.025 to 0.046, mean 0.003 to 0.0063 (against the unrounded plain result: max up to 0.063, mean
+up to 0.0081).  The rounded oracle takes out the part of the difference that is the same rounding on both sides;
+what is left is rounding that falls differently because sums run in another order and factors are applied at
+another place (a norm's factor after the product instead of before, softmax terms against a running maximum).
 """
 import random
 
@@ -26,6 +31,14 @@ LENGTHS = {"A": {"a": 37, "b": 9, "c": 120, "d": 1, "e": 64, "f": 40, "g": 33},
            "D": {"a": 150, "b": 21, "c": 64, "d": 3, "e": 129, "f": 40}}
 
 
+BF16_MAX, BF16_MEAN = 0.08, 0.01
+
+
+def plain_forward(cfg, w, tokens, dtype: str, **kw):
+    """The plain implementation's logits as the engine of this dtype should reproduce them."""
+    return plain.forward(cfg, w, tokens, stored=plain.as_bf16 if dtype == "bfloat16" else plain.same, **kw)
+
+
 def close(got: torch.Tensor, want: torch.Tensor, dtype: str, what=""):
     got, want = got.float().cpu(), want.float()
     assert got.shape == want.shape, (got.shape, want.shape)
@@ -37,8 +50,8 @@ def close(got: torch.Tensor, want: torch.Tensor, dtype: str, what=""):
             raise AssertionError(f"{what}: first wrong position {first} of {got.shape[0]}, max err {err.max():.3e}")
     else:
         rowmax = err.max(dim=1).values
-        if err.max() > 0.15 or err.mean() > 0.02:
-            first = int(torch.nonzero(rowmax > 0.15)[0]) if (rowmax > 0.15).any() else -1
+        if err.max() > BF16_MAX or err.mean() > BF16_MEAN:
+            first = int(torch.nonzero(rowmax > BF16_MAX)[0]) if (rowmax > BF16_MAX).any() else -1
             raise AssertionError(f"{what}: max err {err.max():.3e} mean {err.mean():.3e}, first position over the limit {first}")
 
 
@@ -54,7 +67,7 @@ class Case:
         self.cfg, self.w = plain.read_config(self.dir), plain.read_weights(self.dir)
         rng = random.Random(5)
         self.tokens = {rid: random_prompt(rng, raw["vocab_size"], n) for rid, n in LENGTHS[name].items()}
-        self.want = {rid: plain.forward(self.cfg, self.w, t) for rid, t in self.tokens.items()}
+        self.want = {rid: plain_forward(self.cfg, self.w, t, dtype) for rid, t in self.tokens.items()}
         self.rt = Runtime(torch.device("cuda:0"), parse_dtype(dtype))
         self.config, self.model = load_model(self.dir, self.rt)
         self.page = PAGE[name]
@@ -125,7 +138,7 @@ def test_long_decoding(case):
     """A short prompt, then every further token one by one up to the context limit."""
     n = case.raw["max_position_embeddings"]
     toks = random_prompt(random.Random(9), case.raw["vocab_size"], n)
-    want = plain.forward(case.cfg, case.w, toks)
+    want = plain_forward(case.cfg, case.w, toks, case.dtype)
     runner = case.runner(num_pages=-(-n // case.page), graphs=True)
     runner.GRAPH_MIN_SPAN = 32           # several graphs on the way: one per span of lengths (32, 64, 128, ...)
     close(run_portions(runner, "long", toks, [5] + [1] * (n - 5)), want, case.dtype, "long decoding")
@@ -137,7 +150,7 @@ def test_first_tokens_of_a_sequence(case):
     rng = random.Random(10)
     for n in (1, 2, 3, 5):
         toks = random_prompt(rng, case.raw["vocab_size"], n)
-        want = plain.forward(case.cfg, case.w, toks)
+        want = plain_forward(case.cfg, case.w, toks, case.dtype)
         close(run_whole(runner, f"w{n}", toks), want, case.dtype, f"first {n} whole")
         close(run_portions(runner, f"p{n}", toks, [1] * n), want, case.dtype, f"first {n} one by one")
 
@@ -264,6 +277,6 @@ def test_schedule_may_repeat_a_layer_and_share_a_cache(case):
     assert len(cache.groups) == 1 and len(cache.groups[0].entries) == 3
     runner = Runner(model, cache, case.rt, 128)
     toks = case.tokens["a"]
-    want = plain.forward(case.cfg, case.w, toks, schedule=[(0, None), (1, None), (1, None), (0, 0)])
+    want = plain_forward(case.cfg, case.w, toks, case.dtype, schedule=[(0, None), (1, None), (1, None), (0, 0)])
     close(run_whole(runner, "w", toks), want, case.dtype, "schedule whole")
     close(run_portions(runner, "p", toks, portions(len(toks), [5, 2, 1, 9])), want, case.dtype, "schedule portions")

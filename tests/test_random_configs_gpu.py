@@ -9,7 +9,7 @@ import torch
 
 import plain_qwen3 as plain
 from helpers import make_model_dir, portions, random_prompt, run_portions, run_whole
-from test_engine_gpu import close
+from test_engine_gpu import close, plain_forward
 
 pytestmark = pytest.mark.gpu
 
@@ -61,7 +61,7 @@ def test_a_random_configuration(tmp_path, seed, dtype):
     rt = Runtime(torch.device("cuda:0"), parse_dtype(dtype))
     _, model = load_model(folder, rt)
     toks = random_prompt(rng, raw["vocab_size"], n)
-    want = plain.forward(cfg, w, toks)
+    want = plain_forward(cfg, w, toks, dtype)
     cache = CacheManager(model.cache_needs(), [e.cache_of for e in model.spec.schedule], page, -(-200 // page) * 2, 4)
     cache.allocate(rt.device, rt.dtype)
     runner = Runner(model, cache, rt, 200)

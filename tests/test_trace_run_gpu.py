@@ -13,7 +13,7 @@ import torch
 
 import plain_qwen3 as plain
 from helpers import MATRIX_STD, CONFIGS, make_model_dir, mixed_schedule, portions, random_prompt
-from test_engine_gpu import close
+from test_engine_gpu import close, plain_forward
 
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -53,7 +53,7 @@ def test_trace_replay_modes(tmp_path, name, dtype):
     cap = raw["max_position_embeddings"]
     lengths = {"a": 70, "b": min(cap, 130), "c": 41, "d": 64, "e": 100, "f": 2}
     tokens = {rid: random_prompt(rng, vocab, n) for rid, n in lengths.items()}
-    want = {rid: plain.forward(cfg, w, t) for rid, t in tokens.items()}
+    want = {rid: plain_forward(cfg, w, t, dtype) for rid, t in tokens.items()}
 
     # alone and whole; then most in one step and the last 32 one by one; then changing portions
     steps, expect = [], []
