@@ -8,8 +8,9 @@ sequences and a context of 4096 positions (the last timed step reaches it).  A "
 step.  One JSON line is printed:
 
   value      decoded tokens a second, K steps timed on the device with CUDA events
-  e2e        the same through the Python entry point (Engine.step): token ids from the host in, sampled ids
-             back on the host, every step
+  e2e        the same through the Python entry point (Engine.step): every step the host packs and sends the next
+             step's inputs from pinned memory and reads the sampled ids back (the step after the running one is
+             launched before those ids have arrived: its token ids are fed on the device)
   prefill    one 2,048-token prompt in one step: tokens a second and the fraction of the bf16 peak
   roofline   bytes a decode step has to read (every weight once, the cache of the live requests) / its time
   points     decode at batch 1 and 64
@@ -211,8 +212,12 @@ def decode_e2e(engine, batch, steps, warmup, context):
     for i in ids:
         engine.scheduler.cancel(i)
         engine.forget(i)
-    h2d = 4 * (batch * 3 + (batch + 1) + batch * 2 + batch + batch * (engine.runner.max_pages_per_seq + 1))
-    return {"value": got / seconds, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * batch,
+    # per step the host sends the packed inputs of the next step without its token ids (those are fed on the device:
+    # the step is launched before the host has read the ids of the one before) and reads, from pinned memory that the
+    # arg-max kernel writes itself, four ints of status and the sampled ids
+    bucket = next(b for b in engine.runner.graph_sizes if b >= batch)
+    h2d = 4 * (engine.runner.packed_size(bucket) + 1 - bucket)
+    return {"value": got / seconds, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * (4 + batch),
             "tokens": got}
 
 

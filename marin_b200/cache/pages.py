@@ -40,6 +40,7 @@ def host_lib() -> ctypes.CDLL:
         "mbs_create": (vp, [vp, i32, i32, i32]), "mbs_destroy": (None, [vp]),
         "mbs_add": (i32, [vp, vp, i32, i32, vp, i32, pi64]), "mbs_cancel": (i32, [vp, i64]), "mbs_forget": (i32, [vp, i64]),
         "mbs_has_work": (i32, [vp]), "mbs_schedule": (i32, [vp, vp, i32, vp, i32, pi32]),
+        "mbs_schedule_running": (i32, [vp, vp, i32, vp, i32]),
         "mbs_update": (i32, [vp, vp, i32, vp, vp, pi32]), "mbs_states": (i32, [vp, i32, vp, vp]),
         "mbs_output": (i32, [vp, i64, vp, i32]), "mbs_list": (i32, [vp, i32, vp, i32]),
         "mbp_best_index": (i32, [vp, i32]), "mbp_distribution": (i32, [vp, i32, i32, ctypes.c_float, i32, ctypes.c_float, vp, vp, i32]),

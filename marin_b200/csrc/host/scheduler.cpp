@@ -157,6 +157,31 @@ class Scheduler {
         return plan_;
     }
 
+    // The plan of a step that is ALREADY RUNNING: the engine launched it before it knew the tokens of the step before,
+    // supposing that the same requests go on with one token each (their pages were taken then).  Requests that have
+    // ended or been cancelled since are left out; nobody is admitted or preempted, and nothing is planned for a
+    // request that has more than its one next token to read.  Returns false (and an empty plan) if a request of the
+    // plan would need a page: such a step must not have been launched.
+    bool schedule_decode_only() {
+        plan_.clear();
+        membership_changed_ = false;
+        std::vector<int64_t> order = running_;
+        std::sort(order.begin(), order.end(), [this](int64_t a, int64_t b) { return reqs_[a].admitted_at < reqs_[b].admitted_at; });
+        for (int64_t id : order) {
+            SReq& r = reqs_[id];
+            if (r.num_tokens() - r.computed != 1) continue;
+            PlanItem item = portion(r, 1);
+            item.missing.assign(cache_->groups(), 0);
+            Request* rc = cache_->find(r.handle);
+            if (rc == nullptr) continue;
+            cache_->missing(*rc, r.computed + 1, item.missing.data());
+            for (int m : item.missing)
+                if (m != 0) { plan_.clear(); return false; }
+            plan_.push_back(std::move(item));
+        }
+        return true;
+    }
+
     // ---- after the step -------------------------------------------------------------------------------------------
     // tokens[k] is the token sampled for the k-th plan item that asked for one (negative: its logits were not finite, the
     // request ends with STOP_NON_FINITE and emits nothing); emitted receives (id, token) pairs.
@@ -274,10 +299,22 @@ MBH_API int mbs_has_work(void* s) { return static_cast<Scheduler*>(s)->has_work(
 // Plans the next step.  items receives up to cap rows of (id, first token, count, sample, cache handle, slot); the
 // step's tokens, in the same order, go to tokens (up to token_cap).  Returns the number of rows, or a negative code.
 // *changed is set when requests were admitted, preempted or ended while planning.
+static int mbs_write_plan(Scheduler* sched, const std::vector<PlanItem>& plan, int64_t* items, int cap, int* tokens, int token_cap);
+
 MBH_API int mbs_schedule(void* s, int64_t* items, int cap, int* tokens, int token_cap, int* changed) {
     Scheduler* sched = static_cast<Scheduler*>(s);
     const std::vector<PlanItem>& plan = sched->schedule();
     *changed = sched->membership_changed() ? 1 : 0;
+    return mbs_write_plan(sched, plan, items, cap, tokens, token_cap);
+}
+// The plan of a step that is already running (see Scheduler::schedule_decode_only): rows as mbs_schedule, or -MBH_BAD_ARG
+// if that step needed pages it does not have.
+MBH_API int mbs_schedule_running(void* s, int64_t* items, int cap, int* tokens, int token_cap) {
+    Scheduler* sched = static_cast<Scheduler*>(s);
+    if (!sched->schedule_decode_only()) return -MBH_BAD_ARG;
+    return mbs_write_plan(sched, sched->plan(), items, cap, tokens, token_cap);
+}
+static int mbs_write_plan(Scheduler* sched, const std::vector<PlanItem>& plan, int64_t* items, int cap, int* tokens, int token_cap) {
     if ((int)plan.size() > cap) return -MBH_TOO_SMALL;
     int at = 0;
     for (size_t k = 0; k < plan.size(); ++k) {

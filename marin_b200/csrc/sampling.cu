@@ -7,6 +7,13 @@
 // 135-137): both kernels write the id -1 for such a row.  report[0] receives the code another kernel left in
 // `error_flag` when one of its bounded waits gave up (untouched otherwise), so that the host learns of both with the
 // ids it reads anyway; the host clears it after it has seen a non-zero value.
+//
+// arg-max can leave its ids in two more places (ArgmaxAlso).  `feed`: where the NEXT step reads its token ids, so that a
+// step launched before the host has seen these ids is fed on the device.  `mirror`: memory of the host that the device
+// can write (pinned): row *which of [rows of `mirror_stride` ints] receives the error code, three zeros and the ids,
+// and the host reads them there once an event behind the kernel has completed, with no copy of its own in the
+// stream.  Two rows in turn (the host says which, in device memory, before each step): the step that runs must not
+// overwrite what the host still reads of the step before.
 #include "common.cuh"
 #include "launch.cuh"
 #include <limits.h>
@@ -25,10 +32,18 @@ __device__ __forceinline__ unsigned long long am_key(float v, int idx) {
     return ((unsigned long long)b << 32) | (unsigned long long)(0xffffffffu - (unsigned int)idx);
 }
 
+struct ArgmaxAlso {
+    int* feed;                 // [rows] or null
+    int* mirror;               // host memory the device can write, [2][mirror_stride], or null
+    int mirror_stride;
+    const int* which;          // device int: 0 or 1, the mirror's row for this launch
+    int row0;                  // first row of this launch among the caller's rows
+};
+
 // keys, count: one entry per row of this launch, zero between launches (the caller's scratch memory).
 __global__ void __launch_bounds__(AM_THREADS) argmax_kernel(const float* __restrict__ logits, int vocab, int usable,
                                                             int per_block, int* __restrict__ out, unsigned long long* keys,
-                                                            int* count, int* report, const int* error_flag) {
+                                                            int* count, int* report, const int* error_flag, const ArgmaxAlso also) {
     PDL_ENTER();
     logits = pdl_fresh(logits);
     __shared__ float best_v[AM_THREADS / 32];
@@ -48,6 +63,11 @@ __global__ void __launch_bounds__(AM_THREADS) argmax_kernel(const float* __restr
     if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0 && report != nullptr && error_flag != nullptr) {
         const int code = *(const volatile int*)error_flag;   // every earlier kernel of the stream has ended
         if (code != 0) report[0] = code;
+        if (also.mirror != nullptr && also.row0 == 0) {
+            int* head = also.mirror + (size_t)(*also.which & 1) * also.mirror_stride;
+            head[0] = code != 0 ? code : report[0];
+            head[1] = head[2] = head[3] = 0;
+        }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -74,7 +94,10 @@ __global__ void __launch_bounds__(AM_THREADS) argmax_kernel(const float* __restr
                 __threadfence();
                 const unsigned long long key = atomicExch(&keys[r], 0ull);
                 count[r] = 0;
-                out[r] = key == AM_BAD_ROW ? -1 : key == 0ull ? 0 : (int)(0xffffffffu - (unsigned int)(key & 0xffffffffull));
+                const int id = key == AM_BAD_ROW ? -1 : key == 0ull ? 0 : (int)(0xffffffffu - (unsigned int)(key & 0xffffffffull));
+                out[r] = id;
+                if (also.feed != nullptr) also.feed[also.row0 + r] = id < 0 ? 0 : id;
+                if (also.mirror != nullptr) also.mirror[(size_t)(*also.which & 1) * also.mirror_stride + 4 + also.row0 + r] = id;
             }
         }
     }
@@ -83,9 +106,11 @@ __global__ void __launch_bounds__(AM_THREADS) argmax_kernel(const float* __restr
 // keys/count hold `key_rows` entries; `blocks_wanted` is about how many blocks the launch should have in all (the
 // caller knows the device: two per SM).  report and error_flag may be null.
 MB_API int mb_argmax(const float* logits, int rows, int vocab, int usable, int* out, unsigned long long* keys, int* count,
-                     int key_rows, int blocks_wanted, int* report, const int* error_flag, cudaStream_t s) {
+                     int key_rows, int blocks_wanted, int* report, const int* error_flag, int* feed, int* mirror, int mirror_stride,
+                     const int* mirror_which, cudaStream_t s) {
     if (rows <= 0) return 0;
     if (usable <= 0 || usable > vocab || key_rows <= 0 || keys == nullptr || count == nullptr) return MB_ERR_BAD_SIZE;
+    if (mirror != nullptr && (mirror_which == nullptr || report == nullptr || error_flag == nullptr || mirror_stride < 4 + rows)) return MB_ERR_BAD_SIZE;
     if (blocks_wanted <= 0) blocks_wanted = 1;
     for (int r0 = 0; r0 < rows; r0 += key_rows) {
         const int n = rows - r0 < key_rows ? rows - r0 : key_rows;
@@ -95,7 +120,7 @@ MB_API int mb_argmax(const float* logits, int rows, int vocab, int usable, int* 
         const int per_block = (usable + blocks - 1) / blocks;
         blocks = (usable + per_block - 1) / per_block;
         const int rc = launch_kernel(argmax_kernel, dim3(blocks, n), AM_THREADS, 0, s, 0, logits + (size_t)r0 * vocab, vocab, usable,
-                                     per_block, out + r0, keys, count, report, error_flag);
+                                     per_block, out + r0, keys, count, report, error_flag, ArgmaxAlso{feed, mirror, mirror_stride, mirror_which, r0});
         if (rc) return rc;
     }
     return 0;

@@ -152,6 +152,9 @@ class Engine:
         self.device_sampling = device_sampling and on_gpu
         #: pack the next decode step's inputs while the GPU runs the current one (Runner.prepare_next)
         self.prepare_ahead = True
+        #: launch the next decode step before the current one's tokens have reached the host (see ``step``)
+        self.run_ahead = True
+        self._ahead: Optional[dict] = None
         self.scheduler = Scheduler(self.cache, max_batch, token_budget, self.ctx)
         self._requests: Dict[Hashable, Request] = {}
         self._samplers: Dict[Hashable, Sampler] = {}
@@ -181,18 +184,61 @@ class Engine:
         Every step learns, with the sampled ids it reads anyway, whether a kernel's bounded wait gave up
         (``KernelError``).  A request whose logits are NaN or infinite is ended, the others' tokens are
         recorded, and ``GenerationError`` is raised naming it (the reference fails such a pass:
-        crates/model/src/qwen3/model.rs:128, crates/sampler/src/lib.rs:135-137)."""
+        crates/model/src/qwen3/model.rs:128, crates/sampler/src/lib.rs:135-137).
+
+        **Running ahead.**  While every request decodes greedily and nobody waits to be admitted, the step after
+        the current one is launched before the current one's tokens have reached the host: its token ids are fed on
+        the device (``Runner.launch_ahead``).  The GPU then goes from step to step without waiting for the host, and
+        a call of ``step`` returns the tokens of the older of the two steps in flight.  A request that turns out to
+        have ended (a stop token) has computed one token for nothing; its row of the step that ran ahead is dropped."""
+        ahead, self._ahead = self._ahead, None
+        if ahead is not None:
+            plan = self.scheduler.schedule_running()          # the step that is running already: who of it goes on
+            if not plan:
+                return self.step()                            # everybody ended: nothing of it counts
+            self.runner.commit_ahead(ahead, {p.request.req_id for p in plan})
+            entries = [StepEntry(p.request.req_id, p.tokens, [0]) for p in plan]
+            rows = {rid: i for i, rid in enumerate(ahead["req_ids"])}
+            if [p.request.req_id for p in plan] == list(ahead["req_ids"]) and self._may_run_ahead(plan):
+                self._ahead = self.runner.launch_ahead(entries)
+            if self._ahead is not None:
+                ids = self.runner.read_ahead(self._ahead)     # the ids of the step that ran ahead; the next one runs meanwhile
+            else:
+                ids = self.runner.read_graph_ids(ahead["rows"], ahead["which"])
+            sampled = {p.request.req_id: int(ids[rows[p.request.req_id]]) for p in plan}
+            return self._record(plan, sampled)
         plan = self.scheduler.schedule()
         if not plan:
             return []
         entries = [StepEntry(p.request.req_id, p.tokens, [len(p.tokens) - 1] if p.sample else []) for p in plan]
         logits = self.runner.step(entries)
-        if self.prepare_ahead and all(p.sample and len(p.tokens) == 1 and len(p.request.output) + 1 < p.request.params.max_tokens
-                                      for p in plan):
+        decoding = all(p.sample and len(p.tokens) == 1 for p in plan)
+        if decoding and self.run_ahead and self.runner.greedy_ids is not None and self._may_run_ahead(plan):
+            self._ahead = self.runner.launch_ahead(entries)
+            if self._ahead is not None:
+                ids = self.runner.read_ahead(self._ahead)
+                return self._record(plan, {p.request.req_id: int(t) for p, t in zip(plan, ids)})
+        if self.prepare_ahead and decoding and all(len(p.request.output) + 1 < p.request.params.max_tokens for p in plan):
             # every request decodes and none reaches its length limit: most likely the next step is this one over
             # again, one position on; its inputs are packed now, while the GPU is busy, instead of after the wait below
             self.runner.prepare_next(entries)
         sampled = self._sample(plan, logits, self._samplers, self.config.vocab_size)
+        return self._record(plan, sampled)
+
+    def _may_run_ahead(self, plan: Sequence[Planned]) -> bool:
+        """Whether the step after the one that runs may be launched before its tokens are known: all requests decode
+        greedily over the whole vocabulary, each has room for the token being made and one more, and nobody waits to
+        be admitted (a newcomer would have to wait a step longer)."""
+        if not (self.run_ahead and self.device_sampling) or self.scheduler.has_waiting():
+            return False
+        vocab = self.config.vocab_size
+        for p in plan:
+            prm = p.request.params
+            if not (prm.greedy and prm.usable_vocab in (None, vocab)) or len(p.request.output) + 2 > prm.max_tokens:
+                return False
+        return True
+
+    def _record(self, plan: Sequence[Planned], sampled: Dict[Hashable, int]) -> List[tuple]:
         emitted = self.scheduler.update(plan, sampled)          # a negative id ends its request (NON_FINITE_LOGITS)
         bad = [rid for rid, token in sampled.items() if token < 0]
         if bad:
@@ -257,10 +303,13 @@ class Engine:
         scratch = self.runner.scratch
         n = len(rows)
         if self.device_sampling and all(p.request.params.greedy and p.request.params.usable_vocab in (None, vocab) for p in rows):
-            if not (self.runner.greedy_ids is not None and len(rows) == len(plan) and self.runner.greedy_ids.numel() == n):
-                with ops.using(scratch):                      # a replayed graph has found the largest logits already
+            if self.runner.greedy_ids is not None and len(rows) == len(plan) and self.runner.greedy_ids.numel() == n:
+                ids = self.runner.read_graph_ids(n)           # a replayed graph has found the largest logits already
+            else:
+                with ops.using(scratch):
                     ops.argmax(logits, vocab, scratch.ids(n))
-            for p, token in zip(rows, scratch.read(n)):
+                ids = scratch.read(n)
+            for p, token in zip(rows, ids):
                 out[p.request.req_id] = int(token)
             return out
         if self.device_sampling:

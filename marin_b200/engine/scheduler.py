@@ -217,6 +217,24 @@ class Scheduler:
             at += count
         return plan
 
+    def schedule_running(self) -> List[Planned]:
+        """The plan of a step that is already running: the engine launched it before it had read the tokens of the step
+        before, supposing that the same requests decode on (``Engine.step``).  Requests that ended or were cancelled
+        since are not in it; nobody is admitted or preempted."""
+        n = self._lib.mbs_schedule_running(self._core, self._items.ctypes.data, len(self._items), self._tokens.ctypes.data, len(self._tokens))
+        if n < 0:
+            raise RuntimeError(f"the step that was launched ahead does not fit the scheduler's state (code {n})")
+        plan: List[Planned] = []
+        flat = self._tokens[:n].tolist()
+        for (sid, start, count, sample, handle, slot), token in zip(self._items[:n].tolist(), flat):
+            request = self._by_sid[sid]
+            request.computed = start
+            plan.append(Planned(request, [token], bool(sample)))
+        return plan
+
+    def has_waiting(self) -> bool:
+        return self._lib.mbs_list(self._core, 0, None, 0) > 0
+
     # ---- after the step ----------------------------------------------------------------------------------
     def update(self, plan: Sequence[Planned], sampled: Dict[Hashable, int]) -> List[tuple]:
         """Records what ran and the tokens sampled for the requests whose portion ended their known

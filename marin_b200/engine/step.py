@@ -71,6 +71,12 @@ class Runner:
         self.scratch = None
         if rt.device.type == "cuda":
             self.scratch = ops.Scratch(rt.device)
+        #: where a replayed graph's arg-max leaves the step's ids for the host (pinned memory the kernel writes itself,
+        #: two rows in turn) and the events behind the last two replays: the host waits for the event and reads,
+        #: with no copy of its own in the stream (``read_graph_ids``)
+        self._mirror: Optional[torch.Tensor] = None
+        self._mirror_done: List[object] = []
+        self._which = self._ran = 0
         self._pinned: Optional[torch.Tensor] = None           # host side of the packed inputs of steps run without a graph
         self._pinned_free = None                               # the event after which it may be written again
         self.steps_run = 0
@@ -165,6 +171,8 @@ class Runner:
         num_decode, max_query_len, max_seq_len = int(info[3]), int(info[4]), int(info[5])
         num_rows = W
         if static is not None:
+            self._which ^= 1
+            packed[total] = self._which          # the row of the ids' mirror this step's arg-max writes (see _graph_for)
             if pack_only:
                 return None
             dev.copy_(host, non_blocking=True)
@@ -197,6 +205,26 @@ class Runner:
         G = len(self.cache.groups)
         return pad_to * 3 + (pad_to + 1) + pad_to * 2 + pad_to + G * pad_to * self.max_pages_per_seq + G * pad_to
 
+    def _replay(self, g: dict) -> None:
+        g["graph"].replay()
+        self._mirror_done[self._which].record()
+        self._ran = self._which                  # the mirror's row the replay writes (packing ahead moves _which on)
+        ops.launches_extra(g["launches"])
+        self._replayed = g
+
+    def read_graph_ids(self, rows: int, which: Optional[int] = None) -> List[int]:
+        """The ids the arg-max of a replayed graph left in the host's mirror (-1: that row's logits were not finite), for
+        the last replay or the one before (``which``): waits for the event behind that replay, not for anything
+        launched since.  Raises ``KernelError`` if a kernel's wait gave up."""
+        w = self._ran if which is None else which
+        self._mirror_done[w].synchronize()
+        both = self._mirror[w, :4 + rows].tolist()
+        if both[0]:
+            torch.cuda.synchronize()
+            self.scratch.clear()
+            raise ops.KernelError(f"a tensor-core kernel's wait on an mbarrier gave up (code {both[0]})")
+        return both[4:]
+
     # ---- decode steps as CUDA graphs -----------------------------------------------------------------------
     def enable_graphs(self, batch_sizes: Sequence[int] = (1, 2, 4, 8, 16, 32, 64)) -> None:
         """Steps in which every request brings exactly one token are replayed from a CUDA graph captured per
@@ -228,8 +256,11 @@ class Runner:
         if g is not None:
             return g
         size = self.packed_size(bucket)
-        host = torch.zeros(size, dtype=torch.int32).pin_memory()
-        dev = torch.zeros(size, dtype=torch.int32, device=self.rt.device)
+        host = torch.zeros(size + 1, dtype=torch.int32).pin_memory()       # one int more: which row of the ids' mirror
+        dev = torch.zeros(size + 1, dtype=torch.int32, device=self.rt.device)
+        if self._mirror is None:
+            self._mirror = torch.zeros(2, 4 + self.scratch.RESULT_ROWS, dtype=torch.int32).pin_memory()
+            self._mirror_done = [torch.cuda.Event(), torch.cuda.Event()]
         # what each kind of mixer fixes ahead for this batch size and span (for attention: the split of the keys, which
         # is part of the captured grid, and scratch of the capture's own), asked of the mixers themselves
         shared = next((o for (b, _), o in self.graphs.items() if b == bucket), None)
@@ -269,7 +300,9 @@ class Runner:
             with ops.using(self.scratch), torch.cuda.graph(graph):
                 g["logits"] = self.model.forward(ctx, self.views)
                 ops.stage_name = "sampling"
-                ops.argmax(g["logits"], self.vocab, g["best"])    # greedy sampling rides in the same graph
+                # greedy sampling rides in the same graph; the ids also go where the next step reads its token ids
+                # (a step launched ahead is fed there) and, written by the kernel itself, to the host's mirror
+                ops.argmax(g["logits"], self.vocab, g["best"], feed=dev[:bucket], mirror=self._mirror, which=dev[size:size + 1])
         finally:
             g["labels"], ops.launch_log = ops.launch_log, logging
             if collecting:
@@ -287,9 +320,7 @@ class Runner:
             return None
         g = self._graph_for(bucket, entries)
         self.build_context(entries, pad_to=bucket, static=g["static"], refresh_only=True)
-        g["graph"].replay()
-        ops.launches_extra(g["launches"])
-        self._replayed = g
+        self._replay(g)
         rows = [i for i, e in enumerate(entries) for _ in e.want]
         if rows == list(range(len(entries))):
             self.greedy_ids = g["best"][: len(entries)]      # the largest logit of each returned row, already found
@@ -358,6 +389,49 @@ class Runner:
         self._prepared = {"graph": g, "ids": [e.req_id for e in entries], "handles": handles, "counts": counts, "longest": longest}
         return True
 
+    # ---- the next step, launched before this one's tokens are known ------------------------------------------------
+    def launch_ahead(self, entries: Sequence[StepEntry]) -> Optional[dict]:
+        """To be called right after a step of single tokens that was replayed from a graph, with the same entries.
+        Supposes that the same requests go on with the tokens this step is about to produce, and launches that next
+        step now: the ids the graph's arg-max leaves on the device are copied into the next step's inputs on the device,
+        so the GPU goes from one step into the next while the host still waits for, reads and books the first one's
+        tokens.  Returns a handle for ``read_ahead`` / ``commit_ahead``, or None if the step could not be prepared (no
+        pages, context full, the sequences grow into another graph): then nothing was launched.
+
+        The launched step's lengths are NOT committed here: the caller commits them for the requests that turn out to
+        go on (``commit_ahead``) once it knows; a request that ended meanwhile has computed one token for nothing."""
+        g = self._replayed
+        if g is None or self.scratch is None or not self.prepare_next(entries):
+            return None
+        prepared, self._prepared = self._prepared, None
+        n, bucket = len(entries), g["key"][0]
+        before = self._ran                                     # the running step's row of the ids' mirror
+        host, dev, copied = g["static"]
+        # positions, lengths, tables and places of the next step; its token ids are on the device already: the running
+        # step's arg-max puts them there, never seen by the host
+        dev[bucket:].copy_(host[bucket:], non_blocking=True)
+        copied.record()
+        self._replay(g)
+        self._longest = prepared["longest"]
+        self.greedy_ids = g["best"][:n]
+        return {"before": before, "which": self._which, "rows": n, "req_ids": prepared["ids"], "handles": prepared["handles"], "graph": g}
+
+    def read_ahead(self, ahead: dict) -> List[int]:
+        """The ids of the step BEFORE the one ``launch_ahead`` launched: waits for that step only, not for the one that runs."""
+        return self.read_graph_ids(ahead["rows"], ahead["before"])
+
+    def commit_ahead(self, ahead: dict, live: Sequence[Hashable]) -> None:
+        """Books the step ``launch_ahead`` launched, for the requests of it that are still live (in ``live``)."""
+        keep = [i for i, rid in enumerate(ahead["req_ids"]) if rid in live and rid in self.cache.requests
+                and self.cache.requests[rid].handle == int(ahead["handles"][i])]
+        if keep:
+            handles = np.ascontiguousarray(ahead["handles"][keep])
+            counts = np.ones(len(keep), np.int32)
+            rc = self.cache._lib.mbh_step_commit(self.cache._core(), len(keep), handles.ctypes.data, counts.ctypes.data)
+            if rc != OK:
+                raise StepError(f"recording the step launched ahead failed (code {rc})")
+        self.steps_run += 1
+
     def _is_the_prepared_step(self, prepared: dict, entries: Sequence[StepEntry]) -> bool:
         ids, handles, requests = prepared["ids"], prepared["handles"], self.cache.requests
         if len(entries) != len(ids):
@@ -373,13 +447,11 @@ class Runner:
         host.numpy()[:n] = [e.tokens[0] for e in entries]      # the token ids lead the packed buffer
         dev.copy_(host, non_blocking=True)
         copied.record()
-        g["graph"].replay()
-        ops.launches_extra(g["launches"])
+        self._replay(g)
         self._longest = prepared["longest"]
         rc = self.cache._lib.mbh_step_commit(self.cache._core(), n, prepared["handles"].ctypes.data, prepared["counts"].ctypes.data)
         if rc != OK:
             raise StepError(f"recording the step failed (code {rc})")
         self.steps_run += 1
-        self._replayed = g
         self.greedy_ids = g["best"][:n]
         return g["logits"][:n]

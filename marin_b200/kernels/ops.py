@@ -731,17 +731,28 @@ def add_into(y: torch.Tensor, x: torch.Tensor) -> None:
     _check(_lib("mb_elementwise").mb_add_into(_ptr(y), _ptr(x), _code(x), _c_size_t(y.numel()), _stream()), "add_into")
 
 
-def argmax(logits: torch.Tensor, usable: int, out: torch.Tensor) -> None:
+def argmax(logits: torch.Tensor, usable: int, out: torch.Tensor, feed: Optional[torch.Tensor] = None,
+           mirror: Optional[torch.Tensor] = None, which: Optional[torch.Tensor] = None) -> None:
     """``out[r]`` = id of the largest of the first ``usable`` logits of row ``r`` (lowest id among equals); -1 for a
-    row that holds a NaN or an infinity among them."""
-    _need_cuda(logits, out)
+    row that holds a NaN or an infinity among them.
+
+    ``feed`` (int32 ``[rows]`` on the device) receives the ids too (0 for such a row): the next step's token ids, for a
+    step that is launched before the host has seen these.  ``mirror`` (pinned host memory, int32 ``[2, 4 + rows or more]``)
+    with ``which`` (a device int, 0 or 1): row ``which`` of it receives the error code of the current scratch, three zeros
+    and the ids, written by the kernel itself; the host reads them once an event recorded behind the launch has completed."""
+    _need_cuda(logits, out, feed, which)
     rows, vocab = logits.shape
     assert logits.dtype == torch.float32 and out.dtype == torch.int32 and out.numel() == rows
+    assert feed is None or (feed.dtype == torch.int32 and feed.numel() >= rows)
+    if mirror is not None:
+        assert (mirror.dtype == torch.int32 and mirror.is_pinned() and mirror.dim() == 2 and mirror.shape[0] == 2 and mirror.is_contiguous()
+                and mirror.shape[1] >= 4 + rows and which is not None and which.dtype == torch.int32 and rows <= _scratch_for(logits.device).ARGMAX_ROWS)
     s = _scratch_for(logits.device)
     _cost(rows * usable * 4)
     _check(_lib("mb_sampling").mb_argmax(_ptr(logits), _c_int(rows), _c_int(vocab), _c_int(usable), _ptr(out), _ptr(s.argmax_keys),
                                         _ptr(s.argmax_count), _c_int(s.ARGMAX_ROWS), _c_int(2 * s.sm_count), _ptr(s.report),
-                                        _ptr(s.error), _stream()), "argmax")
+                                        _ptr(s.error), _ptr(feed), _ptr(mirror), _c_int(mirror.shape[1] if mirror is not None else 0),
+                                        _ptr(which), _stream()), "argmax")
 
 
 def sample(logits: torch.Tensor, usable: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,

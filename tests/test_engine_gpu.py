@@ -180,23 +180,31 @@ def test_greedy_generation_through_the_entry_point(case):
     assert not engine.cache.requests
 
 
-def test_steps_packed_ahead_change_nothing(case):
-    """While a decode step runs the engine packs the next one on the supposition that the same requests go on.  The
-    supposition fails when a request ends on a stop token, is cancelled or another joins: requests of different
-    lengths, one that stops on a token it is known to produce, one added and one cancelled half way, run with and
-    without packing ahead, must give the same tokens, and the packed steps must really have been used."""
+def test_steps_packed_or_launched_ahead_change_nothing(case):
+    """While a decode step runs the engine supposes that the same requests go on: it packs the next step's inputs, and
+    where everybody decodes greedily it even launches that step, fed with the token ids the running step leaves on the
+    device, before the host has seen them.  The supposition fails when a request ends on a stop token, is cancelled or
+    another joins: requests of different lengths, one that stops on a token it is known to produce, one added and one
+    cancelled half way, run with steps launched ahead, with steps only packed ahead, and with neither, must give the
+    same tokens; and the steps launched or packed ahead must really have been used."""
     from marin_b200 import Engine, SamplingParams
 
     rng = random.Random(31)
     prompts = [random_prompt(rng, case.raw["vocab_size"], n) for n in (9, 3, 17, 6)]
 
-    def run(ahead: bool):
+    def run(pack: bool, launch: bool):
         engine = Engine(case.dir, dtype=case.dtype, ctx=case.raw["max_position_embeddings"], page_size=case.page,
                         max_batch=4, token_budget=32)
-        engine.prepare_ahead = ahead
-        used = [0]
-        inner = engine.runner._run_prepared
-        engine.runner._run_prepared = lambda *a: (used.__setitem__(0, used[0] + 1), inner(*a))[1]
+        engine.prepare_ahead, engine.run_ahead = pack, launch
+        used = {"packed": 0, "launched": 0}
+        packed, launched = engine.runner._run_prepared, engine.runner.launch_ahead
+        engine.runner._run_prepared = lambda *a: (used.__setitem__("packed", used["packed"] + 1), packed(*a))[1]
+
+        def count_launch(entries):
+            handle = launched(entries)
+            used["launched"] += handle is not None
+            return handle
+        engine.runner.launch_ahead = count_launch
         first = engine.generate([prompts[0]], SamplingParams(temperature=0.0, max_tokens=10))[0].tokens
         stop = first[6]                                       # request 0 run again ends when it produces this token
         ids = [engine.add_request(prompts[0], SamplingParams(temperature=0.0, max_tokens=30, stop_tokens=(stop,))),
@@ -219,14 +227,18 @@ def test_steps_packed_ahead_change_nothing(case):
             engine.forget(i)
         engine.cache.check()
         assert not engine.cache.requests
-        return first, [out[i] for i in ids], used[0]
+        assert [engine.generate([prompts[0]], SamplingParams(temperature=0.0, max_tokens=10))[0].tokens] == [first]   # and once more after all that
+        engine.cache.check()
+        assert not engine.cache.requests and all(g.pool.num_held == 0 for g in engine.cache.groups)
+        return first, [out[i] for i in ids], used
 
-    first_a, with_ahead, used = run(True)
-    first_b, without, unused = run(False)
-    assert used >= 10 and unused == 0
-    assert first_a == first_b and with_ahead == without
-    assert len(with_ahead[0]) == first_a.index(first_a[6])   # the stop token itself is not emitted
-    assert len(with_ahead[1]) == 14 and len(with_ahead[3]) == 9
+    first_a, launched_ahead, used_a = run(True, True)
+    first_b, packed_ahead, used_b = run(True, False)
+    first_c, neither, used_c = run(False, False)
+    assert used_a["launched"] >= 10 and used_b["packed"] >= 10 and used_b["launched"] == 0 and used_c == {"packed": 0, "launched": 0}
+    assert first_a == first_b == first_c and launched_ahead == packed_ahead == neither
+    assert len(neither[0]) == first_a.index(first_a[6])   # the stop token itself is not emitted
+    assert len(neither[1]) == 14 and len(neither[3]) == 9
 
 
 def test_a_wait_that_gave_up_is_reported(case):
@@ -253,7 +265,8 @@ def test_a_wait_that_gave_up_is_reported(case):
     engine.step()
     flag.fill_(14)
     with pytest.raises(KernelError, match="14"):
-        engine.step()
+        engine.step()                                         # the step that ran ahead was launched before the flag went up ...
+        engine.step()                                         # ... so the one after it brings the news
     engine.check_device()                                     # nothing is left to report
 
 
