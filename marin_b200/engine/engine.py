@@ -21,6 +21,7 @@ from ..config.base import ModelConfig, load_config
 from ..kernels import ops
 from ..models import Model, architecture_of
 from ..parts.base import Runtime
+from ..parts.spec import TensorSpec
 from ..sampling.sampler import Sampler, SamplerError, SamplingParams
 from ..weights.loader import load_tensors
 from ..weights.random_init import random_tensor
@@ -63,10 +64,20 @@ def load_model(model_dir: str, rt: Runtime, extra_tensors: str = "error") -> (Mo
 def load_random(model: Model, seed: int, rt: Runtime) -> None:
     """Random weights made directly on the device (no folder is written)."""
     dev = rt.device if rt.device.type == "cuda" else "cpu"
-    tensors = {}
-    for spec in model.tensor_specs():
-        tensors[spec.name] = random_tensor(spec, seed, rt.dtype if spec.role != "norm" else torch.float32, dev)
-    model.load(tensors, rt)
+
+    class Drawn(dict):
+        """The tensors by name, each drawn when a part takes it: at no time are all of them there twice (once as drawn,
+        once as the parts keep them, fused and laid out for the kernels)."""
+
+        def pop(self, name, *default):
+            spec = super().pop(name, *default)
+            if not isinstance(spec, TensorSpec):
+                return spec
+            return random_tensor(spec, seed, rt.dtype if spec.role != "norm" else torch.float32, dev)
+
+    model.load(Drawn({spec.name: spec for spec in model.tensor_specs()}), rt)
+    if rt.device.type == "cuda":
+        torch.cuda.empty_cache()
 
 
 def random_model(config: ModelConfig, seed: int, rt: Runtime) -> Model:
@@ -131,19 +142,24 @@ class Engine:
         self.footprint = plan_memory(self.model, self.rt.dtype, page_size, self.ctx, max_batch, token_budget, num_pages,
                                      graph_sizes, free)
         self.num_pages = self.footprint.num_pages
+        # The pool first, while the device is still empty: what loading holds for a moment (a float32 draw of a random
+        # table, staging copies) then fits in the room planned for working memory, and no fragment of it is left
+        # standing between the weights when the largest allocation of all is made.
+        needs = self.model.cache_needs()
+        self.cache = CacheManager(needs, [e.cache_of for e in self.model.spec.schedule], page_size,
+                                  self.num_pages, max_requests=max_batch)
+        self.cache.allocate(self.rt.device, self.rt.dtype)
         self.ignored_tensors: List[str] = []
         if model is not None:
             tensors = load_tensors(model, self.model.tensor_specs(), self.model.spec.ignorable, extra_tensors, self.ignored_tensors)
             self.model.load(tensors, self.rt)
+            del tensors
         else:
             load_random(self.model, seed, self.rt)
         if on_gpu:
             from ..kernels import build
             build.build_for(self.model, self.rt.dtype, verbose=True)
-        needs = self.model.cache_needs()
-        self.cache = CacheManager(needs, [e.cache_of for e in self.model.spec.schedule], page_size,
-                                  self.num_pages, max_requests=max_batch)
-        self.cache.allocate(self.rt.device, self.rt.dtype)
+            torch.cuda.empty_cache()
         self.runner = Runner(self.model, self.cache, self.rt, self.ctx)
         if graph_sizes:
             self.runner.enable_graphs(graph_sizes)

@@ -15,8 +15,12 @@ from typing import Optional, Sequence
 
 import torch
 
-#: kept free for kernel code, the CUDA context's own allocations and fragmentation (the reference's figure)
+#: kept free for kernel code, the CUDA context's own allocations and fragmentation (the reference's figure) ...
 SLACK_BYTES = 512 * 1024 * 1024
+#: ... and on top of it this fraction of what is free: an allocator that hands out memory in segments of megabytes
+#: leaves more unusable the more it manages (measured on a 180 GB device filled to the brim: 0.7 GiB held in part-used
+#: segments and as much again in kernel modules loaded after the plan was made)
+SLACK_FRACTION = 1.0 / 64
 
 
 class OutOfDeviceMemory(RuntimeError):
@@ -72,12 +76,14 @@ def workspace_bytes(model, dtype: torch.dtype, token_budget: int, max_batch: int
 
 def plan(model, dtype: torch.dtype, page_size: int, ctx: int, max_batch: int, token_budget: int,
          num_pages: Optional[int], graph_sizes: Sequence[int] = (), free_bytes: Optional[int] = None,
-         slack: int = SLACK_BYTES) -> Footprint:
+         slack: Optional[int] = None) -> Footprint:
     """The footprint of an engine with these options.  ``num_pages`` None: as many pages as ``max_batch`` sequences
     of ``ctx`` positions need, or as many as fit if that is fewer (at least one sequence's worth, else an error).
     Raises ``OutOfDeviceMemory`` naming weights, cache, working memory and the largest pool that would fit."""
     from ..cache.manager import CacheManager
 
+    if slack is None:
+        slack = SLACK_BYTES + (int(free_bytes * SLACK_FRACTION) if free_bytes is not None else 0)
     needs = model.cache_needs()
     probe = CacheManager(needs, [e.cache_of for e in model.spec.schedule], page_size, 1, max_batch)
     page, state = probe.bytes_per_page(dtype), probe.state_bytes()

@@ -21,6 +21,9 @@ from .safetensors_io import write_safetensors
 
 MATRIX_STD = 0.02
 NORM_STD = 0.05
+#: most elements drawn in one go (tensors above this are drawn in runs of rows: same seed, same values every time, but
+#: not the values one draw of the whole tensor would give)
+DRAW_AT_ONCE = 1 << 26
 
 
 def _seed_for(seed: int, name: str) -> int:
@@ -34,6 +37,17 @@ def random_tensor(spec: TensorSpec, seed: int, dtype: torch.dtype, device="cpu",
     gen.manual_seed(_seed_for(seed, spec.name))
     if spec.role == "int_table":
         return torch.randint(0, 2 ** 15, spec.shape, generator=gen, device=device, dtype=torch.int32)
+    count = 1
+    for n in spec.shape:
+        count *= int(n)
+    if count > DRAW_AT_ONCE and dtype != torch.float32 and len(spec.shape) >= 1:
+        # a large table is drawn in runs of rows, so that the float32 draw never holds more than a fraction of it
+        out = torch.empty(spec.shape, device=device, dtype=dtype)
+        rows = max(1, DRAW_AT_ONCE // max(1, count // int(spec.shape[0])))
+        for at in range(0, int(spec.shape[0]), rows):
+            part = torch.randn((min(rows, int(spec.shape[0]) - at), *spec.shape[1:]), generator=gen, device=device, dtype=torch.float32)
+            out[at:at + rows] = ((1.0 + norm_std * part) if spec.role == "norm" else matrix_std * part).to(dtype)
+        return out
     values = torch.randn(spec.shape, generator=gen, device=device, dtype=torch.float32)
     if spec.role == "norm":
         values = 1.0 + norm_std * values

@@ -78,11 +78,11 @@ def test_pool_defaults_to_what_fits_and_too_much_is_refused_with_the_numbers():
     # plenty of room: the pool is what was wanted; the slack counts at the edge
     small = build(TINY_B)
     fp = plan(small, torch.float32, 8, 256, 4, 64, None, (), free_bytes=4 * GIB)
-    assert fp.num_pages == fp.pages_wanted == 4 * 32 and fp.slack == SLACK_BYTES
-    edge = fp.needed
-    assert plan(small, torch.float32, 8, 256, 4, 64, 128, (), free_bytes=edge).num_pages == 128
+    assert fp.num_pages == fp.pages_wanted == 4 * 32 and fp.slack == SLACK_BYTES + 4 * GIB // 64
+    edge = fp.needed - fp.slack + SLACK_BYTES            # with a slack given by the caller the edge is exact
+    assert plan(small, torch.float32, 8, 256, 4, 64, 128, (), free_bytes=edge, slack=SLACK_BYTES).num_pages == 128
     with pytest.raises(OutOfDeviceMemory):
-        plan(small, torch.float32, 8, 256, 4, 64, 128, (), free_bytes=edge - 1)
+        plan(small, torch.float32, 8, 256, 4, 64, 128, (), free_bytes=edge - 1, slack=SLACK_BYTES)
     # nobody asked the device: the plan is made, nothing is refused
     assert plan(model, dtype, 16, 40960, 64, 2048, None, ()).num_pages == 64 * 2560
 
