@@ -539,3 +539,96 @@ def test_two_attention_layouts_in_one_model_decode_from_graphs(tmp_path, dtype):
         torch.testing.assert_close(got[rid].cpu().float(), twin(tokens[rid]), **tol)
     cache.check()
     runner.scratch.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_layers_that_keep_a_window_of_keys_beside_layers_that_keep_all(tmp_path, dtype):
+    """A toy model of three attention layers: one keeps all keys, two keep a window (24 and 40 positions, one of them
+    with other head sizes).  Three cache groups with pools of their own; a windowed group gives a page back as soon as
+    the window has passed it, so its pool can be far smaller than the sequences are long, and the pages come round
+    again within one request.  Whole, in portions, decoded from graphs and mixed with other requests, against the
+    plain implementation's layer function with each layer's own window."""
+    from test_engine_gpu import close
+
+    from marin_b200.cache import CacheManager
+    from marin_b200.config.base import ModelConfig
+    from marin_b200.engine import Runner, StepEntry, load_model, parse_dtype
+    from marin_b200.models import register_architecture
+    from marin_b200.parts import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+    from marin_b200.weights import write_random_model
+
+    layers = [(4, 2, 32, None), (4, 2, 32, 24), (2, 1, 64, 40)]          # (heads, kv heads, head size, window)
+
+    @dataclass
+    class Toy4Config(ModelConfig):
+        @classmethod
+        def from_dict(cls, raw, generation=None):
+            return cls(architecture="ToyWindowLM", model_type="toy_window", vocab_size=raw["vocab_size"], hidden_size=raw["hidden_size"],
+                       max_position_embeddings=raw["max_position_embeddings"], raw=dict(raw))
+
+        def to_json_dict(self):
+            return dict(self.raw)
+
+    def build_spec(cfg):
+        h = cfg.hidden_size
+        norm = PartSpec("rmsnorm", {"dim": h, "eps": 1e-6})
+        names = {"norm1": "input_layernorm", "mixer": "self_attn", "norm2": "post_attention_layernorm", "feedforward": "mlp"}
+        specs = [LayerSpec("prenorm", norm,
+                           PartSpec("gqa_attention", {"hidden": h, "heads": H, "kv_heads": K, "head_dim": d, "qk_norm": True, "norm_eps": 1e-6,
+                                                      "window": w, "position": PartSpec("rope", {"head_dim": d, "theta": 1e4})}),
+                           PartSpec("swiglu", {"hidden": h, "intermediate": 160}), f"model.layers.{i}", names)
+                 for i, (H, K, d, w) in enumerate(layers)]
+        return ModelSpec(hidden_size=h, vocab_size=cfg.vocab_size,
+                         embedding=PartSpec("token_table", {"vocab": cfg.vocab_size, "hidden": h, "name": "model.embed_tokens"}),
+                         final_norm=PartSpec("rmsnorm", {"dim": h, "eps": 1e-6, "name": "model.norm"}),
+                         head=PartSpec("linear", {"vocab": cfg.vocab_size, "hidden": h, "name": "lm_head"}),
+                         layers=specs, schedule=[ScheduleEntry(i) for i in range(len(layers))])
+
+    register_architecture("ToyWindowLM", "toy_window", Toy4Config, build_spec)
+    raw = {"architectures": ["ToyWindowLM"], "model_type": "toy_window", "vocab_size": 173, "hidden_size": 128, "max_position_embeddings": 400}
+    d = write_random_model(str(tmp_path / "toy4"), Toy4Config.from_dict(raw), seed=8, dtype=parse_dtype(dtype), matrix_std=0.09)
+    rt = runtime(parse_dtype(dtype))
+    config, model = load_model(d, rt)
+    w = plain.read_weights(d)
+    stored = plain.as_bf16 if dtype == "bfloat16" else plain.same
+
+    def twin(ids):
+        x = plain.embed(ids, w["model.embed_tokens.weight"])
+        for i, (H, K, hd, window) in enumerate(layers):
+            cfg = {"heads": H, "kv_heads": K, "head_dim": hd, "eps": 1e-6, "theta": 1e4}
+            x, _ = plain.layer_forward(cfg, w, i, x, window=window, stored=stored)
+        return plain.linear(stored(plain.rms_norm(x, w["model.norm.weight"], 1e-6)), w["lm_head.weight"])
+
+    page = 8
+    # every group gets the same number of pages: enough for three requests side by side where all keys are kept; the
+    # windowed groups prove below that they live on a handful of them
+    cache = CacheManager(model.cache_needs(), [e.cache_of for e in model.spec.schedule], page, 96, 4)
+    cache.allocate(rt.device, rt.dtype)
+    assert [g.need.window for g in cache.groups] == [None, 24, 40]
+    runner = Runner(model, cache, rt, 400)
+    runner.GRAPH_MIN_SPAN = 64
+    runner.enable_graphs((1, 2, 4))
+    rng = random.Random(12)
+    lengths = {"a": 370, "b": 30, "c": 121, "d": 64, "e": 200}
+    tokens = {rid: random_prompt(rng, 173, n) for rid, n in lengths.items()}
+    want = {rid: twin(t) for rid, t in tokens.items()}
+    close(run_whole(runner, "w", tokens["a"]), want["a"], dtype, "whole")
+    close(run_portions(runner, "p", tokens["a"], portions(370, [23, 2, 57, 9, 1, 1, 1, 30])), want["a"], dtype, "portions")
+    # a long decode: the windowed groups never hold more than the window's pages (+1 for the page being filled, +1 for alignment)
+    runner.begin("long")
+    runner.step([StepEntry("long", tokens["a"][:10], [])])
+    most = [0, 0, 0]
+    rows = []
+    for t in range(10, 370):
+        rows.append(runner.step([StepEntry("long", [tokens["a"][t]], [0])]).clone())
+        for g, group in enumerate(cache.groups):
+            most[g] = max(most[g], group.pool.num_held)
+    close(torch.cat(rows), want["a"][10:], dtype, "decoded one by one")
+    assert most[0] == -(-370 // page) and most[1] <= 24 // page + 2 and most[2] <= 40 // page + 2, most
+    runner.end("long")
+    got = run_mixed(runner, tokens, mixed_schedule(rng, lengths, max_live=3, decode_tail=40, sizes=(31, 2, 70, 5)))
+    for rid in tokens:
+        close(got[rid], want[rid], dtype, f"mixed {rid}")
+    cache.check()
+    assert all(g.pool.num_held == 0 for g in cache.groups)
+    runner.scratch.check()
