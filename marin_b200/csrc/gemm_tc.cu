@@ -665,6 +665,10 @@ __global__ void __launch_bounds__(320) gemm_tc_persistent_kernel(const __grid_co
 
 // ---- host side ----------------------------------------------------------------------------------------------
 
+#ifndef TC_STAGES16
+#define TC_STAGES16 6          // ring depth with up to 16 tokens per CTA
+#endif
+
 template <int BN, int STAGES>
 static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int mode, int T, int N, int K, int splits,
                      int kb_per_split, float* partials, int* counters, int* error_flag, int cluster_reduce,
@@ -822,7 +826,7 @@ static int gemm_tc_dispatch(const void* x, const void* w, void* out, int mode, i
     rc = make_map(&mx, x, T, K, bn);
     if (rc) return rc;
     switch (bn) {
-        case 16: return launch_tc<16, 6>(mw, mx, out, mode, T, N, K, splits, kb_per_split, partials, counters, error_flag, cluster_reduce, norm, scale, heads, s);
+        case 16: return launch_tc<16, TC_STAGES16>(mw, mx, out, mode, T, N, K, splits, kb_per_split, partials, counters, error_flag, cluster_reduce, norm, scale, heads, s);
         case 32: return launch_tc<32, 5>(mw, mx, out, mode, T, N, K, splits, kb_per_split, partials, counters, error_flag, cluster_reduce, norm, scale, heads, s);
         case 64: return launch_tc<64, 4>(mw, mx, out, mode, T, N, K, splits, kb_per_split, partials, counters, error_flag, cluster_reduce, norm, scale, heads, s);
         case 128: return launch_tc<128, 3>(mw, mx, out, mode, T, N, K, splits, kb_per_split, partials, counters, error_flag, cluster_reduce, norm, scale, heads, s);
