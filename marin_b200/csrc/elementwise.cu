@@ -300,6 +300,25 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
     }
 }
 
+// cos and sin of position * inv_freq for every token of a step, made once per step for the kernels that rotate heads
+// inside a matrix product's epilogue: out[t][0 .. half) = cos, out[t][half .. 2 half) = sin (float32 angles, sincosf).
+__global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq, int half, float* __restrict__ out, int T) {
+    PDL_ENTER();
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= T * half) return;
+    const int t = idx / half, i = idx - t * half;
+    float sn, cs;
+    sincosf((float)positions[t] * inv_freq[i], &sn, &cs);
+    out[(size_t)t * 2 * half + i] = cs;
+    out[(size_t)t * 2 * half + half + i] = sn;
+}
+
+MB_API int mb_rope_table(const int* positions, const float* inv_freq, int half, float* out, int T, cudaStream_t s) {
+    if (T <= 0 || half <= 0) return 0;
+    const int total = T * half;
+    return launch_kernel(rope_table_kernel, dim3((total + 255) / 256), dim3(256), 0, s, 0, positions, inv_freq, half, out, T);
+}
+
 MB_API int mb_swiglu(const void* gate_up, void* out, int dtype, int tokens, int I, int interleaved, cudaStream_t s) {
     const size_t total = (size_t)tokens * I;
     if (total == 0) return 0;

@@ -421,17 +421,18 @@ struct TcStreamK {
 struct TcWalk {
     int nkb, limit, step, at, token_tile, tiles_t;
     bool streamk;
-    __device__ TcWalk(const TcStreamK& sk, bool streamk_, int tiles_n, int tiles_t_, int nkb_) : nkb(nkb_), tiles_t(tiles_t_), streamk(streamk_) {
+    // `unit` of `units` walkers: a CTA of the grid, or a pair of CTAs
+    __device__ TcWalk(const TcStreamK& sk, bool streamk_, int tiles_n, int tiles_t_, int nkb_, int unit, int units) : nkb(nkb_), tiles_t(tiles_t_), streamk(streamk_) {
         if (streamk) {
-            const int group = blockIdx.x / tiles_t_;
-            token_tile = blockIdx.x - group * tiles_t_;
+            const int group = unit / tiles_t_;
+            token_tile = unit - group * tiles_t_;
             const long long total = (long long)tiles_n * nkb_;
             const long long from = (long long)group * sk.units_per_group, to = from + sk.units_per_group;
             at = (int)(from < total ? from : total);
             limit = (int)(to < total ? to : total);
             step = 0;
         } else {
-            at = blockIdx.x; limit = tiles_n * tiles_t_; step = gridDim.x; token_tile = 0;
+            at = unit; limit = tiles_n * tiles_t_; step = units; token_tile = 0;
         }
     }
     // the next piece: k-blocks [kb0, kb1) of `tile` (numbered with the token tiles fastest)
@@ -447,40 +448,59 @@ struct TcWalk {
     }
 };
 
-template <int BN, int STAGES, bool SK>
+// PAIR: two CTAs (a cluster of two, on the two SMs of a TPC) share a tile of 256 weight rows x BN tokens.  Each loads
+// its own 128 weight rows and half of the tokens; one thread of the even CTA issues MMAs of 256 rows
+// (tcgen05 cta_group::2) that read both CTAs' shared memory and fill both CTAs' tensor memory, so each SM moves
+// two thirds of the shared-memory bytes per flop of the single-CTA form; each CTA drains its own 128 rows.
+template <int BN, int STAGES, bool SK, bool PAIR = false>
 __global__ void __launch_bounds__(320) gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                  const __grid_constant__ CUtensorMap map_x,
                                                                  void* __restrict__ out, int mode, int T, int N, int K,
                                                                  int* __restrict__ error_flag, const TcNormOut norm,
-                                                                 const TcRowScale scale, const TcStreamK sk) {
+                                                                 const TcRowScale scale, const TcStreamK sk, const TcHeadsOut heads,
+                                                                 const float* __restrict__ rope) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ float s_pscale[2][BN];          // the per-token factors of a coupled norm, for the tile in each accumulator
+    // heads finished in the epilogue: per half of the columns (its four warps), two staging buffers of sixteen tokens
+    __shared__ __align__(16) bf16 s_hx[2][2][16 * TC_BM];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    static_assert(!(PAIR && SK), "pairs walk whole tiles");
     using L = TcSmem<BN>;
-    uint64_t* full = (uint64_t*)(smem + STAGES * L::STAGE_BYTES);
+    constexpr int BNL = PAIR ? BN / 2 : BN;                          // tokens this CTA loads of a tile
+    constexpr int STAGE_BYTES = L::A_BYTES + BNL * TC_BK * 2;
+    constexpr int ROWS = PAIR ? 2 * TC_BM : TC_BM;                   // weight rows of a tile
+    uint64_t* full = (uint64_t*)(smem + STAGES * STAGE_BYTES);
     uint64_t* empty = full + STAGES;
     uint64_t* acc_full = empty + STAGES;       // [2]
     uint64_t* acc_empty = acc_full + 2;        // [2]
     uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tiles_n = (N + TC_BM - 1) / TC_BM, tiles_t = (T + BN - 1) / BN;
-    const int total_tiles = tiles_n * tiles_t;
+    const uint32_t rank = PAIR ? cluster_ctarank() : 0u;             // 0: the CTA whose barriers count and whose thread issues
+    const int unit = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x, units = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+    const int tiles_n = (N + ROWS - 1) / ROWS, tiles_t = (T + BN - 1) / BN;
     const int nkb = (K + TC_BK - 1) / TC_BK;
     constexpr uint32_t TMEM_COLS = 2 * BN <= 32 ? 32 : 2 * BN <= 64 ? 64 : 2 * BN <= 128 ? 128 : 2 * BN <= 256 ? 256 : 512;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 8); }
+        // the accumulators are given back by the eight epilogue warps of every CTA that holds a part of them
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], PAIR ? 16 : 8); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
         __syncwarp();
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if (PAIR) {          // a warp of each CTA of the pair asks; each CTA finds the address in its own slot
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    if (PAIR) cluster_sync_all();              // the other CTA's barriers are there before anything arrives on them
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
     PDL_ENTER_EARLY();
@@ -488,24 +508,33 @@ __global__ void __launch_bounds__(320) gemm_tc_persistent_kernel(const __grid_co
     if (warp == 0 && lane == 0) {
         int it = 0;                                                   // k-blocks issued so far, over all tiles
         bool ok = true;
-        TcWalk walk(sk, SK, tiles_n, tiles_t, nkb);
+        TcWalk walk(sk, SK, tiles_n, tiles_t, nkb, unit, units);
         for (int tile, kb0, kb1; ok && walk.next(tile, kb0, kb1);) {
-            const int n0 = tile_rows(tile, tiles_n, tiles_t) * TC_BM, t0 = tile_tokens(tile, tiles_n, tiles_t) * BN;
+            const int n0 = tile_rows(tile, tiles_n, tiles_t) * ROWS + (int)rank * TC_BM;
+            const int t0 = tile_tokens(tile, tiles_n, tiles_t) * BN + (int)rank * BNL;
             for (int kb = kb0; kb < kb1; ++kb, ++it) {
                 const int s = it % STAGES;
                 const uint32_t phase = (it / STAGES) & 1;
                 if (!mbar_wait(&empty[s], phase ^ 1)) { atomicExch(error_flag, 11); ok = false; break; }
-                mbar_expect_tx(&full[s], L::STAGE_BYTES);
-                uint8_t* a = smem + s * L::STAGE_BYTES;
-                tma_load_2d(a, &map_w, kb * TC_BK, n0, &full[s]);
-                tma_load_2d(a + L::A_BYTES, &map_x, kb * TC_BK, t0, &full[s]);
+                uint8_t* a = smem + s * STAGE_BYTES;
+                if (PAIR) {
+                    // both CTAs' bytes are counted on the even CTA's barrier, which its MMA thread waits on
+                    if (rank == 0) mbar_expect_tx(&full[s], 2 * STAGE_BYTES);
+                    const uint32_t bar = cluster_addr(smem_u32(&full[s]), 0);
+                    tma_load_2d_pair(a, &map_w, kb * TC_BK, n0, bar);
+                    tma_load_2d_pair(a + L::A_BYTES, &map_x, kb * TC_BK, t0, bar);
+                } else {
+                    mbar_expect_tx(&full[s], STAGE_BYTES);
+                    tma_load_2d(a, &map_w, kb * TC_BK, n0, &full[s]);
+                    tma_load_2d(a + L::A_BYTES, &map_x, kb * TC_BK, t0, &full[s]);
+                }
             }
         }
-    } else if (warp == 1 && lane == 0) {
-        constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+    } else if (warp == 1 && lane == 0 && rank == 0) {
+        constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);
         int it = 0, local = 0;
         bool ok = true;
-        TcWalk walk(sk, SK, tiles_n, tiles_t, nkb);
+        TcWalk walk(sk, SK, tiles_n, tiles_t, nkb, unit, units);
         for (int tile, kb0, kb1; ok && walk.next(tile, kb0, kb1); ++local) {
             const int buf = local & 1;
             const uint32_t acc_phase = (local >> 1) & 1;
@@ -517,27 +546,30 @@ __global__ void __launch_bounds__(320) gemm_tc_persistent_kernel(const __grid_co
                 const uint32_t phase = (it / STAGES) & 1;
                 if (!mbar_wait(&full[s], phase)) { atomicExch(error_flag, 13); ok = false; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t a = smem_u32(smem + s * L::STAGE_BYTES);
+                const uint32_t a = smem_u32(smem + s * STAGE_BYTES);
                 const uint64_t adesc = umma_desc(a), bdesc = umma_desc(a + L::A_BYTES);
 #pragma unroll
-                for (int kk = 0; kk < TC_BK / 16; ++kk)
-                    umma_bf16(tmem_d, adesc + 2 * kk, bdesc + 2 * kk, idesc, (kb > kb0 || kk > 0) ? 1u : 0u);
-                umma_commit(&empty[s]);
+                for (int kk = 0; kk < TC_BK / 16; ++kk) {
+                    if (PAIR) umma_bf16_pair(tmem_d, adesc + 2 * kk, bdesc + 2 * kk, idesc, (kb > kb0 || kk > 0) ? 1u : 0u);
+                    else umma_bf16(tmem_d, adesc + 2 * kk, bdesc + 2 * kk, idesc, (kb > kb0 || kk > 0) ? 1u : 0u);
+                }
+                if (PAIR) umma_commit_pair(&empty[s]); else umma_commit(&empty[s]);
             }
-            umma_commit(&acc_full[buf]);
+            if (PAIR) umma_commit_pair(&acc_full[buf]); else umma_commit(&acc_full[buf]);
         }
     } else if (warp >= 2) {
         const int quarter = warp & 3;                                 // the 32 TMEM lanes this warp may read
         const int col_half = (warp - 2) >> 2;                         // two warps share a quarter: each takes half the columns
         constexpr int HALF_COLS = ((BN / 16 + 1) / 2) * 16;
         int local = 0;
+        int heads_chunk = 0;                                          // chunks this warp has staged (TcHeadsOut): picks the buffer
         bool ok = true;
-        TcWalk walk(sk, SK, tiles_n, tiles_t, nkb);
+        TcWalk walk(sk, SK, tiles_n, tiles_t, nkb, unit, units);
         for (int tile, kb0, kb1; walk.next(tile, kb0, kb1); ++local) {
             const bool is_tail = SK && kb0 > 0;    // the tile's last k-blocks: parked for the CTA that has its first ones
             const bool is_head = SK && kb1 < nkb;  // the tile's first k-blocks: the next CTA's parked piece is added
-            const int tile_row = tile_rows(tile, tiles_n, tiles_t);
-            const int n0 = tile_row * TC_BM, t0 = tile_tokens(tile, tiles_n, tiles_t) * BN;
+            const int n0 = tile_rows(tile, tiles_n, tiles_t) * ROWS + (int)rank * TC_BM, t0 = tile_tokens(tile, tiles_n, tiles_t) * BN;
+            const int tile_row = n0 / TC_BM;
             const int buf = local & 1;
             const uint32_t acc_phase = (local >> 1) & 1;
             if (scale.sumsq != nullptr) {
@@ -561,8 +593,111 @@ __global__ void __launch_bounds__(320) gemm_tc_persistent_kernel(const __grid_co
             }
             const int c_begin = col_half * HALF_COLS, c_end = col_half == 0 ? HALF_COLS : BN;
             const int n = n0 + quarter * 32 + lane;
+            float4 rope_c[2], rope_s[2];
+            int kv_slot[2];
+            // TcHeadsOut: the angles and the cache slot of the two tokens this lane finishes in a chunk come from global
+            // memory, an L2 round trip that nothing in the chunk could hide: they are asked for one chunk ahead
+            auto heads_fetch = [&](int c0) {
+#pragma unroll
+                for (int r = 0; r < 2; ++r) {
+                    const int t = t0 + c0 + r * 8 + quarter * 2 + (lane >> 4);
+                    const bool is_q = tile_row < heads.H;
+                    const bool there = t < T && c0 < c_end;
+                    if (there && rope != nullptr && tile_row < heads.H + heads.K) {
+                        rope_c[r] = __ldg(reinterpret_cast<const float4*>(rope + (size_t)t * TC_BM) + (lane & 15));
+                        rope_s[r] = __ldg(reinterpret_cast<const float4*>(rope + (size_t)t * TC_BM + 64) + (lane & 15));
+                    }
+                    kv_slot[r] = (there && !is_q) ? __ldg(heads.slot_mapping + t) : -1;
+                }
+            };
+            if (!SK && heads.q_out != nullptr) heads_fetch(c_begin);
             // what happens to 16 finished columns of this thread's row
             auto finish_chunk = [&](float* v, int c0) {
+                if (!SK && heads.q_out != nullptr) {
+                    // This tile is one head (128 rows) of sixteen tokens here.  The four warps that share this half of
+                    // the columns lay their values, rounded to bf16 as a stored row would be, token by token into a
+                    // staging buffer and meet at a barrier of their own (id 2 or 3; every one of them makes every
+                    // trip).  Then half a warp takes one token: a lane holds elements 4l..4l+3 and 64+4l..64+4l+3,
+                    // a rotation pair each, so the per-head RMS norm needs four shuffles and the rotation none, and the
+                    // head leaves as 128 contiguous bytes twice: to the query rows or into the paged cache, as the
+                    // kernel of few tokens does it (TcHeadsOut).  Two buffers in turn: a warp reaches the next
+                    // chunk's barrier only after it has read this chunk's buffer, so one barrier a chunk is enough.
+                    const int head = tile_row;
+                    const bool is_q = head < heads.H, is_k = !is_q && head < heads.H + heads.K;
+                    const float* hw = is_q ? heads.q_weight : (is_k ? heads.k_weight : nullptr);
+                    const bool rotate = (is_q || is_k) && rope != nullptr;
+                    bf16* stage = s_hx[col_half][heads_chunk & 1];
+                    ++heads_chunk;
+                    const int row = quarter * 32 + lane;
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) stage[j * TC_BM + row] = __float2bfloat16_rn(v[j]);
+                    asm volatile("bar.sync %0, 128;" ::"r"(2 + col_half) : "memory");
+                    const int hl = lane & 15;
+                    float4 w_lo = make_float4(1.0f, 1.0f, 1.0f, 1.0f), w_hi = w_lo;
+                    if (hw != nullptr) {
+                        w_lo = __ldg(reinterpret_cast<const float4*>(hw) + hl);
+                        w_hi = __ldg(reinterpret_cast<const float4*>(hw + 64) + hl);
+                    }
+#pragma unroll
+                    for (int r = 0; r < 2; ++r) {
+                        const int j = r * 8 + quarter * 2 + (lane >> 4);
+                        const int t = t0 + c0 + j;
+                        const uint2 raw_lo = *reinterpret_cast<const uint2*>(stage + j * TC_BM + 4 * hl);
+                        const uint2 raw_hi = *reinterpret_cast<const uint2*>(stage + j * TC_BM + 64 + 4 * hl);
+                        float a[4], b[4];
+                        {
+                            const float2 a0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw_lo.x));
+                            const float2 a1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw_lo.y));
+                            const float2 b0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw_hi.x));
+                            const float2 b1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw_hi.y));
+                            a[0] = a0.x; a[1] = a0.y; a[2] = a1.x; a[3] = a1.y;
+                            b[0] = b0.x; b[1] = b0.y; b[2] = b1.x; b[3] = b1.y;
+                        }
+                        if (hw != nullptr) {
+                            float ss = 0.0f;
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) ss += a[e] * a[e] + b[e] * b[e];
+                            ss = group_sum(ss, 16);
+                            const float rstd = 1.0f / sqrtf(ss / (float)TC_BM + heads.eps);
+                            const float wl[4] = {w_lo.x, w_lo.y, w_lo.z, w_lo.w}, wh[4] = {w_hi.x, w_hi.y, w_hi.z, w_hi.w};
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) { a[e] = a[e] * rstd * wl[e]; b[e] = b[e] * rstd * wh[e]; }
+                        }
+                        if (t >= T) continue;
+                        if (rotate) {
+                            const float4 c4 = rope_c[r], s4 = rope_s[r];
+                            const float cs[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const float x = a[e], y = b[e];
+                                a[e] = x * cs[e] - y * sn[e];
+                                b[e] = y * cs[e] + x * sn[e];
+                            }
+                        }
+                        bf16* dst = nullptr;
+                        if (is_q) {
+                            dst = heads.q_out + ((size_t)t * heads.H + head) * TC_BM;
+                        } else {
+                            const int slot = kv_slot[r];
+                            if (slot >= 0) {
+                                const int kh = is_k ? head - heads.H : head - heads.H - heads.K;
+                                dst = (is_k ? heads.k_cache : heads.v_cache) +
+                                      (((size_t)(slot / heads.page_size) * heads.K + kh) * heads.page_size + (size_t)(slot % heads.page_size)) * TC_BM;
+                            }
+                        }
+                        if (dst != nullptr) {
+                            uint2 out_lo, out_hi;
+                            *reinterpret_cast<__nv_bfloat162*>(&out_lo.x) = __floats2bfloat162_rn(a[0], a[1]);
+                            *reinterpret_cast<__nv_bfloat162*>(&out_lo.y) = __floats2bfloat162_rn(a[2], a[3]);
+                            *reinterpret_cast<__nv_bfloat162*>(&out_hi.x) = __floats2bfloat162_rn(b[0], b[1]);
+                            *reinterpret_cast<__nv_bfloat162*>(&out_hi.y) = __floats2bfloat162_rn(b[2], b[3]);
+                            *reinterpret_cast<uint2*>(dst + 4 * hl) = out_lo;
+                            *reinterpret_cast<uint2*>(dst + 64 + 4 * hl) = out_hi;
+                        }
+                    }
+                    heads_fetch(c0 + 16);
+                    return;
+                }
                 if (scale.sumsq != nullptr) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j) v[j] *= s_pscale[buf][c0 + j];
@@ -631,6 +766,13 @@ __global__ void __launch_bounds__(320) gemm_tc_persistent_kernel(const __grid_co
                 // a warp whose wait gave up keeps walking the tiles (the barrier above counts on it) but touches nothing
                 if (ok && !mbar_wait(&acc_full[buf], acc_phase)) { if (lane == 0) atomicExch(error_flag, 14); ok = false; }
                 ok = __all_sync(0xffffffffu, ok);
+                if (!SK && heads.q_out != nullptr) {
+                    // the four warps of this half meet at barriers inside the chunks: they go on together or not at all
+                    uint32_t all_ok;
+                    asm volatile("{ .reg .pred p, q; setp.ne.u32 p, %1, 0; bar.red.and.pred q, %2, 128, p; selp.u32 %0, 1, 0, q; }"
+                                 : "=r"(all_ok) : "r"((uint32_t)ok), "r"(2 + col_half) : "memory");
+                    ok = all_ok != 0;
+                }
                 if (!ok) continue;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
@@ -649,7 +791,8 @@ __global__ void __launch_bounds__(320) gemm_tc_persistent_kernel(const __grid_co
             if (is_tail) __threadfence();
             __syncwarp();
             if (lane == 0) {
-                mbar_arrive(&acc_empty[buf]);
+                if (PAIR && rank != 0) mbar_arrive_cluster(cluster_addr(smem_u32(&acc_empty[buf]), 0));
+                else mbar_arrive(&acc_empty[buf]);
                 if (is_tail) asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(parked_flag), "r"(1) : "memory");
                 if (is_head) asm volatile("st.relaxed.gpu.global.s32 [%0], %1;" ::"l"(parked_flag), "r"(0) : "memory");   // for the next launch
             }
@@ -657,9 +800,11 @@ __global__ void __launch_bounds__(320) gemm_tc_persistent_kernel(const __grid_co
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    if (PAIR) cluster_sync_all();              // neither CTA leaves while the other's MMAs read its memory or arrive on its barriers
     if (warp == 0) {
         __syncwarp();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+        if (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+        else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     }
 }
 
@@ -692,7 +837,8 @@ MB_API int mb_gemm_tc_tiles(int T, int N, int bn) { return ((N + TC_BM - 1) / TC
 
 template <int BN, int STAGES, bool SK>
 static int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int mode, int T, int N, int K, int ctas,
-                             int* error_flag, const TcNormOut& norm, const TcRowScale& scale, TcStreamK sk, cudaStream_t s) {
+                             int* error_flag, const TcNormOut& norm, const TcRowScale& scale, TcStreamK sk, cudaStream_t s,
+                             const TcHeadsOut& heads = TcHeadsOut{}, const float* rope = nullptr) {
     constexpr int smem = STAGES * TcSmem<BN>::STAGE_BYTES + 1024 + 256;
     static_assert(smem <= 227 * 1024, "the ring does not fit shared memory");
     static bool configured = false;
@@ -711,11 +857,12 @@ static int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, void*
         grid = groups * tiles_t;
     }
     return launch_kernel(gemm_tc_persistent_kernel<BN, STAGES, SK>, dim3(grid), dim3(320), smem, s, 0, mw, mx, out, mode, T, N, K,
-                         error_flag, norm, scale, sk);
+                         error_flag, norm, scale, sk, heads, rope);
 }
 
 static int persistent_dispatch(const void* x, const void* w, void* out, int mode, int T, int N, int K, int bn, int ctas,
-                               int* error_flag, const TcNormOut& norm, const TcRowScale& scale, const TcStreamK& sk, cudaStream_t s) {
+                               int* error_flag, const TcNormOut& norm, const TcRowScale& scale, const TcStreamK& sk, cudaStream_t s,
+                               const TcHeadsOut& heads = TcHeadsOut{}, const float* rope = nullptr) {
     if (T <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15) || ctas <= 0) return MB_ERR_BAD_SIZE;
     if (mode < 0 || mode > 3 || (mode == 3 && N % 32 != 0)) return MB_ERR_BAD_DTYPE;
@@ -735,15 +882,15 @@ static int persistent_dispatch(const void* x, const void* w, void* out, int mode
         }
     }
     switch (bn) {
-        case 128: return launch_persistent<128, 6, false>(mw, mx, out, mode, T, N, K, ctas, error_flag, norm, scale, sk, s);
-        case 144: return launch_persistent<144, 6, false>(mw, mx, out, mode, T, N, K, ctas, error_flag, norm, scale, sk, s);
-        case 160: return launch_persistent<160, 5, false>(mw, mx, out, mode, T, N, K, ctas, error_flag, norm, scale, sk, s);
-        case 176: return launch_persistent<176, 5, false>(mw, mx, out, mode, T, N, K, ctas, error_flag, norm, scale, sk, s);
-        case 192: return launch_persistent<192, 5, false>(mw, mx, out, mode, T, N, K, ctas, error_flag, norm, scale, sk, s);
-        case 208: return launch_persistent<208, 4, false>(mw, mx, out, mode, T, N, K, ctas, error_flag, norm, scale, sk, s);
-        case 224: return launch_persistent<224, 4, false>(mw, mx, out, mode, T, N, K, ctas, error_flag, norm, scale, sk, s);
-        case 240: return launch_persistent<240, 4, false>(mw, mx, out, mode, T, N, K, ctas, error_flag, norm, scale, sk, s);
-        case 256: return launch_persistent<256, 4, false>(mw, mx, out, mode, T, N, K, ctas, error_flag, norm, scale, sk, s);
+        case 128: return launch_persistent<128, 6, false>(mw, mx, out, mode, T, N, K, ctas, error_flag, norm, scale, sk, s, heads, rope);
+        case 144: return launch_persistent<144, 6, false>(mw, mx, out, mode, T, N, K, ctas, error_flag, norm, scale, sk, s, heads, rope);
+        case 160: return launch_persistent<160, 5, false>(mw, mx, out, mode, T, N, K, ctas, error_flag, norm, scale, sk, s, heads, rope);
+        case 176: return launch_persistent<176, 5, false>(mw, mx, out, mode, T, N, K, ctas, error_flag, norm, scale, sk, s, heads, rope);
+        case 192: return launch_persistent<192, 5, false>(mw, mx, out, mode, T, N, K, ctas, error_flag, norm, scale, sk, s, heads, rope);
+        case 208: return launch_persistent<208, 4, false>(mw, mx, out, mode, T, N, K, ctas, error_flag, norm, scale, sk, s, heads, rope);
+        case 224: return launch_persistent<224, 4, false>(mw, mx, out, mode, T, N, K, ctas, error_flag, norm, scale, sk, s, heads, rope);
+        case 240: return launch_persistent<240, 4, false>(mw, mx, out, mode, T, N, K, ctas, error_flag, norm, scale, sk, s, heads, rope);
+        case 256: return launch_persistent<256, 4, false>(mw, mx, out, mode, T, N, K, ctas, error_flag, norm, scale, sk, s, heads, rope);
         default: return MB_ERR_BAD_SIZE;
     }
 }
@@ -791,6 +938,18 @@ MB_API int mb_gemm_tc_persistent_coupled(const void* x, const void* w, void* out
     TcNormOut norm{norm_weight, (bf16*)scaled_out, sumsq_out, norm_unit_offset};
     TcRowScale scale{scale_sumsq, scale_slots, scale_dim, scale_eps};
     return persistent_dispatch(x, w, out, mode, T, N, K, bn, ctas, error_flag, norm, scale, TcStreamK{}, s);
+}
+
+// The q|k|v product of many tokens with heads of 128 elements, each head finished in the persistent kernel's epilogue
+// (see TcHeadsOut; mb_gemm_tc_heads is the same for at most 16 tokens).  rope: [T][128] float32, cos of the 64 angles
+// then sin (mb_rope_table), or null for no rotation.
+MB_API int mb_gemm_tc_persistent_heads(const void* x, const void* w, int T, int N, int K, int bn, int ctas, void* q_out, void* k_cache,
+                                       void* v_cache, const float* q_weight, const float* k_weight, float eps, const float* rope,
+                                       const int* slot_mapping, int H, int KV, int page_size, int* error_flag, cudaStream_t s) {
+    if (q_out == nullptr || H <= 0 || KV < 0 || (N != H * TC_BM && N != (H + 2 * KV) * TC_BM)) return MB_ERR_BAD_SIZE;
+    if (N != H * TC_BM && (k_cache == nullptr || v_cache == nullptr || slot_mapping == nullptr || page_size <= 0)) return MB_ERR_BAD_SIZE;
+    TcHeadsOut heads{(bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, q_weight, k_weight, nullptr, nullptr, slot_mapping, eps, H, KV, page_size};
+    return persistent_dispatch(x, w, q_out, TC_OUT_BF16, T, N, K, bn, ctas, error_flag, TcNormOut{}, TcRowScale{}, TcStreamK{}, s, heads, rope);
 }
 
 // x [T, K] bf16, w [N, K] bf16, out [T, N]: bf16 (mode 0), float32 (1), float32 += (2).  K must be a multiple

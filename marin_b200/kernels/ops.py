@@ -450,23 +450,59 @@ fuse_heads = True
 FUSED_HEADS_MAX_TOKENS = 16
 
 
+#: the same for many tokens, in the persistent kernel's epilogue (tile by tile, no stream-K)
+fuse_heads_many_tokens = True
+
+
+def rope_table(ctx, positions, inv_freq) -> torch.Tensor:
+    """cos and sin of ``positions * inv_freq`` for every token of the step, float32 ``[T, 2 * len(inv_freq)]`` (cos
+    first), made once per step and position encoding and kept in ``ctx.extras``."""
+    key = ("rope_table", inv_freq.data_ptr())
+    table = ctx.extras.get(key)
+    if table is None:
+        T, half = positions.shape[0], inv_freq.shape[0]
+        table = ctx.workspace.get(f"rope_table_{len(ctx.extras)}", (T, 2 * half), torch.float32)
+        _cost(_size(table), 2.0 * T * half)
+        _check(_lib("mb_elementwise").mb_rope_table(_ptr(positions), _ptr(inv_freq), _c_int(half), _ptr(table), _c_int(T), _stream()),
+               "rope_table")
+        ctx.extras[key] = table
+    return table
+
+
 def gemm_qkv_heads(x, w: torch.Tensor, q_out: torch.Tensor, q_weight, k_weight, eps: float, positions, inv_freq, rotary_dim: int,
-                   interleaved: bool, slot_mapping, k_cache, v_cache, H: int, K: int, d: int, write_kv: bool = True) -> bool:
-    """The product ``x w^T`` of a few tokens with ``w`` = query, key and value rows (or query rows only), each head
-    normed, rotated and stored by the product's own epilogue: queries to ``q_out``, keys and values into the paged
-    caches at ``slot_mapping``.  Returns False, having done nothing, where this does not apply (many tokens, heads
-    that are not 128 wide, a partial or interleaved rotation, float32): the caller then runs ``gemm`` and
-    ``qk_norm_rope_write``."""
+                   interleaved: bool, slot_mapping, k_cache, v_cache, H: int, K: int, d: int, write_kv: bool = True, ctx=None) -> bool:
+    """The product ``x w^T`` with ``w`` = query, key and value rows (or query rows only), each head normed, rotated
+    and stored by the product's own epilogue: queries to ``q_out``, keys and values into the paged caches at
+    ``slot_mapping``.  Two kernels do it: the one for up to sixteen tokens computes the angles itself; the persistent
+    one for many tokens reads them from the step's table (``rope_table``, which needs ``ctx``).  Returns False,
+    having done nothing, where neither applies (heads that are not 128 wide, a partial or interleaved rotation,
+    float32, a token count between the two): the caller then runs ``gemm`` and ``qk_norm_rope_write``."""
     scaled = x if isinstance(x, NormedRows) else None
     rows = scaled.rows if scaled is not None else x
     T, Kdim = rows.shape
     N = w.shape[0]
     heads_total = H + 2 * K if write_kv else H
     if not (fuse_heads and use_tensor_cores and rows.is_cuda and rows.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
-            and q_out.dtype == torch.bfloat16 and d == 128 and 0 < T <= FUSED_HEADS_MAX_TOKENS and N == heads_total * d
+            and q_out.dtype == torch.bfloat16 and d == 128 and T > 0 and N == heads_total * d
             and Kdim % 8 == 0 and not interleaved and (inv_freq is None or rotary_dim == d)
             and rows.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and (not write_kv or k_cache.dtype == torch.bfloat16)):
         return False
+    page_size = k_cache.shape[2] if write_kv else 0
+    if T > FUSED_HEADS_MAX_TOKENS:
+        if not (fuse_heads_many_tokens and scaled is None and T > 128 and -(-N // 128) * -(-T // 128) >= SM_COUNT // 2
+                and (inv_freq is None or ctx is not None)):
+            return False
+        _need_cuda(rows, w, q_out)
+        assert tuple(q_out.shape) == (T, H * d) and w.shape[1] == Kdim
+        table = rope_table(ctx, positions, inv_freq) if inv_freq is not None else None
+        _cost(_size(w) + _size(rows) + T * N * 2 + (_size(table) if table is not None else 0), 2.0 * T * N * Kdim)
+        s = _scratch_for(rows.device)
+        _check(_lib("mb_gemm_tc").mb_gemm_tc_persistent_heads(
+            _ptr(rows), _ptr(w), _c_int(T), _c_int(N), _c_int(Kdim), _c_int(persistent_plan(T, N)), _c_int(SM_COUNT), _ptr(q_out),
+            _ptr(k_cache) if write_kv else None, _ptr(v_cache) if write_kv else None, _ptr(q_weight), _ptr(k_weight), _c_float(eps),
+            _ptr(table), _ptr(slot_mapping) if write_kv else None, _c_int(H), _c_int(K), _c_int(page_size), _ptr(s.error), _stream()),
+            "gemm (persistent) with heads finished in the epilogue")
+        return True
     bn, splits = gemm_plan(T, N, Kdim)
     if bn != 16 or splits < 2:
         return False
@@ -474,7 +510,6 @@ def gemm_qkv_heads(x, w: torch.Tensor, q_out: torch.Tensor, q_weight, k_weight, 
     assert tuple(q_out.shape) == (T, H * d) and w.shape[1] == Kdim
     _cost(_size(w) + _size(rows) + T * N * 2, 2.0 * T * N * Kdim)
     s = _scratch_for(rows.device)
-    page_size = k_cache.shape[2] if write_kv else 0
     _check(_lib("mb_gemm_tc").mb_gemm_tc_heads(
         _ptr(rows), _ptr(w), _c_int(T), _c_int(N), _c_int(Kdim), _c_int(splits), _ptr(q_out),
         _ptr(k_cache) if write_kv else None, _ptr(v_cache) if write_kv else None, _ptr(q_weight), _ptr(k_weight), _c_float(eps),

@@ -169,7 +169,7 @@ class GQAttention(Mixer):
         ops.stage_name = "q|k|v, heads"
         if not ops.gemm_qkv_heads(x, w, q, self.q_weight, self.k_weight, self.norm_eps, ctx.positions, pos.inv_freq,
                                   pos.rotary_dim, pos.interleaved, cache.slot_mapping, cache.k, cache.v, self.heads,
-                                  self.kv_heads, self.head_dim, writes):
+                                  self.kv_heads, self.head_dim, writes, ctx):
             qkv = ws.get("qkv", (T, w.shape[0]), x.dtype)
             ops.gemm(x, w, qkv)
             ops.qk_norm_rope_write(
