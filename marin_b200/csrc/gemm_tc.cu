@@ -421,18 +421,17 @@ struct TcStreamK {
 struct TcWalk {
     int nkb, limit, step, at, token_tile, tiles_t;
     bool streamk;
-    // `unit` of `units` walkers: a CTA of the grid, or a pair of CTAs
-    __device__ TcWalk(const TcStreamK& sk, bool streamk_, int tiles_n, int tiles_t_, int nkb_, int unit, int units) : nkb(nkb_), tiles_t(tiles_t_), streamk(streamk_) {
+    __device__ TcWalk(const TcStreamK& sk, bool streamk_, int tiles_n, int tiles_t_, int nkb_) : nkb(nkb_), tiles_t(tiles_t_), streamk(streamk_) {
         if (streamk) {
-            const int group = unit / tiles_t_;
-            token_tile = unit - group * tiles_t_;
+            const int group = blockIdx.x / tiles_t_;
+            token_tile = blockIdx.x - group * tiles_t_;
             const long long total = (long long)tiles_n * nkb_;
             const long long from = (long long)group * sk.units_per_group, to = from + sk.units_per_group;
             at = (int)(from < total ? from : total);
             limit = (int)(to < total ? to : total);
             step = 0;
         } else {
-            at = unit; limit = tiles_n * tiles_t_; step = units; token_tile = 0;
+            at = blockIdx.x; limit = tiles_n * tiles_t_; step = gridDim.x; token_tile = 0;
         }
     }
     // the next piece: k-blocks [kb0, kb1) of `tile` (numbered with the token tiles fastest)
@@ -448,11 +447,24 @@ struct TcWalk {
     }
 };
 
-// PAIR: two CTAs (a cluster of two, on the two SMs of a TPC) share a tile of 256 weight rows x BN tokens.  Each loads
-// its own 128 weight rows and half of the tokens; one thread of the even CTA issues MMAs of 256 rows
-// (tcgen05 cta_group::2) that read both CTAs' shared memory and fill both CTAs' tensor memory, so each SM moves
-// two thirds of the shared-memory bytes per flop of the single-CTA form; each CTA drains its own 128 rows.
-template <int BN, int STAGES, bool SK, bool PAIR = false>
+#ifdef TC_PROBE
+// Where the roles of the persistent kernel spend their time (a build for measuring only, -DTC_PROBE): per CTA, clock
+// ticks of [0] the producer waiting for a free stage, [1] the producer issuing, [2] the MMA thread waiting for a full
+// stage, [3] the MMA thread waiting for a free accumulator, [4] the MMA thread in all.
+__device__ long long tc_probe[148 * 8];
+MB_API int mb_gemm_tc_probe_read(long long* host) { return (int)cudaMemcpyFromSymbol(host, tc_probe, sizeof(tc_probe)); }
+#define PROBE_DECL(name) long long name = 0
+#define PROBE_T() clock64()
+#define PROBE_ADD(name, since) name += clock64() - (since)
+#define PROBE_OUT(slot, name) if (blockIdx.x < 148) tc_probe[blockIdx.x * 8 + (slot)] = name
+#else
+#define PROBE_DECL(name)
+#define PROBE_T() 0
+#define PROBE_ADD(name, since) (void)(since)
+#define PROBE_OUT(slot, name)
+#endif
+
+template <int BN, int STAGES, bool SK>
 __global__ void __launch_bounds__(320) gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                  const __grid_constant__ CUtensorMap map_x,
                                                                  void* __restrict__ out, int mode, int T, int N, int K,
@@ -464,43 +476,30 @@ __global__ void __launch_bounds__(320) gemm_tc_persistent_kernel(const __grid_co
     // heads finished in the epilogue: per half of the columns (its four warps), two staging buffers of sixteen tokens
     __shared__ __align__(16) bf16 s_hx[2][2][16 * TC_BM];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    static_assert(!(PAIR && SK), "pairs walk whole tiles");
     using L = TcSmem<BN>;
-    constexpr int BNL = PAIR ? BN / 2 : BN;                          // tokens this CTA loads of a tile
-    constexpr int STAGE_BYTES = L::A_BYTES + BNL * TC_BK * 2;
-    constexpr int ROWS = PAIR ? 2 * TC_BM : TC_BM;                   // weight rows of a tile
-    uint64_t* full = (uint64_t*)(smem + STAGES * STAGE_BYTES);
+    uint64_t* full = (uint64_t*)(smem + STAGES * L::STAGE_BYTES);
     uint64_t* empty = full + STAGES;
     uint64_t* acc_full = empty + STAGES;       // [2]
     uint64_t* acc_empty = acc_full + 2;        // [2]
     uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t rank = PAIR ? cluster_ctarank() : 0u;             // 0: the CTA whose barriers count and whose thread issues
-    const int unit = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x, units = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
-    const int tiles_n = (N + ROWS - 1) / ROWS, tiles_t = (T + BN - 1) / BN;
+    const int tiles_n = (N + TC_BM - 1) / TC_BM, tiles_t = (T + BN - 1) / BN;
     const int nkb = (K + TC_BK - 1) / TC_BK;
     constexpr uint32_t TMEM_COLS = 2 * BN <= 32 ? 32 : 2 * BN <= 64 ? 64 : 2 * BN <= 128 ? 128 : 2 * BN <= 256 ? 256 : 512;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-        // the accumulators are given back by the eight epilogue warps of every CTA that holds a part of them
-        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], PAIR ? 16 : 8); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 8); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
         __syncwarp();
-        if (PAIR) {          // a warp of each CTA of the pair asks; each CTA finds the address in its own slot
-            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
-            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-        } else {
-            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
-            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-        }
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (PAIR) cluster_sync_all();              // the other CTA's barriers are there before anything arrives on them
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
     PDL_ENTER_EARLY();
@@ -508,55 +507,58 @@ __global__ void __launch_bounds__(320) gemm_tc_persistent_kernel(const __grid_co
     if (warp == 0 && lane == 0) {
         int it = 0;                                                   // k-blocks issued so far, over all tiles
         bool ok = true;
-        TcWalk walk(sk, SK, tiles_n, tiles_t, nkb, unit, units);
+        PROBE_DECL(p_wait); PROBE_DECL(p_issue);
+        TcWalk walk(sk, SK, tiles_n, tiles_t, nkb);
         for (int tile, kb0, kb1; ok && walk.next(tile, kb0, kb1);) {
-            const int n0 = tile_rows(tile, tiles_n, tiles_t) * ROWS + (int)rank * TC_BM;
-            const int t0 = tile_tokens(tile, tiles_n, tiles_t) * BN + (int)rank * BNL;
+            const int n0 = tile_rows(tile, tiles_n, tiles_t) * TC_BM, t0 = tile_tokens(tile, tiles_n, tiles_t) * BN;
             for (int kb = kb0; kb < kb1; ++kb, ++it) {
                 const int s = it % STAGES;
                 const uint32_t phase = (it / STAGES) & 1;
+                const long long pt0 = PROBE_T();
                 if (!mbar_wait(&empty[s], phase ^ 1)) { atomicExch(error_flag, 11); ok = false; break; }
-                uint8_t* a = smem + s * STAGE_BYTES;
-                if (PAIR) {
-                    // both CTAs' bytes are counted on the even CTA's barrier, which its MMA thread waits on
-                    if (rank == 0) mbar_expect_tx(&full[s], 2 * STAGE_BYTES);
-                    const uint32_t bar = cluster_addr(smem_u32(&full[s]), 0);
-                    tma_load_2d_pair(a, &map_w, kb * TC_BK, n0, bar);
-                    tma_load_2d_pair(a + L::A_BYTES, &map_x, kb * TC_BK, t0, bar);
-                } else {
-                    mbar_expect_tx(&full[s], STAGE_BYTES);
-                    tma_load_2d(a, &map_w, kb * TC_BK, n0, &full[s]);
-                    tma_load_2d(a + L::A_BYTES, &map_x, kb * TC_BK, t0, &full[s]);
-                }
+                PROBE_ADD(p_wait, pt0);
+                const long long pt1 = PROBE_T();
+                mbar_expect_tx(&full[s], L::STAGE_BYTES);
+                uint8_t* a = smem + s * L::STAGE_BYTES;
+                tma_load_2d(a, &map_w, kb * TC_BK, n0, &full[s]);
+                tma_load_2d(a + L::A_BYTES, &map_x, kb * TC_BK, t0, &full[s]);
+                PROBE_ADD(p_issue, pt1);
             }
         }
-    } else if (warp == 1 && lane == 0 && rank == 0) {
-        constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);
+        PROBE_OUT(0, p_wait); PROBE_OUT(1, p_issue);
+    } else if (warp == 1 && lane == 0) {
+        constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
         int it = 0, local = 0;
         bool ok = true;
-        TcWalk walk(sk, SK, tiles_n, tiles_t, nkb, unit, units);
+        PROBE_DECL(m_full); PROBE_DECL(m_acc); PROBE_DECL(m_all);
+        const long long mt_start = PROBE_T();
+        TcWalk walk(sk, SK, tiles_n, tiles_t, nkb);
         for (int tile, kb0, kb1; ok && walk.next(tile, kb0, kb1); ++local) {
             const int buf = local & 1;
             const uint32_t acc_phase = (local >> 1) & 1;
+            const long long mt0 = PROBE_T();
             if (!mbar_wait(&acc_empty[buf], acc_phase ^ 1)) { atomicExch(error_flag, 12); ok = false; break; }
+            PROBE_ADD(m_acc, mt0);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
             for (int kb = kb0; kb < kb1; ++kb, ++it) {
                 const int s = it % STAGES;
                 const uint32_t phase = (it / STAGES) & 1;
+                const long long mt1 = PROBE_T();
                 if (!mbar_wait(&full[s], phase)) { atomicExch(error_flag, 13); ok = false; break; }
+                PROBE_ADD(m_full, mt1);
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t a = smem_u32(smem + s * STAGE_BYTES);
+                const uint32_t a = smem_u32(smem + s * L::STAGE_BYTES);
                 const uint64_t adesc = umma_desc(a), bdesc = umma_desc(a + L::A_BYTES);
 #pragma unroll
-                for (int kk = 0; kk < TC_BK / 16; ++kk) {
-                    if (PAIR) umma_bf16_pair(tmem_d, adesc + 2 * kk, bdesc + 2 * kk, idesc, (kb > kb0 || kk > 0) ? 1u : 0u);
-                    else umma_bf16(tmem_d, adesc + 2 * kk, bdesc + 2 * kk, idesc, (kb > kb0 || kk > 0) ? 1u : 0u);
-                }
-                if (PAIR) umma_commit_pair(&empty[s]); else umma_commit(&empty[s]);
+                for (int kk = 0; kk < TC_BK / 16; ++kk)
+                    umma_bf16(tmem_d, adesc + 2 * kk, bdesc + 2 * kk, idesc, (kb > kb0 || kk > 0) ? 1u : 0u);
+                umma_commit(&empty[s]);
             }
-            if (PAIR) umma_commit_pair(&acc_full[buf]); else umma_commit(&acc_full[buf]);
+            umma_commit(&acc_full[buf]);
         }
+        PROBE_ADD(m_all, mt_start);
+        PROBE_OUT(2, m_full); PROBE_OUT(3, m_acc); PROBE_OUT(4, m_all);
     } else if (warp >= 2) {
         const int quarter = warp & 3;                                 // the 32 TMEM lanes this warp may read
         const int col_half = (warp - 2) >> 2;                         // two warps share a quarter: each takes half the columns
@@ -564,12 +566,12 @@ __global__ void __launch_bounds__(320) gemm_tc_persistent_kernel(const __grid_co
         int local = 0;
         int heads_chunk = 0;                                          // chunks this warp has staged (TcHeadsOut): picks the buffer
         bool ok = true;
-        TcWalk walk(sk, SK, tiles_n, tiles_t, nkb, unit, units);
+        TcWalk walk(sk, SK, tiles_n, tiles_t, nkb);
         for (int tile, kb0, kb1; walk.next(tile, kb0, kb1); ++local) {
             const bool is_tail = SK && kb0 > 0;    // the tile's last k-blocks: parked for the CTA that has its first ones
             const bool is_head = SK && kb1 < nkb;  // the tile's first k-blocks: the next CTA's parked piece is added
-            const int n0 = tile_rows(tile, tiles_n, tiles_t) * ROWS + (int)rank * TC_BM, t0 = tile_tokens(tile, tiles_n, tiles_t) * BN;
-            const int tile_row = n0 / TC_BM;
+            const int tile_row = tile_rows(tile, tiles_n, tiles_t);
+            const int n0 = tile_row * TC_BM, t0 = tile_tokens(tile, tiles_n, tiles_t) * BN;
             const int buf = local & 1;
             const uint32_t acc_phase = (local >> 1) & 1;
             if (scale.sumsq != nullptr) {
@@ -791,8 +793,7 @@ __global__ void __launch_bounds__(320) gemm_tc_persistent_kernel(const __grid_co
             if (is_tail) __threadfence();
             __syncwarp();
             if (lane == 0) {
-                if (PAIR && rank != 0) mbar_arrive_cluster(cluster_addr(smem_u32(&acc_empty[buf]), 0));
-                else mbar_arrive(&acc_empty[buf]);
+                mbar_arrive(&acc_empty[buf]);
                 if (is_tail) asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(parked_flag), "r"(1) : "memory");
                 if (is_head) asm volatile("st.relaxed.gpu.global.s32 [%0], %1;" ::"l"(parked_flag), "r"(0) : "memory");   // for the next launch
             }
@@ -800,11 +801,9 @@ __global__ void __launch_bounds__(320) gemm_tc_persistent_kernel(const __grid_co
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (PAIR) cluster_sync_all();              // neither CTA leaves while the other's MMAs read its memory or arrive on its barriers
     if (warp == 0) {
         __syncwarp();
-        if (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
-        else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     }
 }
 
