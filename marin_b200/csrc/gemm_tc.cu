@@ -23,6 +23,89 @@
 #include "tc_epilogue.cuh"
 #include "launch.cuh"
 
+// The cluster's reduction of a split-K tile, four weight rows of one token per thread (N a multiple of 4): every peer's
+// slice of the partial tile comes through distributed shared memory in 16-byte loads, all of a thread's loads (up to
+// U items x S slices) asked for before any is used; the slices are added in slice order, whatever S or the batch
+// is, so the sums are the same bits as row by row.  Then what follows the product: "+=" into the residual stream with
+// the norm's side outputs, the per-token factor of a norm ahead, or the plain store.
+template <int S, int U>
+__device__ __forceinline__ void cluster_reduce_rows4(uint32_t red_addr, void* out, int mode, int T, int N, int n0, int t0, int t_count,
+                                                     const TcNormOut& norm, const TcRowScale& scale, const float* s_scale) {
+    constexpr int rows_per = TC_BM / S, per_token = rows_per / 4;
+    constexpr int group = rows_per < 32 ? rows_per : 32;              // rows whose squares are added into one slot
+    constexpr int slots_per_tile = S < 4 ? 4 : S;
+    const int row_first = blockIdx.z * rows_per;
+    const int total = t_count * per_token;
+    const bool acc_mode = mode == TC_OUT_F32_ACC;
+    for (int base = 0; base < total; base += 128 * U) {               // every thread makes every trip (shuffles below)
+        float4 old[U], gain[U], pv[U][S];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int idx = base + u * 128 + threadIdx.x;
+            const int tt = idx / per_token, row = row_first + 4 * (idx % per_token);
+            const bool valid = idx < total && n0 + row < N;
+            old[u] = (acc_mode && valid) ? *reinterpret_cast<const float4*>((const float*)out + (size_t)(t0 + tt) * N + n0 + row) : make_float4(0.f, 0.f, 0.f, 0.f);
+            gain[u] = (norm.weight != nullptr && valid) ? *reinterpret_cast<const float4*>(norm.weight + n0 + row) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int z = 0; z < S; ++z) {
+                pv[u][z] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (idx < total) {
+                    uint32_t remote;
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(red_addr + (uint32_t)(tt * TC_BM + row) * 4u), "r"(z));
+                    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                                 : "=f"(pv[u][z].x), "=f"(pv[u][z].y), "=f"(pv[u][z].z), "=f"(pv[u][z].w) : "r"(remote) : "memory");
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (base + u * 128 >= total) break;                       // the same for every thread
+            const int idx = base + u * 128 + threadIdx.x;
+            const bool active = idx < total;
+            const int tt = idx / per_token, in_slice = 4 * (idx % per_token), row = row_first + in_slice;
+            float sum[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int z = 0; z < S; ++z) { sum[0] += pv[u][z].x; sum[1] += pv[u][z].y; sum[2] += pv[u][z].z; sum[3] += pv[u][z].w; }
+            if (scale.sumsq != nullptr && active) {
+                const float f = s_scale[tt];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) sum[e] *= f;
+            }
+            const bool valid = active && n0 + row < N;
+            const size_t at = (size_t)(t0 + tt) * N + n0 + row;
+            float nv[4] = {0.f, 0.f, 0.f, 0.f};
+            if (valid) {
+                if (acc_mode) {
+                    nv[0] = old[u].x + sum[0]; nv[1] = old[u].y + sum[1]; nv[2] = old[u].z + sum[2]; nv[3] = old[u].w + sum[3];
+                    *reinterpret_cast<float4*>((float*)out + at) = make_float4(nv[0], nv[1], nv[2], nv[3]);
+                    if (norm.weight != nullptr) {
+                        const float o1 = norm.unit_offset ? 1.0f : 0.0f;
+                        uint2 packed;
+                        *reinterpret_cast<__nv_bfloat162*>(&packed.x) = __floats2bfloat162_rn(nv[0] * (gain[u].x + o1), nv[1] * (gain[u].y + o1));
+                        *reinterpret_cast<__nv_bfloat162*>(&packed.y) = __floats2bfloat162_rn(nv[2] * (gain[u].z + o1), nv[3] * (gain[u].w + o1));
+                        *reinterpret_cast<uint2*>(norm.scaled + at) = packed;
+                    }
+                } else if (mode == TC_OUT_BF16) {
+                    uint2 packed;
+                    *reinterpret_cast<__nv_bfloat162*>(&packed.x) = __floats2bfloat162_rn(sum[0], sum[1]);
+                    *reinterpret_cast<__nv_bfloat162*>(&packed.y) = __floats2bfloat162_rn(sum[2], sum[3]);
+                    *reinterpret_cast<uint2*>((bf16*)out + at) = packed;
+                } else {
+                    *reinterpret_cast<float4*>((float*)out + at) = make_float4(sum[0], sum[1], sum[2], sum[3]);
+                }
+            }
+            if (norm.weight != nullptr) {
+                // the squares of a group of rows: this thread's four, then the group's threads in a fixed tree
+                const float sq = group_sum(((nv[0] * nv[0] + nv[1] * nv[1]) + nv[2] * nv[2]) + nv[3] * nv[3], group / 4);
+                if (active && in_slice % group == 0) {
+                    const int slot = blockIdx.x * slots_per_tile + blockIdx.z * (slots_per_tile / S) + in_slice / group;
+                    norm.sumsq[(size_t)slot * T + t0 + tt] = sq;
+                }
+            }
+        }
+    }
+}
+
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,
                                                       const __grid_constant__ CUtensorMap map_x, void* __restrict__ out,
@@ -234,6 +317,15 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
                 }
                 __syncthreads();                                      // s_part and s_head are used again
             }
+            asm volatile("barrier.cluster.arrive.relaxed.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+        } else if (N % 4 == 0) {
+            asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+            const uint32_t red_addr = smem_u32(red);
+            // items of a thread in flight at a time: all of them where the registers allow
+            constexpr int U8 = BN >= 32 ? 2 : 1, U4 = BN >= 64 ? 4 : (BN >= 32 ? 2 : 1), U2 = BN >= 32 ? 4 : (BN >= 16 ? 2 : 1);
+            if (splits == 8) cluster_reduce_rows4<8, U8>(red_addr, out, mode, T, N, n0, t0, t_count, norm, scale, s_scale);
+            else if (splits == 4) cluster_reduce_rows4<4, U4>(red_addr, out, mode, T, N, n0, t0, t_count, norm, scale, s_scale);
+            else cluster_reduce_rows4<2, U2>(red_addr, out, mode, T, N, n0, t0, t_count, norm, scale, s_scale);
             asm volatile("barrier.cluster.arrive.relaxed.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
         } else {
         // Trips of 128 (token, row) pairs, four at a time: all loads of the four (the old values from global memory,
