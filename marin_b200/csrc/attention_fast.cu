@@ -13,6 +13,8 @@
 //    (The reference's counterpart: crates/cuda/src/attention_mma.cu:43-180, f16, whole prompts.)
 //
 // Page layout: [page][kv_head][offset in page][HEAD_DIM]; block_table[request][logical page] -> page.
+#define MB_LIB "attention_fast"
+#define MB_LIB_ID 3
 #include "tc_common.cuh"
 #include "launch.cuh"
 #include <type_traits>

@@ -3,6 +3,8 @@
 // alike, any head size, with or without a window.  It is the 32-bit path's attention and the plain twin
 // of the fast kernels (the reference's generic kernel has the same shape, crates/cuda/src/attention.cu:6-96).
 // Page layout: [page][kv_head][offset in page][d].
+#define MB_LIB "attention_simple"
+#define MB_LIB_ID 7
 #include "common.cuh"
 #include "launch.cuh"
 

@@ -24,6 +24,8 @@
 // bounded and record a code in *error_flag.
 // The mma.sync kernel in attention_fast.cu is the fallback and the plain twin (the reference's counterpart:
 // crates/cuda/src/attention_mma.cu:43-180).
+#define MB_LIB "attention_tc"
+#define MB_LIB_ID 4
 #include "tc_common.cuh"
 #include "launch.cuh"
 

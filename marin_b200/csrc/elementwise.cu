@@ -2,6 +2,8 @@
 // Each kernel takes its sizes as arguments; sums, norms and angles are float32 whatever the
 // activation dtype.  The formulas are the reference's (crates/cuda/src/kernels.cu:43-67,147-175,
 // crates/cuda/src/kv_format.cu:48-72); the fusion and the page layout are this engine's own.
+#define MB_LIB "elementwise"
+#define MB_LIB_ID 1
 #include "common.cuh"
 #include "launch.cuh"
 

@@ -3,6 +3,8 @@
 // rows the batch holds.  This is the whole 32-bit path's matrix product (no tensor cores, no reduced-
 // precision mode) and the plain twin the tensor-core kernel is tested against.  The reference's
 // counterpart is its warp-per-row kernel (crates/cuda/src/kernels.cu:73-116).
+#define MB_LIB "gemm_simple"
+#define MB_LIB_ID 6
 #include "common.cuh"
 #include "launch.cuh"
 

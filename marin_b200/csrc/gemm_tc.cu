@@ -20,8 +20,14 @@
 // Every wait on an mbarrier has a time limit; a wait that gives up records a code in *error_flag and the
 // kernel winds down (tensor memory is freed on every path).  The reference's counterpart is its mma.sync
 // kernel with hi/lo-split activations (crates/cuda/src/mma.cu:52-141).
+#define MB_LIB "gemm_tc"
+#define MB_LIB_ID 2
 #include "tc_epilogue.cuh"
 #include "launch.cuh"
+
+#ifndef TC_ROWS4
+#define TC_ROWS4 1             // the cluster's reduction four rows per thread (0: row by row)
+#endif
 
 // The cluster's reduction of a split-K tile, four weight rows of one token per thread (N a multiple of 4): every peer's
 // slice of the partial tile comes through distributed shared memory in 16-byte loads, all of a thread's loads (up to
@@ -106,6 +112,101 @@ __device__ __forceinline__ void cluster_reduce_rows4(uint32_t red_addr, void* ou
     }
 }
 
+// The same meeting of the cluster where the tile is one head of 128 elements (TcHeadsOut): CTA z finishes tokens z,
+// z + S, ...; half a warp takes one token, a lane elements 4l..4l+3 and 64+4l..64+4l+3 (a rotation pair each), so the
+// head's sum of squares needs four shuffles and the rotation none; eight tokens of a CTA are in flight at a time.
+// All threads make every trip.
+template <int S>
+__device__ __forceinline__ void cluster_reduce_heads(uint32_t red_addr, int T, int t0, int t_count, const TcHeadsOut& heads,
+                                                     const TcRowScale& scale, const float* s_scale) {
+    const int head = blockIdx.x, lane = threadIdx.x & 31, hl = lane & 15, sub = threadIdx.x >> 4;
+    const bool is_q = head < heads.H, is_k = !is_q && head < heads.H + heads.K;
+    const float* hw = is_q ? heads.q_weight : (is_k ? heads.k_weight : nullptr);
+    const bool rotate = (is_q || is_k) && heads.inv_freq != nullptr;
+    float4 w_lo = make_float4(1.f, 1.f, 1.f, 1.f), w_hi = w_lo, freq = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (hw != nullptr) {
+        w_lo = *reinterpret_cast<const float4*>(hw + 4 * hl);
+        w_hi = *reinterpret_cast<const float4*>(hw + 64 + 4 * hl);
+    }
+    if (rotate) freq = *reinterpret_cast<const float4*>(heads.inv_freq + 4 * hl);
+    const int mine = t_count > (int)blockIdx.z ? (t_count - (int)blockIdx.z + S - 1) / S : 0;
+    for (int k0 = 0; k0 < mine; k0 += 8) {
+        const int k = k0 + sub;
+        const bool active = k < mine;
+        const int tt = (int)blockIdx.z + S * k, t = t0 + tt;
+        float4 lo[S], hi[S];
+#pragma unroll
+        for (int z = 0; z < S; ++z) {
+            lo[z] = hi[z] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (active) {
+                uint32_t remote;
+                asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(red_addr + (uint32_t)(tt * TC_BM + 4 * hl) * 4u), "r"(z));
+                asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                             : "=f"(lo[z].x), "=f"(lo[z].y), "=f"(lo[z].z), "=f"(lo[z].w) : "r"(remote) : "memory");
+                asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                             : "=f"(hi[z].x), "=f"(hi[z].y), "=f"(hi[z].z), "=f"(hi[z].w) : "r"(remote + 256u) : "memory");
+            }
+        }
+        int pos = 0, slot = -1;
+        if (active) {
+            if (rotate) pos = heads.positions[t];
+            if (!is_q) slot = heads.slot_mapping[t];
+        }
+        float a[4] = {0.f, 0.f, 0.f, 0.f}, b[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int z = 0; z < S; ++z) {                                  // in slice order
+            a[0] += lo[z].x; a[1] += lo[z].y; a[2] += lo[z].z; a[3] += lo[z].w;
+            b[0] += hi[z].x; b[1] += hi[z].y; b[2] += hi[z].z; b[3] += hi[z].w;
+        }
+        const float f = (scale.sumsq != nullptr && active) ? s_scale[tt] : 1.0f;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            // rounded to bf16 here, as the q|k|v rows are when they are written out and normed by a second kernel
+            a[e] = __bfloat162float(__float2bfloat16_rn(a[e] * f));
+            b[e] = __bfloat162float(__float2bfloat16_rn(b[e] * f));
+        }
+        if (hw != nullptr) {
+            float ss = 0.0f;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) ss += a[e] * a[e] + b[e] * b[e];
+            ss = group_sum(ss, 16);
+            const float rstd = 1.0f / sqrtf(ss / (float)TC_BM + heads.eps);
+            const float wl[4] = {w_lo.x, w_lo.y, w_lo.z, w_lo.w}, wh[4] = {w_hi.x, w_hi.y, w_hi.z, w_hi.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { a[e] = a[e] * rstd * wl[e]; b[e] = b[e] * rstd * wh[e]; }
+        }
+        if (!active) continue;
+        if (rotate) {
+            const float fr[4] = {freq.x, freq.y, freq.z, freq.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                float sn, cs;
+                sincosf((float)pos * fr[e], &sn, &cs);
+                const float x = a[e], y = b[e];
+                a[e] = x * cs - y * sn;
+                b[e] = y * cs + x * sn;
+            }
+        }
+        bf16* dst = nullptr;
+        if (is_q) {
+            dst = heads.q_out + ((size_t)t * heads.H + head) * TC_BM;
+        } else if (slot >= 0) {
+            const int kh = is_k ? head - heads.H : head - heads.H - heads.K;
+            dst = (is_k ? heads.k_cache : heads.v_cache) +
+                  (((size_t)(slot / heads.page_size) * heads.K + kh) * heads.page_size + (size_t)(slot % heads.page_size)) * TC_BM;
+        }
+        if (dst != nullptr) {
+            uint2 out_lo, out_hi;
+            *reinterpret_cast<__nv_bfloat162*>(&out_lo.x) = __floats2bfloat162_rn(a[0], a[1]);
+            *reinterpret_cast<__nv_bfloat162*>(&out_lo.y) = __floats2bfloat162_rn(a[2], a[3]);
+            *reinterpret_cast<__nv_bfloat162*>(&out_hi.x) = __floats2bfloat162_rn(b[0], b[1]);
+            *reinterpret_cast<__nv_bfloat162*>(&out_hi.y) = __floats2bfloat162_rn(b[2], b[3]);
+            *reinterpret_cast<uint2*>(dst + 4 * hl) = out_lo;
+            *reinterpret_cast<uint2*>(dst + 64 + 4 * hl) = out_hi;
+        }
+    }
+}
+
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,
                                                       const __grid_constant__ CUtensorMap map_x, void* __restrict__ out,
@@ -134,6 +235,12 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
     // that, not the data, sets the pace once the weights have landed: up to 64 tokens two threads issue, even k-blocks
     // into one accumulator and odd ones into a second, and the epilogue adds the two.
     constexpr bool DUAL = BN <= 64;
+    // With two issuers the ring must have an even number of stages: a stage then belongs to one issuer for good.  With
+    // an odd number the issuers take turns on a stage, and an issuer's first wait on it can be for the barrier's
+    // second phase: a parity wait cannot tell "the second phase is over" from "the first has not ended yet", so the
+    // issuer that is ahead would run MMAs on a stage that is still being filled and give it back once too often
+    // (seen with five stages at 32 tokens: a launch failure once in a few hundred steps).
+    static_assert(!DUAL || STAGES % 2 == 0, "two MMA issuers need an even number of stages");
     constexpr int NSC = DUAL ? 32 : 64;                               // threads that work out the per-token factors
     constexpr uint32_t TMEM_COLS = (DUAL ? 2 * BN : BN) < 32 ? 32 : (DUAL ? 2 * BN : BN);
 
@@ -152,6 +259,7 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
 
+    MB_TRACE_MARK();
     pdl_launch_dependents();
     if (warp == 0 && lane == 0) {
         // ---- producer: TMA loads into the ring.  The weights are written by no kernel, so the first tiles of w
@@ -267,58 +375,69 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
         const int row_first = blockIdx.z * rows_per;
         const int t_count = min(BN, T - t0);
         if (heads.q_out != nullptr) {
-            // ---- this tile is one head: CTA z finishes tokens z, z + splits, ...; a thread is one element of the head
-            const int head = blockIdx.x, i = threadIdx.x;
-            const bool is_q = head < heads.H, is_k = !is_q && head < heads.H + heads.K;
-            const float* hw = is_q ? heads.q_weight : (is_k ? heads.k_weight : nullptr);
-            const float wi = hw != nullptr ? hw[i] : 1.0f;
-            const bool rotate = (is_q || is_k) && heads.inv_freq != nullptr;
-            const float freq = rotate ? heads.inv_freq[i & 63] : 0.0f;
-            asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-            const uint32_t red_addr = smem_u32(red);
-            for (int tt = blockIdx.z; tt < t_count; tt += splits) {
-                const int t = t0 + tt;
-                float sum = 0.0f;
-                for (int z = 0; z < splits; ++z) {
-                    uint32_t remote;
-                    float pv;
-                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(red_addr + (uint32_t)(tt * TC_BM + i) * 4u), "r"(z));
-                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(pv) : "r"(remote) : "memory");
-                    sum += pv;
-                }
-                if (scale.sumsq != nullptr) sum *= s_scale[tt];
-                // rounded to bf16 here, as the q|k|v rows are when they are written out and normed by a second kernel
-                float v = __bfloat162float(__float2bfloat16_rn(sum));
-                if (hw != nullptr) {
-                    const float ss = group_sum(v * v, 32);
-                    if (lane == 0) s_part[warp] = ss;
-                    __syncthreads();
-                    const float total = ((s_part[0] + s_part[1]) + s_part[2]) + s_part[3];
-                    v = v * (1.0f / sqrtf(total / (float)TC_BM + heads.eps)) * wi;
-                }
-                if (rotate) {
-                    s_head[i] = v;
-                    __syncthreads();
-                    const float other = s_head[i ^ 64];
-                    float sn, cs;
-                    sincosf((float)heads.positions[t] * freq, &sn, &cs);
-                    v = i < 64 ? v * cs - other * sn : v * cs + other * sn;
-                }
-                if (is_q) {
-                    heads.q_out[((size_t)t * heads.H + head) * TC_BM + i] = __float2bfloat16_rn(v);
-                } else {
-                    const int slot = heads.slot_mapping[t];
-                    if (slot >= 0) {
-                        const int kh = is_k ? head - heads.H : head - heads.H - heads.K;
-                        bf16* cache = is_k ? heads.k_cache : heads.v_cache;
-                        cache[(((size_t)(slot / heads.page_size) * heads.K + kh) * heads.page_size + (size_t)(slot % heads.page_size)) * TC_BM + i] =
-                            __float2bfloat16_rn(v);
+            if (BN <= 16) {
+                // few tokens: all 128 threads on one token at a time (one angle each) is the shorter chain
+                // ---- this tile is one head: CTA z finishes tokens z, z + splits, ...; a thread is one element of the head
+                const int head = blockIdx.x, i = threadIdx.x;
+                const bool is_q = head < heads.H, is_k = !is_q && head < heads.H + heads.K;
+                const float* hw = is_q ? heads.q_weight : (is_k ? heads.k_weight : nullptr);
+                const float wi = hw != nullptr ? hw[i] : 1.0f;
+                const bool rotate = (is_q || is_k) && heads.inv_freq != nullptr;
+                const float freq = rotate ? heads.inv_freq[i & 63] : 0.0f;
+                asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+                const uint32_t red_addr = smem_u32(red);
+                for (int tt = blockIdx.z; tt < t_count; tt += splits) {
+                    const int t = t0 + tt;
+                    float sum = 0.0f;
+                    for (int z = 0; z < splits; ++z) {
+                        uint32_t remote;
+                        float pv;
+                        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(red_addr + (uint32_t)(tt * TC_BM + i) * 4u), "r"(z));
+                        asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(pv) : "r"(remote) : "memory");
+                        sum += pv;
                     }
+                    if (scale.sumsq != nullptr) sum *= s_scale[tt];
+                    // rounded to bf16 here, as the q|k|v rows are when they are written out and normed by a second kernel
+                    float v = __bfloat162float(__float2bfloat16_rn(sum));
+                    if (hw != nullptr) {
+                        const float ss = group_sum(v * v, 32);
+                        if (lane == 0) s_part[warp] = ss;
+                        __syncthreads();
+                        const float total = ((s_part[0] + s_part[1]) + s_part[2]) + s_part[3];
+                        v = v * (1.0f / sqrtf(total / (float)TC_BM + heads.eps)) * wi;
+                    }
+                    if (rotate) {
+                        s_head[i] = v;
+                        __syncthreads();
+                        const float other = s_head[i ^ 64];
+                        float sn, cs;
+                        sincosf((float)heads.positions[t] * freq, &sn, &cs);
+                        v = i < 64 ? v * cs - other * sn : v * cs + other * sn;
+                    }
+                    if (is_q) {
+                        heads.q_out[((size_t)t * heads.H + head) * TC_BM + i] = __float2bfloat16_rn(v);
+                    } else {
+                        const int slot = heads.slot_mapping[t];
+                        if (slot >= 0) {
+                            const int kh = is_k ? head - heads.H : head - heads.H - heads.K;
+                            bf16* cache = is_k ? heads.k_cache : heads.v_cache;
+                            cache[(((size_t)(slot / heads.page_size) * heads.K + kh) * heads.page_size + (size_t)(slot % heads.page_size)) * TC_BM + i] =
+                                __float2bfloat16_rn(v);
+                        }
+                    }
+                    __syncthreads();                                      // s_part and s_head are used again
                 }
-                __syncthreads();                                      // s_part and s_head are used again
+                asm volatile("barrier.cluster.arrive.relaxed.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+            } else {
+                // ---- this tile is one head ----
+                asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+                const uint32_t red_addr = smem_u32(red);
+                if (splits == 8) cluster_reduce_heads<8>(red_addr, T, t0, t_count, heads, scale, s_scale);
+                else if (splits == 4) cluster_reduce_heads<4>(red_addr, T, t0, t_count, heads, scale, s_scale);
+                else cluster_reduce_heads<2>(red_addr, T, t0, t_count, heads, scale, s_scale);
+                asm volatile("barrier.cluster.arrive.relaxed.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
             }
-            asm volatile("barrier.cluster.arrive.relaxed.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-        } else if (N % 4 == 0) {
+        } else if (TC_ROWS4 && N % 4 == 0) {
             asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
             const uint32_t red_addr = smem_u32(red);
             // items of a thread in flight at a time: all of them where the registers allow
@@ -1051,7 +1170,7 @@ static int gemm_tc_dispatch(const void* x, const void* w, void* out, int mode, i
                             const TcRowScale& scale, const TcHeadsOut& heads, cudaStream_t s) {
     if (T <= 0 || N <= 0) return 0;
     // heads are finished only where the K slices of a tile meet as a cluster
-    if (heads.q_out != nullptr && (!cluster_reduce || splits < 2 || N % TC_BM != 0 || bn > 16 || T > bn)) return MB_ERR_BAD_SIZE;
+    if (heads.q_out != nullptr && (!cluster_reduce || splits < 2 || N % TC_BM != 0 || bn > 128 || T > bn)) return MB_ERR_BAD_SIZE;
     // the norm's side outputs exist for "+=" without global split-K scratch
     if (norm.weight != nullptr && (mode != TC_OUT_F32_ACC || norm.scaled == nullptr || norm.sumsq == nullptr)) return MB_ERR_BAD_DTYPE;
     if (norm.weight != nullptr && !cluster_reduce && splits > 1) return MB_ERR_BAD_SIZE;
@@ -1077,7 +1196,7 @@ static int gemm_tc_dispatch(const void* x, const void* w, void* out, int mode, i
     if (rc) return rc;
     switch (bn) {
         case 16: return launch_tc<16, TC_STAGES16>(mw, mx, out, mode, T, N, K, splits, kb_per_split, partials, counters, error_flag, cluster_reduce, norm, scale, heads, s);
-        case 32: return launch_tc<32, 5>(mw, mx, out, mode, T, N, K, splits, kb_per_split, partials, counters, error_flag, cluster_reduce, norm, scale, heads, s);
+        case 32: return launch_tc<32, 4>(mw, mx, out, mode, T, N, K, splits, kb_per_split, partials, counters, error_flag, cluster_reduce, norm, scale, heads, s);
         case 64: return launch_tc<64, 4>(mw, mx, out, mode, T, N, K, splits, kb_per_split, partials, counters, error_flag, cluster_reduce, norm, scale, heads, s);
         case 128: return launch_tc<128, 3>(mw, mx, out, mode, T, N, K, splits, kb_per_split, partials, counters, error_flag, cluster_reduce, norm, scale, heads, s);
         case 256: return launch_tc<256, 4>(mw, mx, out, mode, T, N, K, splits, kb_per_split, partials, counters, error_flag, cluster_reduce, norm, scale, heads, s);
@@ -1116,10 +1235,10 @@ MB_API int mb_gemm_tc_coupled(const void* x, const void* w, void* out, int mode,
     return gemm_tc_dispatch(x, w, out, mode, T, N, K, bn, splits, nullptr, nullptr, error_flag, 1, norm, scale, TcHeadsOut{}, s);
 }
 
-// The q|k|v product of at most 16 tokens with heads of 128 elements, each head finished in the epilogue (see
-// TcHeadsOut): w is [(H + 2 K) * 128, Kdim] (or [H * 128, Kdim]: queries only, when k_cache is null); splits >= 2.
+// The q|k|v product of at most bn tokens (16, 32, 64 or 128) with heads of 128 elements, each head finished in the
+// epilogue (see TcHeadsOut): w is [(H + 2 K) * 128, Kdim] (or [H * 128, Kdim]: queries only, when k_cache is null); splits >= 2.
 // q_weight / k_weight null: no norm; inv_freq null: no rotation.  scale_*: as for mb_gemm_tc_coupled.
-MB_API int mb_gemm_tc_heads(const void* x, const void* w, int T, int N, int K, int splits, void* q_out, void* k_cache, void* v_cache,
+MB_API int mb_gemm_tc_heads(const void* x, const void* w, int T, int N, int K, int bn, int splits, void* q_out, void* k_cache, void* v_cache,
                             const float* q_weight, const float* k_weight, float eps, const int* positions, const float* inv_freq,
                             const int* slot_mapping, int H, int KV, int page_size, const float* scale_sumsq, int scale_slots,
                             int scale_dim, float scale_eps, int* error_flag, cudaStream_t s) {
@@ -1128,7 +1247,7 @@ MB_API int mb_gemm_tc_heads(const void* x, const void* w, int T, int N, int K, i
     if (inv_freq != nullptr && positions == nullptr) return MB_ERR_BAD_SIZE;
     TcHeadsOut heads{(bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, q_weight, k_weight, positions, inv_freq, slot_mapping, eps, H, KV, page_size};
     TcRowScale scale{scale_sumsq, scale_slots, scale_dim, scale_eps};
-    return gemm_tc_dispatch(x, w, nullptr, TC_OUT_BF16, T, N, K, 16, splits, nullptr, nullptr, error_flag, 1, TcNormOut{}, scale, heads, s);
+    return gemm_tc_dispatch(x, w, nullptr, TC_OUT_BF16, T, N, K, bn, splits, nullptr, nullptr, error_flag, 1, TcNormOut{}, scale, heads, s);
 }
 
 // ---- the entry point that allocates nothing (see gemm_tc_noalloc.h) --------------------------------------------

@@ -4,10 +4,38 @@
 //   * nothing that an earlier kernel may write is read, and no global memory is written, before pdl_wait(); pointers
 //     to such data are renewed with pdl_fresh() after the wait, so that the compiler cannot move their loads up;
 //   * pdl_wait() returns once every earlier kernel in the stream has finished and its writes are visible.
-// Without the launch attribute both instructions do nothing.  MARIN_B200_PDL=0 in the environment turns it off.
+// Without the launch attribute both instructions do nothing.  MARIN_B200_PDL=0 in the environment turns it off;
+// MARIN_B200_PDL_OFF=gemm_tc,sampling turns it off for the launches of some libraries (each source file names its
+// library in MB_LIB before it includes this header): a tool for finding which kernel a race between neighbours is in.
 #pragma once
 #include <cuda_runtime.h>
 #include <stdlib.h>
+#include <string.h>
+
+#ifndef MB_LIB
+#define MB_LIB ""
+#endif
+
+// -DMB_TRACE: every kernel's first block leaves a mark in a buffer the host owns (pinned memory: it outlives a fault of
+// the context): buffer[0] counts the marks, mark i is at buffer[1 + i % 1023] = library id << 20 | source line of the
+// kernel's entry.  A tool for finding which kernels were running when a launch failed; nothing is built with it by default.
+#ifdef MB_TRACE
+#ifndef MB_LIB_ID
+#define MB_LIB_ID 0
+#endif
+__device__ int* mb_trace_buf;
+extern "C" __attribute__((visibility("default"))) int mb_set_trace(int* p) { return (int)cudaMemcpyToSymbol(mb_trace_buf, &p, sizeof p); }
+#define MB_TRACE_MARK()                                                                                      \
+    do {                                                                                                     \
+        if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && mb_trace_buf != nullptr) { \
+            const int mark_at = atomicAdd_system(mb_trace_buf, 1);                                           \
+            mb_trace_buf[1 + mark_at % 1023] = (MB_LIB_ID << 20) | __LINE__;                                 \
+            __threadfence_system();                                                                          \
+        }                                                                                                    \
+    } while (0)
+#else
+#define MB_TRACE_MARK() do { } while (0)
+#endif
 
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
@@ -28,8 +56,8 @@ __device__ __forceinline__ T* pdl_fresh(T* p) {
 // SMs, set up and waiting, while this kernel runs.  Measured on B200: early scheduling gains 3 % on a prompt of 2,048
 // tokens when the long kernels (the persistent matrix product, prefill attention) do it, and loses 5 % in decode
 // steps when the short kernels do it too.  -DPDL_WAIT_FIRST or -DPDL_LAUNCH_FIRST force one order everywhere.
-#define PDL_ENTER_LATE() do { pdl_wait(); pdl_launch_dependents(); } while (0)
-#define PDL_ENTER_AT_ONCE() do { pdl_launch_dependents(); pdl_wait(); } while (0)
+#define PDL_ENTER_LATE() do { MB_TRACE_MARK(); pdl_wait(); pdl_launch_dependents(); } while (0)
+#define PDL_ENTER_AT_ONCE() do { MB_TRACE_MARK(); pdl_launch_dependents(); pdl_wait(); } while (0)
 #if defined(PDL_WAIT_FIRST)
 #define PDL_ENTER() PDL_ENTER_LATE()
 #define PDL_ENTER_EARLY() PDL_ENTER_LATE()
@@ -46,6 +74,8 @@ static inline bool pdl_enabled() {
     if (state < 0) {
         const char* v = getenv("MARIN_B200_PDL");
         state = (v != nullptr && v[0] == '0') ? 0 : 1;
+        const char* off = getenv("MARIN_B200_PDL_OFF");
+        if (off != nullptr && MB_LIB[0] != 0 && strstr(off, MB_LIB) != nullptr) state = 0;
     }
     return state == 1;
 }

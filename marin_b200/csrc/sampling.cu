@@ -14,6 +14,8 @@
 // and the host reads them there once an event behind the kernel has completed, with no copy of its own in the
 // stream.  Two rows in turn (the host says which, in device memory, before each step): the step that runs must not
 // overwrite what the host still reads of the step before.
+#define MB_LIB "sampling"
+#define MB_LIB_ID 5
 #include "common.cuh"
 #include "launch.cuh"
 #include <limits.h>

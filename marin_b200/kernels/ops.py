@@ -447,7 +447,7 @@ def gemm(x, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False, then_n
 
 #: with few tokens the q|k|v product finishes its heads itself (norm, rotation, cache write) where the layout allows
 fuse_heads = True
-FUSED_HEADS_MAX_TOKENS = 16
+FUSED_HEADS_MAX_TOKENS = 128
 
 
 #: the same for many tokens, in the persistent kernel's epilogue (tile by tile, no stream-K)
@@ -504,14 +504,14 @@ def gemm_qkv_heads(x, w: torch.Tensor, q_out: torch.Tensor, q_weight, k_weight, 
             "gemm (persistent) with heads finished in the epilogue")
         return True
     bn, splits = gemm_plan(T, N, Kdim)
-    if bn != 16 or splits < 2:
+    if T > bn or splits < 2:
         return False
     _need_cuda(rows, w, q_out)
     assert tuple(q_out.shape) == (T, H * d) and w.shape[1] == Kdim
     _cost(_size(w) + _size(rows) + T * N * 2, 2.0 * T * N * Kdim)
     s = _scratch_for(rows.device)
     _check(_lib("mb_gemm_tc").mb_gemm_tc_heads(
-        _ptr(rows), _ptr(w), _c_int(T), _c_int(N), _c_int(Kdim), _c_int(splits), _ptr(q_out),
+        _ptr(rows), _ptr(w), _c_int(T), _c_int(N), _c_int(Kdim), _c_int(bn), _c_int(splits), _ptr(q_out),
         _ptr(k_cache) if write_kv else None, _ptr(v_cache) if write_kv else None, _ptr(q_weight), _ptr(k_weight), _c_float(eps),
         _ptr(positions), _ptr(inv_freq), _ptr(slot_mapping) if write_kv else None, _c_int(H), _c_int(K), _c_int(page_size),
         _ptr(scaled.sumsq) if scaled is not None else None, _c_int(scaled.slots if scaled is not None else 0),
