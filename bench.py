@@ -259,7 +259,7 @@ def profile_mode(engine, args, pk):
     peaks_line = f"peaks ({pk['source']}): {pk['hbm_gbs']:.0f} GB/s copy, {pk['bf16_tflops']:.0f} TFLOP/s bf16"
     print(f"{where}; {peaks_line}; in-step times under the CUDA profiling interface (medians of 6 steps)\n")
     steps, warmup = 6, 4
-    for batch in (1, 8, 64):
+    for batch in sorted({1, 8, 64, args.batch}):
         ids = [f"prof{batch}_{i}" for i in range(batch)]
         for rid in ids:
             runner.begin(rid)

@@ -301,6 +301,17 @@ def _tile_by_tile(T: int, N: int):
     return best
 
 
+def many_tokens(T: int, N: int, with_heads: bool = False) -> bool:
+    """Whether a product of T tokens and N weight rows goes to the persistent kernel (else: one CTA per tile, K cut
+    over the CTAs of a cluster where tiles are few).  It needs a round of tiles to be worth it: with fewer tiles than SMs
+    the clusters' many CTAs ask for more at once (measured at Qwen3-4B sizes: the down product at 512 tokens 43 us
+    against 52, at 768 tokens 45 against 53; o at 768 tokens 23 against 26).  The q|k|v product that finishes its heads
+    stays persistent from half a round on: beyond 128 tokens only that kernel can finish them (17.6 us at 256 tokens
+    against 18.2 plus the q/k kernel)."""
+    tiles = -(-N // 128) * -(-T // 128)
+    return T > 128 and tiles >= (SM_COUNT // 2 if with_heads else SM_COUNT)
+
+
 #: the persistent kernel deals k-blocks instead of tiles over the SMs where whole tiles would leave SMs idle
 stream_k = True
 
@@ -398,7 +409,7 @@ def gemm(x, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False, then_n
     if (use_tensor_cores and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and K % 8 == 0
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and T > 0):
         mode = 2 if accumulate else (0 if out.dtype == torch.bfloat16 else 1)
-        if T > 128 and -(-N // 128) * -(-T // 128) >= SM_COUNT // 2:
+        if many_tokens(T, N):
             s = _scratch_for(x.device)
             lib = _lib("mb_gemm_tc")
             carried = None
@@ -489,7 +500,7 @@ def gemm_qkv_heads(x, w: torch.Tensor, q_out: torch.Tensor, q_weight, k_weight, 
         return False
     page_size = k_cache.shape[2] if write_kv else 0
     if T > FUSED_HEADS_MAX_TOKENS:
-        if not (fuse_heads_many_tokens and scaled is None and T > 128 and -(-N // 128) * -(-T // 128) >= SM_COUNT // 2
+        if not (fuse_heads_many_tokens and scaled is None and many_tokens(T, N, with_heads=True)
                 and (inv_freq is None or ctx is not None)):
             return False
         _need_cuda(rows, w, q_out)
@@ -730,7 +741,7 @@ def gemm_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor, out: torch.Tensor,
         return
     s = _scratch_for(x.device)
     _cost(_size(w_interleaved) + _size(x) + _size(out), 2.0 * T * N * K)
-    if T > 128 and -(-N // 128) * -(-T // 128) >= SM_COUNT // 2:
+    if many_tokens(T, N):
         if scaled is not None:
             _check(_lib("mb_gemm_tc").mb_gemm_tc_persistent_coupled(
                 _ptr(x), _ptr(w_interleaved), _ptr(out), _c_int(3), _c_int(T), _c_int(N), _c_int(K), _c_int(persistent_plan(T, N)),
