@@ -16,10 +16,13 @@
 // two buffers each.  S (and with it P) has two buffers as well; the MMAs run in the order they are issued, so S of
 // block i + 2 may follow P V of block i without a barrier.  Every barrier used once per block exists per buffer parity,
 // since the rows may run a block ahead of the MMA warp.
-// Seven warps: four own the 128 query rows (softmax, output), one issues the MMAs, one asks for keys and one for values.
+// Eight warps: four own the 128 query rows (softmax, output), one issues S, one P V, one asks for keys and one for values.
 // (A cycle-stamped timeline of one CTA showed that asking for a block of K or V, or issuing a block's MMAs, takes a
-// warp 700 to 900 cycles each; one warp doing all four jobs set the pace of the kernel at 3,400 cycles a block, three
-// warps bring it to 1,800, where the latency of the K copy plus S, and the rows' softmax, are about level.)
+// warp 700 to 900 cycles each; one warp doing all four jobs set the pace of the kernel at 3,400 cycles a block, a warp
+// for each brings it to 1,500, which is the rows' softmax: a -DTA_PROBE build counts where the rows and the issuers
+// wait.  The rows read a block's 64 scores twice, each time with one load of 64 columns; keeping them in registers
+// instead takes the thread to 128 registers with spills and is slower, and two threads per row, each with half of
+// the keys, meet at a barrier every block and are slower too: 1,800 cycles.)
 // Two CTAs fit an SM: one's softmax overlaps the other's MMAs.  Needs pages of at least 16 positions.  Waits are
 // bounded and record a code in *error_flag.
 // The mma.sync kernel in attention_fast.cu is the fallback and the plain twin (the reference's counterpart:
@@ -77,6 +80,20 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// 64 columns of this thread's lane in one instruction and one wait (two loads of 32 cost two round trips to tensor
+// memory, about 200 cycles each, that nothing in the thread can hide).
+__device__ __forceinline__ void tmem_ld64(uint32_t taddr, float* v) {
+    uint32_t r[64];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x64.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];\n\t"
+        "tcgen05.wait::ld.sync.aligned;"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
+        : "r"(taddr)
+        : "memory");
+#pragma unroll
+    for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
+}
+
 // Waits for a phase; gives up at once if another thread of the CTA already gave up (`*abort`), and says so itself when
 // its own time limit passes.
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort, int* error_flag, int code) {
@@ -127,7 +144,7 @@ __device__ __forceinline__ void umma_bf16_tmem_a(uint32_t tmem_d, uint32_t tmem_
         : "memory");
 }
 
-// 224 threads: warps 0..3 own the 128 query rows (softmax, output); warp 4 issues the MMAs; warp 5 asks for keys, warp 6 for values.
+// 256 threads: warps 0..3 own the 128 query rows (softmax, output); warp 4 issues S, warp 7 P V; warp 5 asks for keys, warp 6 for values.
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
@@ -156,7 +173,20 @@ __device__ __forceinline__ void tmem_st32_bits(uint32_t taddr, const uint32_t* v
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
-__global__ void __launch_bounds__(224, 2) attn_prefill_tc_kernel(
+#ifdef TA_PROBE
+// Where the roles wait (a build for measuring only, -DTA_PROBE): per CTA (x + gridDim.x * y of request 0), clock ticks
+// of [0] row 0 waiting for S, [1] row 0 waiting for O before a rescale, [2] row 0's loop in all, [3] the MMA thread
+// finding nothing to issue, [4] the MMA thread's loop in all, [5] the key blocks.
+__device__ long long ta_probe[4096 * 8];
+MB_API int mb_attn_prefill_tc_probe_read(long long* host) { return (int)cudaMemcpyFromSymbol(host, ta_probe, sizeof(ta_probe)); }
+#define TA_T() clock64()
+#define TA_OUT(slot, v) do { const int cta_ = blockIdx.x + gridDim.x * blockIdx.y; if (blockIdx.z == 0 && cta_ < 4096) ta_probe[cta_ * 8 + (slot)] = (v); } while (0)
+#else
+#define TA_T() 0LL
+#define TA_OUT(slot, v) do { } while (0)
+#endif
+
+__global__ void __launch_bounds__(256, 2) attn_prefill_tc_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
     bf16* __restrict__ out, const int* __restrict__ block_table, int max_pages, const int* __restrict__ cu_tokens,
     const int* __restrict__ seq_lens, int first_req, int K, int page_shift, float scale, int window, int* __restrict__ error_flag,
@@ -221,7 +251,7 @@ __global__ void __launch_bounds__(224, 2) attn_prefill_tc_kernel(
     const int rot = (int)(((unsigned)(h * gridDim.x + qt) * 37u) % (unsigned)nblk);
     auto block_of = [&](int i) { const int j = i + rot; return kb_first + (j >= nblk ? j - nblk : j); };
 
-    if (warp >= 5) {
+    if (warp == 5 || warp == 6) {
         // ---- the loader warps: warp 5 asks for Q once and then for every block of K, warp 6 for every block of V, each
         // as soon as the block's buffer is free.  Lanes 0..3 each ask for one box of a block, so that one instruction
         // starts four TMA copies.  (Measured with cycle stamps: asking for a block takes a warp about 900 cycles, issuing
@@ -275,15 +305,14 @@ __global__ void __launch_bounds__(224, 2) attn_prefill_tc_kernel(
             }
         }
     } else if (warp == 4) {
-        // ---- the MMA warp: one lane issues S = Q K^T of the next block as soon as its keys have landed (and P V of two
-        // blocks ago has been issued: S(i) goes where P(i - 2) lies, and the MMAs run in the order they are issued),
-        // and O += P V of the oldest block whose P is in tensor memory and whose values have landed ----
+        // ---- the issuer of S: one lane issues S(i) = Q K(i)^T as soon as the block's keys have landed and P V of block
+        // i - 2 is done (S(i) goes where P(i - 2) lies).  Issuing an MMA costs the thread over a hundred cycles, and a
+        // block has twelve: one thread for all of them set the kernel's pace (1,600 of a block's 1,620 cycles busy), so
+        // S and P V have an issuer each. ----
         if (lane == 0) {
             constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TA_BN >> 3) << 17) | ((uint32_t)(TA_BM >> 4) << 24);
-            constexpr uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(TA_BM >> 4) << 24);
-            // the descriptors of every MMA of a block, for either buffer, worked out once
             const uint32_t sq = smem_u32(sQ);
-            uint64_t qdesc[D / 16], kdesc[2][D / 16], vdesc[2][TA_BN / 16];
+            uint64_t qdesc[D / 16], kdesc[2][D / 16];
 #pragma unroll
             for (int kk = 0; kk < D / 16; ++kk) {
                 qdesc[kk] = umma_desc(sq + (kk / 4) * (TA_BM * 128)) + 2 * (kk % 4);
@@ -291,12 +320,15 @@ __global__ void __launch_bounds__(224, 2) attn_prefill_tc_kernel(
                 for (int b = 0; b < 2; ++b)
                     kdesc[b][kk] = umma_desc(smem_u32(sKV + (size_t)b * 2 * TA_KV_BYTES) + (kk / 4) * (TA_BN * 128)) + 2 * (kk % 4);
             }
-#pragma unroll
-            for (int kk = 0; kk < TA_BN / 16; ++kk)
-#pragma unroll
-                for (int b = 0; b < 2; ++b)
-                    vdesc[b][kk] = umma_desc_mn(smem_u32(sKV + (size_t)b * 2 * TA_KV_BYTES) + TA_KV_BYTES + kk * 2048, TA_BN * 128);
-            auto issue_s = [&](int i) {                     // S(i) = Q K(i)^T into S buffer i & 1
+            bool ok = wait_or_abort(q_full, 0, abort, error_flag, 21);
+            const long long start = TA_T();
+            long long m_idle = 0;
+            for (int i = 0; ok && i < nblk; ++i) {
+                const long long m_t0 = TA_T();
+                ok = wait_or_abort(&k_full[i & 1], (i >> 1) & 1, abort, error_flag, 29);
+                if (ok && i >= 2) ok = wait_or_abort(&v_free[i & 1], ((i - 2) >> 1) & 1, abort, error_flag, 29);
+                m_idle += TA_T() - m_t0;
+                if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 if (i & 1) {
 #pragma unroll
@@ -306,42 +338,45 @@ __global__ void __launch_bounds__(224, 2) attn_prefill_tc_kernel(
                     for (int kk = 0; kk < D / 16; ++kk) umma_bf16(tmem_base, qdesc[kk], kdesc[0][kk], idesc_s, kk > 0 ? 1u : 0u);
                 }
                 umma_commit(&s_done[i & 1]);
-            };
-            bool ok = wait_or_abort(q_full, 0, abort, error_flag, 21);
-            int next_s = 0, next_pv = 0;
-            unsigned idle = 0;
-            const long long start = clock64();
-            while (ok && next_pv < nblk) {
-                bool progressed = false;
-                if (next_s < nblk && next_s < next_pv + 2 && mbar_test(&k_full[next_s & 1], (next_s >> 1) & 1)) {
-                    issue_s(next_s);
-                    ++next_s;
-                    progressed = true;
-                }
-                if (next_pv < next_s && mbar_test(&p_ready[next_pv & 1], (next_pv >> 1) & 1) && mbar_test(&v_full[next_pv & 1], (next_pv >> 1) & 1)) {
-                    // O += P(i) V(i) in TMEM columns [128, 128 + D); any rescaling of O by the rows happened before they arrived
-                    const int buf = next_pv & 1;
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    // P is the A operand straight from tensor memory: row = lane, two bf16 per 32-bit column
-                    const uint32_t tp = tmem_base + (uint32_t)(buf * TA_BN);
-                    if (buf) {
-#pragma unroll
-                        for (int kk = 0; kk < TA_BN / 16; ++kk)
-                            umma_bf16_tmem_a(tmem_base + TA_O_COL, tp + (uint32_t)(kk * 8), vdesc[1][kk], idesc_pv, (next_pv > 0 || kk > 0) ? 1u : 0u);
-                    } else {
-#pragma unroll
-                        for (int kk = 0; kk < TA_BN / 16; ++kk)
-                            umma_bf16_tmem_a(tmem_base + TA_O_COL, tp + (uint32_t)(kk * 8), vdesc[0][kk], idesc_pv, (next_pv > 0 || kk > 0) ? 1u : 0u);
-                    }
-                    umma_commit(&v_free[buf]);
-                    ++next_pv;
-                    progressed = true;
-                }
-                if (!progressed && (++idle & 63) == 0) {
-                    if (*abort) ok = false;
-                    else if (clock64() - start > 8 * TC_WAIT_LIMIT) { *abort = 1; atomicExch(error_flag, 29); ok = false; }
-                }
             }
+            TA_OUT(3, m_idle); TA_OUT(4, TA_T() - start); TA_OUT(5, (long long)nblk);
+        }
+    } else if (warp == 7) {
+        // ---- the issuer of P V: O += P(i) V(i) once the rows have put P(i) into tensor memory and the values have landed
+        // (any rescaling of O by the rows happened before they arrived) ----
+        if (lane == 0) {
+            constexpr uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(D >> 3) << 17) | ((uint32_t)(TA_BM >> 4) << 24);
+            uint64_t vdesc[2][TA_BN / 16];
+#pragma unroll
+            for (int kk = 0; kk < TA_BN / 16; ++kk)
+#pragma unroll
+                for (int b = 0; b < 2; ++b)
+                    vdesc[b][kk] = umma_desc_mn(smem_u32(sKV + (size_t)b * 2 * TA_KV_BYTES) + TA_KV_BYTES + kk * 2048, TA_BN * 128);
+            bool ok = true;
+            const long long start = TA_T();
+            long long m_idle = 0;
+            for (int i = 0; ok && i < nblk; ++i) {
+                const int buf = i & 1;
+                const long long m_t0 = TA_T();
+                ok = wait_or_abort(&p_ready[buf], (i >> 1) & 1, abort, error_flag, 29);
+                if (ok) ok = wait_or_abort(&v_full[buf], (i >> 1) & 1, abort, error_flag, 29);
+                m_idle += TA_T() - m_t0;
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                // P is the A operand straight from tensor memory: row = lane, two bf16 per 32-bit column
+                const uint32_t tp = tmem_base + (uint32_t)(buf * TA_BN);
+                if (buf) {
+#pragma unroll
+                    for (int kk = 0; kk < TA_BN / 16; ++kk)
+                        umma_bf16_tmem_a(tmem_base + TA_O_COL, tp + (uint32_t)(kk * 8), vdesc[1][kk], idesc_pv, (i > 0 || kk > 0) ? 1u : 0u);
+                } else {
+#pragma unroll
+                    for (int kk = 0; kk < TA_BN / 16; ++kk)
+                        umma_bf16_tmem_a(tmem_base + TA_O_COL, tp + (uint32_t)(kk * 8), vdesc[0][kk], idesc_pv, (i > 0 || kk > 0) ? 1u : 0u);
+                }
+                umma_commit(&v_free[buf]);
+            }
+            TA_OUT(6, m_idle); TA_OUT(7, TA_T() - start);
         }
     } else {
         // ---- the rows: thread t owns query row t ----
@@ -352,10 +387,14 @@ __global__ void __launch_bounds__(224, 2) attn_prefill_tc_kernel(
         const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16);
         float m_used = -INFINITY, l_run = 0.0f;           // the maximum O and l are currently scaled by (log2 units)
         bool ok = true;
+        long long r_s = 0, r_o = 0;
+        const long long r_start = TA_T();
         for (int i = 0; i < nblk; ++i) {
             const int key0 = block_of(i) * TA_BN;
             const uint32_t s_col = lane_base + (uint32_t)((i & 1) * TA_BN);
+            const long long r_t0 = TA_T();
             ok = ok && wait_or_abort(&s_done[i & 1], (i >> 1) & 1, abort, error_flag, 23);
+            r_s += TA_T() - r_t0;
             ok = __all_sync(0xffffffffu, ok);              // tcgen05.ld is warp-wide: the warp takes one path
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -363,17 +402,20 @@ __global__ void __launch_bounds__(224, 2) attn_prefill_tc_kernel(
             // the row maximum first, then the probabilities
             const bool interior = key0 + TA_BN - 1 <= q_first && (window <= 0 || key0 >= q_last - window + 1);
             float mx = -INFINITY;
-#pragma unroll
-            for (int hf = 0; hf < 2; ++hf) {
-                float s[32];
-                tmem_ld32(s_col + hf * 32, s);
+            {
+                float s[64];
+                tmem_ld64(s_col, s);
                 if (!interior) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j)
-                        if (!(key0 + hf * 32 + j <= qp && key0 + hf * 32 + j >= lo_t)) s[j] = -INFINITY;
+                    for (int j = 0; j < 64; ++j)
+                        if (!(key0 + j <= qp && key0 + j >= lo_t)) s[j] = -INFINITY;
                 }
+                float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-                for (int j = 0; j < 32; ++j) mx = fmaxf(mx, s[j]);
+                for (int j = 0; j < 64; j += 4) {
+                    m4[0] = fmaxf(m4[0], s[j]); m4[1] = fmaxf(m4[1], s[j + 1]); m4[2] = fmaxf(m4[2], s[j + 2]); m4[3] = fmaxf(m4[3], s[j + 3]);
+                }
+                mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
             }
             // raise the scaling maximum only when the true one has moved by more than 8 (or from -inf)
             const float m_true = fmaxf(m_used, mx * sl2);
@@ -382,7 +424,9 @@ __global__ void __launch_bounds__(224, 2) attn_prefill_tc_kernel(
             const float corr = raise ? ta_exp2(m_used - m_new) : 1.0f;      // exp2(-inf) = 0 on the first raise
             if (__any_sync(0xffffffffu, raise) && i >= 1) {
                 // O is being added to by the MMAs of block i - 1 until they are done (blocks up to i - 2 are: S(i) came after them)
+                const long long r_t1 = TA_T();
                 ok = wait_or_abort(&v_free[(i - 1) & 1], ((i - 1) >> 1) & 1, abort, error_flag, 24);
+                r_o += TA_T() - r_t1;
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -399,24 +443,25 @@ __global__ void __launch_bounds__(224, 2) attn_prefill_tc_kernel(
             const float base = m_used == -INFINITY ? 0.0f : m_used;
             float sum = 0.0f;
             uint4 packed[TA_BN / 8];                           // the row of P, kept until the last block's P has been consumed
-#pragma unroll
-            for (int hf = 0; hf < 2; ++hf) {
-                float s[32];
-                tmem_ld32(s_col + hf * 32, s);
+            {
+                float s[64];
+                tmem_ld64(s_col, s);
                 if (!interior) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j)
-                        if (!(key0 + hf * 32 + j <= qp && key0 + hf * 32 + j >= lo_t)) s[j] = -INFINITY;
+                    for (int j = 0; j < 64; ++j)
+                        if (!(key0 + j <= qp && key0 + j >= lo_t)) s[j] = -INFINITY;
                 }
+                float sum2[2] = {0.0f, 0.0f};
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
+                for (int c = 0; c < 8; ++c) {
                     float p[8];
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) { p[e] = ta_exp2(fmaf(s[c * 8 + e], sl2, -base)); sum += p[e]; }
-                    __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&packed[hf * 4 + c]);
+                    for (int e = 0; e < 8; ++e) { p[e] = ta_exp2(fmaf(s[c * 8 + e], sl2, -base)); sum2[e & 1] += p[e]; }
+                    __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&packed[c]);
 #pragma unroll
                     for (int e = 0; e < 4; ++e) p2[e] = __floats2bfloat162_rn(p[2 * e], p[2 * e + 1]);
                 }
+                sum = sum2[0] + sum2[1];
             }
             l_run = l_run * corr + sum;
             // the row of P goes over the first 32 columns of its own scores (all 64 are in registers by now)
@@ -425,6 +470,7 @@ __global__ void __launch_bounds__(224, 2) attn_prefill_tc_kernel(
             __syncwarp();
             if (lane == 0) mbar_arrive_one(&p_ready[i & 1]);
         }
+        if (threadIdx.x == 0) { TA_OUT(0, r_s); TA_OUT(1, r_o); TA_OUT(2, TA_T() - r_start); }
         if (ok) {
             ok = wait_or_abort(&v_free[(nblk - 1) & 1], ((nblk - 1) >> 1) & 1, abort, error_flag, 24);
             ok = __all_sync(0xffffffffu, ok);
@@ -500,6 +546,6 @@ MB_API int mb_attn_prefill_tc(const void* q, const void* k_cache, const void* v_
     rc = map_2d(&mv, v_cache, cache_rows, D, box_rows);
     if (rc) return rc;
     dim3 grid((max_query_len + TA_BM - 1) / TA_BM, K * GROUP, requests);
-    return launch_kernel(attn_prefill_tc_kernel, grid, 224, TA_SMEM, s, 0, mq, mk, mv, (bf16*)out, block_table, max_pages, cu_tokens,
+    return launch_kernel(attn_prefill_tc_kernel, grid, 256, TA_SMEM, s, 0, mq, mk, mv, (bf16*)out, block_table, max_pages, cu_tokens,
                          seq_lens, first_req, K, page_shift, scale, window, error_flag, box_rows);
 }
