@@ -183,7 +183,7 @@ MB_API int mb_attn_prefill_tc_probe_read(long long* host) { return (int)cudaMemc
 #define TA_OUT(slot, v) do { const int cta_ = blockIdx.x + gridDim.x * blockIdx.y; if (blockIdx.z == 0 && cta_ < 4096) ta_probe[cta_ * 8 + (slot)] = (v); } while (0)
 #else
 #define TA_T() 0LL
-#define TA_OUT(slot, v) do { } while (0)
+#define TA_OUT(slot, v) do { (void)(v); } while (0)
 #endif
 
 __global__ void __launch_bounds__(256, 2) attn_prefill_tc_kernel(
