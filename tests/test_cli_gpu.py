@@ -63,3 +63,27 @@ def test_run_random_and_bench_commands(tmp_path):
     assert rec["prompt_tokens"] == 16 and rec["decode_tokens_per_s"] > 0 and rec["batch_size"] == 1
     f = subprocess.run(RUN + [model, "--max-tokens", "6"], capture_output=True, text=True)
     assert f.returncode != 0 and "prompt" in f.stderr
+
+
+def test_the_measuring_aids_run(tmp_path):
+    """``python -m marin_b200.kernels.probe`` (the many-token product built with -DTC_PROBE: where its producer and its MMA
+    thread wait) prints its table, and ``kernels.trace.Marks`` hands its pinned buffer to the loaded libraries: none of
+    the normal build takes it, so no mark is left."""
+    import torch
+
+    out = subprocess.run([sys.executable, "-m", "marin_b200.kernels.probe", "--tokens", "512", "--rows", "1024", "--width", "512", "--tile", "256"],
+                         capture_output=True, text=True, cwd=ROOT)
+    assert out.returncode == 0, out.stderr[-2000:]
+    lines = out.stdout.strip().splitlines()
+    assert "TFLOP/s" in lines[0] and lines[1].startswith("CTA")
+    first = lines[2].split()
+    assert int(first[0]) == 0 and int(first[1]) > 0 and all(float(v) >= 0 for v in first[2:])
+    assert float(first[-1]) > 0                                 # the MMA thread's loop took some cycles per k-block
+
+    from marin_b200.kernels import ops, trace
+
+    x = torch.zeros(4, 64, device="cuda:0", dtype=torch.bfloat16)
+    w = torch.zeros(128, 64, device="cuda:0", dtype=torch.bfloat16)
+    ops.gemm(x, w, torch.empty(4, 128, device="cuda:0"))        # a library is loaded
+    marks = trace.Marks()
+    assert marks.arm() == 0 and marks.count() == 0 and marks.last() == []
