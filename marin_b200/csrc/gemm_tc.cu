@@ -681,11 +681,12 @@ __global__ void __launch_bounds__(320) gemm_tc_persistent_kernel(const __grid_co
                                                                  void* __restrict__ out, int mode, int T, int N, int K,
                                                                  int* __restrict__ error_flag, const TcNormOut norm,
                                                                  const TcRowScale scale, const TcStreamK sk, const TcHeadsOut heads,
-                                                                 const float* __restrict__ rope) {
+                                                                 const float* __restrict__ rope,
+                                                                 const __grid_constant__ CUtensorMap map_out, int reduce_out) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ float s_pscale[2][BN];          // the per-token factors of a coupled norm, for the tile in each accumulator
     // heads finished in the epilogue: per half of the columns (its four warps), two staging buffers of sixteen tokens
-    __shared__ __align__(16) bf16 s_hx[2][2][16 * TC_BM];
+    __shared__ __align__(128) bf16 s_hx[2][2][16 * TC_BM];     // (also, as floats, the staging of a "+=" by TMA reduction: 8 KB per half)
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     using L = TcSmem<BN>;
     uint64_t* full = (uint64_t*)(smem + STAGES * L::STAGE_BYTES);
@@ -824,6 +825,14 @@ __global__ void __launch_bounds__(320) gemm_tc_persistent_kernel(const __grid_co
                 }
             };
             if (!SK && heads.q_out != nullptr) heads_fetch(c_begin);
+            // the four warps that share a half of the columns meet at barriers inside some epilogues' chunks (ids 2 and
+            // 3): there they go on together or not at all
+            auto half_agrees = [&](bool mine) {
+                uint32_t all_ok;
+                asm volatile("{ .reg .pred p, q; setp.ne.u32 p, %1, 0; bar.red.and.pred q, %2, 128, p; selp.u32 %0, 1, 0, q; }"
+                             : "=r"(all_ok) : "r"((uint32_t)mine), "r"(2 + col_half) : "memory");
+                return all_ok != 0;
+            };
             // what happens to 16 finished columns of this thread's row
             auto finish_chunk = [&](float* v, int c0) {
                 if (!SK && heads.q_out != nullptr) {
@@ -919,6 +928,24 @@ __global__ void __launch_bounds__(320) gemm_tc_persistent_kernel(const __grid_co
                     store_chunk_norm(out, t0 + c0, n, n < N, T, N, v, norm, norm.sumsq + (size_t)(tile_row * 4 + quarter) * T, lane);
                 } else if (mode == TC_OUT_SWIGLU) {
                     if (n0 + quarter * 32 < N) store_chunk_swiglu(out, t0 + c0, n0 + quarter * 32, lane, T, N, v);
+                } else if (reduce_out) {
+                    // "+=" into float32 without reading the old values: the four warps that share this half of the columns
+                    // lay sixteen tokens of the tile into shared memory and one thread hands them to a TMA reduction
+                    // (an add in L2; rows and tokens past the matrix are clipped).  One add per element and launch: the
+                    // same bits every time.  The buffer is used again once the reduction before has read it.
+                    float* stage = reinterpret_cast<float*>(&s_hx[col_half][0][0]);
+                    const bool issuer = quarter == 0 && lane == 0;
+                    if (issuer) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                    asm volatile("bar.sync %0, 128;" ::"r"(2 + col_half) : "memory");
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) stage[j * TC_BM + quarter * 32 + lane] = v[j];
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    asm volatile("bar.sync %0, 128;" ::"r"(2 + col_half) : "memory");
+                    if (issuer) {
+                        asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+                                     ::"l"(&map_out), "r"(smem_u32(stage)), "r"(n0), "r"(t0 + c0) : "memory");
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    }
                 } else if (n < N) store_chunk(out, mode, t0 + c0, n, T, N, v);
             };
             // the parked piece: [BN columns][128 rows], so that a warp's 32 lanes store and load 128 contiguous bytes;
@@ -956,6 +983,7 @@ __global__ void __launch_bounds__(320) gemm_tc_persistent_kernel(const __grid_co
                 }
                 if (ok && !mbar_wait(&acc_full[buf], acc_phase)) { if (lane == 0) atomicExch(error_flag, 14); ok = false; }
                 ok = __all_sync(0xffffffffu, ok);
+                if (reduce_out) ok = half_agrees(ok);
                 if (!ok) continue;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
@@ -979,13 +1007,7 @@ __global__ void __launch_bounds__(320) gemm_tc_persistent_kernel(const __grid_co
                 // a warp whose wait gave up keeps walking the tiles (the barrier above counts on it) but touches nothing
                 if (ok && !mbar_wait(&acc_full[buf], acc_phase)) { if (lane == 0) atomicExch(error_flag, 14); ok = false; }
                 ok = __all_sync(0xffffffffu, ok);
-                if (!SK && heads.q_out != nullptr) {
-                    // the four warps of this half meet at barriers inside the chunks: they go on together or not at all
-                    uint32_t all_ok;
-                    asm volatile("{ .reg .pred p, q; setp.ne.u32 p, %1, 0; bar.red.and.pred q, %2, 128, p; selp.u32 %0, 1, 0, q; }"
-                                 : "=r"(all_ok) : "r"((uint32_t)ok), "r"(2 + col_half) : "memory");
-                    ok = all_ok != 0;
-                }
+                if ((!SK && heads.q_out != nullptr) || reduce_out) ok = half_agrees(ok);
                 if (!ok) continue;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
@@ -1009,6 +1031,8 @@ __global__ void __launch_bounds__(320) gemm_tc_persistent_kernel(const __grid_co
                 if (is_head) asm volatile("st.relaxed.gpu.global.s32 [%0], %1;" ::"l"(parked_flag), "r"(0) : "memory");   // for the next launch
             }
         }
+        // the reductions this thread handed to TMA are done before the kernel ends
+        if (reduce_out && quarter == 0 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -1045,10 +1069,33 @@ static int launch_tc(const CUtensorMap& mw, const CUtensorMap& mx, void* out, in
 // Tiles a launch with `bn` tokens per CTA would have (for the caller's choice of split).
 MB_API int mb_gemm_tc_tiles(int T, int N, int bn) { return ((N + TC_BM - 1) / TC_BM) * ((T + bn - 1) / bn); }
 
+// MARIN_B200_TMA_REDUCE=0 in the environment: the "+=" epilogue of the persistent kernel reads and writes instead.
+static bool tc_reduce_out() {
+    static int state = -1;
+    if (state < 0) {
+        const char* v = getenv("MARIN_B200_TMA_REDUCE");
+        state = (v != nullptr && v[0] == '0') ? 0 : 1;
+    }
+    return state == 1;
+}
+
 template <int BN, int STAGES, bool SK>
 static int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, void* out, int mode, int T, int N, int K, int ctas,
                              int* error_flag, const TcNormOut& norm, const TcRowScale& scale, TcStreamK sk, cudaStream_t s,
                              const TcHeadsOut& heads = TcHeadsOut{}, const float* rope = nullptr) {
+    // "+=" into float32 with nothing riding on it: by TMA reduction, if the rows of out can be a tensor map's
+    CUtensorMap mo = mw;
+    int reduce_out = 0;
+    if (mode == TC_OUT_F32_ACC && norm.weight == nullptr && tc_reduce_out() && N % 4 == 0 && ((uintptr_t)out & 15) == 0) {
+        EncodeTiled enc = encode_tiled();
+        cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)T};
+        cuuint64_t strides[1] = {(cuuint64_t)N * 4};
+        cuuint32_t box[2] = {TC_BM, 16};
+        cuuint32_t elem[2] = {1, 1};
+        if (enc != nullptr && enc(&mo, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, out, dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                  CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS)
+            reduce_out = 1;
+    }
     constexpr int smem = STAGES * TcSmem<BN>::STAGE_BYTES + 1024 + 256;
     static_assert(smem <= 227 * 1024, "the ring does not fit shared memory");
     static bool configured = false;
@@ -1067,7 +1114,7 @@ static int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, void*
         grid = groups * tiles_t;
     }
     return launch_kernel(gemm_tc_persistent_kernel<BN, STAGES, SK>, dim3(grid), dim3(320), smem, s, 0, mw, mx, out, mode, T, N, K,
-                         error_flag, norm, scale, sk, heads, rope);
+                         error_flag, norm, scale, sk, heads, rope, mo, reduce_out);
 }
 
 static int persistent_dispatch(const void* x, const void* w, void* out, int mode, int T, int N, int K, int bn, int ctas,

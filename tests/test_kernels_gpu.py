@@ -92,6 +92,28 @@ def test_gemm_of_a_few_tokens_many_times_back_to_back_gives_the_same_bits(ops, T
     assert bool(same.all()), f"launch {int(torch.nonzero(~same)[0])} of 300 gave other bits than the first"
 
 
+@pytest.mark.parametrize("T,N,K", [(1000, 2560, 512), (2048, 2560, 4096), (777, 3000, 320), (1500, 1981, 256), (1031, 4100, 192)])
+def test_gemm_of_many_tokens_adds_into_float32(ops, T, N, K):
+    """``out += x w^T`` in the persistent kernel (by TMA reduction where the rows of ``out`` can be a tensor map's: N a
+    multiple of 4; by read and write otherwise), with token counts and widths that leave partial tiles, against
+    float64; twice, so that a second launch adds to what the first left."""
+    g = torch.Generator(device=DEV).manual_seed(50)
+    assert ops.many_tokens(T, N)
+    x = torch.randn(T, K, device=DEV, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=DEV, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    base = torch.randn(T, N, device=DEV, generator=g)
+    guard = torch.full((T + 2, N), 7.0, device=DEV)             # rows around the matrix: nothing may be written there
+    out = guard[1:T + 1]
+    out.copy_(base)
+    product = x.double() @ w.double().t()
+    ops.gemm(x, w, out, accumulate=True)
+    torch.testing.assert_close(out.double(), base.double() + product, rtol=1e-5, atol=2e-5)
+    ops.gemm(x, w, out, accumulate=True)
+    torch.testing.assert_close(out.double(), base.double() + 2 * product, rtol=1e-5, atol=4e-5)
+    assert bool((guard[0] == 7.0).all()) and bool((guard[T + 1] == 7.0).all())
+    ops.check_device_errors()
+
+
 def test_gemm_rows_do_not_depend_on_the_batch(ops):
     """A row's result is the same alone and among 200 other rows (float32 path: bit for bit)."""
     g = torch.Generator(device=DEV).manual_seed(4)
